@@ -1,0 +1,300 @@
+"""asca_b200 -- B200 (sm_100a) backend for ASCA's Delta Memory / hash-MoE hot path.
+
+The product is ``libasca_b200.so`` (hand-written CUDA behind the C ABI of
+``include/asca_b200.h``). This package is the thin host side above it:
+
+* :class:`Gpu` mirrors the reference's ``impl Gpu`` (rust/src/cuda/mod.rs): the same method
+  names, argument meaning and error behaviour (an exception carrying the library's message
+  where the reference returns ``Err(String)``), on host (numpy) arrays.
+* :mod:`asca_b200.ops` exposes the device-pointer entry points on torch CUDA tensors, for
+  callers that keep activations resident in HBM.
+
+There is no CPU fallback: if the library is missing or no CUDA device is present, creating
+a :class:`Gpu` raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+import numpy as np
+
+_DIR = Path(__file__).resolve().parent
+LIB_PATH = _DIR / "libasca_b200.so"
+
+F32, BF16 = 0, 1
+NN, TN, NT = 0, 1, 2
+
+_lib = None
+
+
+class AscaError(RuntimeError):
+    """A library call returned a negative ASCA_ERR_* status."""
+
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"asca_b200 error {code}: {msg}")
+        self.code = code
+
+
+def load() -> C.CDLL:
+    """dlopen the in-tree library (built by ``python -m asca_b200.build``). Never falls back."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m asca_b200.build` "
+                "(nvcc, sm_100a). There is no CPU fallback.")
+        _lib = C.CDLL(str(LIB_PATH))
+        _lib.asca_last_error.restype = C.c_char_p
+        _lib.asca_describe.restype = C.c_char_p
+        _lib.asca_version.restype = C.c_char_p
+        _lib.asca_launch_count.restype = C.c_int64
+        _lib.asca_delta_ckpt_floats.restype = C.c_int64
+        _lib.asca_delta_ckpt_floats.argtypes = [C.c_int64] * 5
+    return _lib
+
+
+def _p(a):
+    """Pointer of a numpy array / torch tensor / raw int / None as c_void_p."""
+    if a is None:
+        return C.c_void_p(0)
+    if isinstance(a, int):
+        return C.c_void_p(a)
+    if isinstance(a, np.ndarray):
+        assert a.flags.c_contiguous, "array must be C-contiguous"
+        return C.c_void_p(a.ctypes.data)
+    if hasattr(a, "data_ptr"):
+        assert a.is_contiguous(), "tensor must be contiguous"
+        return C.c_void_p(a.data_ptr())
+    raise TypeError(type(a))
+
+
+def _i64(v):
+    return C.c_int64(int(v))
+
+
+def _f(v):
+    return C.c_float(float(v))
+
+
+def _as_f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+class DeltaDev:
+    """Device-resident q,k,v,alpha,beta + chunk checkpoints between delta_scan and delta_bwd_dev
+    (the reference's DeltaDev, rust/src/cuda/mod.rs:1386-1397)."""
+
+    def __init__(self, gpu, handle, batch, seq, n_heads, dh):
+        self._gpu, self._h = gpu, handle
+        self.batch, self.seq, self.n_heads, self.dh = batch, seq, n_heads, dh
+
+    def download_states(self):
+        """Per-step state history, list of H*B arrays of (seq+1)*dh*dh floats, chain index
+        h*B + b (rust/src/cuda/mod.rs:1473-1480). Recomputed on the device; refused when large."""
+        n = self.n_heads * self.batch
+        out = np.empty((n, (self.seq + 1) * self.dh * self.dh), np.float32)
+        self._gpu._call("asca_delta_dev_download_states", self._gpu._ctx, self._h, _p(out))
+        return [out[i] for i in range(n)]
+
+    def free(self):
+        if self._h is not None:
+            self._gpu._call("asca_delta_dev_free", self._gpu._ctx, self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class MoeDev:
+    """Device-resident xn, weights, pre/hidden and the dispatch between moe_forward_dev and
+    moe_bwd_dev (the reference's MoeDev, rust/src/cuda/mod.rs:1416-1431)."""
+
+    def __init__(self, gpu, handle, t_len, d, d_ff, n_experts):
+        self._gpu, self._h = gpu, handle
+        self.t_len, self.d, self.d_ff, self.n_experts = t_len, d, d_ff, n_experts
+
+    def download_pre_hidden(self):
+        pre = np.empty((self.t_len, self.d_ff), np.float32)
+        hid = np.empty((self.t_len, self.d_ff), np.float32)
+        self._gpu._call("asca_moe_dev_download_pre_hidden", self._gpu._ctx, self._h, _p(pre), _p(hid))
+        return pre, hid
+
+    def free(self):
+        if self._h is not None:
+            self._gpu._call("asca_moe_dev_free", self._gpu._ctx, self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class MoeBwd:
+    """Result of moe_bwd_dev (rust/src/cuda/mod.rs:745-824)."""
+
+    def __init__(self, d_w1, d_b1, d_w2, d_b2, dxn):
+        self.d_w1, self.d_b1, self.d_w2, self.d_b2, self.dxn = d_w1, d_b1, d_w2, d_b2, dxn
+
+
+class Gpu:
+    """One context per GPU; host-array methods named after the reference's ``impl Gpu``."""
+
+    def __init__(self, device: int = 0):
+        self.lib = load()
+        ctx = C.c_void_p()
+        rc = self.lib.asca_ctx_create(C.c_int(device), C.byref(ctx))
+        if rc != 0 or not ctx:
+            raise AscaError(rc, f"cannot create a context on CUDA device {device} (no GPU, or driver missing); "
+                                "there is no CPU fallback")
+        self._ctx = ctx
+        self.device = device
+
+    # ---- plumbing
+    def _call(self, name, *args):
+        rc = getattr(self.lib, name)(*args)
+        if rc != 0:
+            raise AscaError(rc, self.lib.asca_last_error(self._ctx).decode())
+
+    def describe(self) -> str:
+        return self.lib.asca_describe(self._ctx).decode()
+
+    def launch_count(self) -> int:
+        return int(self.lib.asca_launch_count(self._ctx))
+
+    def set_stream(self, cuda_stream: int | None):
+        self._call("asca_ctx_set_stream", self._ctx, C.c_void_p(cuda_stream or 0))
+
+    def use_torch_stream(self):
+        import torch
+
+        self.set_stream(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def sync(self):
+        self._call("asca_ctx_sync", self._ctx)
+
+    def close(self):
+        if self._ctx:
+            self.lib.asca_ctx_destroy(self._ctx)
+            self._ctx = None
+
+    # ---- Gpu::matmul / matmul_ta (rust/src/cuda/mod.rs:286-344)
+    def matmul(self, a, b):
+        a, b = _as_f32(a), _as_f32(b)
+        assert a.shape[1] == b.shape[0], "matmul: inner dims differ"
+        c = np.empty((a.shape[0], b.shape[1]), np.float32)
+        self._call("asca_matmul_host", self._ctx, _p(a), _p(b), _p(c), _i64(a.shape[0]), _i64(a.shape[1]),
+                   _i64(b.shape[1]), C.c_int(NN))
+        return c
+
+    def matmul_ta(self, a, b):
+        a, b = _as_f32(a), _as_f32(b)
+        assert a.shape[0] == b.shape[0], "matmul_ta: row counts differ"
+        c = np.empty((a.shape[1], b.shape[1]), np.float32)
+        self._call("asca_matmul_host", self._ctx, _p(a), _p(b), _p(c), _i64(a.shape[1]), _i64(a.shape[0]),
+                   _i64(b.shape[1]), C.c_int(TN))
+        return c
+
+    def matmul_t(self, a, b):
+        a, b = _as_f32(a), _as_f32(b)
+        assert a.shape[1] == b.shape[1], "matmul_t: inner dims differ"
+        c = np.empty((a.shape[0], b.shape[0]), np.float32)
+        self._call("asca_matmul_host", self._ctx, _p(a), _p(b), _p(c), _i64(a.shape[0]), _i64(a.shape[1]),
+                   _i64(b.shape[0]), C.c_int(NT))
+        return c
+
+    # ---- Gpu::rmsnorm / rmsnorm_bwd (rust/src/cuda/mod.rs:911-939, :1122-1153)
+    def rmsnorm(self, x, eps=1e-6):
+        x = _as_f32(x)
+        y = np.empty_like(x)
+        inv = np.empty(x.shape[0], np.float32)
+        self._call("asca_rmsnorm_fwd_host", self._ctx, _p(x), _p(y), _p(inv), _i64(x.shape[0]), _i64(x.shape[1]), _f(eps))
+        return y, inv
+
+    def rmsnorm_bwd(self, x, dy, eps=1e-6):
+        x, dy = _as_f32(x), _as_f32(dy)
+        dx = np.empty_like(x)
+        self._call("asca_rmsnorm_bwd_host", self._ctx, _p(x), _p(dy), _p(dx), _i64(x.shape[0]), _i64(x.shape[1]), _f(eps))
+        return dx
+
+    # ---- Gpu::gather_rows / scatter_rows (rust/src/cuda/mod.rs:1156-1221)
+    def gather_rows(self, src, idx):
+        src = _as_f32(src)
+        idx = np.ascontiguousarray(idx, dtype=np.int32)
+        dst = np.empty((idx.size, src.shape[1]), np.float32)
+        self._call("asca_gather_rows_host", self._ctx, _p(src), _i64(src.shape[0]), _p(idx), _i64(idx.size),
+                   _i64(src.shape[1]), _p(dst))
+        return dst
+
+    def scatter_rows(self, src, idx, dst):
+        src = _as_f32(src)
+        idx = np.ascontiguousarray(idx, dtype=np.int32)
+        assert dst.dtype == np.float32 and dst.flags.c_contiguous
+        self._call("asca_scatter_rows_host", self._ctx, _p(src), _p(idx), _i64(idx.size), _i64(src.shape[1]), _p(dst),
+                   _i64(dst.shape[0]))
+
+    # ---- Gpu::adamw_update (rust/src/cuda/mod.rs:1057-1120), CPU-path decay
+    def adamw_update(self, val, grad, m, v, lr, beta1, beta2, eps_t, wd):
+        for a in (val, grad, m, v):
+            assert a.dtype == np.float32 and a.flags.c_contiguous
+        self._call("asca_adamw_host", self._ctx, _p(val), _p(grad), _p(m), _p(v), _i64(val.size), _f(lr), _f(beta1),
+                   _f(beta2), _f(eps_t), _f(wd))
+
+    # ---- Gpu::delta_scan / delta_bwd_dev (rust/src/cuda/mod.rs:1253-1382)
+    def delta_scan(self, q, k, v, alpha, beta, batch, seq, n_heads, dh, keep=True):
+        q, k, v, alpha, beta = map(_as_f32, (q, k, v, alpha, beta))
+        assert q.shape == (batch * seq, n_heads * dh), "delta_scan: q rows must be batch*seq"
+        o = np.empty_like(q)
+        h = C.c_void_p()
+        self._call("asca_delta_scan_host", self._ctx, _p(q), _p(k), _p(v), _p(alpha), _p(beta), _i64(batch), _i64(seq),
+                   _i64(n_heads), _i64(dh), _p(o), C.byref(h) if keep else None)
+        return o, (DeltaDev(self, h, batch, seq, n_heads, dh) if keep else None)
+
+    def delta_bwd_dev(self, dev: DeltaDev, d_o, qnorm, knorm):
+        d_o, qnorm, knorm = map(_as_f32, (d_o, qnorm, knorm))
+        n, d = dev.batch * dev.seq, dev.n_heads * dev.dh
+        assert d_o.shape == (n, d)
+        d_qkv = np.empty((n, 3 * d), np.float32)
+        d_gate = np.empty((n, 2 * dev.n_heads), np.float32)
+        self._call("asca_delta_bwd_dev_host", self._ctx, dev._h, _p(d_o), _p(qnorm), _p(knorm), _p(d_qkv), _p(d_gate))
+        return d_qkv, d_gate
+
+    # ---- hash-MoE: dispatch + Gpu::moe_forward_dev / moe_bwd_dev (rust/src/cuda/mod.rs:523-824)
+    def moe_dispatch(self, ids, n_experts):
+        ids = np.ascontiguousarray(ids, dtype=np.uint32)
+        perm = np.empty(ids.size, np.int32)
+        offsets = np.empty(n_experts + 1, np.int32)
+        route = np.empty(ids.size, np.int32)
+        self._call("asca_moe_dispatch_host", self._ctx, _p(ids), _i64(ids.size), _i64(n_experts), _p(perm), _p(offsets),
+                   _p(route))
+        return perm, offsets, route
+
+    def moe_forward_dev(self, xn, w1, b1, w2, b2, ids, d_ff, keep=True):
+        """`ids` stands where the reference passes host-built `buckets`: the same buckets are
+        rebuilt on the device by the counting-sort dispatch."""
+        xn, w1, b1, w2, b2 = map(_as_f32, (xn, w1, b1, w2, b2))
+        ids = np.ascontiguousarray(ids, dtype=np.uint32)
+        n, d = xn.shape
+        e = w1.shape[1] // d_ff
+        out = np.empty((n, d), np.float32)
+        h = C.c_void_p()
+        self._call("asca_moe_forward_dev_host", self._ctx, _p(xn), _p(w1), _p(b1), _p(w2), _p(b2), _p(ids), _i64(n),
+                   _i64(d), _i64(d_ff), _i64(e), _p(out), C.byref(h) if keep else None)
+        return out, (MoeDev(self, h, n, d, d_ff, e) if keep else None)
+
+    def moe_bwd_dev(self, dev: MoeDev, dout):
+        dout = _as_f32(dout)
+        n, d, f, e = dev.t_len, dev.d, dev.d_ff, dev.n_experts
+        r = MoeBwd(np.empty((d, e * f), np.float32), np.empty(e * f, np.float32), np.empty((e * f, d), np.float32),
+                   np.empty(d, np.float32), np.empty((n, d), np.float32))
+        self._call("asca_moe_bwd_dev_host", self._ctx, dev._h, _p(dout), _p(r.d_w1), _p(r.d_b1), _p(r.d_w2), _p(r.d_b2),
+                   _p(r.dxn))
+        return r
+
+
+__all__ = ["Gpu", "DeltaDev", "MoeDev", "MoeBwd", "AscaError", "load", "LIB_PATH", "F32", "BF16", "NN", "TN", "NT"]

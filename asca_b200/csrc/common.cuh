@@ -1,0 +1,100 @@
+// Shared internals of libasca_b200: the context object, error plumbing, launch accounting.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "../../include/asca_b200.h"
+
+struct asca_ctx {
+    int device = 0;
+    cudaStream_t own_stream = nullptr;
+    cudaStream_t stream = nullptr;
+    int sm_count = 0;
+    size_t smem_optin = 0;
+    std::string err;
+    std::string desc;
+    int64_t launches = 0;
+    // size-class cache of freed blocks (the role of the reference's DevBuf pool,
+    // rust/src/cuda/mod.rs:104-174): key = rounded size.
+    std::multimap<size_t, void*> pool;
+    std::map<void*, size_t> live;
+    // lazily grown scratch owned by the context (partials, tile tables, error words)
+    void* ws = nullptr;
+    size_t ws_bytes = 0;
+    int* err_word = nullptr;  // device int the kernels with bounded waits write to
+};
+
+int asca_fail(asca_ctx* ctx, int code, const char* fmt, ...);
+// Returns scratch of at least `bytes` (256-byte aligned); contents are undefined.
+int asca_workspace(asca_ctx* ctx, size_t bytes, void** out);
+
+#define ASCA_CUDA(ctx, call)                                                                  \
+    do {                                                                                      \
+        cudaError_t e__ = (call);                                                             \
+        if (e__ != cudaSuccess)                                                               \
+            return asca_fail((ctx), e__ == cudaErrorMemoryAllocation ? ASCA_ERR_OOM : ASCA_ERR_CUDA, \
+                             "CUDA error %d (%s) at %s:%d", (int)e__, cudaGetErrorString(e__),\
+                             __FILE__, __LINE__);                                             \
+    } while (0)
+
+#define ASCA_CHECK_LAUNCH(ctx)                                                                \
+    do {                                                                                      \
+        (ctx)->launches++;                                                                    \
+        ASCA_CUDA((ctx), cudaGetLastError());                                                 \
+    } while (0)
+
+#define ASCA_REQUIRE(ctx, cond, ...)                                                          \
+    do {                                                                                      \
+        if (!(cond)) return asca_fail((ctx), ASCA_ERR_ARG, __VA_ARGS__);                      \
+    } while (0)
+
+#define ASCA_TRY(expr)                                                                        \
+    do {                                                                                      \
+        int rc__ = (expr);                                                                    \
+        if (rc__ != ASCA_OK) return rc__;                                                     \
+    } while (0)
+
+static inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// ---- small device helpers shared by several kernels
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+// Deterministic block-wide sum (fixed tree), result broadcast to all threads.
+// `red` must hold at least 33 floats. blockDim.x must be a multiple of 32.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) red[w] = v;
+    __syncthreads();
+    if (w == 0) {
+        float t = lane < nw ? red[lane] : 0.0f;
+        t = warp_sum(t);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16(v); }

@@ -1,0 +1,219 @@
+// Hash-MoE expert FFN: grouped forward and backward products over the dispatch permutation,
+// and the per-token decode step. Math of rust/src/model.rs:237-293 (forward), :417-495
+// (backward), :309-337 (step); replaces Gpu::moe_forward_dev / moe_bwd_dev
+// (rust/src/cuda/mod.rs:523-607, :745-824), which loop over experts with 7 + 10 launches and
+// fresh allocations per expert. Here every product is ONE grouped launch over all experts:
+// the row gather is fused into the operand load, bias + SiLU (forward) and SiLU' (backward)
+// into the epilogue, and the un-permute scatter into the output store.
+#include "gemm_simt.cuh"
+
+namespace {
+
+// Column sums of a (rows x cols) f32 matrix, optionally per expert segment of the permuted
+// order and optionally through a row map. Deterministic: each CTA owns 32 columns of one
+// segment and reduces rows in a fixed order. out[g*out_gstride + c].
+__global__ void __launch_bounds__(256) colsum_kernel(const float* __restrict__ src, int64_t ld,
+                                                     const int32_t* __restrict__ row_idx,
+                                                     const int32_t* __restrict__ offsets, int64_t rows_total,
+                                                     int cols, float* __restrict__ out, int64_t out_gstride) {
+    __shared__ float part[8][33];
+    const int g = blockIdx.y;
+    const int64_t lo = offsets ? offsets[g] : 0, hi = offsets ? offsets[g + 1] : rows_total;
+    const int c = blockIdx.x * 32 + (threadIdx.x & 31);
+    const int w = threadIdx.x >> 5;
+    float acc = 0.0f;
+    if (c < cols)
+        for (int64_t r = lo + w; r < hi; r += 8) {
+            int64_t mr = row_idx ? (int64_t)row_idx[r] : r;
+            acc += src[mr * ld + c];
+        }
+    part[w][threadIdx.x & 31] = acc;
+    __syncthreads();
+    if (w == 0 && c < cols) {
+        float t = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) t += part[i][threadIdx.x];
+        out[(int64_t)g * out_gstride + c] = t;
+    }
+}
+
+// Decode step: one CTA per token. rmsnorm -> pre = b1[e] + xn W1[:, e] -> silu -> out = b2 + h W2[e].
+template <typename T>
+__global__ void __launch_bounds__(256) moe_step_kernel(const float* __restrict__ x, const uint32_t* __restrict__ ids,
+                                                       const T* __restrict__ w1, const float* __restrict__ b1,
+                                                       const T* __restrict__ w2, const float* __restrict__ b2, int d,
+                                                       int F, int E, float* __restrict__ out) {
+    extern __shared__ float sh[];  // xn[d] | hid[F] | red[33]
+    float* xn = sh;
+    float* hid = sh + d;
+    float* red = hid + F;
+    const int s = blockIdx.x;
+    uint32_t h = ids[s] * 0x9E3779B1u;
+    h ^= h >> 15;
+    h *= 0x85EBCA6Bu;
+    h ^= h >> 13;
+    const int e = (int)(h % (uint32_t)E);
+    const float* xr = x + (int64_t)s * d;
+    float acc = 0.0f;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) acc += xr[c] * xr[c];
+    const float ss = block_sum(acc, red);
+    const float inv = 1.0f / sqrtf(ss / (float)d + 1e-6f);
+    for (int c = threadIdx.x; c < d; c += blockDim.x) xn[c] = xr[c] * inv;
+    __syncthreads();
+    const int64_t EF = (int64_t)E * F;
+    for (int j = threadIdx.x; j < F; j += blockDim.x) {  // coalesced over j
+        float a = b1[(int64_t)e * F + j];
+        const T* col = w1 + (int64_t)e * F + j;
+        for (int c = 0; c < d; ++c) a = fmaf(xn[c], to_f32<T>(col[(int64_t)c * EF]), a);
+        hid[j] = a / (1.0f + expf(-a));
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {  // coalesced over c
+        float a = b2[c];
+        const T* col = w2 + (int64_t)e * F * d + c;
+        for (int j = 0; j < F; ++j) a = fmaf(hid[j], to_f32<T>(col[(int64_t)j * d]), a);
+        out[(int64_t)s * d + c] = a;
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+int asca_moe_fwd(asca_ctx* ctx, const void* xn, const void* w1, const float* b1, const void* w2, const float* b2,
+                 const int32_t* perm, const int32_t* offsets, int64_t N, int64_t d, int64_t F, int64_t E, int dtype,
+                 float* out, float* pre_p, void* hid_p) {
+    if (!ctx) return ASCA_ERR_ARG;
+    ASCA_REQUIRE(ctx, xn && w1 && b1 && w2 && b2 && perm && offsets && out && pre_p && hid_p, "moe_fwd: null pointer");
+    ASCA_REQUIRE(ctx, N >= 0 && d > 0 && F > 0 && E > 0 && N < (1ll << 31) && E * F < (1ll << 31), "moe_fwd: bad shape");
+    ASCA_REQUIRE(ctx, dtype == ASCA_F32 || dtype == ASCA_BF16, "moe_fwd: unknown dtype");
+    if (N == 0) return ASCA_OK;
+    const int bf = dtype == ASCA_BF16;
+    // pre_p[r,:] = xn[perm[r],:] W1[:, eF:(e+1)F] + b1[e];  hid_p = silu(pre_p)
+    gemm::Params p{};
+    p.A = xn; p.lda = d; p.a_idx = perm;
+    p.B = w1; p.ldb = E * F; p.b_gstride = F;
+    p.C = pre_p; p.ldc = F;
+    p.M = 0; p.N = (int)F; p.K = (int)d;
+    p.bias = b1; p.bias_gstride = F;
+    p.offsets = offsets; p.n_groups = (int)E; p.group_dim = gemm::GROUP_M;
+    p.epi = gemm::EPI_SILU; p.C2 = hid_p; p.ldc2 = F;
+    if (bf) ASCA_CUDA(ctx, gemm::launch<__nv_bfloat16>(p, ASCA_NN, 1, 1, N, ctx->stream));
+    else ASCA_CUDA(ctx, gemm::launch<float>(p, ASCA_NN, 0, 0, N, ctx->stream));
+    ctx->launches++;
+    // out[perm[r],:] = hid_p[r,:] W2[eF:(e+1)F,:] + b2
+    gemm::Params q{};
+    q.A = hid_p; q.lda = F;
+    q.B = w2; q.ldb = d; q.b_gstride = F * d;
+    q.C = out; q.ldc = d; q.c_idx = perm;
+    q.M = 0; q.N = (int)d; q.K = (int)F;
+    q.bias = b2; q.bias_gstride = 0;
+    q.offsets = offsets; q.n_groups = (int)E; q.group_dim = gemm::GROUP_M;
+    q.epi = gemm::EPI_NONE;
+    ASCA_CUDA(ctx, gemm::launch<float>(q, ASCA_NN, bf, bf, N, ctx->stream));
+    ctx->launches++;
+    return ASCA_OK;
+}
+
+int asca_moe_bwd(asca_ctx* ctx, const void* xn, const void* w1, const void* w2, const float* pre_p, const void* hid_p,
+                 const float* dout, const int32_t* perm, const int32_t* offsets, int64_t N, int64_t d, int64_t F,
+                 int64_t E, int dtype, float* d_w1, float* d_b1, float* d_w2, float* d_b2, float* dxn) {
+    if (!ctx) return ASCA_ERR_ARG;
+    ASCA_REQUIRE(ctx, xn && w1 && w2 && pre_p && hid_p && dout && perm && offsets && d_w1 && d_b1 && d_w2 && d_b2 && dxn,
+                 "moe_bwd: null pointer");
+    ASCA_REQUIRE(ctx, N >= 0 && d > 0 && F > 0 && E > 0 && N < (1ll << 31) && E * F < (1ll << 31), "moe_bwd: bad shape");
+    ASCA_REQUIRE(ctx, dtype == ASCA_F32 || dtype == ASCA_BF16, "moe_bwd: unknown dtype");
+    const int bf = dtype == ASCA_BF16;
+    cudaStream_t s = ctx->stream;
+    if (N == 0) {
+        ASCA_CUDA(ctx, cudaMemsetAsync(d_w1, 0, (size_t)(d * E * F) * 4, s));
+        ASCA_CUDA(ctx, cudaMemsetAsync(d_w2, 0, (size_t)(d * E * F) * 4, s));
+        ASCA_CUDA(ctx, cudaMemsetAsync(d_b1, 0, (size_t)(E * F) * 4, s));
+        ASCA_CUDA(ctx, cudaMemsetAsync(d_b2, 0, (size_t)d * 4, s));
+        return ASCA_OK;
+    }
+    // scratch: dpre_p (N x F) f32, in the permuted order
+    void* ws;
+    ASCA_TRY(asca_workspace(ctx, (size_t)N * F * 4 + 256, &ws));
+    float* dpre_p = (float*)ws;
+
+    // d_b2[c] = sum over all tokens of dout[t,c]
+    colsum_kernel<<<dim3((unsigned)ceil_div64(d, 32), 1), 256, 0, s>>>(dout, d, nullptr, nullptr, N, (int)d, d_b2, 0);
+    ASCA_CHECK_LAUNCH(ctx);
+    // d_w2[eF+j, c] = sum_r hid_p[r,j] dout[perm[r],c]      (TN, K = rows of expert e)
+    {
+        gemm::Params p{};
+        p.A = hid_p; p.lda = F;
+        p.B = dout; p.ldb = d; p.b_idx = perm;
+        p.C = d_w2; p.ldc = d; p.c_gstride = F * d;
+        p.M = (int)F; p.N = (int)d; p.K = 0;
+        p.offsets = offsets; p.n_groups = (int)E; p.group_dim = gemm::GROUP_K;
+        ASCA_CUDA(ctx, gemm::launch<float>(p, ASCA_TN, bf, 0, N, s));
+        ctx->launches++;
+    }
+    // dpre_p[r,j] = (sum_c dout[perm[r],c] W2[eF+j,c]) * silu'(pre_p[r,j])   (NT)
+    {
+        gemm::Params p{};
+        p.A = dout; p.lda = d; p.a_idx = perm;
+        p.B = w2; p.ldb = d; p.b_gstride = F * d;
+        p.C = dpre_p; p.ldc = F;
+        p.M = 0; p.N = (int)F; p.K = (int)d;
+        p.offsets = offsets; p.n_groups = (int)E; p.group_dim = gemm::GROUP_M;
+        p.epi = gemm::EPI_SILU_BWD; p.aux = pre_p; p.ldaux = F;
+        ASCA_CUDA(ctx, gemm::launch<float>(p, ASCA_NT, 0, bf, N, s));
+        ctx->launches++;
+    }
+    // d_b1[eF+j] = sum over expert e's rows of dpre_p[r,j]
+    colsum_kernel<<<dim3((unsigned)ceil_div64(F, 32), (unsigned)E), 256, 0, s>>>(dpre_p, F, nullptr, offsets, N, (int)F,
+                                                                               d_b1, F);
+    ASCA_CHECK_LAUNCH(ctx);
+    // d_w1[c, eF+j] = sum_r xn[perm[r],c] dpre_p[r,j]        (TN, K = rows of expert e)
+    {
+        gemm::Params p{};
+        p.A = xn; p.lda = d; p.a_idx = perm;
+        p.B = dpre_p; p.ldb = F;
+        p.C = d_w1; p.ldc = E * F; p.c_gstride = F;
+        p.M = (int)d; p.N = (int)F; p.K = 0;
+        p.offsets = offsets; p.n_groups = (int)E; p.group_dim = gemm::GROUP_K;
+        ASCA_CUDA(ctx, gemm::launch<float>(p, ASCA_TN, bf, 0, N, s));
+        ctx->launches++;
+    }
+    // dxn[perm[r], c] = sum_j dpre_p[r,j] W1[c, eF+j]          (NT)
+    {
+        gemm::Params p{};
+        p.A = dpre_p; p.lda = F;
+        p.B = w1; p.ldb = E * F; p.b_gstride = F;
+        p.C = dxn; p.ldc = d; p.c_idx = perm;
+        p.M = 0; p.N = (int)d; p.K = (int)F;
+        p.offsets = offsets; p.n_groups = (int)E; p.group_dim = gemm::GROUP_M;
+        ASCA_CUDA(ctx, gemm::launch<float>(p, ASCA_NT, 0, bf, N, s));
+        ctx->launches++;
+    }
+    return ASCA_OK;
+}
+
+int asca_moe_step(asca_ctx* ctx, const float* x, const uint32_t* ids, const void* w1, const float* b1, const void* w2,
+                  const float* b2, int64_t n_streams, int64_t d, int64_t F, int64_t E, int dtype, float* out) {
+    if (!ctx) return ASCA_ERR_ARG;
+    ASCA_REQUIRE(ctx, x && ids && w1 && b1 && w2 && b2 && out && n_streams >= 0 && d > 0 && F > 0 && E > 0,
+                 "moe_step: bad arguments");
+    ASCA_REQUIRE(ctx, dtype == ASCA_F32 || dtype == ASCA_BF16, "moe_step: unknown dtype");
+    if (n_streams == 0) return ASCA_OK;
+    const size_t smem = (size_t)(d + F + 33) * 4;
+    ASCA_REQUIRE(ctx, smem <= 200 * 1024, "moe_step: d + F too large for one CTA");
+    if (dtype == ASCA_BF16) {
+        auto kern = moe_step_kernel<__nv_bfloat16>;
+        if (smem > 48 * 1024) ASCA_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        kern<<<(unsigned)n_streams, 256, smem, ctx->stream>>>(x, ids, (const __nv_bfloat16*)w1, b1,
+                                                              (const __nv_bfloat16*)w2, b2, (int)d, (int)F, (int)E, out);
+    } else {
+        auto kern = moe_step_kernel<float>;
+        if (smem > 48 * 1024) ASCA_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        kern<<<(unsigned)n_streams, 256, smem, ctx->stream>>>(x, ids, (const float*)w1, b1, (const float*)w2, b2, (int)d,
+                                                              (int)F, (int)E, out);
+    }
+    ASCA_CHECK_LAUNCH(ctx);
+    return ASCA_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,314 @@
+#!/usr/bin/env python
+"""Benchmark of the Delta Memory hot path: one step = the gated delta-rule forward (chunk
+checkpoints every 64 tokens) plus the BPTT backward over one batch of synthetic input.
+
+Workload (the isolated delta op of the baseline configuration list): B=8 sequences, H=16
+heads, T=4096 tokens, dh=128, q/k L2-normalised N(0,1), v ~ N(0,1), alpha = sigmoid(N(2,.5)),
+beta = sigmoid(N(0,1)), dO ~ N(0,1); seeded synthetic data.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--dtype f32|bf16] [--impl ours|reference]
+
+Under torchrun every rank owns its own batch of B sequences (weak scaling, no collective on the
+data path: chains are independent per (sequence, head)). Timing: CUDA events on the launching
+stream, barrier + synchronize on both sides, max over ranks. The inputs (4 x 268 MB in f32)
+are larger than the 126 MB L2, so no flush is needed between iterations.
+
+`--impl reference` times the reference's own CPU algorithm for the same path (its Rust crate
+cannot be built here, so this is the C++ restatement under oracle/) on the host cores, on a
+bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+B, H, T, DH, CHUNK = 8, 16, 4096, 128, 64
+METRIC = "delta fwd+bwd tok/s"
+WORKLOAD = f"isolated gated delta-rule op fwd+BPTT: B{B} H{H} T{T} dh{DH} chunk{CHUNK} per GPU"
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        sm, mx, reasons = [], None, set()
+        for r in self.rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1]))
+                mx = float(r[2])
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def make_inputs(seed: int, b: int, t: int, h: int, dh: int):
+    """Seeded synthetic inputs with the workload's distributions (numpy, host)."""
+    rs = np.random.RandomState(seed)
+    n, d = b * t, h * dh
+    q = rs.standard_normal((n, h, dh)).astype(np.float32)
+    k = rs.standard_normal((n, h, dh)).astype(np.float32)
+    qn = np.linalg.norm(q, axis=-1).astype(np.float32)
+    kn = np.linalg.norm(k, axis=-1).astype(np.float32)
+    q = (q / qn[..., None]).reshape(n, d)
+    k = (k / kn[..., None]).reshape(n, d)
+    v = rs.standard_normal((n, d)).astype(np.float32)
+    d_o = rs.standard_normal((n, d)).astype(np.float32)
+    alpha = (1 / (1 + np.exp(-(2 + 0.5 * rs.standard_normal((n, h)))))).astype(np.float32)
+    beta = (1 / (1 + np.exp(-rs.standard_normal((n, h))))).astype(np.float32)
+    return q, k, v, alpha, beta, qn, kn, d_o
+
+
+# ------------------------------------------------------------------ reference arm (CPU)
+def cpu_sample(threads: int):
+    """Bounded sample of the same workload: T tokens of dh=128 chains, one chain per host thread
+    (the reference's BPTT partitioning, rust/src/delta.rs:461-475), full sequence length cut to
+    keep the run at 10-30 s. Threads are capped at 64: every running chain holds its own
+    (T+1)*dh*dh state history (268 MB at T=4096)."""
+    import oracle
+
+    oracle.build()
+    t_s = T
+    h_s = max(threads, 1)
+    arrs = make_inputs(1, 2, t_s, h_s, DH)
+    return oracle, arrs, (2, t_s, h_s, DH)
+
+
+def time_cpu(steps: int, warmup: int):
+    threads = min(os.cpu_count() or 1, 64)
+    oracle, arrs, (b, t, h, dh) = cpu_sample(threads)
+    q, k, v, alpha, beta, qn, kn, d_o = arrs
+
+    def step():
+        oracle.delta_scan(q, k, v, alpha, beta, b, t, h, dh)
+        oracle.delta_bptt(q, k, v, alpha, beta, qn, kn, d_o, b, t, h, dh, max_workers=threads)
+
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / steps
+    chain_steps = b * t * h
+    tok_s = chain_steps / H / dt  # a workload token carries H=16 heads
+    sample = (f"{b * h} chains x {t} tokens, dh={dh}, scan + BPTT with per-chain state history, one chain per thread; "
+              f"tok/s = chain-steps/s / {H} heads")
+    return tok_s, dt * 1e3, threads, sample
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps, warmup = max(args.steps, 1), max(args.warmup, 0)
+    steps = min(steps, 5)
+    tok_s, ms, threads, sample = time_cpu(steps, min(warmup, 1))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tok_s, "unit": "tok/s", "n_gpus": args.gpus, "steps": steps,
+        "warmup": min(warmup, 1), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "l2": "n/a (CPU)"},
+        "cpu_baseline": {"value": tok_s, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": tok_s, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------ our arm (GPU)
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    import asca_b200
+    from asca_b200 import ops
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the hot path has no CPU fallback")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    gpu = asca_b200.Gpu(local)
+    gpu.use_torch_stream()
+    dev = torch.device("cuda", local)
+    bf16 = args.dtype == "bf16"
+    b, t, h, dh = args.batch, args.seq, H, DH
+
+    host = make_inputs(1234 + rank, b, t, h, dh)
+    pin = [torch.from_numpy(a).pin_memory() for a in host]
+    q, k, v, alpha, beta, qn, kn, d_o = (x.to(dev) for x in pin)
+    if bf16:
+        q, k, v, d_o = (x.bfloat16() for x in (q, k, v, d_o))
+    n, d = b * t, h * dh
+    f32 = dict(dtype=torch.float32, device=dev)
+    o = torch.empty_like(q)
+    ckpt = torch.empty(ops.delta_ckpt_floats(gpu, b, t, h, dh, CHUNK), **f32)
+    d_qkv = torch.empty((n, 3 * d), **f32)
+    d_gate = torch.empty((n, 2 * h), **f32)
+
+    def step(ev=None):
+        if ev:
+            ev[0].record()
+        ops.delta_fwd(gpu, q, k, v, alpha, beta, b, t, h, dh, chunk=CHUNK, out=o, ckpt=ckpt)
+        if ev:
+            ev[1].record()
+        ops.delta_bwd(gpu, q, k, v, alpha, beta, qn, kn, d_o, ckpt, b, t, h, dh, chunk=CHUNK, d_qkv=d_qkv,
+                      d_gate=d_gate)
+        if ev:
+            ev[2].record()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = gpu.launch_count()
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        step(evs[i])
+    e1.record()
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    launches = gpu.launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    fwd_ms = float(np.mean([e[0].elapsed_time(e[1]) for e in evs]))
+    bwd_ms = float(np.mean([e[1].elapsed_time(e[2]) for e in evs]))
+    if world > 1:
+        tt = torch.tensor([ms_total], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms_total = float(tt.item())
+    ms_step = ms_total / args.steps
+    tok_s = world * b * t / (ms_step * 1e-3)
+
+    # ---- end to end through the host-pointer API (pinned host buffers in, host results out)
+    e2e_steps = max(1, min(args.steps, 3))
+    hq, hk, hv, ha, hb, hqn, hkn, hdo = (x.numpy() for x in pin)
+    for _ in range(1):
+        o_h, dd = gpu.delta_scan(hq, hk, hv, ha, hb, b, t, h, dh)
+        gpu.delta_bwd_dev(dd, hdo, hqn, hkn)
+        dd.free()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        o_h, dd = gpu.delta_scan(hq, hk, hv, ha, hb, b, t, h, dh)
+        dqkv_h, dgate_h = gpu.delta_bwd_dev(dd, hdo, hqn, hkn)
+        dd.free()
+    barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+    if world > 1:
+        tt = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        e2e_ms = float(tt.item())
+    h2d = sum(a.nbytes for a in (hq, hk, hv, ha, hb, hdo, hqn, hkn))
+    d2h = o_h.nbytes + dqkv_h.nbytes + dgate_h.nbytes
+
+    if rank == 0:
+        peak, which = measured_peaks()
+        s = 2 if bf16 else 4
+        bwd_bytes = 7 * n * d * s + 6 * n * h * 4       # q,k,v,dO in; dq,dk,dv out (+ gates)
+        fwd_bytes = 4 * n * d * s + 2 * n * h * 4
+        achieved = bwd_bytes / (bwd_ms * 1e-3) / 1e9
+        cpu_tok, cpu_ms, cores, sample = time_cpu(1, 1) if world == 1 and not args.no_cpu else (None, None, 0, "skipped")
+        line = {
+            "metric": METRIC, "value": tok_s, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "io_dtype": args.dtype, "data": "synthetic",
+            "config": {"workload": WORKLOAD if (b, t) == (B, T) else f"delta fwd+BPTT B{b} H{h} T{t} dh{dh} chunk{CHUNK}",
+                       "l2": "inputs larger than L2 (no flush)", "parallelism": f"dp{world} by sequence, no collective"},
+            "kernels_ms": {"delta_fwd": fwd_ms, "delta_bwd": bwd_ms},
+            "roofline": {"kernel": "delta_bwd_kernel", "bound": "hbm", "achieved": achieved, "peak": peak,
+                         "unit": "GB/s", "frac": achieved / peak, "peak_source": which, "traffic": None,
+                         "algorithmic_bytes": bwd_bytes,
+                         "fwd": {"achieved": fwd_bytes / (fwd_ms * 1e-3) / 1e9, "algorithmic_bytes": fwd_bytes}},
+            "cpu_baseline": {"value": cpu_tok, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": world * b * t / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+            "gpu_launches": launches,
+            "clocks": clocks,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--dtype", default="f32", choices=["f32", "bf16"])
+    ap.add_argument("--batch", type=int, default=B)
+    ap.add_argument("--seq", type=int, default=T)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        args.warmup = max(args.warmup, 3)
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

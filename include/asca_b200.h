@@ -1,0 +1,236 @@
+/* asca_b200 -- C ABI of the B200 (sm_100a) backend for ASCA's Delta Memory / hash-MoE path.
+ *
+ * This header is the drop-in boundary: each entry point replaces one method of the
+ * reference's `impl Gpu` (rust/src/cuda/mod.rs) or one kernel of rust/kernels/asca.cu, and is
+ * what a Rust `extern "C"` block (or any FFI) binds. Plain pointers and sizes only.
+ *
+ * Conventions
+ *  - Every function returns 0 (ASCA_OK) or a negative ASCA_ERR_* code; the message is kept
+ *    per context and read with asca_last_error(). Nothing throws across the boundary and
+ *    nothing falls back to the CPU: if the device path cannot run, the call fails.
+ *  - One asca_ctx per GPU. A context is not thread-safe; different contexts may be used from
+ *    different threads. All work is enqueued on the context's stream (asca_ctx_set_stream).
+ *  - Functions without the `_host` suffix take DEVICE pointers and are asynchronous with
+ *    respect to the host. `_host` variants take HOST pointers, copy in, run the same
+ *    kernels, copy out and synchronise -- the semantics of today's `Gpu::*` methods.
+ *  - Matrices are row-major. f32 unless a `dtype` argument says otherwise; ASCA_BF16 means
+ *    the activation/weight operands are bfloat16 while recurrent state, gates, accumulators
+ *    and gradients of parameters stay f32.
+ *  - Token rows are B sequences of T tokens stacked: row = b*T + t (rust/src/delta.rs:118-127).
+ *    Head h owns columns [h*dh, (h+1)*dh). State S[a][i] is row-major a*dh + i (a = key
+ *    index, i = value index), one dh x dh f32 matrix per (sequence, head).
+ */
+#ifndef ASCA_B200_H
+#define ASCA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct asca_ctx asca_ctx;
+
+enum {
+    ASCA_OK = 0,
+    ASCA_ERR_ARG = -1,         /* bad shape / null pointer / unsupported combination */
+    ASCA_ERR_CUDA = -2,        /* a CUDA runtime or driver call failed */
+    ASCA_ERR_OOM = -3,         /* device allocation failed */
+    ASCA_ERR_UNSUPPORTED = -4, /* valid request the build does not cover (e.g. dh) */
+    ASCA_ERR_DEVICE = -5       /* a kernel reported an error word (bounded wait ran out) */
+};
+enum { ASCA_F32 = 0, ASCA_BF16 = 1 };
+enum { ASCA_NN = 0, ASCA_TN = 1, ASCA_NT = 2 };
+
+/* ------------------------------------------------------------------ context
+ * Replaces the lazily created singleton `Gpu` (rust/src/cuda/mod.rs:177-237, :1488-1496). */
+int asca_ctx_create(int device, asca_ctx** out);
+int asca_ctx_destroy(asca_ctx* ctx);
+/* Use an existing cudaStream_t (e.g. the caller framework's current stream); NULL = the
+ * context's own stream. */
+int asca_ctx_set_stream(asca_ctx* ctx, void* cuda_stream);
+int asca_ctx_sync(asca_ctx* ctx);
+const char* asca_last_error(const asca_ctx* ctx);
+/* One-line description: device name, SM count, memory (rust/src/cuda/mod.rs:1566-1579). */
+const char* asca_describe(asca_ctx* ctx);
+/* Kernel launches issued through this context since creation (rust/src/cuda/mod.rs:25-33). */
+int64_t asca_launch_count(const asca_ctx* ctx);
+/* Library version string and the arch it was compiled for ("sm_100a"). */
+const char* asca_version(void);
+
+/* Device memory for callers that have no allocator of their own (the reference's DevBuf,
+ * rust/src/cuda/mod.rs:104-174). Freed blocks are cached per size class. */
+int asca_malloc(asca_ctx* ctx, size_t bytes, void** dptr);
+int asca_free(asca_ctx* ctx, void* dptr);
+int asca_memcpy_h2d(asca_ctx* ctx, void* dst, const void* src, size_t bytes);
+int asca_memcpy_d2h(asca_ctx* ctx, void* dst, const void* src, size_t bytes);
+int asca_memset(asca_ctx* ctx, void* dst, int byte, size_t bytes);
+
+/* ------------------------------------------------------------------ GEMM (G1)
+ * Gpu::matmul (rust/src/cuda/mod.rs:286-313), Gpu::matmul_ta (:316-344) and the NT form the
+ * CPU engine has as Mat::matmul_t (rust/src/tensor.rs:180-201).
+ *   ASCA_NN: C[M,N] = A[M,K] B[K,N];  ASCA_TN: C[M,N] = A[K,M]^T B[K,N];
+ *   ASCA_NT: C[M,N] = A[M,K] B[N,K]^T.
+ * asca_gemm adds leading dimensions, an optional per-column bias (C += bias[n]) and
+ * accumulate (C += result) -- the fused forms of add_row_bias and of `grad.axpy(1, dW)`. */
+int asca_matmul(asca_ctx* ctx, const void* A, const void* B, void* C, int64_t M, int64_t K,
+                int64_t N, int mode, int dtype);
+int asca_gemm(asca_ctx* ctx, int mode, int64_t M, int64_t N, int64_t K, const void* A,
+              int64_t lda, const void* B, int64_t ldb, void* C, int64_t ldc, const float* bias,
+              int accumulate, int dtype);
+int asca_matmul_host(asca_ctx* ctx, const float* A, const float* B, float* C, int64_t M,
+                     int64_t K, int64_t N, int mode);
+
+/* ------------------------------------------------------------------ RMSNorm (N1)
+ * Gpu::rmsnorm (rust/src/cuda/mod.rs:911-939) / Gpu::rmsnorm_bwd (:1122-1153); math of
+ * rust/src/tensor.rs:251-297 (no gain). inv (rows) may be NULL. */
+int asca_rmsnorm_fwd(asca_ctx* ctx, const float* x, float* y, float* inv, int64_t rows,
+                     int64_t cols, float eps);
+int asca_rmsnorm_bwd(asca_ctx* ctx, const float* x, const float* dy, float* dx, int64_t rows,
+                     int64_t cols, float eps);
+int asca_rmsnorm_fwd_host(asca_ctx* ctx, const float* x, float* y, float* inv, int64_t rows,
+                          int64_t cols, float eps);
+int asca_rmsnorm_bwd_host(asca_ctx* ctx, const float* x, const float* dy, float* dx,
+                          int64_t rows, int64_t cols, float eps);
+/* Fused residual + norm: x_mid = x + y (written to x_mid) and xn = rmsnorm(x_mid); the pair
+ * rust/src/model.rs:666-667 + :200 computes. xn may be NULL (residual only). */
+int asca_residual_rmsnorm(asca_ctx* ctx, const float* x, const float* y, float* x_mid, float* xn,
+                          int64_t rows, int64_t cols, float eps);
+
+/* ------------------------------------------------------------------ gather / scatter
+ * Gpu::gather_rows (rust/src/cuda/mod.rs:1156-1187): dst[r,:] = src[idx[r],:];
+ * Gpu::scatter_rows (:1190-1221): dst[idx[r],:] = src[r,:] (overwrite). idx is int32. */
+int asca_gather_rows(asca_ctx* ctx, const float* src, const int32_t* idx, int64_t n_rows,
+                     int64_t cols, float* dst);
+int asca_scatter_rows(asca_ctx* ctx, const float* src, const int32_t* idx, int64_t n_rows,
+                      int64_t cols, float* dst);
+int asca_gather_rows_host(asca_ctx* ctx, const float* src, int64_t src_rows, const int32_t* idx,
+                          int64_t n_rows, int64_t cols, float* dst);
+int asca_scatter_rows_host(asca_ctx* ctx, const float* src, const int32_t* idx, int64_t n_rows,
+                           int64_t cols, float* dst, int64_t dst_rows);
+
+/* ------------------------------------------------------------------ AdamW (A1)
+ * Gpu::adamw_update (rust/src/cuda/mod.rs:1057-1120) with the CPU path's decay
+ * (rust/src/tensor.rs:444-453): m=b1 m+(1-b1)g; v=b2 v+(1-b2)g^2; p-=wd_eff p;
+ * p-=lr_t m/(sqrt(v)+eps_t). The caller derives lr_t, eps_t, wd_eff per tensor
+ * (rust/src/tensor.rs:393-402). */
+int asca_adamw(asca_ctx* ctx, float* p, const float* g, float* m, float* v, int64_t n, float lr_t,
+               float beta1, float beta2, float eps_t, float wd_eff);
+/* Same update over a flat buffer holding n_seg tensors; seg_off[n_seg+1] (element offsets,
+ * host array) and per-tensor lr_t / eps_t (host arrays). One launch for the whole model. */
+int asca_adamw_segmented(asca_ctx* ctx, float* p, const float* g, float* m, float* v,
+                         const int64_t* seg_off, const float* lr_t, const float* eps_t,
+                         int n_seg, float beta1, float beta2, float wd_eff);
+int asca_adamw_host(asca_ctx* ctx, float* p, const float* g, float* m, float* v, int64_t n,
+                    float lr_t, float beta1, float beta2, float eps_t, float wd_eff);
+
+/* ------------------------------------------------------------------ delta rule (D1, D2, D4)
+ * Forward scan: Gpu::delta_scan (rust/src/cuda/mod.rs:1253-1321), recurrence of
+ * rust/src/delta.rs:281-315. q,k already L2-normalised per head; q,k,v,o are (B*T, H*dh) in
+ * `dtype`; alpha,beta (B*T, H) f32.
+ *   s_final : nullable, (B, H, dh, dh) f32 -- the state after the last token (prefill).
+ *   ckpt    : nullable, asca_delta_ckpt_floats() f32 -- the state at every `chunk`-token
+ *             boundary, layout (B, H, ceil(T/chunk), dh, dh); entry c is S before token
+ *             c*chunk. This replaces the reference's per-step state history
+ *             ((T+1)*dh*dh per chain) and is what asca_delta_bwd recomputes from.
+ *   s_init  : nullable, (B, H, dh, dh) f32 initial state (continuing a prefix); NULL = 0. */
+int64_t asca_delta_ckpt_floats(int64_t B, int64_t T, int64_t H, int64_t dh, int64_t chunk);
+int asca_delta_fwd(asca_ctx* ctx, const void* q, const void* k, const void* v, const float* alpha,
+                   const float* beta, int64_t B, int64_t T, int64_t H, int64_t dh, int64_t chunk,
+                   int dtype, void* o, const float* s_init, float* s_final, float* ckpt);
+/* BPTT: Gpu::delta_bwd_dev (rust/src/cuda/mod.rs:1328-1382), math of
+ * rust/src/delta.rs:485-611. Outputs d_qkv (B*T, 3*H*dh) = [dq|dk|dv] after the per-head
+ * L2-norm backward and d_gate (B*T, 2H) after the sigmoid backward, both f32. qnorm, knorm
+ * (B*T, H) are the pre-normalisation norms from the forward. ckpt comes from asca_delta_fwd
+ * with the same `chunk`. */
+int asca_delta_bwd(asca_ctx* ctx, const void* q, const void* k, const void* v, const float* alpha,
+                   const float* beta, const float* qnorm, const float* knorm, const void* d_o,
+                   const float* ckpt, int64_t B, int64_t T, int64_t H, int64_t dh, int64_t chunk,
+                   int dtype, float* d_qkv, float* d_gate);
+/* Decode step for n_streams independent streams (DeltaBlock::step, rust/src/delta.rs:356-406):
+ * S (n_streams, H, dh, dh) f32 updated in place, o (n_streams, H*dh) f32.
+ *   fused = 0: q,k,v are separate (n_streams, H*dh) arrays, q,k already normalised; alpha,
+ *              beta (n_streams, H) are the gate values.
+ *   fused = 1: q points at the raw qkv projection (n_streams, 3*H*dh), alpha at the raw gate
+ *              logits (n_streams, 2H); k, v, beta are ignored. The kernel applies
+ *              z/max(|z|,1e-8) and the sigmoids itself (rust/src/delta.rs:358-376). */
+int asca_delta_step(asca_ctx* ctx, const float* q, const float* k, const float* v,
+                    const float* alpha, const float* beta, float* S, int64_t n_streams, int64_t H,
+                    int64_t dh, int fused, float* o);
+/* Fused prologue of DeltaBlock::forward (rust/src/delta.rs:134-179): split qkv (N, 3d) into
+ * q,k,v (N, d), L2-normalise q,k per head keeping the norms, and alpha/beta = sigmoid of the
+ * gate logits (N, 2H). */
+int asca_delta_prep(asca_ctx* ctx, const float* qkv, const float* gate, int64_t N, int64_t H,
+                    int64_t dh, float* q, float* k, float* v, float* qnorm, float* knorm,
+                    float* alpha, float* beta);
+
+/* Host-pointer forms with the reference's ownership model: the forward returns an opaque
+ * device-resident handle (DeltaDev, rust/src/cuda/mod.rs:1386-1397) that the backward
+ * consumes. */
+typedef struct asca_delta_dev asca_delta_dev;
+int asca_delta_scan_host(asca_ctx* ctx, const float* q, const float* k, const float* v,
+                         const float* alpha, const float* beta, int64_t B, int64_t T, int64_t H,
+                         int64_t dh, float* o, asca_delta_dev** dev);
+int asca_delta_bwd_dev_host(asca_ctx* ctx, const asca_delta_dev* dev, const float* d_o,
+                            const float* qnorm, const float* knorm, float* d_qkv, float* d_gate);
+/* DeltaDev::download_states (rust/src/cuda/mod.rs:1473-1480): the per-step history
+ * ((H*B) chains of (T+1)*dh*dh floats, chain index h*B+b) recomputed on the device from the
+ * checkpoints. Refused with ASCA_ERR_ARG above 2^28 floats. */
+int asca_delta_dev_download_states(asca_ctx* ctx, const asca_delta_dev* dev, float* states);
+int asca_delta_dev_free(asca_ctx* ctx, asca_delta_dev* dev);
+
+/* ------------------------------------------------------------------ hash MoE (M0-M5)
+ * Dispatch: expert(t) = hash_route(ids[t], E) (rust/src/model.rs:69-77) and the stable
+ * bucket order of rust/src/model.rs:190-193 as one permutation:
+ *   perm[offsets[e] .. offsets[e+1]) = tokens of expert e in ascending token order.
+ * perm (N) and offsets (E+1) are int32 device arrays; route (N, nullable) gets the expert of
+ * each token. Integer only; bit-exact with the reference. */
+int asca_moe_dispatch(asca_ctx* ctx, const uint32_t* ids, int64_t N, int64_t E, int32_t* perm,
+                      int32_t* offsets, int32_t* route);
+int asca_moe_dispatch_host(asca_ctx* ctx, const uint32_t* ids, int64_t N, int64_t E,
+                           int32_t* perm, int32_t* offsets, int32_t* route);
+/* Expert FFN forward: Gpu::moe_forward_dev (rust/src/cuda/mod.rs:523-607), math of
+ * rust/src/model.rs:237-293. xn (N,d) normalised rows; w1 (d, E*F), b1 (E*F) f32, w2 (E*F, d),
+ * b2 (d) f32; out (N,d) f32 in token order. pre_p / hid_p (N,F): pre-activation and SiLU
+ * output in PERMUTED (expert-contiguous) row order, kept for the backward. xn,w1,w2,hid_p
+ * are `dtype`; pre_p is f32. */
+int asca_moe_fwd(asca_ctx* ctx, const void* xn, const void* w1, const float* b1, const void* w2,
+                 const float* b2, const int32_t* perm, const int32_t* offsets, int64_t N, int64_t d,
+                 int64_t F, int64_t E, int dtype, float* out, float* pre_p, void* hid_p);
+/* Expert FFN backward: Gpu::moe_bwd_dev (rust/src/cuda/mod.rs:745-824), math of
+ * rust/src/model.rs:417-495. Writes (overwrites) d_w1 (d,E*F), d_b1 (E*F), d_w2 (E*F,d),
+ * d_b2 (d), dxn (N,d), all f32. */
+int asca_moe_bwd(asca_ctx* ctx, const void* xn, const void* w1, const void* w2,
+                 const float* pre_p, const void* hid_p, const float* dout, const int32_t* perm,
+                 const int32_t* offsets, int64_t N, int64_t d, int64_t F, int64_t E, int dtype,
+                 float* d_w1, float* d_b1, float* d_w2, float* d_b2, float* dxn);
+/* Fused combine: x_out = x_mid + moe_out (rust/src/model.rs:669-671); when xn_next is not
+ * NULL also xn_next = rmsnorm(x_out) (the final norm, rust/src/model.rs:680). Alias of
+ * asca_residual_rmsnorm kept under the name the MoE path uses. */
+int asca_moe_combine(asca_ctx* ctx, const float* x_mid, const float* moe_out, float* x_out,
+                     float* xn_next, int64_t rows, int64_t cols, float eps);
+/* Decode step for n_streams tokens (HashMoe::step, rust/src/model.rs:309-337): rmsnorm, one
+ * expert per token, two GEMVs. x (n,d) f32 -> out (n,d) f32. */
+int asca_moe_step(asca_ctx* ctx, const float* x, const uint32_t* ids, const void* w1,
+                  const float* b1, const void* w2, const float* b2, int64_t n_streams, int64_t d,
+                  int64_t F, int64_t E, int dtype, float* out);
+
+typedef struct asca_moe_dev asca_moe_dev;
+/* Host forms. `ids` replaces the reference's host-built `buckets` argument (the library
+ * builds the same buckets on the device). */
+int asca_moe_forward_dev_host(asca_ctx* ctx, const float* xn, const float* w1, const float* b1,
+                              const float* w2, const float* b2, const uint32_t* ids, int64_t N,
+                              int64_t d, int64_t F, int64_t E, float* out, asca_moe_dev** dev);
+int asca_moe_bwd_dev_host(asca_ctx* ctx, const asca_moe_dev* dev, const float* dout, float* d_w1,
+                          float* d_b1, float* d_w2, float* d_b2, float* dxn);
+/* MoeDev::download_pre_hidden (rust/src/cuda/mod.rs:1445-1470): pre and hidden as (N,F) in
+ * token order. */
+int asca_moe_dev_download_pre_hidden(asca_ctx* ctx, const asca_moe_dev* dev, float* pre,
+                                     float* hidden);
+int asca_moe_dev_free(asca_ctx* ctx, asca_moe_dev* dev);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ASCA_B200_H */

@@ -1,0 +1,433 @@
+"""GPU-vs-oracle parity of every entry point, through the C ABI. Modelled on the reference's own
+GPU gate `asca gpu` (rust/src/main.rs:790-1203): same ops, same shapes where it names them,
+same error metric max|a-b| / max|ref|.
+
+Tolerances: 1e-5 relative for f32 mode, 2e-2 for bf16 mode; integer results bit-exact.
+"""
+import numpy as np
+import pytest
+
+from conftest import rel_err
+
+pytestmark = pytest.mark.gpu
+
+F32_TOL = 1e-5
+BF16_TOL = 2e-2
+
+
+def _delta_inputs(orc, seed, B, T, H, dh):
+    """q,k L2-normalised N(0,1); v N(0,1); alpha = sigmoid(N(2,.5)); beta = sigmoid(N(0,1))."""
+    rng = orc.Rng(seed)
+    n, d = B * T, H * dh
+    q, k, v, d_o = (rng.normal((n, d)) for _ in range(4))
+    qn = np.linalg.norm(q.reshape(n, H, dh), axis=-1).astype(np.float32)
+    kn = np.linalg.norm(k.reshape(n, H, dh), axis=-1).astype(np.float32)
+    q = (q.reshape(n, H, dh) / qn[..., None]).reshape(n, d).astype(np.float32)
+    k = (k.reshape(n, H, dh) / kn[..., None]).reshape(n, d).astype(np.float32)
+    alpha = (1 / (1 + np.exp(-(2 + 0.5 * rng.normal((n, H)))))).astype(np.float32)
+    beta = (1 / (1 + np.exp(-rng.normal((n, H))))).astype(np.float32)
+    return q, k, v, alpha, beta, qn, kn, d_o
+
+
+# ------------------------------------------------------------------ GEMM
+@pytest.mark.parametrize("m,k,n", [(64, 64, 192), (128, 64, 512), (37, 53, 91), (256, 256, 256), (1, 64, 192),
+                                   (300, 1, 5), (513, 130, 257)])
+def test_matmul_and_matmul_ta(orc, gpu, m, k, n):
+    rng = orc.Rng(7)
+    a, b = rng.normal((m, k), 0.1), rng.normal((k, n), 0.1)
+    assert rel_err(gpu.matmul(a, b), orc.matmul(a, b)) < F32_TOL
+    at = rng.normal((k, m), 0.1)
+    assert rel_err(gpu.matmul_ta(at, b), orc.matmul(np.ascontiguousarray(at.T), b)) < F32_TOL
+    bt = rng.normal((n, k), 0.1)
+    assert rel_err(gpu.matmul_t(a, bt), orc.matmul_t(a, bt)) < F32_TOL
+
+
+def test_gemm_bias_accumulate_and_bf16(orc, gpu):
+    import torch
+    from asca_b200 import ops, NN, TN, NT
+
+    rng = orc.Rng(3)
+    m, k, n = 200, 96, 136
+    a, b, bias, c0 = rng.normal((m, k)), rng.normal((k, n)), rng.normal(n), rng.normal((m, n))
+    ref = a.astype(np.float64) @ b + bias + c0
+    ta, tb, tbias = (torch.from_numpy(x).cuda() for x in (a, b, bias))
+    out = torch.from_numpy(c0.copy()).cuda()
+    ops.gemm(gpu, ta, tb, NN, bias=tbias, out=out, accumulate=True)
+    gpu.sync()
+    assert rel_err(out.cpu().numpy(), ref) < F32_TOL
+    # bf16 operands, f32 accumulate
+    a16, b16 = ta.bfloat16(), tb.bfloat16()
+    ref16 = a16.float().cpu().numpy().astype(np.float64) @ b16.float().cpu().numpy()
+    got = ops.gemm(gpu, a16, b16, NN)
+    gpu.sync()
+    assert rel_err(got.cpu().numpy(), ref16) < 1e-5  # exact products of the rounded inputs
+    got_t = ops.gemm(gpu, a16.t().contiguous(), b16, TN)
+    got_nt = ops.gemm(gpu, a16, b16.t().contiguous(), NT)
+    gpu.sync()
+    assert rel_err(got_t.cpu().numpy(), ref16) < 1e-5 and rel_err(got_nt.cpu().numpy(), ref16) < 1e-5
+
+
+# ------------------------------------------------------------------ RMSNorm
+@pytest.mark.parametrize("rows,cols", [(1, 64), (257, 64), (100, 192), (33, 1024), (17, 2048), (5, 1000), (9, 7)])
+def test_rmsnorm_fwd_bwd(orc, gpu, rows, cols):
+    rng = orc.Rng(rows * 31 + cols)
+    x, dy = rng.normal((rows, cols)), rng.normal((rows, cols))
+    y, inv = gpu.rmsnorm(x, 1e-6)
+    y_ref, inv_ref = orc.rmsnorm(x, 1e-6)
+    assert rel_err(y, y_ref) < F32_TOL and rel_err(inv, inv_ref) < F32_TOL
+    assert rel_err(gpu.rmsnorm_bwd(x, dy, 1e-6), orc.rmsnorm_bwd(x, dy, 1e-6)) < F32_TOL
+
+
+def test_residual_rmsnorm_fusion(orc, gpu):
+    import torch
+    from asca_b200 import ops
+
+    rng = orc.Rng(11)
+    for rows, cols in ((300, 64), (70, 768), (12, 2048)):
+        x, y = rng.normal((rows, cols)), rng.normal((rows, cols))
+        x_mid, xn = ops.residual_rmsnorm(gpu, torch.from_numpy(x).cuda(), torch.from_numpy(y).cuda())
+        gpu.sync()
+        s = (x + np.float32(1.0) * y).astype(np.float32)
+        assert np.array_equal(x_mid.cpu().numpy(), s)
+        assert rel_err(xn.cpu().numpy(), orc.rmsnorm(s)[0]) < F32_TOL
+
+
+# ------------------------------------------------------------------ gather / scatter / AdamW
+def test_gather_scatter_rows(orc, gpu):
+    rng = orc.Rng(5)
+    src = rng.normal((100, 48))
+    idx = rng.below(100, 37).astype(np.int32)
+    assert np.array_equal(gpu.gather_rows(src, idx), src[idx])
+    perm = np.random.RandomState(0).permutation(100).astype(np.int32)
+    dst = np.full((100, 48), -1.0, np.float32)
+    gpu.scatter_rows(src[:60].copy(), perm[:60], dst)
+    want = np.full((100, 48), -1.0, np.float32)
+    want[perm[:60]] = src[:60]
+    assert np.array_equal(dst, want)
+    import asca_b200
+    with pytest.raises(asca_b200.AscaError):
+        gpu.gather_rows(src, np.array([0, 100], np.int32))
+
+
+def test_adamw_matches_cpu_decay_and_per_tensor_counter(orc, gpu):
+    import torch
+    from asca_b200 import ops
+
+    rng = orc.Rng(13)
+    for n in (1, 7, 1023, 40000):
+        p, g = rng.normal(n), rng.normal(n, 0.1)
+        m, v = rng.normal(n, 0.01), np.abs(rng.normal(n, 0.01)).astype(np.float32)
+        lr_t, eps_t, wd_eff = orc.adamw_scalars(3e-3, 0.9, 0.95, 1e-8, 0.01, 5)
+        p2, m2, v2 = p.copy(), m.copy(), v.copy()
+        orc.adamw_apply(p2, g, m2, v2, lr_t, 0.9, 0.95, eps_t, wd_eff)
+        gpu.adamw_update(p, g, m, v, lr_t, 0.9, 0.95, eps_t, wd_eff)
+        assert rel_err(p, p2) < F32_TOL and rel_err(m, m2) < F32_TOL and rel_err(v, v2) < F32_TOL
+    # whole model, flat buffer, one segmented launch == the oracle's per-tensor loop
+    model = orc.Model(256, 16, 2, 1, 2, 16)
+    model.init_reference(orc.Rng(1))
+    grads = orc.Rng(2).normal(model.n, 0.1)
+    mm, vv = np.zeros(model.n, np.float32), np.zeros(model.n, np.float32)
+    tp, tg, tm, tv = (torch.from_numpy(x.copy()).cuda() for x in (model.params, grads, mm, vv))
+    counter = 24  # second optimizer step: tensor i uses t = 24 + i + 1
+    sc = [orc.adamw_scalars(3e-3, 0.9, 0.95, 1e-8, 0.01, counter + i + 1) for i in range(len(model.names))]
+    seg = np.concatenate([model.tensor_off, [model.n]])
+    ops.adamw_segmented(gpu, tp, tg, tm, tv, seg, [s[0] for s in sc], [s[1] for s in sc], 0.9, 0.95, sc[0][2])
+    gpu.sync()
+    assert model.adamw_step(grads, mm, vv, counter, 3e-3) == counter + len(model.names)
+    assert rel_err(tp.cpu().numpy(), model.params) < F32_TOL
+    assert rel_err(tm.cpu().numpy(), mm) < F32_TOL and rel_err(tv.cpu().numpy(), vv) < F32_TOL
+
+
+# ------------------------------------------------------------------ dispatch (bit-exact)
+def _zipf_ids(orc, seed, n, s=1.1):
+    w = 1.0 / np.arange(1, 257) ** s
+    cdf = np.cumsum(w) / w.sum()
+    u = orc.Rng(seed).uniform(n)
+    return np.minimum(np.searchsorted(cdf, u), 255).astype(np.uint32)
+
+
+@pytest.mark.parametrize("n,e", [(0, 4), (1, 4), (31, 8), (1000, 8), (4097, 16), (65536, 64), (5000, 1), (3000, 300)])
+def test_dispatch_bit_exact(orc, gpu, n, e):
+    ids = orc.Rng(n + e).below(256 if e < 300 else 100000, max(n, 1))[:n].copy()
+    perm, off, route = gpu.moe_dispatch(ids, e)
+    p2, o2, r2 = orc.moe_dispatch(ids, e)
+    assert np.array_equal(off, o2) and np.array_equal(perm, p2) and np.array_equal(route, r2)
+
+
+def test_dispatch_bit_exact_zipf_skew_config3(orc, gpu):
+    ids = _zipf_ids(orc, 9, 65536)
+    perm, off, route = gpu.moe_dispatch(ids, 64)
+    p2, o2, r2 = orc.moe_dispatch(ids, 64)
+    assert np.array_equal(off, o2) and np.array_equal(perm, p2) and np.array_equal(route, r2)
+    load = np.diff(off) / 65536
+    assert load.max() > 0.15 and load.min() > 0  # skewed, no empty expert
+    # all tokens collide on one expert
+    same = np.full(5000, 42, np.uint32)
+    perm, off, _ = gpu.moe_dispatch(same, 16)
+    assert np.array_equal(perm, np.arange(5000, dtype=np.int32))
+
+
+# ------------------------------------------------------------------ delta rule
+def test_delta_scan_reference_gate_shape(orc, gpu):
+    # rust/src/main.rs:853-952: B=3, seq=24, H=4, dh=16, states compared too
+    B, T, H, dh = 3, 24, 4, 16
+    q, k, v, alpha, beta, *_ = _delta_inputs(orc, 7, B, T, H, dh)
+    o_ref, _, st_ref = orc.delta_scan(q, k, v, alpha, beta, B, T, H, dh, want_states=True)
+    o, dev = gpu.delta_scan(q, k, v, alpha, beta, B, T, H, dh)
+    assert rel_err(o, o_ref) < F32_TOL
+    assert rel_err(o, orc.delta_scan_scalar(q, k, v, alpha, beta, B, T, H, dh)) < F32_TOL
+    st = np.stack(dev.download_states()).reshape(H, B, T + 1, dh, dh)
+    assert rel_err(st, st_ref) < F32_TOL
+    # sequence isolation: batch=3 equals three batch=1 launches (rust/src/main.rs:954-981)
+    for b in range(B):
+        s = slice(b * T, (b + 1) * T)
+        ob, _ = gpu.delta_scan(q[s], k[s], v[s], alpha[s], beta[s], 1, T, H, dh, keep=False)
+        assert np.array_equal(ob, o[s])
+
+
+@pytest.mark.parametrize("B,T,H,dh", [(2, 1, 2, 16), (1, 15, 3, 16), (2, 70, 2, 32), (2, 130, 3, 64), (1, 200, 2, 128),
+                                      (3, 64, 1, 128)])
+def test_delta_fwd_bwd_f32(orc, gpu, B, T, H, dh):
+    q, k, v, alpha, beta, qn, kn, d_o = _delta_inputs(orc, 100 + T + dh, B, T, H, dh)
+    o_ref, sfin_ref = orc.delta_scan(q, k, v, alpha, beta, B, T, H, dh)
+    dqkv_ref, dgate_ref = orc.delta_bptt(q, k, v, alpha, beta, qn, kn, d_o, B, T, H, dh)
+    o, dev = gpu.delta_scan(q, k, v, alpha, beta, B, T, H, dh)
+    d_qkv, d_gate = gpu.delta_bwd_dev(dev, d_o, qn, kn)
+    assert rel_err(o, o_ref) < F32_TOL
+    d = H * dh
+    for name, sl in (("dq", slice(0, d)), ("dk", slice(d, 2 * d)), ("dv", slice(2 * d, 3 * d))):
+        assert rel_err(d_qkv[:, sl], dqkv_ref[:, sl]) < F32_TOL, name
+    assert rel_err(d_gate[:, :H], dgate_ref[:, :H]) < F32_TOL
+    assert rel_err(d_gate[:, H:], dgate_ref[:, H:]) < F32_TOL
+
+
+@pytest.mark.parametrize("chunk", [1, 16, 24, 64, 256])
+def test_delta_chunk_size_does_not_change_results(orc, gpu, chunk):
+    import torch
+    from asca_b200 import ops
+
+    B, T, H, dh = 2, 150, 2, 64
+    arrs = _delta_inputs(orc, 55, B, T, H, dh)
+    q, k, v, alpha, beta, qn, kn, d_o = (torch.from_numpy(a).cuda() for a in arrs)
+    o, s_final, ckpt = ops.delta_fwd(gpu, q, k, v, alpha, beta, B, T, H, dh, chunk=chunk, want_final=True)
+    d_qkv, d_gate = ops.delta_bwd(gpu, q, k, v, alpha, beta, qn, kn, d_o, ckpt, B, T, H, dh, chunk=chunk)
+    gpu.sync()
+    o_ref, sfin_ref = orc.delta_scan(*arrs[:5], B, T, H, dh)
+    dqkv_ref, dgate_ref = orc.delta_bptt(*arrs[:5], arrs[5], arrs[6], arrs[7], B, T, H, dh)
+    assert rel_err(o.cpu().numpy(), o_ref) < F32_TOL
+    assert rel_err(s_final.cpu().numpy(), sfin_ref) < F32_TOL
+    assert rel_err(d_qkv.cpu().numpy(), dqkv_ref) < F32_TOL
+    assert rel_err(d_gate.cpu().numpy(), dgate_ref) < F32_TOL
+
+
+def test_delta_prefill_continuation_with_initial_state(orc, gpu):
+    import torch
+    from asca_b200 import ops
+
+    B, T, H, dh = 2, 96, 2, 64
+    arrs = _delta_inputs(orc, 77, B, T, H, dh)
+    q, k, v, alpha, beta = (torch.from_numpy(a).cuda() for a in arrs[:5])
+    o_full, s_full, _ = ops.delta_fwd(gpu, q, k, v, alpha, beta, B, T, H, dh, want_final=True, want_ckpt=False)
+    half = T // 2
+
+    def part(x, lo, hi):
+        return x.view(B, T, -1)[:, lo:hi].contiguous().view(B * (hi - lo), -1)
+
+    a1 = [part(x, 0, half) for x in (q, k, v, alpha, beta)]
+    a2 = [part(x, half, T) for x in (q, k, v, alpha, beta)]
+    o1, s1, _ = ops.delta_fwd(gpu, *a1, B, half, H, dh, want_final=True, want_ckpt=False)
+    o2, s2, _ = ops.delta_fwd(gpu, *a2, B, T - half, H, dh, s_init=s1, want_final=True, want_ckpt=False)
+    gpu.sync()
+    assert torch.equal(part(o_full, 0, half), o1) and torch.equal(part(o_full, half, T), o2)
+    assert torch.equal(s_full, s2)
+
+
+def test_delta_bf16_mode(orc, gpu):
+    import torch
+    from asca_b200 import ops
+
+    B, T, H, dh = 2, 128, 2, 128
+    arrs = _delta_inputs(orc, 91, B, T, H, dh)
+    q, k, v, alpha, beta, qn, kn, d_o = (torch.from_numpy(a).cuda() for a in arrs)
+    q16, k16, v16, do16 = (x.bfloat16() for x in (q, k, v, d_o))
+    o, _, ckpt = ops.delta_fwd(gpu, q16, k16, v16, alpha, beta, B, T, H, dh)
+    d_qkv, d_gate = ops.delta_bwd(gpu, q16, k16, v16, alpha, beta, qn, kn, do16, ckpt, B, T, H, dh)
+    gpu.sync()
+    o_ref, _ = orc.delta_scan(*arrs[:5], B, T, H, dh)
+    dqkv_ref, dgate_ref = orc.delta_bptt(*arrs[:5], arrs[5], arrs[6], arrs[7], B, T, H, dh)
+    assert o.dtype == torch.bfloat16
+    assert rel_err(o.float().cpu().numpy(), o_ref) < BF16_TOL
+    assert rel_err(d_qkv.cpu().numpy(), dqkv_ref) < BF16_TOL
+    assert rel_err(d_gate.cpu().numpy(), dgate_ref) < BF16_TOL
+
+
+@pytest.mark.parametrize("dh", [16, 32, 64, 128])
+def test_delta_decode_step(orc, gpu, dh):
+    import torch
+    from asca_b200 import ops
+
+    ns, H, steps = 5, 3, 6
+    d = H * dh
+    rng = orc.Rng(dh)
+    S_ref = rng.normal((ns, H, dh, dh), 0.1)
+    S = torch.from_numpy(S_ref.copy()).cuda()
+    for _ in range(steps):
+        q, k, v, alpha, beta, *_ = _delta_inputs(orc, int(rng.below(1000, 1)[0]), ns, 1, H, dh)
+        o_ref = orc.delta_step_core(q, k, v, alpha, beta, S_ref, H, dh)
+        o = ops.delta_step(gpu, *(torch.from_numpy(a).cuda() for a in (q, k, v, alpha, beta)), S, H, dh)
+        gpu.sync()
+        assert rel_err(o.cpu().numpy(), o_ref) < F32_TOL
+        assert rel_err(S.cpu().numpy(), S_ref) < F32_TOL
+    # fused prologue: raw qkv + gate logits, compared with the block-level step of the oracle
+    blk = orc.DeltaBlock(d, H, orc.Rng(3))
+    x = rng.normal((1, d))
+    st_ref = rng.normal((H, dh, dh), 0.1)
+    st = torch.from_numpy(st_ref.copy()).cuda().view(1, H, dh, dh)
+    qkv = orc.matmul(x, blk.w_qkv) + blk.b_qkv
+    gate = orc.matmul(x, blk.w_gate) + blk.b_gate
+    o = ops.delta_step(gpu, torch.from_numpy(qkv).cuda(), None, None, torch.from_numpy(gate).cuda(), None, st, H, dh,
+                       fused=True)
+    gpu.sync()
+    y = orc.matmul(o.cpu().numpy(), blk.w_o) + blk.b_o
+    if dh <= 64 or True:  # the oracle's step uses heap scratch, so dh=128 is checkable too
+        y_ref = blk.step(x, st_ref)
+        assert rel_err(y, y_ref) < F32_TOL
+        assert rel_err(st.cpu().numpy().reshape(H, dh, dh), st_ref) < F32_TOL
+
+
+def test_delta_block_gradient_gpu_vs_cpu(orc, gpu):
+    """rust/src/main.rs:1104-1150: a whole DeltaBlock at B=8, seq=128, d=192, H=6 with the scan and
+    the BPTT on the device and the projections through the library's GEMMs."""
+    import torch
+    from asca_b200 import ops, NN, TN, NT
+
+    B, T, d, H = 8, 128, 192, 6
+    dh, n = d // H, B * T
+    rng = orc.Rng(42)
+    blk = orc.DeltaBlock(d, H, rng)
+    x, dy = rng.normal((n, d), 0.5), rng.normal((n, d))
+    y_ref, cache = blk.forward(x, B)
+    dx_ref, g_ref = blk.backward(cache, dy)
+    blk.free(cache)
+    t = {nm: torch.from_numpy(getattr(blk, nm)).cuda() for nm in blk.NAMES}
+    tx, tdy = torch.from_numpy(x).cuda(), torch.from_numpy(dy).cuda()
+    qkv = ops.gemm(gpu, tx, t["w_qkv"], NN, bias=t["b_qkv"])
+    gate = ops.gemm(gpu, tx, t["w_gate"], NN, bias=t["b_gate"])
+    q, k, v, qn, kn, al, be = ops.delta_prep(gpu, qkv, gate, H, dh)
+    o, _, ckpt = ops.delta_fwd(gpu, q, k, v, al, be, B, T, H, dh)
+    y = ops.gemm(gpu, o, t["w_o"], NN, bias=t["b_o"])
+    d_o = ops.gemm(gpu, tdy, t["w_o"], NT)
+    g_w_o = ops.gemm(gpu, o, tdy, TN)
+    d_qkv, d_gate = ops.delta_bwd(gpu, q, k, v, al, be, qn, kn, d_o, ckpt, B, T, H, dh)
+    g_w_qkv = ops.gemm(gpu, tx, d_qkv, TN)
+    g_w_gate = ops.gemm(gpu, tx, d_gate, TN)
+    dx = ops.gemm(gpu, d_qkv, t["w_qkv"], NT)
+    ops.gemm(gpu, d_gate, t["w_gate"], NT, out=dx, accumulate=True)
+    gpu.sync()
+    assert rel_err(y.cpu().numpy(), y_ref) < F32_TOL
+    assert rel_err(dx.cpu().numpy(), dx_ref) < F32_TOL
+    assert rel_err(g_w_o.cpu().numpy(), g_ref["w_o"]) < F32_TOL
+    assert rel_err(g_w_qkv.cpu().numpy(), g_ref["w_qkv"]) < F32_TOL
+    assert rel_err(g_w_gate.cpu().numpy(), g_ref["w_gate"]) < F32_TOL
+    assert rel_err(d_qkv.sum(0).cpu().numpy(), g_ref["b_qkv"]) < 1e-4  # bias grads: column sums
+    assert rel_err(d_gate.sum(0).cpu().numpy(), g_ref["b_gate"]) < 1e-4
+
+
+# ------------------------------------------------------------------ hash MoE
+def _moe_params(orc, seed, d, F, E, bias=True):
+    rng = orc.Rng(seed)
+    w1 = rng.normal((d, E * F), float(np.sqrt(1.0 / d)))
+    w2 = rng.normal((E * F, d), float(np.sqrt(1.0 / F)))
+    b1 = rng.normal(E * F, 0.1) if bias else np.zeros(E * F, np.float32)
+    b2 = rng.normal(d, 0.1) if bias else np.zeros(d, np.float32)
+    return w1, b1, w2, b2
+
+
+@pytest.mark.parametrize("n,d,F,E,vocab", [(1024, 192, 384, 8, 4096), (300, 64, 256, 4, 256), (77, 16, 20, 3, 256),
+                                           (2048, 64, 128, 64, 40)])
+def test_moe_forward_backward_f32(orc, gpu, n, d, F, E, vocab):
+    # first case = rust/src/main.rs:991-1051 (T=1024, d=192, d_ff=384, E=8, ids below 4096);
+    # last case leaves many experts empty
+    w1, b1, w2, b2 = _moe_params(orc, 77, d, F, E)
+    rng = orc.Rng(n)
+    x = rng.normal((n, d), 0.5)
+    ids = rng.below(vocab, n)
+    dout = rng.normal((n, d))
+    xn, _ = orc.rmsnorm(x)
+    out_ref, pre_ref, hid_ref = orc.moe_ffn_forward(xn, w1, b1, w2, b2, ids, F, E, want_cache=True)
+    g_ref = orc.moe_ffn_backward(xn, w1, w2, pre_ref, hid_ref, ids, dout, F, E)
+    out, dev = gpu.moe_forward_dev(xn, w1, b1, w2, b2, ids, F)
+    pre, hid = dev.download_pre_hidden()
+    assert rel_err(out, out_ref) < F32_TOL
+    assert rel_err(pre, pre_ref) < F32_TOL and rel_err(hid, hid_ref) < F32_TOL
+    r = gpu.moe_bwd_dev(dev, dout)
+    for name, got, want in (("d_w1", r.d_w1, g_ref[0]), ("d_b1", r.d_b1, g_ref[1]), ("d_w2", r.d_w2, g_ref[2]),
+                            ("d_b2", r.d_b2, g_ref[3]), ("dxn", r.dxn, g_ref[4])):
+        assert rel_err(got, want) < F32_TOL, name
+
+
+def test_moe_bf16_mode(orc, gpu):
+    import torch
+    from asca_b200 import ops
+
+    n, d, F, E = 600, 128, 256, 8
+    w1, b1, w2, b2 = _moe_params(orc, 5, d, F, E, bias=False)
+    rng = orc.Rng(8)
+    xn = orc.rmsnorm(rng.normal((n, d)))[0]
+    ids = rng.below(256, n)
+    dout = rng.normal((n, d))
+    out_ref, pre_ref, hid_ref = orc.moe_ffn_forward(xn, w1, b1, w2, b2, ids, F, E, want_cache=True)
+    g_ref = orc.moe_ffn_backward(xn, w1, w2, pre_ref, hid_ref, ids, dout, F, E)
+    c = lambda a: torch.from_numpy(a).cuda()
+    perm, offsets = ops.moe_dispatch(gpu, c(ids.view(np.int32)), E)
+    txn, tw1, tw2 = c(xn).bfloat16(), c(w1).bfloat16(), c(w2).bfloat16()
+    out, pre_p, hid_p = ops.moe_fwd(gpu, txn, tw1, c(b1), tw2, c(b2), perm, offsets, F, E)
+    grads = ops.moe_bwd(gpu, txn, tw1, tw2, pre_p, hid_p, c(dout), perm, offsets, F, E)
+    gpu.sync()
+    assert hid_p.dtype == torch.bfloat16
+    assert rel_err(out.cpu().numpy(), out_ref) < BF16_TOL
+    for got, want in zip(grads, g_ref):
+        assert rel_err(got.cpu().numpy(), want) < BF16_TOL
+
+
+def test_moe_layer_with_norm_and_decode_step(orc, gpu):
+    import torch
+    from asca_b200 import ops
+
+    n, d, F, E = 256, 64, 256, 4
+    w1, b1, w2, b2 = _moe_params(orc, 21, d, F, E)
+    rng = orc.Rng(2)
+    x, dout = rng.normal((n, d)), rng.normal((n, d))
+    ids = rng.below(256, n)
+    ref = orc.moe_forward_backward(x, w1, b1, w2, b2, ids, dout, F, E)
+    c = lambda a: torch.from_numpy(a).cuda()
+    tx = c(x)
+    xn = ops.rmsnorm_fwd(gpu, tx)
+    perm, offsets = ops.moe_dispatch(gpu, c(ids.view(np.int32)), E)
+    out, pre_p, hid_p = ops.moe_fwd(gpu, xn, c(w1), c(b1), c(w2), c(b2), perm, offsets, F, E)
+    d_w1, d_b1, d_w2, d_b2, dxn = ops.moe_bwd(gpu, xn, c(w1), c(w2), pre_p, hid_p, c(dout), perm, offsets, F, E)
+    dx = ops.rmsnorm_bwd(gpu, tx, dxn)
+    gpu.sync()
+    for got, want in zip((out, d_w1, d_b1, d_w2, d_b2, dx), ref):
+        assert rel_err(got.cpu().numpy(), want) < F32_TOL
+    # decode: one token per stream
+    step = ops.moe_step(gpu, tx[:32].contiguous(), c(ids[:32].view(np.int32)), c(w1), c(b1), c(w2), c(b2), F, E)
+    gpu.sync()
+    want = np.concatenate([orc.moe_step(x[i:i + 1], w1, b1, w2, b2, int(ids[i]), F, E) for i in range(32)])
+    assert rel_err(step.cpu().numpy(), want) < F32_TOL
+    assert rel_err(step.cpu().numpy(), ref[0][:32]) < F32_TOL  # decode == forward rows
+
+
+# ------------------------------------------------------------------ argument errors (host side, before any launch)
+def test_bad_arguments_fail_before_launch(orc, gpu):
+    import asca_b200
+
+    q = np.zeros((8, 24), np.float32)
+    a = np.zeros((8, 1), np.float32)
+    with pytest.raises(asca_b200.AscaError) as e:
+        gpu.delta_scan(q, q, q, a, a, 1, 8, 1, 24)  # dh = 24 unsupported
+    assert e.value.code == -4
+    before = gpu.launch_count()
+    with pytest.raises(asca_b200.AscaError):
+        gpu._call("asca_rmsnorm_fwd", gpu._ctx, None, None, None, 1, 1, asca_b200._f(1e-6))
+    assert gpu.launch_count() == before
