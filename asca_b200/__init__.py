@@ -173,7 +173,9 @@ class Gpu:
     def use_torch_stream(self):
         import torch
 
-        self.set_stream(torch.cuda.current_stream(self.device).cuda_stream)
+        # torch's default stream has handle 0, which the C ABI reads as "the context's own
+        # stream"; CUDA's explicit handle for the legacy default stream is 1 (cudaStreamLegacy).
+        self.set_stream(torch.cuda.current_stream(self.device).cuda_stream or 1)
 
     def sync(self):
         self._call("asca_ctx_sync", self._ctx)
@@ -246,21 +248,21 @@ class Gpu:
                    _f(beta2), _f(eps_t), _f(wd))
 
     # ---- Gpu::delta_scan / delta_bwd_dev (rust/src/cuda/mod.rs:1253-1382)
-    def delta_scan(self, q, k, v, alpha, beta, batch, seq, n_heads, dh, keep=True):
+    def delta_scan(self, q, k, v, alpha, beta, batch, seq, n_heads, dh, keep=True, out=None):
         q, k, v, alpha, beta = map(_as_f32, (q, k, v, alpha, beta))
         assert q.shape == (batch * seq, n_heads * dh), "delta_scan: q rows must be batch*seq"
-        o = np.empty_like(q)
+        o = np.empty_like(q) if out is None else out
         h = C.c_void_p()
         self._call("asca_delta_scan_host", self._ctx, _p(q), _p(k), _p(v), _p(alpha), _p(beta), _i64(batch), _i64(seq),
                    _i64(n_heads), _i64(dh), _p(o), C.byref(h) if keep else None)
         return o, (DeltaDev(self, h, batch, seq, n_heads, dh) if keep else None)
 
-    def delta_bwd_dev(self, dev: DeltaDev, d_o, qnorm, knorm):
+    def delta_bwd_dev(self, dev: DeltaDev, d_o, qnorm, knorm, out=None):
         d_o, qnorm, knorm = map(_as_f32, (d_o, qnorm, knorm))
         n, d = dev.batch * dev.seq, dev.n_heads * dev.dh
         assert d_o.shape == (n, d)
-        d_qkv = np.empty((n, 3 * d), np.float32)
-        d_gate = np.empty((n, 2 * dev.n_heads), np.float32)
+        d_qkv, d_gate = out if out is not None else (np.empty((n, 3 * d), np.float32),
+                                                     np.empty((n, 2 * dev.n_heads), np.float32))
         self._call("asca_delta_bwd_dev_host", self._ctx, dev._h, _p(d_o), _p(qnorm), _p(knorm), _p(d_qkv), _p(d_gate))
         return d_qkv, d_gate
 

@@ -22,7 +22,6 @@ from __future__ import annotations
 import argparse
 import json
 import os
-import subprocess
 import sys
 import threading
 import time
@@ -47,48 +46,61 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+    """SM clock and throttle reasons sampled every 20 ms (NVML, read-only) while the timed region runs."""
 
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
     def __init__(self, index: int):
         self.index = index
-        self.rows = []
-        self.proc = None
+        self.sm, self.mask, self.mx = [], 0, None
+        self._stop = threading.Event()
+        self._th = None
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "200", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
-            threading.Thread(target=self._read, daemon=True).start()
-        except OSError:
-            self.proc = None
+            import pynvml
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            pynvml.nvmlInit()
+            # CUDA_VISIBLE_DEVICES may renumber devices: match by the UUID torch reports
+            import torch
+
+            uuid = str(torch.cuda.get_device_properties(self.index).uuid)
+            self.h = None
+            for i in range(pynvml.nvmlDeviceGetCount()):
+                h = pynvml.nvmlDeviceGetHandleByIndex(i)
+                u = pynvml.nvmlDeviceGetUUID(h)
+                u = u.decode() if isinstance(u, bytes) else u
+                if uuid in u:
+                    self.h = h
+            if self.h is None:
+                self.h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.nv = pynvml
+            self.mx = float(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+        except Exception as e:  # noqa: BLE001
+            self.err = repr(e)
+            self.nv = None
+            return
+        self._th = threading.Thread(target=self._run, daemon=True)
+        self._th.start()
+
+    def _run(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                self.sm.append(float(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                self.mask |= int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.h))
+            except Exception:  # noqa: BLE001
+                pass
+            time.sleep(0.02)
 
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.25)
-        self.proc.terminate()
-        sm, mx, reasons = [], None, set()
-        for r in self.rows:
-            if len(r) < 9:
-                continue
-            try:
-                sm.append(float(r[1]))
-                mx = float(r[2])
-            except ValueError:
-                continue
-            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
-                "samples": len(sm)}
+        if self._th is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvml unavailable: " + getattr(self, "err", "")]}
+        self._stop.set()
+        self._th.join()
+        reasons = sorted(n for bit, n in self.REASONS.items() if self.mask & bit)
+        return {"sm_mhz": float(np.median(self.sm)) if self.sm else None, "sm_max_mhz": self.mx, "reasons": reasons,
+                "samples": len(self.sm)}
 
 
 def make_inputs(seed: int, b: int, t: int, h: int, dh: int):
@@ -244,15 +256,20 @@ def run_ours(args):
     # ---- end to end through the host-pointer API (pinned host buffers in, host results out)
     e2e_steps = max(1, min(args.steps, 3))
     hq, hk, hv, ha, hb, hqn, hkn, hdo = (x.numpy() for x in pin)
+    o_h = torch.empty((n, d), dtype=torch.float32).pin_memory().numpy()
+    dqkv_h = torch.empty((n, 3 * d), dtype=torch.float32).pin_memory().numpy()
+    dgate_h = torch.empty((n, 2 * h), dtype=torch.float32).pin_memory().numpy()
+    del q, k, v, d_o, o, ckpt, d_qkv, d_gate
+    torch.cuda.empty_cache()
     for _ in range(1):
-        o_h, dd = gpu.delta_scan(hq, hk, hv, ha, hb, b, t, h, dh)
-        gpu.delta_bwd_dev(dd, hdo, hqn, hkn)
+        _, dd = gpu.delta_scan(hq, hk, hv, ha, hb, b, t, h, dh, out=o_h)
+        gpu.delta_bwd_dev(dd, hdo, hqn, hkn, out=(dqkv_h, dgate_h))
         dd.free()
     barrier()
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
-        o_h, dd = gpu.delta_scan(hq, hk, hv, ha, hb, b, t, h, dh)
-        dqkv_h, dgate_h = gpu.delta_bwd_dev(dd, hdo, hqn, hkn)
+        _, dd = gpu.delta_scan(hq, hk, hv, ha, hb, b, t, h, dh, out=o_h)
+        gpu.delta_bwd_dev(dd, hdo, hqn, hkn, out=(dqkv_h, dgate_h))
         dd.free()
     barrier()
     e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
