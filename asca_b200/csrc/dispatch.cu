@@ -150,3 +150,60 @@ extern "C" int asca_moe_dispatch(asca_ctx* ctx, const uint32_t* ids, int64_t N, 
     ASCA_CHECK_LAUNCH(ctx);
     return ASCA_OK;
 }
+
+// ------------------------------------------------------------------ allocation-free variant
+// Scratch for asca_moe_dispatch_noalloc: the per-segment expert histogram that the three
+// kernels above pass between each other. It lives in the library's device image, so every GPU
+// that loads the library carries these 256 KiB until the process exits.
+constexpr int NOALLOC_MAX_INTS = 65536;  // (segments rounded up to a multiple of 4) * E
+static __device__ __align__(256) int32_t g_dispatch_scratch[NOALLOC_MAX_INTS];
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+int32_t* g_scratch_addr[MAX_DEVICES];  // device address of g_dispatch_scratch, per device ordinal
+}  // namespace
+
+extern "C" int asca_moe_dispatch_noalloc(asca_ctx* ctx, const uint32_t* ids, int64_t N, int64_t E, int32_t* perm,
+                                         int32_t* offsets, int32_t* route) {
+    if (!ctx) return ASCA_ERR_ARG;
+    ASCA_REQUIRE(ctx, ids && perm && offsets && N >= 0 && E >= 1, "moe_dispatch_noalloc: bad arguments");
+    ASCA_REQUIRE(ctx, E <= MAX_E, "moe_dispatch_noalloc: at most %d experts", MAX_E);
+    ASCA_REQUIRE(ctx, N < ((int64_t)1 << 31), "moe_dispatch_noalloc: N must fit int32");
+    ASCA_REQUIRE(ctx, ctx->device >= 0 && ctx->device < MAX_DEVICES, "moe_dispatch_noalloc: device ordinal out of range");
+    const int64_t n_seg = ceil_div64(N, SEG);
+    const int64_t n_blk = ceil_div64(n_seg, WARPS);
+    if (n_blk * WARPS * E > NOALLOC_MAX_INTS)
+        return asca_fail(ctx, ASCA_ERR_ARG,
+                         "moe_dispatch_noalloc: ceil(N/%d) rounded up to a multiple of %d, times E, is %lld and must "
+                         "not exceed %d (N=%lld, E=%lld); use asca_moe_dispatch for larger problems",
+                         SEG, WARPS, (long long)(n_blk * WARPS * E), NOALLOC_MAX_INTS, (long long)N, (long long)E);
+    if (N == 0) {
+        ASCA_CUDA(ctx, cudaMemsetAsync(offsets, 0, (size_t)(E + 1) * 4, ctx->stream));
+        return ASCA_OK;
+    }
+    // One-time set-up per device: the array's name is only a host-side stand-in here, so ask the
+    // runtime for its address on this device, with this device current.
+    if (!g_scratch_addr[ctx->device]) {
+        int cur = -1;
+        ASCA_CUDA(ctx, cudaGetDevice(&cur));
+        if (cur != ctx->device) ASCA_CUDA(ctx, cudaSetDevice(ctx->device));
+        void* addr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&addr, g_dispatch_scratch);
+        if (cur != ctx->device) cudaSetDevice(cur);
+        if (e != cudaSuccess || !addr)
+            return asca_fail(ctx, ASCA_ERR_CUDA, "moe_dispatch_noalloc: cudaGetSymbolAddress failed: %s",
+                             cudaGetErrorString(e));
+        g_scratch_addr[ctx->device] = (int32_t*)addr;
+    }
+    int32_t* counts = g_scratch_addr[ctx->device];
+    // Nothing in the scratch has to start at zero: hist_kernel overwrites every entry that
+    // scan_kernel and place_kernel read (segments 0 .. n_seg-1), whatever the last call left.
+    const size_t smem = (size_t)WARPS * E * 4;
+    hist_kernel<<<(unsigned)n_blk, WARPS * 32, smem, ctx->stream>>>(ids, N, (int)E, counts, route);
+    ASCA_CHECK_LAUNCH(ctx);
+    scan_kernel<<<1, 1024, 0, ctx->stream>>>(counts, (int)n_seg, (int)E, offsets);
+    ASCA_CHECK_LAUNCH(ctx);
+    place_kernel<<<(unsigned)n_blk, WARPS * 32, smem, ctx->stream>>>(ids, N, (int)E, counts, perm);
+    ASCA_CHECK_LAUNCH(ctx);
+    return ASCA_OK;
+}

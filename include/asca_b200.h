@@ -191,6 +191,24 @@ int asca_moe_dispatch(asca_ctx* ctx, const uint32_t* ids, int64_t N, int64_t E, 
                       int32_t* offsets, int32_t* route);
 int asca_moe_dispatch_host(asca_ctx* ctx, const uint32_t* ids, int64_t N, int64_t E,
                            int32_t* perm, int32_t* offsets, int32_t* route);
+/* The same dispatch for callers that must not allocate device memory while they run: a
+ * serving loop that has handed all of HBM to its own arena at start-up (so a later cudaMalloc
+ * fails or stalls the device), or a host whose policy forbids cudaMalloc / cudaFree once
+ * requests are flowing because both synchronise the GPU. asca_moe_dispatch may grow the
+ * context's scratch with cudaMalloc; this variant keeps its scratch (the per-segment expert
+ * histogram) in a fixed 256 KiB array inside the library's device image instead, and calls no
+ * cudaMalloc, cudaFree or other allocating routine. It has no counterpart in the reference.
+ *   - Limit: ceil(N/1024), rounded up to a multiple of 4, times E must be <= 65536 (e.g.
+ *     N <= 1,048,576 tokens at E = 64); larger requests return ASCA_ERR_ARG with a message.
+ *   - The first call on each device looks the array's device address up (a host-side set-up
+ *     step); make that first call before starting any stream capture.
+ *   - Every call on a device shares the one array, and it keeps the previous call's contents
+ *     (each call overwrites all entries it later reads, so nothing needs clearing). Two calls
+ *     that overlap on the same GPU -- different streams or contexts -- race on it; serialise
+ *     them.
+ * Inputs, outputs and results are exactly those of asca_moe_dispatch. */
+int asca_moe_dispatch_noalloc(asca_ctx* ctx, const uint32_t* ids, int64_t N, int64_t E,
+                              int32_t* perm, int32_t* offsets, int32_t* route);
 /* Expert FFN forward: Gpu::moe_forward_dev (rust/src/cuda/mod.rs:523-607), math of
  * rust/src/model.rs:237-293. xn (N,d) normalised rows; w1 (d, E*F), b1 (E*F) f32, w2 (E*F, d),
  * b2 (d) f32; out (N,d) f32 in token order. pre_p / hid_p (N,F): pre-activation and SiLU
