@@ -4,9 +4,10 @@ A ctypes front-end to ``asca_oracle.cpp``, the C++ restatement of the reference'
 path. Only the tests, the smoke check and the benchmark's CPU-baseline leg import this
 package; the CUDA library and the ``asca_b200`` package never do.
 
-Parity is unpinned by fixtures: the reference has no golden vectors for this path and
-cannot be built where this runs (Rust). The oracle is validated by the reference's own
-self-consistency gates restated in ``tests/test_oracle_*.py``.
+The reference has no golden vectors for this path and its Rust crate cannot be built where
+this runs. The oracle is pinned on a GPU against the reference's own CUDA kernels
+(``oracle/build_ref.py``, ``tests/test_reference_pin.py``) and by the reference's own
+self-consistency gates restated in ``tests/test_oracle_gates.py``.
 """
 from __future__ import annotations
 

@@ -4,12 +4,15 @@
 // THIS IS TEST INFRASTRUCTURE, NOT PRODUCT CODE. Only the test suite, the smoke check and
 // the benchmark's CPU-baseline leg may load it; the CUDA library never calls into it.
 //
-// PARITY UNPINNED BY FIXTURES: the reference (MythEclipse/asca, a dependency-free Rust
-// crate) ships no golden vectors or known-answer tests for this path, and no Rust toolchain
-// exists where this oracle is built, so the reference binary cannot be run to produce any.
-// The oracle is instead validated by re-running the reference's own self-consistency gates
-// on it (finite-difference gradcheck of the block and of the whole model, batch parity,
-// decode parity, the independent scalar scan of `asca gpu`) -- see tests/test_oracle_*.py.
+// PINNING: the reference (MythEclipse/asca, a dependency-free Rust crate) ships no golden vectors
+// or known-answer tests for this path and cannot be built where this oracle is built (no Rust
+// toolchain). The oracle is pinned (a) on a GPU against the reference's own CUDA kernels,
+// compiled unmodified by oracle/build_ref.py (tests/test_reference_pin.py: delta forward and
+// backward, GEMMs, RMSNorm, SiLU, cross-entropy), and (b) by re-running the reference's own
+// self-consistency gates on it (tests/test_oracle_gates.py: finite-difference gradchecks, batch
+// parity, decode parity, the independent scalar scan of `asca gpu`). The hash dispatch, the
+// composed MoE layer, AdamW and the model glue have no reference GPU kernel or fixture and are
+// pinned by (b) only.
 //
 // Every function cites the reference lines it follows (paths relative to the reference
 // repository root). Arithmetic order follows the reference: f32 throughout, fused
