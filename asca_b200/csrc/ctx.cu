@@ -85,6 +85,13 @@ int asca_ctx_set_stream(asca_ctx* ctx, void* s) {
 int asca_ctx_sync(asca_ctx* ctx) {
     if (!ctx) return ASCA_ERR_ARG;
     ASCA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    // kernels with bounded waits report a give-up through this word
+    int word = 0;
+    ASCA_CUDA(ctx, cudaMemcpy(&word, ctx->err_word, sizeof(int), cudaMemcpyDeviceToHost));
+    if (word != 0) {
+        cudaMemset(ctx->err_word, 0, sizeof(int));
+        return asca_fail(ctx, ASCA_ERR_DEVICE, "a kernel gave up on a bounded wait (code %d)", word);
+    }
     return ASCA_OK;
 }
 

@@ -1,0 +1,386 @@
+// bf16 GEMM on the 5th-generation tensor cores (tcgen05) for sm_100a.
+//
+// One CTA computes a 128 x 128 f32 output tile. Warp roles (192 threads):
+//   warp 0      TMA producer: one thread streams 128x64 A and 64x128 B bf16 tiles (128-byte
+//               swizzle, plain non-multicast cp.async.bulk.tensor) through a 3-stage ring of
+//               mbarriers;
+//   warp 1      allocates 128 TMEM columns, and one thread issues tcgen05.mma (M128 N128 K16,
+//               4 per k-tile) with the accumulator in TMEM; tcgen05.commit releases ring slots
+//               and finally signals the epilogue;
+//   warps 2-5   epilogue: tcgen05.ld the accumulator (each warp its 32-lane quarter), apply
+//               bias / SiLU / SiLU' / accumulate, store f32 (and an optional bf16 second output),
+//               optionally through a row map (the un-permute scatter of the MoE combine).
+// 96 KiB of shared memory per CTA lets two CTAs share an SM, so one CTA's epilogue overlaps the
+// other's main loop.
+//
+// Operand majorness covers the three modes without any transposed copy: NN = A K-major, B
+// MN-major; TN = A MN-major, B MN-major; NT = A K-major, B K-major. Expert grouping: GROUP_M
+// tiles the rows of each expert's segment (rows past the segment end are computed and not
+// stored); GROUP_K runs the k-loop over an expert's rows and zeroes the ragged last k-tile in
+// shared memory before it is multiplied.
+//
+// Every mbarrier wait is bounded; a wait that runs out raises an error word that the host reads
+// back as ASCA_ERR_DEVICE, and the CTA still frees its TMEM and exits.
+#include "gemm_tc.cuh"
+#include "tc_common.cuh"
+
+namespace gemm_tc {
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 64, STAGES = 3, THREADS = 192;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int TMEM_COLS = 128;
+constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+
+struct KP {
+    float* C;
+    int64_t ldc;
+    int M, N, K;
+    const float* bias;
+    int accumulate;
+    const int32_t* c_idx;
+    const int32_t* offsets;
+    int n_groups, group_dim;
+    int b_goff_inner, b_goff_outer;
+    int64_t c_gstride, bias_gstride;
+    int epi;
+    const float* aux;
+    int64_t ldaux;
+    __nv_bfloat16* C2;
+    int64_t ldc2;
+    int* err_word;
+};
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
+__device__ __forceinline__ float silu_grad_f(float p) {
+    float sg = 1.0f / (1.0f + expf(-p));
+    return sg * (1.0f + p * (1.0f - sg));
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA,
+                                                          const __grid_constant__ CUtensorMap mapB, const KP p) {
+    constexpr bool A_MN = (MODE == ASCA_TN);   // A operand MN-major
+    constexpr bool B_MN = (MODE != ASCA_NT);   // B operand MN-major
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + STAGES * STAGE_BYTES);
+    uint64_t* empty = full + STAGES;
+    uint64_t* tmem_full = empty + STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    int* sh_info = const_cast<int*>(abort_flag) + 1;  // [0] group, [1] tile within group
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_n = (p.N + BN - 1) / BN;
+
+    // ---- which (group, tile) is this CTA?
+    if (warp == 0) {
+        int found_g = -1, found_t = 0;
+        if (p.group_dim == GROUP_NONE) {
+            found_g = 0;
+            found_t = blockIdx.x;
+        } else {
+            int base = 0;
+            for (int g0 = 0; g0 < p.n_groups && found_g < 0; g0 += 32) {
+                const int g = g0 + lane;
+                int cnt = 0;
+                if (g < p.n_groups) {
+                    const int n_g = p.offsets[g + 1] - p.offsets[g];
+                    cnt = p.group_dim == GROUP_M ? ((n_g + BM - 1) / BM) * tiles_n : ((p.M + BM - 1) / BM) * tiles_n;
+                }
+                int inc = cnt;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    int n = __shfl_up_sync(0xffffffffu, inc, o);
+                    if (lane >= o) inc += n;
+                }
+                const int start = base + inc - cnt;
+                const bool mine = (int)blockIdx.x >= start && (int)blockIdx.x < start + cnt;
+                const unsigned m = __ballot_sync(0xffffffffu, mine);
+                if (m) {
+                    const int src = __ffs(m) - 1;
+                    found_g = __shfl_sync(0xffffffffu, g, src);
+                    found_t = (int)blockIdx.x - __shfl_sync(0xffffffffu, start, src);
+                }
+                base += __shfl_sync(0xffffffffu, inc, 31);
+            }
+        }
+        if (lane == 0) {
+            sh_info[0] = found_g;
+            sh_info[1] = found_t;
+            *abort_flag = 0;
+            for (int s = 0; s < STAGES; ++s) {
+                tc::mbar_init(&full[s], 1);
+                tc::mbar_init(&empty[s], 1);
+            }
+            tc::mbar_init(tmem_full, 1);
+            tc::mbar_fence_init();
+            tc::prefetch_tensormap(&mapA);
+            tc::prefetch_tensormap(&mapB);
+        }
+    }
+    __syncthreads();
+    const int g = sh_info[0];
+    if (g < 0) return;  // surplus CTA of the upper-bound grid (uniform: no TMEM held yet)
+    if (warp == 1) tc::tmem_alloc(tmem_slot, TMEM_COLS);
+    tc::tcgen05_fence_before();
+    __syncthreads();
+    tc::tcgen05_fence_after();
+    const uint32_t tmem_acc = *tmem_slot;
+
+    const int tile_n = sh_info[1] % tiles_n, tile_m = sh_info[1] / tiles_n;
+    const int m0 = tile_m * BM, n0 = tile_n * BN;
+    int lo = 0, M = p.M, K = p.K;
+    if (p.group_dim != GROUP_NONE) {
+        lo = p.offsets[g];
+        const int n_g = p.offsets[g + 1] - lo;
+        if (p.group_dim == GROUP_M) M = n_g; else K = n_g;
+    }
+    const int num_k = (K + BK - 1) / BK;
+    const int row_base_m = p.group_dim == GROUP_M ? lo : 0;   // added to A/C row coordinates
+    const int row_base_k = p.group_dim == GROUP_K ? lo : 0;   // added to k-row coordinates (TN)
+    const int b_in = g * p.b_goff_inner, b_out = g * p.b_goff_outer;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            for (int kt = 0; kt < num_k; ++kt) {
+                const int s = kt % STAGES;
+                if (kt >= STAGES &&
+                    !tc::mbar_wait(&empty[s], ((kt / STAGES) - 1) & 1, abort_flag, p.err_word, 101))
+                    break;
+                uint8_t* a_s = tiles + s * STAGE_BYTES;
+                uint8_t* b_s = a_s + A_BYTES;
+                tc::mbar_expect_tx(&full[s], STAGE_BYTES);
+                const int k0 = kt * BK;
+                if (A_MN) {   // memory (k rows x M): two boxes of 64 columns
+                    tc::tma_load_2d(a_s, &mapA, m0, row_base_k + k0, &full[s]);
+                    tc::tma_load_2d(a_s + 8192, &mapA, m0 + 64, row_base_k + k0, &full[s]);
+                } else {      // memory (rows x K): one box 64 k x 128 rows
+                    tc::tma_load_2d(a_s, &mapA, k0, row_base_m + m0, &full[s]);
+                }
+                if (B_MN) {   // memory (k rows x N)
+                    const int kr = (MODE == ASCA_TN ? row_base_k : 0) + k0 + b_out;
+                    tc::tma_load_2d(b_s, &mapB, n0 + b_in, kr, &full[s]);
+                    tc::tma_load_2d(b_s + 8192, &mapB, n0 + 64 + b_in, kr, &full[s]);
+                } else {      // memory (N rows x K)
+                    tc::tma_load_2d(b_s, &mapB, k0 + b_in, n0 + b_out, &full[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        constexpr uint32_t IDESC = tc::idesc_bf16_f32(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+        bool ok = true;
+        for (int kt = 0; kt < num_k && ok; ++kt) {
+            const int s = kt % STAGES;
+            // lane 0 polls, the verdict is broadcast so the warp stays converged
+            int got = 0;
+            if (lane == 0) got = tc::mbar_wait(&full[s], (kt / STAGES) & 1, abort_flag, p.err_word, 102) ? 1 : 0;
+            ok = __shfl_sync(0xffffffffu, got, 0) != 0;
+            if (!ok) break;
+            tc::tcgen05_fence_after();
+            uint8_t* a_s = tiles + s * STAGE_BYTES;
+            uint8_t* b_s = a_s + A_BYTES;
+            if (p.group_dim == GROUP_K && (kt + 1) * BK > K) {
+                // ragged last k-tile of this expert: rows >= K - kt*BK belong to the next expert
+                const int valid = K - kt * BK;
+                const int lines = (BK - valid) * 2;  // 128-byte lines in the two A boxes
+                for (int i = lane; i < lines * 8; i += 32) {
+                    const int line = i >> 3, chunk = i & 7;
+                    const int h = line / (BK - valid), kr = valid + line % (BK - valid);
+                    *reinterpret_cast<uint4*>(a_s + h * 8192 + kr * 128 + chunk * 16) = make_uint4(0, 0, 0, 0);
+                }
+                tc::fence_proxy_async_smem();
+                __syncwarp();
+            }
+            if (lane == 0) {
+                const uint32_t a_addr = tc::smem_u32(a_s), b_addr = tc::smem_u32(b_s);
+#pragma unroll
+                for (int k16 = 0; k16 < BK / 16; ++k16) {
+                    const uint64_t ad = A_MN ? tc::smem_desc_sw128(a_addr + k16 * 2048, 8192, 1024)
+                                             : tc::smem_desc_sw128(a_addr + k16 * 32, 16, 1024);
+                    const uint64_t bd = B_MN ? tc::smem_desc_sw128(b_addr + k16 * 2048, 8192, 1024)
+                                             : tc::smem_desc_sw128(b_addr + k16 * 32, 16, 1024);
+                    tc::umma_bf16(tmem_acc, ad, bd, IDESC, (kt > 0 || k16 > 0) ? 1u : 0u);
+                }
+                tc::umma_commit(&empty[s]);                 // slot free once these MMAs retire
+                if (kt == num_k - 1) tc::umma_commit(tmem_full);
+            }
+            __syncwarp();
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 2..5)
+        int got = 1;
+        if (num_k > 0 && lane == 0) got = tc::mbar_wait(tmem_full, 0, abort_flag, p.err_word, 103) ? 1 : 0;
+        const bool ok = __shfl_sync(0xffffffffu, got, 0) != 0;  // uniform: tcgen05.ld below is warp-aligned
+        tc::tcgen05_fence_after();
+        const int q = warp & 3;                 // TMEM lane quarter this warp may read
+        const int m = m0 + q * 32 + lane;
+        const bool row_ok = ok && m < M;
+        const int64_t lr = (int64_t)row_base_m + m;
+        int64_t cr = lr;
+        if (row_ok && p.c_idx) cr = p.c_idx[lr];
+        float* crow = p.C + (p.group_dim == GROUP_K ? (int64_t)g * p.c_gstride : 0) + cr * p.ldc;
+        const float* bias = p.bias ? p.bias + (int64_t)g * p.bias_gstride : nullptr;
+        const bool vec_ok = ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
+                            ((p.c_gstride & 3) == 0);
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+            uint32_t r[32];
+            if (num_k > 0 && ok) {
+                tc::tmem_ld_32x32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
+                tc::tmem_ld_wait();
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) r[j] = 0u;
+            }
+            const int nb = n0 + c * 32;
+            if (!row_ok || nb >= p.N) continue;
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+            const bool full_chunk = nb + 32 <= p.N;
+            if (bias) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (full_chunk || nb + j < p.N) v[j] += bias[nb + j];
+            }
+            if (p.epi == EPI_SILU_BWD) {
+                const float* ax = p.aux + lr * p.ldaux + nb;
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (full_chunk || nb + j < p.N) v[j] *= silu_grad_f(ax[j]);
+            }
+            if (full_chunk && vec_ok) {
+                float4* dst = reinterpret_cast<float4*>(crow + nb);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    float4 o = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                    if (p.accumulate) {
+                        const float4 old = dst[j];
+                        o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                        v[4 * j] = o.x; v[4 * j + 1] = o.y; v[4 * j + 2] = o.z; v[4 * j + 3] = o.w;
+                    }
+                    dst[j] = o;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (nb + j < p.N) {
+                        if (p.accumulate) v[j] += crow[nb + j];
+                        crow[nb + j] = v[j];
+                    }
+            }
+            if (p.C2) {
+                __nv_bfloat16* c2 = p.C2 + lr * p.ldc2 + nb;
+                if (full_chunk && (p.ldc2 & 7) == 0 && (reinterpret_cast<uintptr_t>(p.C2) & 15) == 0) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int t = 0; t < 4; ++t) {
+                            float x0 = v[8 * j + 2 * t], x1 = v[8 * j + 2 * t + 1];
+                            if (p.epi == EPI_SILU) { x0 = silu_f(x0); x1 = silu_f(x1); }
+                            __nv_bfloat162 h2 = __floats2bfloat162_rn(x0, x1);
+                            w[t] = *reinterpret_cast<uint32_t*>(&h2);
+                        }
+                        reinterpret_cast<uint4*>(c2)[j] = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (nb + j < p.N) c2[j] = __float2bfloat16(p.epi == EPI_SILU ? silu_f(v[j]) : v[j]);
+                }
+            }
+        }
+    }
+    // ---- teardown: everyone meets, then the allocating warp frees TMEM
+    tc::tcgen05_fence_before();
+    __syncthreads();
+    if (*abort_flag) __nanosleep(20000);  // let copies already in flight land before the CTA exits
+    if (warp == 1) tc::tmem_dealloc(tmem_acc, TMEM_COLS);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// 2-D bf16 tensor map: `cols` contiguous elements per row, `rows` rows, row pitch `ld` elements.
+bool make_map(CUtensorMap* m, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_cols, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+bool supported(const Args& a) {
+    if (!encode_fn()) return false;
+    if ((reinterpret_cast<uintptr_t>(a.A) & 15) || (reinterpret_cast<uintptr_t>(a.B) & 15)) return false;
+    if ((a.lda & 7) || (a.ldb & 7)) return false;                       // row pitch multiple of 16 bytes
+    if ((a.b_goff_inner & 7)) return false;                             // TMA inner coordinate: 16-byte aligned
+    if (a.a_rows <= 0 || a.b_rows <= 0 || a.a_cols <= 0 || a.b_cols <= 0) return false;
+    // grouped coordinate offsets must not let a ragged tile read a neighbouring expert's k range
+    if (a.group_dim == GROUP_M && a.mode == ASCA_NT && a.b_goff_inner != 0 && (a.K % BK) != 0) return false;
+    if (a.group_dim == GROUP_M && a.mode == ASCA_NN && a.b_goff_outer != 0 && (a.K % BK) != 0) return false;
+    if (a.group_dim == GROUP_K && a.mode != ASCA_TN) return false;
+    if (a.group_dim == GROUP_M && a.mode == ASCA_TN) return false;
+    return true;
+}
+
+int launch(asca_ctx* ctx, const Args& a) {
+    CUtensorMap mapA, mapB;
+    bool ok;
+    if (a.mode == ASCA_TN) ok = make_map(&mapA, a.A, a.a_rows, a.a_cols, a.lda, 64, 64);
+    else ok = make_map(&mapA, a.A, a.a_rows, a.a_cols, a.lda, 64, 128);
+    if (a.mode == ASCA_NT) ok = ok && make_map(&mapB, a.B, a.b_rows, a.b_cols, a.ldb, 64, 128);
+    else ok = ok && make_map(&mapB, a.B, a.b_rows, a.b_cols, a.ldb, 64, 64);
+    if (!ok) return asca_fail(ctx, ASCA_ERR_CUDA, "gemm_tc: cuTensorMapEncodeTiled failed");
+    KP p{};
+    p.C = a.C; p.ldc = a.ldc; p.M = a.M; p.N = a.N; p.K = a.K;
+    p.bias = a.bias; p.accumulate = a.accumulate; p.c_idx = a.c_idx;
+    p.offsets = a.offsets; p.n_groups = a.n_groups; p.group_dim = a.group_dim;
+    p.b_goff_inner = a.b_goff_inner; p.b_goff_outer = a.b_goff_outer;
+    p.c_gstride = a.c_gstride; p.bias_gstride = a.bias_gstride;
+    p.epi = a.epi; p.aux = a.aux; p.ldaux = a.ldaux; p.C2 = a.C2; p.ldc2 = a.ldc2;
+    p.err_word = ctx->err_word;
+    const int64_t tn = (a.N + BN - 1) / BN;
+    int64_t grid;
+    if (a.group_dim == GROUP_NONE) grid = ((int64_t)(a.M + BM - 1) / BM) * tn;
+    else if (a.group_dim == GROUP_M) grid = (a.total_rows / BM + a.n_groups) * tn;
+    else grid = (int64_t)a.n_groups * ((a.M + BM - 1) / BM) * tn;
+    if (grid <= 0) return ASCA_OK;
+    auto go = [&](auto kern) -> cudaError_t {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+        if (e != cudaSuccess) return e;
+        kern<<<(unsigned)grid, THREADS, SMEM_BYTES, ctx->stream>>>(mapA, mapB, p);
+        return cudaGetLastError();
+    };
+    cudaError_t e = a.mode == ASCA_NN ? go(gemm_tc_kernel<ASCA_NN>)
+                    : a.mode == ASCA_TN ? go(gemm_tc_kernel<ASCA_TN>) : go(gemm_tc_kernel<ASCA_NT>);
+    ASCA_CUDA(ctx, e);
+    ctx->launches++;
+    return ASCA_OK;
+}
+
+}  // namespace gemm_tc

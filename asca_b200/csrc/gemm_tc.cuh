@@ -1,0 +1,45 @@
+// bf16 tensor-core GEMM for sm_100a: TMA-fed, tcgen05.mma with the f32 accumulator in TMEM.
+// Interface shared by gemm.cu (dense) and moe.cu (grouped expert products).
+#pragma once
+#include "common.cuh"
+
+namespace gemm_tc {
+
+enum { EPI_NONE = 0, EPI_SILU = 1, EPI_SILU_BWD = 2 };
+enum { GROUP_NONE = 0, GROUP_M = 1, GROUP_K = 2 };
+
+struct Args {
+    int mode;                 // ASCA_NN / ASCA_TN / ASCA_NT
+    const void* A;            // bf16; NN/NT: (rowsA x K) row-major, TN: (rowsK x M) row-major
+    const void* B;            // bf16; NN/TN: (rowsK x colsB) row-major, NT: (rowsN x K) row-major
+    int64_t lda, ldb;         // elements
+    int64_t a_rows, b_rows;   // memory rows of A and B (tensor-map bounds)
+    int64_t a_cols, b_cols;   // memory columns of A and B
+    float* C;
+    int64_t ldc;
+    int M, N, K;              // per-group problem (GROUP_M: M ignored, GROUP_K: K ignored)
+    const float* bias;        // per output column, nullable
+    int accumulate;
+    const int32_t* c_idx;     // optional logical-row -> memory-row map for C
+    // grouping
+    const int32_t* offsets;   // device, n_groups + 1
+    int n_groups;
+    int group_dim;
+    int64_t total_rows;       // sum of group sizes (host upper bound for the GROUP_M grid)
+    int b_goff_inner, b_goff_outer;  // B tensor-map coordinate offsets per group (elements / rows)
+    int64_t c_gstride, bias_gstride; // C / bias element offsets per group
+    // epilogue
+    int epi;
+    const float* aux;         // EPI_SILU_BWD: pre-activation, rows follow the logical row
+    int64_t ldaux;
+    __nv_bfloat16* C2;        // EPI_SILU: silu(C); EPI_SILU_BWD: bf16 copy of C; nullable
+    int64_t ldc2;
+};
+
+// True when the tensor-core kernel can take this problem (alignment and divisibility rules of
+// TMA and of the grouped coordinate offsets); otherwise the caller uses the SIMT kernel.
+bool supported(const Args& a);
+// Enqueues the kernel on ctx->stream. Returns ASCA_OK or an error code.
+int launch(asca_ctx* ctx, const Args& a);
+
+}  // namespace gemm_tc

@@ -6,6 +6,9 @@
 // the row gather is fused into the operand load, bias + SiLU (forward) and SiLU' (backward)
 // into the epilogue, and the un-permute scatter into the output store.
 #include "gemm_simt.cuh"
+#include "gemm_tc.cuh"
+
+bool asca_tc_enabled();  // gemm.cu
 
 namespace {
 
@@ -76,6 +79,136 @@ __global__ void __launch_bounds__(256) moe_step_kernel(const float* __restrict__
     }
 }
 
+
+// dst[r,:] = src[idx[r],:] for bf16 rows (cols % 8 == 0): 16-byte copies, one warp per row.
+__global__ void __launch_bounds__(256) gather_rows_bf16_kernel(const __nv_bfloat16* __restrict__ src,
+                                                               const int32_t* __restrict__ idx,
+                                                               __nv_bfloat16* __restrict__ dst, int64_t n_rows,
+                                                               int cols) {
+    const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t r = (int64_t)blockIdx.x * 8 + w;
+    if (r >= n_rows) return;
+    const uint4* s = reinterpret_cast<const uint4*>(src + (int64_t)idx[r] * cols);
+    uint4* d = reinterpret_cast<uint4*>(dst + r * cols);
+    for (int c = lane; c < cols / 8; c += 32) d[c] = s[c];
+}
+// dst[r,:] = bf16(src[idx[r],:]) for f32 rows (cols % 4 == 0).
+__global__ void __launch_bounds__(256) gather_rows_f32_to_bf16_kernel(const float* __restrict__ src,
+                                                                      const int32_t* __restrict__ idx,
+                                                                      __nv_bfloat16* __restrict__ dst, int64_t n_rows,
+                                                                      int cols) {
+    const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t r = (int64_t)blockIdx.x * 8 + w;
+    if (r >= n_rows) return;
+    const float4* s = reinterpret_cast<const float4*>(src + (int64_t)idx[r] * cols);
+    uint2* d = reinterpret_cast<uint2*>(dst + r * cols);
+    for (int c = lane; c < cols / 4; c += 32) {
+        const float4 v = s[c];
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        d[c] = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+    }
+}
+
+inline bool tc_shapes_ok(int64_t d, int64_t F) { return asca_tc_enabled() && d % 64 == 0 && F % 64 == 0; }
+
+inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+
+// Tensor-core forward: permute xn once, then two grouped tcgen05 GEMMs.
+int moe_fwd_tc(asca_ctx* ctx, const __nv_bfloat16* xn, const __nv_bfloat16* w1, const float* b1,
+               const __nv_bfloat16* w2, const float* b2, const int32_t* perm, const int32_t* offsets, int64_t N,
+               int64_t d, int64_t F, int64_t E, float* out, float* pre_p, __nv_bfloat16* hid_p) {
+    void* ws;
+    ASCA_TRY(asca_workspace(ctx, align256((size_t)N * d * 2) + 256, &ws));
+    __nv_bfloat16* xp = (__nv_bfloat16*)ws;
+    gather_rows_bf16_kernel<<<(unsigned)ceil_div64(N, 8), 256, 0, ctx->stream>>>(xn, perm, xp, N, (int)d);
+    ASCA_CHECK_LAUNCH(ctx);
+    gemm_tc::Args a{};
+    a.mode = ASCA_NN;
+    a.A = xp; a.lda = d; a.a_rows = N; a.a_cols = d;
+    a.B = w1; a.ldb = E * F; a.b_rows = d; a.b_cols = E * F; a.b_goff_inner = (int)F;
+    a.C = pre_p; a.ldc = F; a.N = (int)F; a.K = (int)d;
+    a.bias = b1; a.bias_gstride = F;
+    a.offsets = offsets; a.n_groups = (int)E; a.group_dim = gemm_tc::GROUP_M; a.total_rows = N;
+    a.epi = gemm_tc::EPI_SILU; a.C2 = hid_p; a.ldc2 = F;
+    if (!gemm_tc::supported(a)) return ASCA_ERR_UNSUPPORTED;
+    ASCA_TRY(gemm_tc::launch(ctx, a));
+    gemm_tc::Args b{};
+    b.mode = ASCA_NN;
+    b.A = hid_p; b.lda = F; b.a_rows = N; b.a_cols = F;
+    b.B = w2; b.ldb = d; b.b_rows = E * F; b.b_cols = d; b.b_goff_outer = (int)F;
+    b.C = out; b.ldc = d; b.N = (int)d; b.K = (int)F; b.c_idx = perm;
+    b.bias = b2; b.bias_gstride = 0;
+    b.offsets = offsets; b.n_groups = (int)E; b.group_dim = gemm_tc::GROUP_M; b.total_rows = N;
+    if (!gemm_tc::supported(b)) return ASCA_ERR_UNSUPPORTED;
+    return gemm_tc::launch(ctx, b);
+}
+
+// Tensor-core backward: permuted bf16 copies of xn and dout, then four grouped tcgen05 GEMMs.
+int moe_bwd_tc(asca_ctx* ctx, const __nv_bfloat16* xn, const __nv_bfloat16* w1, const __nv_bfloat16* w2,
+               const float* pre_p, const __nv_bfloat16* hid_p, const float* dout, const int32_t* perm,
+               const int32_t* offsets, int64_t N, int64_t d, int64_t F, int64_t E, float* d_w1, float* d_b1,
+               float* d_w2, float* d_b2, float* dxn) {
+    cudaStream_t s = ctx->stream;
+    const size_t b_xp = align256((size_t)N * d * 2), b_dp = align256((size_t)N * F * 4), b_dp16 = align256((size_t)N * F * 2);
+    void* ws;
+    ASCA_TRY(asca_workspace(ctx, 2 * b_xp + b_dp + b_dp16 + 256, &ws));
+    char* w = (char*)ws;
+    __nv_bfloat16* xp = (__nv_bfloat16*)w;
+    __nv_bfloat16* dout_p = (__nv_bfloat16*)(w + b_xp);
+    float* dpre_p = (float*)(w + 2 * b_xp);
+    __nv_bfloat16* dpre16 = (__nv_bfloat16*)(w + 2 * b_xp + b_dp);
+    gather_rows_bf16_kernel<<<(unsigned)ceil_div64(N, 8), 256, 0, s>>>(xn, perm, xp, N, (int)d);
+    ASCA_CHECK_LAUNCH(ctx);
+    gather_rows_f32_to_bf16_kernel<<<(unsigned)ceil_div64(N, 8), 256, 0, s>>>(dout, perm, dout_p, N, (int)d);
+    ASCA_CHECK_LAUNCH(ctx);
+    colsum_kernel<<<dim3((unsigned)ceil_div64(d, 32), 1), 256, 0, s>>>(dout, d, nullptr, nullptr, N, (int)d, d_b2, 0);
+    ASCA_CHECK_LAUNCH(ctx);
+    {   // d_w2[eF+j, c] = sum_r hid_p[r,j] dout_p[r,c]
+        gemm_tc::Args a{};
+        a.mode = ASCA_TN;
+        a.A = hid_p; a.lda = F; a.a_rows = N; a.a_cols = F;
+        a.B = dout_p; a.ldb = d; a.b_rows = N; a.b_cols = d;
+        a.C = d_w2; a.ldc = d; a.c_gstride = F * d; a.M = (int)F; a.N = (int)d;
+        a.offsets = offsets; a.n_groups = (int)E; a.group_dim = gemm_tc::GROUP_K; a.total_rows = N;
+        if (!gemm_tc::supported(a)) return ASCA_ERR_UNSUPPORTED;
+        ASCA_TRY(gemm_tc::launch(ctx, a));
+    }
+    {   // dpre_p[r,j] = (sum_c dout_p[r,c] W2[eF+j,c]) * silu'(pre_p[r,j]), plus a bf16 copy
+        gemm_tc::Args a{};
+        a.mode = ASCA_NT;
+        a.A = dout_p; a.lda = d; a.a_rows = N; a.a_cols = d;
+        a.B = w2; a.ldb = d; a.b_rows = E * F; a.b_cols = d; a.b_goff_outer = (int)F;
+        a.C = dpre_p; a.ldc = F; a.N = (int)F; a.K = (int)d;
+        a.offsets = offsets; a.n_groups = (int)E; a.group_dim = gemm_tc::GROUP_M; a.total_rows = N;
+        a.epi = gemm_tc::EPI_SILU_BWD; a.aux = pre_p; a.ldaux = F; a.C2 = dpre16; a.ldc2 = F;
+        if (!gemm_tc::supported(a)) return ASCA_ERR_UNSUPPORTED;
+        ASCA_TRY(gemm_tc::launch(ctx, a));
+    }
+    colsum_kernel<<<dim3((unsigned)ceil_div64(F, 32), (unsigned)E), 256, 0, s>>>(dpre_p, F, nullptr, offsets, N, (int)F, d_b1, F);
+    ASCA_CHECK_LAUNCH(ctx);
+    {   // d_w1[c, eF+j] = sum_r xp[r,c] dpre16[r,j]
+        gemm_tc::Args a{};
+        a.mode = ASCA_TN;
+        a.A = xp; a.lda = d; a.a_rows = N; a.a_cols = d;
+        a.B = dpre16; a.ldb = F; a.b_rows = N; a.b_cols = F;
+        a.C = d_w1; a.ldc = E * F; a.c_gstride = F; a.M = (int)d; a.N = (int)F;
+        a.offsets = offsets; a.n_groups = (int)E; a.group_dim = gemm_tc::GROUP_K; a.total_rows = N;
+        if (!gemm_tc::supported(a)) return ASCA_ERR_UNSUPPORTED;
+        ASCA_TRY(gemm_tc::launch(ctx, a));
+    }
+    {   // dxn[perm[r], c] = sum_j dpre16[r,j] W1[c, eF+j]
+        gemm_tc::Args a{};
+        a.mode = ASCA_NT;
+        a.A = dpre16; a.lda = F; a.a_rows = N; a.a_cols = F;
+        a.B = w1; a.ldb = E * F; a.b_rows = d; a.b_cols = E * F; a.b_goff_inner = (int)F;
+        a.C = dxn; a.ldc = d; a.N = (int)d; a.K = (int)F; a.c_idx = perm;
+        a.offsets = offsets; a.n_groups = (int)E; a.group_dim = gemm_tc::GROUP_M; a.total_rows = N;
+        if (!gemm_tc::supported(a)) return ASCA_ERR_UNSUPPORTED;
+        ASCA_TRY(gemm_tc::launch(ctx, a));
+    }
+    return ASCA_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -89,6 +222,11 @@ int asca_moe_fwd(asca_ctx* ctx, const void* xn, const void* w1, const float* b1,
     ASCA_REQUIRE(ctx, dtype == ASCA_F32 || dtype == ASCA_BF16, "moe_fwd: unknown dtype");
     if (N == 0) return ASCA_OK;
     const int bf = dtype == ASCA_BF16;
+    if (bf && tc_shapes_ok(d, F)) {
+        int rc = moe_fwd_tc(ctx, (const __nv_bfloat16*)xn, (const __nv_bfloat16*)w1, b1, (const __nv_bfloat16*)w2, b2,
+                            perm, offsets, N, d, F, E, out, pre_p, (__nv_bfloat16*)hid_p);
+        if (rc != ASCA_ERR_UNSUPPORTED) return rc;
+    }
     // pre_p[r,:] = xn[perm[r],:] W1[:, eF:(e+1)F] + b1[e];  hid_p = silu(pre_p)
     gemm::Params p{};
     p.A = xn; p.lda = d; p.a_idx = perm;
@@ -131,6 +269,11 @@ int asca_moe_bwd(asca_ctx* ctx, const void* xn, const void* w1, const void* w2, 
         ASCA_CUDA(ctx, cudaMemsetAsync(d_b1, 0, (size_t)(E * F) * 4, s));
         ASCA_CUDA(ctx, cudaMemsetAsync(d_b2, 0, (size_t)d * 4, s));
         return ASCA_OK;
+    }
+    if (bf && tc_shapes_ok(d, F)) {
+        int rc = moe_bwd_tc(ctx, (const __nv_bfloat16*)xn, (const __nv_bfloat16*)w1, (const __nv_bfloat16*)w2, pre_p,
+                            (const __nv_bfloat16*)hid_p, dout, perm, offsets, N, d, F, E, d_w1, d_b1, d_w2, d_b2, dxn);
+        if (rc != ASCA_ERR_UNSUPPORTED) return rc;
     }
     // scratch: dpre_p (N x F) f32, in the permuted order
     void* ws;

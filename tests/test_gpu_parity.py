@@ -418,6 +418,60 @@ def test_moe_layer_with_norm_and_decode_step(orc, gpu):
     assert rel_err(step.cpu().numpy(), ref[0][:32]) < F32_TOL  # decode == forward rows
 
 
+@pytest.mark.parametrize("m,k,n", [(128, 64, 128), (300, 200, 264), (1000, 1032, 520), (129, 72, 8)])
+def test_bf16_tensor_core_gemm_all_modes(orc, gpu, m, k, n):
+    """bf16 operands go through the tcgen05 kernel (row pitches are multiples of 8): ragged M, N
+    and K tails, bias and accumulate, all three modes."""
+    import torch
+    from asca_b200 import ops, NN, TN, NT
+
+    rng = orc.Rng(m + k + n)
+    a, b = rng.normal((m, k)), rng.normal((k, n))
+    bias, c0 = rng.normal(n), rng.normal((m, n))
+    a16, b16 = torch.from_numpy(a).cuda().bfloat16(), torch.from_numpy(b).cuda().bfloat16()
+    ref = a16.float().cpu().numpy().astype(np.float64) @ b16.float().cpu().numpy().astype(np.float64)
+    got = ops.gemm(gpu, a16, b16, NN)
+    got_tn = ops.gemm(gpu, a16.t().contiguous(), b16, TN) if m % 8 == 0 else None
+    got_nt = ops.gemm(gpu, a16, b16.t().contiguous(), NT)
+    out = torch.from_numpy(c0.copy()).cuda()
+    ops.gemm(gpu, a16, b16, NN, bias=torch.from_numpy(bias).cuda(), out=out, accumulate=True)
+    gpu.sync()
+    assert rel_err(got.cpu().numpy(), ref) < 1e-5
+    assert rel_err(got_nt.cpu().numpy(), ref) < 1e-5
+    if got_tn is not None:
+        assert rel_err(got_tn.cpu().numpy(), ref) < 1e-5
+    assert rel_err(out.cpu().numpy(), ref + bias + c0) < 1e-5
+
+
+@pytest.mark.parametrize("n,d,F,E,vocab", [(4096, 256, 512, 16, 256), (700, 64, 128, 64, 30), (9000, 128, 192, 8, 256)])
+def test_moe_bf16_tensor_core_ragged_experts(orc, gpu, n, d, F, E, vocab):
+    """Grouped tcgen05 products: skewed loads, experts with fewer than 64 rows and empty experts."""
+    import torch
+    from asca_b200 import ops
+
+    w1, b1, w2, b2 = _moe_params(orc, 15, d, F, E)
+    rng = orc.Rng(n)
+    ids = _zipf_ids(orc, n, n) % vocab
+    xn = orc.rmsnorm(rng.normal((n, d)))[0]
+    dout = rng.normal((n, d))
+    c = lambda a: torch.from_numpy(a).cuda()
+    txn, tw1, tw2 = c(xn).bfloat16(), c(w1).bfloat16(), c(w2).bfloat16()
+    # oracle on the bf16-rounded operands, so only accumulation / intermediate rounding differs
+    xr, w1r, w2r = (t.float().cpu().numpy() for t in (txn, tw1, tw2))
+    out_ref, pre_ref, hid_ref = orc.moe_ffn_forward(xr, w1r, b1, w2r, b2, ids, F, E, want_cache=True)
+    g_ref = orc.moe_ffn_backward(xr, w1r, w2r, pre_ref, hid_ref, ids, dout, F, E)
+    perm, offsets = ops.moe_dispatch(gpu, c(ids.view(np.int32)), E)
+    out, pre_p, hid_p = ops.moe_fwd(gpu, txn, tw1, c(b1), tw2, c(b2), perm, offsets, F, E)
+    grads = ops.moe_bwd(gpu, txn, tw1, tw2, pre_p, hid_p, c(dout), perm, offsets, F, E)
+    gpu.sync()
+    pre_tok = np.empty_like(pre_ref)
+    pre_tok[perm.cpu().numpy()] = pre_p.cpu().numpy()
+    assert rel_err(pre_tok, pre_ref) < 1e-5          # f32 accumulate of identical bf16 operands
+    assert rel_err(out.cpu().numpy(), out_ref) < BF16_TOL
+    for name, got, want in zip(("d_w1", "d_b1", "d_w2", "d_b2", "dxn"), grads, g_ref):
+        assert rel_err(got.cpu().numpy(), want) < BF16_TOL, name
+
+
 # ------------------------------------------------------------------ argument errors (host side, before any launch)
 def test_bad_arguments_fail_before_launch(orc, gpu):
     import asca_b200
