@@ -94,6 +94,92 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const float* __restric
     for (int c = tir; c < cols; c += TPR) o[c] = inv * (dr[c] - xr[c] * inv * mean);
 }
 
+
+// Warp-per-row variants for rows that fit in registers (cols % 4 == 0, cols <= 128 * NV): every
+// load of the row is issued before the first use, the reduction is a warp shuffle tree, and the
+// row is read from HBM exactly once.
+template <int NV, bool RESIDUAL>
+__global__ void __launch_bounds__(256) rmsnorm_fwd_warp_kernel(const float* __restrict__ x,
+                                                               const float* __restrict__ res,
+                                                               float* __restrict__ xsum, float* __restrict__ y,
+                                                               float* __restrict__ inv_out, int64_t rows, int cols,
+                                                               float eps) {
+    const int lane = threadIdx.x & 31;
+    const int64_t r = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    const float4* xr = reinterpret_cast<const float4*>(x + r * (int64_t)cols);
+    const int n4 = cols >> 2;
+    float4 v[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = lane + 32 * i;
+        v[i] = c < n4 ? xr[c] : make_float4(0, 0, 0, 0);
+    }
+    if (RESIDUAL) {
+        const float4* rr = reinterpret_cast<const float4*>(res + r * (int64_t)cols);
+        float4* sr = reinterpret_cast<float4*>(xsum + r * (int64_t)cols);
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int c = lane + 32 * i;
+            if (c < n4) {
+                const float4 b = rr[c];
+                v[i].x += b.x; v[i].y += b.y; v[i].z += b.z; v[i].w += b.w;
+                sr[c] = v[i];
+            }
+        }
+    }
+    float acc = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) acc += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+    acc = warp_sum(acc);
+    if (y == nullptr) return;
+    const float inv = 1.0f / sqrtf(acc / (float)cols + eps);
+    if (lane == 0 && inv_out) inv_out[r] = inv;
+    float4* yr = reinterpret_cast<float4*>(y + r * (int64_t)cols);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = lane + 32 * i;
+        if (c < n4) yr[c] = make_float4(v[i].x * inv, v[i].y * inv, v[i].z * inv, v[i].w * inv);
+    }
+}
+
+template <int NV>
+__global__ void __launch_bounds__(256) rmsnorm_bwd_warp_kernel(const float* __restrict__ x,
+                                                               const float* __restrict__ dy, float* __restrict__ dx,
+                                                               int64_t rows, int cols, float eps) {
+    const int lane = threadIdx.x & 31;
+    const int64_t r = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    const float4* xr = reinterpret_cast<const float4*>(x + r * (int64_t)cols);
+    const float4* dr = reinterpret_cast<const float4*>(dy + r * (int64_t)cols);
+    const int n4 = cols >> 2;
+    float4 a[NV], g[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = lane + 32 * i;
+        a[i] = c < n4 ? xr[c] : make_float4(0, 0, 0, 0);
+        g[i] = c < n4 ? dr[c] : make_float4(0, 0, 0, 0);
+    }
+    float s2 = 0.0f, sd = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        s2 += a[i].x * a[i].x + a[i].y * a[i].y + a[i].z * a[i].z + a[i].w * a[i].w;
+        sd += g[i].x * a[i].x + g[i].y * a[i].y + g[i].z * a[i].z + g[i].w * a[i].w;
+    }
+    s2 = warp_sum(s2);
+    sd = warp_sum(sd);
+    const float inv = 1.0f / sqrtf(s2 / (float)cols + eps);
+    const float im = inv * ((sd * inv) / (float)cols);
+    float4* o = reinterpret_cast<float4*>(dx + r * (int64_t)cols);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = lane + 32 * i;
+        if (c < n4)
+            o[c] = make_float4(inv * (g[i].x - a[i].x * im), inv * (g[i].y - a[i].y * im), inv * (g[i].z - a[i].z * im),
+                               inv * (g[i].w - a[i].w * im));
+    }
+}
+
 // ------------------------------------------------------------------ gather / scatter rows
 template <bool SCATTER>
 __global__ void __launch_bounds__(256) move_rows_kernel(const float* __restrict__ src,
@@ -216,6 +302,10 @@ __global__ void __launch_bounds__(256) delta_prep_kernel(const float* __restrict
     }
 }
 
+inline bool warp_rows_ok(int64_t cols, const void* a, const void* b) {
+    return (cols & 3) == 0 && cols <= 2048 && ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15) == 0;
+}
+
 }  // namespace
 
 extern "C" {
@@ -224,6 +314,14 @@ int asca_rmsnorm_fwd(asca_ctx* ctx, const float* x, float* y, float* inv, int64_
     if (!ctx) return ASCA_ERR_ARG;
     ASCA_REQUIRE(ctx, x && y && rows >= 0 && cols > 0 && cols < (1 << 30), "rmsnorm_fwd: bad arguments");
     if (rows == 0) return ASCA_OK;
+    if (warp_rows_ok(cols, x, y)) {
+        const unsigned grid = (unsigned)ceil_div64(rows, 8);
+#define ASCA_RN(NV_) rmsnorm_fwd_warp_kernel<NV_, false><<<grid, 256, 0, ctx->stream>>>(x, nullptr, nullptr, y, inv, rows, (int)cols, eps)
+        if (cols <= 512) ASCA_RN(4); else if (cols <= 1024) ASCA_RN(8); else ASCA_RN(16);
+#undef ASCA_RN
+        ASCA_CHECK_LAUNCH(ctx);
+        return ASCA_OK;
+    }
     if (cols <= 512)
         rmsnorm_fwd_kernel<32, false><<<(unsigned)ceil_div64(rows, 8), 256, 0, ctx->stream>>>(x, nullptr, nullptr, y, inv, rows, (int)cols, eps);
     else
@@ -237,6 +335,14 @@ int asca_residual_rmsnorm(asca_ctx* ctx, const float* x, const float* yadd, floa
     if (!ctx) return ASCA_ERR_ARG;
     ASCA_REQUIRE(ctx, x && yadd && x_mid && rows >= 0 && cols > 0 && cols < (1 << 30), "residual_rmsnorm: bad arguments");
     if (rows == 0) return ASCA_OK;
+    if (warp_rows_ok(cols, x, yadd) && warp_rows_ok(cols, x_mid, xn ? xn : x_mid)) {
+        const unsigned grid = (unsigned)ceil_div64(rows, 8);
+#define ASCA_RN(NV_) rmsnorm_fwd_warp_kernel<NV_, true><<<grid, 256, 0, ctx->stream>>>(x, yadd, x_mid, xn, nullptr, rows, (int)cols, eps)
+        if (cols <= 512) ASCA_RN(4); else if (cols <= 1024) ASCA_RN(8); else ASCA_RN(16);
+#undef ASCA_RN
+        ASCA_CHECK_LAUNCH(ctx);
+        return ASCA_OK;
+    }
     if (cols <= 512)
         rmsnorm_fwd_kernel<32, true><<<(unsigned)ceil_div64(rows, 8), 256, 0, ctx->stream>>>(x, yadd, x_mid, xn, nullptr, rows, (int)cols, eps);
     else
@@ -254,6 +360,14 @@ int asca_rmsnorm_bwd(asca_ctx* ctx, const float* x, const float* dy, float* dx, 
     if (!ctx) return ASCA_ERR_ARG;
     ASCA_REQUIRE(ctx, x && dy && dx && rows >= 0 && cols > 0 && cols < (1 << 30), "rmsnorm_bwd: bad arguments");
     if (rows == 0) return ASCA_OK;
+    if (warp_rows_ok(cols, x, dy) && warp_rows_ok(cols, dx, dx)) {
+        const unsigned grid = (unsigned)ceil_div64(rows, 8);
+#define ASCA_RN(NV_) rmsnorm_bwd_warp_kernel<NV_><<<grid, 256, 0, ctx->stream>>>(x, dy, dx, rows, (int)cols, eps)
+        if (cols <= 512) ASCA_RN(4); else if (cols <= 1024) ASCA_RN(8); else ASCA_RN(16);
+#undef ASCA_RN
+        ASCA_CHECK_LAUNCH(ctx);
+        return ASCA_OK;
+    }
     if (cols <= 512)
         rmsnorm_bwd_kernel<32><<<(unsigned)ceil_div64(rows, 8), 256, 0, ctx->stream>>>(x, dy, dx, rows, (int)cols, eps);
     else

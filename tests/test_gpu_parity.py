@@ -261,6 +261,46 @@ def test_delta_bf16_mode(orc, gpu):
     assert rel_err(d_gate.cpu().numpy(), dgate_ref) < BF16_TOL
 
 
+@pytest.mark.parametrize("B,T,H", [(1, 64, 1), (2, 128, 2), (2, 200, 3), (1, 1000, 2), (3, 37, 1)])
+def test_delta_bf16_tensor_core_forward(orc, gpu, B, T, H):
+    """bf16 inputs at dh = 128 take the chunked WY/UT tcgen05 forward: outputs, final state and every
+    chunk checkpoint against the f32 recurrence on the same (bf16-rounded) inputs; ragged last chunk;
+    continuation from an initial state."""
+    import torch
+    from asca_b200 import ops
+
+    dh = 128
+    arrs = _delta_inputs(orc, 300 + T, B, T, H, dh)
+    q, k, v, alpha, beta = (torch.from_numpy(a).cuda() for a in arrs[:5])
+    q16, k16, v16 = q.bfloat16(), k.bfloat16(), v.bfloat16()
+    qr, kr, vr = (x.float().cpu().numpy() for x in (q16, k16, v16))
+    o_ref, sfin_ref, st_ref = orc.delta_scan(qr, kr, vr, arrs[3], arrs[4], B, T, H, dh, want_states=True)
+    o, s_final, ckpt = ops.delta_fwd(gpu, q16, k16, v16, alpha, beta, B, T, H, dh, chunk=64, want_final=True)
+    gpu.sync()
+    assert o.dtype == torch.bfloat16
+    assert rel_err(o.float().cpu().numpy(), o_ref) < BF16_TOL
+    assert rel_err(s_final.cpu().numpy(), sfin_ref) < BF16_TOL
+    n_ck = (T + 63) // 64
+    ck = ckpt.view(B, H, n_ck, dh, dh).cpu().numpy()
+    want = st_ref[:, :, 0:T:64].transpose(1, 0, 2, 3, 4)      # (H,B,..) -> (B,H,n_ck,dh,dh)
+    assert ck.shape == want.shape
+    assert rel_err(ck, want) < BF16_TOL
+    # continuation: second half from the first half's final state
+    if T >= 128:
+        half = (T // 128) * 64
+
+        def part(x, lo, hi):
+            return x.view(B, T, -1)[:, lo:hi].contiguous().view(B * (hi - lo), -1)
+
+        a1 = [part(x, 0, half) for x in (q16, k16, v16, alpha, beta)]
+        a2 = [part(x, half, T) for x in (q16, k16, v16, alpha, beta)]
+        o1, s1, _ = ops.delta_fwd(gpu, *a1, B, half, H, dh, want_final=True, want_ckpt=False)
+        o2, s2, _ = ops.delta_fwd(gpu, *a2, B, T - half, H, dh, s_init=s1, want_final=True, want_ckpt=False)
+        gpu.sync()
+        assert rel_err(part(o, half, T).float().cpu().numpy(), o2.float().cpu().numpy()) < 1e-2
+        assert rel_err(s2.cpu().numpy(), sfin_ref) < BF16_TOL
+
+
 @pytest.mark.parametrize("dh", [16, 32, 64, 128])
 def test_delta_decode_step(orc, gpu, dh):
     import torch
