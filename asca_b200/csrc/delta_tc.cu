@@ -37,6 +37,16 @@ struct Tiles {            // intermediate buffers, one tile per (chain, chunk)
     __nv_bfloat16* KW;    // [tile][64][DH]
     __nv_bfloat16* AA;    // [tile][64][64]
     float* GC;            // [tile] gam_C (total decay of the chunk)
+    // backward-only outputs (null in the forward)
+    __nv_bfloat16* BK;    // [tile][64][DH]  beta gam K
+    __nv_bfloat16* BV;    // [tile][64][DH]  beta V
+    __nv_bfloat16* KR;    // [tile][64][DH]  K (zero-padded copy)
+    __nv_bfloat16* QR;    // [tile][64][DH]  Q (zero-padded copy)
+    __nv_bfloat16* TP;    // [tile][64][64]  T' = (I+L)^-1 - I, row-major
+    __nv_bfloat16* KKo;   // [tile][64][64]  K K^T
+    __nv_bfloat16* QKo;   // [tile][64][64]  Q K^T
+    float* GV;            // [tile][64] cumulative log alpha
+    float* BE;            // [tile][64] beta (0 on padded steps)
 };
 
 // ------------------------------------------------------------------ pre-pass
@@ -132,6 +142,21 @@ __global__ void __launch_bounds__(PRE_THREADS) delta_prep_tc_kernel(
 #pragma unroll
         for (int e = 0; e < 8; ++e) tmp[e] = eg * kf[e];
         *reinterpret_cast<uint4*>(out.KW + (tix * 64 + t) * DH + j * 8) = tc::pack8_bf16(tmp);
+        if (out.BK) {
+            const int64_t o64 = (tix * 64 + t) * DH + j * 8;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) tmp[e] = be * gm * kf[e];
+            *reinterpret_cast<uint4*>(out.BK + o64) = tc::pack8_bf16(tmp);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) tmp[e] = be * vf[e];
+            *reinterpret_cast<uint4*>(out.BV + o64) = tc::pack8_bf16(tmp);
+            *reinterpret_cast<uint4*>(out.KR + o64) = k8;
+            *reinterpret_cast<uint4*>(out.QR + o64) = q8;
+        }
+    }
+    if (out.GV && tid < C) {
+        out.GV[tix * 64 + tid] = g_s[tid];
+        out.BE[tix * 64 + tid] = be_s[tid];
     }
     // rows 64-127 of the T' operand stay zero
     for (int i = tid; i < 8192 / 16; i += PRE_THREADS) *reinterpret_cast<uint4*>(Tp_s + 8192 + i * 16) = make_uint4(0, 0, 0, 0);
@@ -169,7 +194,23 @@ __global__ void __launch_bounds__(PRE_THREADS) delta_prep_tc_kernel(
                     const int i = cc * 32 + j;
                     Lf[t * LF_LD + i] = i < t ? bt * __expf(gt - g_s[i]) * __uint_as_float(r[j]) : 0.0f;
                 }
-            } else {          // A = lower(Gam QK), bf16 tile for the chain kernel
+                if (out.KKo) {
+                    float a[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) a[j] = __uint_as_float(r[j]);
+                    uint4* dst = reinterpret_cast<uint4*>(out.KKo + (tix * 64 + t) * 64 + cc * 32);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) dst[j] = tc::pack8_bf16(a + 8 * j);
+                }
+            } else {
+                if (out.QKo) {
+                    float a[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) a[j] = __uint_as_float(r[j]);
+                    uint4* dst = reinterpret_cast<uint4*>(out.QKo + (tix * 64 + t) * 64 + cc * 32);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) dst[j] = tc::pack8_bf16(a + 8 * j);
+                }          // A = lower(Gam QK), bf16 tile for the chain kernel
                 float a[32];
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
@@ -209,6 +250,13 @@ __global__ void __launch_bounds__(PRE_THREADS) delta_prep_tc_kernel(
     }
     tc::fence_proxy_async_smem();
     __syncthreads();
+    if (out.TP) {
+        for (int idx = tid; idx < 64 * 8; idx += PRE_THREADS) {
+            const int t = idx >> 3, jc = idx & 7;
+            *reinterpret_cast<uint4*>(out.TP + (tix * 64 + t) * 64 + jc * 8) =
+                *reinterpret_cast<const uint4*>(Tp_s + tc::sw128_off(t, jc));
+        }
+    }
 
     // ---- MMA-B: [T'(beta gam K) | T'(beta V)]   (M128 N256 K64)
     if (tid == 0 && ok) {
@@ -510,6 +558,465 @@ __global__ void __launch_bounds__(CH_THREADS, 1) delta_fwd_tc_kernel(
     if (warp == 4) tc::tmem_dealloc(tmem_S, 2 * DH);
 }
 
+// ------------------------------------------------------------------ backward chain kernel
+// One CTA (128 threads) per (sequence, head) walks the chunks in reverse with dS (f32) resident
+// in TMEM columns [0,128). Products with 64 token rows use M = 64 MMAs; two of them share a
+// column range by living in the two 16-lane halves of every 32-lane TMEM quarter (lane offset 0
+// and 16), so thread (warp w, lane l) sees row 16w + (l & 15) of the product in half (l >> 4).
+//
+//   G1  ACC_A.h0 = W^ S0               ACC_A.h1 = (beta gam K) S0  (= P2)
+//   G2  ACC_B.h1 = A^T dO + Kw dS      (= dU)
+//   G3  ACC_B.h1 += T'^T dU            (= dR)         G8  ACC_C.h1 = U dS^T (= dW)
+//   G4  ACC_C.h0 = [dR U^T | dO U^T]   (-> dL, dA)    G5  ACC_A.h0 = dO S0^T,  ACC_A.h1 = dR S0^T
+//   G6  ACC_B.h0 = (dA.Gam) K          ACC_B.h1 = M K + M^T K + (dA.Gam)^T Q
+//   G9  dS = gam_C dS + Qg^T dO - (beta gam K)^T dR
+// with U = Uv - W^ S0, R = beta V - P2, dV = beta dR, M = dL.Gam.beta, and
+//   dq = gam X + G6.h0,  dk = G6.h1 + eg dW - beta gam Y  (X, Y = the two halves of G5),
+// followed by the L2-norm backward, the gate gradients and the [dq|dk|dv] concat as in the f32
+// kernel (delta_bwd.cu).
+constexpr int BW_THREADS = 128;
+constexpr int R_WH = 0, R_BK = 16384, R_QG = 32768, R_KW = 49152, R_K = 65536, R_Q = 81920, R_DO = 98304,
+              R_A = 114688, R_TP = 122880, R_S0 = 131072, R_DS = 163840, R_DR = 196608, R_END = 212992;
+constexpr int R_U = R_WH, R_P = R_KW, R_DAG = R_A, R_M = R_TP;
+constexpr size_t BW_SMEM = 1024 + R_END + 10 * 64 * 4 + 256;
+constexpr int BW_TX = 16384 * 7 + 8192 * 2;
+
+__global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
+    const __grid_constant__ CUtensorMap mapWQ, const __grid_constant__ CUtensorMap map64x128,  // BK,KW,KR,QR tiles
+    const __grid_constant__ CUtensorMap mapKW, const __grid_constant__ CUtensorMap mapKR,
+    const __grid_constant__ CUtensorMap mapQR, const __grid_constant__ CUtensorMap mapDO,
+    const __grid_constant__ CUtensorMap mapAA, const __grid_constant__ CUtensorMap mapTP, Tiles tl,
+    const float* __restrict__ alpha, const float* __restrict__ qnorm, const float* __restrict__ knorm,
+    const float* __restrict__ ckpt, int T, int H, int n_chunks, float* __restrict__ d_qkv,
+    float* __restrict__ d_gate, int* err_word) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    float* vec = reinterpret_cast<float*>(sm + R_END);
+    float* g_s = vec;            // cumulative log alpha
+    float* be_s = vec + 64;      // beta
+    float* v_rowp = vec + 128;   // rowsum of P
+    float* v_colp = vec + 192;
+    float* v_rqs = vec + 256;
+    float* v_rkg = vec + 320;
+    float* v_rkw = vec + 384;
+    float* v_dbe = vec + 448;    // r_dr + beta * sum dLGam KK
+    float* v_red = vec + 512;    // 128 partials of <S0, dS>
+    uint64_t* bars = reinterpret_cast<uint64_t*>(vec + 640);   // [0] TMA, [1..6] MMA groups
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int half = (lane >> 4) & 1, row = 16 * warp + (lane & 15);   // M=64 accumulator mapping
+    const int chain = blockIdx.x;
+    const int b = chain / H, h = chain % H;
+    const int d = H * DH;
+    const int64_t seq_row0 = (int64_t)b * T;
+    const int64_t tile0 = (int64_t)chain * n_chunks;
+
+    if (tid == 0) {
+        *abort_flag = 0;
+        for (int i = 0; i < 7; ++i) tc::mbar_init(&bars[i], 1);
+        tc::mbar_fence_init();
+    }
+    if (warp == 0) tc::tmem_alloc(tmem_slot, 512);
+    tc::tcgen05_fence_before();
+    __syncthreads();
+    tc::tcgen05_fence_after();
+    const uint32_t tm = *tmem_slot;
+    const uint32_t ACC_S = tm, ACC_A = tm + 128, ACC_B = tm + 256, ACC_C = tm + 384;
+    const uint32_t H1 = 16u << 16;                         // lane offset of the second M=64 half
+    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+
+    // dS = 0 (TMEM f32 and the bf16 operand copy)
+    {
+        uint32_t z[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) z[j] = 0u;
+#pragma unroll 1
+        for (int cc = 0; cc < 4; ++cc) tc::tmem_st_32x32(ACC_S + lane_addr + cc * 32, z);
+        tc::tmem_st_wait();
+        for (int i = tid; i < 32768 / 16; i += BW_THREADS) *reinterpret_cast<uint4*>(sm + R_DS + i * 16) = make_uint4(0, 0, 0, 0);
+    }
+
+    auto issue_tma = [&](int c) {
+        const int t = (int)(tile0 + c);
+        const int grow = (int)(seq_row0 + (int64_t)c * C);
+        tc::mbar_expect_tx(&bars[0], BW_TX);
+#pragma unroll
+        for (int kb = 0; kb < 2; ++kb) {
+            tc::tma_load_2d(sm + R_WH + kb * 8192, &mapWQ, kb * 64, t * 128, &bars[0]);
+            tc::tma_load_2d(sm + R_QG + kb * 8192, &mapWQ, kb * 64, t * 128 + 64, &bars[0]);
+            tc::tma_load_2d(sm + R_BK + kb * 8192, &map64x128, kb * 64, t * 64, &bars[0]);
+            tc::tma_load_2d(sm + R_KW + kb * 8192, &mapKW, kb * 64, t * 64, &bars[0]);
+            tc::tma_load_2d(sm + R_K + kb * 8192, &mapKR, kb * 64, t * 64, &bars[0]);
+            tc::tma_load_2d(sm + R_Q + kb * 8192, &mapQR, kb * 64, t * 64, &bars[0]);
+            tc::tma_load_2d(sm + R_DO + kb * 8192, &mapDO, h * DH + kb * 64, grow, &bars[0]);
+        }
+        tc::tma_load_2d(sm + R_A, &mapAA, 0, t * 64, &bars[0]);
+        tc::tma_load_2d(sm + R_TP, &mapTP, 0, t * 64, &bars[0]);
+    };
+    auto wait_bar = [&](int i, uint32_t parity) {
+        if (lane == 0) tc::mbar_wait(&bars[i], parity, abort_flag, err_word, 300 + i);
+        __syncwarp();
+    };
+    // descriptor helpers (all tiles: 128-byte rows, 8-row groups 1024 B apart)
+    const uint32_t sb = tc::smem_u32(sm);
+    auto kmaj = [&](int reg, int k16) {       // K-major, 64-row tile, 8 KiB per 64-wide k box
+        return tc::smem_desc_sw128(sb + reg + (k16 >> 2) * 8192 + (k16 & 3) * 32, 16, 1024);
+    };
+    auto kmaj128 = [&](int reg, int k16) {    // K-major, 128-row tile (S0 / dS), 16 KiB per k box
+        return tc::smem_desc_sw128(sb + reg + (k16 >> 2) * 16384 + (k16 & 3) * 32, 16, 1024);
+    };
+    auto mnmaj = [&](int reg, int k16, int lbo) {   // MN-major: k rows, 64-wide mn boxes `lbo` bytes apart
+        return tc::smem_desc_sw128(sb + reg + k16 * 2048, lbo, 1024);
+    };
+    constexpr uint32_t I64_KM = tc::idesc_bf16_f32(64, 128, 0, 1);    // A K-major, B MN-major
+    constexpr uint32_t I64_MM = tc::idesc_bf16_f32(64, 128, 1, 1);    // A MN-major, B MN-major
+    constexpr uint32_t I64_KK = tc::idesc_bf16_f32(64, 128, 0, 0);    // A K-major, B K-major
+    constexpr uint32_t I64_KK64 = tc::idesc_bf16_f32(64, 64, 0, 0);
+    constexpr uint32_t I128_MM = tc::idesc_bf16_f32(128, 128, 1, 1);
+    constexpr uint32_t I128_MM_NEG = I128_MM | (1u << 13);            // negate A
+
+    if (tid == 0) issue_tma(n_chunks - 1);
+    // A wait that gives up raises *abort_flag; later waits then return at once, the iteration runs to its
+    // end on whatever data it has (every block barrier is still reached by every thread) and the loop
+    // exits at the block-uniform check below. The host sees the error word.
+    for (int c = n_chunks - 1, it = 0; c >= 0; --c, ++it) {
+        const uint32_t par = it & 1;
+        const int t0 = c * C;
+        const int n = T - t0 < C ? T - t0 : C;
+        const int64_t tix = tile0 + c;
+        const int64_t grow = seq_row0 + t0;       // global row of token 0 of this chunk
+        const float* s0g = ckpt + tix * DH * DH;
+        // ---- A. S0 (f32 checkpoint) -> bf16 operand tile; gates
+        {
+            const int a = tid;
+#pragma unroll 1
+            for (int cc = 0; cc < 4; ++cc) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float4 x0 = *reinterpret_cast<const float4*>(s0g + a * DH + cc * 32 + j * 8);
+                    const float4 x1 = *reinterpret_cast<const float4*>(s0g + a * DH + cc * 32 + j * 8 + 4);
+                    const float f8[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+                    const int chunk16 = cc * 4 + j;
+                    *reinterpret_cast<uint4*>(sm + R_S0 + (chunk16 >> 3) * 16384 + tc::sw128_off(a, chunk16 & 7)) =
+                        tc::pack8_bf16(f8);
+                }
+            }
+            if (tid < 64) {
+                g_s[tid] = tl.GV[tix * 64 + tid];
+                be_s[tid] = tl.BE[tix * 64 + tid];
+            }
+        }
+        tc::fence_proxy_async_smem();
+        tc::tcgen05_fence_before();
+        __syncthreads();
+        wait_bar(0, par);
+        if (tid == 0) {
+            tc::tcgen05_fence_after();
+            for (int k16 = 0; k16 < 8; ++k16) tc::umma_bf16(ACC_A, kmaj(R_WH, k16), mnmaj(R_S0, k16, 16384), I64_KM, k16 > 0);
+            for (int k16 = 0; k16 < 8; ++k16) tc::umma_bf16(ACC_A + H1, kmaj(R_BK, k16), mnmaj(R_S0, k16, 16384), I64_KM, k16 > 0);
+            tc::umma_commit(&bars[1]);
+            for (int k16 = 0; k16 < 4; ++k16) tc::umma_bf16(ACC_B + H1, mnmaj(R_A, k16, 8192), mnmaj(R_DO, k16, 8192), I64_MM, k16 > 0);
+            for (int k16 = 0; k16 < 8; ++k16) tc::umma_bf16(ACC_B + H1, kmaj(R_KW, k16), mnmaj(R_DS, k16, 16384), I64_KM, 1u);
+            tc::umma_commit(&bars[2]);
+        }
+        const float g_row = g_s[row], g_last = g_s[C - 1];
+        const float gam_row = __expf(g_row), eg_row = __expf(g_last - g_row), be_row = be_s[row];
+        const bool live = row < n;
+        // ---- B. U = Uv - W^ S0 (half 0);  dU -> bf16 (half 1)
+        wait_bar(1, par);
+        tc::tcgen05_fence_after();
+#pragma unroll 1
+        for (int cc = 0; cc < 4; ++cc) {
+            uint32_t r[32];
+            tc::tmem_ld_32x32(ACC_A + lane_addr + cc * 32, r);
+            tc::tmem_ld_wait();
+            if (half == 0) {
+                const __nv_bfloat16* uv = tl.UV + (tix * 64 + row) * DH + cc * 32;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    float x8[8], u8[8];
+                    tc::unpack8_bf16(*reinterpret_cast<const uint4*>(uv + 8 * j), x8);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) u8[e] = x8[e] - __uint_as_float(r[8 * j + e]);
+                    const int chunk16 = cc * 4 + j;
+                    *reinterpret_cast<uint4*>(sm + R_U + (chunk16 >> 3) * 8192 + tc::sw128_off(row, chunk16 & 7)) = tc::pack8_bf16(u8);
+                }
+            }
+        }
+        wait_bar(2, par);
+        tc::tcgen05_fence_after();
+#pragma unroll 1
+        for (int cc = 0; cc < 4; ++cc) {
+            uint32_t r[32];
+            tc::tmem_ld_32x32(ACC_B + lane_addr + cc * 32, r);
+            tc::tmem_ld_wait();
+            if (half == 1) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    float f8[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) f8[e] = __uint_as_float(r[8 * j + e]);
+                    const int chunk16 = cc * 4 + j;
+                    *reinterpret_cast<uint4*>(sm + R_DR + (chunk16 >> 3) * 8192 + tc::sw128_off(row, chunk16 & 7)) = tc::pack8_bf16(f8);
+                }
+            }
+        }
+        tc::fence_proxy_async_smem();
+        tc::tcgen05_fence_before();
+        __syncthreads();
+        if (tid == 0) {
+            tc::tcgen05_fence_after();
+            for (int k16 = 0; k16 < 4; ++k16) tc::umma_bf16(ACC_B + H1, mnmaj(R_TP, k16, 8192), mnmaj(R_DR, k16, 8192), I64_MM, 1u);
+            for (int k16 = 0; k16 < 8; ++k16) tc::umma_bf16(ACC_C + H1, kmaj(R_U, k16), kmaj128(R_DS, k16), I64_KK, k16 > 0);
+            tc::umma_commit(&bars[3]);
+        }
+        // ---- C. dR: dV out, R = beta V - P2, r_dr, r_kg, bf16 dR tile (half 1)
+        wait_bar(3, par);
+        tc::tcgen05_fence_after();
+        {
+            float r_dr = 0.0f, r_kg = 0.0f;
+#pragma unroll 1
+            for (int cc = 0; cc < 4; ++cc) {
+                uint32_t r[32], p2[32];
+                tc::tmem_ld_32x32(ACC_B + lane_addr + cc * 32, r);
+                tc::tmem_ld_32x32(ACC_A + lane_addr + cc * 32, p2);
+                tc::tmem_ld_wait();
+                if (half == 1) {
+                    const __nv_bfloat16* bv = tl.BV + (tix * 64 + row) * DH + cc * 32;
+                    float* dv = d_qkv + (grow + row) * 3 * d + 2 * d + h * DH + cc * 32;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        float x8[8], f8[8];
+                        tc::unpack8_bf16(*reinterpret_cast<const uint4*>(bv + 8 * j), x8);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            const float dr = __uint_as_float(r[8 * j + e]), pp = __uint_as_float(p2[8 * j + e]);
+                            f8[e] = dr;
+                            r_dr = fmaf(dr, x8[e] - pp, r_dr);
+                            r_kg = fmaf(-dr, pp, r_kg);
+                        }
+                        if (live) {
+                            reinterpret_cast<float4*>(dv)[2 * j] = make_float4(be_row * f8[0], be_row * f8[1], be_row * f8[2], be_row * f8[3]);
+                            reinterpret_cast<float4*>(dv)[2 * j + 1] = make_float4(be_row * f8[4], be_row * f8[5], be_row * f8[6], be_row * f8[7]);
+                        }
+                        const int chunk16 = cc * 4 + j;
+                        *reinterpret_cast<uint4*>(sm + R_DR + (chunk16 >> 3) * 8192 + tc::sw128_off(row, chunk16 & 7)) = tc::pack8_bf16(f8);
+                    }
+                }
+            }
+            if (half == 1) {
+                v_dbe[row] = r_dr;
+                v_rkg[row] = r_kg;
+            }
+        }
+        tc::fence_proxy_async_smem();
+        tc::tcgen05_fence_before();
+        __syncthreads();
+        if (tid == 0) {
+            tc::tcgen05_fence_after();
+            for (int k16 = 0; k16 < 8; ++k16) tc::umma_bf16(ACC_C, kmaj(R_DR, k16), kmaj(R_U, k16), I64_KK64, k16 > 0);
+            for (int k16 = 0; k16 < 8; ++k16) tc::umma_bf16(ACC_C + 64, kmaj(R_DO, k16), kmaj(R_U, k16), I64_KK64, k16 > 0);
+            for (int k16 = 0; k16 < 8; ++k16) tc::umma_bf16(ACC_A, kmaj(R_DO, k16), kmaj128(R_S0, k16), I64_KK, k16 > 0);
+            for (int k16 = 0; k16 < 8; ++k16) tc::umma_bf16(ACC_A + H1, kmaj(R_DR, k16), kmaj128(R_S0, k16), I64_KK, k16 > 0);
+            tc::umma_commit(&bars[4]);
+        }
+        // ---- D. scale dS by gam_C (and <S0, dS>) while G4/G5 run
+        {
+            const int a = tid;
+            const float gC = __expf(g_last);
+            float part = 0.0f;
+#pragma unroll 1
+            for (int cc = 0; cc < 4; ++cc) {
+                uint32_t r[32];
+                tc::tmem_ld_32x32(ACC_S + lane_addr + cc * 32, r);
+                tc::tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float4 s4 = *reinterpret_cast<const float4*>(s0g + a * DH + cc * 32 + 4 * j);
+                    part = fmaf(s4.x, __uint_as_float(r[4 * j]), part);
+                    part = fmaf(s4.y, __uint_as_float(r[4 * j + 1]), part);
+                    part = fmaf(s4.z, __uint_as_float(r[4 * j + 2]), part);
+                    part = fmaf(s4.w, __uint_as_float(r[4 * j + 3]), part);
+                }
+#pragma unroll
+                for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(gC * __uint_as_float(r[j]));
+                tc::tmem_st_32x32(ACC_S + lane_addr + cc * 32, r);
+            }
+            tc::tmem_st_wait();
+            v_red[tid] = part;
+        }
+        wait_bar(4, par);
+        tc::tcgen05_fence_after();
+        // dL / dA rows (half 0): M tile, dA.Gam tile, P row, dbeta
+        {
+            float rowp = 0.0f, dls = 0.0f;
+#pragma unroll 1
+            for (int cc = 0; cc < 2; ++cc) {
+                uint32_t rl[32], ra[32];
+                tc::tmem_ld_32x32(ACC_C + lane_addr + cc * 32, rl);
+                tc::tmem_ld_32x32(ACC_C + lane_addr + 64 + cc * 32, ra);
+                tc::tmem_ld_wait();
+                if (half == 0) {
+                    const __nv_bfloat16* kk = tl.KKo + (tix * 64 + row) * 64 + cc * 32;
+                    const __nv_bfloat16* qk = tl.QKo + (tix * 64 + row) * 64 + cc * 32;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        float kk8[8], qk8[8], m8[8], a8[8];
+                        tc::unpack8_bf16(*reinterpret_cast<const uint4*>(kk + 8 * j), kk8);
+                        tc::unpack8_bf16(*reinterpret_cast<const uint4*>(qk + 8 * j), qk8);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            const int i = cc * 32 + 8 * j + e;
+                            const float gm = i <= row ? __expf(g_row - g_s[i]) : 0.0f;
+                            const float dlg = i < row ? -__uint_as_float(rl[8 * j + e]) * gm : 0.0f;   // dL.Gam
+                            const float dag = __uint_as_float(ra[8 * j + e]) * gm;                     // dA.Gam
+                            dls = fmaf(dlg, kk8[e], dls);
+                            m8[e] = dlg * be_row;
+                            a8[e] = dag;
+                            const float pv = dag * qk8[e] + m8[e] * kk8[e];
+                            rowp += pv;
+                            reinterpret_cast<float*>(sm + R_P)[row * 64 + ((i + row) & 63)] = pv;
+                        }
+                        const int chunk16 = cc * 4 + j;
+                        *reinterpret_cast<uint4*>(sm + R_M + tc::sw128_off(row, chunk16)) = tc::pack8_bf16(m8);
+                        *reinterpret_cast<uint4*>(sm + R_DAG + tc::sw128_off(row, chunk16)) = tc::pack8_bf16(a8);
+                    }
+                }
+            }
+            if (half == 0) {
+                v_rowp[row] = rowp;
+                v_dbe[row] += be_row * dls;   // v_dbe[row] was written by the half-1 thread of the same warp
+            }
+        }
+        tc::fence_proxy_async_smem();
+        tc::tcgen05_fence_before();
+        __syncthreads();
+        if (tid == 0) {
+            tc::tcgen05_fence_after();
+            for (int k16 = 0; k16 < 4; ++k16)
+                tc::umma_bf16(ACC_B, tc::smem_desc_sw128(sb + R_DAG + k16 * 32, 16, 1024), mnmaj(R_K, k16, 8192), I64_KM, k16 > 0);
+            for (int k16 = 0; k16 < 4; ++k16)
+                tc::umma_bf16(ACC_B + H1, tc::smem_desc_sw128(sb + R_M + k16 * 32, 16, 1024), mnmaj(R_K, k16, 8192), I64_KM, k16 > 0);
+            for (int k16 = 0; k16 < 4; ++k16) tc::umma_bf16(ACC_B + H1, mnmaj(R_M, k16, 8192), mnmaj(R_K, k16, 8192), I64_MM, 1u);
+            for (int k16 = 0; k16 < 4; ++k16) tc::umma_bf16(ACC_B + H1, mnmaj(R_DAG, k16, 8192), mnmaj(R_Q, k16, 8192), I64_MM, 1u);
+            tc::umma_commit(&bars[5]);
+            for (int k16 = 0; k16 < 4; ++k16) tc::umma_bf16(ACC_S, mnmaj(R_QG, k16, 8192), mnmaj(R_DO, k16, 8192), I128_MM, 1u);
+            for (int k16 = 0; k16 < 4; ++k16) tc::umma_bf16(ACC_S, mnmaj(R_BK, k16, 8192), mnmaj(R_DR, k16, 8192), I128_MM_NEG, 1u);
+            tc::umma_commit(&bars[6]);
+        }
+        // column sums of P (threads 0..63) while G6 runs
+        if (tid < 64) {
+            float cs = 0.0f;
+            const float* P = reinterpret_cast<const float*>(sm + R_P);
+#pragma unroll 8
+            for (int t = 0; t < 64; ++t) cs += P[t * 64 + ((tid + t) & 63)];
+            v_colp[tid] = cs;
+        }
+        // ---- E. dq (half 0) and dk (half 1): assemble, L2-norm backward, store
+        wait_bar(5, par);
+        tc::tcgen05_fence_after();
+        {
+            const uint8_t* yt = sm + (half == 0 ? R_Q : R_K);       // normalised q / k rows (bf16)
+            float dot = 0.0f, rr = 0.0f;                             // y.g and (r_qs | r_kw)
+            const float nrm = live ? (half == 0 ? qnorm : knorm)[(grow + row) * H + h] : 1.0f;
+            float* dst = d_qkv + (grow + row) * 3 * d + (half == 0 ? 0 : d) + h * DH;
+#pragma unroll 1
+            for (int pass = 0; pass < 2; ++pass) {
+#pragma unroll 1
+                for (int cc = 0; cc < 4; ++cc) {
+                    uint32_t xa[32], xb[32], xc[32];
+                    tc::tmem_ld_32x32(ACC_A + lane_addr + cc * 32, xa);    // X (h0) | Y (h1)
+                    tc::tmem_ld_32x32(ACC_B + lane_addr + cc * 32, xb);    // G6
+                    tc::tmem_ld_32x32(ACC_C + lane_addr + cc * 32, xc);    // (h0: dL|dA, unused) | dW (h1)
+                    tc::tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int chunk16 = cc * 4 + j;
+                        float y8[8], z8[8], g8[8];
+                        tc::unpack8_bf16(*reinterpret_cast<const uint4*>(yt + (chunk16 >> 3) * 8192 + tc::sw128_off(row, chunk16 & 7)), y8);
+                        if (half == 0)
+                            tc::unpack8_bf16(*reinterpret_cast<const uint4*>(sm + R_QG + (chunk16 >> 3) * 8192 + tc::sw128_off(row, chunk16 & 7)), z8);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            const float A_ = __uint_as_float(xa[8 * j + e]), B_ = __uint_as_float(xb[8 * j + e]),
+                                        C_ = __uint_as_float(xc[8 * j + e]);
+                            if (half == 0) {
+                                g8[e] = fmaf(gam_row, A_, B_);
+                                if (pass == 0) rr = fmaf(z8[e], A_, rr);                // Qg_t . X_t
+                            } else {
+                                g8[e] = B_ + eg_row * C_ - be_row * gam_row * A_;
+                                if (pass == 0) rr = fmaf(eg_row * y8[e], C_, rr);       // eg k_t . dW_t
+                            }
+                            if (pass == 0) dot = fmaf(y8[e], g8[e], dot);
+                        }
+                        if (pass == 1 && live) {
+                            float* o8 = dst + cc * 32 + 8 * j;
+                            reinterpret_cast<float4*>(o8)[0] = make_float4((g8[0] - y8[0] * dot) / nrm, (g8[1] - y8[1] * dot) / nrm,
+                                                                           (g8[2] - y8[2] * dot) / nrm, (g8[3] - y8[3] * dot) / nrm);
+                            reinterpret_cast<float4*>(o8)[1] = make_float4((g8[4] - y8[4] * dot) / nrm, (g8[5] - y8[5] * dot) / nrm,
+                                                                           (g8[6] - y8[6] * dot) / nrm, (g8[7] - y8[7] * dot) / nrm);
+                        }
+                    }
+                }
+            }
+            if (half == 0) v_rqs[row] = rr; else v_rkw[row] = rr;
+        }
+        __syncthreads();
+        // gates: dg, reverse cumulative sum, sigmoid backward
+        if (tid == 0) {
+            float sds = 0.0f;
+            for (int i = 0; i < 128; ++i) sds += v_red[i];
+            float extra = __expf(g_last) * sds;
+            for (int t = 0; t < C; ++t) extra += v_rkw[t];
+            float run = 0.0f;
+            for (int t = C - 1; t >= 0; --t) {
+                float dg = v_rowp[t] - v_colp[t] + v_rqs[t] + v_rkg[t] - v_rkw[t];
+                if (t == C - 1) dg += extra;
+                run += dg;
+                v_rowp[t] = run;   // dlogalpha_t
+            }
+        }
+        __syncthreads();
+        if (tid < n) {
+            const int64_t r = grow + tid;
+            const float al = alpha[r * H + h], be = be_s[tid];
+            d_gate[r * 2 * H + h] = v_rowp[tid] * (1.0f - al);
+            d_gate[r * 2 * H + H + h] = v_dbe[tid] * (1.0f - be);
+        }
+        // ---- F. new dS -> bf16 operand copy for the next chunk; next chunk's tiles
+        wait_bar(6, par);
+        tc::tcgen05_fence_after();
+        if (c > 0) {
+            if (tid == 0) {
+                tc::fence_proxy_async_smem();
+                issue_tma(c - 1);
+            }
+            const int a = tid;
+#pragma unroll 1
+            for (int cc = 0; cc < 4; ++cc) {
+                uint32_t r[32];
+                tc::tmem_ld_32x32(ACC_S + lane_addr + cc * 32, r);
+                tc::tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    float f8[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) f8[e] = __uint_as_float(r[8 * j + e]);
+                    const int chunk16 = cc * 4 + j;
+                    *reinterpret_cast<uint4*>(sm + R_DS + (chunk16 >> 3) * 16384 + tc::sw128_off(a, chunk16 & 7)) = tc::pack8_bf16(f8);
+                }
+            }
+        }
+        if (__syncthreads_or(*abort_flag ? 1 : 0)) break;
+    }
+    tc::tcgen05_fence_before();
+    __syncthreads();
+    if (*abort_flag) __nanosleep(20000);
+    if (warp == 0) tc::tmem_dealloc(tm, 512);
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -549,7 +1056,7 @@ int forward(asca_ctx* ctx, const void* q, const void* k, const void* v, const fl
     void* ws;
     ASCA_TRY(asca_workspace(ctx, b_wq + 2 * b_uv + b_aa + b_gc + 1024, &ws));
     char* w = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(ws) + 1023) & ~(uintptr_t)1023);
-    Tiles t;
+    Tiles t{};
     t.WQ = (__nv_bfloat16*)w;
     t.UV = (__nv_bfloat16*)(w + b_wq);
     t.KW = (__nv_bfloat16*)(w + b_wq + b_uv);
@@ -568,6 +1075,50 @@ int forward(asca_ctx* ctx, const void* q, const void* k, const void* v, const fl
     ASCA_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)CH_SMEM));
     kern<<<(unsigned)chains, CH_THREADS, CH_SMEM, ctx->stream>>>(mWQ, mUV, mKW, mAA, t.GC, (int)T, (int)H, (int)n_chunks,
                                                                 (__nv_bfloat16*)o, s_init, s_final, ckpt, ctx->err_word);
+    ASCA_CHECK_LAUNCH(ctx);
+    return ASCA_OK;
+}
+
+// Backward for bf16 q,k,v,d_o (dh = 128, checkpoints every 64 tokens from the forward).
+int backward(asca_ctx* ctx, const void* q, const void* k, const void* v, const float* alpha, const float* beta,
+             const float* qnorm, const float* knorm, const void* d_o, const float* ckpt, int64_t B, int64_t T, int64_t H,
+             float* d_qkv, float* d_gate) {
+    const int64_t n_chunks = (T + C - 1) / C, chains = B * H, n_tiles = chains * n_chunks;
+    const size_t b128 = al((size_t)n_tiles * 128 * DH * 2), b64 = al((size_t)n_tiles * 64 * DH * 2),
+                 bcc = al((size_t)n_tiles * 64 * 64 * 2), bv = al((size_t)n_tiles * 64 * 4), bg = al((size_t)n_tiles * 4);
+    void* ws;
+    ASCA_TRY(asca_workspace(ctx, b128 + 6 * b64 + 4 * bcc + 2 * bv + bg + 2048, &ws));
+    char* w = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(ws) + 1023) & ~(uintptr_t)1023);
+    Tiles t{};
+    t.WQ = (__nv_bfloat16*)w; w += b128;
+    t.UV = (__nv_bfloat16*)w; w += b64;
+    t.KW = (__nv_bfloat16*)w; w += b64;
+    t.BK = (__nv_bfloat16*)w; w += b64;
+    t.BV = (__nv_bfloat16*)w; w += b64;
+    t.KR = (__nv_bfloat16*)w; w += b64;
+    t.QR = (__nv_bfloat16*)w; w += b64;
+    t.AA = (__nv_bfloat16*)w; w += bcc;
+    t.TP = (__nv_bfloat16*)w; w += bcc;
+    t.KKo = (__nv_bfloat16*)w; w += bcc;
+    t.QKo = (__nv_bfloat16*)w; w += bcc;
+    t.GV = (float*)w; w += bv;
+    t.BE = (float*)w; w += bv;
+    t.GC = (float*)w;
+    ASCA_CUDA(ctx, cudaFuncSetAttribute(delta_prep_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PRE_SMEM));
+    delta_prep_tc_kernel<<<dim3((unsigned)n_chunks, (unsigned)chains), PRE_THREADS, PRE_SMEM, ctx->stream>>>(
+        (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, alpha, beta, (int)T, (int)H,
+        (int)n_chunks, t, ctx->err_word);
+    ASCA_CHECK_LAUNCH(ctx);
+    CUtensorMap mWQ, mBK, mKW, mKR, mQR, mDO, mAA, mTP;
+    bool ok = make_map(&mWQ, t.WQ, n_tiles * 128, DH, 64, 64) && make_map(&mBK, t.BK, n_tiles * 64, DH, 64, 64) &&
+              make_map(&mKW, t.KW, n_tiles * 64, DH, 64, 64) && make_map(&mKR, t.KR, n_tiles * 64, DH, 64, 64) &&
+              make_map(&mQR, t.QR, n_tiles * 64, DH, 64, 64) && make_map(&mDO, d_o, B * T, H * DH, 64, 64) &&
+              make_map(&mAA, t.AA, n_tiles * 64, 64, 64, 64) && make_map(&mTP, t.TP, n_tiles * 64, 64, 64, 64);
+    if (!ok) return asca_fail(ctx, ASCA_ERR_CUDA, "delta_tc: cuTensorMapEncodeTiled failed");
+    ASCA_CUDA(ctx, cudaFuncSetAttribute(delta_bwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)BW_SMEM));
+    delta_bwd_tc_kernel<<<(unsigned)chains, BW_THREADS, BW_SMEM, ctx->stream>>>(
+        mWQ, mBK, mKW, mKR, mQR, mDO, mAA, mTP, t, alpha, qnorm, knorm, ckpt, (int)T, (int)H, (int)n_chunks, d_qkv, d_gate,
+        ctx->err_word);
     ASCA_CHECK_LAUNCH(ctx);
     return ASCA_OK;
 }

@@ -301,6 +301,31 @@ def test_delta_bf16_tensor_core_forward(orc, gpu, B, T, H):
         assert rel_err(s2.cpu().numpy(), sfin_ref) < BF16_TOL
 
 
+@pytest.mark.parametrize("B,T,H", [(1, 64, 1), (2, 128, 2), (2, 200, 3), (1, 700, 2), (3, 37, 1)])
+def test_delta_bf16_tensor_core_backward(orc, gpu, B, T, H):
+    """bf16 inputs at dh = 128, chunk 64: the reverse chunked scan on tcgen05 against the f32 BPTT of
+    the oracle on the same (bf16-rounded) inputs; every output block checked separately."""
+    import torch
+    from asca_b200 import ops
+
+    dh = 128
+    d = H * dh
+    arrs = _delta_inputs(orc, 500 + T, B, T, H, dh)
+    q, k, v, alpha, beta, qn, kn, d_o = (torch.from_numpy(a).cuda() for a in arrs)
+    q16, k16, v16, do16 = (x.bfloat16() for x in (q, k, v, d_o))
+    qr, kr, vr, dor = (x.float().cpu().numpy() for x in (q16, k16, v16, do16))
+    dqkv_ref, dgate_ref = orc.delta_bptt(qr, kr, vr, arrs[3], arrs[4], arrs[5], arrs[6], dor, B, T, H, dh)
+    o, _, ckpt = ops.delta_fwd(gpu, q16, k16, v16, alpha, beta, B, T, H, dh, chunk=64)
+    d_qkv, d_gate = ops.delta_bwd(gpu, q16, k16, v16, alpha, beta, qn, kn, do16, ckpt, B, T, H, dh, chunk=64)
+    gpu.sync()
+    got, gg = d_qkv.cpu().numpy(), d_gate.cpu().numpy()
+    assert rel_err(got[:, 2 * d:], dqkv_ref[:, 2 * d:]) < BF16_TOL, "dv"
+    assert rel_err(got[:, :d], dqkv_ref[:, :d]) < BF16_TOL, "dq"
+    assert rel_err(got[:, d:2 * d], dqkv_ref[:, d:2 * d]) < BF16_TOL, "dk"
+    assert rel_err(gg[:, H:], dgate_ref[:, H:]) < BF16_TOL, "d_gate beta"
+    assert rel_err(gg[:, :H], dgate_ref[:, :H]) < BF16_TOL, "d_gate alpha"
+
+
 @pytest.mark.parametrize("dh", [16, 32, 64, 128])
 def test_delta_decode_step(orc, gpu, dh):
     import torch
