@@ -177,6 +177,19 @@ class Gpu:
         # stream"; CUDA's explicit handle for the legacy default stream is 1 (cudaStreamLegacy).
         self.set_stream(torch.cuda.current_stream(self.device).cuda_stream or 1)
 
+    def profile(self, on: bool):
+        """Switch per-kernel CUDA-event timing of the delta-rule kernels on or off (clears the record)."""
+        self._call("asca_ctx_profile", self._ctx, C.c_int(1 if on else 0))
+
+    def profile_read(self):
+        """[(kernel name, milliseconds)] recorded since profile(True)."""
+        out, i = [], 0
+        name, ms = C.c_char_p(), C.c_float()
+        while self.lib.asca_ctx_profile_read(self._ctx, C.c_int(i), C.byref(name), C.byref(ms)) == 0:
+            out.append((name.value.decode(), float(ms.value)))
+            i += 1
+        return out
+
     def sync(self):
         self._call("asca_ctx_sync", self._ctx)
 

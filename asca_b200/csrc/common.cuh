@@ -29,6 +29,31 @@ struct asca_ctx {
     void* ws = nullptr;
     size_t ws_bytes = 0;
     int* err_word = nullptr;  // device int the kernels with bounded waits write to
+    // optional per-kernel timing (asca_ctx_profile): CUDA events around selected launches
+    bool profiling = false;
+    struct Span {
+        const char* name;
+        cudaEvent_t e0, e1;
+    };
+    std::vector<Span> spans;
+};
+
+// Brackets one kernel launch with CUDA events on the context's stream when profiling is on.
+struct asca_span {
+    asca_ctx* ctx;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    const char* name;
+    asca_span(asca_ctx* c, const char* n) : ctx(c), name(n) {
+        if (!ctx->profiling) return;
+        cudaEventCreate(&e0);
+        cudaEventCreate(&e1);
+        cudaEventRecord(e0, ctx->stream);
+    }
+    ~asca_span() {
+        if (!e0) return;
+        cudaEventRecord(e1, ctx->stream);
+        ctx->spans.push_back({name, e0, e1});
+    }
 };
 
 int asca_fail(asca_ctx* ctx, int code, const char* fmt, ...);

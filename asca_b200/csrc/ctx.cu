@@ -95,6 +95,26 @@ int asca_ctx_sync(asca_ctx* ctx) {
     return ASCA_OK;
 }
 
+int asca_ctx_profile(asca_ctx* ctx, int on) {
+    if (!ctx) return ASCA_ERR_ARG;
+    for (auto& sp : ctx->spans) {
+        cudaEventDestroy(sp.e0);
+        cudaEventDestroy(sp.e1);
+    }
+    ctx->spans.clear();
+    ctx->profiling = on != 0;
+    return ASCA_OK;
+}
+
+int asca_ctx_profile_read(asca_ctx* ctx, int index, const char** name, float* ms) {
+    if (!ctx || !name || !ms) return ASCA_ERR_ARG;
+    if (index < 0 || index >= (int)ctx->spans.size()) return 1;  // past the end
+    ASCA_CUDA(ctx, cudaEventSynchronize(ctx->spans[index].e1));
+    ASCA_CUDA(ctx, cudaEventElapsedTime(ms, ctx->spans[index].e0, ctx->spans[index].e1));
+    *name = ctx->spans[index].name;
+    return ASCA_OK;
+}
+
 const char* asca_last_error(const asca_ctx* ctx) { return ctx ? ctx->err.c_str() : "null context"; }
 const char* asca_describe(asca_ctx* ctx) { return ctx ? ctx->desc.c_str() : "null context"; }
 int64_t asca_launch_count(const asca_ctx* ctx) { return ctx ? ctx->launches : 0; }

@@ -540,6 +540,7 @@ int launch_bwd(asca_ctx* ctx, const void* q, const void* k, const void* v, const
     ASCA_TRY(asca_workspace(ctx, (size_t)B * H * sub_per_ck * DH * DH * 4 + 256, &ws));
     auto kern = delta_bwd_kernel<DH, C, T>;
     ASCA_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SM::bytes));
+    asca_span sp(ctx, "delta_bwd_kernel");
     kern<<<B * H, BT, SM::bytes, ctx->stream>>>((const T*)q, (const T*)k, (const T*)v, alpha, beta, qnorm, knorm,
                                                 (const T*)d_o, ckpt, (float*)ws, B, Tlen, H, chunk, d_qkv, d_gate);
     ASCA_CHECK_LAUNCH(ctx);

@@ -353,6 +353,7 @@ int asca_delta_fwd(asca_ctx* ctx, const void* q, const void* k, const void* v, c
         return delta_tc::forward(ctx, q, k, v, alpha, beta, B, T, H, o, s_init, s_final, ckpt);
     const int ch = ckpt ? (int)chunk : 1;
     cudaError_t e;
+    asca_span sp(ctx, "delta_fwd_rec_kernel");
 #define ASCA_FWD(DH_)                                                                                              \
     e = dtype == ASCA_BF16                                                                                         \
             ? launch_fwd<DH_, __nv_bfloat16>(ctx->stream, q, k, v, alpha, beta, (int)B, (int)T, (int)H, ch, o, s_init, \

@@ -1063,9 +1063,12 @@ int forward(asca_ctx* ctx, const void* q, const void* k, const void* v, const fl
     t.AA = (__nv_bfloat16*)(w + b_wq + 2 * b_uv);
     t.GC = (float*)(w + b_wq + 2 * b_uv + b_aa);
     ASCA_CUDA(ctx, cudaFuncSetAttribute(delta_prep_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PRE_SMEM));
-    delta_prep_tc_kernel<<<dim3((unsigned)n_chunks, (unsigned)chains), PRE_THREADS, PRE_SMEM, ctx->stream>>>(
-        (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, alpha, beta, (int)T, (int)H,
-        (int)n_chunks, t, ctx->err_word);
+    {
+        asca_span sp(ctx, "delta_prep_tc_kernel");
+        delta_prep_tc_kernel<<<dim3((unsigned)n_chunks, (unsigned)chains), PRE_THREADS, PRE_SMEM, ctx->stream>>>(
+            (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, alpha, beta, (int)T, (int)H,
+            (int)n_chunks, t, ctx->err_word);
+    }
     ASCA_CHECK_LAUNCH(ctx);
     CUtensorMap mWQ, mUV, mKW, mAA;
     if (!make_map(&mWQ, t.WQ, n_tiles * 128, DH, 64, 128) || !make_map(&mUV, t.UV, n_tiles * 64, DH, 64, 64) ||
@@ -1073,8 +1076,12 @@ int forward(asca_ctx* ctx, const void* q, const void* k, const void* v, const fl
         return asca_fail(ctx, ASCA_ERR_CUDA, "delta_tc: cuTensorMapEncodeTiled failed");
     auto kern = delta_fwd_tc_kernel<__nv_bfloat16>;
     ASCA_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)CH_SMEM));
-    kern<<<(unsigned)chains, CH_THREADS, CH_SMEM, ctx->stream>>>(mWQ, mUV, mKW, mAA, t.GC, (int)T, (int)H, (int)n_chunks,
-                                                                (__nv_bfloat16*)o, s_init, s_final, ckpt, ctx->err_word);
+    {
+        asca_span sp(ctx, "delta_fwd_tc_kernel");
+        kern<<<(unsigned)chains, CH_THREADS, CH_SMEM, ctx->stream>>>(mWQ, mUV, mKW, mAA, t.GC, (int)T, (int)H,
+                                                                    (int)n_chunks, (__nv_bfloat16*)o, s_init, s_final,
+                                                                    ckpt, ctx->err_word);
+    }
     ASCA_CHECK_LAUNCH(ctx);
     return ASCA_OK;
 }
@@ -1105,9 +1112,12 @@ int backward(asca_ctx* ctx, const void* q, const void* k, const void* v, const f
     t.BE = (float*)w; w += bv;
     t.GC = (float*)w;
     ASCA_CUDA(ctx, cudaFuncSetAttribute(delta_prep_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PRE_SMEM));
-    delta_prep_tc_kernel<<<dim3((unsigned)n_chunks, (unsigned)chains), PRE_THREADS, PRE_SMEM, ctx->stream>>>(
-        (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, alpha, beta, (int)T, (int)H,
-        (int)n_chunks, t, ctx->err_word);
+    {
+        asca_span sp(ctx, "delta_prep_tc_kernel");
+        delta_prep_tc_kernel<<<dim3((unsigned)n_chunks, (unsigned)chains), PRE_THREADS, PRE_SMEM, ctx->stream>>>(
+            (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, alpha, beta, (int)T, (int)H,
+            (int)n_chunks, t, ctx->err_word);
+    }
     ASCA_CHECK_LAUNCH(ctx);
     CUtensorMap mWQ, mBK, mKW, mKR, mQR, mDO, mAA, mTP;
     bool ok = make_map(&mWQ, t.WQ, n_tiles * 128, DH, 64, 64) && make_map(&mBK, t.BK, n_tiles * 64, DH, 64, 64) &&
@@ -1116,9 +1126,12 @@ int backward(asca_ctx* ctx, const void* q, const void* k, const void* v, const f
               make_map(&mAA, t.AA, n_tiles * 64, 64, 64, 64) && make_map(&mTP, t.TP, n_tiles * 64, 64, 64, 64);
     if (!ok) return asca_fail(ctx, ASCA_ERR_CUDA, "delta_tc: cuTensorMapEncodeTiled failed");
     ASCA_CUDA(ctx, cudaFuncSetAttribute(delta_bwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)BW_SMEM));
-    delta_bwd_tc_kernel<<<(unsigned)chains, BW_THREADS, BW_SMEM, ctx->stream>>>(
-        mWQ, mBK, mKW, mKR, mQR, mDO, mAA, mTP, t, alpha, qnorm, knorm, ckpt, (int)T, (int)H, (int)n_chunks, d_qkv, d_gate,
-        ctx->err_word);
+    {
+        asca_span sp(ctx, "delta_bwd_tc_kernel");
+        delta_bwd_tc_kernel<<<(unsigned)chains, BW_THREADS, BW_SMEM, ctx->stream>>>(
+            mWQ, mBK, mKW, mKR, mQR, mDO, mAA, mTP, t, alpha, qnorm, knorm, ckpt, (int)T, (int)H, (int)n_chunks, d_qkv,
+            d_gate, ctx->err_word);
+    }
     ASCA_CHECK_LAUNCH(ctx);
     return ASCA_OK;
 }

@@ -6,7 +6,10 @@ Workload (the isolated delta op of the baseline configuration list): B=8 sequenc
 heads, T=4096 tokens, dh=128, q/k L2-normalised N(0,1), v ~ N(0,1), alpha = sigmoid(N(2,.5)),
 beta = sigmoid(N(0,1)), dO ~ N(0,1); seeded synthetic data.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--dtype f32|bf16] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--dtype bf16|f32] [--impl ours|reference]
+
+Default mode: bf16 activations (tcgen05 tensor cores, f32 accumulation, f32 recurrent state and
+gates; parity tolerance 2e-2). --dtype f32 runs the f32-exact FFMA kernels (tolerance 1e-5).
 
 Under torchrun every rank owns its own batch of B sequences (weak scaling, no collective on the
 data path: chains are independent per (sequence, head)). Timing: CUDA events on the launching
@@ -233,6 +236,7 @@ def run_ours(args):
     if rank == 0:
         sampler.start()
     launches0 = gpu.launch_count()
+    gpu.profile(True)   # CUDA events around every delta kernel launch, on the launching stream
     evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
@@ -244,6 +248,10 @@ def run_ours(args):
     ms_total = e0.elapsed_time(e1)
     launches = gpu.launch_count() - launches0
     clocks = sampler.stop() if rank == 0 else None
+    per_kernel = {}
+    for name, ms in gpu.profile_read():
+        per_kernel.setdefault(name, []).append(ms)
+    gpu.profile(False)
     fwd_ms = float(np.mean([e[0].elapsed_time(e[1]) for e in evs]))
     bwd_ms = float(np.mean([e[1].elapsed_time(e[2]) for e in evs]))
     if world > 1:
@@ -253,54 +261,90 @@ def run_ours(args):
     ms_step = ms_total / args.steps
     tok_s = world * b * t / (ms_step * 1e-3)
 
-    # ---- end to end through the host-pointer API (pinned host buffers in, host results out)
+    # ---- end to end: pinned host buffers in, host results out, every copy inside the timed region
     e2e_steps = max(1, min(args.steps, 3))
-    hq, hk, hv, ha, hb, hqn, hkn, hdo = (x.numpy() for x in pin)
-    o_h = torch.empty((n, d), dtype=torch.float32).pin_memory().numpy()
-    dqkv_h = torch.empty((n, 3 * d), dtype=torch.float32).pin_memory().numpy()
-    dgate_h = torch.empty((n, 2 * h), dtype=torch.float32).pin_memory().numpy()
-    del q, k, v, d_o, o, ckpt, d_qkv, d_gate
-    torch.cuda.empty_cache()
-    for _ in range(1):
-        _, dd = gpu.delta_scan(hq, hk, hv, ha, hb, b, t, h, dh, out=o_h)
-        gpu.delta_bwd_dev(dd, hdo, hqn, hkn, out=(dqkv_h, dgate_h))
-        dd.free()
+    s_io = 2 if bf16 else 4
+    if bf16:
+        # bf16 mode: the caller holds bf16 activations; device-pointer API + explicit pinned copies
+        hp = [x.bfloat16().pin_memory() if i in (0, 1, 2, 7) else x for i, x in enumerate(pin)]
+        o_h = torch.empty((n, d), dtype=torch.bfloat16).pin_memory()
+        dqkv_h = torch.empty((n, 3 * d), dtype=torch.float32).pin_memory()
+        dgate_h = torch.empty((n, 2 * h), dtype=torch.float32).pin_memory()
+
+        def e2e_step():
+            dq_, dk_, dv_, da_, db_, dqn_, dkn_, ddo_ = (x.to(dev, non_blocking=True) for x in hp)
+            ops.delta_fwd(gpu, dq_, dk_, dv_, da_, db_, b, t, h, dh, chunk=CHUNK, out=o, ckpt=ckpt)
+            ops.delta_bwd(gpu, dq_, dk_, dv_, da_, db_, dqn_, dkn_, ddo_, ckpt, b, t, h, dh, chunk=CHUNK, d_qkv=d_qkv,
+                          d_gate=d_gate)
+            o_h.copy_(o, non_blocking=True)
+            dqkv_h.copy_(d_qkv, non_blocking=True)
+            dgate_h.copy_(d_gate, non_blocking=True)
+            torch.cuda.synchronize()
+
+        h2d = sum(x.numel() * x.element_size() for x in hp)
+        d2h = sum(x.numel() * x.element_size() for x in (o_h, dqkv_h, dgate_h))
+        api = "asca_b200.ops (device-pointer C ABI) with pinned host copies"
+    else:
+        # f32 mode: the host-pointer API with the reference's call shape (Gpu.delta_scan + Gpu.delta_bwd_dev)
+        hq, hk, hv, ha, hb, hqn, hkn, hdo = (x.numpy() for x in pin)
+        o_h = torch.empty((n, d), dtype=torch.float32).pin_memory().numpy()
+        dqkv_h = torch.empty((n, 3 * d), dtype=torch.float32).pin_memory().numpy()
+        dgate_h = torch.empty((n, 2 * h), dtype=torch.float32).pin_memory().numpy()
+        del q, k, v, d_o, o, ckpt, d_qkv, d_gate
+        torch.cuda.empty_cache()
+
+        def e2e_step():
+            _, dd = gpu.delta_scan(hq, hk, hv, ha, hb, b, t, h, dh, out=o_h)
+            gpu.delta_bwd_dev(dd, hdo, hqn, hkn, out=(dqkv_h, dgate_h))
+            dd.free()
+
+        h2d = sum(a.nbytes for a in (hq, hk, hv, ha, hb, hdo, hqn, hkn))
+        d2h = o_h.nbytes + dqkv_h.nbytes + dgate_h.nbytes
+        api = "asca_b200.Gpu.delta_scan + delta_bwd_dev (host-pointer C ABI)"
+    e2e_step()
     barrier()
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
-        _, dd = gpu.delta_scan(hq, hk, hv, ha, hb, b, t, h, dh, out=o_h)
-        gpu.delta_bwd_dev(dd, hdo, hqn, hkn, out=(dqkv_h, dgate_h))
-        dd.free()
+        e2e_step()
     barrier()
     e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
     if world > 1:
         tt = torch.tensor([e2e_ms], device=dev)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         e2e_ms = float(tt.item())
-    h2d = sum(a.nbytes for a in (hq, hk, hv, ha, hb, hdo, hqn, hkn))
-    d2h = o_h.nbytes + dqkv_h.nbytes + dgate_h.nbytes
 
     if rank == 0:
         peak, which = measured_peaks()
-        s = 2 if bf16 else 4
-        bwd_bytes = 7 * n * d * s + 6 * n * h * 4       # q,k,v,dO in; dq,dk,dv out (+ gates)
-        fwd_bytes = 4 * n * d * s + 2 * n * h * 4
-        achieved = bwd_bytes / (bwd_ms * 1e-3) / 1e9
+        # algorithmic bytes of the two ops (q,k,v,o / q,k,v,dO,dq,dk,dv + gates), s_io bytes per activation
+        bwd_bytes = 4 * n * d * s_io + 3 * n * d * 4 + 6 * n * h * 4
+        fwd_bytes = 4 * n * d * s_io + 2 * n * h * 4
+        kern_ms = {name: float(np.mean(v)) for name, v in per_kernel.items()}
+        kern_n = {name: len(v) for name, v in per_kernel.items()}
+        total_k = sum(float(np.sum(v)) for v in per_kernel.values()) or 1.0
+        share = {name: float(np.sum(v)) / total_k for name, v in per_kernel.items()}
+        top = max(share, key=share.get)
+        # the dominant kernel: the backward chain kernel moves the whole backward's algorithmic bytes
+        top_bytes = bwd_bytes if "bwd" in top else fwd_bytes
+        achieved = top_bytes / (kern_ms[top] * 1e-3) / 1e9
         cpu_tok, cpu_ms, cores, sample = time_cpu(1, 1) if world == 1 and not args.no_cpu else (None, None, 0, "skipped")
         line = {
             "metric": METRIC, "value": tok_s, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f32", "io_dtype": args.dtype, "data": "synthetic",
+            "vs_baseline": None, "dtype": "bf16" if bf16 else "f32", "data": "synthetic",
             "config": {"workload": WORKLOAD if (b, t) == (B, T) else f"delta fwd+BPTT B{b} H{h} T{t} dh{dh} chunk{CHUNK}",
+                       "mode": ("bf16 activations on tcgen05 tensor cores, f32 accumulate, f32 state and gates"
+                                if bf16 else "f32 activations and arithmetic (FFMA)"),
                        "l2": "inputs larger than L2 (no flush)", "parallelism": f"dp{world} by sequence, no collective"},
-            "kernels_ms": {"delta_fwd": fwd_ms, "delta_bwd": bwd_ms},
-            "roofline": {"kernel": "delta_bwd_kernel", "bound": "hbm", "achieved": achieved, "peak": peak,
-                         "unit": "GB/s", "frac": achieved / peak, "peak_source": which, "traffic": None,
-                         "algorithmic_bytes": bwd_bytes,
-                         "fwd": {"achieved": fwd_bytes / (fwd_ms * 1e-3) / 1e9, "algorithmic_bytes": fwd_bytes}},
+            "ops_ms": {"delta_fwd": fwd_ms, "delta_bwd": bwd_ms},
+            "kernels_ms": kern_ms, "kernel_launches_per_step": {k_: v_ / args.steps for k_, v_ in kern_n.items()},
+            "kernel_share": share,
+            "roofline": {"kernel": top, "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "peak_source": which, "traffic": None,
+                         "algorithmic_bytes": top_bytes,
+                         "note": "algorithmic bytes of the op the kernel belongs to / that kernel's mean CUDA-event time"},
             "cpu_baseline": {"value": cpu_tok, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": world * b * t / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "api": api},
             "gpu_launches": launches,
             "clocks": clocks,
         }
@@ -315,7 +359,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--dtype", default="f32", choices=["f32", "bf16"])
+    ap.add_argument("--dtype", default="bf16", choices=["f32", "bf16"])
     ap.add_argument("--batch", type=int, default=B)
     ap.add_argument("--seq", type=int, default=T)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")

@@ -57,6 +57,12 @@ const char* asca_last_error(const asca_ctx* ctx);
 const char* asca_describe(asca_ctx* ctx);
 /* Kernel launches issued through this context since creation (rust/src/cuda/mod.rs:25-33). */
 int64_t asca_launch_count(const asca_ctx* ctx);
+/* Per-kernel timing for measurement harnesses (the role of the reference's ASCA_PROF scopes,
+ * rust/src/prof.rs): while on, the delta-rule kernels are bracketed by CUDA events on the
+ * context's stream. asca_ctx_profile(ctx, on) clears the record and switches it;
+ * asca_ctx_profile_read returns entry `index` (kernel name, milliseconds), or 1 past the end. */
+int asca_ctx_profile(asca_ctx* ctx, int on);
+int asca_ctx_profile_read(asca_ctx* ctx, int index, const char** name, float* ms);
 /* Library version string and the arch it was compiled for ("sm_100a"). */
 const char* asca_version(void);
 
