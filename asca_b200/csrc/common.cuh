@@ -29,6 +29,11 @@ struct asca_ctx {
     void* ws = nullptr;
     size_t ws_bytes = 0;
     int* err_word = nullptr;  // device int the kernels with bounded waits write to
+    // tiles of the last tensor-core delta forward that wrote checkpoints, kept for its backward
+    void* dcache = nullptr;
+    size_t dcache_bytes = 0;
+    const void* dcache_ckpt = nullptr;   // key: the checkpoint buffer the forward filled
+    int64_t dcache_B = 0, dcache_T = 0, dcache_H = 0;
     // optional per-kernel timing (asca_ctx_profile): CUDA events around selected launches
     bool profiling = false;
     struct Span {

@@ -1047,21 +1047,40 @@ static inline size_t al(size_t x) { return (x + 1023) & ~(size_t)1023; }
 
 bool available() { return encode_fn() != nullptr; }
 
-// Forward for bf16 q,k,v (dh = 128). o may be bf16 (same dtype as the inputs).
-int forward(asca_ctx* ctx, const void* q, const void* k, const void* v, const float* alpha, const float* beta,
-            int64_t B, int64_t T, int64_t H, void* o, const float* s_init, float* s_final, float* ckpt) {
-    const int64_t n_chunks = (T + C - 1) / C, chains = B * H, n_tiles = chains * n_chunks;
-    const size_t b_wq = al((size_t)n_tiles * 128 * DH * 2), b_uv = al((size_t)n_tiles * 64 * DH * 2),
-                 b_aa = al((size_t)n_tiles * 64 * 64 * 2), b_gc = al((size_t)n_tiles * 4);
-    void* ws;
-    ASCA_TRY(asca_workspace(ctx, b_wq + 2 * b_uv + b_aa + b_gc + 1024, &ws));
-    char* w = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(ws) + 1023) & ~(uintptr_t)1023);
-    Tiles t{};
-    t.WQ = (__nv_bfloat16*)w;
-    t.UV = (__nv_bfloat16*)(w + b_wq);
-    t.KW = (__nv_bfloat16*)(w + b_wq + b_uv);
-    t.AA = (__nv_bfloat16*)(w + b_wq + 2 * b_uv);
-    t.GC = (float*)(w + b_wq + 2 * b_uv + b_aa);
+// Carves the per-(chain, chunk) tile buffers out of `w` (1024-byte aligned). With `full` the
+// backward-only tiles are included.
+static size_t carve_tiles(char* w, int64_t n_tiles, bool full, Tiles* t) {
+    const size_t b128 = al((size_t)n_tiles * 128 * DH * 2), b64 = al((size_t)n_tiles * 64 * DH * 2),
+                 bcc = al((size_t)n_tiles * 64 * 64 * 2), bv = al((size_t)n_tiles * 64 * 4), bg = al((size_t)n_tiles * 4);
+    char* p = w;
+    auto take = [&](size_t n) {
+        char* r = p;
+        p += n;
+        return r;
+    };
+    Tiles z{};
+    z.WQ = (__nv_bfloat16*)take(b128);
+    z.UV = (__nv_bfloat16*)take(b64);
+    z.KW = (__nv_bfloat16*)take(b64);
+    z.AA = (__nv_bfloat16*)take(bcc);
+    z.GC = (float*)take(bg);
+    if (full) {
+        z.BK = (__nv_bfloat16*)take(b64);
+        z.BV = (__nv_bfloat16*)take(b64);
+        z.KR = (__nv_bfloat16*)take(b64);
+        z.QR = (__nv_bfloat16*)take(b64);
+        z.TP = (__nv_bfloat16*)take(bcc);
+        z.KKo = (__nv_bfloat16*)take(bcc);
+        z.QKo = (__nv_bfloat16*)take(bcc);
+        z.GV = (float*)take(bv);
+        z.BE = (float*)take(bv);
+    }
+    if (t) *t = z;
+    return (size_t)(p - w);
+}
+
+static int run_prepass(asca_ctx* ctx, const void* q, const void* k, const void* v, const float* alpha,
+                       const float* beta, int64_t T, int64_t H, int64_t n_chunks, int64_t chains, const Tiles& t) {
     ASCA_CUDA(ctx, cudaFuncSetAttribute(delta_prep_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PRE_SMEM));
     {
         asca_span sp(ctx, "delta_prep_tc_kernel");
@@ -1070,6 +1089,38 @@ int forward(asca_ctx* ctx, const void* q, const void* k, const void* v, const fl
             (int)n_chunks, t, ctx->err_word);
     }
     ASCA_CHECK_LAUNCH(ctx);
+    return ASCA_OK;
+}
+
+// Forward for bf16 q,k,v (dh = 128). o is bf16. When checkpoints are requested (a backward will
+// follow) the pre-pass also writes the backward-only tiles into a context-owned buffer keyed by
+// the checkpoint pointer, so that the backward does not repeat the pre-pass.
+int forward(asca_ctx* ctx, const void* q, const void* k, const void* v, const float* alpha, const float* beta,
+            int64_t B, int64_t T, int64_t H, void* o, const float* s_init, float* s_final, float* ckpt) {
+    const int64_t n_chunks = (T + C - 1) / C, chains = B * H, n_tiles = chains * n_chunks;
+    Tiles t{};
+    const bool keep = ckpt != nullptr;
+    const size_t need = carve_tiles(nullptr, n_tiles, keep, nullptr) + 1024;
+    char* w;
+    if (keep) {
+        ctx->dcache_ckpt = nullptr;
+        if (need > ctx->dcache_bytes) {
+            ASCA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+            if (ctx->dcache) cudaFree(ctx->dcache);
+            ctx->dcache = nullptr;
+            ctx->dcache_bytes = 0;
+            ASCA_CUDA(ctx, cudaMalloc(&ctx->dcache, need));
+            ctx->dcache_bytes = need;
+        }
+        w = (char*)ctx->dcache;
+    } else {
+        void* ws;
+        ASCA_TRY(asca_workspace(ctx, need, &ws));
+        w = (char*)ws;
+    }
+    w = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(w) + 1023) & ~(uintptr_t)1023);
+    carve_tiles(w, n_tiles, keep, &t);
+    ASCA_TRY(run_prepass(ctx, q, k, v, alpha, beta, T, H, n_chunks, chains, t));
     CUtensorMap mWQ, mUV, mKW, mAA;
     if (!make_map(&mWQ, t.WQ, n_tiles * 128, DH, 64, 128) || !make_map(&mUV, t.UV, n_tiles * 64, DH, 64, 64) ||
         !make_map(&mKW, t.KW, n_tiles * 64, DH, 64, 64) || !make_map(&mAA, t.AA, n_tiles * 64, 64, 64, 64))
@@ -1083,6 +1134,12 @@ int forward(asca_ctx* ctx, const void* q, const void* k, const void* v, const fl
                                                                     ckpt, ctx->err_word);
     }
     ASCA_CHECK_LAUNCH(ctx);
+    if (keep) {
+        ctx->dcache_ckpt = ckpt;
+        ctx->dcache_B = B;
+        ctx->dcache_T = T;
+        ctx->dcache_H = H;
+    }
     return ASCA_OK;
 }
 
@@ -1091,34 +1148,20 @@ int backward(asca_ctx* ctx, const void* q, const void* k, const void* v, const f
              const float* qnorm, const float* knorm, const void* d_o, const float* ckpt, int64_t B, int64_t T, int64_t H,
              float* d_qkv, float* d_gate) {
     const int64_t n_chunks = (T + C - 1) / C, chains = B * H, n_tiles = chains * n_chunks;
-    const size_t b128 = al((size_t)n_tiles * 128 * DH * 2), b64 = al((size_t)n_tiles * 64 * DH * 2),
-                 bcc = al((size_t)n_tiles * 64 * 64 * 2), bv = al((size_t)n_tiles * 64 * 4), bg = al((size_t)n_tiles * 4);
-    void* ws;
-    ASCA_TRY(asca_workspace(ctx, b128 + 6 * b64 + 4 * bcc + 2 * bv + bg + 2048, &ws));
-    char* w = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(ws) + 1023) & ~(uintptr_t)1023);
     Tiles t{};
-    t.WQ = (__nv_bfloat16*)w; w += b128;
-    t.UV = (__nv_bfloat16*)w; w += b64;
-    t.KW = (__nv_bfloat16*)w; w += b64;
-    t.BK = (__nv_bfloat16*)w; w += b64;
-    t.BV = (__nv_bfloat16*)w; w += b64;
-    t.KR = (__nv_bfloat16*)w; w += b64;
-    t.QR = (__nv_bfloat16*)w; w += b64;
-    t.AA = (__nv_bfloat16*)w; w += bcc;
-    t.TP = (__nv_bfloat16*)w; w += bcc;
-    t.KKo = (__nv_bfloat16*)w; w += bcc;
-    t.QKo = (__nv_bfloat16*)w; w += bcc;
-    t.GV = (float*)w; w += bv;
-    t.BE = (float*)w; w += bv;
-    t.GC = (float*)w;
-    ASCA_CUDA(ctx, cudaFuncSetAttribute(delta_prep_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PRE_SMEM));
-    {
-        asca_span sp(ctx, "delta_prep_tc_kernel");
-        delta_prep_tc_kernel<<<dim3((unsigned)n_chunks, (unsigned)chains), PRE_THREADS, PRE_SMEM, ctx->stream>>>(
-            (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, alpha, beta, (int)T, (int)H,
-            (int)n_chunks, t, ctx->err_word);
+    const bool cached = ctx->dcache && ctx->dcache_ckpt == (const void*)ckpt && ctx->dcache_B == B && ctx->dcache_T == T &&
+                        ctx->dcache_H == H;
+    if (cached) {
+        // the forward that wrote `ckpt` left its tiles (functions of the same q,k,v,alpha,beta) here
+        char* w = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(ctx->dcache) + 1023) & ~(uintptr_t)1023);
+        carve_tiles(w, n_tiles, true, &t);
+    } else {
+        void* ws;
+        ASCA_TRY(asca_workspace(ctx, carve_tiles(nullptr, n_tiles, true, nullptr) + 1024, &ws));
+        char* w = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(ws) + 1023) & ~(uintptr_t)1023);
+        carve_tiles(w, n_tiles, true, &t);
+        ASCA_TRY(run_prepass(ctx, q, k, v, alpha, beta, T, H, n_chunks, chains, t));
     }
-    ASCA_CHECK_LAUNCH(ctx);
     CUtensorMap mWQ, mBK, mKW, mKR, mQR, mDO, mAA, mTP;
     bool ok = make_map(&mWQ, t.WQ, n_tiles * 128, DH, 64, 64) && make_map(&mBK, t.BK, n_tiles * 64, DH, 64, 64) &&
               make_map(&mKW, t.KW, n_tiles * 64, DH, 64, 64) && make_map(&mKR, t.KR, n_tiles * 64, DH, 64, 64) &&
