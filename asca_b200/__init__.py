@@ -312,4 +312,75 @@ class Gpu:
         return r
 
 
-__all__ = ["Gpu", "DeltaDev", "MoeDev", "MoeBwd", "AscaError", "load", "LIB_PATH", "F32", "BF16", "NN", "TN", "NT"]
+class Model:
+    """Device-resident ASCA model on one flat f32 parameter buffer (reference parameter order,
+    rust/src/model.rs:593-609): forward + backward + AdamW and the per-token decode step."""
+
+    def __init__(self, gpu: Gpu, vocab, d, H, L, E, F):
+        self.gpu, self.cfg = gpu, (vocab, d, H, L, E, F)
+        h = C.c_void_p()
+        gpu._call("asca_model_create", gpu._ctx, *[_i64(v) for v in self.cfg], C.byref(h))
+        self._h = h
+        gpu.lib.asca_model_num_params.restype = C.c_int64
+        self.n = int(gpu.lib.asca_model_num_params(h))
+
+    def set_params(self, params):
+        params = _as_f32(params)
+        assert params.size == self.n
+        self.gpu._call("asca_model_set_params_host", self.gpu._ctx, self._h, _p(params))
+
+    def get(self):
+        p, g = np.empty(self.n, np.float32), np.empty(self.n, np.float32)
+        self.gpu._call("asca_model_get_host", self.gpu._ctx, self._h, _p(p), _p(g))
+        return p, g
+
+    def zero_grads(self):
+        self.gpu._call("asca_model_zero_grads", self.gpu._ctx, self._h)
+
+    def buffers(self):
+        """Device addresses (ints) of the flat params, grads, Adam m and Adam v buffers."""
+        ptrs = [C.c_void_p() for _ in range(4)]
+        self.gpu._call("asca_model_buffers", self._h, *[C.byref(x) for x in ptrs])
+        return [x.value for x in ptrs]
+
+    def set_grads(self, grads):
+        grads = _as_f32(grads)
+        assert grads.size == self.n
+        self.gpu._call("asca_memcpy_h2d", self.gpu._ctx, C.c_void_p(self.buffers()[1]), _p(grads), C.c_size_t(self.n * 4))
+
+    def forward_backward(self, ids, targets, batch, want_logits=False):
+        ids = np.ascontiguousarray(ids, dtype=np.uint32)
+        targets = np.ascontiguousarray(targets, dtype=np.uint32)
+        n = ids.size
+        loss = C.c_float()
+        logits = np.empty((n, self.cfg[0]), np.float32) if want_logits else None
+        self.gpu._call("asca_model_forward_backward_host", self.gpu._ctx, self._h, _p(ids), _p(targets), _i64(batch),
+                       _i64(n // batch), C.byref(loss), _p(logits))
+        return (loss.value, logits) if want_logits else loss.value
+
+    def adamw_step(self, lr, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.01):
+        self.gpu._call("asca_model_adamw_step", self.gpu._ctx, self._h, _f(lr), _f(beta1), _f(beta2), _f(eps), _f(wd))
+
+    def new_decode_state(self, n_streams):
+        import torch
+
+        _, d, H, L, _, _ = self.cfg
+        dh = d // H
+        return torch.zeros((L, n_streams, H, dh, dh), dtype=torch.float32, device=f"cuda:{self.gpu.device}")
+
+    def decode_step(self, state, ids, want_logits=True):
+        ids = np.ascontiguousarray(ids, dtype=np.uint32)
+        ns = ids.size
+        logits = np.empty((ns, self.cfg[0]), np.float32) if want_logits else None
+        nxt = np.empty(ns, np.uint32)
+        self.gpu._call("asca_model_decode_step_host", self.gpu._ctx, self._h, _p(state), _p(ids), _i64(ns), _p(logits),
+                       _p(nxt))
+        return logits, nxt
+
+    def free(self):
+        if self._h is not None:
+            self.gpu.lib.asca_model_destroy(self.gpu._ctx, self._h)
+            self._h = None
+
+
+__all__ = ["Gpu", "Model", "DeltaDev", "MoeDev", "MoeBwd", "AscaError", "load", "LIB_PATH", "F32", "BF16", "NN", "TN", "NT"]

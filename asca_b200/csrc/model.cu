@@ -1,0 +1,445 @@
+// Model glue: embedding, N x [x += Delta(x); x += HashMoE(RMSNorm(x))], final RMSNorm, head,
+// cross-entropy, backward, AdamW, and the per-token decode step -- the dataflow of
+// rust/src/model.rs:631-802 and rust/src/delta.rs:121-207 / :615-674, composed from the
+// library's own entry points with every activation resident in HBM. f32 arithmetic.
+#include "common.cuh"
+
+namespace {
+
+// ------------------------------------------------------------------ small kernels
+// out[c] (+)= sum_r src[r, c]: each CTA owns 32 columns, 8 warps stride the rows, fixed-order tree.
+__global__ void __launch_bounds__(256) colsum_plain_kernel(const float* __restrict__ src, int64_t ld, int64_t rows,
+                                                           int cols, float* __restrict__ out, int accumulate) {
+    __shared__ float part[8][33];
+    const int c = blockIdx.x * 32 + (threadIdx.x & 31), w = threadIdx.x >> 5;
+    float acc = 0.0f;
+    if (c < cols)
+        for (int64_t r = w; r < rows; r += 8) acc += src[r * ld + c];
+    part[w][threadIdx.x & 31] = acc;
+    __syncthreads();
+    if (w == 0 && c < cols) {
+        float t = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) t += part[i][threadIdx.x];
+        out[c] = accumulate ? out[c] + t : t;
+    }
+}
+
+// One warp per row: log-sum-exp, loss_t, dlogits = (p - onehot) * inv_n. rust/src/model.rs:821-837.
+__global__ void __launch_bounds__(256) cross_entropy_kernel(const float* __restrict__ logits,
+                                                            const uint32_t* __restrict__ targets, int64_t N, int V,
+                                                            float* __restrict__ dlogits, float* __restrict__ losses,
+                                                            float inv_n) {
+    const int lane = threadIdx.x & 31;
+    const int64_t t = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (t >= N) return;
+    const float* row = logits + t * V;
+    float mx = -INFINITY;
+    for (int c = lane; c < V; c += 32) mx = fmaxf(mx, row[c]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.0f;
+    for (int c = lane; c < V; c += 32) sum += expf(row[c] - mx);
+    sum = warp_sum(sum);
+    const float lse = mx + logf(sum);
+    const uint32_t tg = targets[t];
+    if (lane == 0) losses[t] = lse - row[tg];
+    if (dlogits) {
+        float* drow = dlogits + t * V;
+        for (int c = lane; c < V; c += 32) drow[c] = expf(row[c] - lse) * inv_n - ((uint32_t)c == tg ? inv_n : 0.0f);
+    }
+}
+// Deterministic mean of n values (one CTA, fixed tree).
+__global__ void __launch_bounds__(1024) mean_kernel(const float* __restrict__ v, int64_t n, float scale,
+                                                    float* __restrict__ out) {
+    __shared__ float red[33];
+    float acc = 0.0f;
+    for (int64_t i = threadIdx.x; i < n; i += 1024) acc += v[i];
+    const float s = block_sum(acc, red);
+    if (threadIdx.x == 0) *out = s * scale;
+}
+
+__global__ void __launch_bounds__(256) embed_fwd_kernel(const float* __restrict__ table,
+                                                        const uint32_t* __restrict__ ids, int64_t N, int d,
+                                                        float* __restrict__ x) {
+    const int lane = threadIdx.x & 31;
+    const int64_t t = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (t >= N) return;
+    const float* src = table + (int64_t)ids[t] * d;
+    for (int c = lane; c < d; c += 32) x[t * d + c] = src[c];
+}
+// d_table[v, c] += sum over tokens t (ascending) with ids[t] == v of dx[t, c]. grid (vocab, ceil(d/128)).
+__global__ void __launch_bounds__(128) embed_bwd_kernel(const float* __restrict__ dx, const uint32_t* __restrict__ ids,
+                                                        int64_t N, int d, float* __restrict__ d_table) {
+    const uint32_t v = blockIdx.x;
+    const int c = blockIdx.y * 128 + threadIdx.x;
+    float acc = 0.0f;
+    bool any = false;
+    for (int64_t t = 0; t < N; ++t)
+        if (ids[t] == v) {
+            any = true;
+            if (c < d) acc += dx[t * d + c];
+        }
+    if (any && c < d) d_table[(int64_t)v * d + c] += acc;
+}
+__global__ void __launch_bounds__(256) add_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                                                  float* __restrict__ out, int64_t n) {
+    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (i < n) out[i] = a[i] + 1.0f * b[i];
+}
+// greedy argmax per row, lowest index on ties
+__global__ void __launch_bounds__(256) argmax_kernel(const float* __restrict__ logits, int64_t N, int V,
+                                                     uint32_t* __restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    const int64_t t = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (t >= N) return;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int c = lane; c < V; c += 32) {
+        const float x = logits[t * V + c];
+        if (x > best) {
+            best = x;
+            bi = c;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ob > best || (ob == best && oi < bi)) {
+            best = ob;
+            bi = oi;
+        }
+    }
+    if (lane == 0) out[t] = (uint32_t)bi;
+}
+
+struct Lyr {
+    int64_t w_qkv, b_qkv, w_gate, b_gate, w_o, b_o, w1, b1, w2, b2;
+};
+
+struct Bufs {   // device buffers from the context cache, released together
+    asca_ctx* ctx;
+    std::vector<void*> p;
+    explicit Bufs(asca_ctx* c) : ctx(c) {}
+    ~Bufs() {
+        for (void* x : p) asca_free(ctx, x);
+    }
+    float* f(int64_t n) {
+        void* d = nullptr;
+        if (asca_malloc(ctx, (size_t)(n > 0 ? n : 1) * 4, &d) != ASCA_OK) return nullptr;
+        p.push_back(d);
+        return (float*)d;
+    }
+};
+
+}  // namespace
+
+struct asca_model {
+    int64_t vocab, d, H, L, E, F, n_params;
+    int64_t embed, head;
+    std::vector<Lyr> lay;
+    std::vector<int64_t> seg_off;   // tensor offsets in parameter order, + total
+    float *params = nullptr, *grads = nullptr, *m = nullptr, *v = nullptr;
+    uint32_t adam_counter = 0;
+};
+
+extern "C" {
+
+int asca_colsum(asca_ctx* ctx, const float* src, int64_t ld, int64_t rows, int64_t cols, float* out, int accumulate) {
+    if (!ctx) return ASCA_ERR_ARG;
+    ASCA_REQUIRE(ctx, src && out && rows >= 0 && cols > 0 && ld >= cols, "colsum: bad arguments");
+    colsum_plain_kernel<<<(unsigned)ceil_div64(cols, 32), 256, 0, ctx->stream>>>(src, ld, rows, (int)cols, out, accumulate);
+    ASCA_CHECK_LAUNCH(ctx);
+    return ASCA_OK;
+}
+
+int asca_cross_entropy(asca_ctx* ctx, const float* logits, const uint32_t* targets, int64_t N, int64_t V,
+                       float* dlogits, float* loss) {
+    if (!ctx) return ASCA_ERR_ARG;
+    ASCA_REQUIRE(ctx, logits && targets && loss && N > 0 && V > 0, "cross_entropy: bad arguments");
+    void* ws;
+    ASCA_TRY(asca_workspace(ctx, (size_t)N * 4 + 256, &ws));
+    cross_entropy_kernel<<<(unsigned)ceil_div64(N, 8), 256, 0, ctx->stream>>>(logits, targets, N, (int)V, dlogits,
+                                                                              (float*)ws, 1.0f / (float)N);
+    ASCA_CHECK_LAUNCH(ctx);
+    mean_kernel<<<1, 1024, 0, ctx->stream>>>((const float*)ws, N, 1.0f / (float)N, loss);
+    ASCA_CHECK_LAUNCH(ctx);
+    return ASCA_OK;
+}
+
+int asca_embed_fwd(asca_ctx* ctx, const float* table, const uint32_t* ids, int64_t N, int64_t d, float* x) {
+    if (!ctx) return ASCA_ERR_ARG;
+    ASCA_REQUIRE(ctx, table && ids && x && N >= 0 && d > 0, "embed_fwd: bad arguments");
+    if (N == 0) return ASCA_OK;
+    embed_fwd_kernel<<<(unsigned)ceil_div64(N, 8), 256, 0, ctx->stream>>>(table, ids, N, (int)d, x);
+    ASCA_CHECK_LAUNCH(ctx);
+    return ASCA_OK;
+}
+
+int asca_embed_bwd(asca_ctx* ctx, const float* dx, const uint32_t* ids, int64_t N, int64_t d, int64_t vocab,
+                   float* d_table) {
+    if (!ctx) return ASCA_ERR_ARG;
+    ASCA_REQUIRE(ctx, dx && ids && d_table && N >= 0 && d > 0 && vocab > 0 && vocab < 65536, "embed_bwd: bad arguments");
+    if (N == 0) return ASCA_OK;
+    embed_bwd_kernel<<<dim3((unsigned)vocab, (unsigned)ceil_div64(d, 128)), 128, 0, ctx->stream>>>(dx, ids, N, (int)d, d_table);
+    ASCA_CHECK_LAUNCH(ctx);
+    return ASCA_OK;
+}
+
+int asca_model_create(asca_ctx* ctx, int64_t vocab, int64_t d, int64_t H, int64_t L, int64_t E, int64_t F,
+                      asca_model** out) {
+    if (!ctx || !out) return ASCA_ERR_ARG;
+    ASCA_REQUIRE(ctx, vocab > 0 && d > 0 && H > 0 && L > 0 && E > 0 && F > 0 && d % H == 0, "model_create: bad config");
+    const int64_t dh = d / H;
+    if (dh != 16 && dh != 32 && dh != 64 && dh != 128)
+        return asca_fail(ctx, ASCA_ERR_UNSUPPORTED, "model_create: d/H must be 16, 32, 64 or 128");
+    asca_model* m = new asca_model();
+    m->vocab = vocab; m->d = d; m->H = H; m->L = L; m->E = E; m->F = F;
+    int64_t o = 0;
+    auto take = [&](int64_t n) {
+        const int64_t at = o;
+        m->seg_off.push_back(at);
+        o += n;
+        return at;
+    };
+    m->embed = take(vocab * d);
+    m->head = take(d * vocab);
+    for (int64_t i = 0; i < L; ++i) {
+        Lyr y;
+        y.w_qkv = take(d * 3 * d); y.b_qkv = take(3 * d);
+        y.w_gate = take(d * 2 * H); y.b_gate = take(2 * H);
+        y.w_o = take(d * d); y.b_o = take(d);
+        y.w1 = take(d * E * F); y.b1 = take(E * F);
+        y.w2 = take(E * F * d); y.b2 = take(d);
+        m->lay.push_back(y);
+    }
+    m->seg_off.push_back(o);
+    m->n_params = o;
+    float** bufs[4] = {&m->params, &m->grads, &m->m, &m->v};
+    for (auto b : bufs) {
+        if (cudaMalloc((void**)b, (size_t)o * 4) != cudaSuccess) {
+            asca_model_destroy(ctx, m);
+            return asca_fail(ctx, ASCA_ERR_OOM, "model_create: cannot allocate %lld parameters", (long long)o);
+        }
+        cudaMemsetAsync(*b, 0, (size_t)o * 4, ctx->stream);
+    }
+    *out = m;
+    return ASCA_OK;
+}
+
+int asca_model_destroy(asca_ctx* ctx, asca_model* m) {
+    if (!m) return ASCA_OK;
+    if (ctx) cudaStreamSynchronize(ctx->stream);
+    for (float* b : {m->params, m->grads, m->m, m->v})
+        if (b) cudaFree(b);
+    delete m;
+    return ASCA_OK;
+}
+
+int64_t asca_model_num_params(const asca_model* m) { return m ? m->n_params : 0; }
+
+int asca_model_buffers(asca_model* m, float** params, float** grads, float** adam_m, float** adam_v) {
+    if (!m) return ASCA_ERR_ARG;
+    if (params) *params = m->params;
+    if (grads) *grads = m->grads;
+    if (adam_m) *adam_m = m->m;
+    if (adam_v) *adam_v = m->v;
+    return ASCA_OK;
+}
+
+int asca_model_set_params_host(asca_ctx* ctx, asca_model* m, const float* params) {
+    if (!ctx || !m || !params) return ASCA_ERR_ARG;
+    m->adam_counter = 0;
+    ASCA_CUDA(ctx, cudaMemsetAsync(m->m, 0, (size_t)m->n_params * 4, ctx->stream));
+    ASCA_CUDA(ctx, cudaMemsetAsync(m->v, 0, (size_t)m->n_params * 4, ctx->stream));
+    return asca_memcpy_h2d(ctx, m->params, params, (size_t)m->n_params * 4);
+}
+
+int asca_model_get_host(asca_ctx* ctx, asca_model* m, float* params, float* grads) {
+    if (!ctx || !m) return ASCA_ERR_ARG;
+    if (params) ASCA_TRY(asca_memcpy_d2h(ctx, params, m->params, (size_t)m->n_params * 4));
+    if (grads) ASCA_TRY(asca_memcpy_d2h(ctx, grads, m->grads, (size_t)m->n_params * 4));
+    return ASCA_OK;
+}
+
+int asca_model_zero_grads(asca_ctx* ctx, asca_model* m) {
+    if (!ctx || !m) return ASCA_ERR_ARG;
+    ASCA_CUDA(ctx, cudaMemsetAsync(m->grads, 0, (size_t)m->n_params * 4, ctx->stream));
+    return ASCA_OK;
+}
+
+int asca_model_forward_backward_host(asca_ctx* ctx, asca_model* m, const uint32_t* ids_h, const uint32_t* tg_h,
+                                     int64_t B, int64_t T, float* loss_h, float* logits_h) {
+    if (!ctx || !m) return ASCA_ERR_ARG;
+    ASCA_REQUIRE(ctx, ids_h && tg_h && loss_h && B > 0 && T > 0, "model_forward_backward: bad arguments");
+    const int64_t N = B * T, d = m->d, H = m->H, dh = d / H, E = m->E, F = m->F, V = m->vocab, L = m->L;
+    const int64_t CH = 64;
+    for (int64_t i = 0; i < N; ++i)
+        ASCA_REQUIRE(ctx, ids_h[i] < (uint32_t)V && tg_h[i] < (uint32_t)V, "model_forward_backward: id out of range");
+    float* P = m->params;
+    float* G = m->grads;
+    Bufs bf(ctx);
+    uint32_t* ids = (uint32_t*)bf.f(N);
+    uint32_t* tg = (uint32_t*)bf.f(N);
+    int32_t* perm = (int32_t*)bf.f(N);
+    int32_t* offs = (int32_t*)bf.f(E + 1);
+    ASCA_REQUIRE(ctx, ids && tg && perm && offs, "model_forward_backward: out of memory");
+    ASCA_CUDA(ctx, cudaMemcpyAsync(ids, ids_h, (size_t)N * 4, cudaMemcpyHostToDevice, ctx->stream));
+    ASCA_CUDA(ctx, cudaMemcpyAsync(tg, tg_h, (size_t)N * 4, cudaMemcpyHostToDevice, ctx->stream));
+    ASCA_TRY(asca_moe_dispatch(ctx, ids, N, E, perm, offs, nullptr));   // same routing for every layer
+
+    struct Act {
+        float *x_in, *q, *k, *v, *qn, *kn, *al, *be, *o, *ckpt, *x_mid, *xn, *pre_p, *hid_p;
+    };
+    std::vector<Act> acts(L);
+    const int64_t nck = asca_delta_ckpt_floats(B, T, H, dh, CH);
+    float* x = bf.f(N * d);
+    float* qkv = bf.f(N * 3 * d);
+    float* gate = bf.f(N * 2 * H);
+    float* y = bf.f(N * d);
+    float* mo = bf.f(N * d);
+    ASCA_REQUIRE(ctx, x && qkv && gate && y && mo, "model_forward_backward: out of memory");
+    ASCA_TRY(asca_embed_fwd(ctx, P + m->embed, ids, N, d, x));
+    // ---- forward (rust/src/model.rs:651-700)
+    for (int64_t li = 0; li < L; ++li) {
+        const Lyr& w = m->lay[li];
+        Act& a = acts[li];
+        a.x_in = bf.f(N * d); a.q = bf.f(N * d); a.k = bf.f(N * d); a.v = bf.f(N * d);
+        a.qn = bf.f(N * H); a.kn = bf.f(N * H); a.al = bf.f(N * H); a.be = bf.f(N * H);
+        a.o = bf.f(N * d); a.ckpt = bf.f(nck); a.x_mid = bf.f(N * d); a.xn = bf.f(N * d);
+        a.pre_p = bf.f(N * F); a.hid_p = bf.f(N * F);
+        ASCA_REQUIRE(ctx, a.x_in && a.q && a.k && a.v && a.qn && a.kn && a.al && a.be && a.o && a.ckpt && a.x_mid && a.xn &&
+                              a.pre_p && a.hid_p, "model_forward_backward: out of memory");
+        ASCA_CUDA(ctx, cudaMemcpyAsync(a.x_in, x, (size_t)N * d * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+        ASCA_TRY(asca_gemm(ctx, ASCA_NN, N, 3 * d, d, x, d, P + w.w_qkv, 3 * d, qkv, 3 * d, P + w.b_qkv, 0, ASCA_F32));
+        ASCA_TRY(asca_gemm(ctx, ASCA_NN, N, 2 * H, d, x, d, P + w.w_gate, 2 * H, gate, 2 * H, P + w.b_gate, 0, ASCA_F32));
+        ASCA_TRY(asca_delta_prep(ctx, qkv, gate, N, H, dh, a.q, a.k, a.v, a.qn, a.kn, a.al, a.be));
+        ASCA_TRY(asca_delta_fwd(ctx, a.q, a.k, a.v, a.al, a.be, B, T, H, dh, CH, ASCA_F32, a.o, nullptr, nullptr, a.ckpt));
+        ASCA_TRY(asca_gemm(ctx, ASCA_NN, N, d, d, a.o, d, P + w.w_o, d, y, d, P + w.b_o, 0, ASCA_F32));
+        ASCA_TRY(asca_residual_rmsnorm(ctx, x, y, a.x_mid, a.xn, N, d, 1e-6f));
+        ASCA_TRY(asca_moe_fwd(ctx, a.xn, P + w.w1, P + w.b1, P + w.w2, P + w.b2, perm, offs, N, d, F, E, ASCA_F32, mo,
+                              a.pre_p, a.hid_p));
+        ASCA_TRY(asca_residual_rmsnorm(ctx, a.x_mid, mo, x, nullptr, N, d, 1e-6f));   // x_out
+    }
+    float* h_final = bf.f(N * d);
+    float* logits = bf.f(N * V);
+    float* dlogits = bf.f(N * V);
+    float* loss_d = bf.f(1);
+    ASCA_REQUIRE(ctx, h_final && logits && dlogits && loss_d, "model_forward_backward: out of memory");
+    ASCA_TRY(asca_rmsnorm_fwd(ctx, x, h_final, nullptr, N, d, 1e-6f));
+    ASCA_TRY(asca_gemm(ctx, ASCA_NN, N, V, d, h_final, d, P + m->head, V, logits, V, nullptr, 0, ASCA_F32));
+    if (logits_h) ASCA_CUDA(ctx, cudaMemcpyAsync(logits_h, logits, (size_t)N * V * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    // ---- backward (rust/src/model.rs:744-794)
+    ASCA_TRY(asca_cross_entropy(ctx, logits, tg, N, V, dlogits, loss_d));
+    ASCA_CUDA(ctx, cudaMemcpyAsync(loss_h, loss_d, 4, cudaMemcpyDeviceToHost, ctx->stream));
+    ASCA_TRY(asca_gemm(ctx, ASCA_TN, d, V, N, h_final, d, dlogits, V, G + m->head, V, nullptr, 1, ASCA_F32));
+    float* dh_ = bf.f(N * d);
+    float* dx = bf.f(N * d);
+    float* dxn = bf.f(N * d);
+    float* d_moe = bf.f(N * d);
+    float* d_o = bf.f(N * d);
+    float* d_qkv = bf.f(N * 3 * d);
+    float* d_gate = bf.f(N * 2 * H);
+    float* tmp_w1 = bf.f(d * E * F);
+    float* tmp_b1 = bf.f(E * F);
+    float* tmp_w2 = bf.f(E * F * d);
+    float* tmp_b2 = bf.f(d);
+    ASCA_REQUIRE(ctx, dh_ && dx && dxn && d_moe && d_o && d_qkv && d_gate && tmp_w1 && tmp_b1 && tmp_w2 && tmp_b2,
+                 "model_forward_backward: out of memory");
+    ASCA_TRY(asca_gemm(ctx, ASCA_NT, N, d, V, dlogits, V, P + m->head, V, dh_, d, nullptr, 0, ASCA_F32));
+    ASCA_TRY(asca_rmsnorm_bwd(ctx, x, dh_, dx, N, d, 1e-6f));   // x = x_out of the last layer
+    const int64_t blocks_nd = ceil_div64(N * d, 256);
+    for (int64_t li = L - 1; li >= 0; --li) {
+        const Lyr& w = m->lay[li];
+        Act& a = acts[li];
+        // HashMoe::backward: gradients accumulate into the flat buffer
+        ASCA_TRY(asca_moe_bwd(ctx, a.xn, P + w.w1, P + w.w2, a.pre_p, a.hid_p, dx, perm, offs, N, d, F, E, ASCA_F32, tmp_w1,
+                              tmp_b1, tmp_w2, tmp_b2, dxn));
+        add_kernel<<<(unsigned)ceil_div64(d * E * F, 256), 256, 0, ctx->stream>>>(G + w.w1, tmp_w1, G + w.w1, d * E * F);
+        add_kernel<<<(unsigned)ceil_div64(E * F, 256), 256, 0, ctx->stream>>>(G + w.b1, tmp_b1, G + w.b1, E * F);
+        add_kernel<<<(unsigned)ceil_div64(E * F * d, 256), 256, 0, ctx->stream>>>(G + w.w2, tmp_w2, G + w.w2, E * F * d);
+        add_kernel<<<(unsigned)ceil_div64(d, 256), 256, 0, ctx->stream>>>(G + w.b2, tmp_b2, G + w.b2, d);
+        ctx->launches += 4;
+        ASCA_TRY(asca_rmsnorm_bwd(ctx, a.x_mid, dxn, d_moe, N, d, 1e-6f));
+        add_kernel<<<(unsigned)blocks_nd, 256, 0, ctx->stream>>>(dx, d_moe, dx, N * d);   // d_mid
+        ctx->launches++;
+        // DeltaBlock::backward (rust/src/delta.rs:615-674)
+        ASCA_TRY(asca_gemm(ctx, ASCA_NT, N, d, d, dx, d, P + w.w_o, d, d_o, d, nullptr, 0, ASCA_F32));
+        ASCA_TRY(asca_gemm(ctx, ASCA_TN, d, d, N, a.o, d, dx, d, G + w.w_o, d, nullptr, 1, ASCA_F32));
+        ASCA_TRY(asca_colsum(ctx, dx, d, N, d, G + w.b_o, 1));
+        ASCA_TRY(asca_delta_bwd(ctx, a.q, a.k, a.v, a.al, a.be, a.qn, a.kn, d_o, a.ckpt, B, T, H, dh, CH, ASCA_F32, d_qkv,
+                                d_gate));
+        ASCA_TRY(asca_gemm(ctx, ASCA_TN, d, 3 * d, N, a.x_in, d, d_qkv, 3 * d, G + w.w_qkv, 3 * d, nullptr, 1, ASCA_F32));
+        ASCA_TRY(asca_colsum(ctx, d_qkv, 3 * d, N, 3 * d, G + w.b_qkv, 1));
+        ASCA_TRY(asca_gemm(ctx, ASCA_TN, d, 2 * H, N, a.x_in, d, d_gate, 2 * H, G + w.w_gate, 2 * H, nullptr, 1, ASCA_F32));
+        ASCA_TRY(asca_colsum(ctx, d_gate, 2 * H, N, 2 * H, G + w.b_gate, 1));
+        // dx = d_mid + d_qkv Wqkv^T + d_gate Wg^T   (accumulate onto d_mid in place)
+        ASCA_TRY(asca_gemm(ctx, ASCA_NT, N, d, 3 * d, d_qkv, 3 * d, P + w.w_qkv, 3 * d, dx, d, nullptr, 1, ASCA_F32));
+        ASCA_TRY(asca_gemm(ctx, ASCA_NT, N, d, 2 * H, d_gate, 2 * H, P + w.w_gate, 2 * H, dx, d, nullptr, 1, ASCA_F32));
+    }
+    ASCA_TRY(asca_embed_bwd(ctx, dx, ids, N, d, V, G + m->embed));
+    ASCA_CUDA(ctx, cudaGetLastError());
+    return asca_ctx_sync(ctx);
+}
+
+int asca_model_adamw_step(asca_ctx* ctx, asca_model* m, float lr, float beta1, float beta2, float eps, float wd) {
+    if (!ctx || !m) return ASCA_ERR_ARG;
+    const int n_seg = (int)m->seg_off.size() - 1;
+    std::vector<float> lr_t(n_seg), eps_t(n_seg);
+    auto powi = [](float b, int e) {   // f32 exponentiation by squaring, as `f32::powi` lowers
+        float r = 1.0f, x = b;
+        while (e > 0) {
+            if (e & 1) r *= x;
+            x *= x;
+            e >>= 1;
+        }
+        return r;
+    };
+    for (int i = 0; i < n_seg; ++i) {
+        m->adam_counter += 1;   // once per tensor (rust/src/tensor.rs:393)
+        const float bc1 = 1.0f - powi(beta1, (int)m->adam_counter), bc2 = 1.0f - powi(beta2, (int)m->adam_counter);
+        lr_t[i] = lr * sqrtf(bc1 / bc2);
+        eps_t[i] = eps * sqrtf(bc2);
+    }
+    return asca_adamw_segmented(ctx, m->params, m->grads, m->m, m->v, m->seg_off.data(), lr_t.data(), eps_t.data(), n_seg,
+                                beta1, beta2, lr * wd);
+}
+
+int asca_model_decode_step_host(asca_ctx* ctx, asca_model* m, float* state, const uint32_t* ids_h, int64_t ns,
+                                float* logits_h, uint32_t* next_h) {
+    if (!ctx || !m) return ASCA_ERR_ARG;
+    ASCA_REQUIRE(ctx, state && ids_h && ns > 0, "model_decode_step: bad arguments");
+    const int64_t d = m->d, H = m->H, dh = d / H, E = m->E, F = m->F, V = m->vocab;
+    for (int64_t i = 0; i < ns; ++i) ASCA_REQUIRE(ctx, ids_h[i] < (uint32_t)V, "model_decode_step: id out of range");
+    float* P = m->params;
+    Bufs bf(ctx);
+    uint32_t* ids = (uint32_t*)bf.f(ns);
+    uint32_t* nxt = (uint32_t*)bf.f(ns);
+    float *x = bf.f(ns * d), *qkv = bf.f(ns * 3 * d), *gate = bf.f(ns * 2 * H), *o = bf.f(ns * d), *y = bf.f(ns * d),
+          *x_mid = bf.f(ns * d), *mo = bf.f(ns * d), *hf = bf.f(ns * d), *logits = bf.f(ns * V);
+    ASCA_REQUIRE(ctx, ids && nxt && x && qkv && gate && o && y && x_mid && mo && hf && logits, "model_decode_step: out of memory");
+    ASCA_CUDA(ctx, cudaMemcpyAsync(ids, ids_h, (size_t)ns * 4, cudaMemcpyHostToDevice, ctx->stream));
+    ASCA_TRY(asca_embed_fwd(ctx, P + m->embed, ids, ns, d, x));
+    for (int64_t li = 0; li < m->L; ++li) {
+        const Lyr& w = m->lay[li];
+        ASCA_TRY(asca_gemm(ctx, ASCA_NN, ns, 3 * d, d, x, d, P + w.w_qkv, 3 * d, qkv, 3 * d, P + w.b_qkv, 0, ASCA_F32));
+        ASCA_TRY(asca_gemm(ctx, ASCA_NN, ns, 2 * H, d, x, d, P + w.w_gate, 2 * H, gate, 2 * H, P + w.b_gate, 0, ASCA_F32));
+        ASCA_TRY(asca_delta_step(ctx, qkv, nullptr, nullptr, gate, nullptr, state + li * ns * H * dh * dh, ns, H, dh, 1, o));
+        ASCA_TRY(asca_gemm(ctx, ASCA_NN, ns, d, d, o, d, P + w.w_o, d, y, d, P + w.b_o, 0, ASCA_F32));
+        ASCA_TRY(asca_residual_rmsnorm(ctx, x, y, x_mid, nullptr, ns, d, 1e-6f));
+        ASCA_TRY(asca_moe_step(ctx, x_mid, ids, P + w.w1, P + w.b1, P + w.w2, P + w.b2, ns, d, F, E, ASCA_F32, mo));
+        ASCA_TRY(asca_residual_rmsnorm(ctx, x_mid, mo, x, nullptr, ns, d, 1e-6f));
+    }
+    ASCA_TRY(asca_rmsnorm_fwd(ctx, x, hf, nullptr, ns, d, 1e-6f));
+    ASCA_TRY(asca_gemm(ctx, ASCA_NN, ns, V, d, hf, d, P + m->head, V, logits, V, nullptr, 0, ASCA_F32));
+    if (logits_h) ASCA_CUDA(ctx, cudaMemcpyAsync(logits_h, logits, (size_t)ns * V * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    if (next_h) {
+        argmax_kernel<<<(unsigned)ceil_div64(ns, 8), 256, 0, ctx->stream>>>(logits, ns, (int)V, nxt);
+        ASCA_CHECK_LAUNCH(ctx);
+        ASCA_CUDA(ctx, cudaMemcpyAsync(next_h, nxt, (size_t)ns * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    }
+    return asca_ctx_sync(ctx);
+}
+
+}  // extern "C"

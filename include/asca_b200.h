@@ -255,6 +255,61 @@ int asca_moe_dev_download_pre_hidden(asca_ctx* ctx, const asca_moe_dev* dev, flo
                                      float* hidden);
 int asca_moe_dev_free(asca_ctx* ctx, asca_moe_dev* dev);
 
+
+/* ------------------------------------------------------------------ column sums, cross-entropy, embedding
+ * Helpers of the model glue (bias gradients, loss, embedding table), all deterministic.
+ * asca_colsum: out[c] (+)= sum_r src[r, c] over `rows` rows of pitch `ld` -- the bias-gradient
+ * loops of rust/src/delta.rs:623-666 and the reference kernel colsum_f32
+ * (rust/kernels/asca.cu:166-178). */
+int asca_colsum(asca_ctx* ctx, const float* src, int64_t ld, int64_t rows, int64_t cols, float* out,
+                int accumulate);
+/* Cross-entropy over N rows of V logits (cpu_cross_entropy, rust/src/model.rs:804-844; reference
+ * kernel cross_entropy_bwd_f32, rust/kernels/asca.cu:490-548): writes dlogits = (softmax -
+ * onehot) / N (nullable) and the mean loss to *loss (device float). targets are uint32. */
+int asca_cross_entropy(asca_ctx* ctx, const float* logits, const uint32_t* targets, int64_t N,
+                       int64_t V, float* dlogits, float* loss);
+/* Embedding lookup x[t,:] = table[ids[t],:] (rust/src/model.rs:654-660) and its gradient
+ * d_table[v,:] += sum over tokens with ids[t] == v, in token order, of dx[t,:]
+ * (rust/src/model.rs:785-791). */
+int asca_embed_fwd(asca_ctx* ctx, const float* table, const uint32_t* ids, int64_t N, int64_t d,
+                   float* x);
+int asca_embed_bwd(asca_ctx* ctx, const float* dx, const uint32_t* ids, int64_t N, int64_t d,
+                   int64_t vocab, float* d_table);
+
+/* ------------------------------------------------------------------ model glue (X1)
+ * Model::forward / backward / step and the AdamW loop (rust/src/model.rs:631-802) on one flat
+ * f32 parameter buffer in the reference's parameter order (rust/src/model.rs:593-609: embed,
+ * head, then per layer w_qkv, b_qkv, w_gate, b_gate, w_o, b_o, w1, b1, w2, b2). Everything
+ * stays on the device between calls; the Delta block takes the un-normalised residual stream
+ * as the reference code does (rust/src/model.rs:664-667). f32 arithmetic. */
+typedef struct asca_model asca_model;
+int asca_model_create(asca_ctx* ctx, int64_t vocab, int64_t d, int64_t H, int64_t L, int64_t E,
+                      int64_t F, asca_model** out);
+int asca_model_destroy(asca_ctx* ctx, asca_model* m);
+int64_t asca_model_num_params(const asca_model* m);
+/* Device pointers of the flat buffers (params, grads, Adam m, Adam v), each num_params floats. */
+int asca_model_buffers(asca_model* m, float** params, float** grads, float** adam_m, float** adam_v);
+int asca_model_set_params_host(asca_ctx* ctx, asca_model* m, const float* params);
+int asca_model_get_host(asca_ctx* ctx, asca_model* m, float* params, float* grads);
+int asca_model_zero_grads(asca_ctx* ctx, asca_model* m);
+/* Forward + backward over B sequences of T tokens (ids, targets: host uint32 arrays of B*T).
+ * Gradients are accumulated into the flat grad buffer; *loss gets the mean token loss; logits
+ * (host, B*T x vocab, nullable) receives the forward's logits. */
+int asca_model_forward_backward_host(asca_ctx* ctx, asca_model* m, const uint32_t* ids,
+                                     const uint32_t* targets, int64_t B, int64_t T, float* loss,
+                                     float* logits);
+/* One optimizer step = AdamW::update per tensor in parameter order; the step counter advances
+ * once per TENSOR (rust/src/tensor.rs:393), bias corrections and decay as in
+ * rust/src/tensor.rs:396-402. One segmented launch. */
+int asca_model_adamw_step(asca_ctx* ctx, asca_model* m, float lr, float beta1, float beta2, float eps,
+                          float wd);
+/* Decode: n_streams independent streams advance one token each (Model::step,
+ * rust/src/model.rs:631-649). state: device f32 (L, n_streams, H, dh, dh), updated in place;
+ * ids: host uint32 (n_streams); logits: host (n_streams x vocab), nullable; next_ids: host
+ * uint32 (n_streams), nullable -- the greedy argmax (lowest index on ties). */
+int asca_model_decode_step_host(asca_ctx* ctx, asca_model* m, float* state, const uint32_t* ids,
+                                int64_t n_streams, float* logits, uint32_t* next_ids);
+
 #ifdef __cplusplus
 }
 #endif
