@@ -47,6 +47,7 @@ struct Tiles {            // intermediate buffers, one tile per (chain, chunk)
     __nv_bfloat16* QKo;   // [tile][64][64]  Q K^T
     float* GV;            // [tile][64] cumulative log alpha
     float* BE;            // [tile][64] beta (0 on padded steps)
+    __nv_bfloat16* S0B;   // [tile][DH][DH] state at the start of the chunk (written by the chain forward)
 };
 
 // ------------------------------------------------------------------ pre-pass
@@ -317,7 +318,7 @@ __global__ void __launch_bounds__(CH_THREADS, 1) delta_fwd_tc_kernel(
     const __grid_constant__ CUtensorMap mapWQ, const __grid_constant__ CUtensorMap mapUV,
     const __grid_constant__ CUtensorMap mapKW, const __grid_constant__ CUtensorMap mapAA, const float* __restrict__ GC,
     int T, int H, int n_chunks, TO* __restrict__ o, const float* __restrict__ s_init, float* __restrict__ s_final,
-    float* __restrict__ ckpt, int* err_word) {
+    float* __restrict__ ckpt, __nv_bfloat16* __restrict__ s0b, int* err_word) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* stage0 = base;
@@ -422,6 +423,8 @@ __global__ void __launch_bounds__(CH_THREADS, 1) delta_fwd_tc_kernel(
         // ------------------------------------------------------------ compute threads: TMEM lane = tid
         const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
         float* ck = ckpt ? ckpt + tile0 * DH * DH : nullptr;
+        // bf16 copy of every chunk's starting state, row-major [DH][DH], for the backward's TMA loads
+        __nv_bfloat16* sb16 = s0b ? s0b + tile0 * DH * DH + (int64_t)tid * DH : nullptr;
         // initial state: checkpoint 0, bf16 operand copy, f32 state scaled by the first chunk's decay
         {
             const float g0 = GC[tile0];
@@ -441,8 +444,9 @@ __global__ void __launch_bounds__(CH_THREADS, 1) delta_fwd_tc_kernel(
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int chunk16 = cc * 4 + j;   // 16-byte chunk index along the row (8 bf16 each)
-                    *reinterpret_cast<uint4*>(S_s + (chunk16 >> 3) * (DH * 128) + tc::sw128_off(tid, chunk16 & 7)) =
-                        tc::pack8_bf16(f + 8 * j);
+                    const uint4 pk = tc::pack8_bf16(f + 8 * j);
+                    *reinterpret_cast<uint4*>(S_s + (chunk16 >> 3) * (DH * 128) + tc::sw128_off(tid, chunk16 & 7)) = pk;
+                    if (sb16) reinterpret_cast<uint4*>(sb16)[chunk16] = pk;
                 }
 #pragma unroll
                 for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(g0 * f[j]);
@@ -536,8 +540,9 @@ __global__ void __launch_bounds__(CH_THREADS, 1) delta_fwd_tc_kernel(
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         const int chunk16 = cc * 4 + j;
-                        *reinterpret_cast<uint4*>(S_s + (chunk16 >> 3) * (DH * 128) + tc::sw128_off(tid, chunk16 & 7)) =
-                            tc::pack8_bf16(f + 8 * j);
+                        const uint4 pk = tc::pack8_bf16(f + 8 * j);
+                        *reinterpret_cast<uint4*>(S_s + (chunk16 >> 3) * (DH * 128) + tc::sw128_off(tid, chunk16 & 7)) = pk;
+                        if (sb16) reinterpret_cast<uint4*>(sb16 + (int64_t)(c + 1) * DH * DH)[chunk16] = pk;
                     }
 #pragma unroll
                     for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(gnext * f[j]);
@@ -574,39 +579,49 @@ __global__ void __launch_bounds__(CH_THREADS, 1) delta_fwd_tc_kernel(
 //   dq = gam X + G6.h0,  dk = G6.h1 + eg dW - beta gam Y  (X, Y = the two halves of G5),
 // followed by the L2-norm backward, the gate gradients and the [dq|dk|dv] concat as in the f32
 // kernel (delta_bwd.cu).
-constexpr int BW_THREADS = 128;
+constexpr int BW_THREADS = 256;
 constexpr int R_WH = 0, R_BK = 16384, R_QG = 32768, R_KW = 49152, R_K = 65536, R_Q = 81920, R_DO = 98304,
               R_A = 114688, R_TP = 122880, R_S0 = 131072, R_DS = 163840, R_DR = 196608, R_END = 212992;
-constexpr int R_U = R_WH, R_P = R_KW, R_DAG = R_A, R_M = R_TP;
-constexpr size_t BW_SMEM = 1024 + R_END + 10 * 64 * 4 + 256;
-constexpr int BW_TX = 16384 * 7 + 8192 * 2;
+constexpr int R_U = R_WH, R_P = R_KW, R_DAG = R_A, R_M = R_TP, R_STG = R_S0;   // staging: S0 + dS regions (64 KiB)
+constexpr int BW_NVEC = 1664;
+constexpr size_t BW_SMEM = 1024 + R_END + BW_NVEC * 4 + 256;
+constexpr int BW_TX_A = 32768 + 16384 * 2;        // S0, W^, beta gam K
+constexpr int BW_TX_B = 16384 * 2 + 8192;         // Kw, dO, A
+constexpr int BW_TX_C = 16384 * 3 + 8192;         // Qg, K, Q, T'
 
+// 256 threads: warp w and warp w+4 share TMEM lane quarter (w & 3) and split every row's 128
+// columns in two (colhalf = w >> 2), so each thread handles 64 columns of one row.
 __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
-    const __grid_constant__ CUtensorMap mapWQ, const __grid_constant__ CUtensorMap map64x128,  // BK,KW,KR,QR tiles
+    const __grid_constant__ CUtensorMap mapWQ, const __grid_constant__ CUtensorMap map64x128,  // BK tiles
     const __grid_constant__ CUtensorMap mapKW, const __grid_constant__ CUtensorMap mapKR,
     const __grid_constant__ CUtensorMap mapQR, const __grid_constant__ CUtensorMap mapDO,
-    const __grid_constant__ CUtensorMap mapAA, const __grid_constant__ CUtensorMap mapTP, Tiles tl,
-    const float* __restrict__ alpha, const float* __restrict__ qnorm, const float* __restrict__ knorm,
-    const float* __restrict__ ckpt, int T, int H, int n_chunks, float* __restrict__ d_qkv,
+    const __grid_constant__ CUtensorMap mapAA, const __grid_constant__ CUtensorMap mapTP,
+    const __grid_constant__ CUtensorMap mapS0, Tiles tl,
+    const float* __restrict__ alpha, const float* __restrict__ qnorm, const float* __restrict__ knorm, int T, int H, int n_chunks, float* __restrict__ d_qkv,
     float* __restrict__ d_gate, int* err_word) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     float* vec = reinterpret_cast<float*>(sm + R_END);
-    float* g_s = vec;            // cumulative log alpha
-    float* be_s = vec + 64;      // beta
-    float* v_rowp = vec + 128;   // rowsum of P
-    float* v_colp = vec + 192;
-    float* v_rqs = vec + 256;
-    float* v_rkg = vec + 320;
-    float* v_rkw = vec + 384;
-    float* v_dbe = vec + 448;    // r_dr + beta * sum dLGam KK
-    float* v_red = vec + 512;    // 128 partials of <S0, dS>
-    uint64_t* bars = reinterpret_cast<uint64_t*>(vec + 640);   // [0] TMA, [1..6] MMA groups
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+    float* g_s = vec;              // cumulative log alpha
+    float* be_s = vec + 64;        // beta
+    float* v_rowp = vec + 128;     // [2][64] row sums of P per column half
+    float* v_rqs = vec + 320;      // [2][64]
+    float* v_rkg = vec + 448;      // [2][64]
+    float* v_rkw = vec + 576;      // [2][64]
+    float* v_rdr = vec + 704;      // [2][64]
+    float* v_dls = vec + 832;      // [2][64]
+    float* v_red = vec + 960;      // [256] partials of <S0, dS>
+    float* v_nrm = vec + 1216;     // [128] |q| rows then |k| rows of the chunk
+    float* v_al = vec + 1344;      // [64] alpha
+    float* v_colp4 = vec + 1408;   // [4][64] partial column sums of P
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sm + R_END + BW_NVEC * 4);   // [0],[7],[8] TMA groups, [1..6] MMA groups
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int half = (lane >> 4) & 1, row = 16 * warp + (lane & 15);   // M=64 accumulator mapping
+    const int wq = warp & 3, colhalf = warp >> 2;
+    const int half = (lane >> 4) & 1, row = 16 * wq + (lane & 15);   // M=64 accumulator mapping
+    const int arow = 32 * wq + lane;                                 // M=128 accumulator (dS) mapping
     const int chain = blockIdx.x;
     const int b = chain / H, h = chain % H;
     const int d = H * DH;
@@ -615,7 +630,7 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
 
     if (tid == 0) {
         *abort_flag = 0;
-        for (int i = 0; i < 7; ++i) tc::mbar_init(&bars[i], 1);
+        for (int i = 0; i < 9; ++i) tc::mbar_init(&bars[i], 1);
         tc::mbar_fence_init();
     }
     if (warp == 0) tc::tmem_alloc(tmem_slot, 512);
@@ -625,57 +640,81 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
     const uint32_t tm = *tmem_slot;
     const uint32_t ACC_S = tm, ACC_A = tm + 128, ACC_B = tm + 256, ACC_C = tm + 384;
     const uint32_t H1 = 16u << 16;                         // lane offset of the second M=64 half
-    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
+    const int c0 = colhalf * 2;                            // first 32-column chunk of this thread
 
     // dS = 0 (TMEM f32 and the bf16 operand copy)
     {
         uint32_t z[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) z[j] = 0u;
-#pragma unroll 1
-        for (int cc = 0; cc < 4; ++cc) tc::tmem_st_32x32(ACC_S + lane_addr + cc * 32, z);
+        tc::tmem_st_32x32(ACC_S + lane_addr + c0 * 32, z);
+        tc::tmem_st_32x32(ACC_S + lane_addr + c0 * 32 + 32, z);
         tc::tmem_st_wait();
         for (int i = tid; i < 32768 / 16; i += BW_THREADS) *reinterpret_cast<uint4*>(sm + R_DS + i * 16) = make_uint4(0, 0, 0, 0);
     }
 
+    // Three groups in the order the chunk needs them: [0] S0, W^, beta gam K; [7] Kw, dO, A; [8] the rest.
     auto issue_tma = [&](int c) {
         const int t = (int)(tile0 + c);
         const int grow = (int)(seq_row0 + (int64_t)c * C);
-        tc::mbar_expect_tx(&bars[0], BW_TX);
+        tc::mbar_expect_tx(&bars[0], BW_TX_A);
 #pragma unroll
         for (int kb = 0; kb < 2; ++kb) {
+            tc::tma_load_2d(sm + R_S0 + kb * 16384, &mapS0, kb * 64, t * 128, &bars[0]);
             tc::tma_load_2d(sm + R_WH + kb * 8192, &mapWQ, kb * 64, t * 128, &bars[0]);
-            tc::tma_load_2d(sm + R_QG + kb * 8192, &mapWQ, kb * 64, t * 128 + 64, &bars[0]);
             tc::tma_load_2d(sm + R_BK + kb * 8192, &map64x128, kb * 64, t * 64, &bars[0]);
-            tc::tma_load_2d(sm + R_KW + kb * 8192, &mapKW, kb * 64, t * 64, &bars[0]);
-            tc::tma_load_2d(sm + R_K + kb * 8192, &mapKR, kb * 64, t * 64, &bars[0]);
-            tc::tma_load_2d(sm + R_Q + kb * 8192, &mapQR, kb * 64, t * 64, &bars[0]);
-            tc::tma_load_2d(sm + R_DO + kb * 8192, &mapDO, h * DH + kb * 64, grow, &bars[0]);
         }
-        tc::tma_load_2d(sm + R_A, &mapAA, 0, t * 64, &bars[0]);
-        tc::tma_load_2d(sm + R_TP, &mapTP, 0, t * 64, &bars[0]);
+        tc::mbar_expect_tx(&bars[7], BW_TX_B);
+        tc::tma_load_2d(sm + R_A, &mapAA, 0, t * 64, &bars[7]);
+#pragma unroll
+        for (int kb = 0; kb < 2; ++kb) {
+            tc::tma_load_2d(sm + R_DO + kb * 8192, &mapDO, h * DH + kb * 64, grow, &bars[7]);
+            tc::tma_load_2d(sm + R_KW + kb * 8192, &mapKW, kb * 64, t * 64, &bars[7]);
+        }
+        tc::mbar_expect_tx(&bars[8], BW_TX_C);
+        tc::tma_load_2d(sm + R_TP, &mapTP, 0, t * 64, &bars[8]);
+#pragma unroll
+        for (int kb = 0; kb < 2; ++kb) {
+            tc::tma_load_2d(sm + R_QG + kb * 8192, &mapWQ, kb * 64, t * 128 + 64, &bars[8]);
+            tc::tma_load_2d(sm + R_K + kb * 8192, &mapKR, kb * 64, t * 64, &bars[8]);
+            tc::tma_load_2d(sm + R_Q + kb * 8192, &mapQR, kb * 64, t * 64, &bars[8]);
+        }
     };
     auto wait_bar = [&](int i, uint32_t parity) {
         if (lane == 0) tc::mbar_wait(&bars[i], parity, abort_flag, err_word, 300 + i);
         __syncwarp();
     };
-    // descriptor helpers (all tiles: 128-byte rows, 8-row groups 1024 B apart)
-    const uint32_t sb = tc::smem_u32(sm);
+    // Shared-memory matrix descriptors (128-byte swizzle, version 1). The address field is (base + offset) >> 4
+    // with every offset a compile-time constant, so one add per descriptor remains at run time.
+    const uint32_t sb4 = tc::smem_u32(sm) >> 4;
+    auto desc = [&](uint32_t off, uint32_t lbo, uint32_t sbo) -> uint64_t {
+        const uint32_t lo = sb4 + ((off >> 4) + ((lbo >> 4) << 16));
+        const uint32_t hi = (sbo >> 4) | (1u << 14) | (2u << 29);
+        return ((uint64_t)hi << 32) | lo;
+    };
     auto kmaj = [&](int reg, int k16) {       // K-major, 64-row tile, 8 KiB per 64-wide k box
-        return tc::smem_desc_sw128(sb + reg + (k16 >> 2) * 8192 + (k16 & 3) * 32, 16, 1024);
+        return desc(reg + (k16 >> 2) * 8192 + (k16 & 3) * 32, 16, 1024);
     };
     auto kmaj128 = [&](int reg, int k16) {    // K-major, 128-row tile (S0 / dS), 16 KiB per k box
-        return tc::smem_desc_sw128(sb + reg + (k16 >> 2) * 16384 + (k16 & 3) * 32, 16, 1024);
+        return desc(reg + (k16 >> 2) * 16384 + (k16 & 3) * 32, 16, 1024);
     };
     auto mnmaj = [&](int reg, int k16, int lbo) {   // MN-major: k rows, 64-wide mn boxes `lbo` bytes apart
-        return tc::smem_desc_sw128(sb + reg + k16 * 2048, lbo, 1024);
+        return desc(reg + k16 * 2048, lbo, 1024);
     };
-    constexpr uint32_t I64_KM = tc::idesc_bf16_f32(64, 128, 0, 1);    // A K-major, B MN-major
-    constexpr uint32_t I64_MM = tc::idesc_bf16_f32(64, 128, 1, 1);    // A MN-major, B MN-major
-    constexpr uint32_t I64_KK = tc::idesc_bf16_f32(64, 128, 0, 0);    // A K-major, B K-major
+    // 64-row operand tile written by the threads: 16-byte chunk `chunk16` (0..15) of row r
+    auto tile64 = [&](int reg, int r, int chunk16) -> uint4* {
+        return reinterpret_cast<uint4*>(sm + reg + (chunk16 >> 3) * 8192 + tc::sw128_off(r, chunk16 & 7));
+    };
+    auto tile128 = [&](int reg, int r, int chunk16) -> uint4* {
+        return reinterpret_cast<uint4*>(sm + reg + (chunk16 >> 3) * 16384 + tc::sw128_off(r, chunk16 & 7));
+    };
+    constexpr uint32_t I64_KM = tc::idesc_bf16_f32(64, 128, 0, 1);
+    constexpr uint32_t I64_MM = tc::idesc_bf16_f32(64, 128, 1, 1);
+    constexpr uint32_t I64_KK = tc::idesc_bf16_f32(64, 128, 0, 0);
     constexpr uint32_t I64_KK64 = tc::idesc_bf16_f32(64, 64, 0, 0);
     constexpr uint32_t I128_MM = tc::idesc_bf16_f32(128, 128, 1, 1);
-    constexpr uint32_t I128_MM_NEG = I128_MM | (1u << 13);            // negate A
+    constexpr uint32_t I128_MM_NEG = I128_MM | (1u << 13);
 
     if (tid == 0) issue_tma(n_chunks - 1);
     // A wait that gives up raises *abort_flag; later waits then return at once, the iteration runs to its
@@ -686,39 +725,39 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
         const int t0 = c * C;
         const int n = T - t0 < C ? T - t0 : C;
         const int64_t tix = tile0 + c;
-        const int64_t grow = seq_row0 + t0;       // global row of token 0 of this chunk
-        const float* s0g = ckpt + tix * DH * DH;
-        // ---- A. S0 (f32 checkpoint) -> bf16 operand tile; gates
+        const int64_t grow = seq_row0 + t0;
+        // rows of Uv (half 0) / beta V (half 1), 64 columns, fetched ahead of their use
+        uint4 pre[8];
         {
-            const int a = tid;
-#pragma unroll 1
-            for (int cc = 0; cc < 4; ++cc) {
+            const __nv_bfloat16* src = (half == 0 ? tl.UV : tl.BV) + (tix * 64 + row) * DH + colhalf * 64;
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const float4 x0 = *reinterpret_cast<const float4*>(s0g + a * DH + cc * 32 + j * 8);
-                    const float4 x1 = *reinterpret_cast<const float4*>(s0g + a * DH + cc * 32 + j * 8 + 4);
-                    const float f8[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
-                    const int chunk16 = cc * 4 + j;
-                    *reinterpret_cast<uint4*>(sm + R_S0 + (chunk16 >> 3) * 16384 + tc::sw128_off(a, chunk16 & 7)) =
-                        tc::pack8_bf16(f8);
-                }
-            }
-            if (tid < 64) {
-                g_s[tid] = tl.GV[tix * 64 + tid];
-                be_s[tid] = tl.BE[tix * 64 + tid];
-            }
+            for (int j = 0; j < 8; ++j) pre[j] = *reinterpret_cast<const uint4*>(src + 8 * j);
         }
-        tc::fence_proxy_async_smem();
+        // ---- A. per-token scalars of the chunk
+        if (tid < 64) {
+            g_s[tid] = tl.GV[tix * 64 + tid];
+            be_s[tid] = tl.BE[tix * 64 + tid];
+        } else if (tid < 128) {
+            const int t = tid - 64;
+            v_al[t] = t < n ? alpha[(grow + t) * H + h] : 0.0f;
+        } else {
+            const int t = tid & 63;
+            v_nrm[tid - 128] = t < n ? (tid < 192 ? qnorm : knorm)[(grow + t) * H + h] : 1.0f;
+        }
+        tc::fence_proxy_async_smem();   // the dS operand copy written at the end of the previous chunk
         tc::tcgen05_fence_before();
         __syncthreads();
         wait_bar(0, par);
         if (tid == 0) {
             tc::tcgen05_fence_after();
-            for (int k16 = 0; k16 < 8; ++k16) tc::umma_bf16(ACC_A, kmaj(R_WH, k16), mnmaj(R_S0, k16, 16384), I64_KM, k16 > 0);
-            for (int k16 = 0; k16 < 8; ++k16) tc::umma_bf16(ACC_A + H1, kmaj(R_BK, k16), mnmaj(R_S0, k16, 16384), I64_KM, k16 > 0);
+            _Pragma("unroll") for (int k16 = 0; k16 < 8; ++k16) tc::umma_bf16(ACC_A, kmaj(R_WH, k16), mnmaj(R_S0, k16, 16384), I64_KM, k16 > 0);
+            _Pragma("unroll") for (int k16 = 0; k16 < 8; ++k16) tc::umma_bf16(ACC_A + H1, kmaj(R_BK, k16), mnmaj(R_S0, k16, 16384), I64_KM, k16 > 0);
             tc::umma_commit(&bars[1]);
-            for (int k16 = 0; k16 < 4; ++k16) tc::umma_bf16(ACC_B + H1, mnmaj(R_A, k16, 8192), mnmaj(R_DO, k16, 8192), I64_MM, k16 > 0);
-            for (int k16 = 0; k16 < 8; ++k16) tc::umma_bf16(ACC_B + H1, kmaj(R_KW, k16), mnmaj(R_DS, k16, 16384), I64_KM, 1u);
+        }
+        wait_bar(7, par);
+        if (tid == 0) {
+            _Pragma("unroll") for (int k16 = 0; k16 < 4; ++k16) tc::umma_bf16(ACC_B + H1, mnmaj(R_A, k16, 8192), mnmaj(R_DO, k16, 8192), I64_MM, k16 > 0);
+            _Pragma("unroll") for (int k16 = 0; k16 < 8; ++k16) tc::umma_bf16(ACC_B + H1, kmaj(R_KW, k16), mnmaj(R_DS, k16, 16384), I64_KM, 1u);
             tc::umma_commit(&bars[2]);
         }
         const float g_row = g_s[row], g_last = g_s[C - 1];
@@ -727,30 +766,28 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
         // ---- B. U = Uv - W^ S0 (half 0);  dU -> bf16 (half 1)
         wait_bar(1, par);
         tc::tcgen05_fence_after();
-#pragma unroll 1
-        for (int cc = 0; cc < 4; ++cc) {
+#pragma unroll
+        for (int ci = 0; ci < 2; ++ci) {
             uint32_t r[32];
-            tc::tmem_ld_32x32(ACC_A + lane_addr + cc * 32, r);
+            tc::tmem_ld_32x32(ACC_A + lane_addr + (c0 + ci) * 32, r);
             tc::tmem_ld_wait();
             if (half == 0) {
-                const __nv_bfloat16* uv = tl.UV + (tix * 64 + row) * DH + cc * 32;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     float x8[8], u8[8];
-                    tc::unpack8_bf16(*reinterpret_cast<const uint4*>(uv + 8 * j), x8);
+                    tc::unpack8_bf16(pre[ci * 4 + j], x8);
 #pragma unroll
                     for (int e = 0; e < 8; ++e) u8[e] = x8[e] - __uint_as_float(r[8 * j + e]);
-                    const int chunk16 = cc * 4 + j;
-                    *reinterpret_cast<uint4*>(sm + R_U + (chunk16 >> 3) * 8192 + tc::sw128_off(row, chunk16 & 7)) = tc::pack8_bf16(u8);
+                    *tile64(R_U, row, (c0 + ci) * 4 + j) = tc::pack8_bf16(u8);
                 }
             }
         }
         wait_bar(2, par);
         tc::tcgen05_fence_after();
-#pragma unroll 1
-        for (int cc = 0; cc < 4; ++cc) {
+#pragma unroll
+        for (int ci = 0; ci < 2; ++ci) {
             uint32_t r[32];
-            tc::tmem_ld_32x32(ACC_B + lane_addr + cc * 32, r);
+            tc::tmem_ld_32x32(ACC_B + lane_addr + (c0 + ci) * 32, r);
             tc::tmem_ld_wait();
             if (half == 1) {
 #pragma unroll
@@ -758,38 +795,48 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
                     float f8[8];
 #pragma unroll
                     for (int e = 0; e < 8; ++e) f8[e] = __uint_as_float(r[8 * j + e]);
-                    const int chunk16 = cc * 4 + j;
-                    *reinterpret_cast<uint4*>(sm + R_DR + (chunk16 >> 3) * 8192 + tc::sw128_off(row, chunk16 & 7)) = tc::pack8_bf16(f8);
+                    *tile64(R_DR, row, (c0 + ci) * 4 + j) = tc::pack8_bf16(f8);
                 }
             }
         }
         tc::fence_proxy_async_smem();
         tc::tcgen05_fence_before();
+        wait_bar(8, par);
         __syncthreads();
         if (tid == 0) {
             tc::tcgen05_fence_after();
-            for (int k16 = 0; k16 < 4; ++k16) tc::umma_bf16(ACC_B + H1, mnmaj(R_TP, k16, 8192), mnmaj(R_DR, k16, 8192), I64_MM, 1u);
-            for (int k16 = 0; k16 < 8; ++k16) tc::umma_bf16(ACC_C + H1, kmaj(R_U, k16), kmaj128(R_DS, k16), I64_KK, k16 > 0);
+            _Pragma("unroll") for (int k16 = 0; k16 < 4; ++k16) tc::umma_bf16(ACC_B + H1, mnmaj(R_TP, k16, 8192), mnmaj(R_DR, k16, 8192), I64_MM, 1u);
+            _Pragma("unroll") for (int k16 = 0; k16 < 8; ++k16) tc::umma_bf16(ACC_C + H1, kmaj(R_U, k16), kmaj128(R_DS, k16), I64_KK, k16 > 0);
             tc::umma_commit(&bars[3]);
+        }
+        // rows of K K^T and Q K^T (32 columns each) for the dL / dA phase, fetched ahead
+        uint4 pkk[4], pqk[4];
+        if (half == 0) {
+            const __nv_bfloat16* kk = tl.KKo + (tix * 64 + row) * 64 + colhalf * 32;
+            const __nv_bfloat16* qk = tl.QKo + (tix * 64 + row) * 64 + colhalf * 32;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                pkk[j] = *reinterpret_cast<const uint4*>(kk + 8 * j);
+                pqk[j] = *reinterpret_cast<const uint4*>(qk + 8 * j);
+            }
         }
         // ---- C. dR: dV out, R = beta V - P2, r_dr, r_kg, bf16 dR tile (half 1)
         wait_bar(3, par);
         tc::tcgen05_fence_after();
         {
             float r_dr = 0.0f, r_kg = 0.0f;
-#pragma unroll 1
-            for (int cc = 0; cc < 4; ++cc) {
+#pragma unroll
+            for (int ci = 0; ci < 2; ++ci) {
                 uint32_t r[32], p2[32];
-                tc::tmem_ld_32x32(ACC_B + lane_addr + cc * 32, r);
-                tc::tmem_ld_32x32(ACC_A + lane_addr + cc * 32, p2);
+                tc::tmem_ld_32x32(ACC_B + lane_addr + (c0 + ci) * 32, r);
+                tc::tmem_ld_32x32(ACC_A + lane_addr + (c0 + ci) * 32, p2);
                 tc::tmem_ld_wait();
                 if (half == 1) {
-                    const __nv_bfloat16* bv = tl.BV + (tix * 64 + row) * DH + cc * 32;
-                    float* dv = d_qkv + (grow + row) * 3 * d + 2 * d + h * DH + cc * 32;
+                    float* dv = d_qkv + (grow + row) * 3 * d + 2 * d + h * DH + (c0 + ci) * 32;
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         float x8[8], f8[8];
-                        tc::unpack8_bf16(*reinterpret_cast<const uint4*>(bv + 8 * j), x8);
+                        tc::unpack8_bf16(pre[ci * 4 + j], x8);
 #pragma unroll
                         for (int e = 0; e < 8; ++e) {
                             const float dr = __uint_as_float(r[8 * j + e]), pp = __uint_as_float(p2[8 * j + e]);
@@ -801,14 +848,13 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
                             reinterpret_cast<float4*>(dv)[2 * j] = make_float4(be_row * f8[0], be_row * f8[1], be_row * f8[2], be_row * f8[3]);
                             reinterpret_cast<float4*>(dv)[2 * j + 1] = make_float4(be_row * f8[4], be_row * f8[5], be_row * f8[6], be_row * f8[7]);
                         }
-                        const int chunk16 = cc * 4 + j;
-                        *reinterpret_cast<uint4*>(sm + R_DR + (chunk16 >> 3) * 8192 + tc::sw128_off(row, chunk16 & 7)) = tc::pack8_bf16(f8);
+                        *tile64(R_DR, row, (c0 + ci) * 4 + j) = tc::pack8_bf16(f8);
                     }
                 }
             }
             if (half == 1) {
-                v_dbe[row] = r_dr;
-                v_rkg[row] = r_kg;
+                v_rdr[colhalf * 64 + row] = r_dr;
+                v_rkg[colhalf * 64 + row] = r_kg;
             }
         }
         tc::fence_proxy_async_smem();
@@ -816,78 +862,69 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
         __syncthreads();
         if (tid == 0) {
             tc::tcgen05_fence_after();
-            for (int k16 = 0; k16 < 8; ++k16) tc::umma_bf16(ACC_C, kmaj(R_DR, k16), kmaj(R_U, k16), I64_KK64, k16 > 0);
-            for (int k16 = 0; k16 < 8; ++k16) tc::umma_bf16(ACC_C + 64, kmaj(R_DO, k16), kmaj(R_U, k16), I64_KK64, k16 > 0);
-            for (int k16 = 0; k16 < 8; ++k16) tc::umma_bf16(ACC_A, kmaj(R_DO, k16), kmaj128(R_S0, k16), I64_KK, k16 > 0);
-            for (int k16 = 0; k16 < 8; ++k16) tc::umma_bf16(ACC_A + H1, kmaj(R_DR, k16), kmaj128(R_S0, k16), I64_KK, k16 > 0);
+            _Pragma("unroll") for (int k16 = 0; k16 < 8; ++k16) tc::umma_bf16(ACC_C, kmaj(R_DR, k16), kmaj(R_U, k16), I64_KK64, k16 > 0);
+            _Pragma("unroll") for (int k16 = 0; k16 < 8; ++k16) tc::umma_bf16(ACC_C + 64, kmaj(R_DO, k16), kmaj(R_U, k16), I64_KK64, k16 > 0);
+            _Pragma("unroll") for (int k16 = 0; k16 < 8; ++k16) tc::umma_bf16(ACC_A, kmaj(R_DO, k16), kmaj128(R_S0, k16), I64_KK, k16 > 0);
+            _Pragma("unroll") for (int k16 = 0; k16 < 8; ++k16) tc::umma_bf16(ACC_A + H1, kmaj(R_DR, k16), kmaj128(R_S0, k16), I64_KK, k16 > 0);
             tc::umma_commit(&bars[4]);
         }
-        // ---- D. scale dS by gam_C (and <S0, dS>) while G4/G5 run
+        // ---- D. scale dS by gam_C, and <S0, dS> from the bf16 copy of S0, while G4/G5 run
         {
-            const int a = tid;
             const float gC = __expf(g_last);
             float part = 0.0f;
-#pragma unroll 1
-            for (int cc = 0; cc < 4; ++cc) {
+#pragma unroll
+            for (int ci = 0; ci < 2; ++ci) {
                 uint32_t r[32];
-                tc::tmem_ld_32x32(ACC_S + lane_addr + cc * 32, r);
+                tc::tmem_ld_32x32(ACC_S + lane_addr + (c0 + ci) * 32, r);
                 tc::tmem_ld_wait();
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const float4 s4 = *reinterpret_cast<const float4*>(s0g + a * DH + cc * 32 + 4 * j);
-                    part = fmaf(s4.x, __uint_as_float(r[4 * j]), part);
-                    part = fmaf(s4.y, __uint_as_float(r[4 * j + 1]), part);
-                    part = fmaf(s4.z, __uint_as_float(r[4 * j + 2]), part);
-                    part = fmaf(s4.w, __uint_as_float(r[4 * j + 3]), part);
+                for (int j = 0; j < 4; ++j) {
+                    float s8[8];
+                    tc::unpack8_bf16(*tile128(R_S0, arow, (c0 + ci) * 4 + j), s8);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) part = fmaf(s8[e], __uint_as_float(r[8 * j + e]), part);
                 }
 #pragma unroll
                 for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(gC * __uint_as_float(r[j]));
-                tc::tmem_st_32x32(ACC_S + lane_addr + cc * 32, r);
+                tc::tmem_st_32x32(ACC_S + lane_addr + (c0 + ci) * 32, r);
             }
             tc::tmem_st_wait();
             v_red[tid] = part;
         }
         wait_bar(4, par);
         tc::tcgen05_fence_after();
-        // dL / dA rows (half 0): M tile, dA.Gam tile, P row, dbeta
+        // dL / dA rows (half 0; this thread's 32 columns): M tile, dA.Gam tile, P row, dbeta
         {
             float rowp = 0.0f, dls = 0.0f;
-#pragma unroll 1
-            for (int cc = 0; cc < 2; ++cc) {
-                uint32_t rl[32], ra[32];
-                tc::tmem_ld_32x32(ACC_C + lane_addr + cc * 32, rl);
-                tc::tmem_ld_32x32(ACC_C + lane_addr + 64 + cc * 32, ra);
-                tc::tmem_ld_wait();
-                if (half == 0) {
-                    const __nv_bfloat16* kk = tl.KKo + (tix * 64 + row) * 64 + cc * 32;
-                    const __nv_bfloat16* qk = tl.QKo + (tix * 64 + row) * 64 + cc * 32;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        float kk8[8], qk8[8], m8[8], a8[8];
-                        tc::unpack8_bf16(*reinterpret_cast<const uint4*>(kk + 8 * j), kk8);
-                        tc::unpack8_bf16(*reinterpret_cast<const uint4*>(qk + 8 * j), qk8);
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) {
-                            const int i = cc * 32 + 8 * j + e;
-                            const float gm = i <= row ? __expf(g_row - g_s[i]) : 0.0f;
-                            const float dlg = i < row ? -__uint_as_float(rl[8 * j + e]) * gm : 0.0f;   // dL.Gam
-                            const float dag = __uint_as_float(ra[8 * j + e]) * gm;                     // dA.Gam
-                            dls = fmaf(dlg, kk8[e], dls);
-                            m8[e] = dlg * be_row;
-                            a8[e] = dag;
-                            const float pv = dag * qk8[e] + m8[e] * kk8[e];
-                            rowp += pv;
-                            reinterpret_cast<float*>(sm + R_P)[row * 64 + ((i + row) & 63)] = pv;
-                        }
-                        const int chunk16 = cc * 4 + j;
-                        *reinterpret_cast<uint4*>(sm + R_M + tc::sw128_off(row, chunk16)) = tc::pack8_bf16(m8);
-                        *reinterpret_cast<uint4*>(sm + R_DAG + tc::sw128_off(row, chunk16)) = tc::pack8_bf16(a8);
-                    }
-                }
-            }
+            uint32_t rl[32], ra[32];
+            tc::tmem_ld_32x32(ACC_C + lane_addr + colhalf * 32, rl);
+            tc::tmem_ld_32x32(ACC_C + lane_addr + 64 + colhalf * 32, ra);
+            tc::tmem_ld_wait();
             if (half == 0) {
-                v_rowp[row] = rowp;
-                v_dbe[row] += be_row * dls;   // v_dbe[row] was written by the half-1 thread of the same warp
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    float kk8[8], qk8[8], m8[8], a8[8];
+                    tc::unpack8_bf16(pkk[j], kk8);
+                    tc::unpack8_bf16(pqk[j], qk8);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        const int i = colhalf * 32 + 8 * j + e;
+                        const float gm = i <= row ? __expf(g_row - g_s[i]) : 0.0f;
+                        const float dlg = i < row ? -__uint_as_float(rl[8 * j + e]) * gm : 0.0f;   // dL.Gam
+                        const float dag = __uint_as_float(ra[8 * j + e]) * gm;                     // dA.Gam
+                        dls = fmaf(dlg, kk8[e], dls);
+                        m8[e] = dlg * be_row;
+                        a8[e] = dag;
+                        const float pv = dag * qk8[e] + m8[e] * kk8[e];
+                        rowp += pv;
+                        reinterpret_cast<float*>(sm + R_P)[row * 64 + ((i + row) & 63)] = pv;
+                    }
+                    const int chunk16 = colhalf * 4 + j;
+                    *reinterpret_cast<uint4*>(sm + R_M + tc::sw128_off(row, chunk16)) = tc::pack8_bf16(m8);
+                    *reinterpret_cast<uint4*>(sm + R_DAG + tc::sw128_off(row, chunk16)) = tc::pack8_bf16(a8);
+                }
+                v_rowp[colhalf * 64 + row] = rowp;
+                v_dls[colhalf * 64 + row] = dls;
             }
         }
         tc::fence_proxy_async_smem();
@@ -895,117 +932,137 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
         __syncthreads();
         if (tid == 0) {
             tc::tcgen05_fence_after();
-            for (int k16 = 0; k16 < 4; ++k16)
-                tc::umma_bf16(ACC_B, tc::smem_desc_sw128(sb + R_DAG + k16 * 32, 16, 1024), mnmaj(R_K, k16, 8192), I64_KM, k16 > 0);
-            for (int k16 = 0; k16 < 4; ++k16)
-                tc::umma_bf16(ACC_B + H1, tc::smem_desc_sw128(sb + R_M + k16 * 32, 16, 1024), mnmaj(R_K, k16, 8192), I64_KM, k16 > 0);
-            for (int k16 = 0; k16 < 4; ++k16) tc::umma_bf16(ACC_B + H1, mnmaj(R_M, k16, 8192), mnmaj(R_K, k16, 8192), I64_MM, 1u);
-            for (int k16 = 0; k16 < 4; ++k16) tc::umma_bf16(ACC_B + H1, mnmaj(R_DAG, k16, 8192), mnmaj(R_Q, k16, 8192), I64_MM, 1u);
+            _Pragma("unroll") for (int k16 = 0; k16 < 4; ++k16)
+                tc::umma_bf16(ACC_B, desc(R_DAG + k16 * 32, 16, 1024), mnmaj(R_K, k16, 8192), I64_KM, k16 > 0);
+            _Pragma("unroll") for (int k16 = 0; k16 < 4; ++k16)
+                tc::umma_bf16(ACC_B + H1, desc(R_M + k16 * 32, 16, 1024), mnmaj(R_K, k16, 8192), I64_KM, k16 > 0);
+            _Pragma("unroll") for (int k16 = 0; k16 < 4; ++k16) tc::umma_bf16(ACC_B + H1, mnmaj(R_M, k16, 8192), mnmaj(R_K, k16, 8192), I64_MM, 1u);
+            _Pragma("unroll") for (int k16 = 0; k16 < 4; ++k16) tc::umma_bf16(ACC_B + H1, mnmaj(R_DAG, k16, 8192), mnmaj(R_Q, k16, 8192), I64_MM, 1u);
             tc::umma_commit(&bars[5]);
-            for (int k16 = 0; k16 < 4; ++k16) tc::umma_bf16(ACC_S, mnmaj(R_QG, k16, 8192), mnmaj(R_DO, k16, 8192), I128_MM, 1u);
-            for (int k16 = 0; k16 < 4; ++k16) tc::umma_bf16(ACC_S, mnmaj(R_BK, k16, 8192), mnmaj(R_DR, k16, 8192), I128_MM_NEG, 1u);
+            _Pragma("unroll") for (int k16 = 0; k16 < 4; ++k16) tc::umma_bf16(ACC_S, mnmaj(R_QG, k16, 8192), mnmaj(R_DO, k16, 8192), I128_MM, 1u);
+            _Pragma("unroll") for (int k16 = 0; k16 < 4; ++k16) tc::umma_bf16(ACC_S, mnmaj(R_BK, k16, 8192), mnmaj(R_DR, k16, 8192), I128_MM_NEG, 1u);
             tc::umma_commit(&bars[6]);
         }
-        // column sums of P (threads 0..63) while G6 runs
-        if (tid < 64) {
+        // column sums of P while G6 runs: 4 threads per column, 16 rows each
+        {
+            const int col = tid & 63, part = tid >> 6;
             float cs = 0.0f;
             const float* P = reinterpret_cast<const float*>(sm + R_P);
-#pragma unroll 8
-            for (int t = 0; t < 64; ++t) cs += P[t * 64 + ((tid + t) & 63)];
-            v_colp[tid] = cs;
+#pragma unroll
+            for (int t = part * 16; t < part * 16 + 16; ++t) cs += P[t * 64 + ((col + t) & 63)];
+            v_colp4[part * 64 + col] = cs;
         }
-        // ---- E. dq (half 0) and dk (half 1): assemble, L2-norm backward, store
+        // ---- E. dq rows (half 0) and dk rows (half 1) into the f32 staging area (S0 + dS regions are free)
         wait_bar(5, par);
         tc::tcgen05_fence_after();
         {
-            const uint8_t* yt = sm + (half == 0 ? R_Q : R_K);       // normalised q / k rows (bf16)
-            float dot = 0.0f, rr = 0.0f;                             // y.g and (r_qs | r_kw)
-            const float nrm = live ? (half == 0 ? qnorm : knorm)[(grow + row) * H + h] : 1.0f;
-            float* dst = d_qkv + (grow + row) * 3 * d + (half == 0 ? 0 : d) + h * DH;
-#pragma unroll 1
-            for (int pass = 0; pass < 2; ++pass) {
-#pragma unroll 1
-                for (int cc = 0; cc < 4; ++cc) {
-                    uint32_t xa[32], xb[32], xc[32];
-                    tc::tmem_ld_32x32(ACC_A + lane_addr + cc * 32, xa);    // X (h0) | Y (h1)
-                    tc::tmem_ld_32x32(ACC_B + lane_addr + cc * 32, xb);    // G6
-                    tc::tmem_ld_32x32(ACC_C + lane_addr + cc * 32, xc);    // (h0: dL|dA, unused) | dW (h1)
-                    tc::tmem_ld_wait();
+            const int srow = half * 64 + row;
+            float4* stg = reinterpret_cast<float4*>(sm + R_STG) + srow * 32;
+            const int swz = (row + 16 * half) & 31;
+            float rr = 0.0f;
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const int chunk16 = cc * 4 + j;
-                        float y8[8], z8[8], g8[8];
-                        tc::unpack8_bf16(*reinterpret_cast<const uint4*>(yt + (chunk16 >> 3) * 8192 + tc::sw128_off(row, chunk16 & 7)), y8);
-                        if (half == 0)
-                            tc::unpack8_bf16(*reinterpret_cast<const uint4*>(sm + R_QG + (chunk16 >> 3) * 8192 + tc::sw128_off(row, chunk16 & 7)), z8);
+            for (int ci = 0; ci < 2; ++ci) {
+                uint32_t xa[32], xb[32], xc[32];
+                tc::tmem_ld_32x32(ACC_A + lane_addr + (c0 + ci) * 32, xa);    // X (h0) | Y (h1)
+                tc::tmem_ld_32x32(ACC_B + lane_addr + (c0 + ci) * 32, xb);    // G6
+                tc::tmem_ld_32x32(ACC_C + lane_addr + (c0 + ci) * 32, xc);    // (h0: dL|dA) | dW (h1)
+                tc::tmem_ld_wait();
 #pragma unroll
-                        for (int e = 0; e < 8; ++e) {
-                            const float A_ = __uint_as_float(xa[8 * j + e]), B_ = __uint_as_float(xb[8 * j + e]),
-                                        C_ = __uint_as_float(xc[8 * j + e]);
-                            if (half == 0) {
-                                g8[e] = fmaf(gam_row, A_, B_);
-                                if (pass == 0) rr = fmaf(z8[e], A_, rr);                // Qg_t . X_t
-                            } else {
-                                g8[e] = B_ + eg_row * C_ - be_row * gam_row * A_;
-                                if (pass == 0) rr = fmaf(eg_row * y8[e], C_, rr);       // eg k_t . dW_t
-                            }
-                            if (pass == 0) dot = fmaf(y8[e], g8[e], dot);
-                        }
-                        if (pass == 1 && live) {
-                            float* o8 = dst + cc * 32 + 8 * j;
-                            reinterpret_cast<float4*>(o8)[0] = make_float4((g8[0] - y8[0] * dot) / nrm, (g8[1] - y8[1] * dot) / nrm,
-                                                                           (g8[2] - y8[2] * dot) / nrm, (g8[3] - y8[3] * dot) / nrm);
-                            reinterpret_cast<float4*>(o8)[1] = make_float4((g8[4] - y8[4] * dot) / nrm, (g8[5] - y8[5] * dot) / nrm,
-                                                                           (g8[6] - y8[6] * dot) / nrm, (g8[7] - y8[7] * dot) / nrm);
+                for (int j = 0; j < 4; ++j) {
+                    const int chunk16 = (c0 + ci) * 4 + j;
+                    float z8[8], g8[8];
+                    tc::unpack8_bf16(*tile64(half == 0 ? R_QG : R_K, row, chunk16), z8);   // Qg_t | k_t
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        const float A_ = __uint_as_float(xa[8 * j + e]), B_ = __uint_as_float(xb[8 * j + e]),
+                                    C_ = __uint_as_float(xc[8 * j + e]);
+                        if (half == 0) {
+                            g8[e] = fmaf(gam_row, A_, B_);
+                            rr = fmaf(z8[e], A_, rr);                    // Qg_t . X_t
+                        } else {
+                            g8[e] = B_ + eg_row * C_ - be_row * gam_row * A_;
+                            rr = fmaf(eg_row * z8[e], C_, rr);           // eg k_t . dW_t
                         }
                     }
+                    stg[(2 * chunk16) ^ swz] = make_float4(g8[0], g8[1], g8[2], g8[3]);
+                    stg[(2 * chunk16 + 1) ^ swz] = make_float4(g8[4], g8[5], g8[6], g8[7]);
                 }
             }
-            if (half == 0) v_rqs[row] = rr; else v_rkw[row] = rr;
+            (half == 0 ? v_rqs : v_rkw)[colhalf * 64 + row] = rr;
         }
         __syncthreads();
-        // gates: dg, reverse cumulative sum, sigmoid backward
-        if (tid == 0) {
+        // L2-norm backward and store, one warp per staged row, coalesced
+        for (int srow = warp; srow < 128; srow += BW_THREADS / 32) {
+            const int hh = srow >> 6, r_ = srow & 63;
+            if (r_ >= n) continue;
+            const int swz = (r_ + 16 * hh) & 31;
+            const float4 g4 = reinterpret_cast<const float4*>(sm + R_STG)[srow * 32 + (lane ^ swz)];
+            const uint2 yraw = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(tile64(hh == 0 ? R_Q : R_K, r_, lane >> 1)) + (lane & 1) * 8);
+            const __nv_bfloat162 y01 = *reinterpret_cast<const __nv_bfloat162*>(&yraw.x), y23 = *reinterpret_cast<const __nv_bfloat162*>(&yraw.y);
+            const float y0 = __low2float(y01), y1 = __high2float(y01), y2 = __low2float(y23), y3 = __high2float(y23);
+            float dot = y0 * g4.x + y1 * g4.y + y2 * g4.z + y3 * g4.w;
+            dot = warp_sum(dot);
+            const float inv = 1.0f / v_nrm[srow];
+            float* dst = d_qkv + (grow + r_) * 3 * d + (hh == 0 ? 0 : d) + h * DH;
+            reinterpret_cast<float4*>(dst)[lane] = make_float4((g4.x - y0 * dot) * inv, (g4.y - y1 * dot) * inv,
+                                                               (g4.z - y2 * dot) * inv, (g4.w - y3 * dot) * inv);
+        }
+        // gates (warp 0): dg, reverse cumulative sum, sigmoid backward
+        if (warp == 0) {
             float sds = 0.0f;
-            for (int i = 0; i < 128; ++i) sds += v_red[i];
-            float extra = __expf(g_last) * sds;
-            for (int t = 0; t < C; ++t) extra += v_rkw[t];
-            float run = 0.0f;
-            for (int t = C - 1; t >= 0; --t) {
-                float dg = v_rowp[t] - v_colp[t] + v_rqs[t] + v_rkg[t] - v_rkw[t];
-                if (t == C - 1) dg += extra;
-                run += dg;
-                v_rowp[t] = run;   // dlogalpha_t
+            for (int i = lane; i < 256; i += 32) sds += v_red[i];
+            sds = warp_sum(sds);
+            const int tA = lane, tB = lane + 32;
+            const float kwA = v_rkw[tA] + v_rkw[64 + tA], kwB = v_rkw[tB] + v_rkw[64 + tB];
+            const float extra = __expf(g_last) * sds + warp_sum(kwA + kwB);
+            float dgA = v_rowp[tA] + v_rowp[64 + tA] - (v_colp4[tA] + v_colp4[64 + tA] + v_colp4[128 + tA] + v_colp4[192 + tA]) + v_rqs[tA] + v_rqs[64 + tA] + v_rkg[tA] + v_rkg[64 + tA] - kwA;
+            float dgB = v_rowp[tB] + v_rowp[64 + tB] - (v_colp4[tB] + v_colp4[64 + tB] + v_colp4[128 + tB] + v_colp4[192 + tB]) + v_rqs[tB] + v_rqs[64 + tB] + v_rkg[tB] + v_rkg[64 + tB] - kwB;
+            if (lane == 31) dgB += extra;
+            // suffix sums over t = 0..63 (A holds 0..31, B holds 32..63)
+            float sB = dgB, sA = dgA;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const float nb = __shfl_down_sync(0xffffffffu, sB, o), na = __shfl_down_sync(0xffffffffu, sA, o);
+                if (lane + o < 32) {
+                    sB += nb;
+                    sA += na;
+                }
             }
-        }
-        __syncthreads();
-        if (tid < n) {
-            const int64_t r = grow + tid;
-            const float al = alpha[r * H + h], be = be_s[tid];
-            d_gate[r * 2 * H + h] = v_rowp[tid] * (1.0f - al);
-            d_gate[r * 2 * H + H + h] = v_dbe[tid] * (1.0f - be);
+            const float totB = __shfl_sync(0xffffffffu, sB, 0);
+            sA += totB;
+            if (tA < n) {
+                const int64_t r = grow + tA;
+                const float be = be_s[tA];
+                d_gate[r * 2 * H + h] = sA * (1.0f - v_al[tA]);
+                d_gate[r * 2 * H + H + h] = (v_rdr[tA] + v_rdr[64 + tA] + be * (v_dls[tA] + v_dls[64 + tA])) * (1.0f - be);
+            }
+            if (tB < n) {
+                const int64_t r = grow + tB;
+                const float be = be_s[tB];
+                d_gate[r * 2 * H + h] = sB * (1.0f - v_al[tB]);
+                d_gate[r * 2 * H + H + h] = (v_rdr[tB] + v_rdr[64 + tB] + be * (v_dls[tB] + v_dls[64 + tB])) * (1.0f - be);
+            }
         }
         // ---- F. new dS -> bf16 operand copy for the next chunk; next chunk's tiles
         wait_bar(6, par);
         tc::tcgen05_fence_after();
+        __syncthreads();   // staging reads are finished before the dS region is rewritten
         if (c > 0) {
             if (tid == 0) {
                 tc::fence_proxy_async_smem();
                 issue_tma(c - 1);
             }
-            const int a = tid;
-#pragma unroll 1
-            for (int cc = 0; cc < 4; ++cc) {
+#pragma unroll
+            for (int ci = 0; ci < 2; ++ci) {
                 uint32_t r[32];
-                tc::tmem_ld_32x32(ACC_S + lane_addr + cc * 32, r);
+                tc::tmem_ld_32x32(ACC_S + lane_addr + (c0 + ci) * 32, r);
                 tc::tmem_ld_wait();
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     float f8[8];
 #pragma unroll
                     for (int e = 0; e < 8; ++e) f8[e] = __uint_as_float(r[8 * j + e]);
-                    const int chunk16 = cc * 4 + j;
-                    *reinterpret_cast<uint4*>(sm + R_DS + (chunk16 >> 3) * 16384 + tc::sw128_off(a, chunk16 & 7)) = tc::pack8_bf16(f8);
+                    *tile128(R_DS, arow, (c0 + ci) * 4 + j) = tc::pack8_bf16(f8);
                 }
             }
         }
@@ -1015,6 +1072,15 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
     __syncthreads();
     if (*abort_flag) __nanosleep(20000);
     if (warp == 0) tc::tmem_dealloc(tm, 512);
+}
+
+// f32 chunk-start states -> the bf16 tiles the backward loads (used when the forward's own copy is gone)
+__global__ void state_to_bf16_kernel(const float4* __restrict__ in, uint2* __restrict__ out, int64_t n4) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+        const float4 x = in[i];
+        const __nv_bfloat162 a = __floats2bfloat162_rn(x.x, x.y), b = __floats2bfloat162_rn(x.z, x.w);
+        out[i] = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+    }
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -1074,6 +1140,7 @@ static size_t carve_tiles(char* w, int64_t n_tiles, bool full, Tiles* t) {
         z.QKo = (__nv_bfloat16*)take(bcc);
         z.GV = (float*)take(bv);
         z.BE = (float*)take(bv);
+        z.S0B = (__nv_bfloat16*)take(al((size_t)n_tiles * DH * DH * 2));
     }
     if (t) *t = z;
     return (size_t)(p - w);
@@ -1131,7 +1198,7 @@ int forward(asca_ctx* ctx, const void* q, const void* k, const void* v, const fl
         asca_span sp(ctx, "delta_fwd_tc_kernel");
         kern<<<(unsigned)chains, CH_THREADS, CH_SMEM, ctx->stream>>>(mWQ, mUV, mKW, mAA, t.GC, (int)T, (int)H,
                                                                     (int)n_chunks, (__nv_bfloat16*)o, s_init, s_final,
-                                                                    ckpt, ctx->err_word);
+                                                                    ckpt, keep ? t.S0B : nullptr, ctx->err_word);
     }
     ASCA_CHECK_LAUNCH(ctx);
     if (keep) {
@@ -1161,18 +1228,26 @@ int backward(asca_ctx* ctx, const void* q, const void* k, const void* v, const f
         char* w = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(ws) + 1023) & ~(uintptr_t)1023);
         carve_tiles(w, n_tiles, true, &t);
         ASCA_TRY(run_prepass(ctx, q, k, v, alpha, beta, T, H, n_chunks, chains, t));
+        const int64_t n4 = n_tiles * DH * DH / 4;
+        {
+            asca_span sp(ctx, "state_to_bf16_kernel");
+            state_to_bf16_kernel<<<(unsigned)std::min<int64_t>((n4 + 255) / 256, 148 * 16), 256, 0, ctx->stream>>>(
+                reinterpret_cast<const float4*>(ckpt), reinterpret_cast<uint2*>(t.S0B), n4);
+        }
+        ASCA_CHECK_LAUNCH(ctx);
     }
-    CUtensorMap mWQ, mBK, mKW, mKR, mQR, mDO, mAA, mTP;
+    CUtensorMap mWQ, mBK, mKW, mKR, mQR, mDO, mAA, mTP, mS0;
     bool ok = make_map(&mWQ, t.WQ, n_tiles * 128, DH, 64, 64) && make_map(&mBK, t.BK, n_tiles * 64, DH, 64, 64) &&
               make_map(&mKW, t.KW, n_tiles * 64, DH, 64, 64) && make_map(&mKR, t.KR, n_tiles * 64, DH, 64, 64) &&
               make_map(&mQR, t.QR, n_tiles * 64, DH, 64, 64) && make_map(&mDO, d_o, B * T, H * DH, 64, 64) &&
-              make_map(&mAA, t.AA, n_tiles * 64, 64, 64, 64) && make_map(&mTP, t.TP, n_tiles * 64, 64, 64, 64);
+              make_map(&mAA, t.AA, n_tiles * 64, 64, 64, 64) && make_map(&mTP, t.TP, n_tiles * 64, 64, 64, 64) &&
+              make_map(&mS0, t.S0B, n_tiles * DH, DH, 64, 128);
     if (!ok) return asca_fail(ctx, ASCA_ERR_CUDA, "delta_tc: cuTensorMapEncodeTiled failed");
     ASCA_CUDA(ctx, cudaFuncSetAttribute(delta_bwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)BW_SMEM));
     {
         asca_span sp(ctx, "delta_bwd_tc_kernel");
         delta_bwd_tc_kernel<<<(unsigned)chains, BW_THREADS, BW_SMEM, ctx->stream>>>(
-            mWQ, mBK, mKW, mKR, mQR, mDO, mAA, mTP, t, alpha, qnorm, knorm, ckpt, (int)T, (int)H, (int)n_chunks, d_qkv,
+            mWQ, mBK, mKW, mKR, mQR, mDO, mAA, mTP, mS0, t, alpha, qnorm, knorm, (int)T, (int)H, (int)n_chunks, d_qkv,
             d_gate, ctx->err_word);
     }
     ASCA_CHECK_LAUNCH(ctx);
