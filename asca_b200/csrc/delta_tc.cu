@@ -39,16 +39,28 @@ struct Tiles {            // intermediate buffers, one tile per (chain, chunk)
     float* GC;            // [tile] gam_C (total decay of the chunk)
     // backward-only outputs (null in the forward)
     __nv_bfloat16* BK;    // [tile][64][DH]  beta gam K
-    __nv_bfloat16* BV;    // [tile][64][DH]  beta V
+    __nv_bfloat16* BV;    // [tile] beta V, 64 x DH, lane-major (see lm_off128)
+    __nv_bfloat16* UVT;   // [tile] Uv, 64 x DH, lane-major copy for the backward
     __nv_bfloat16* KR;    // [tile][64][DH]  K (zero-padded copy)
     __nv_bfloat16* QR;    // [tile][64][DH]  Q (zero-padded copy)
     __nv_bfloat16* TP;    // [tile][64][64]  T' = (I+L)^-1 - I, row-major
-    __nv_bfloat16* KKo;   // [tile][64][64]  K K^T
-    __nv_bfloat16* QKo;   // [tile][64][64]  Q K^T
+    __nv_bfloat16* KKo;   // [tile] K K^T, 64 x 64, lane-major (see lm_off64)
+    __nv_bfloat16* QKo;   // [tile] Q K^T, 64 x 64, lane-major
     float* GV;            // [tile][64] cumulative log alpha
     float* BE;            // [tile][64] beta (0 on padded steps)
     __nv_bfloat16* S0B;   // [tile][DH][DH] state at the start of the chunk (written by the chain forward)
 };
+
+// Lane-major tile layouts for rows that the backward's threads read straight from global memory.
+// There, thread (warp quarter wq = row / 16, lane = row % 16, column half) reads its 16-byte chunks
+// j = 0.. one per instruction; storing chunk j of 16 consecutive rows side by side makes each such
+// instruction touch 256 contiguous bytes. Offsets are in bf16 elements within one tile.
+__device__ __forceinline__ int lm_off128(int row, int chunk16) {   // 64 x 128 tile, column halves of 8 chunks
+    return ((((row >> 4) * 2 + (chunk16 >> 3)) * 8 + (chunk16 & 7)) * 16 + (row & 15)) * 8;
+}
+__device__ __forceinline__ int lm_off64(int row, int chunk16) {    // 64 x 64 tile, column halves of 4 chunks
+    return ((((row >> 4) * 2 + (chunk16 >> 2)) * 4 + (chunk16 & 3)) * 16 + (row & 15)) * 8;
+}
 
 // ------------------------------------------------------------------ pre-pass
 constexpr int PRE_THREADS = 128;
@@ -150,7 +162,7 @@ __global__ void __launch_bounds__(PRE_THREADS) delta_prep_tc_kernel(
             *reinterpret_cast<uint4*>(out.BK + o64) = tc::pack8_bf16(tmp);
 #pragma unroll
             for (int e = 0; e < 8; ++e) tmp[e] = be * vf[e];
-            *reinterpret_cast<uint4*>(out.BV + o64) = tc::pack8_bf16(tmp);
+            *reinterpret_cast<uint4*>(out.BV + tix * (64 * DH) + lm_off128(t, j)) = tc::pack8_bf16(tmp);
             *reinterpret_cast<uint4*>(out.KR + o64) = k8;
             *reinterpret_cast<uint4*>(out.QR + o64) = q8;
         }
@@ -199,18 +211,18 @@ __global__ void __launch_bounds__(PRE_THREADS) delta_prep_tc_kernel(
                     float a[32];
 #pragma unroll
                     for (int j = 0; j < 32; ++j) a[j] = __uint_as_float(r[j]);
-                    uint4* dst = reinterpret_cast<uint4*>(out.KKo + (tix * 64 + t) * 64 + cc * 32);
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) dst[j] = tc::pack8_bf16(a + 8 * j);
+                    for (int j = 0; j < 4; ++j)
+                        *reinterpret_cast<uint4*>(out.KKo + tix * 4096 + lm_off64(t, cc * 4 + j)) = tc::pack8_bf16(a + 8 * j);
                 }
             } else {
                 if (out.QKo) {
                     float a[32];
 #pragma unroll
                     for (int j = 0; j < 32; ++j) a[j] = __uint_as_float(r[j]);
-                    uint4* dst = reinterpret_cast<uint4*>(out.QKo + (tix * 64 + t) * 64 + cc * 32);
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) dst[j] = tc::pack8_bf16(a + 8 * j);
+                    for (int j = 0; j < 4; ++j)
+                        *reinterpret_cast<uint4*>(out.QKo + tix * 4096 + lm_off64(t, cc * 4 + j)) = tc::pack8_bf16(a + 8 * j);
                 }          // A = lower(Gam QK), bf16 tile for the chain kernel
                 float a[32];
 #pragma unroll
@@ -296,7 +308,9 @@ __global__ void __launch_bounds__(PRE_THREADS) delta_prep_tc_kernel(
                     if (live) tc::unpack8_bf16(*reinterpret_cast<const uint4*>(src + 8 * j), x8);
 #pragma unroll
                     for (int e = 0; e < 8; ++e) o8[e] = __uint_as_float(r[8 * j + e]) + (live ? sc * x8[e] : 0.0f);
-                    *reinterpret_cast<uint4*>(dst + 8 * j) = tc::pack8_bf16(o8);
+                    const uint4 pk = tc::pack8_bf16(o8);
+                    *reinterpret_cast<uint4*>(dst + 8 * j) = pk;
+                    if (!is_w && out.UVT) *reinterpret_cast<uint4*>(out.UVT + tix * (64 * DH) + lm_off128(t, (c0 >> 3) + j)) = pk;
                 }
             }
         }
@@ -716,6 +730,30 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
     constexpr uint32_t I128_MM = tc::idesc_bf16_f32(128, 128, 1, 1);
     constexpr uint32_t I128_MM_NEG = I128_MM | (1u << 13);
 
+    // Small per-chunk inputs are fetched one chunk ahead, before that chunk's TMA traffic is queued:
+    // rows of Uv (half 0) / beta V (half 1), 64 columns each, and the per-token scalars.
+    uint4 pre[8];
+    float nx0 = 0.0f, nx1 = 0.0f;
+    auto fetch_small = [&](int c) {
+        const int64_t tix = tile0 + c;
+        const int t0 = c * C;
+        const int n = T - t0 < C ? T - t0 : C;
+        const int64_t grow = seq_row0 + t0;
+        const __nv_bfloat16* src = (half == 0 ? tl.UVT : tl.BV) + tix * (64 * DH) + lm_off128(row, colhalf * 8);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) pre[j] = *reinterpret_cast<const uint4*>(src + j * 128);
+        if (tid < 64) {
+            nx0 = tl.GV[tix * 64 + tid];
+            nx1 = tl.BE[tix * 64 + tid];
+        } else if (tid < 128) {
+            const int t = min(tid - 64, n - 1);          // unconditional loads: nothing waits on them here
+            nx0 = alpha[(grow + t) * H + h];
+        } else {
+            const int t = min(tid & 63, n - 1);
+            nx0 = (tid < 192 ? qnorm : knorm)[(grow + t) * H + h];
+        }
+    };
+    fetch_small(n_chunks - 1);
     if (tid == 0) issue_tma(n_chunks - 1);
     // A wait that gives up raises *abort_flag; later waits then return at once, the iteration runs to its
     // end on whatever data it has (every block barrier is still reached by every thread) and the loop
@@ -726,23 +764,14 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
         const int n = T - t0 < C ? T - t0 : C;
         const int64_t tix = tile0 + c;
         const int64_t grow = seq_row0 + t0;
-        // rows of Uv (half 0) / beta V (half 1), 64 columns, fetched ahead of their use
-        uint4 pre[8];
-        {
-            const __nv_bfloat16* src = (half == 0 ? tl.UV : tl.BV) + (tix * 64 + row) * DH + colhalf * 64;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) pre[j] = *reinterpret_cast<const uint4*>(src + 8 * j);
-        }
-        // ---- A. per-token scalars of the chunk
+        // ---- A. per-token scalars of the chunk (fetched during the previous chunk)
         if (tid < 64) {
-            g_s[tid] = tl.GV[tix * 64 + tid];
-            be_s[tid] = tl.BE[tix * 64 + tid];
+            g_s[tid] = nx0;
+            be_s[tid] = nx1;
         } else if (tid < 128) {
-            const int t = tid - 64;
-            v_al[t] = t < n ? alpha[(grow + t) * H + h] : 0.0f;
+            v_al[tid - 64] = nx0;
         } else {
-            const int t = tid & 63;
-            v_nrm[tid - 128] = t < n ? (tid < 192 ? qnorm : knorm)[(grow + t) * H + h] : 1.0f;
+            v_nrm[tid - 128] = nx0;
         }
         tc::fence_proxy_async_smem();   // the dS operand copy written at the end of the previous chunk
         tc::tcgen05_fence_before();
@@ -812,12 +841,12 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
         // rows of K K^T and Q K^T (32 columns each) for the dL / dA phase, fetched ahead
         uint4 pkk[4], pqk[4];
         if (half == 0) {
-            const __nv_bfloat16* kk = tl.KKo + (tix * 64 + row) * 64 + colhalf * 32;
-            const __nv_bfloat16* qk = tl.QKo + (tix * 64 + row) * 64 + colhalf * 32;
+            const __nv_bfloat16* kk = tl.KKo + tix * 4096 + lm_off64(row, colhalf * 4);
+            const __nv_bfloat16* qk = tl.QKo + tix * 4096 + lm_off64(row, colhalf * 4);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                pkk[j] = *reinterpret_cast<const uint4*>(kk + 8 * j);
-                pqk[j] = *reinterpret_cast<const uint4*>(qk + 8 * j);
+                pkk[j] = *reinterpret_cast<const uint4*>(kk + j * 128);
+                pqk[j] = *reinterpret_cast<const uint4*>(qk + j * 128);
             }
         }
         // ---- C. dR: dV out, R = beta V - P2, r_dr, r_kg, bf16 dR tile (half 1)
@@ -832,7 +861,7 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
                 tc::tmem_ld_32x32(ACC_A + lane_addr + (c0 + ci) * 32, p2);
                 tc::tmem_ld_wait();
                 if (half == 1) {
-                    float* dv = d_qkv + (grow + row) * 3 * d + 2 * d + h * DH + (c0 + ci) * 32;
+                    float4* dvs = reinterpret_cast<float4*>(sm + R_DS) + row * 32;   // dV rows staged in the free dS region
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         float x8[8], f8[8];
@@ -844,9 +873,10 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
                             r_dr = fmaf(dr, x8[e] - pp, r_dr);
                             r_kg = fmaf(-dr, pp, r_kg);
                         }
-                        if (live) {
-                            reinterpret_cast<float4*>(dv)[2 * j] = make_float4(be_row * f8[0], be_row * f8[1], be_row * f8[2], be_row * f8[3]);
-                            reinterpret_cast<float4*>(dv)[2 * j + 1] = make_float4(be_row * f8[4], be_row * f8[5], be_row * f8[6], be_row * f8[7]);
+                        {
+                            const int f4 = ((c0 + ci) * 4 + j) * 2, swz = row & 31;
+                            dvs[f4 ^ swz] = make_float4(be_row * f8[0], be_row * f8[1], be_row * f8[2], be_row * f8[3]);
+                            dvs[(f4 + 1) ^ swz] = make_float4(be_row * f8[4], be_row * f8[5], be_row * f8[6], be_row * f8[7]);
                         }
                         *tile64(R_DR, row, (c0 + ci) * 4 + j) = tc::pack8_bf16(f8);
                     }
@@ -868,7 +898,17 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
             _Pragma("unroll") for (int k16 = 0; k16 < 8; ++k16) tc::umma_bf16(ACC_A + H1, kmaj(R_DR, k16), kmaj128(R_S0, k16), I64_KK, k16 > 0);
             tc::umma_commit(&bars[4]);
         }
-        // ---- D. scale dS by gam_C, and <S0, dS> from the bf16 copy of S0, while G4/G5 run
+        // ---- D. while G4/G5 run: dV rows out (8 lanes per row, coalesced), scale dS by gam_C, <S0, dS>
+#pragma unroll
+        for (int itv = 0; itv < 2; ++itv) {
+            const int r_ = itv * 32 + (tid >> 3), l8 = tid & 7;
+            if (r_ < n) {
+                float* dv = d_qkv + (grow + r_) * 3 * d + 2 * d + h * DH;
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    reinterpret_cast<float4*>(dv)[l8 + 8 * i] = reinterpret_cast<const float4*>(sm + R_DS)[r_ * 32 + ((l8 + 8 * i) ^ (r_ & 31))];
+            }
+        }
         {
             const float gC = __expf(g_last);
             float part = 0.0f;
@@ -991,21 +1031,39 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
             (half == 0 ? v_rqs : v_rkw)[colhalf * 64 + row] = rr;
         }
         __syncthreads();
-        // L2-norm backward and store, one warp per staged row, coalesced
-        for (int srow = warp; srow < 128; srow += BW_THREADS / 32) {
-            const int hh = srow >> 6, r_ = srow & 63;
-            if (r_ >= n) continue;
-            const int swz = (r_ + 16 * hh) & 31;
-            const float4 g4 = reinterpret_cast<const float4*>(sm + R_STG)[srow * 32 + (lane ^ swz)];
-            const uint2 yraw = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(tile64(hh == 0 ? R_Q : R_K, r_, lane >> 1)) + (lane & 1) * 8);
-            const __nv_bfloat162 y01 = *reinterpret_cast<const __nv_bfloat162*>(&yraw.x), y23 = *reinterpret_cast<const __nv_bfloat162*>(&yraw.y);
-            const float y0 = __low2float(y01), y1 = __high2float(y01), y2 = __low2float(y23), y3 = __high2float(y23);
-            float dot = y0 * g4.x + y1 * g4.y + y2 * g4.z + y3 * g4.w;
-            dot = warp_sum(dot);
-            const float inv = 1.0f / v_nrm[srow];
-            float* dst = d_qkv + (grow + r_) * 3 * d + (hh == 0 ? 0 : d) + h * DH;
-            reinterpret_cast<float4*>(dst)[lane] = make_float4((g4.x - y0 * dot) * inv, (g4.y - y1 * dot) * inv,
-                                                               (g4.z - y2 * dot) * inv, (g4.w - y3 * dot) * inv);
+        if (c > 0) fetch_small(c - 1);
+        // L2-norm backward and store: 8 lanes per staged row (4 float4 each), 4 rows per warp at a time
+        {
+            const int l8 = lane & 7, hh = warp >> 2;
+            const int ytile = hh == 0 ? R_Q : R_K;
+#pragma unroll
+            for (int itn = 0; itn < 4; ++itn) {
+                const int srow = warp * 16 + itn * 4 + (lane >> 3), r_ = srow & 63;
+                const int swz = (r_ + 16 * hh) & 31;
+                float4 g4[4];
+                float y[4][4];
+                float dot = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int f4 = l8 + 8 * i;
+                    g4[i] = reinterpret_cast<const float4*>(sm + R_STG)[srow * 32 + (f4 ^ swz)];
+                    const uint2 yraw = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(tile64(ytile, r_, f4 >> 1)) + (f4 & 1) * 8);
+                    const __nv_bfloat162 y01 = *reinterpret_cast<const __nv_bfloat162*>(&yraw.x), y23 = *reinterpret_cast<const __nv_bfloat162*>(&yraw.y);
+                    y[i][0] = __low2float(y01), y[i][1] = __high2float(y01), y[i][2] = __low2float(y23), y[i][3] = __high2float(y23);
+                    dot += y[i][0] * g4[i].x + y[i][1] * g4[i].y + y[i][2] * g4[i].z + y[i][3] * g4[i].w;
+                }
+                dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+                dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+                dot += __shfl_xor_sync(0xffffffffu, dot, 4);
+                if (r_ < n) {
+                    const float inv = 1.0f / v_nrm[srow];
+                    float* dst = d_qkv + (grow + r_) * 3 * d + (hh == 0 ? 0 : d) + h * DH;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        reinterpret_cast<float4*>(dst)[l8 + 8 * i] = make_float4((g4[i].x - y[i][0] * dot) * inv, (g4[i].y - y[i][1] * dot) * inv,
+                                                                                  (g4[i].z - y[i][2] * dot) * inv, (g4[i].w - y[i][3] * dot) * inv);
+                }
+            }
         }
         // gates (warp 0): dg, reverse cumulative sum, sigmoid backward
         if (warp == 0) {
@@ -1133,6 +1191,7 @@ static size_t carve_tiles(char* w, int64_t n_tiles, bool full, Tiles* t) {
     if (full) {
         z.BK = (__nv_bfloat16*)take(b64);
         z.BV = (__nv_bfloat16*)take(b64);
+        z.UVT = (__nv_bfloat16*)take(b64);
         z.KR = (__nv_bfloat16*)take(b64);
         z.QR = (__nv_bfloat16*)take(b64);
         z.TP = (__nv_bfloat16*)take(bcc);
