@@ -6,9 +6,10 @@
 //   pre-pass (one CTA per (sequence, head, chunk) -- fully parallel, nothing depends on S):
 //     KK = K K^T, QK = Q K^T                                   tcgen05, M128 N64 K128 ([K;Q] stacked)
 //     L  = strictlower(beta_t Gam KK)   A = lower(Gam QK)      f32 registers
-//     T' = (I + L)^-1 - I                                      f32 forward substitution per column
-//     [W^ | Uv] = (I + T') [beta gam K | beta V]               tcgen05, M128(padded) N256 K64; the
-//                                                              identity part is added exactly in f32
+//     X  = (I + L)^-1  (T' = X - I)                            f32, 16 x 16 blocks: substitution on the
+//                                                              diagonal, block products below it
+//     W^ = X (beta gam K),  Uv = X (beta V)                    tcgen05, two M64 N128 K64 products sharing
+//                                                              TMEM columns in the two lane halves
 //     Qg = gam Q,  Kw = eg K                                   bf16 tiles for the chain kernel
 //   chain (one CTA per (sequence, head), 64 dependent chunks):
 //     [W^ S0 ; Qg S0]                                          tcgen05, M128 N128 K128
@@ -64,8 +65,27 @@ __device__ __forceinline__ int lm_off64(int row, int chunk16) {    // 64 x 64 ti
 
 // ------------------------------------------------------------------ pre-pass
 constexpr int PRE_THREADS = 128;
-constexpr int LF_LD = 68;
-constexpr size_t PRE_SMEM = 1024 + NB * 16384 /*KQ*/ + 2 * NB * 8192 /*Bop*/ + 16384 /*Tp*/ + 64 * LF_LD * 4 + 4 * 64 * 4 + 64;
+constexpr int LF_LD = 68;     // row stride (floats) of the f32 L and X matrices: float4 rows, conflict-free
+constexpr int YF_LD = 16;
+constexpr size_t PRE_SMEM = 1024 + NB * 16384 /*KQ, later X and Y*/ + 2 * NB * 8192 /*Bop, later W^/Uv staging*/ +
+                            8192 /*T, before that A staging*/ + 64 * LF_LD * 4 + 4 * 64 * 4 + 64;
+
+// One 1 x 4 strip of a 16 x 16 block product  acc += Lrow[0..16) * X[0..16)[c4..c4+4)  (f32, shared memory).
+__device__ __forceinline__ void strip16(const float* __restrict__ lrow, const float* __restrict__ x, int ldx, float acc[4]) {
+#pragma unroll
+    for (int k4 = 0; k4 < 4; ++k4) {
+        const float4 l4 = *reinterpret_cast<const float4*>(lrow + 4 * k4);
+        const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float4 x4 = *reinterpret_cast<const float4*>(x + (4 * k4 + e) * ldx);
+            acc[0] = fmaf(lv[e], x4.x, acc[0]);
+            acc[1] = fmaf(lv[e], x4.y, acc[1]);
+            acc[2] = fmaf(lv[e], x4.z, acc[2]);
+            acc[3] = fmaf(lv[e], x4.w, acc[3]);
+        }
+    }
+}
 
 __global__ void __launch_bounds__(PRE_THREADS) delta_prep_tc_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
@@ -75,8 +95,8 @@ __global__ void __launch_bounds__(PRE_THREADS) delta_prep_tc_kernel(
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* KQ_s = base;                         // NB k-boxes x (128 rows x 128 B): rows 0-63 K, 64-127 Q
     uint8_t* Bop_s = KQ_s + NB * 16384;           // 2*NB n-boxes x (64 k-rows x 128 B): [beta gam K | beta V]
-    uint8_t* Tp_s = Bop_s + 2 * NB * 8192;        // 128 rows x 128 B: T' (rows 64-127 zero)
-    float* Lf = reinterpret_cast<float*>(Tp_s + 16384);
+    uint8_t* Tp_s = Bop_s + 2 * NB * 8192;        // 64 rows x 128 B: (I + L)^-1, K-major
+    float* Lf = reinterpret_cast<float*>(Tp_s + 8192);
     float* g_s = Lf + 64 * LF_LD;
     float* gam_s = g_s + 64;
     float* eg_s = gam_s + 64;
@@ -84,6 +104,9 @@ __global__ void __launch_bounds__(PRE_THREADS) delta_prep_tc_kernel(
     uint64_t* bar = reinterpret_cast<uint64_t*>(be_s + 64);   // [0] MMA-A done, [1] MMA-B done
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    float* wtot = reinterpret_cast<float*>(tmem_slot + 2);
+    float* Xf = reinterpret_cast<float*>(KQ_s);   // (I + L)^-1 in f32, once K and Q have been consumed
+    float* Yf = Xf + 64 * LF_LD;                  // [3][16][YF_LD] block products in flight
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int chunk = blockIdx.x, chain = blockIdx.y;
@@ -94,85 +117,91 @@ __global__ void __launch_bounds__(PRE_THREADS) delta_prep_tc_kernel(
     const int64_t row0 = (int64_t)b * T + t0;
     const int64_t tix = (int64_t)chain * n_chunks + chunk;
 
+    // K, Q, V rows of the chunk: every load is issued before anything waits on one
+    const int sj = tid & 15;                      // 16-byte chunk of the row handled by this thread
+    uint4 k8[8], q8[8], v8[8];
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+        const int t = (tid >> 4) + it * 8;
+        k8[it] = q8[it] = v8[it] = make_uint4(0, 0, 0, 0);
+        if (t < n) {
+            const int64_t off = (row0 + t) * d + h * DH + sj * 8;
+            k8[it] = *reinterpret_cast<const uint4*>(k + off);
+            q8[it] = *reinterpret_cast<const uint4*>(q + off);
+            v8[it] = *reinterpret_cast<const uint4*>(v + off);
+        }
+    }
     if (tid == 0) {
         *abort_flag = 0;
         tc::mbar_init(&bar[0], 1);
         tc::mbar_init(&bar[1], 1);
         tc::mbar_fence_init();
     }
-    if (warp == 0) tc::tmem_alloc(tmem_slot, 256);
+    if (warp == 0) tc::tmem_alloc(tmem_slot, 128);
+    // g = cumsum(log alpha): warp scans over the 64 tokens
+    float gx = 0.0f;
     if (tid < C) {
         const bool live = tid < n;
-        const float a = live ? alpha[(row0 + tid) * H + h] : 1.0f;
         be_s[tid] = live ? beta[(row0 + tid) * H + h] : 0.0f;
-        g_s[tid] = logf(a);
+        gx = live ? logf(alpha[(row0 + tid) * H + h]) : 0.0f;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float y = __shfl_up_sync(0xffffffffu, gx, o);
+            if (lane >= o) gx += y;
+        }
+        if (tid == 31) *wtot = gx;
     }
     tc::tcgen05_fence_before();
     __syncthreads();
     tc::tcgen05_fence_after();
     const uint32_t tmem = *tmem_slot;
-    if (tid == 0) {
-        float run = 0.0f;
-        for (int t = 0; t < C; ++t) {
-            run += g_s[t];
-            g_s[t] = run;
-        }
+    if (tid < C) {
+        if (tid >= 32) gx += *wtot;
+        g_s[tid] = gx;
+        gam_s[tid] = expf(gx);
     }
     __syncthreads();
-    if (tid < C) {
-        gam_s[tid] = expf(g_s[tid]);
-        eg_s[tid] = expf(g_s[C - 1] - g_s[tid]);
-    }
+    if (tid < C) eg_s[tid] = expf(g_s[C - 1] - g_s[tid]);
     __syncthreads();
 
-    // ---- stage K, Q (K-major, swizzled), build [beta gam K | beta V], emit Qg and Kw
-    for (int idx = tid; idx < C * (DH / 8); idx += PRE_THREADS) {
-        const int t = idx / (DH / 8), j = idx % (DH / 8);
-        uint4 k8 = make_uint4(0, 0, 0, 0), q8 = k8, v8 = k8;
-        if (t < n) {
-            const int64_t off = (row0 + t) * d + h * DH + j * 8;
-            k8 = *reinterpret_cast<const uint4*>(k + off);
-            q8 = *reinterpret_cast<const uint4*>(q + off);
-            v8 = *reinterpret_cast<const uint4*>(v + off);
-        }
-        const int box = j >> 3, jc = j & 7;
-        *reinterpret_cast<uint4*>(KQ_s + box * 16384 + tc::sw128_off(t, jc)) = k8;
-        *reinterpret_cast<uint4*>(KQ_s + box * 16384 + tc::sw128_off(64 + t, jc)) = q8;
-        float kf[8], qf[8], vf[8], tmp[8];
-        tc::unpack8_bf16(k8, kf);
-        tc::unpack8_bf16(q8, qf);
-        tc::unpack8_bf16(v8, vf);
-        const float be = be_s[t], gm = gam_s[t], eg = eg_s[t];
+    // ---- stage K, Q (K-major, swizzled), build [beta gam K | beta V], emit Qg, Kw and the backward's copies
+    {
+        const int box = sj >> 3, jc = sj & 7;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) tmp[e] = be * gm * kf[e];
-        *reinterpret_cast<uint4*>(Bop_s + box * 8192 + tc::sw128_off(t, jc)) = tc::pack8_bf16(tmp);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) tmp[e] = be * vf[e];
-        *reinterpret_cast<uint4*>(Bop_s + (NB + box) * 8192 + tc::sw128_off(t, jc)) = tc::pack8_bf16(tmp);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) tmp[e] = gm * qf[e];
-        *reinterpret_cast<uint4*>(out.WQ + (tix * 128 + 64 + t) * DH + j * 8) = tc::pack8_bf16(tmp);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) tmp[e] = eg * kf[e];
-        *reinterpret_cast<uint4*>(out.KW + (tix * 64 + t) * DH + j * 8) = tc::pack8_bf16(tmp);
-        if (out.BK) {
-            const int64_t o64 = (tix * 64 + t) * DH + j * 8;
+        for (int it = 0; it < 8; ++it) {
+            const int t = (tid >> 4) + it * 8;
+            *reinterpret_cast<uint4*>(KQ_s + box * 16384 + tc::sw128_off(t, jc)) = k8[it];
+            *reinterpret_cast<uint4*>(KQ_s + box * 16384 + tc::sw128_off(64 + t, jc)) = q8[it];
+            float kf[8], qf[8], vf[8], tmp[8];
+            tc::unpack8_bf16(k8[it], kf);
+            tc::unpack8_bf16(q8[it], qf);
+            tc::unpack8_bf16(v8[it], vf);
+            const float be = be_s[t], gm = gam_s[t], eg = eg_s[t];
+            const int64_t o64 = (tix * 64 + t) * DH + sj * 8;
 #pragma unroll
             for (int e = 0; e < 8; ++e) tmp[e] = be * gm * kf[e];
-            *reinterpret_cast<uint4*>(out.BK + o64) = tc::pack8_bf16(tmp);
+            const uint4 bk = tc::pack8_bf16(tmp);
+            *reinterpret_cast<uint4*>(Bop_s + box * 8192 + tc::sw128_off(t, jc)) = bk;
 #pragma unroll
             for (int e = 0; e < 8; ++e) tmp[e] = be * vf[e];
-            *reinterpret_cast<uint4*>(out.BV + tix * (64 * DH) + lm_off128(t, j)) = tc::pack8_bf16(tmp);
-            *reinterpret_cast<uint4*>(out.KR + o64) = k8;
-            *reinterpret_cast<uint4*>(out.QR + o64) = q8;
+            *reinterpret_cast<uint4*>(Bop_s + (NB + box) * 8192 + tc::sw128_off(t, jc)) = tc::pack8_bf16(tmp);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) tmp[e] = gm * qf[e];
+            *reinterpret_cast<uint4*>(out.WQ + (tix * 128 + 64 + t) * DH + sj * 8) = tc::pack8_bf16(tmp);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) tmp[e] = eg * kf[e];
+            *reinterpret_cast<uint4*>(out.KW + o64) = tc::pack8_bf16(tmp);
+            if (out.BK) {
+                *reinterpret_cast<uint4*>(out.BK + o64) = bk;
+                *reinterpret_cast<uint4*>(out.KR + o64) = k8[it];
+                *reinterpret_cast<uint4*>(out.QR + o64) = q8[it];
+            }
         }
     }
     if (out.GV && tid < C) {
         out.GV[tix * 64 + tid] = g_s[tid];
         out.BE[tix * 64 + tid] = be_s[tid];
     }
-    // rows 64-127 of the T' operand stay zero
-    for (int i = tid; i < 8192 / 16; i += PRE_THREADS) *reinterpret_cast<uint4*>(Tp_s + 8192 + i * 16) = make_uint4(0, 0, 0, 0);
     tc::fence_proxy_async_smem();
     __syncthreads();
 
@@ -188,24 +217,40 @@ __global__ void __launch_bounds__(PRE_THREADS) delta_prep_tc_kernel(
         }
         tc::umma_commit(&bar[0]);
     }
+    // beta V in the lane-major layout, from the operand tile (consecutive threads, consecutive 16 bytes)
+    if (out.BV) {
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+            const int L = tid + it * PRE_THREADS;
+            const int row = (L >> 8) * 16 + (L & 15), c16 = ((L >> 7) & 1) * 8 + ((L >> 4) & 7);
+            *reinterpret_cast<uint4*>(out.BV + tix * (64 * DH) + L * 8) =
+                *reinterpret_cast<const uint4*>(Bop_s + (NB + (c16 >> 3)) * 8192 + tc::sw128_off(row, c16 & 7));
+        }
+    }
     int got = 1;
     if (lane == 0) got = tc::mbar_wait(&bar[0], 0, abort_flag, err_word, 201) ? 1 : 0;
     bool ok = __shfl_sync(0xffffffffu, got, 0) != 0;
     ok = __syncthreads_and(ok ? 1 : 0) != 0;
     tc::tcgen05_fence_after();
+    // ---- L = strictlower(beta_t Gam KK) (f32, threads 0-63); A = lower(Gam QK) (bf16, threads 64-127)
     if (ok) {
         uint32_t r[32];
         const int t = tid & 63;
         const float gt = g_s[t], bt = be_s[t];
-#pragma unroll 1
+#pragma unroll
         for (int cc = 0; cc < 2; ++cc) {
             tc::tmem_ld_32x32(tmem + ((uint32_t)(warp * 32) << 16) + cc * 32, r);
             tc::tmem_ld_wait();
-            if (tid < 64) {   // L = strictlower(beta_t Gam KK), f32
+            if (tid < 64) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int i = cc * 32 + j;
-                    Lf[t * LF_LD + i] = i < t ? bt * __expf(gt - g_s[i]) * __uint_as_float(r[j]) : 0.0f;
+                for (int j4 = 0; j4 < 8; ++j4) {
+                    float l[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int i = cc * 32 + 4 * j4 + e;
+                        l[e] = i < t ? bt * __expf(gt - g_s[i]) * __uint_as_float(r[4 * j4 + e]) : 0.0f;
+                    }
+                    *reinterpret_cast<float4*>(&Lf[t * LF_LD + cc * 32 + 4 * j4]) = make_float4(l[0], l[1], l[2], l[3]);
                 }
                 if (out.KKo) {
                     float a[32];
@@ -216,109 +261,169 @@ __global__ void __launch_bounds__(PRE_THREADS) delta_prep_tc_kernel(
                         *reinterpret_cast<uint4*>(out.KKo + tix * 4096 + lm_off64(t, cc * 4 + j)) = tc::pack8_bf16(a + 8 * j);
                 }
             } else {
+                float a[32];
                 if (out.QKo) {
-                    float a[32];
 #pragma unroll
                     for (int j = 0; j < 32; ++j) a[j] = __uint_as_float(r[j]);
 #pragma unroll
                     for (int j = 0; j < 4; ++j)
                         *reinterpret_cast<uint4*>(out.QKo + tix * 4096 + lm_off64(t, cc * 4 + j)) = tc::pack8_bf16(a + 8 * j);
-                }          // A = lower(Gam QK), bf16 tile for the chain kernel
-                float a[32];
+                }
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
                     const int i = cc * 32 + j;
                     a[j] = i <= t ? __expf(gt - g_s[i]) * __uint_as_float(r[j]) : 0.0f;
                 }
-                uint4* dst = reinterpret_cast<uint4*>(out.AA + (tix * 64 + t) * 64 + cc * 32);
+                // staged in the (still unused) T region, 16-byte chunks XOR-swizzled by row, for a coalesced copy-out
 #pragma unroll
-                for (int j = 0; j < 4; ++j) dst[j] = tc::pack8_bf16(a + 8 * j);
+                for (int j = 0; j < 4; ++j)
+                    *reinterpret_cast<uint4*>(Tp_s + t * 128 + (((cc * 4 + j) ^ (t & 7)) << 4)) = tc::pack8_bf16(a + 8 * j);
             }
         }
     }
     tc::tcgen05_fence_before();
     __syncthreads();
 
-    // ---- T' = (I + L)^-1 - I, one column per thread (f32 forward substitution)
-    if (tid < 64 && ok) {
-        const int j = tid;
-        float x[C];
+    // ---- X = (I + L)^-1 in f32, by 16 x 16 blocks: the four diagonal blocks by forward substitution (one
+    //      column per thread), then the blocks 1, 2 and 3 below the diagonal as X_IJ = -X_II (sum_K L_IK X_KJ)
+    if (tid < 64) {
+        const int I = tid >> 4, jj = tid & 15;
+        const float* Lb = Lf + (I * 16) * LF_LD + I * 16;
+        float x[16];
 #pragma unroll
-        for (int t = 0; t < C; ++t) {
-            float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+        for (int t = 0; t < 16; ++t) x[t] = 0.0f;
 #pragma unroll
-            for (int i = 0; i + 3 < t; i += 4) {
-                const float4 l4 = *reinterpret_cast<const float4*>(&Lf[t * LF_LD + i]);
-                s0 = fmaf(l4.x, x[i], s0);
-                s1 = fmaf(l4.y, x[i + 1], s1);
-                s2 = fmaf(l4.z, x[i + 2], s2);
-                s3 = fmaf(l4.w, x[i + 3], s3);
+        for (int t = 0; t < 16; ++t) {
+            float s = 0.0f;
+#pragma unroll
+            for (int g4 = 0; g4 < (t + 3) / 4; ++g4) {      // entries at and right of the diagonal are zero in L
+                const float4 l4 = *reinterpret_cast<const float4*>(Lb + t * LF_LD + 4 * g4);
+                s = fmaf(l4.x, x[4 * g4], s);
+                s = fmaf(l4.y, x[4 * g4 + 1], s);
+                s = fmaf(l4.z, x[4 * g4 + 2], s);
+                s = fmaf(l4.w, x[4 * g4 + 3], s);
             }
+            x[t] = (t == jj ? 1.0f : 0.0f) - s;
+        }
 #pragma unroll
-            for (int i = t & ~3; i < t; ++i) s0 = fmaf(Lf[t * LF_LD + i], x[i], s0);
-            x[t] = (t == j ? 1.0f : 0.0f) - ((s0 + s1) + (s2 + s3));
-            const float tp = t == j ? 0.0f : x[t];
-            *reinterpret_cast<__nv_bfloat16*>(Tp_s + tc::sw128_off(t, j >> 3) + (j & 7) * 2) = __float2bfloat16(tp);
+        for (int t = 0; t < 16; ++t) Xf[(I * 16 + t) * LF_LD + I * 16 + jj] = x[t];
+    } else {
+        // meanwhile threads 64-127 write the A tile out, 128 contiguous bytes per row
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+            const int idx = (tid - 64) + it * 64, t = idx >> 3, jc = idx & 7;
+            *reinterpret_cast<uint4*>(out.AA + (tix * 64 + t) * 64 + jc * 8) =
+                *reinterpret_cast<const uint4*>(Tp_s + t * 128 + ((jc ^ (t & 7)) << 4));
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int dd = 1; dd < 4; ++dd) {
+        const int pieces = (4 - dd) * 64;           // 1 x 4 strips of the (4 - dd) blocks at distance dd
+        for (int p = tid; p < pieces; p += PRE_THREADS) {
+            const int bI = (p >> 6) + dd, bJ = p >> 6, r = (p >> 2) & 15, c4 = (p & 3) * 4;
+            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int kk = 0; kk < dd; ++kk)
+                strip16(Lf + (bI * 16 + r) * LF_LD + (bJ + kk) * 16, Xf + ((bJ + kk) * 16) * LF_LD + bJ * 16 + c4, LF_LD, acc);
+            *reinterpret_cast<float4*>(&Yf[((p >> 6) * 16 + r) * YF_LD + c4]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        }
+        __syncthreads();
+        for (int p = tid; p < pieces; p += PRE_THREADS) {
+            const int bI = (p >> 6) + dd, bJ = p >> 6, r = (p >> 2) & 15, c4 = (p & 3) * 4;
+            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            strip16(Xf + (bI * 16 + r) * LF_LD + bI * 16, Yf + ((p >> 6) * 16) * YF_LD + c4, YF_LD, acc);
+            *reinterpret_cast<float4*>(&Xf[(bI * 16 + r) * LF_LD + bJ * 16 + c4]) = make_float4(-acc[0], -acc[1], -acc[2], -acc[3]);
+        }
+        __syncthreads();
+    }
+    // ---- X -> bf16 operand tile (K-major) and, for the backward, T' = X - I row-major
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+        const int idx = tid + it * PRE_THREADS, t = idx >> 3, jc = idx & 7;
+        float x8[8];
+        if ((jc >> 1) <= (t >> 4)) {
+            const float4 a = *reinterpret_cast<const float4*>(&Xf[t * LF_LD + jc * 8]);
+            const float4 c = *reinterpret_cast<const float4*>(&Xf[t * LF_LD + jc * 8 + 4]);
+            x8[0] = a.x, x8[1] = a.y, x8[2] = a.z, x8[3] = a.w, x8[4] = c.x, x8[5] = c.y, x8[6] = c.z, x8[7] = c.w;
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) x8[e] = 0.0f;
+        }
+        *reinterpret_cast<uint4*>(Tp_s + tc::sw128_off(t, jc)) = tc::pack8_bf16(x8);
+        if (out.TP) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+                if (jc * 8 + e == t) x8[e] = 0.0f;
+            *reinterpret_cast<uint4*>(out.TP + (tix * 64 + t) * 64 + jc * 8) = tc::pack8_bf16(x8);
         }
     }
     tc::fence_proxy_async_smem();
     __syncthreads();
-    if (out.TP) {
-        for (int idx = tid; idx < 64 * 8; idx += PRE_THREADS) {
-            const int t = idx >> 3, jc = idx & 7;
-            *reinterpret_cast<uint4*>(out.TP + (tix * 64 + t) * 64 + jc * 8) =
-                *reinterpret_cast<const uint4*>(Tp_s + tc::sw128_off(t, jc));
-        }
-    }
 
-    // ---- MMA-B: [T'(beta gam K) | T'(beta V)]   (M128 N256 K64)
+    // ---- MMA-B: W^ = X (beta gam K) in lane half 0, Uv = X (beta V) in lane half 1   (2 x M64 N128 K64)
     if (tid == 0 && ok) {
-        constexpr uint32_t IDESC = tc::idesc_bf16_f32(128, 2 * DH, 0, 1);
+        constexpr uint32_t IDESC = tc::idesc_bf16_f32(64, DH, 0, 1);
         const uint32_t ta = tc::smem_u32(Tp_s), bo = tc::smem_u32(Bop_s);
         tc::tcgen05_fence_after();
 #pragma unroll
         for (int k16 = 0; k16 < C / 16; ++k16)
-            tc::umma_bf16(tmem, tc::smem_desc_sw128(ta + k16 * 32, 16, 1024),
-                          tc::smem_desc_sw128(bo + k16 * 2048, 8192, 1024), IDESC, k16 > 0 ? 1u : 0u);
+            tc::umma_bf16(tmem, tc::smem_desc_sw128(ta + k16 * 32, 16, 1024), tc::smem_desc_sw128(bo + k16 * 2048, 8192, 1024),
+                          IDESC, k16 > 0 ? 1u : 0u);
+#pragma unroll
+        for (int k16 = 0; k16 < C / 16; ++k16)
+            tc::umma_bf16(tmem + (16u << 16), tc::smem_desc_sw128(ta + k16 * 32, 16, 1024),
+                          tc::smem_desc_sw128(bo + NB * 8192 + k16 * 2048, 8192, 1024), IDESC, k16 > 0 ? 1u : 0u);
         tc::umma_commit(&bar[1]);
     }
-    if (warp < 2 && ok) {
+    if (ok) {
         got = 1;
         if (lane == 0) got = tc::mbar_wait(&bar[1], 0, abort_flag, err_word, 202) ? 1 : 0;
-        const bool ok2 = __shfl_sync(0xffffffffu, got, 0) != 0;
-        tc::tcgen05_fence_after();
-        if (ok2) {
-            const int t = tid;
-            const float be = be_s[t], bg = be_s[t] * gam_s[t];
-            const bool live = t < n;
-            const int64_t in_off = (row0 + (live ? t : 0)) * d + h * DH;
+        ok = __shfl_sync(0xffffffffu, got, 0) != 0;
+    }
+    ok = __syncthreads_and(ok ? 1 : 0) != 0;
+    tc::tcgen05_fence_after();
+    // rows to the staging area (the operand tiles are consumed): [W^ | Uv] 64 x 256 B each, chunks XOR-swizzled
+    if (ok) {
+        const int half = lane >> 4, row = 16 * warp + (lane & 15);
+        uint8_t* stg = Bop_s + half * 16384 + row * 256;
+#pragma unroll
+        for (int cc = 0; cc < DH / 32; ++cc) {
             uint32_t r[32];
-#pragma unroll 1
-            for (int cc = 0; cc < 2 * DH / 32; ++cc) {
-                tc::tmem_ld_32x32(tmem + ((uint32_t)(warp * 32) << 16) + cc * 32, r);
-                tc::tmem_ld_wait();
-                const bool is_w = cc < DH / 32;
-                const int c0 = (is_w ? cc : cc - DH / 32) * 32;
-                const __nv_bfloat16* src = (is_w ? k : v) + in_off + c0;
-                const float sc = is_w ? bg : be;
-                __nv_bfloat16* dst = is_w ? out.WQ + (tix * 128 + t) * DH + c0 : out.UV + (tix * 64 + t) * DH + c0;
+            tc::tmem_ld_32x32(tmem + ((uint32_t)(warp * 32) << 16) + cc * 32, r);
+            tc::tmem_ld_wait();
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    float x8[8], o8[8];
-                    if (live) tc::unpack8_bf16(*reinterpret_cast<const uint4*>(src + 8 * j), x8);
+            for (int j = 0; j < 4; ++j) {
+                float o8[8];
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) o8[e] = __uint_as_float(r[8 * j + e]) + (live ? sc * x8[e] : 0.0f);
-                    const uint4 pk = tc::pack8_bf16(o8);
-                    *reinterpret_cast<uint4*>(dst + 8 * j) = pk;
-                    if (!is_w && out.UVT) *reinterpret_cast<uint4*>(out.UVT + tix * (64 * DH) + lm_off128(t, (c0 >> 3) + j)) = pk;
-                }
+                for (int e = 0; e < 8; ++e) o8[e] = __uint_as_float(r[8 * j + e]);
+                *reinterpret_cast<uint4*>(stg + (((cc * 4 + j) ^ (row & 15)) << 4)) = tc::pack8_bf16(o8);
+            }
+        }
+    }
+    __syncthreads();
+    if (ok) {
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+            const int idx = tid + it * PRE_THREADS, t = idx >> 4, c16 = idx & 15;
+            const uint32_t so = t * 256 + ((c16 ^ (t & 15)) << 4);
+            *reinterpret_cast<uint4*>(out.WQ + (tix * 128 + t) * DH + c16 * 8) = *reinterpret_cast<const uint4*>(Bop_s + so);
+            *reinterpret_cast<uint4*>(out.UV + (tix * 64 + t) * DH + c16 * 8) = *reinterpret_cast<const uint4*>(Bop_s + 16384 + so);
+        }
+        if (out.UVT) {
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+                const int L = tid + it * PRE_THREADS;
+                const int row = (L >> 8) * 16 + (L & 15), c16 = ((L >> 7) & 1) * 8 + ((L >> 4) & 7);
+                *reinterpret_cast<uint4*>(out.UVT + tix * (64 * DH) + L * 8) =
+                    *reinterpret_cast<const uint4*>(Bop_s + 16384 + row * 256 + ((c16 ^ (row & 15)) << 4));
             }
         }
     }
     if (tid == 0) out.GC[tix] = gam_s[C - 1];
     tc::tcgen05_fence_before();
     __syncthreads();
-    if (warp == 0) tc::tmem_dealloc(tmem, 256);
+    if (warp == 0) tc::tmem_dealloc(tmem, 128);
 }
 
 // ------------------------------------------------------------------ chain kernel
