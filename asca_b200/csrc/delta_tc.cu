@@ -49,7 +49,6 @@ struct Tiles {            // intermediate buffers, one tile per (chain, chunk)
     __nv_bfloat16* QKo;   // [tile] Q K^T, 64 x 64, lane-major
     float* GV;            // [tile][64] cumulative log alpha
     float* BE;            // [tile][64] beta (0 on padded steps)
-    __nv_bfloat16* S0B;   // [tile][DH][DH] state at the start of the chunk (written by the chain forward)
 };
 
 // Lane-major tile layouts for rows that the backward's threads read straight from global memory.
@@ -67,8 +66,11 @@ __device__ __forceinline__ int lm_off64(int row, int chunk16) {    // 64 x 64 ti
 constexpr int PRE_THREADS = 128;
 constexpr int LF_LD = 68;     // row stride (floats) of the f32 L and X matrices: float4 rows, conflict-free
 constexpr int YF_LD = 16;
-constexpr size_t PRE_SMEM = 1024 + NB * 16384 /*KQ, later X and Y*/ + 2 * NB * 8192 /*Bop, later W^/Uv staging*/ +
-                            8192 /*T, before that A staging*/ + 64 * LF_LD * 4 + 4 * 64 * 4 + 64;
+// Shared memory is sized for three CTAs per SM: the K/Q operand tiles are dead once KK and QK exist, so the
+// f32 L and X matrices, and later the bf16 operand tile of X, live in the same region.
+constexpr int PRE_R1 = 2 * 64 * LF_LD * 4;        // >= NB * 16384
+constexpr size_t PRE_SMEM = 1024 + PRE_R1 + 2 * NB * 8192 /*Bop, later W^/Uv staging*/ + 3 * 16 * YF_LD * 4 + 4 * 64 * 4 + 64;
+static_assert(PRE_R1 >= NB * 16384 && PRE_R1 % 1024 == 0 && (64 * LF_LD * 4) % 1024 == 0, "pre-pass shared-memory layout");
 
 // One 1 x 4 strip of a 16 x 16 block product  acc += Lrow[0..16) * X[0..16)[c4..c4+4)  (f32, shared memory).
 __device__ __forceinline__ void strip16(const float* __restrict__ lrow, const float* __restrict__ x, int ldx, float acc[4]) {
@@ -87,17 +89,19 @@ __device__ __forceinline__ void strip16(const float* __restrict__ lrow, const fl
     }
 }
 
-__global__ void __launch_bounds__(PRE_THREADS) delta_prep_tc_kernel(
+__global__ void __launch_bounds__(PRE_THREADS, 3) delta_prep_tc_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
     const float* __restrict__ alpha, const float* __restrict__ beta, int T, int H, int n_chunks, Tiles out,
     int* err_word) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* KQ_s = base;                         // NB k-boxes x (128 rows x 128 B): rows 0-63 K, 64-127 Q
-    uint8_t* Bop_s = KQ_s + NB * 16384;           // 2*NB n-boxes x (64 k-rows x 128 B): [beta gam K | beta V]
-    uint8_t* Tp_s = Bop_s + 2 * NB * 8192;        // 64 rows x 128 B: (I + L)^-1, K-major
-    float* Lf = reinterpret_cast<float*>(Tp_s + 8192);
-    float* g_s = Lf + 64 * LF_LD;
+    uint8_t* Bop_s = KQ_s + PRE_R1;               // 2*NB n-boxes x (64 k-rows x 128 B): [beta gam K | beta V]
+    float* Xf = reinterpret_cast<float*>(KQ_s);   // (I + L)^-1 in f32, once K and Q have been consumed
+    float* Lf = Xf + 64 * LF_LD;                  // L in f32
+    uint8_t* Tp_s = reinterpret_cast<uint8_t*>(Lf);   // 64 rows x 128 B: (I + L)^-1 as the K-major operand, once L is dead
+    float* Yf = reinterpret_cast<float*>(Bop_s + 2 * NB * 8192);   // [3][16][YF_LD] block products in flight
+    float* g_s = Yf + 3 * 16 * YF_LD;
     float* gam_s = g_s + 64;
     float* eg_s = gam_s + 64;
     float* be_s = eg_s + 64;
@@ -105,8 +109,6 @@ __global__ void __launch_bounds__(PRE_THREADS) delta_prep_tc_kernel(
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     float* wtot = reinterpret_cast<float*>(tmem_slot + 2);
-    float* Xf = reinterpret_cast<float*>(KQ_s);   // (I + L)^-1 in f32, once K and Q have been consumed
-    float* Yf = Xf + 64 * LF_LD;                  // [3][16][YF_LD] block products in flight
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int chunk = blockIdx.x, chain = blockIdx.y;
@@ -274,10 +276,9 @@ __global__ void __launch_bounds__(PRE_THREADS) delta_prep_tc_kernel(
                     const int i = cc * 32 + j;
                     a[j] = i <= t ? __expf(gt - g_s[i]) * __uint_as_float(r[j]) : 0.0f;
                 }
-                // staged in the (still unused) T region, 16-byte chunks XOR-swizzled by row, for a coalesced copy-out
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
-                    *reinterpret_cast<uint4*>(Tp_s + t * 128 + (((cc * 4 + j) ^ (t & 7)) << 4)) = tc::pack8_bf16(a + 8 * j);
+                    *reinterpret_cast<uint4*>(out.AA + (tix * 64 + t) * 64 + cc * 32 + j * 8) = tc::pack8_bf16(a + 8 * j);
             }
         }
     }
@@ -307,14 +308,6 @@ __global__ void __launch_bounds__(PRE_THREADS) delta_prep_tc_kernel(
         }
 #pragma unroll
         for (int t = 0; t < 16; ++t) Xf[(I * 16 + t) * LF_LD + I * 16 + jj] = x[t];
-    } else {
-        // meanwhile threads 64-127 write the A tile out, 128 contiguous bytes per row
-#pragma unroll
-        for (int it = 0; it < 8; ++it) {
-            const int idx = (tid - 64) + it * 64, t = idx >> 3, jc = idx & 7;
-            *reinterpret_cast<uint4*>(out.AA + (tix * 64 + t) * 64 + jc * 8) =
-                *reinterpret_cast<const uint4*>(Tp_s + t * 128 + ((jc ^ (t & 7)) << 4));
-        }
     }
     __syncthreads();
 #pragma unroll
@@ -1237,15 +1230,6 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
     if (warp == 0) tc::tmem_dealloc(tm, 512);
 }
 
-// f32 chunk-start states -> the bf16 tiles the backward loads (used when the forward's own copy is gone)
-__global__ void state_to_bf16_kernel(const float4* __restrict__ in, uint2* __restrict__ out, int64_t n4) {
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
-        const float4 x = in[i];
-        const __nv_bfloat162 a = __floats2bfloat162_rn(x.x, x.y), b = __floats2bfloat162_rn(x.z, x.w);
-        out[i] = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
-    }
-}
-
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -1304,7 +1288,6 @@ static size_t carve_tiles(char* w, int64_t n_tiles, bool full, Tiles* t) {
         z.QKo = (__nv_bfloat16*)take(bcc);
         z.GV = (float*)take(bv);
         z.BE = (float*)take(bv);
-        z.S0B = (__nv_bfloat16*)take(al((size_t)n_tiles * DH * DH * 2));
     }
     if (t) *t = z;
     return (size_t)(p - w);
@@ -1325,7 +1308,9 @@ static int run_prepass(asca_ctx* ctx, const void* q, const void* k, const void* 
 
 // Forward for bf16 q,k,v (dh = 128). o is bf16. When checkpoints are requested (a backward will
 // follow) the pre-pass also writes the backward-only tiles into a context-owned buffer keyed by
-// the checkpoint pointer, so that the backward does not repeat the pre-pass.
+// the checkpoint pointer, so that the backward does not repeat the pre-pass. In this mode the
+// checkpoint buffer holds the chunk-start states rounded to bf16, (B, H, n_chunks, DH, DH) row-major
+// in its first half: the backward loads them by TMA as tensor-core operands.
 int forward(asca_ctx* ctx, const void* q, const void* k, const void* v, const float* alpha, const float* beta,
             int64_t B, int64_t T, int64_t H, void* o, const float* s_init, float* s_final, float* ckpt) {
     const int64_t n_chunks = (T + C - 1) / C, chains = B * H, n_tiles = chains * n_chunks;
@@ -1362,7 +1347,7 @@ int forward(asca_ctx* ctx, const void* q, const void* k, const void* v, const fl
         asca_span sp(ctx, "delta_fwd_tc_kernel");
         kern<<<(unsigned)chains, CH_THREADS, CH_SMEM, ctx->stream>>>(mWQ, mUV, mKW, mAA, t.GC, (int)T, (int)H,
                                                                     (int)n_chunks, (__nv_bfloat16*)o, s_init, s_final,
-                                                                    ckpt, keep ? t.S0B : nullptr, ctx->err_word);
+                                                                    nullptr, reinterpret_cast<__nv_bfloat16*>(ckpt), ctx->err_word);
     }
     ASCA_CHECK_LAUNCH(ctx);
     if (keep) {
@@ -1392,20 +1377,13 @@ int backward(asca_ctx* ctx, const void* q, const void* k, const void* v, const f
         char* w = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(ws) + 1023) & ~(uintptr_t)1023);
         carve_tiles(w, n_tiles, true, &t);
         ASCA_TRY(run_prepass(ctx, q, k, v, alpha, beta, T, H, n_chunks, chains, t));
-        const int64_t n4 = n_tiles * DH * DH / 4;
-        {
-            asca_span sp(ctx, "state_to_bf16_kernel");
-            state_to_bf16_kernel<<<(unsigned)std::min<int64_t>((n4 + 255) / 256, 148 * 16), 256, 0, ctx->stream>>>(
-                reinterpret_cast<const float4*>(ckpt), reinterpret_cast<uint2*>(t.S0B), n4);
-        }
-        ASCA_CHECK_LAUNCH(ctx);
     }
     CUtensorMap mWQ, mBK, mKW, mKR, mQR, mDO, mAA, mTP, mS0;
     bool ok = make_map(&mWQ, t.WQ, n_tiles * 128, DH, 64, 64) && make_map(&mBK, t.BK, n_tiles * 64, DH, 64, 64) &&
               make_map(&mKW, t.KW, n_tiles * 64, DH, 64, 64) && make_map(&mKR, t.KR, n_tiles * 64, DH, 64, 64) &&
               make_map(&mQR, t.QR, n_tiles * 64, DH, 64, 64) && make_map(&mDO, d_o, B * T, H * DH, 64, 64) &&
               make_map(&mAA, t.AA, n_tiles * 64, 64, 64, 64) && make_map(&mTP, t.TP, n_tiles * 64, 64, 64, 64) &&
-              make_map(&mS0, t.S0B, n_tiles * DH, DH, 64, 128);
+              make_map(&mS0, ckpt, n_tiles * DH, DH, 64, 128);
     if (!ok) return asca_fail(ctx, ASCA_ERR_CUDA, "delta_tc: cuTensorMapEncodeTiled failed");
     ASCA_CUDA(ctx, cudaFuncSetAttribute(delta_bwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)BW_SMEM));
     {

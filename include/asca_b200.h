@@ -141,6 +141,9 @@ int asca_adamw_host(asca_ctx* ctx, float* p, const float* g, float* m, float* v,
  *             boundary, layout (B, H, ceil(T/chunk), dh, dh); entry c is S before token
  *             c*chunk. This replaces the reference's per-step state history
  *             ((T+1)*dh*dh per chain) and is what asca_delta_bwd recomputes from.
+ *             With dtype ASCA_BF16, dh = 128 and chunk = 64 (the tensor-core kernels) the same
+ *             states are stored rounded to bf16, same layout, in the first half of the buffer;
+ *             either way the buffer is meant to be handed back to asca_delta_bwd unchanged.
  *   s_init  : nullable, (B, H, dh, dh) f32 initial state (continuing a prefix); NULL = 0. */
 int64_t asca_delta_ckpt_floats(int64_t B, int64_t T, int64_t H, int64_t dh, int64_t chunk);
 int asca_delta_fwd(asca_ctx* ctx, const void* q, const void* k, const void* v, const float* alpha,
