@@ -196,3 +196,69 @@ def moe_step(gpu, x, ids, w1, b1, w2, b2, F, E):
     gpu._call("asca_moe_step", gpu._ctx, _p(x), _p(ids), _p(w1), _p(b1), _p(w2), _p(b2), _i64(x.shape[0]),
               _i64(x.shape[1]), _i64(F), _i64(E), C.c_int(_dt(w1)), _p(out))
     return out
+
+
+class DeltaHostPipeline:
+    """Delta-rule forward + BPTT for sequences that live in pinned host memory.
+
+    The op is independent per sequence, so the step is cut into one stage per sequence and the
+    stages are pipelined over three streams: the host->device copy of sequence s+1, the kernels
+    of sequence s and the device->host copy of sequence s-1 run at the same time (PCIe is full
+    duplex). ``depth`` device slots bound the memory held: each slot has room for one
+    sequence's inputs, checkpoints and outputs.
+
+    All host tensors must be pinned; q, k, v, d_o in one dtype (f32 or bf16), the rest f32.
+    """
+
+    def __init__(self, gpu: Gpu, T, H, dh, chunk=64, dtype=torch.bfloat16, depth=3):
+        self.gpu, self.T, self.H, self.dh, self.chunk, self.depth = gpu, T, H, dh, chunk, depth
+        dev = torch.device("cuda", gpu.device)
+        self.dev = dev
+        d = H * dh
+        f = dict(dtype=torch.float32, device=dev)
+        a = dict(dtype=dtype, device=dev)
+        self.slots = []
+        for _ in range(depth):
+            self.slots.append(dict(
+                q=torch.empty((T, d), **a), k=torch.empty((T, d), **a), v=torch.empty((T, d), **a),
+                d_o=torch.empty((T, d), **a), alpha=torch.empty((T, H), **f), beta=torch.empty((T, H), **f),
+                qn=torch.empty((T, H), **f), kn=torch.empty((T, H), **f), o=torch.empty((T, d), **a),
+                ckpt=torch.empty(delta_ckpt_floats(gpu, 1, T, H, dh, chunk), **f),
+                d_qkv=torch.empty((T, 3 * d), **f), d_gate=torch.empty((T, 2 * H), **f),
+                computed=torch.cuda.Event(), drained=torch.cuda.Event()))
+        self.s_in, self.s_run, self.s_out = (torch.cuda.Stream(dev) for _ in range(3))
+
+    def run(self, q, k, v, alpha, beta, qnorm, knorm, d_o, o, d_qkv, d_gate, B):
+        """Host in, host out; returns after every result has landed in o, d_qkv, d_gate."""
+        T, H, dh, gpu = self.T, self.H, self.dh, self.gpu
+        for x in (q, k, v, alpha, beta, qnorm, knorm, d_o, o, d_qkv, d_gate):
+            assert not x.is_cuda and x.is_pinned() and x.shape[0] == B * T, "expected pinned host tensors of B*T rows"
+        for s in range(B):
+            sl = self.slots[s % self.depth]
+            rows = slice(s * T, (s + 1) * T)
+            with torch.cuda.stream(self.s_in):
+                if s >= self.depth:
+                    self.s_in.wait_event(sl["computed"])      # the slot's inputs have been consumed
+                for name, src in (("q", q), ("k", k), ("v", v), ("alpha", alpha), ("beta", beta), ("qn", qnorm),
+                                  ("kn", knorm), ("d_o", d_o)):
+                    sl[name].copy_(src[rows], non_blocking=True)
+                loaded = self.s_in.record_event()
+            with torch.cuda.stream(self.s_run):
+                self.s_run.wait_event(loaded)
+                if s >= self.depth:
+                    self.s_run.wait_event(sl["drained"])      # the slot's outputs have been copied out
+                gpu.use_torch_stream()
+                delta_fwd(gpu, sl["q"], sl["k"], sl["v"], sl["alpha"], sl["beta"], 1, T, H, dh, chunk=self.chunk,
+                          out=sl["o"], ckpt=sl["ckpt"])
+                delta_bwd(gpu, sl["q"], sl["k"], sl["v"], sl["alpha"], sl["beta"], sl["qn"], sl["kn"], sl["d_o"],
+                          sl["ckpt"], 1, T, H, dh, chunk=self.chunk, d_qkv=sl["d_qkv"], d_gate=sl["d_gate"])
+                sl["computed"].record(self.s_run)
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(sl["computed"])
+                o[rows].copy_(sl["o"], non_blocking=True)
+                d_qkv[rows].copy_(sl["d_qkv"], non_blocking=True)
+                d_gate[rows].copy_(sl["d_gate"], non_blocking=True)
+                sl["drained"].record(self.s_out)
+        self.s_out.synchronize()
+        self.s_run.synchronize()
+        gpu.use_torch_stream()   # back on the caller's stream

@@ -49,7 +49,7 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """SM clock and throttle reasons sampled every 20 ms (NVML, read-only) while the timed region runs."""
+    """SM clock and throttle reasons sampled every 2 ms (NVML, read-only) while the timed region runs."""
 
     REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
@@ -94,7 +94,7 @@ class ClockSampler:
                 self.mask |= int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.h))
             except Exception:  # noqa: BLE001
                 pass
-            time.sleep(0.02)
+            time.sleep(0.002)
 
     def stop(self):
         if self._th is None:
@@ -271,19 +271,14 @@ def run_ours(args):
         dqkv_h = torch.empty((n, 3 * d), dtype=torch.float32).pin_memory()
         dgate_h = torch.empty((n, 2 * h), dtype=torch.float32).pin_memory()
 
+        pipe = ops.DeltaHostPipeline(gpu, t, h, dh, chunk=CHUNK, dtype=torch.bfloat16)
+
         def e2e_step():
-            dq_, dk_, dv_, da_, db_, dqn_, dkn_, ddo_ = (x.to(dev, non_blocking=True) for x in hp)
-            ops.delta_fwd(gpu, dq_, dk_, dv_, da_, db_, b, t, h, dh, chunk=CHUNK, out=o, ckpt=ckpt)
-            ops.delta_bwd(gpu, dq_, dk_, dv_, da_, db_, dqn_, dkn_, ddo_, ckpt, b, t, h, dh, chunk=CHUNK, d_qkv=d_qkv,
-                          d_gate=d_gate)
-            o_h.copy_(o, non_blocking=True)
-            dqkv_h.copy_(d_qkv, non_blocking=True)
-            dgate_h.copy_(d_gate, non_blocking=True)
-            torch.cuda.synchronize()
+            pipe.run(hp[0], hp[1], hp[2], hp[3], hp[4], hp[5], hp[6], hp[7], o_h, dqkv_h, dgate_h, b)
 
         h2d = sum(x.numel() * x.element_size() for x in hp)
         d2h = sum(x.numel() * x.element_size() for x in (o_h, dqkv_h, dgate_h))
-        api = "asca_b200.ops (device-pointer C ABI) with pinned host copies"
+        api = "asca_b200.ops.DeltaHostPipeline (device-pointer C ABI; per-sequence copy/compute/copy pipeline from pinned host memory)"
     else:
         # f32 mode: the host-pointer API with the reference's call shape (Gpu.delta_scan + Gpu.delta_bwd_dev)
         hq, hk, hv, ha, hb, hqn, hkn, hdo = (x.numpy() for x in pin)
@@ -356,7 +351,7 @@ def run_ours(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--dtype", default="bf16", choices=["f32", "bf16"])
