@@ -324,6 +324,14 @@ class Model:
         gpu.lib.asca_model_num_params.restype = C.c_int64
         self.n = int(gpu.lib.asca_model_num_params(h))
 
+    def set_compute(self, dtype):
+        """F32 (default) or BF16: tensor-core products on a bf16 copy of the weights, f32 everything else."""
+        self.gpu._call("asca_model_set_compute", self.gpu._ctx, self._h, C.c_int(dtype))
+
+    def params_changed(self):
+        """Tell the model that the flat parameter buffer was written through :meth:`buffers`."""
+        self.gpu._call("asca_model_params_changed", self._h)
+
     def set_params(self, params):
         params = _as_f32(params)
         assert params.size == self.n

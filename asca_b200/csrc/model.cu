@@ -139,10 +139,149 @@ struct asca_model {
     int64_t vocab, d, H, L, E, F, n_params;
     int64_t embed, head;
     std::vector<Lyr> lay;
+    // offsets of the same tensors in the bf16 copy, each rounded up to 8 elements (16 bytes: TMA base alignment)
+    std::vector<Lyr> lay16;
+    int64_t embed16 = 0, head16 = 0, n16 = 0;
+    std::vector<int64_t> seg16;
     std::vector<int64_t> seg_off;   // tensor offsets in parameter order, + total
     float *params = nullptr, *grads = nullptr, *m = nullptr, *v = nullptr;
     uint32_t adam_counter = 0;
+    int compute = ASCA_F32;              // ASCA_BF16: tensor-core products on a bf16 copy of the weights
+    __nv_bfloat16* params16 = nullptr;   // refreshed from the f32 master copy whenever that changed
+    bool params16_stale = true;
 };
+
+// ---------------------------------------------------------------------------------------------
+// bf16 compute mode: the dataflow of Model::forward / Model::backward (rust/src/model.rs:631-700,
+// :744-794) with every product on the tensor cores. The residual stream, norms, gates, the
+// recurrent state, the loss, the gradients and the master weights stay f32; what a product reads
+// is bf16 (weights from a bf16 copy of the master buffer, activations written as bf16 by the
+// kernel that produces them or by a cast pass).
+static int forward_backward_bf16(asca_ctx* ctx, asca_model* m, const uint32_t* ids_h, const uint32_t* tg_h, int64_t B,
+                                 int64_t T, float* loss_h, float* logits_h) {
+    typedef __nv_bfloat16 bf16;
+    const int64_t N = B * T, d = m->d, H = m->H, dh = d / H, E = m->E, F = m->F, V = m->vocab, L = m->L;
+    const int64_t CH = 64;
+    const int BF = ASCA_BF16;
+    if (!m->params16) {
+        if (cudaMalloc((void**)&m->params16, (size_t)m->n16 * 2) != cudaSuccess)
+            return asca_fail(ctx, ASCA_ERR_OOM, "model: cannot allocate the bf16 weight copy");
+        m->params16_stale = true;
+    }
+    if (m->params16_stale) {
+        if (m->n16 == m->n_params) {   // no padding anywhere: one pass over the flat buffer
+            ASCA_TRY(asca_cast_bf16(ctx, m->params, m->params16, m->n_params));
+        } else {
+            for (size_t i = 0; i + 1 < m->seg_off.size(); ++i)
+                ASCA_TRY(asca_cast_bf16(ctx, m->params + m->seg_off[i], m->params16 + m->seg16[i], m->seg_off[i + 1] - m->seg_off[i]));
+        }
+        m->params16_stale = false;
+    }
+    const float* P = m->params;
+    const bf16* W = m->params16;
+    float* G = m->grads;
+    Bufs bf(ctx);
+    auto h16 = [&](int64_t n) { return (bf16*)bf.f((n + 1) / 2); };
+    uint32_t* ids = (uint32_t*)bf.f(N);
+    uint32_t* tg = (uint32_t*)bf.f(N);
+    int32_t* perm = (int32_t*)bf.f(N);
+    int32_t* offs = (int32_t*)bf.f(E + 1);
+    ASCA_REQUIRE(ctx, ids && tg && perm && offs, "model_forward_backward: out of memory");
+    ASCA_CUDA(ctx, cudaMemcpyAsync(ids, ids_h, (size_t)N * 4, cudaMemcpyHostToDevice, ctx->stream));
+    ASCA_CUDA(ctx, cudaMemcpyAsync(tg, tg_h, (size_t)N * 4, cudaMemcpyHostToDevice, ctx->stream));
+    ASCA_TRY(asca_moe_dispatch(ctx, ids, N, E, perm, offs, nullptr));
+
+    struct Act {
+        bf16 *x_in, *q, *k, *v, *o, *xn, *hid_p;
+        float *qn, *kn, *al, *be, *ckpt, *x_mid, *pre_p;
+    };
+    std::vector<Act> acts(L);
+    const int64_t nck = asca_delta_ckpt_floats(B, T, H, dh, CH);
+    float* x = bf.f(N * d);
+    float* qkv = bf.f(N * 3 * d);
+    float* gate = bf.f(N * 2 * H);
+    float* y = bf.f(N * d);
+    float* mo = bf.f(N * d);
+    ASCA_REQUIRE(ctx, x && qkv && gate && y && mo, "model_forward_backward: out of memory");
+    ASCA_TRY(asca_embed_fwd(ctx, P + m->embed, ids, N, d, x));
+    for (int64_t li = 0; li < L; ++li) {
+        const Lyr& w = m->lay[li];
+        const Lyr& w16 = m->lay16[li];
+        Act& a = acts[li];
+        a.x_in = h16(N * d); a.q = h16(N * d); a.k = h16(N * d); a.v = h16(N * d); a.o = h16(N * d); a.xn = h16(N * d);
+        a.hid_p = h16(N * F);
+        a.qn = bf.f(N * H); a.kn = bf.f(N * H); a.al = bf.f(N * H); a.be = bf.f(N * H);
+        a.ckpt = bf.f(nck); a.x_mid = bf.f(N * d); a.pre_p = bf.f(N * F);
+        ASCA_REQUIRE(ctx, a.x_in && a.q && a.k && a.v && a.o && a.xn && a.hid_p && a.qn && a.kn && a.al && a.be && a.ckpt &&
+                              a.x_mid && a.pre_p, "model_forward_backward: out of memory");
+        ASCA_TRY(asca_cast_bf16(ctx, x, a.x_in, N * d));
+        ASCA_TRY(asca_gemm(ctx, ASCA_NN, N, 3 * d, d, a.x_in, d, W + w16.w_qkv, 3 * d, qkv, 3 * d, P + w.b_qkv, 0, BF));
+        ASCA_TRY(asca_gemm(ctx, ASCA_NN, N, 2 * H, d, a.x_in, d, W + w16.w_gate, 2 * H, gate, 2 * H, P + w.b_gate, 0, BF));
+        ASCA_TRY(asca_delta_prep_bf16(ctx, qkv, gate, N, H, dh, a.q, a.k, a.v, a.qn, a.kn, a.al, a.be));
+        ASCA_TRY(asca_delta_fwd(ctx, a.q, a.k, a.v, a.al, a.be, B, T, H, dh, CH, BF, a.o, nullptr, nullptr, a.ckpt));
+        ASCA_TRY(asca_gemm(ctx, ASCA_NN, N, d, d, a.o, d, W + w16.w_o, d, y, d, P + w.b_o, 0, BF));
+        ASCA_TRY(asca_residual_rmsnorm_bf16(ctx, x, y, a.x_mid, a.xn, N, d, 1e-6f));
+        ASCA_TRY(asca_moe_fwd(ctx, a.xn, W + w16.w1, P + w.b1, W + w16.w2, P + w.b2, perm, offs, N, d, F, E, BF, mo, a.pre_p,
+                              a.hid_p));
+        ASCA_TRY(asca_residual_rmsnorm(ctx, a.x_mid, mo, x, nullptr, N, d, 1e-6f));
+    }
+    bf16* h_final = h16(N * d);
+    float* logits = bf.f(N * V);
+    float* dlogits = bf.f(N * V);
+    bf16* dl16 = h16(N * V);
+    float* loss_d = bf.f(1);
+    ASCA_REQUIRE(ctx, h_final && logits && dlogits && dl16 && loss_d, "model_forward_backward: out of memory");
+    ASCA_TRY(asca_residual_rmsnorm_bf16(ctx, x, nullptr, nullptr, h_final, N, d, 1e-6f));
+    ASCA_TRY(asca_gemm(ctx, ASCA_NN, N, V, d, h_final, d, W + m->head16, V, logits, V, nullptr, 0, BF));
+    if (logits_h) ASCA_CUDA(ctx, cudaMemcpyAsync(logits_h, logits, (size_t)N * V * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    ASCA_TRY(asca_cross_entropy(ctx, logits, tg, N, V, dlogits, loss_d));
+    ASCA_CUDA(ctx, cudaMemcpyAsync(loss_h, loss_d, 4, cudaMemcpyDeviceToHost, ctx->stream));
+    ASCA_TRY(asca_cast_bf16(ctx, dlogits, dl16, N * V));
+    ASCA_TRY(asca_gemm(ctx, ASCA_TN, d, V, N, h_final, d, dl16, V, G + m->head, V, nullptr, 1, BF));
+    float* dh_ = bf.f(N * d);
+    float* dx = bf.f(N * d);
+    float* dxn = bf.f(N * d);
+    float* d_moe = bf.f(N * d);
+    float* d_o = bf.f(N * d);
+    float* d_qkv = bf.f(N * 3 * d);
+    float* d_gate = bf.f(N * 2 * H);
+    bf16* dx16 = h16(N * d);
+    bf16* do16 = h16(N * d);
+    bf16* dqkv16 = h16(N * 3 * d);
+    bf16* dg16 = h16(N * 2 * H);
+    ASCA_REQUIRE(ctx, dh_ && dx && dxn && d_moe && d_o && d_qkv && d_gate && dx16 && do16 && dqkv16 && dg16,
+                 "model_forward_backward: out of memory");
+    ASCA_TRY(asca_gemm(ctx, ASCA_NT, N, d, V, dl16, V, W + m->head16, V, dh_, d, nullptr, 0, BF));
+    ASCA_TRY(asca_rmsnorm_bwd(ctx, x, dh_, dx, N, d, 1e-6f));
+    const int64_t blocks_nd = ceil_div64(N * d, 256);
+    for (int64_t li = L - 1; li >= 0; --li) {
+        const Lyr& w = m->lay[li];
+        const Lyr& w16 = m->lay16[li];
+        Act& a = acts[li];
+        ASCA_TRY(asca_moe_bwd_acc(ctx, a.xn, W + w16.w1, W + w16.w2, a.pre_p, a.hid_p, dx, perm, offs, N, d, F, E, BF, G + w.w1,
+                                  G + w.b1, G + w.w2, G + w.b2, dxn));
+        ASCA_TRY(asca_rmsnorm_bwd(ctx, a.x_mid, dxn, d_moe, N, d, 1e-6f));
+        add_kernel<<<(unsigned)blocks_nd, 256, 0, ctx->stream>>>(dx, d_moe, dx, N * d);   // d_mid
+        ctx->launches++;
+        ASCA_TRY(asca_cast_bf16(ctx, dx, dx16, N * d));
+        ASCA_TRY(asca_gemm(ctx, ASCA_NT, N, d, d, dx16, d, W + w16.w_o, d, d_o, d, nullptr, 0, BF));
+        ASCA_TRY(asca_cast_bf16(ctx, d_o, do16, N * d));
+        ASCA_TRY(asca_gemm(ctx, ASCA_TN, d, d, N, a.o, d, dx16, d, G + w.w_o, d, nullptr, 1, BF));
+        ASCA_TRY(asca_colsum(ctx, dx, d, N, d, G + w.b_o, 1));
+        ASCA_TRY(asca_delta_bwd(ctx, a.q, a.k, a.v, a.al, a.be, a.qn, a.kn, do16, a.ckpt, B, T, H, dh, CH, BF, d_qkv, d_gate));
+        ASCA_TRY(asca_cast_bf16(ctx, d_qkv, dqkv16, N * 3 * d));
+        ASCA_TRY(asca_cast_bf16(ctx, d_gate, dg16, N * 2 * H));
+        ASCA_TRY(asca_gemm(ctx, ASCA_TN, d, 3 * d, N, a.x_in, d, dqkv16, 3 * d, G + w.w_qkv, 3 * d, nullptr, 1, BF));
+        ASCA_TRY(asca_colsum(ctx, d_qkv, 3 * d, N, 3 * d, G + w.b_qkv, 1));
+        ASCA_TRY(asca_gemm(ctx, ASCA_TN, d, 2 * H, N, a.x_in, d, dg16, 2 * H, G + w.w_gate, 2 * H, nullptr, 1, BF));
+        ASCA_TRY(asca_colsum(ctx, d_gate, 2 * H, N, 2 * H, G + w.b_gate, 1));
+        ASCA_TRY(asca_gemm(ctx, ASCA_NT, N, d, 3 * d, dqkv16, 3 * d, W + w16.w_qkv, 3 * d, dx, d, nullptr, 1, BF));
+        ASCA_TRY(asca_gemm(ctx, ASCA_NT, N, d, 2 * H, dg16, 2 * H, W + w16.w_gate, 2 * H, dx, d, nullptr, 1, BF));
+    }
+    ASCA_TRY(asca_embed_bwd(ctx, dx, ids, N, d, V, G + m->embed));
+    ASCA_CUDA(ctx, cudaGetLastError());
+    return asca_ctx_sync(ctx);
+}
 
 extern "C" {
 
@@ -196,26 +335,31 @@ int asca_model_create(asca_ctx* ctx, int64_t vocab, int64_t d, int64_t H, int64_
         return asca_fail(ctx, ASCA_ERR_UNSUPPORTED, "model_create: d/H must be 16, 32, 64 or 128");
     asca_model* m = new asca_model();
     m->vocab = vocab; m->d = d; m->H = H; m->L = L; m->E = E; m->F = F;
-    int64_t o = 0;
-    auto take = [&](int64_t n) {
+    int64_t o = 0, o16 = 0;
+    auto take = [&](int64_t n, int64_t* at16) {
         const int64_t at = o;
         m->seg_off.push_back(at);
+        m->seg16.push_back(o16);
+        *at16 = o16;
         o += n;
+        o16 += (n + 7) & ~(int64_t)7;
         return at;
     };
-    m->embed = take(vocab * d);
-    m->head = take(d * vocab);
+    m->embed = take(vocab * d, &m->embed16);
+    m->head = take(d * vocab, &m->head16);
     for (int64_t i = 0; i < L; ++i) {
-        Lyr y;
-        y.w_qkv = take(d * 3 * d); y.b_qkv = take(3 * d);
-        y.w_gate = take(d * 2 * H); y.b_gate = take(2 * H);
-        y.w_o = take(d * d); y.b_o = take(d);
-        y.w1 = take(d * E * F); y.b1 = take(E * F);
-        y.w2 = take(E * F * d); y.b2 = take(d);
+        Lyr y, z;
+        y.w_qkv = take(d * 3 * d, &z.w_qkv); y.b_qkv = take(3 * d, &z.b_qkv);
+        y.w_gate = take(d * 2 * H, &z.w_gate); y.b_gate = take(2 * H, &z.b_gate);
+        y.w_o = take(d * d, &z.w_o); y.b_o = take(d, &z.b_o);
+        y.w1 = take(d * E * F, &z.w1); y.b1 = take(E * F, &z.b1);
+        y.w2 = take(E * F * d, &z.w2); y.b2 = take(d, &z.b2);
         m->lay.push_back(y);
+        m->lay16.push_back(z);
     }
     m->seg_off.push_back(o);
     m->n_params = o;
+    m->n16 = o16;
     float** bufs[4] = {&m->params, &m->grads, &m->m, &m->v};
     for (auto b : bufs) {
         if (cudaMalloc((void**)b, (size_t)o * 4) != cudaSuccess) {
@@ -233,6 +377,7 @@ int asca_model_destroy(asca_ctx* ctx, asca_model* m) {
     if (ctx) cudaStreamSynchronize(ctx->stream);
     for (float* b : {m->params, m->grads, m->m, m->v})
         if (b) cudaFree(b);
+    if (m->params16) cudaFree(m->params16);
     delete m;
     return ASCA_OK;
 }
@@ -248,11 +393,25 @@ int asca_model_buffers(asca_model* m, float** params, float** grads, float** ada
     return ASCA_OK;
 }
 
+int asca_model_set_compute(asca_ctx* ctx, asca_model* m, int dtype) {
+    if (!ctx || !m) return ASCA_ERR_ARG;
+    ASCA_REQUIRE(ctx, dtype == ASCA_F32 || dtype == ASCA_BF16, "model_set_compute: unknown dtype %d", dtype);
+    m->compute = dtype;
+    return ASCA_OK;
+}
+
+int asca_model_params_changed(asca_model* m) {
+    if (!m) return ASCA_ERR_ARG;
+    m->params16_stale = true;
+    return ASCA_OK;
+}
+
 int asca_model_set_params_host(asca_ctx* ctx, asca_model* m, const float* params) {
     if (!ctx || !m || !params) return ASCA_ERR_ARG;
     m->adam_counter = 0;
     ASCA_CUDA(ctx, cudaMemsetAsync(m->m, 0, (size_t)m->n_params * 4, ctx->stream));
     ASCA_CUDA(ctx, cudaMemsetAsync(m->v, 0, (size_t)m->n_params * 4, ctx->stream));
+    m->params16_stale = true;
     return asca_memcpy_h2d(ctx, m->params, params, (size_t)m->n_params * 4);
 }
 
@@ -277,6 +436,7 @@ int asca_model_forward_backward_host(asca_ctx* ctx, asca_model* m, const uint32_
     const int64_t CH = 64;
     for (int64_t i = 0; i < N; ++i)
         ASCA_REQUIRE(ctx, ids_h[i] < (uint32_t)V && tg_h[i] < (uint32_t)V, "model_forward_backward: id out of range");
+    if (m->compute == ASCA_BF16) return forward_backward_bf16(ctx, m, ids_h, tg_h, B, T, loss_h, logits_h);
     float* P = m->params;
     float* G = m->grads;
     Bufs bf(ctx);
@@ -341,12 +501,7 @@ int asca_model_forward_backward_host(asca_ctx* ctx, asca_model* m, const uint32_
     float* d_o = bf.f(N * d);
     float* d_qkv = bf.f(N * 3 * d);
     float* d_gate = bf.f(N * 2 * H);
-    float* tmp_w1 = bf.f(d * E * F);
-    float* tmp_b1 = bf.f(E * F);
-    float* tmp_w2 = bf.f(E * F * d);
-    float* tmp_b2 = bf.f(d);
-    ASCA_REQUIRE(ctx, dh_ && dx && dxn && d_moe && d_o && d_qkv && d_gate && tmp_w1 && tmp_b1 && tmp_w2 && tmp_b2,
-                 "model_forward_backward: out of memory");
+    ASCA_REQUIRE(ctx, dh_ && dx && dxn && d_moe && d_o && d_qkv && d_gate, "model_forward_backward: out of memory");
     ASCA_TRY(asca_gemm(ctx, ASCA_NT, N, d, V, dlogits, V, P + m->head, V, dh_, d, nullptr, 0, ASCA_F32));
     ASCA_TRY(asca_rmsnorm_bwd(ctx, x, dh_, dx, N, d, 1e-6f));   // x = x_out of the last layer
     const int64_t blocks_nd = ceil_div64(N * d, 256);
@@ -354,13 +509,8 @@ int asca_model_forward_backward_host(asca_ctx* ctx, asca_model* m, const uint32_
         const Lyr& w = m->lay[li];
         Act& a = acts[li];
         // HashMoe::backward: gradients accumulate into the flat buffer
-        ASCA_TRY(asca_moe_bwd(ctx, a.xn, P + w.w1, P + w.w2, a.pre_p, a.hid_p, dx, perm, offs, N, d, F, E, ASCA_F32, tmp_w1,
-                              tmp_b1, tmp_w2, tmp_b2, dxn));
-        add_kernel<<<(unsigned)ceil_div64(d * E * F, 256), 256, 0, ctx->stream>>>(G + w.w1, tmp_w1, G + w.w1, d * E * F);
-        add_kernel<<<(unsigned)ceil_div64(E * F, 256), 256, 0, ctx->stream>>>(G + w.b1, tmp_b1, G + w.b1, E * F);
-        add_kernel<<<(unsigned)ceil_div64(E * F * d, 256), 256, 0, ctx->stream>>>(G + w.w2, tmp_w2, G + w.w2, E * F * d);
-        add_kernel<<<(unsigned)ceil_div64(d, 256), 256, 0, ctx->stream>>>(G + w.b2, tmp_b2, G + w.b2, d);
-        ctx->launches += 4;
+        ASCA_TRY(asca_moe_bwd_acc(ctx, a.xn, P + w.w1, P + w.w2, a.pre_p, a.hid_p, dx, perm, offs, N, d, F, E, ASCA_F32,
+                                  G + w.w1, G + w.b1, G + w.w2, G + w.b2, dxn));
         ASCA_TRY(asca_rmsnorm_bwd(ctx, a.x_mid, dxn, d_moe, N, d, 1e-6f));
         add_kernel<<<(unsigned)blocks_nd, 256, 0, ctx->stream>>>(dx, d_moe, dx, N * d);   // d_mid
         ctx->launches++;
@@ -402,6 +552,7 @@ int asca_model_adamw_step(asca_ctx* ctx, asca_model* m, float lr, float beta1, f
         lr_t[i] = lr * sqrtf(bc1 / bc2);
         eps_t[i] = eps * sqrtf(bc2);
     }
+    m->params16_stale = true;
     return asca_adamw_segmented(ctx, m->params, m->grads, m->m, m->v, m->seg_off.data(), lr_t.data(), eps_t.data(), n_seg,
                                 beta1, beta2, lr * wd);
 }

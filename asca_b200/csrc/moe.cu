@@ -18,7 +18,7 @@ namespace {
 __global__ void __launch_bounds__(256) colsum_kernel(const float* __restrict__ src, int64_t ld,
                                                      const int32_t* __restrict__ row_idx,
                                                      const int32_t* __restrict__ offsets, int64_t rows_total,
-                                                     int cols, float* __restrict__ out, int64_t out_gstride) {
+                                                     int cols, float* __restrict__ out, int64_t out_gstride, int accumulate) {
     __shared__ float part[8][33];
     const int g = blockIdx.y;
     const int64_t lo = offsets ? offsets[g] : 0, hi = offsets ? offsets[g + 1] : rows_total;
@@ -36,7 +36,8 @@ __global__ void __launch_bounds__(256) colsum_kernel(const float* __restrict__ s
         float t = 0.0f;
 #pragma unroll
         for (int i = 0; i < 8; ++i) t += part[i][threadIdx.x];
-        out[(int64_t)g * out_gstride + c] = t;
+        float* o = out + (int64_t)g * out_gstride + c;
+        *o = accumulate ? *o + t : t;
     }
 }
 
@@ -120,8 +121,6 @@ int moe_fwd_tc(asca_ctx* ctx, const __nv_bfloat16* xn, const __nv_bfloat16* w1, 
     void* ws;
     ASCA_TRY(asca_workspace(ctx, align256((size_t)N * d * 2) + 256, &ws));
     __nv_bfloat16* xp = (__nv_bfloat16*)ws;
-    gather_rows_bf16_kernel<<<(unsigned)ceil_div64(N, 8), 256, 0, ctx->stream>>>(xn, perm, xp, N, (int)d);
-    ASCA_CHECK_LAUNCH(ctx);
     gemm_tc::Args a{};
     a.mode = ASCA_NN;
     a.A = xp; a.lda = d; a.a_rows = N; a.a_cols = d;
@@ -130,8 +129,6 @@ int moe_fwd_tc(asca_ctx* ctx, const __nv_bfloat16* xn, const __nv_bfloat16* w1, 
     a.bias = b1; a.bias_gstride = F;
     a.offsets = offsets; a.n_groups = (int)E; a.group_dim = gemm_tc::GROUP_M; a.total_rows = N;
     a.epi = gemm_tc::EPI_SILU; a.C2 = hid_p; a.ldc2 = F;
-    if (!gemm_tc::supported(a)) return ASCA_ERR_UNSUPPORTED;
-    ASCA_TRY(gemm_tc::launch(ctx, a));
     gemm_tc::Args b{};
     b.mode = ASCA_NN;
     b.A = hid_p; b.lda = F; b.a_rows = N; b.a_cols = F;
@@ -139,7 +136,11 @@ int moe_fwd_tc(asca_ctx* ctx, const __nv_bfloat16* xn, const __nv_bfloat16* w1, 
     b.C = out; b.ldc = d; b.N = (int)d; b.K = (int)F; b.c_idx = perm;
     b.bias = b2; b.bias_gstride = 0;
     b.offsets = offsets; b.n_groups = (int)E; b.group_dim = gemm_tc::GROUP_M; b.total_rows = N;
-    if (!gemm_tc::supported(b)) return ASCA_ERR_UNSUPPORTED;
+    // nothing is launched unless every product can run here: the caller falls back as a whole
+    if (!gemm_tc::supported(a) || !gemm_tc::supported(b)) return ASCA_ERR_UNSUPPORTED;
+    gather_rows_bf16_kernel<<<(unsigned)ceil_div64(N, 8), 256, 0, ctx->stream>>>(xn, perm, xp, N, (int)d);
+    ASCA_CHECK_LAUNCH(ctx);
+    ASCA_TRY(gemm_tc::launch(ctx, a));
     return gemm_tc::launch(ctx, b);
 }
 
@@ -147,7 +148,7 @@ int moe_fwd_tc(asca_ctx* ctx, const __nv_bfloat16* xn, const __nv_bfloat16* w1, 
 int moe_bwd_tc(asca_ctx* ctx, const __nv_bfloat16* xn, const __nv_bfloat16* w1, const __nv_bfloat16* w2,
                const float* pre_p, const __nv_bfloat16* hid_p, const float* dout, const int32_t* perm,
                const int32_t* offsets, int64_t N, int64_t d, int64_t F, int64_t E, float* d_w1, float* d_b1,
-               float* d_w2, float* d_b2, float* dxn) {
+               float* d_w2, float* d_b2, float* dxn, int acc) {
     cudaStream_t s = ctx->stream;
     const size_t b_xp = align256((size_t)N * d * 2), b_dp = align256((size_t)N * F * 4), b_dp16 = align256((size_t)N * F * 2);
     void* ws;
@@ -157,56 +158,48 @@ int moe_bwd_tc(asca_ctx* ctx, const __nv_bfloat16* xn, const __nv_bfloat16* w1, 
     __nv_bfloat16* dout_p = (__nv_bfloat16*)(w + b_xp);
     float* dpre_p = (float*)(w + 2 * b_xp);
     __nv_bfloat16* dpre16 = (__nv_bfloat16*)(w + 2 * b_xp + b_dp);
+    gemm_tc::Args g1{}, g2{}, g3{}, g4{};
+    // d_w2[eF+j, c] = sum_r hid_p[r,j] dout_p[r,c]
+    g1.mode = ASCA_TN;
+    g1.A = hid_p; g1.lda = F; g1.a_rows = N; g1.a_cols = F;
+    g1.B = dout_p; g1.ldb = d; g1.b_rows = N; g1.b_cols = d;
+    g1.C = d_w2; g1.ldc = d; g1.c_gstride = F * d; g1.M = (int)F; g1.N = (int)d; g1.accumulate = acc;
+    g1.offsets = offsets; g1.n_groups = (int)E; g1.group_dim = gemm_tc::GROUP_K; g1.total_rows = N;
+    // dpre_p[r,j] = (sum_c dout_p[r,c] W2[eF+j,c]) * silu'(pre_p[r,j]), plus a bf16 copy
+    g2.mode = ASCA_NT;
+    g2.A = dout_p; g2.lda = d; g2.a_rows = N; g2.a_cols = d;
+    g2.B = w2; g2.ldb = d; g2.b_rows = E * F; g2.b_cols = d; g2.b_goff_outer = (int)F;
+    g2.C = dpre_p; g2.ldc = F; g2.N = (int)F; g2.K = (int)d;
+    g2.offsets = offsets; g2.n_groups = (int)E; g2.group_dim = gemm_tc::GROUP_M; g2.total_rows = N;
+    g2.epi = gemm_tc::EPI_SILU_BWD; g2.aux = pre_p; g2.ldaux = F; g2.C2 = dpre16; g2.ldc2 = F;
+    // d_w1[c, eF+j] = sum_r xp[r,c] dpre16[r,j]
+    g3.mode = ASCA_TN;
+    g3.A = xp; g3.lda = d; g3.a_rows = N; g3.a_cols = d;
+    g3.B = dpre16; g3.ldb = F; g3.b_rows = N; g3.b_cols = F;
+    g3.C = d_w1; g3.ldc = E * F; g3.c_gstride = F; g3.M = (int)d; g3.N = (int)F; g3.accumulate = acc;
+    g3.offsets = offsets; g3.n_groups = (int)E; g3.group_dim = gemm_tc::GROUP_K; g3.total_rows = N;
+    // dxn[perm[r], c] = sum_j dpre16[r,j] W1[c, eF+j]
+    g4.mode = ASCA_NT;
+    g4.A = dpre16; g4.lda = F; g4.a_rows = N; g4.a_cols = F;
+    g4.B = w1; g4.ldb = E * F; g4.b_rows = d; g4.b_cols = E * F; g4.b_goff_inner = (int)F;
+    g4.C = dxn; g4.ldc = d; g4.N = (int)d; g4.K = (int)F; g4.c_idx = perm;
+    g4.offsets = offsets; g4.n_groups = (int)E; g4.group_dim = gemm_tc::GROUP_M; g4.total_rows = N;
+    // nothing is launched unless every product can run here: the caller falls back as a whole, and with
+    // `acc` a partial run followed by the fallback would add some gradients twice
+    if (!gemm_tc::supported(g1) || !gemm_tc::supported(g2) || !gemm_tc::supported(g3) || !gemm_tc::supported(g4))
+        return ASCA_ERR_UNSUPPORTED;
     gather_rows_bf16_kernel<<<(unsigned)ceil_div64(N, 8), 256, 0, s>>>(xn, perm, xp, N, (int)d);
     ASCA_CHECK_LAUNCH(ctx);
     gather_rows_f32_to_bf16_kernel<<<(unsigned)ceil_div64(N, 8), 256, 0, s>>>(dout, perm, dout_p, N, (int)d);
     ASCA_CHECK_LAUNCH(ctx);
-    colsum_kernel<<<dim3((unsigned)ceil_div64(d, 32), 1), 256, 0, s>>>(dout, d, nullptr, nullptr, N, (int)d, d_b2, 0);
+    colsum_kernel<<<dim3((unsigned)ceil_div64(d, 32), 1), 256, 0, s>>>(dout, d, nullptr, nullptr, N, (int)d, d_b2, 0, acc);
     ASCA_CHECK_LAUNCH(ctx);
-    {   // d_w2[eF+j, c] = sum_r hid_p[r,j] dout_p[r,c]
-        gemm_tc::Args a{};
-        a.mode = ASCA_TN;
-        a.A = hid_p; a.lda = F; a.a_rows = N; a.a_cols = F;
-        a.B = dout_p; a.ldb = d; a.b_rows = N; a.b_cols = d;
-        a.C = d_w2; a.ldc = d; a.c_gstride = F * d; a.M = (int)F; a.N = (int)d;
-        a.offsets = offsets; a.n_groups = (int)E; a.group_dim = gemm_tc::GROUP_K; a.total_rows = N;
-        if (!gemm_tc::supported(a)) return ASCA_ERR_UNSUPPORTED;
-        ASCA_TRY(gemm_tc::launch(ctx, a));
-    }
-    {   // dpre_p[r,j] = (sum_c dout_p[r,c] W2[eF+j,c]) * silu'(pre_p[r,j]), plus a bf16 copy
-        gemm_tc::Args a{};
-        a.mode = ASCA_NT;
-        a.A = dout_p; a.lda = d; a.a_rows = N; a.a_cols = d;
-        a.B = w2; a.ldb = d; a.b_rows = E * F; a.b_cols = d; a.b_goff_outer = (int)F;
-        a.C = dpre_p; a.ldc = F; a.N = (int)F; a.K = (int)d;
-        a.offsets = offsets; a.n_groups = (int)E; a.group_dim = gemm_tc::GROUP_M; a.total_rows = N;
-        a.epi = gemm_tc::EPI_SILU_BWD; a.aux = pre_p; a.ldaux = F; a.C2 = dpre16; a.ldc2 = F;
-        if (!gemm_tc::supported(a)) return ASCA_ERR_UNSUPPORTED;
-        ASCA_TRY(gemm_tc::launch(ctx, a));
-    }
-    colsum_kernel<<<dim3((unsigned)ceil_div64(F, 32), (unsigned)E), 256, 0, s>>>(dpre_p, F, nullptr, offsets, N, (int)F, d_b1, F);
+    ASCA_TRY(gemm_tc::launch(ctx, g1));
+    ASCA_TRY(gemm_tc::launch(ctx, g2));
+    colsum_kernel<<<dim3((unsigned)ceil_div64(F, 32), (unsigned)E), 256, 0, s>>>(dpre_p, F, nullptr, offsets, N, (int)F, d_b1, F, acc);
     ASCA_CHECK_LAUNCH(ctx);
-    {   // d_w1[c, eF+j] = sum_r xp[r,c] dpre16[r,j]
-        gemm_tc::Args a{};
-        a.mode = ASCA_TN;
-        a.A = xp; a.lda = d; a.a_rows = N; a.a_cols = d;
-        a.B = dpre16; a.ldb = F; a.b_rows = N; a.b_cols = F;
-        a.C = d_w1; a.ldc = E * F; a.c_gstride = F; a.M = (int)d; a.N = (int)F;
-        a.offsets = offsets; a.n_groups = (int)E; a.group_dim = gemm_tc::GROUP_K; a.total_rows = N;
-        if (!gemm_tc::supported(a)) return ASCA_ERR_UNSUPPORTED;
-        ASCA_TRY(gemm_tc::launch(ctx, a));
-    }
-    {   // dxn[perm[r], c] = sum_j dpre16[r,j] W1[c, eF+j]
-        gemm_tc::Args a{};
-        a.mode = ASCA_NT;
-        a.A = dpre16; a.lda = F; a.a_rows = N; a.a_cols = F;
-        a.B = w1; a.ldb = E * F; a.b_rows = d; a.b_cols = E * F; a.b_goff_inner = (int)F;
-        a.C = dxn; a.ldc = d; a.N = (int)d; a.K = (int)F; a.c_idx = perm;
-        a.offsets = offsets; a.n_groups = (int)E; a.group_dim = gemm_tc::GROUP_M; a.total_rows = N;
-        if (!gemm_tc::supported(a)) return ASCA_ERR_UNSUPPORTED;
-        ASCA_TRY(gemm_tc::launch(ctx, a));
-    }
-    return ASCA_OK;
+    ASCA_TRY(gemm_tc::launch(ctx, g3));
+    return gemm_tc::launch(ctx, g4);
 }
 
 }  // namespace
@@ -253,9 +246,9 @@ int asca_moe_fwd(asca_ctx* ctx, const void* xn, const void* w1, const float* b1,
     return ASCA_OK;
 }
 
-int asca_moe_bwd(asca_ctx* ctx, const void* xn, const void* w1, const void* w2, const float* pre_p, const void* hid_p,
-                 const float* dout, const int32_t* perm, const int32_t* offsets, int64_t N, int64_t d, int64_t F,
-                 int64_t E, int dtype, float* d_w1, float* d_b1, float* d_w2, float* d_b2, float* dxn) {
+static int moe_bwd_impl(asca_ctx* ctx, const void* xn, const void* w1, const void* w2, const float* pre_p, const void* hid_p,
+                        const float* dout, const int32_t* perm, const int32_t* offsets, int64_t N, int64_t d, int64_t F,
+                        int64_t E, int dtype, float* d_w1, float* d_b1, float* d_w2, float* d_b2, float* dxn, int acc) {
     if (!ctx) return ASCA_ERR_ARG;
     ASCA_REQUIRE(ctx, xn && w1 && w2 && pre_p && hid_p && dout && perm && offsets && d_w1 && d_b1 && d_w2 && d_b2 && dxn,
                  "moe_bwd: null pointer");
@@ -263,6 +256,7 @@ int asca_moe_bwd(asca_ctx* ctx, const void* xn, const void* w1, const void* w2, 
     ASCA_REQUIRE(ctx, dtype == ASCA_F32 || dtype == ASCA_BF16, "moe_bwd: unknown dtype");
     const int bf = dtype == ASCA_BF16;
     cudaStream_t s = ctx->stream;
+    if (N == 0 && acc) return ASCA_OK;
     if (N == 0) {
         ASCA_CUDA(ctx, cudaMemsetAsync(d_w1, 0, (size_t)(d * E * F) * 4, s));
         ASCA_CUDA(ctx, cudaMemsetAsync(d_w2, 0, (size_t)(d * E * F) * 4, s));
@@ -272,7 +266,7 @@ int asca_moe_bwd(asca_ctx* ctx, const void* xn, const void* w1, const void* w2, 
     }
     if (bf && tc_shapes_ok(d, F)) {
         int rc = moe_bwd_tc(ctx, (const __nv_bfloat16*)xn, (const __nv_bfloat16*)w1, (const __nv_bfloat16*)w2, pre_p,
-                            (const __nv_bfloat16*)hid_p, dout, perm, offsets, N, d, F, E, d_w1, d_b1, d_w2, d_b2, dxn);
+                            (const __nv_bfloat16*)hid_p, dout, perm, offsets, N, d, F, E, d_w1, d_b1, d_w2, d_b2, dxn, acc);
         if (rc != ASCA_ERR_UNSUPPORTED) return rc;
     }
     // scratch: dpre_p (N x F) f32, in the permuted order
@@ -281,14 +275,14 @@ int asca_moe_bwd(asca_ctx* ctx, const void* xn, const void* w1, const void* w2, 
     float* dpre_p = (float*)ws;
 
     // d_b2[c] = sum over all tokens of dout[t,c]
-    colsum_kernel<<<dim3((unsigned)ceil_div64(d, 32), 1), 256, 0, s>>>(dout, d, nullptr, nullptr, N, (int)d, d_b2, 0);
+    colsum_kernel<<<dim3((unsigned)ceil_div64(d, 32), 1), 256, 0, s>>>(dout, d, nullptr, nullptr, N, (int)d, d_b2, 0, acc);
     ASCA_CHECK_LAUNCH(ctx);
     // d_w2[eF+j, c] = sum_r hid_p[r,j] dout[perm[r],c]      (TN, K = rows of expert e)
     {
         gemm::Params p{};
         p.A = hid_p; p.lda = F;
         p.B = dout; p.ldb = d; p.b_idx = perm;
-        p.C = d_w2; p.ldc = d; p.c_gstride = F * d;
+        p.C = d_w2; p.ldc = d; p.c_gstride = F * d; p.accumulate = acc;
         p.M = (int)F; p.N = (int)d; p.K = 0;
         p.offsets = offsets; p.n_groups = (int)E; p.group_dim = gemm::GROUP_K;
         ASCA_CUDA(ctx, gemm::launch<float>(p, ASCA_TN, bf, 0, N, s));
@@ -308,14 +302,14 @@ int asca_moe_bwd(asca_ctx* ctx, const void* xn, const void* w1, const void* w2, 
     }
     // d_b1[eF+j] = sum over expert e's rows of dpre_p[r,j]
     colsum_kernel<<<dim3((unsigned)ceil_div64(F, 32), (unsigned)E), 256, 0, s>>>(dpre_p, F, nullptr, offsets, N, (int)F,
-                                                                               d_b1, F);
+                                                                               d_b1, F, acc);
     ASCA_CHECK_LAUNCH(ctx);
     // d_w1[c, eF+j] = sum_r xn[perm[r],c] dpre_p[r,j]        (TN, K = rows of expert e)
     {
         gemm::Params p{};
         p.A = xn; p.lda = d; p.a_idx = perm;
         p.B = dpre_p; p.ldb = F;
-        p.C = d_w1; p.ldc = E * F; p.c_gstride = F;
+        p.C = d_w1; p.ldc = E * F; p.c_gstride = F; p.accumulate = acc;
         p.M = (int)d; p.N = (int)F; p.K = 0;
         p.offsets = offsets; p.n_groups = (int)E; p.group_dim = gemm::GROUP_K;
         ASCA_CUDA(ctx, gemm::launch<float>(p, ASCA_TN, bf, 0, N, s));
@@ -333,6 +327,18 @@ int asca_moe_bwd(asca_ctx* ctx, const void* xn, const void* w1, const void* w2, 
         ctx->launches++;
     }
     return ASCA_OK;
+}
+
+int asca_moe_bwd(asca_ctx* ctx, const void* xn, const void* w1, const void* w2, const float* pre_p, const void* hid_p,
+                 const float* dout, const int32_t* perm, const int32_t* offsets, int64_t N, int64_t d, int64_t F,
+                 int64_t E, int dtype, float* d_w1, float* d_b1, float* d_w2, float* d_b2, float* dxn) {
+    return moe_bwd_impl(ctx, xn, w1, w2, pre_p, hid_p, dout, perm, offsets, N, d, F, E, dtype, d_w1, d_b1, d_w2, d_b2, dxn, 0);
+}
+
+int asca_moe_bwd_acc(asca_ctx* ctx, const void* xn, const void* w1, const void* w2, const float* pre_p, const void* hid_p,
+                     const float* dout, const int32_t* perm, const int32_t* offsets, int64_t N, int64_t d, int64_t F,
+                     int64_t E, int dtype, float* d_w1, float* d_b1, float* d_w2, float* d_b2, float* dxn) {
+    return moe_bwd_impl(ctx, xn, w1, w2, pre_p, hid_p, dout, perm, offsets, N, d, F, E, dtype, d_w1, d_b1, d_w2, d_b2, dxn, 1);
 }
 
 int asca_moe_step(asca_ctx* ctx, const float* x, const uint32_t* ids, const void* w1, const float* b1, const void* w2,

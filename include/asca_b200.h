@@ -174,6 +174,17 @@ int asca_delta_step(asca_ctx* ctx, const float* q, const float* k, const float* 
 int asca_delta_prep(asca_ctx* ctx, const float* qkv, const float* gate, int64_t N, int64_t H,
                     int64_t dh, float* q, float* k, float* v, float* qnorm, float* knorm,
                     float* alpha, float* beta);
+/* bf16-mode companions (no counterpart in the reference, whose backend is f32 only): the same
+ * math with the operands of the next tensor-core product written as bf16.
+ *   asca_cast_bf16             dst[i] = bf16(src[i])
+ *   asca_residual_rmsnorm_bf16 x_mid = x + yadd (yadd, x_mid nullable: plain norm), xn = bf16(rmsnorm(x_mid))
+ *   asca_delta_prep_bf16       asca_delta_prep with bf16 q, k, v */
+int asca_cast_bf16(asca_ctx* ctx, const float* src, void* dst, int64_t n);
+int asca_residual_rmsnorm_bf16(asca_ctx* ctx, const float* x, const float* yadd, float* x_mid, void* xn,
+                               int64_t rows, int64_t cols, float eps);
+int asca_delta_prep_bf16(asca_ctx* ctx, const float* qkv, const float* gate, int64_t N, int64_t H,
+                         int64_t dh, void* q, void* k, void* v, float* qnorm, float* knorm,
+                         float* alpha, float* beta);
 
 /* Host-pointer forms with the reference's ownership model: the forward returns an opaque
  * device-resident handle (DeltaDev, rust/src/cuda/mod.rs:1386-1397) that the backward
@@ -233,6 +244,12 @@ int asca_moe_bwd(asca_ctx* ctx, const void* xn, const void* w1, const void* w2,
                  const float* pre_p, const void* hid_p, const float* dout, const int32_t* perm,
                  const int32_t* offsets, int64_t N, int64_t d, int64_t F, int64_t E, int dtype,
                  float* d_w1, float* d_b1, float* d_w2, float* d_b2, float* dxn);
+/* Same, but d_w1, d_b1, d_w2, d_b2 are accumulated into (+=) instead of overwritten: the form
+ * `grad.axpy(1.0, &dW)` of HashMoe::backward (rust/src/model.rs:483-493) without a temporary. */
+int asca_moe_bwd_acc(asca_ctx* ctx, const void* xn, const void* w1, const void* w2,
+                     const float* pre_p, const void* hid_p, const float* dout, const int32_t* perm,
+                     const int32_t* offsets, int64_t N, int64_t d, int64_t F, int64_t E, int dtype,
+                     float* d_w1, float* d_b1, float* d_w2, float* d_b2, float* dxn);
 /* Fused combine: x_out = x_mid + moe_out (rust/src/model.rs:669-671); when xn_next is not
  * NULL also xn_next = rmsnorm(x_out) (the final norm, rust/src/model.rs:680). Alias of
  * asca_residual_rmsnorm kept under the name the MoE path uses. */
@@ -284,7 +301,10 @@ int asca_embed_bwd(asca_ctx* ctx, const float* dx, const uint32_t* ids, int64_t 
  * f32 parameter buffer in the reference's parameter order (rust/src/model.rs:593-609: embed,
  * head, then per layer w_qkv, b_qkv, w_gate, b_gate, w_o, b_o, w1, b1, w2, b2). Everything
  * stays on the device between calls; the Delta block takes the un-normalised residual stream
- * as the reference code does (rust/src/model.rs:664-667). f32 arithmetic. */
+ * as the reference code does (rust/src/model.rs:664-667). f32 arithmetic by default;
+ * asca_model_set_compute(ASCA_BF16) moves every product of the training step to the tensor cores
+ * (bf16 operands from a bf16 copy of the weights, f32 accumulation; residual stream, norms,
+ * gates, recurrent state, loss, gradients, master weights and AdamW stay f32). */
 typedef struct asca_model asca_model;
 int asca_model_create(asca_ctx* ctx, int64_t vocab, int64_t d, int64_t H, int64_t L, int64_t E,
                       int64_t F, asca_model** out);
@@ -292,6 +312,9 @@ int asca_model_destroy(asca_ctx* ctx, asca_model* m);
 int64_t asca_model_num_params(const asca_model* m);
 /* Device pointers of the flat buffers (params, grads, Adam m, Adam v), each num_params floats. */
 int asca_model_buffers(asca_model* m, float** params, float** grads, float** adam_m, float** adam_v);
+int asca_model_set_compute(asca_ctx* ctx, asca_model* m, int dtype);
+/* Call after writing the parameter buffer directly (asca_model_buffers): derived copies are rebuilt. */
+int asca_model_params_changed(asca_model* m);
 int asca_model_set_params_host(asca_ctx* ctx, asca_model* m, const float* params);
 int asca_model_get_host(asca_ctx* ctx, asca_model* m, float* params, float* grads);
 int asca_model_zero_grads(asca_ctx* ctx, asca_model* m);
