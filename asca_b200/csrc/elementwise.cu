@@ -243,6 +243,8 @@ __global__ void __launch_bounds__(256) adamw_seg_kernel(float* __restrict__ p, c
                                                         float b2, float wd) {
     const int64_t n = seg_off[n_seg];
     const int64_t stride = (int64_t)gridDim.x * blockDim.x * 4;
+    const bool vec_ok = ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(m) |
+                          reinterpret_cast<uintptr_t>(v)) & 15) == 0;
     for (int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += stride) {
         int lo = 0, hi = n_seg - 1;  // last segment with seg_off[s] <= i
         while (lo < hi) {
@@ -251,6 +253,19 @@ __global__ void __launch_bounds__(256) adamw_seg_kernel(float* __restrict__ p, c
         }
         int s = lo;
         float lr = lr_t[s], ep = eps_t[s];
+        if (i + 4 <= seg_off[s + 1] && vec_ok) {   // the common case: four elements of one tensor, 16-byte accesses
+            float4 P = *reinterpret_cast<float4*>(p + i), M = *reinterpret_cast<float4*>(m + i),
+                   V = *reinterpret_cast<float4*>(v + i);
+            const float4 G = *reinterpret_cast<const float4*>(g + i);
+            adamw_one(P.x, G.x, M.x, V.x, lr, b1, b2, ep, wd);
+            adamw_one(P.y, G.y, M.y, V.y, lr, b1, b2, ep, wd);
+            adamw_one(P.z, G.z, M.z, V.z, lr, b1, b2, ep, wd);
+            adamw_one(P.w, G.w, M.w, V.w, lr, b1, b2, ep, wd);
+            *reinterpret_cast<float4*>(p + i) = P;
+            *reinterpret_cast<float4*>(m + i) = M;
+            *reinterpret_cast<float4*>(v + i) = V;
+            continue;
+        }
         const int64_t end = i + 4 < n ? i + 4 : n;
         for (int64_t j = i; j < end; ++j) {
             while (j >= seg_off[s + 1]) {

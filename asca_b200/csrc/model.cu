@@ -7,22 +7,38 @@
 namespace {
 
 // ------------------------------------------------------------------ small kernels
-// out[c] (+)= sum_r src[r, c]: each CTA owns 32 columns, 8 warps stride the rows, fixed-order tree.
-__global__ void __launch_bounds__(256) colsum_plain_kernel(const float* __restrict__ src, int64_t ld, int64_t rows,
-                                                           int cols, float* __restrict__ out, int accumulate) {
-    __shared__ float part[8][33];
+// out[c] (+)= sum_r src[r, c], deterministic. Pass 1: CTA (x, y) owns 32 columns of row slice y, its 8 warps
+// stride the slice's rows, fixed-order tree -> part[y][c]. Pass 2 adds the slices in order.
+__global__ void __launch_bounds__(256) colsum_slices_kernel(const float* __restrict__ src, int64_t ld, int64_t rows,
+                                                            int cols, int64_t rows_per_slice, float* __restrict__ part) {
+    __shared__ float red[8][33];
     const int c = blockIdx.x * 32 + (threadIdx.x & 31), w = threadIdx.x >> 5;
+    const int64_t lo = blockIdx.y * rows_per_slice, hi = lo + rows_per_slice < rows ? lo + rows_per_slice : rows;
     float acc = 0.0f;
-    if (c < cols)
-        for (int64_t r = w; r < rows; r += 8) acc += src[r * ld + c];
-    part[w][threadIdx.x & 31] = acc;
+    if (c < cols) {
+        int64_t r = lo + w;
+        for (; r + 24 < hi; r += 32) {   // four independent loads in flight
+            const float a0 = src[r * ld + c], a1 = src[(r + 8) * ld + c], a2 = src[(r + 16) * ld + c], a3 = src[(r + 24) * ld + c];
+            acc += (a0 + a1) + (a2 + a3);
+        }
+        for (; r < hi; r += 8) acc += src[r * ld + c];
+    }
+    red[w][threadIdx.x & 31] = acc;
     __syncthreads();
     if (w == 0 && c < cols) {
         float t = 0.0f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) t += part[i][threadIdx.x];
-        out[c] = accumulate ? out[c] + t : t;
+        for (int i = 0; i < 8; ++i) t += red[i][threadIdx.x];
+        part[(int64_t)blockIdx.y * cols + c] = t;
     }
+}
+__global__ void __launch_bounds__(256) colsum_finish_kernel(const float* __restrict__ part, int n_slices, int cols,
+                                                            float* __restrict__ out, int accumulate) {
+    const int c = blockIdx.x * 256 + threadIdx.x;
+    if (c >= cols) return;
+    float t = 0.0f;
+    for (int s = 0; s < n_slices; ++s) t += part[(int64_t)s * cols + c];
+    out[c] = accumulate ? out[c] + t : t;
 }
 
 // One warp per row: log-sum-exp, loss_t, dlogits = (p - onehot) * inv_n. rust/src/model.rs:821-837.
@@ -68,7 +84,8 @@ __global__ void __launch_bounds__(256) embed_fwd_kernel(const float* __restrict_
     const float* src = table + (int64_t)ids[t] * d;
     for (int c = lane; c < d; c += 32) x[t * d + c] = src[c];
 }
-// d_table[v, c] += sum over tokens t (ascending) with ids[t] == v of dx[t, c]. grid (vocab, ceil(d/128)).
+// d_table[v, c] += sum over tokens t with ids[t] == v of dx[t, c]. grid (vocab, ceil(d/128)): the fallback for
+// row lengths that are not a multiple of 4.
 __global__ void __launch_bounds__(128) embed_bwd_kernel(const float* __restrict__ dx, const uint32_t* __restrict__ ids,
                                                         int64_t N, int d, float* __restrict__ d_table) {
     const uint32_t v = blockIdx.x;
@@ -81,6 +98,45 @@ __global__ void __launch_bounds__(128) embed_bwd_kernel(const float* __restrict_
             if (c < d) acc += dx[t * d + c];
         }
     if (any && c < d) d_table[(int64_t)v * d + c] += acc;
+}
+// Same sum, deterministic, for d % 4 == 0: CTA (v, y) owns 256 columns of table row v; each of its 8 warps scans
+// a fixed stride of the ids 32 at a time (ballot), adds the matching rows with every lane holding 8 columns,
+// and the 8 partial rows are added in warp order.
+__global__ void __launch_bounds__(256) embed_bwd_ballot_kernel(const float* __restrict__ dx, const uint32_t* __restrict__ ids,
+                                                               int64_t N, int d, float* __restrict__ d_table) {
+    __shared__ float red[8][256];
+    const uint32_t v = blockIdx.x;
+    const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int c0 = blockIdx.y * 256 + lane * 8;
+    const bool lo_ok = c0 + 4 <= d, hi_ok = c0 + 8 <= d;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int64_t base = (int64_t)w * 32; base < N; base += 256) {
+        const int64_t t = base + lane;
+        unsigned mask = __ballot_sync(0xffffffffu, t < N && ids[t] == v);
+        while (mask) {
+            const int b = __ffs(mask) - 1;
+            mask &= mask - 1;
+            const float* row = dx + (base + b) * d + c0;
+            if (lo_ok) {
+                const float4 x = *reinterpret_cast<const float4*>(row);
+                acc[0] += x.x; acc[1] += x.y; acc[2] += x.z; acc[3] += x.w;
+            }
+            if (hi_ok) {
+                const float4 x = *reinterpret_cast<const float4*>(row + 4);
+                acc[4] += x.x; acc[5] += x.y; acc[6] += x.z; acc[7] += x.w;
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) red[w][lane * 8 + j] = acc[j];
+    __syncthreads();
+    const int c = blockIdx.y * 256 + threadIdx.x;
+    if (c < d) {
+        float t = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) t += red[i][threadIdx.x];
+        d_table[(int64_t)v * d + c] += t;
+    }
 }
 __global__ void __launch_bounds__(256) add_kernel(const float* __restrict__ a, const float* __restrict__ b,
                                                   float* __restrict__ out, int64_t n) {
@@ -149,7 +205,21 @@ struct asca_model {
     int compute = ASCA_F32;              // ASCA_BF16: tensor-core products on a bf16 copy of the weights
     __nv_bfloat16* params16 = nullptr;   // refreshed from the f32 master copy whenever that changed
     bool params16_stale = true;
+    // asca_model_zero_grads only records the request: the next backward overwrites every gradient tensor instead
+    // of adding to it (each tensor is written exactly once per backward), which saves the clearing pass and the
+    // read half of the accumulation. Anything that exposes the buffer earlier clears it for real first.
+    bool grads_zero_pending = false;
 };
+
+static int materialize_zero_grads(asca_ctx* ctx, asca_model* m) {
+    if (!m->grads_zero_pending) return ASCA_OK;
+    m->grads_zero_pending = false;
+    if (ctx) {
+        ASCA_CUDA(ctx, cudaMemsetAsync(m->grads, 0, (size_t)m->n_params * 4, ctx->stream));
+        return ASCA_OK;
+    }
+    return cudaMemset(m->grads, 0, (size_t)m->n_params * 4) == cudaSuccess ? ASCA_OK : ASCA_ERR_CUDA;
+}
 
 // ---------------------------------------------------------------------------------------------
 // bf16 compute mode: the dataflow of Model::forward / Model::backward (rust/src/model.rs:631-700,
@@ -180,6 +250,8 @@ static int forward_backward_bf16(asca_ctx* ctx, asca_model* m, const uint32_t* i
     const float* P = m->params;
     const bf16* W = m->params16;
     float* G = m->grads;
+    const int acc = m->grads_zero_pending ? 0 : 1;   // first backward after zero_grads: overwrite
+    m->grads_zero_pending = false;
     Bufs bf(ctx);
     auto h16 = [&](int64_t n) { return (bf16*)bf.f((n + 1) / 2); };
     uint32_t* ids = (uint32_t*)bf.f(N);
@@ -237,7 +309,7 @@ static int forward_backward_bf16(asca_ctx* ctx, asca_model* m, const uint32_t* i
     ASCA_TRY(asca_cross_entropy(ctx, logits, tg, N, V, dlogits, loss_d));
     ASCA_CUDA(ctx, cudaMemcpyAsync(loss_h, loss_d, 4, cudaMemcpyDeviceToHost, ctx->stream));
     ASCA_TRY(asca_cast_bf16(ctx, dlogits, dl16, N * V));
-    ASCA_TRY(asca_gemm(ctx, ASCA_TN, d, V, N, h_final, d, dl16, V, G + m->head, V, nullptr, 1, BF));
+    ASCA_TRY(asca_gemm(ctx, ASCA_TN, d, V, N, h_final, d, dl16, V, G + m->head, V, nullptr, acc, BF));
     float* dh_ = bf.f(N * d);
     float* dx = bf.f(N * d);
     float* dxn = bf.f(N * d);
@@ -258,7 +330,7 @@ static int forward_backward_bf16(asca_ctx* ctx, asca_model* m, const uint32_t* i
         const Lyr& w = m->lay[li];
         const Lyr& w16 = m->lay16[li];
         Act& a = acts[li];
-        ASCA_TRY(asca_moe_bwd_acc(ctx, a.xn, W + w16.w1, W + w16.w2, a.pre_p, a.hid_p, dx, perm, offs, N, d, F, E, BF, G + w.w1,
+        ASCA_TRY((acc ? asca_moe_bwd_acc : asca_moe_bwd)(ctx, a.xn, W + w16.w1, W + w16.w2, a.pre_p, a.hid_p, dx, perm, offs, N, d, F, E, BF, G + w.w1,
                                   G + w.b1, G + w.w2, G + w.b2, dxn));
         ASCA_TRY(asca_rmsnorm_bwd(ctx, a.x_mid, dxn, d_moe, N, d, 1e-6f));
         add_kernel<<<(unsigned)blocks_nd, 256, 0, ctx->stream>>>(dx, d_moe, dx, N * d);   // d_mid
@@ -266,18 +338,19 @@ static int forward_backward_bf16(asca_ctx* ctx, asca_model* m, const uint32_t* i
         ASCA_TRY(asca_cast_bf16(ctx, dx, dx16, N * d));
         ASCA_TRY(asca_gemm(ctx, ASCA_NT, N, d, d, dx16, d, W + w16.w_o, d, d_o, d, nullptr, 0, BF));
         ASCA_TRY(asca_cast_bf16(ctx, d_o, do16, N * d));
-        ASCA_TRY(asca_gemm(ctx, ASCA_TN, d, d, N, a.o, d, dx16, d, G + w.w_o, d, nullptr, 1, BF));
-        ASCA_TRY(asca_colsum(ctx, dx, d, N, d, G + w.b_o, 1));
+        ASCA_TRY(asca_gemm(ctx, ASCA_TN, d, d, N, a.o, d, dx16, d, G + w.w_o, d, nullptr, acc, BF));
+        ASCA_TRY(asca_colsum(ctx, dx, d, N, d, G + w.b_o, acc));
         ASCA_TRY(asca_delta_bwd(ctx, a.q, a.k, a.v, a.al, a.be, a.qn, a.kn, do16, a.ckpt, B, T, H, dh, CH, BF, d_qkv, d_gate));
         ASCA_TRY(asca_cast_bf16(ctx, d_qkv, dqkv16, N * 3 * d));
         ASCA_TRY(asca_cast_bf16(ctx, d_gate, dg16, N * 2 * H));
-        ASCA_TRY(asca_gemm(ctx, ASCA_TN, d, 3 * d, N, a.x_in, d, dqkv16, 3 * d, G + w.w_qkv, 3 * d, nullptr, 1, BF));
-        ASCA_TRY(asca_colsum(ctx, d_qkv, 3 * d, N, 3 * d, G + w.b_qkv, 1));
-        ASCA_TRY(asca_gemm(ctx, ASCA_TN, d, 2 * H, N, a.x_in, d, dg16, 2 * H, G + w.w_gate, 2 * H, nullptr, 1, BF));
-        ASCA_TRY(asca_colsum(ctx, d_gate, 2 * H, N, 2 * H, G + w.b_gate, 1));
+        ASCA_TRY(asca_gemm(ctx, ASCA_TN, d, 3 * d, N, a.x_in, d, dqkv16, 3 * d, G + w.w_qkv, 3 * d, nullptr, acc, BF));
+        ASCA_TRY(asca_colsum(ctx, d_qkv, 3 * d, N, 3 * d, G + w.b_qkv, acc));
+        ASCA_TRY(asca_gemm(ctx, ASCA_TN, d, 2 * H, N, a.x_in, d, dg16, 2 * H, G + w.w_gate, 2 * H, nullptr, acc, BF));
+        ASCA_TRY(asca_colsum(ctx, d_gate, 2 * H, N, 2 * H, G + w.b_gate, acc));
         ASCA_TRY(asca_gemm(ctx, ASCA_NT, N, d, 3 * d, dqkv16, 3 * d, W + w16.w_qkv, 3 * d, dx, d, nullptr, 1, BF));
         ASCA_TRY(asca_gemm(ctx, ASCA_NT, N, d, 2 * H, dg16, 2 * H, W + w16.w_gate, 2 * H, dx, d, nullptr, 1, BF));
     }
+    if (!acc) ASCA_CUDA(ctx, cudaMemsetAsync(G + m->embed, 0, (size_t)V * d * 4, ctx->stream));
     ASCA_TRY(asca_embed_bwd(ctx, dx, ids, N, d, V, G + m->embed));
     ASCA_CUDA(ctx, cudaGetLastError());
     return asca_ctx_sync(ctx);
@@ -288,7 +361,24 @@ extern "C" {
 int asca_colsum(asca_ctx* ctx, const float* src, int64_t ld, int64_t rows, int64_t cols, float* out, int accumulate) {
     if (!ctx) return ASCA_ERR_ARG;
     ASCA_REQUIRE(ctx, src && out && rows >= 0 && cols > 0 && ld >= cols, "colsum: bad arguments");
-    colsum_plain_kernel<<<(unsigned)ceil_div64(cols, 32), 256, 0, ctx->stream>>>(src, ld, rows, (int)cols, out, accumulate);
+    if (rows == 0) {
+        if (!accumulate) ASCA_CUDA(ctx, cudaMemsetAsync(out, 0, (size_t)cols * 4, ctx->stream));
+        return ASCA_OK;
+    }
+    // enough row slices to fill the GPU, at least 256 rows each
+    const int64_t col_blocks = ceil_div64(cols, 32);
+    int64_t n_slices = ceil_div64(148 * 8, col_blocks);
+    if (n_slices > ceil_div64(rows, 256)) n_slices = ceil_div64(rows, 256);
+    if (n_slices < 1) n_slices = 1;
+    const int64_t rps = ceil_div64(rows, n_slices);
+    n_slices = ceil_div64(rows, rps);
+    void* ws;
+    ASCA_TRY(asca_workspace(ctx, (size_t)n_slices * cols * 4 + 256, &ws));
+    colsum_slices_kernel<<<dim3((unsigned)col_blocks, (unsigned)n_slices), 256, 0, ctx->stream>>>(src, ld, rows, (int)cols, rps,
+                                                                                               (float*)ws);
+    ASCA_CHECK_LAUNCH(ctx);
+    colsum_finish_kernel<<<(unsigned)ceil_div64(cols, 256), 256, 0, ctx->stream>>>((const float*)ws, (int)n_slices, (int)cols, out,
+                                                                                  accumulate);
     ASCA_CHECK_LAUNCH(ctx);
     return ASCA_OK;
 }
@@ -321,7 +411,10 @@ int asca_embed_bwd(asca_ctx* ctx, const float* dx, const uint32_t* ids, int64_t 
     if (!ctx) return ASCA_ERR_ARG;
     ASCA_REQUIRE(ctx, dx && ids && d_table && N >= 0 && d > 0 && vocab > 0 && vocab < 65536, "embed_bwd: bad arguments");
     if (N == 0) return ASCA_OK;
-    embed_bwd_kernel<<<dim3((unsigned)vocab, (unsigned)ceil_div64(d, 128)), 128, 0, ctx->stream>>>(dx, ids, N, (int)d, d_table);
+    if ((d & 3) == 0 && (reinterpret_cast<uintptr_t>(dx) & 15) == 0)
+        embed_bwd_ballot_kernel<<<dim3((unsigned)vocab, (unsigned)ceil_div64(d, 256)), 256, 0, ctx->stream>>>(dx, ids, N, (int)d, d_table);
+    else
+        embed_bwd_kernel<<<dim3((unsigned)vocab, (unsigned)ceil_div64(d, 128)), 128, 0, ctx->stream>>>(dx, ids, N, (int)d, d_table);
     ASCA_CHECK_LAUNCH(ctx);
     return ASCA_OK;
 }
@@ -387,7 +480,10 @@ int64_t asca_model_num_params(const asca_model* m) { return m ? m->n_params : 0;
 int asca_model_buffers(asca_model* m, float** params, float** grads, float** adam_m, float** adam_v) {
     if (!m) return ASCA_ERR_ARG;
     if (params) *params = m->params;
-    if (grads) *grads = m->grads;
+    if (grads) {
+        materialize_zero_grads(nullptr, m);
+        *grads = m->grads;
+    }
     if (adam_m) *adam_m = m->m;
     if (adam_v) *adam_v = m->v;
     return ASCA_OK;
@@ -418,15 +514,19 @@ int asca_model_set_params_host(asca_ctx* ctx, asca_model* m, const float* params
 int asca_model_get_host(asca_ctx* ctx, asca_model* m, float* params, float* grads) {
     if (!ctx || !m) return ASCA_ERR_ARG;
     if (params) ASCA_TRY(asca_memcpy_d2h(ctx, params, m->params, (size_t)m->n_params * 4));
-    if (grads) ASCA_TRY(asca_memcpy_d2h(ctx, grads, m->grads, (size_t)m->n_params * 4));
+    if (grads) {
+        ASCA_TRY(materialize_zero_grads(ctx, m));
+        ASCA_TRY(asca_memcpy_d2h(ctx, grads, m->grads, (size_t)m->n_params * 4));
+    }
     return ASCA_OK;
 }
 
 int asca_model_zero_grads(asca_ctx* ctx, asca_model* m) {
     if (!ctx || !m) return ASCA_ERR_ARG;
-    ASCA_CUDA(ctx, cudaMemsetAsync(m->grads, 0, (size_t)m->n_params * 4, ctx->stream));
+    m->grads_zero_pending = true;
     return ASCA_OK;
 }
+
 
 int asca_model_forward_backward_host(asca_ctx* ctx, asca_model* m, const uint32_t* ids_h, const uint32_t* tg_h,
                                      int64_t B, int64_t T, float* loss_h, float* logits_h) {
@@ -439,6 +539,8 @@ int asca_model_forward_backward_host(asca_ctx* ctx, asca_model* m, const uint32_
     if (m->compute == ASCA_BF16) return forward_backward_bf16(ctx, m, ids_h, tg_h, B, T, loss_h, logits_h);
     float* P = m->params;
     float* G = m->grads;
+    const int acc = m->grads_zero_pending ? 0 : 1;   // first backward after zero_grads: overwrite
+    m->grads_zero_pending = false;
     Bufs bf(ctx);
     uint32_t* ids = (uint32_t*)bf.f(N);
     uint32_t* tg = (uint32_t*)bf.f(N);
@@ -493,7 +595,7 @@ int asca_model_forward_backward_host(asca_ctx* ctx, asca_model* m, const uint32_
     // ---- backward (rust/src/model.rs:744-794)
     ASCA_TRY(asca_cross_entropy(ctx, logits, tg, N, V, dlogits, loss_d));
     ASCA_CUDA(ctx, cudaMemcpyAsync(loss_h, loss_d, 4, cudaMemcpyDeviceToHost, ctx->stream));
-    ASCA_TRY(asca_gemm(ctx, ASCA_TN, d, V, N, h_final, d, dlogits, V, G + m->head, V, nullptr, 1, ASCA_F32));
+    ASCA_TRY(asca_gemm(ctx, ASCA_TN, d, V, N, h_final, d, dlogits, V, G + m->head, V, nullptr, acc, ASCA_F32));
     float* dh_ = bf.f(N * d);
     float* dx = bf.f(N * d);
     float* dxn = bf.f(N * d);
@@ -509,25 +611,26 @@ int asca_model_forward_backward_host(asca_ctx* ctx, asca_model* m, const uint32_
         const Lyr& w = m->lay[li];
         Act& a = acts[li];
         // HashMoe::backward: gradients accumulate into the flat buffer
-        ASCA_TRY(asca_moe_bwd_acc(ctx, a.xn, P + w.w1, P + w.w2, a.pre_p, a.hid_p, dx, perm, offs, N, d, F, E, ASCA_F32,
+        ASCA_TRY((acc ? asca_moe_bwd_acc : asca_moe_bwd)(ctx, a.xn, P + w.w1, P + w.w2, a.pre_p, a.hid_p, dx, perm, offs, N, d, F, E, ASCA_F32,
                                   G + w.w1, G + w.b1, G + w.w2, G + w.b2, dxn));
         ASCA_TRY(asca_rmsnorm_bwd(ctx, a.x_mid, dxn, d_moe, N, d, 1e-6f));
         add_kernel<<<(unsigned)blocks_nd, 256, 0, ctx->stream>>>(dx, d_moe, dx, N * d);   // d_mid
         ctx->launches++;
         // DeltaBlock::backward (rust/src/delta.rs:615-674)
         ASCA_TRY(asca_gemm(ctx, ASCA_NT, N, d, d, dx, d, P + w.w_o, d, d_o, d, nullptr, 0, ASCA_F32));
-        ASCA_TRY(asca_gemm(ctx, ASCA_TN, d, d, N, a.o, d, dx, d, G + w.w_o, d, nullptr, 1, ASCA_F32));
-        ASCA_TRY(asca_colsum(ctx, dx, d, N, d, G + w.b_o, 1));
+        ASCA_TRY(asca_gemm(ctx, ASCA_TN, d, d, N, a.o, d, dx, d, G + w.w_o, d, nullptr, acc, ASCA_F32));
+        ASCA_TRY(asca_colsum(ctx, dx, d, N, d, G + w.b_o, acc));
         ASCA_TRY(asca_delta_bwd(ctx, a.q, a.k, a.v, a.al, a.be, a.qn, a.kn, d_o, a.ckpt, B, T, H, dh, CH, ASCA_F32, d_qkv,
                                 d_gate));
-        ASCA_TRY(asca_gemm(ctx, ASCA_TN, d, 3 * d, N, a.x_in, d, d_qkv, 3 * d, G + w.w_qkv, 3 * d, nullptr, 1, ASCA_F32));
-        ASCA_TRY(asca_colsum(ctx, d_qkv, 3 * d, N, 3 * d, G + w.b_qkv, 1));
-        ASCA_TRY(asca_gemm(ctx, ASCA_TN, d, 2 * H, N, a.x_in, d, d_gate, 2 * H, G + w.w_gate, 2 * H, nullptr, 1, ASCA_F32));
-        ASCA_TRY(asca_colsum(ctx, d_gate, 2 * H, N, 2 * H, G + w.b_gate, 1));
+        ASCA_TRY(asca_gemm(ctx, ASCA_TN, d, 3 * d, N, a.x_in, d, d_qkv, 3 * d, G + w.w_qkv, 3 * d, nullptr, acc, ASCA_F32));
+        ASCA_TRY(asca_colsum(ctx, d_qkv, 3 * d, N, 3 * d, G + w.b_qkv, acc));
+        ASCA_TRY(asca_gemm(ctx, ASCA_TN, d, 2 * H, N, a.x_in, d, d_gate, 2 * H, G + w.w_gate, 2 * H, nullptr, acc, ASCA_F32));
+        ASCA_TRY(asca_colsum(ctx, d_gate, 2 * H, N, 2 * H, G + w.b_gate, acc));
         // dx = d_mid + d_qkv Wqkv^T + d_gate Wg^T   (accumulate onto d_mid in place)
         ASCA_TRY(asca_gemm(ctx, ASCA_NT, N, d, 3 * d, d_qkv, 3 * d, P + w.w_qkv, 3 * d, dx, d, nullptr, 1, ASCA_F32));
         ASCA_TRY(asca_gemm(ctx, ASCA_NT, N, d, 2 * H, d_gate, 2 * H, P + w.w_gate, 2 * H, dx, d, nullptr, 1, ASCA_F32));
     }
+    if (!acc) ASCA_CUDA(ctx, cudaMemsetAsync(G + m->embed, 0, (size_t)V * d * 4, ctx->stream));
     ASCA_TRY(asca_embed_bwd(ctx, dx, ids, N, d, V, G + m->embed));
     ASCA_CUDA(ctx, cudaGetLastError());
     return asca_ctx_sync(ctx);
@@ -535,6 +638,7 @@ int asca_model_forward_backward_host(asca_ctx* ctx, asca_model* m, const uint32_
 
 int asca_model_adamw_step(asca_ctx* ctx, asca_model* m, float lr, float beta1, float beta2, float eps, float wd) {
     if (!ctx || !m) return ASCA_ERR_ARG;
+    ASCA_TRY(materialize_zero_grads(ctx, m));
     const int n_seg = (int)m->seg_off.size() - 1;
     std::vector<float> lr_t(n_seg), eps_t(n_seg);
     auto powi = [](float b, int e) {   // f32 exponentiation by squaring, as `f32::powi` lowers
