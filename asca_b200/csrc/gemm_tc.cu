@@ -212,20 +212,15 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
         }
     } else {
         // ------------------------------------------------------------ epilogue (warps 2..5)
+        // Each warp owns the 32 accumulator rows of its TMEM lane quarter. The rows go to shared memory first
+        // (the pipeline stages are idle once the last MMA has retired), then out row by row with all 32
+        // lanes on consecutive addresses, which is also where bias, activation and accumulation are applied.
         int got = 1;
         if (num_k > 0 && lane == 0) got = tc::mbar_wait(tmem_full, 0, abort_flag, p.err_word, 103) ? 1 : 0;
         const bool ok = __shfl_sync(0xffffffffu, got, 0) != 0;  // uniform: tcgen05.ld below is warp-aligned
         tc::tcgen05_fence_after();
         const int q = warp & 3;                 // TMEM lane quarter this warp may read
-        const int m = m0 + q * 32 + lane;
-        const bool row_ok = ok && m < M;
-        const int64_t lr = (int64_t)row_base_m + m;
-        int64_t cr = lr;
-        if (row_ok && p.c_idx) cr = p.c_idx[lr];
-        float* crow = p.C + (p.group_dim == GROUP_K ? (int64_t)g * p.c_gstride : 0) + cr * p.ldc;
-        const float* bias = p.bias ? p.bias + (int64_t)g * p.bias_gstride : nullptr;
-        const bool vec_ok = ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
-                            ((p.c_gstride & 3) == 0);
+        float4* stg = reinterpret_cast<float4*>(tiles + q * 16384);   // [32 rows][32 float4], index XOR row
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
             uint32_t r[32];
@@ -236,62 +231,100 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
 #pragma unroll
                 for (int j = 0; j < 32; ++j) r[j] = 0u;
             }
-            const int nb = n0 + c * 32;
-            if (!row_ok || nb >= p.N) continue;
-            float v[32];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-            const bool full_chunk = nb + 32 <= p.N;
-            if (bias) {
+            for (int j = 0; j < 8; ++j)
+                stg[lane * 32 + ((c * 8 + j) ^ lane)] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                                     __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+        }
+        __syncwarp();
+        const int nb = n0 + 4 * lane;           // this lane's 4 columns
+        const bool c_vec = ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) && ((p.c_gstride & 3) == 0);
+        const bool c2_vec = p.C2 && ((p.ldc2 & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.C2) & 7) == 0);
+        const bool aux_vec = p.aux && ((p.ldaux & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.aux) & 15) == 0);
+        const bool full4 = nb + 4 <= p.N;
+        float bias4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        if (p.bias) {
+            const float* bias = p.bias + (int64_t)g * p.bias_gstride;
 #pragma unroll
-                for (int j = 0; j < 32; ++j)
-                    if (full_chunk || nb + j < p.N) v[j] += bias[nb + j];
-            }
-            if (p.epi == EPI_SILU_BWD) {
-                const float* ax = p.aux + lr * p.ldaux + nb;
+            for (int j = 0; j < 4; ++j)
+                if (nb + j < p.N) bias4[j] = bias[nb + j];
+        }
+        float* cbase = p.C + (p.group_dim == GROUP_K ? (int64_t)g * p.c_gstride : 0);
+        if (ok && nb < p.N) {
+            constexpr int RB = 8;   // rows per batch: their global loads (aux, old C, row map) are all issued before any is used
+#pragma unroll 1
+            for (int r0 = 0; r0 < 32; r0 += RB) {
+                if (m0 + q * 32 + r0 >= M) break;
+                int64_t lrs[RB], crs[RB];
+                float4 aux4[RB], old4[RB];
 #pragma unroll
-                for (int j = 0; j < 32; ++j)
-                    if (full_chunk || nb + j < p.N) v[j] *= silu_grad_f(ax[j]);
-            }
-            if (full_chunk && vec_ok) {
-                float4* dst = reinterpret_cast<float4*>(crow + nb);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    float4 o = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                    if (p.accumulate) {
-                        const float4 old = dst[j];
-                        o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-                        v[4 * j] = o.x; v[4 * j + 1] = o.y; v[4 * j + 2] = o.z; v[4 * j + 3] = o.w;
-                    }
-                    dst[j] = o;
+                for (int i = 0; i < RB; ++i) {
+                    const int m = m0 + q * 32 + r0 + i;
+                    const bool live = m < M;
+                    lrs[i] = (int64_t)row_base_m + (live ? m : m0);
+                    crs[i] = p.c_idx ? (int64_t)p.c_idx[lrs[i]] : lrs[i];
                 }
-            } else {
 #pragma unroll
-                for (int j = 0; j < 32; ++j)
-                    if (nb + j < p.N) {
-                        if (p.accumulate) v[j] += crow[nb + j];
-                        crow[nb + j] = v[j];
-                    }
-            }
-            if (p.C2) {
-                __nv_bfloat16* c2 = p.C2 + lr * p.ldc2 + nb;
-                if (full_chunk && (p.ldc2 & 7) == 0 && (reinterpret_cast<uintptr_t>(p.C2) & 15) == 0) {
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        uint32_t w[4];
-#pragma unroll
-                        for (int t = 0; t < 4; ++t) {
-                            float x0 = v[8 * j + 2 * t], x1 = v[8 * j + 2 * t + 1];
-                            if (p.epi == EPI_SILU) { x0 = silu_f(x0); x1 = silu_f(x1); }
-                            __nv_bfloat162 h2 = __floats2bfloat162_rn(x0, x1);
-                            w[t] = *reinterpret_cast<uint32_t*>(&h2);
+                for (int i = 0; i < RB; ++i) {
+                    aux4[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    old4[i] = aux4[i];
+                    if (p.epi == EPI_SILU_BWD) {
+                        const float* ax = p.aux + lrs[i] * p.ldaux + nb;
+                        if (full4 && aux_vec) aux4[i] = *reinterpret_cast<const float4*>(ax);
+                        else {
+                            aux4[i].x = ax[0];
+                            if (nb + 1 < p.N) aux4[i].y = ax[1];
+                            if (nb + 2 < p.N) aux4[i].z = ax[2];
+                            if (nb + 3 < p.N) aux4[i].w = ax[3];
                         }
-                        reinterpret_cast<uint4*>(c2)[j] = make_uint4(w[0], w[1], w[2], w[3]);
                     }
-                } else {
+                    if (p.accumulate) {
+                        const float* crow = cbase + crs[i] * p.ldc + nb;
+                        if (full4 && c_vec) old4[i] = *reinterpret_cast<const float4*>(crow);
+                        else {
+                            old4[i].x = crow[0];
+                            if (nb + 1 < p.N) old4[i].y = crow[1];
+                            if (nb + 2 < p.N) old4[i].z = crow[2];
+                            if (nb + 3 < p.N) old4[i].w = crow[3];
+                        }
+                    }
+                }
 #pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        if (nb + j < p.N) c2[j] = __float2bfloat16(p.epi == EPI_SILU ? silu_f(v[j]) : v[j]);
+                for (int i = 0; i < RB; ++i) {
+                    const int rr = r0 + i;
+                    if (m0 + q * 32 + rr >= M) break;
+                    const float4 acc4 = stg[rr * 32 + (lane ^ rr)];
+                    float v[4] = {acc4.x + bias4[0], acc4.y + bias4[1], acc4.z + bias4[2], acc4.w + bias4[3]};
+                    if (p.epi == EPI_SILU_BWD) {
+                        v[0] *= silu_grad_f(aux4[i].x); v[1] *= silu_grad_f(aux4[i].y);
+                        v[2] *= silu_grad_f(aux4[i].z); v[3] *= silu_grad_f(aux4[i].w);
+                    }
+                    v[0] += old4[i].x; v[1] += old4[i].y; v[2] += old4[i].z; v[3] += old4[i].w;
+                    float* crow = cbase + crs[i] * p.ldc + nb;
+                    if (full4 && c_vec) {
+                        *reinterpret_cast<float4*>(crow) = make_float4(v[0], v[1], v[2], v[3]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            if (nb + j < p.N) crow[j] = v[j];
+                    }
+                    if (p.C2) {
+                        __nv_bfloat16* c2 = p.C2 + lrs[i] * p.ldc2 + nb;
+                        float x[4] = {v[0], v[1], v[2], v[3]};
+                        if (p.epi == EPI_SILU) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) x[j] = silu_f(x[j]);
+                        }
+                        if (full4 && c2_vec) {
+                            const __nv_bfloat162 lo2 = __floats2bfloat162_rn(x[0], x[1]), hi2 = __floats2bfloat162_rn(x[2], x[3]);
+                            *reinterpret_cast<uint2*>(c2) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo2),
+                                                                       *reinterpret_cast<const uint32_t*>(&hi2));
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                if (nb + j < p.N) c2[j] = __float2bfloat16(x[j]);
+                        }
+                    }
                 }
             }
         }
