@@ -1,17 +1,18 @@
 // bf16 GEMM on the 5th-generation tensor cores (tcgen05) for sm_100a.
 //
-// One CTA computes a 128 x 128 f32 output tile. Warp roles (192 threads):
+// Persistent: two CTAs per SM walk the 128 x 128 f32 output tiles round-robin. Warp roles (192 threads):
 //   warp 0      TMA producer: one thread streams 128x64 A and 64x128 B bf16 tiles (128-byte
 //               swizzle, plain non-multicast cp.async.bulk.tensor) through a 3-stage ring of
-//               mbarriers;
-//   warp 1      allocates 128 TMEM columns, and one thread issues tcgen05.mma (M128 N128 K16,
-//               4 per k-tile) with the accumulator in TMEM; tcgen05.commit releases ring slots
-//               and finally signals the epilogue;
-//   warps 2-5   epilogue: tcgen05.ld the accumulator (each warp its 32-lane quarter), apply
-//               bias / SiLU / SiLU' / accumulate, store f32 (and an optional bf16 second output),
-//               optionally through a row map (the un-permute scatter of the MoE combine).
-// 96 KiB of shared memory per CTA lets two CTAs share an SM, so one CTA's epilogue overlaps the
-// other's main loop.
+//               mbarriers, running ahead across tile boundaries;
+//   warp 1      allocates 256 TMEM columns = two accumulator buffers, and one thread issues
+//               tcgen05.mma (M128 N128 K16, 4 per k-tile) into the buffer of the current tile;
+//               tcgen05.commit releases ring slots and hands the finished buffer to the epilogue;
+//   warps 2-5   epilogue: tcgen05.ld the accumulator (each warp its 32-lane quarter), 32 columns at a
+//               time, through the warp's shared-memory staging rows so that global memory sees
+//               whole 64-byte row segments; bias / SiLU / SiLU' / accumulate are applied there;
+//               f32 output (and an optional bf16 second output), optionally through a row map (the
+//               un-permute scatter of the MoE combine). The buffer is released after the last
+//               tcgen05.ld, and the main loop of the next tile runs meanwhile in the other buffer.
 //
 // Operand majorness covers the three modes without any transposed copy: NN = A K-major, B
 // MN-major; TN = A MN-major, B MN-major; NT = A K-major, B K-major. Expert grouping: GROUP_M
@@ -29,8 +30,10 @@ namespace {
 
 constexpr int BM = 128, BN = 128, BK = 64, STAGES = 3, THREADS = 192;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int TMEM_COLS = 128;
-constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int TMEM_COLS = 2 * BN;      // two accumulator buffers
+constexpr int MAX_GROUPS = 2048;
+constexpr size_t SMEM_FIXED = (size_t)STAGES * STAGE_BYTES + 4 * 2048 /*epilogue staging*/ + 1024 /*alignment slack*/ +
+                              256 /*barriers*/;   // + (groups + 2) * 4 for the tile table
 
 struct KP {
     float* C;
@@ -58,114 +61,128 @@ __device__ __forceinline__ float silu_grad_f(float p) {
 }
 
 template <int MODE>
-__global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA,
-                                                          const __grid_constant__ CUtensorMap mapB, const KP p) {
+__global__ void __launch_bounds__(THREADS, 2) gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA,
+                                                             const __grid_constant__ CUtensorMap mapB, const KP p) {
     constexpr bool A_MN = (MODE == ASCA_TN);   // A operand MN-major
     constexpr bool B_MN = (MODE != ASCA_NT);   // B operand MN-major
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + STAGES * STAGE_BYTES);
+    uint8_t* staging = tiles + STAGES * STAGE_BYTES;                 // 4 epilogue warps x 2 KiB
+    uint64_t* full = reinterpret_cast<uint64_t*>(staging + 4 * 2048);
     uint64_t* empty = full + STAGES;
-    uint64_t* tmem_full = empty + STAGES;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full + 1);
+    uint64_t* acc_full = empty + STAGES;     // [2] accumulator buffer written (MMA -> epilogue)
+    uint64_t* acc_empty = acc_full + 2;      // [2] accumulator buffer read out (epilogue -> MMA)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    int* sh_info = const_cast<int*>(abort_flag) + 1;  // [0] group, [1] tile within group
+    int* prefix = const_cast<int*>(abort_flag) + 1;                  // [n_groups + 1] first tile of every group
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_n = (p.N + BN - 1) / BN;
+    const int n_groups = p.group_dim == GROUP_NONE ? 1 : p.n_groups;
 
-    // ---- which (group, tile) is this CTA?
+    // ---- tile table: group g owns tiles [prefix[g], prefix[g+1]), tile = tile_m * tiles_n + tile_n within it
     if (warp == 0) {
-        int found_g = -1, found_t = 0;
-        if (p.group_dim == GROUP_NONE) {
-            found_g = 0;
-            found_t = blockIdx.x;
-        } else {
-            int base = 0;
-            for (int g0 = 0; g0 < p.n_groups && found_g < 0; g0 += 32) {
-                const int g = g0 + lane;
-                int cnt = 0;
-                if (g < p.n_groups) {
-                    const int n_g = p.offsets[g + 1] - p.offsets[g];
-                    cnt = p.group_dim == GROUP_M ? ((n_g + BM - 1) / BM) * tiles_n : ((p.M + BM - 1) / BM) * tiles_n;
-                }
-                int inc = cnt;
-#pragma unroll
-                for (int o = 1; o < 32; o <<= 1) {
-                    int n = __shfl_up_sync(0xffffffffu, inc, o);
-                    if (lane >= o) inc += n;
-                }
-                const int start = base + inc - cnt;
-                const bool mine = (int)blockIdx.x >= start && (int)blockIdx.x < start + cnt;
-                const unsigned m = __ballot_sync(0xffffffffu, mine);
-                if (m) {
-                    const int src = __ffs(m) - 1;
-                    found_g = __shfl_sync(0xffffffffu, g, src);
-                    found_t = (int)blockIdx.x - __shfl_sync(0xffffffffu, start, src);
-                }
-                base += __shfl_sync(0xffffffffu, inc, 31);
+        int base = 0;
+        for (int g0 = 0; g0 < n_groups; g0 += 32) {
+            const int g = g0 + lane;
+            int cnt = 0;
+            if (g < n_groups) {
+                if (p.group_dim == GROUP_M) cnt = ((p.offsets[g + 1] - p.offsets[g] + BM - 1) / BM) * tiles_n;
+                else cnt = ((p.M + BM - 1) / BM) * tiles_n;
             }
+            int inc = cnt;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int nb = __shfl_up_sync(0xffffffffu, inc, o);
+                if (lane >= o) inc += nb;
+            }
+            if (g < n_groups) prefix[g] = base + inc - cnt;
+            base += __shfl_sync(0xffffffffu, inc, 31);
         }
         if (lane == 0) {
-            sh_info[0] = found_g;
-            sh_info[1] = found_t;
+            prefix[n_groups] = base;
             *abort_flag = 0;
             for (int s = 0; s < STAGES; ++s) {
                 tc::mbar_init(&full[s], 1);
                 tc::mbar_init(&empty[s], 1);
             }
-            tc::mbar_init(tmem_full, 1);
+            for (int b = 0; b < 2; ++b) {
+                tc::mbar_init(&acc_full[b], 1);
+                tc::mbar_init(&acc_empty[b], 4);
+            }
             tc::mbar_fence_init();
             tc::prefetch_tensormap(&mapA);
             tc::prefetch_tensormap(&mapB);
         }
     }
-    __syncthreads();
-    const int g = sh_info[0];
-    if (g < 0) return;  // surplus CTA of the upper-bound grid (uniform: no TMEM held yet)
     if (warp == 1) tc::tmem_alloc(tmem_slot, TMEM_COLS);
     tc::tcgen05_fence_before();
     __syncthreads();
     tc::tcgen05_fence_after();
-    const uint32_t tmem_acc = *tmem_slot;
+    const uint32_t tmem_base = *tmem_slot;
+    const int total_tiles = prefix[n_groups];
 
-    const int tile_n = sh_info[1] % tiles_n, tile_m = sh_info[1] / tiles_n;
-    const int m0 = tile_m * BM, n0 = tile_n * BN;
-    int lo = 0, M = p.M, K = p.K;
-    if (p.group_dim != GROUP_NONE) {
-        lo = p.offsets[g];
-        const int n_g = p.offsets[g + 1] - lo;
-        if (p.group_dim == GROUP_M) M = n_g; else K = n_g;
-    }
-    const int num_k = (K + BK - 1) / BK;
-    const int row_base_m = p.group_dim == GROUP_M ? lo : 0;   // added to A/C row coordinates
-    const int row_base_k = p.group_dim == GROUP_K ? lo : 0;   // added to k-row coordinates (TN)
-    const int b_in = g * p.b_goff_inner, b_out = g * p.b_goff_outer;
+    // Geometry of one tile; every role walks the same tile sequence blockIdx.x, + gridDim.x, ...
+    struct Tile {
+        int g, m0, n0, M, num_k, K, row_base_m, row_base_k, b_in, b_out;
+    };
+    auto locate = [&](int t) {
+        int lo = 0, hi = n_groups - 1;   // last group with prefix[g] <= t
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (prefix[mid] <= t) lo = mid; else hi = mid - 1;
+        }
+        Tile x;
+        x.g = lo;
+        const int in = t - prefix[lo];
+        x.m0 = (in / tiles_n) * BM;
+        x.n0 = (in % tiles_n) * BN;
+        int seg_lo = 0;
+        x.M = p.M;
+        x.K = p.K;
+        if (p.group_dim != GROUP_NONE) {
+            seg_lo = p.offsets[lo];
+            const int n_g = p.offsets[lo + 1] - seg_lo;
+            if (p.group_dim == GROUP_M) x.M = n_g; else x.K = n_g;
+        }
+        x.num_k = (x.K + BK - 1) / BK;
+        x.row_base_m = p.group_dim == GROUP_M ? seg_lo : 0;   // added to A/C row coordinates
+        x.row_base_k = p.group_dim == GROUP_K ? seg_lo : 0;   // added to k-row coordinates (TN)
+        x.b_in = lo * p.b_goff_inner;
+        x.b_out = lo * p.b_goff_outer;
+        return x;
+    };
 
     if (warp == 0) {
-        // ------------------------------------------------------------ TMA producer
+        // ------------------------------------------------------------ TMA producer (one thread)
         if (lane == 0) {
-            for (int kt = 0; kt < num_k; ++kt) {
-                const int s = kt % STAGES;
-                if (kt >= STAGES &&
-                    !tc::mbar_wait(&empty[s], ((kt / STAGES) - 1) & 1, abort_flag, p.err_word, 101))
-                    break;
-                uint8_t* a_s = tiles + s * STAGE_BYTES;
-                uint8_t* b_s = a_s + A_BYTES;
-                tc::mbar_expect_tx(&full[s], STAGE_BYTES);
-                const int k0 = kt * BK;
-                if (A_MN) {   // memory (k rows x M): two boxes of 64 columns
-                    tc::tma_load_2d(a_s, &mapA, m0, row_base_k + k0, &full[s]);
-                    tc::tma_load_2d(a_s + 8192, &mapA, m0 + 64, row_base_k + k0, &full[s]);
-                } else {      // memory (rows x K): one box 64 k x 128 rows
-                    tc::tma_load_2d(a_s, &mapA, k0, row_base_m + m0, &full[s]);
-                }
-                if (B_MN) {   // memory (k rows x N)
-                    const int kr = (MODE == ASCA_TN ? row_base_k : 0) + k0 + b_out;
-                    tc::tma_load_2d(b_s, &mapB, n0 + b_in, kr, &full[s]);
-                    tc::tma_load_2d(b_s + 8192, &mapB, n0 + 64 + b_in, kr, &full[s]);
-                } else {      // memory (N rows x K)
-                    tc::tma_load_2d(b_s, &mapB, k0 + b_in, n0 + b_out, &full[s]);
+            uint32_t it = 0;   // k-tiles issued so far, across tiles: ring slot it % STAGES
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                const Tile x = locate(t);
+                for (int kt = 0; kt < x.num_k; ++kt, ++it) {
+                    const int s = it % STAGES;
+                    if (it >= STAGES && !tc::mbar_wait(&empty[s], ((it / STAGES) - 1) & 1, abort_flag, p.err_word, 101)) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* a_s = tiles + s * STAGE_BYTES;
+                    uint8_t* b_s = a_s + A_BYTES;
+                    tc::mbar_expect_tx(&full[s], STAGE_BYTES);
+                    const int k0 = kt * BK;
+                    if (A_MN) {   // memory (k rows x M): two boxes of 64 columns
+                        tc::tma_load_2d(a_s, &mapA, x.m0, x.row_base_k + k0, &full[s]);
+                        tc::tma_load_2d(a_s + 8192, &mapA, x.m0 + 64, x.row_base_k + k0, &full[s]);
+                    } else {      // memory (rows x K): one box 64 k x 128 rows
+                        tc::tma_load_2d(a_s, &mapA, k0, x.row_base_m + x.m0, &full[s]);
+                    }
+                    if (B_MN) {   // memory (k rows x N)
+                        const int kr = (MODE == ASCA_TN ? x.row_base_k : 0) + k0 + x.b_out;
+                        tc::tma_load_2d(b_s, &mapB, x.n0 + x.b_in, kr, &full[s]);
+                        tc::tma_load_2d(b_s + 8192, &mapB, x.n0 + 64 + x.b_in, kr, &full[s]);
+                    } else {      // memory (N rows x K)
+                        tc::tma_load_2d(b_s, &mapB, k0 + x.b_in, x.n0 + x.b_out, &full[s]);
+                    }
                 }
             }
         }
@@ -173,158 +190,189 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
         // ------------------------------------------------------------ MMA issuer
         constexpr uint32_t IDESC = tc::idesc_bf16_f32(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
         bool ok = true;
-        for (int kt = 0; kt < num_k && ok; ++kt) {
-            const int s = kt % STAGES;
-            // lane 0 polls, the verdict is broadcast so the warp stays converged
-            int got = 0;
-            if (lane == 0) got = tc::mbar_wait(&full[s], (kt / STAGES) & 1, abort_flag, p.err_word, 102) ? 1 : 0;
+        uint32_t it = 0;
+        int tl = 0;   // tiles done by this CTA: accumulator buffer tl & 1
+        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tl) {
+            const Tile x = locate(t);
+            const int buf = tl & 1;
+            const uint32_t tmem_acc = tmem_base + buf * BN;
+            int got = 1;
+            if (tl >= 2 && lane == 0)   // the epilogue has read this buffer's previous tile out
+                got = tc::mbar_wait(&acc_empty[buf], ((tl >> 1) - 1) & 1, abort_flag, p.err_word, 104) ? 1 : 0;
             ok = __shfl_sync(0xffffffffu, got, 0) != 0;
             if (!ok) break;
             tc::tcgen05_fence_after();
-            uint8_t* a_s = tiles + s * STAGE_BYTES;
-            uint8_t* b_s = a_s + A_BYTES;
-            if (p.group_dim == GROUP_K && (kt + 1) * BK > K) {
-                // ragged last k-tile of this expert: rows >= K - kt*BK belong to the next expert
-                const int valid = K - kt * BK;
-                const int lines = (BK - valid) * 2;  // 128-byte lines in the two A boxes
-                for (int i = lane; i < lines * 8; i += 32) {
-                    const int line = i >> 3, chunk = i & 7;
-                    const int h = line / (BK - valid), kr = valid + line % (BK - valid);
-                    *reinterpret_cast<uint4*>(a_s + h * 8192 + kr * 128 + chunk * 16) = make_uint4(0, 0, 0, 0);
+            for (int kt = 0; kt < x.num_k && ok; ++kt, ++it) {
+                const int s = it % STAGES;
+                // lane 0 polls, the verdict is broadcast so the warp stays converged
+                got = 0;
+                if (lane == 0) got = tc::mbar_wait(&full[s], (it / STAGES) & 1, abort_flag, p.err_word, 102) ? 1 : 0;
+                ok = __shfl_sync(0xffffffffu, got, 0) != 0;
+                if (!ok) break;
+                tc::tcgen05_fence_after();
+                uint8_t* a_s = tiles + s * STAGE_BYTES;
+                uint8_t* b_s = a_s + A_BYTES;
+                if (p.group_dim == GROUP_K && (kt + 1) * BK > x.K) {
+                    // ragged last k-tile of this expert: rows >= K - kt*BK belong to the next expert
+                    const int valid = x.K - kt * BK;
+                    const int lines = (BK - valid) * 2;  // 128-byte lines in the two A boxes
+                    for (int i = lane; i < lines * 8; i += 32) {
+                        const int line = i >> 3, chunk = i & 7;
+                        const int h = line / (BK - valid), kr = valid + line % (BK - valid);
+                        *reinterpret_cast<uint4*>(a_s + h * 8192 + kr * 128 + chunk * 16) = make_uint4(0, 0, 0, 0);
+                    }
+                    tc::fence_proxy_async_smem();
+                    __syncwarp();
                 }
-                tc::fence_proxy_async_smem();
+                if (lane == 0) {
+                    const uint32_t a_addr = tc::smem_u32(a_s), b_addr = tc::smem_u32(b_s);
+#pragma unroll
+                    for (int k16 = 0; k16 < BK / 16; ++k16) {
+                        const uint64_t ad = A_MN ? tc::smem_desc_sw128(a_addr + k16 * 2048, 8192, 1024)
+                                                 : tc::smem_desc_sw128(a_addr + k16 * 32, 16, 1024);
+                        const uint64_t bd = B_MN ? tc::smem_desc_sw128(b_addr + k16 * 2048, 8192, 1024)
+                                                 : tc::smem_desc_sw128(b_addr + k16 * 32, 16, 1024);
+                        tc::umma_bf16(tmem_acc, ad, bd, IDESC, (kt > 0 || k16 > 0) ? 1u : 0u);
+                    }
+                    tc::umma_commit(&empty[s]);                       // slot free once these MMAs retire
+                    if (kt == x.num_k - 1) tc::umma_commit(&acc_full[buf]);
+                }
                 __syncwarp();
             }
-            if (lane == 0) {
-                const uint32_t a_addr = tc::smem_u32(a_s), b_addr = tc::smem_u32(b_s);
-#pragma unroll
-                for (int k16 = 0; k16 < BK / 16; ++k16) {
-                    const uint64_t ad = A_MN ? tc::smem_desc_sw128(a_addr + k16 * 2048, 8192, 1024)
-                                             : tc::smem_desc_sw128(a_addr + k16 * 32, 16, 1024);
-                    const uint64_t bd = B_MN ? tc::smem_desc_sw128(b_addr + k16 * 2048, 8192, 1024)
-                                             : tc::smem_desc_sw128(b_addr + k16 * 32, 16, 1024);
-                    tc::umma_bf16(tmem_acc, ad, bd, IDESC, (kt > 0 || k16 > 0) ? 1u : 0u);
-                }
-                tc::umma_commit(&empty[s]);                 // slot free once these MMAs retire
-                if (kt == num_k - 1) tc::umma_commit(tmem_full);
-            }
-            __syncwarp();
+            if (ok && x.num_k == 0 && lane == 0) tc::mbar_arrive(&acc_full[buf]);   // empty expert: the epilogue stores zeros
         }
     } else {
         // ------------------------------------------------------------ epilogue (warps 2..5)
-        // Each warp owns the 32 accumulator rows of its TMEM lane quarter. The rows go to shared memory first
-        // (the pipeline stages are idle once the last MMA has retired), then out row by row with all 32
-        // lanes on consecutive addresses, which is also where bias, activation and accumulation are applied.
-        int got = 1;
-        if (num_k > 0 && lane == 0) got = tc::mbar_wait(tmem_full, 0, abort_flag, p.err_word, 103) ? 1 : 0;
-        const bool ok = __shfl_sync(0xffffffffu, got, 0) != 0;  // uniform: tcgen05.ld below is warp-aligned
-        tc::tcgen05_fence_after();
+        // Each warp owns the 32 accumulator rows of its TMEM lane quarter and moves them 32 columns at a time:
+        // tcgen05.ld (one row per lane) -> the warp's 2 KiB of shared memory, 16 columns per pass -> global
+        // memory with 4 lanes on each row's 64 bytes, where bias, activation and accumulation are applied. The TMEM buffer is
+        // released after the last tcgen05.ld; the next tile's main loop runs meanwhile in the other buffer.
         const int q = warp & 3;                 // TMEM lane quarter this warp may read
-        float4* stg = reinterpret_cast<float4*>(tiles + q * 16384);   // [32 rows][32 float4], index XOR row
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-            uint32_t r[32];
-            if (num_k > 0 && ok) {
-                tc::tmem_ld_32x32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
-                tc::tmem_ld_wait();
-            } else {
-#pragma unroll
-                for (int j = 0; j < 32; ++j) r[j] = 0u;
-            }
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-                stg[lane * 32 + ((c * 8 + j) ^ lane)] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                                                                     __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-        }
-        __syncwarp();
-        const int nb = n0 + 4 * lane;           // this lane's 4 columns
+        float4* stg = reinterpret_cast<float4*>(staging + q * 2048);   // [32 rows][4 float4], index XOR ((row >> 1) & 3)
         const bool c_vec = ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) && ((p.c_gstride & 3) == 0);
         const bool c2_vec = p.C2 && ((p.ldc2 & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.C2) & 7) == 0);
         const bool aux_vec = p.aux && ((p.ldaux & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.aux) & 15) == 0);
-        const bool full4 = nb + 4 <= p.N;
-        float bias4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        if (p.bias) {
-            const float* bias = p.bias + (int64_t)g * p.bias_gstride;
+        const int l4 = lane & 3, rsub = lane >> 2;   // store phase: 4 lanes per row (64 bytes), 8 rows per instruction
+        bool ok = true;
+        int tl = 0;
+        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tl) {
+            const Tile x = locate(t);
+            const int buf = tl & 1;
+            const uint32_t tmem_acc = tmem_base + buf * BN;
+            int got = 0;
+            if (lane == 0) got = tc::mbar_wait(&acc_full[buf], (tl >> 1) & 1, abort_flag, p.err_word, 103) ? 1 : 0;
+            ok = __shfl_sync(0xffffffffu, got, 0) != 0;  // uniform: tcgen05.ld below is warp-aligned
+            if (!ok) break;
+            tc::tcgen05_fence_after();
+            float* cbase = p.C + (p.group_dim == GROUP_K ? (int64_t)x.g * p.c_gstride : 0);
+            const int rows_here = x.M - (x.m0 + q * 32);   // live rows of this warp's quarter (may be <= 0 or > 32)
+            // row bookkeeping of the 4 store iterations: row = 8 * i + rsub
+            int64_t lrs[4], crs[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-                if (nb + j < p.N) bias4[j] = bias[nb + j];
-        }
-        float* cbase = p.C + (p.group_dim == GROUP_K ? (int64_t)g * p.c_gstride : 0);
-        if (ok && nb < p.N) {
-            constexpr int RB = 8;   // rows per batch: their global loads (aux, old C, row map) are all issued before any is used
+            for (int i = 0; i < 4; ++i) {
+                const int rr = 8 * i + rsub;
+                lrs[i] = (int64_t)x.row_base_m + x.m0 + (rr < rows_here ? q * 32 + rr : 0);
+                crs[i] = p.c_idx && rr < rows_here ? (int64_t)p.c_idx[lrs[i]] : lrs[i];
+            }
 #pragma unroll 1
-            for (int r0 = 0; r0 < 32; r0 += RB) {
-                if (m0 + q * 32 + r0 >= M) break;
-                int64_t lrs[RB], crs[RB];
-                float4 aux4[RB], old4[RB];
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                if (x.num_k > 0) {
+                    tc::tmem_ld_32x32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
+                    tc::tmem_ld_wait();
+                } else {
 #pragma unroll
-                for (int i = 0; i < RB; ++i) {
-                    const int m = m0 + q * 32 + r0 + i;
-                    const bool live = m < M;
-                    lrs[i] = (int64_t)row_base_m + (live ? m : m0);
-                    crs[i] = p.c_idx ? (int64_t)p.c_idx[lrs[i]] : lrs[i];
+                    for (int j = 0; j < 32; ++j) r[j] = 0u;
+                }
+                if (c == BN / 32 - 1) {   // this warp's quarter of the buffer is free for the tile after next
+                    tc::tcgen05_fence_before();
+                    __syncwarp();
+                    if (lane == 0) tc::mbar_arrive(&acc_empty[buf]);
                 }
 #pragma unroll
-                for (int i = 0; i < RB; ++i) {
-                    aux4[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                    old4[i] = aux4[i];
-                    if (p.epi == EPI_SILU_BWD) {
-                        const float* ax = p.aux + lrs[i] * p.ldaux + nb;
-                        if (full4 && aux_vec) aux4[i] = *reinterpret_cast<const float4*>(ax);
-                        else {
-                            aux4[i].x = ax[0];
-                            if (nb + 1 < p.N) aux4[i].y = ax[1];
-                            if (nb + 2 < p.N) aux4[i].z = ax[2];
-                            if (nb + 3 < p.N) aux4[i].w = ax[3];
-                        }
-                    }
-                    if (p.accumulate) {
-                        const float* crow = cbase + crs[i] * p.ldc + nb;
-                        if (full4 && c_vec) old4[i] = *reinterpret_cast<const float4*>(crow);
-                        else {
-                            old4[i].x = crow[0];
-                            if (nb + 1 < p.N) old4[i].y = crow[1];
-                            if (nb + 2 < p.N) old4[i].z = crow[2];
-                            if (nb + 3 < p.N) old4[i].w = crow[3];
-                        }
-                    }
-                }
+                for (int hlf = 0; hlf < 2; ++hlf) {
 #pragma unroll
-                for (int i = 0; i < RB; ++i) {
-                    const int rr = r0 + i;
-                    if (m0 + q * 32 + rr >= M) break;
-                    const float4 acc4 = stg[rr * 32 + (lane ^ rr)];
-                    float v[4] = {acc4.x + bias4[0], acc4.y + bias4[1], acc4.z + bias4[2], acc4.w + bias4[3]};
-                    if (p.epi == EPI_SILU_BWD) {
-                        v[0] *= silu_grad_f(aux4[i].x); v[1] *= silu_grad_f(aux4[i].y);
-                        v[2] *= silu_grad_f(aux4[i].z); v[3] *= silu_grad_f(aux4[i].w);
-                    }
-                    v[0] += old4[i].x; v[1] += old4[i].y; v[2] += old4[i].z; v[3] += old4[i].w;
-                    float* crow = cbase + crs[i] * p.ldc + nb;
-                    if (full4 && c_vec) {
-                        *reinterpret_cast<float4*>(crow) = make_float4(v[0], v[1], v[2], v[3]);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            if (nb + j < p.N) crow[j] = v[j];
-                    }
-                    if (p.C2) {
-                        __nv_bfloat16* c2 = p.C2 + lrs[i] * p.ldc2 + nb;
-                        float x[4] = {v[0], v[1], v[2], v[3]};
-                        if (p.epi == EPI_SILU) {
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) x[j] = silu_f(x[j]);
-                        }
-                        if (full4 && c2_vec) {
-                            const __nv_bfloat162 lo2 = __floats2bfloat162_rn(x[0], x[1]), hi2 = __floats2bfloat162_rn(x[2], x[3]);
-                            *reinterpret_cast<uint2*>(c2) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo2),
-                                                                       *reinterpret_cast<const uint32_t*>(&hi2));
-                        } else {
+                    for (int j = 0; j < 4; ++j)
+                        stg[lane * 4 + (j ^ ((lane >> 1) & 3))] =
+                            make_float4(__uint_as_float(r[16 * hlf + 4 * j]), __uint_as_float(r[16 * hlf + 4 * j + 1]),
+                                        __uint_as_float(r[16 * hlf + 4 * j + 2]), __uint_as_float(r[16 * hlf + 4 * j + 3]));
+                    __syncwarp();
+                    const int nb = x.n0 + c * 32 + hlf * 16 + 4 * l4;   // this lane's 4 columns in the store phase
+                    if (nb < p.N) {
+                        const bool full4 = nb + 4 <= p.N;
+                        float bias4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                        if (p.bias) {
+                            const float* bias = p.bias + (int64_t)x.g * p.bias_gstride;
 #pragma unroll
                             for (int j = 0; j < 4; ++j)
-                                if (nb + j < p.N) c2[j] = __float2bfloat16(x[j]);
+                                if (nb + j < p.N) bias4[j] = bias[nb + j];
+                        }
+                        float4 aux4[4], old4[4];   // every global load of the pass is issued before any is used
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            aux4[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                            old4[i] = aux4[i];
+                            if (8 * i + rsub >= rows_here) continue;
+                            if (p.epi == EPI_SILU_BWD) {
+                                const float* ax = p.aux + lrs[i] * p.ldaux + nb;
+                                if (full4 && aux_vec) aux4[i] = *reinterpret_cast<const float4*>(ax);
+                                else {
+                                    aux4[i].x = ax[0];
+                                    if (nb + 1 < p.N) aux4[i].y = ax[1];
+                                    if (nb + 2 < p.N) aux4[i].z = ax[2];
+                                    if (nb + 3 < p.N) aux4[i].w = ax[3];
+                                }
+                            }
+                            if (p.accumulate) {
+                                const float* crow = cbase + crs[i] * p.ldc + nb;
+                                if (full4 && c_vec) old4[i] = *reinterpret_cast<const float4*>(crow);
+                                else {
+                                    old4[i].x = crow[0];
+                                    if (nb + 1 < p.N) old4[i].y = crow[1];
+                                    if (nb + 2 < p.N) old4[i].z = crow[2];
+                                    if (nb + 3 < p.N) old4[i].w = crow[3];
+                                }
+                            }
+                        }
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int rr = 8 * i + rsub;
+                            if (rr >= rows_here) continue;
+                            const float4 acc4 = stg[rr * 4 + (l4 ^ ((rr >> 1) & 3))];
+                            float v[4] = {acc4.x + bias4[0], acc4.y + bias4[1], acc4.z + bias4[2], acc4.w + bias4[3]};
+                            if (p.epi == EPI_SILU_BWD) {
+                                v[0] *= silu_grad_f(aux4[i].x); v[1] *= silu_grad_f(aux4[i].y);
+                                v[2] *= silu_grad_f(aux4[i].z); v[3] *= silu_grad_f(aux4[i].w);
+                            }
+                            v[0] += old4[i].x; v[1] += old4[i].y; v[2] += old4[i].z; v[3] += old4[i].w;
+                            float* crow = cbase + crs[i] * p.ldc + nb;
+                            if (full4 && c_vec) {
+                                *reinterpret_cast<float4*>(crow) = make_float4(v[0], v[1], v[2], v[3]);
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 4; ++j)
+                                    if (nb + j < p.N) crow[j] = v[j];
+                            }
+                            if (p.C2) {
+                                __nv_bfloat16* c2 = p.C2 + lrs[i] * p.ldc2 + nb;
+                                float y[4] = {v[0], v[1], v[2], v[3]};
+                                if (p.epi == EPI_SILU) {
+#pragma unroll
+                                    for (int j = 0; j < 4; ++j) y[j] = silu_f(y[j]);
+                                }
+                                if (full4 && c2_vec) {
+                                    const __nv_bfloat162 lo2 = __floats2bfloat162_rn(y[0], y[1]), hi2 = __floats2bfloat162_rn(y[2], y[3]);
+                                    *reinterpret_cast<uint2*>(c2) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo2),
+                                                                               *reinterpret_cast<const uint32_t*>(&hi2));
+                                } else {
+#pragma unroll
+                                    for (int j = 0; j < 4; ++j)
+                                        if (nb + j < p.N) c2[j] = __float2bfloat16(y[j]);
+                                }
+                            }
                         }
                     }
+                    __syncwarp();   // every lane is done with the staging rows before the next pass overwrites them
                 }
             }
         }
@@ -333,7 +381,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
     tc::tcgen05_fence_before();
     __syncthreads();
     if (*abort_flag) __nanosleep(20000);  // let copies already in flight land before the CTA exits
-    if (warp == 1) tc::tmem_dealloc(tmem_acc, TMEM_COLS);
+    if (warp == 1) tc::tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -376,6 +424,7 @@ bool supported(const Args& a) {
     // grouped coordinate offsets must not let a ragged tile read a neighbouring expert's k range
     if (a.group_dim == GROUP_M && a.mode == ASCA_NT && a.b_goff_inner != 0 && (a.K % BK) != 0) return false;
     if (a.group_dim == GROUP_M && a.mode == ASCA_NN && a.b_goff_outer != 0 && (a.K % BK) != 0) return false;
+    if (a.group_dim != GROUP_NONE && a.n_groups > MAX_GROUPS) return false;
     if (a.group_dim == GROUP_K && a.mode != ASCA_TN) return false;
     if (a.group_dim == GROUP_M && a.mode == ASCA_TN) return false;
     return true;
@@ -403,10 +452,15 @@ int launch(asca_ctx* ctx, const Args& a) {
     else if (a.group_dim == GROUP_M) grid = (a.total_rows / BM + a.n_groups) * tn;
     else grid = (int64_t)a.n_groups * ((a.M + BM - 1) / BM) * tn;
     if (grid <= 0) return ASCA_OK;
+    // persistent: two CTAs per SM walk the tiles round-robin (`grid` is an upper bound on the tile count)
+    int dev = 0, n_sm = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+    if (grid > 2 * n_sm) grid = 2 * n_sm;
+    const size_t smem = SMEM_FIXED + (size_t)((a.group_dim == GROUP_NONE ? 1 : a.n_groups) + 2) * 4;
     auto go = [&](auto kern) -> cudaError_t {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(SMEM_FIXED + (MAX_GROUPS + 2) * 4));
         if (e != cudaSuccess) return e;
-        kern<<<(unsigned)grid, THREADS, SMEM_BYTES, ctx->stream>>>(mapA, mapB, p);
+        kern<<<(unsigned)grid, THREADS, smem, ctx->stream>>>(mapA, mapB, p);
         return cudaGetLastError();
     };
     cudaError_t e = a.mode == ASCA_NN ? go(gemm_tc_kernel<ASCA_NN>)
