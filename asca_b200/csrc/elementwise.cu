@@ -3,6 +3,8 @@
 // Every reduction is a fixed tree (no float atomics), so results are run-to-run identical.
 #include "common.cuh"
 
+#include <cuda_bf16.h>
+
 namespace {
 
 // ------------------------------------------------------------------ RMSNorm
@@ -240,7 +242,7 @@ __global__ void __launch_bounds__(256) adamw_seg_kernel(float* __restrict__ p, c
                                                         const int64_t* __restrict__ seg_off,
                                                         const float* __restrict__ lr_t,
                                                         const float* __restrict__ eps_t, int n_seg, float b1,
-                                                        float b2, float wd) {
+                                                        float b2, float wd, __nv_bfloat16* __restrict__ p16) {
     const int64_t n = seg_off[n_seg];
     const int64_t stride = (int64_t)gridDim.x * blockDim.x * 4;
     const bool vec_ok = ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(m) |
@@ -264,6 +266,11 @@ __global__ void __launch_bounds__(256) adamw_seg_kernel(float* __restrict__ p, c
             *reinterpret_cast<float4*>(p + i) = P;
             *reinterpret_cast<float4*>(m + i) = M;
             *reinterpret_cast<float4*>(v + i) = V;
+            if (p16) {   // bf16 copy of the updated weights for the next step's tensor-core products
+                const __nv_bfloat162 lo2 = __floats2bfloat162_rn(P.x, P.y), hi2 = __floats2bfloat162_rn(P.z, P.w);
+                *reinterpret_cast<uint2*>(p16 + i) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo2),
+                                                                *reinterpret_cast<const uint32_t*>(&hi2));
+            }
             continue;
         }
         const int64_t end = i + 4 < n ? i + 4 : n;
@@ -274,6 +281,7 @@ __global__ void __launch_bounds__(256) adamw_seg_kernel(float* __restrict__ p, c
                 ep = eps_t[s];
             }
             adamw_one(p[j], g[j], m[j], v[j], lr, b1, b2, ep, wd);
+            if (p16) p16[j] = __float2bfloat16(p[j]);
         }
     }
 }
@@ -422,9 +430,20 @@ int asca_adamw(asca_ctx* ctx, float* p, const float* g, float* m, float* v, int6
     return ASCA_OK;
 }
 
+int asca_adamw_segmented_cast(asca_ctx* ctx, float* p, const float* g, float* m, float* v, const int64_t* seg_off,
+                              const float* lr_t, const float* eps_t, int n_seg, float beta1, float beta2, float wd_eff,
+                              void* p_bf16);
+
 int asca_adamw_segmented(asca_ctx* ctx, float* p, const float* g, float* m, float* v, const int64_t* seg_off,
                          const float* lr_t, const float* eps_t, int n_seg, float beta1, float beta2, float wd_eff) {
+    return asca_adamw_segmented_cast(ctx, p, g, m, v, seg_off, lr_t, eps_t, n_seg, beta1, beta2, wd_eff, nullptr);
+}
+
+int asca_adamw_segmented_cast(asca_ctx* ctx, float* p, const float* g, float* m, float* v, const int64_t* seg_off,
+                              const float* lr_t, const float* eps_t, int n_seg, float beta1, float beta2, float wd_eff,
+                              void* p_bf16) {
     if (!ctx) return ASCA_ERR_ARG;
+    ASCA_REQUIRE(ctx, (reinterpret_cast<uintptr_t>(p_bf16) & 7) == 0, "adamw_segmented: bf16 copy must be 8-byte aligned");
     ASCA_REQUIRE(ctx, p && g && m && v && seg_off && lr_t && eps_t && n_seg > 0, "adamw_segmented: bad arguments");
     for (int i = 0; i < n_seg; ++i)
         ASCA_REQUIRE(ctx, seg_off[i] <= seg_off[i + 1], "adamw_segmented: offsets must be non-decreasing");
@@ -444,7 +463,7 @@ int asca_adamw_segmented(asca_ctx* ctx, float* p, const float* g, float* m, floa
     if (blocks > cap) blocks = cap;
     adamw_seg_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(p, g, m, v, (const int64_t*)w, (const float*)(w + off_b),
                                                                  (const float*)(w + off_b + f_b), n_seg, beta1, beta2,
-                                                                 wd_eff);
+                                                                 wd_eff, (__nv_bfloat16*)p_bf16);
     ASCA_CHECK_LAUNCH(ctx);
     return ASCA_OK;
 }

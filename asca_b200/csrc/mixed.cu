@@ -73,6 +73,8 @@ __global__ void __launch_bounds__(256) rmsnorm_bf16_warp_kernel(const float* __r
 }
 
 // rust/src/delta.rs:134-179 with bf16 q, k, v outputs. One warp per (row, head); norms and gates f32.
+// VEC: head dim 128 -- every lane holds 4 consecutive elements of q, k and v, read once.
+template <bool VEC>
 __global__ void __launch_bounds__(256) delta_prep_bf16_kernel(const float* __restrict__ qkv, const float* __restrict__ gate,
                                                               int64_t N, int H, int dh, __nv_bfloat16* __restrict__ q,
                                                               __nv_bfloat16* __restrict__ k, __nv_bfloat16* __restrict__ v,
@@ -85,20 +87,34 @@ __global__ void __launch_bounds__(256) delta_prep_bf16_kernel(const float* __res
     const int h = (int)(unit % H);
     const int d = H * dh;
     const float* src = qkv + r * 3 * (int64_t)d + h * dh;
-    float sq = 0.0f, sk = 0.0f;
-    for (int c = lane; c < dh; c += 32) {
-        const float a = src[c], b = src[d + c];
-        sq += a * a;
-        sk += b * b;
-    }
-    sq = warp_sum(sq);
-    sk = warp_sum(sk);
-    const float nq = fmaxf(sqrtf(sq), 1e-8f), nk = fmaxf(sqrtf(sk), 1e-8f);
     const int64_t o = r * (int64_t)d + h * dh;
-    for (int c = lane; c < dh; c += 32) {
-        q[o + c] = __float2bfloat16(src[c] / nq);
-        k[o + c] = __float2bfloat16(src[d + c] / nk);
-        v[o + c] = __float2bfloat16(src[2 * d + c]);
+    float nq, nk;
+    if (VEC) {
+        const float4 a = reinterpret_cast<const float4*>(src)[lane], b = reinterpret_cast<const float4*>(src + d)[lane],
+                     c = reinterpret_cast<const float4*>(src + 2 * d)[lane];
+        const float sq = warp_sum(a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w);
+        const float sk = warp_sum(b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w);
+        nq = fmaxf(sqrtf(sq), 1e-8f);
+        nk = fmaxf(sqrtf(sk), 1e-8f);
+        reinterpret_cast<uint2*>(q + o)[lane] = pack4_bf16(a.x / nq, a.y / nq, a.z / nq, a.w / nq);
+        reinterpret_cast<uint2*>(k + o)[lane] = pack4_bf16(b.x / nk, b.y / nk, b.z / nk, b.w / nk);
+        reinterpret_cast<uint2*>(v + o)[lane] = pack4_bf16(c.x, c.y, c.z, c.w);
+    } else {
+        float sq = 0.0f, sk = 0.0f;
+        for (int c = lane; c < dh; c += 32) {
+            const float a = src[c], b = src[d + c];
+            sq += a * a;
+            sk += b * b;
+        }
+        sq = warp_sum(sq);
+        sk = warp_sum(sk);
+        nq = fmaxf(sqrtf(sq), 1e-8f);
+        nk = fmaxf(sqrtf(sk), 1e-8f);
+        for (int c = lane; c < dh; c += 32) {
+            q[o + c] = __float2bfloat16(src[c] / nq);
+            k[o + c] = __float2bfloat16(src[d + c] / nk);
+            v[o + c] = __float2bfloat16(src[2 * d + c]);
+        }
     }
     if (lane == 0) {
         qn[r * H + h] = nq;
@@ -146,8 +162,14 @@ int asca_delta_prep_bf16(asca_ctx* ctx, const float* qkv, const float* gate, int
     ASCA_REQUIRE(ctx, qkv && gate && q && k && v && qnorm && knorm && alpha && beta && N >= 0 && H > 0 && dh > 0,
                  "delta_prep_bf16: bad arguments");
     if (N == 0) return ASCA_OK;
-    delta_prep_bf16_kernel<<<(unsigned)ceil_div64(N * H, 8), 256, 0, ctx->stream>>>(
-        qkv, gate, N, (int)H, (int)dh, (__nv_bfloat16*)q, (__nv_bfloat16*)k, (__nv_bfloat16*)v, qnorm, knorm, alpha, beta);
+    const bool vec = dh == 128 && (reinterpret_cast<uintptr_t>(qkv) & 15) == 0 &&
+                     ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 7) == 0;
+    if (vec)
+        delta_prep_bf16_kernel<true><<<(unsigned)ceil_div64(N * H, 8), 256, 0, ctx->stream>>>(
+            qkv, gate, N, (int)H, (int)dh, (__nv_bfloat16*)q, (__nv_bfloat16*)k, (__nv_bfloat16*)v, qnorm, knorm, alpha, beta);
+    else
+        delta_prep_bf16_kernel<false><<<(unsigned)ceil_div64(N * H, 8), 256, 0, ctx->stream>>>(
+            qkv, gate, N, (int)H, (int)dh, (__nv_bfloat16*)q, (__nv_bfloat16*)k, (__nv_bfloat16*)v, qnorm, knorm, alpha, beta);
     ASCA_CHECK_LAUNCH(ctx);
     return ASCA_OK;
 }

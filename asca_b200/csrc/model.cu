@@ -372,14 +372,19 @@ int asca_colsum(asca_ctx* ctx, const float* src, int64_t ld, int64_t rows, int64
     if (n_slices < 1) n_slices = 1;
     const int64_t rps = ceil_div64(rows, n_slices);
     n_slices = ceil_div64(rows, rps);
+    // partial sums from the block pool, not the context's scratch area: callers (the expert-FFN backward) may
+    // be holding that; the block goes back to the pool at once and is reused only by later work on the stream
     void* ws;
-    ASCA_TRY(asca_workspace(ctx, (size_t)n_slices * cols * 4 + 256, &ws));
+    ASCA_TRY(asca_malloc(ctx, (size_t)n_slices * cols * 4 + 256, &ws));
     colsum_slices_kernel<<<dim3((unsigned)col_blocks, (unsigned)n_slices), 256, 0, ctx->stream>>>(src, ld, rows, (int)cols, rps,
                                                                                                (float*)ws);
-    ASCA_CHECK_LAUNCH(ctx);
+    ctx->launches++;
     colsum_finish_kernel<<<(unsigned)ceil_div64(cols, 256), 256, 0, ctx->stream>>>((const float*)ws, (int)n_slices, (int)cols, out,
                                                                                   accumulate);
-    ASCA_CHECK_LAUNCH(ctx);
+    const cudaError_t le = cudaGetLastError();
+    asca_free(ctx, ws);
+    ASCA_CUDA(ctx, le);
+    ctx->launches++;
     return ASCA_OK;
 }
 
@@ -656,9 +661,11 @@ int asca_model_adamw_step(asca_ctx* ctx, asca_model* m, float lr, float beta1, f
         lr_t[i] = lr * sqrtf(bc1 / bc2);
         eps_t[i] = eps * sqrtf(bc2);
     }
-    m->params16_stale = true;
-    return asca_adamw_segmented(ctx, m->params, m->grads, m->m, m->v, m->seg_off.data(), lr_t.data(), eps_t.data(), n_seg,
-                                beta1, beta2, lr * wd);
+    // bf16 mode with an unpadded copy: the update writes the bf16 weights itself
+    const bool fuse = m->compute == ASCA_BF16 && m->params16 && m->n16 == m->n_params;
+    m->params16_stale = !fuse;
+    return asca_adamw_segmented_cast(ctx, m->params, m->grads, m->m, m->v, m->seg_off.data(), lr_t.data(), eps_t.data(), n_seg,
+                                     beta1, beta2, lr * wd, fuse ? (void*)m->params16 : nullptr);
 }
 
 int asca_model_decode_step_host(asca_ctx* ctx, asca_model* m, float* state, const uint32_t* ids_h, int64_t ns,

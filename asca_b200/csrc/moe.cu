@@ -192,8 +192,7 @@ int moe_bwd_tc(asca_ctx* ctx, const __nv_bfloat16* xn, const __nv_bfloat16* w1, 
     ASCA_CHECK_LAUNCH(ctx);
     gather_rows_f32_to_bf16_kernel<<<(unsigned)ceil_div64(N, 8), 256, 0, s>>>(dout, perm, dout_p, N, (int)d);
     ASCA_CHECK_LAUNCH(ctx);
-    colsum_kernel<<<dim3((unsigned)ceil_div64(d, 32), 1), 256, 0, s>>>(dout, d, nullptr, nullptr, N, (int)d, d_b2, 0, acc);
-    ASCA_CHECK_LAUNCH(ctx);
+    ASCA_TRY(asca_colsum(ctx, dout, d, N, d, d_b2, acc));   // row-sliced, deterministic
     ASCA_TRY(gemm_tc::launch(ctx, g1));
     ASCA_TRY(gemm_tc::launch(ctx, g2));
     colsum_kernel<<<dim3((unsigned)ceil_div64(F, 32), (unsigned)E), 256, 0, s>>>(dpre_p, F, nullptr, offsets, N, (int)F, d_b1, F, acc);
@@ -275,8 +274,7 @@ static int moe_bwd_impl(asca_ctx* ctx, const void* xn, const void* w1, const voi
     float* dpre_p = (float*)ws;
 
     // d_b2[c] = sum over all tokens of dout[t,c]
-    colsum_kernel<<<dim3((unsigned)ceil_div64(d, 32), 1), 256, 0, s>>>(dout, d, nullptr, nullptr, N, (int)d, d_b2, 0, acc);
-    ASCA_CHECK_LAUNCH(ctx);
+    ASCA_TRY(asca_colsum(ctx, dout, d, N, d, d_b2, acc));   // row-sliced, deterministic
     // d_w2[eF+j, c] = sum_r hid_p[r,j] dout[perm[r],c]      (TN, K = rows of expert e)
     {
         gemm::Params p{};

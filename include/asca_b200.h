@@ -129,6 +129,11 @@ int asca_adamw(asca_ctx* ctx, float* p, const float* g, float* m, float* v, int6
 int asca_adamw_segmented(asca_ctx* ctx, float* p, const float* g, float* m, float* v,
                          const int64_t* seg_off, const float* lr_t, const float* eps_t,
                          int n_seg, float beta1, float beta2, float wd_eff);
+/* Same update; when p_bf16 is not NULL the updated parameters are also written there as bf16 (same
+ * offsets), which saves the separate cast pass of the bf16 compute mode. */
+int asca_adamw_segmented_cast(asca_ctx* ctx, float* p, const float* g, float* m, float* v,
+                              const int64_t* seg_off, const float* lr_t, const float* eps_t, int n_seg,
+                              float beta1, float beta2, float wd_eff, void* p_bf16);
 int asca_adamw_host(asca_ctx* ctx, float* p, const float* g, float* m, float* v, int64_t n,
                     float lr_t, float beta1, float beta2, float eps_t, float wd_eff);
 
