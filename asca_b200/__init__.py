@@ -328,6 +328,22 @@ class Model:
         """F32 (default) or BF16: tensor-core products on a bf16 copy of the weights, f32 everything else."""
         self.gpu._call("asca_model_set_compute", self.gpu._ctx, self._h, C.c_int(dtype))
 
+    def set_grad_scale(self, scale: float):
+        """Scale of dLoss/dlogits (1 / micro-batches when gradients are accumulated over several calls)."""
+        self.gpu._call("asca_model_set_grad_scale", self._h, _f(scale))
+
+    def set_grad_hook(self, fn):
+        """fn(offset, count) is called from inside forward_backward each time the kernels writing
+        grads[offset:offset+count] have all been enqueued (one block at a time, last block first, then
+        embedding + head). None removes the hook."""
+        if fn is None:
+            self._hook = None
+            self.gpu._call("asca_model_set_grad_hook", self._h, None, None)
+            return
+        proto = C.CFUNCTYPE(None, C.c_void_p, C.c_int64, C.c_int64)
+        self._hook = proto(lambda _user, off, cnt: fn(int(off), int(cnt)))   # kept alive with the model
+        self.gpu._call("asca_model_set_grad_hook", self._h, self._hook, None)
+
     def params_changed(self):
         """Tell the model that the flat parameter buffer was written through :meth:`buffers`."""
         self.gpu._call("asca_model_params_changed", self._h)

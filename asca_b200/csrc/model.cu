@@ -209,7 +209,18 @@ struct asca_model {
     // of adding to it (each tensor is written exactly once per backward), which saves the clearing pass and the
     // read half of the accumulation. Anything that exposes the buffer earlier clears it for real first.
     bool grads_zero_pending = false;
+    // called during the backward, on the host, each time a contiguous range of the gradient buffer has had all its
+    // kernels enqueued (one block's tensors, last block first, then embedding + head): the data-parallel
+    // exchange of that range can be queued behind them while the rest of the backward is still running
+    float grad_scale = 1.0f;   // multiplies dLoss/dlogits: 1 / micro-batches when gradients are accumulated
+    asca_grad_ready_fn grad_hook = nullptr;
+    void* grad_hook_user = nullptr;
 };
+
+extern "C" {
+static int cross_entropy_scaled(asca_ctx* ctx, const float* logits, const uint32_t* targets, int64_t N, int64_t V,
+                                float* dlogits, float* loss, float grad_scale);
+}
 
 static int materialize_zero_grads(asca_ctx* ctx, asca_model* m) {
     if (!m->grads_zero_pending) return ASCA_OK;
@@ -306,7 +317,7 @@ static int forward_backward_bf16(asca_ctx* ctx, asca_model* m, const uint32_t* i
     ASCA_TRY(asca_residual_rmsnorm_bf16(ctx, x, nullptr, nullptr, h_final, N, d, 1e-6f));
     ASCA_TRY(asca_gemm(ctx, ASCA_NN, N, V, d, h_final, d, W + m->head16, V, logits, V, nullptr, 0, BF));
     if (logits_h) ASCA_CUDA(ctx, cudaMemcpyAsync(logits_h, logits, (size_t)N * V * 4, cudaMemcpyDeviceToHost, ctx->stream));
-    ASCA_TRY(asca_cross_entropy(ctx, logits, tg, N, V, dlogits, loss_d));
+    ASCA_TRY(cross_entropy_scaled(ctx, logits, tg, N, V, dlogits, loss_d, m->grad_scale));
     ASCA_CUDA(ctx, cudaMemcpyAsync(loss_h, loss_d, 4, cudaMemcpyDeviceToHost, ctx->stream));
     ASCA_TRY(asca_cast_bf16(ctx, dlogits, dl16, N * V));
     ASCA_TRY(asca_gemm(ctx, ASCA_TN, d, V, N, h_final, d, dl16, V, G + m->head, V, nullptr, acc, BF));
@@ -349,9 +360,11 @@ static int forward_backward_bf16(asca_ctx* ctx, asca_model* m, const uint32_t* i
         ASCA_TRY(asca_colsum(ctx, d_gate, 2 * H, N, 2 * H, G + w.b_gate, acc));
         ASCA_TRY(asca_gemm(ctx, ASCA_NT, N, d, 3 * d, dqkv16, 3 * d, W + w16.w_qkv, 3 * d, dx, d, nullptr, 1, BF));
         ASCA_TRY(asca_gemm(ctx, ASCA_NT, N, d, 2 * H, dg16, 2 * H, W + w16.w_gate, 2 * H, dx, d, nullptr, 1, BF));
+        if (m->grad_hook) m->grad_hook(m->grad_hook_user, w.w_qkv, (li + 1 < L ? m->lay[li + 1].w_qkv : m->n_params) - w.w_qkv);
     }
     if (!acc) ASCA_CUDA(ctx, cudaMemsetAsync(G + m->embed, 0, (size_t)V * d * 4, ctx->stream));
     ASCA_TRY(asca_embed_bwd(ctx, dx, ids, N, d, V, G + m->embed));
+    if (m->grad_hook) m->grad_hook(m->grad_hook_user, 0, m->lay[0].w_qkv);   // embedding + head
     ASCA_CUDA(ctx, cudaGetLastError());
     return asca_ctx_sync(ctx);
 }
@@ -390,12 +403,18 @@ int asca_colsum(asca_ctx* ctx, const float* src, int64_t ld, int64_t rows, int64
 
 int asca_cross_entropy(asca_ctx* ctx, const float* logits, const uint32_t* targets, int64_t N, int64_t V,
                        float* dlogits, float* loss) {
+    return cross_entropy_scaled(ctx, logits, targets, N, V, dlogits, loss, 1.0f);
+}
+
+// grad_scale multiplies dlogits only (1 / micro-batches under gradient accumulation); the loss stays the token mean
+static int cross_entropy_scaled(asca_ctx* ctx, const float* logits, const uint32_t* targets, int64_t N, int64_t V,
+                                float* dlogits, float* loss, float grad_scale) {
     if (!ctx) return ASCA_ERR_ARG;
     ASCA_REQUIRE(ctx, logits && targets && loss && N > 0 && V > 0, "cross_entropy: bad arguments");
     void* ws;
     ASCA_TRY(asca_workspace(ctx, (size_t)N * 4 + 256, &ws));
     cross_entropy_kernel<<<(unsigned)ceil_div64(N, 8), 256, 0, ctx->stream>>>(logits, targets, N, (int)V, dlogits,
-                                                                              (float*)ws, 1.0f / (float)N);
+                                                                              (float*)ws, grad_scale / (float)N);
     ASCA_CHECK_LAUNCH(ctx);
     mean_kernel<<<1, 1024, 0, ctx->stream>>>((const float*)ws, N, 1.0f / (float)N, loss);
     ASCA_CHECK_LAUNCH(ctx);
@@ -501,6 +520,19 @@ int asca_model_set_compute(asca_ctx* ctx, asca_model* m, int dtype) {
     return ASCA_OK;
 }
 
+int asca_model_set_grad_scale(asca_model* m, float scale) {
+    if (!m) return ASCA_ERR_ARG;
+    m->grad_scale = scale;
+    return ASCA_OK;
+}
+
+int asca_model_set_grad_hook(asca_model* m, asca_grad_ready_fn fn, void* user) {
+    if (!m) return ASCA_ERR_ARG;
+    m->grad_hook = fn;
+    m->grad_hook_user = user;
+    return ASCA_OK;
+}
+
 int asca_model_params_changed(asca_model* m) {
     if (!m) return ASCA_ERR_ARG;
     m->params16_stale = true;
@@ -598,7 +630,7 @@ int asca_model_forward_backward_host(asca_ctx* ctx, asca_model* m, const uint32_
     ASCA_TRY(asca_gemm(ctx, ASCA_NN, N, V, d, h_final, d, P + m->head, V, logits, V, nullptr, 0, ASCA_F32));
     if (logits_h) ASCA_CUDA(ctx, cudaMemcpyAsync(logits_h, logits, (size_t)N * V * 4, cudaMemcpyDeviceToHost, ctx->stream));
     // ---- backward (rust/src/model.rs:744-794)
-    ASCA_TRY(asca_cross_entropy(ctx, logits, tg, N, V, dlogits, loss_d));
+    ASCA_TRY(cross_entropy_scaled(ctx, logits, tg, N, V, dlogits, loss_d, m->grad_scale));
     ASCA_CUDA(ctx, cudaMemcpyAsync(loss_h, loss_d, 4, cudaMemcpyDeviceToHost, ctx->stream));
     ASCA_TRY(asca_gemm(ctx, ASCA_TN, d, V, N, h_final, d, dlogits, V, G + m->head, V, nullptr, acc, ASCA_F32));
     float* dh_ = bf.f(N * d);
@@ -634,9 +666,11 @@ int asca_model_forward_backward_host(asca_ctx* ctx, asca_model* m, const uint32_
         // dx = d_mid + d_qkv Wqkv^T + d_gate Wg^T   (accumulate onto d_mid in place)
         ASCA_TRY(asca_gemm(ctx, ASCA_NT, N, d, 3 * d, d_qkv, 3 * d, P + w.w_qkv, 3 * d, dx, d, nullptr, 1, ASCA_F32));
         ASCA_TRY(asca_gemm(ctx, ASCA_NT, N, d, 2 * H, d_gate, 2 * H, P + w.w_gate, 2 * H, dx, d, nullptr, 1, ASCA_F32));
+        if (m->grad_hook) m->grad_hook(m->grad_hook_user, w.w_qkv, (li + 1 < L ? m->lay[li + 1].w_qkv : m->n_params) - w.w_qkv);
     }
     if (!acc) ASCA_CUDA(ctx, cudaMemsetAsync(G + m->embed, 0, (size_t)V * d * 4, ctx->stream));
     ASCA_TRY(asca_embed_bwd(ctx, dx, ids, N, d, V, G + m->embed));
+    if (m->grad_hook) m->grad_hook(m->grad_hook_user, 0, m->lay[0].w_qkv);   // embedding + head
     ASCA_CUDA(ctx, cudaGetLastError());
     return asca_ctx_sync(ctx);
 }

@@ -54,3 +54,49 @@ def allreduce_model_grads(model, local_tokens: int, global_tokens: int, group=No
     grads = device_tensor(model.buffers()[1], model.n, model.gpu.device)
     model.gpu.sync()
     allreduce_mean_(grads, local_tokens / global_tokens, group)
+
+
+class GradOverlap:
+    """All-reduce (average) of an asca_b200.Model's flat gradient buffer, overlapped with its backward.
+
+    The model reports each finished gradient range from inside ``forward_backward`` (one block at a
+    time, last block first). For every range this records an event on the compute stream, makes a
+    side stream wait for it and queues ``all_reduce(AVG)`` of that slice there, so the exchange of
+    block i runs under the backward of blocks i-1 .. 0. ``finish()`` makes the compute stream wait
+    for the exchanges; AdamW queued after it sees the averaged gradients.
+
+    With gradient accumulation, arm it only around the last micro-batch (``with overlap:``).
+    """
+
+    def __init__(self, model, group=None):
+        self.model, self.group = model, group
+        dev = model.gpu.device
+        self.grads = device_tensor(model.buffers()[1], model.n, dev)
+        self.side = torch.cuda.Stream(device=dev)
+        self.works = []
+        self.ranges = []
+
+    def _ready(self, off, cnt):
+        self.ranges.append((off, cnt))
+        if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(self.group) == 1:
+            return
+        ev = torch.cuda.current_stream().record_event()
+        self.side.wait_event(ev)
+        with torch.cuda.stream(self.side):
+            self.works.append(dist.all_reduce(self.grads[off:off + cnt], op=dist.ReduceOp.AVG, group=self.group, async_op=True))
+
+    def __enter__(self):
+        self.ranges = []
+        self.model.set_grad_hook(self._ready)
+        return self
+
+    def __exit__(self, *exc):
+        self.model.set_grad_hook(None)
+        self.finish()
+        return False
+
+    def finish(self):
+        for w in self.works:
+            w.wait()          # stream-level wait on the side stream
+        self.works = []
+        torch.cuda.current_stream().wait_stream(self.side)

@@ -60,7 +60,6 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--only", default="")
     ap.add_argument("--reps", type=int, default=20)
-    ap.add_argument("--layers", type=int, default=2, help="layers of the 1.3B-class architecture in the `train` case")
     args = ap.parse_args()
     only = set(filter(None, args.only.split(",")))
     want = lambda n: not only or n in only  # noqa: E731
@@ -165,52 +164,6 @@ def main():
             ms = timeit(lambda i: ops.moe_bwd(gpu, xn, w1, w2, pre_p, hid_p, dout, perm, off, F, E, grads=grads), 3, warmup=1)
             report(f"moe_bwd {str(dt).split('.')[-1]} (4 grouped GEMMs + 2 column sums)", ms, flops=8 * n * d * F,
                    note="config 3, Zipf load")
-
-    if "train" in only:   # opt-in: allocates 20 GB per layer
-        # the 1.3B-class architecture (d 2048, 16 heads of 128, 64 experts of 2048 -> 4096 -> 2048, byte
-        # vocabulary) cut to --layers blocks; 8 sequences x 4096 uniform random bytes; bf16 compute mode
-        import time
-
-        from asca_b200 import dp
-
-        V, d, H, L, E, F = 256, 2048, 16, args.layers, 64, 4096
-        B, T = 8, 4096
-        model = asca_b200.Model(gpu, V, d, H, L, E, F)
-        model.set_compute(asca_b200.BF16)
-        params = dp.device_tensor(model.buffers()[0], model.n, 0)
-        for lo in range(0, model.n, 1 << 28):   # N(0, 0.02) everywhere, generated on the device
-            hi = min(model.n, lo + (1 << 28))
-            params[lo:hi] = torch.randn(hi - lo, generator=g, **f32) * 0.02
-        model.params_changed()
-        ids = torch.randint(0, 256, (B, T), generator=torch.Generator().manual_seed(1)).numpy().astype("uint32")
-        tg = ids.copy()
-        tg[:, :-1] = ids[:, 1:]
-        steps = max(2, args.reps // 10)
-        t_fb = t_opt = 0.0
-        for i in range(steps + 1):
-            model.zero_grads()
-            torch.cuda.synchronize()
-            t0 = time.perf_counter()
-            loss = model.forward_backward(ids.reshape(-1), tg.reshape(-1), B)
-            t1 = time.perf_counter()
-            model.adamw_step(3e-4)
-            gpu.sync()
-            t2 = time.perf_counter()
-            if i:   # first step warms the pools up
-                t_fb += t1 - t0
-                t_opt += t2 - t1
-        t_fb, t_opt = t_fb / steps, t_opt / steps
-        per_layer = 12582912 + 65536 + 4194304 + 2 * d * F
-        flop_tok = 6 * (L * per_layer + d * V) + 22 * (d // H) ** 2 * H * L
-        n_tok = B * T
-        _, tf, src = peaks()
-        print(json.dumps({"case": "train step, 1.3B-class architecture", "layers": L, "params": model.n, "tokens": n_tok,
-                          "loss": round(float(loss), 4), "fwd_bwd_ms": round(t_fb * 1e3, 2), "adamw_ms": round(t_opt * 1e3, 2),
-                          "tok_s": round(n_tok / (t_fb + t_opt), 1), "algorithmic_flop_per_token": flop_tok,
-                          "TFLOP/s": round(n_tok * flop_tok / (t_fb + t_opt) / 1e12, 1),
-                          "frac_of_bf16_peak": round(n_tok * flop_tok / (t_fb + t_opt) / 1e12 / tf, 4), "peak": src,
-                          "TFLOP/s_fwd_bwd_only": round(n_tok * flop_tok / t_fb / 1e12, 1)}), flush=True)
-        model.free()
 
 
 if __name__ == "__main__":

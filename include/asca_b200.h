@@ -318,6 +318,17 @@ int64_t asca_model_num_params(const asca_model* m);
 /* Device pointers of the flat buffers (params, grads, Adam m, Adam v), each num_params floats. */
 int asca_model_buffers(asca_model* m, float** params, float** grads, float** adam_m, float** adam_v);
 int asca_model_set_compute(asca_ctx* ctx, asca_model* m, int dtype);
+/* Data-parallel overlap (the NCCL gradient all-reduce of the flat buffer, overlapped with the backward):
+ * `fn(user, offset, count)` is called on the host, from inside asca_model_forward_backward_host, each
+ * time every kernel that writes grads[offset, offset+count) has been enqueued on the context's stream --
+ * one call per block, last block first, then one for embedding + head; together they cover the buffer
+ * exactly once. The callee typically records an event on that stream and queues the exchange of the
+ * range on another stream. NULL removes the hook. */
+/* Gradient accumulation over k micro-batches: with scale = 1/k every backward adds its share of the
+ * mean over all k micro-batches (the loss returned stays the mean over the micro-batch's own tokens). */
+int asca_model_set_grad_scale(asca_model* m, float scale);
+typedef void (*asca_grad_ready_fn)(void* user, int64_t offset, int64_t count);
+int asca_model_set_grad_hook(asca_model* m, asca_grad_ready_fn fn, void* user);
 /* Call after writing the parameter buffer directly (asca_model_buffers): derived copies are rebuilt. */
 int asca_model_params_changed(asca_model* m);
 int asca_model_set_params_host(asca_ctx* ctx, asca_model* m, const float* params);

@@ -130,3 +130,33 @@ def test_bf16_compute_train_step_within_tolerance(orc, gpu):
     loss2 = dev.forward_backward(ids, tg, B)
     assert abs(loss2 - loss_ref2) / abs(loss_ref2) < 2e-2
     dev.free()
+
+
+def test_grad_hook_covers_the_buffer_once_and_accumulation_scales(orc, gpu):
+    """The gradient-ready hook reports disjoint ranges that tile the flat buffer (last block first), and
+    two accumulated micro-batches with grad scale 1/2 give the gradient of the whole batch."""
+    import asca_b200
+    from asca_b200 import dp
+
+    ref, dev = _setup(orc, gpu, "n002")
+    rng = orc.Rng(9)
+    B, T = 4, 64
+    ids = rng.below(256, B * T)
+    tg = np.concatenate([ids.reshape(B, T)[:, 1:], rng.below(256, (B, 1))], axis=1).reshape(-1).astype(np.uint32)
+    _, g_ref = ref.forward_backward(ids, tg, B)
+    ov = dp.GradOverlap(dev)
+    dev.set_grad_scale(0.5)
+    dev.zero_grads()
+    half = B // 2 * T
+    dev.forward_backward(ids[:half], tg[:half], B // 2)
+    with ov:
+        dev.forward_backward(ids[half:], tg[half:], B // 2)
+    dev.set_grad_scale(1.0)
+    rs = sorted(ov.ranges)
+    assert rs[0][0] == 0 and all(a + n == b for (a, n), (b, _) in zip(rs, rs[1:])) and rs[-1][0] + rs[-1][1] == dev.n
+    assert ov.ranges[0][0] > ov.ranges[1][0] > 0 and ov.ranges[-1][0] == 0     # last block first, embedding + head last
+    _, g = dev.get()
+    for name in ref.names:
+        a, b = ref.tensor(name, g), ref.tensor(name, g_ref)
+        assert rel_err(a, b) < 2e-5, name
+    dev.free()
