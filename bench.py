@@ -179,6 +179,15 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch at B=2, H=16, T=4096, dh=128 (32 chains), divided by 32:
+# traffic is proportional to the number of chains (profiles/delta_tc_bf16_cfg2.md).
+NCU_TRAFFIC_PER_CHAIN = {
+    ("bf16", "delta_bwd_tc_kernel"): (438.934784e6 + 179.197440e6) / 32,
+    ("bf16", "delta_fwd_tc_kernel"): (151.054336e6 + 63.292160e6) / 32,
+    ("bf16", "delta_prep_tc_kernel"): (102.092288e6 + 310.865920e6) / 32,
+}
+
+
 # ------------------------------------------------------------------ our arm (GPU)
 def run_ours(args):
     import torch
@@ -334,9 +343,12 @@ def run_ours(args):
             "kernels_ms": kern_ms, "kernel_launches_per_step": {k_: v_ / args.steps for k_, v_ in kern_n.items()},
             "kernel_share": share,
             "roofline": {"kernel": top, "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "peak_source": which, "traffic": None,
+                         "frac": achieved / peak, "peak_source": which,
+                         "traffic": NCU_TRAFFIC_PER_CHAIN.get((args.dtype, top), 0) * b * h * t / 4096 or None,
                          "algorithmic_bytes": top_bytes,
-                         "note": "algorithmic bytes of the op the kernel belongs to / that kernel's mean CUDA-event time"},
+                         "note": "algorithmic bytes of the op the kernel belongs to / that kernel's mean CUDA-event time; "
+                                 "traffic = dram bytes read + written per launch, from one ncu capture at B=2 scaled by the "
+                                 "number of (sequence, head) chains (profiles/)"},
             "cpu_baseline": {"value": cpu_tok, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": world * b * t / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "api": api},
