@@ -217,6 +217,69 @@ struct asca_model {
     void* grad_hook_user = nullptr;
 };
 
+// Decode step in bf16 compute mode: same dataflow as Model::step (rust/src/model.rs:703-720) for ns streams at
+// once, products on the tensor cores from the bf16 weight copy, the expert FFN through the dispatch + grouped
+// GEMM path (every expert's weights are read once per step, not once per stream); state, residual stream and
+// logits stay f32.
+static int decode_step_bf16(asca_ctx* ctx, asca_model* m, float* state, const uint32_t* ids_h, int64_t ns, float* logits_h,
+                            uint32_t* next_h) {
+    typedef __nv_bfloat16 bf16;
+    const int64_t d = m->d, H = m->H, dh = d / H, E = m->E, F = m->F, V = m->vocab;
+    const int BF = ASCA_BF16;
+    if (!m->params16) {
+        if (cudaMalloc((void**)&m->params16, (size_t)m->n16 * 2) != cudaSuccess)
+            return asca_fail(ctx, ASCA_ERR_OOM, "model: cannot allocate the bf16 weight copy");
+        m->params16_stale = true;
+    }
+    if (m->params16_stale) {
+        if (m->n16 == m->n_params) {
+            ASCA_TRY(asca_cast_bf16(ctx, m->params, m->params16, m->n_params));
+        } else {
+            for (size_t i = 0; i + 1 < m->seg_off.size(); ++i)
+                ASCA_TRY(asca_cast_bf16(ctx, m->params + m->seg_off[i], m->params16 + m->seg16[i], m->seg_off[i + 1] - m->seg_off[i]));
+        }
+        m->params16_stale = false;
+    }
+    const float* P = m->params;
+    const bf16* W = m->params16;
+    Bufs bf(ctx);
+    auto h16 = [&](int64_t n) { return (bf16*)bf.f((n + 1) / 2); };
+    uint32_t* ids = (uint32_t*)bf.f(ns);
+    uint32_t* nxt = (uint32_t*)bf.f(ns);
+    int32_t* perm = (int32_t*)bf.f(ns);
+    int32_t* offs = (int32_t*)bf.f(E + 1);
+    float *x = bf.f(ns * d), *qkv = bf.f(ns * 3 * d), *gate = bf.f(ns * 2 * H), *o = bf.f(ns * d), *y = bf.f(ns * d),
+          *x_mid = bf.f(ns * d), *mo = bf.f(ns * d), *logits = bf.f(ns * V), *pre_p = bf.f(ns * F);
+    bf16 *x16 = h16(ns * d), *o16 = h16(ns * d), *xn16 = h16(ns * d), *hid16 = h16(ns * F), *hf16 = h16(ns * d);
+    ASCA_REQUIRE(ctx, ids && nxt && perm && offs && x && qkv && gate && o && y && x_mid && mo && logits && pre_p && x16 && o16 &&
+                          xn16 && hid16 && hf16, "model_decode_step: out of memory");
+    ASCA_CUDA(ctx, cudaMemcpyAsync(ids, ids_h, (size_t)ns * 4, cudaMemcpyHostToDevice, ctx->stream));
+    ASCA_TRY(asca_moe_dispatch(ctx, ids, ns, E, perm, offs, nullptr));
+    ASCA_TRY(asca_embed_fwd(ctx, P + m->embed, ids, ns, d, x));
+    for (int64_t li = 0; li < m->L; ++li) {
+        const Lyr& w = m->lay[li];
+        const Lyr& w16 = m->lay16[li];
+        ASCA_TRY(asca_cast_bf16(ctx, x, x16, ns * d));
+        ASCA_TRY(asca_gemm(ctx, ASCA_NN, ns, 3 * d, d, x16, d, W + w16.w_qkv, 3 * d, qkv, 3 * d, P + w.b_qkv, 0, BF));
+        ASCA_TRY(asca_gemm(ctx, ASCA_NN, ns, 2 * H, d, x16, d, W + w16.w_gate, 2 * H, gate, 2 * H, P + w.b_gate, 0, BF));
+        ASCA_TRY(asca_delta_step(ctx, qkv, nullptr, nullptr, gate, nullptr, state + li * ns * H * dh * dh, ns, H, dh, 1, o));
+        ASCA_TRY(asca_cast_bf16(ctx, o, o16, ns * d));
+        ASCA_TRY(asca_gemm(ctx, ASCA_NN, ns, d, d, o16, d, W + w16.w_o, d, y, d, P + w.b_o, 0, BF));
+        ASCA_TRY(asca_residual_rmsnorm_bf16(ctx, x, y, x_mid, xn16, ns, d, 1e-6f));
+        ASCA_TRY(asca_moe_fwd(ctx, xn16, W + w16.w1, P + w.b1, W + w16.w2, P + w.b2, perm, offs, ns, d, F, E, BF, mo, pre_p, hid16));
+        ASCA_TRY(asca_residual_rmsnorm(ctx, x_mid, mo, x, nullptr, ns, d, 1e-6f));
+    }
+    ASCA_TRY(asca_residual_rmsnorm_bf16(ctx, x, nullptr, nullptr, hf16, ns, d, 1e-6f));
+    ASCA_TRY(asca_gemm(ctx, ASCA_NN, ns, V, d, hf16, d, W + m->head16, V, logits, V, nullptr, 0, BF));
+    if (logits_h) ASCA_CUDA(ctx, cudaMemcpyAsync(logits_h, logits, (size_t)ns * V * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    if (next_h) {
+        argmax_kernel<<<(unsigned)ceil_div64(ns, 8), 256, 0, ctx->stream>>>(logits, ns, (int)V, nxt);
+        ASCA_CHECK_LAUNCH(ctx);
+        ASCA_CUDA(ctx, cudaMemcpyAsync(next_h, nxt, (size_t)ns * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    }
+    return asca_ctx_sync(ctx);
+}
+
 extern "C" {
 static int cross_entropy_scaled(asca_ctx* ctx, const float* logits, const uint32_t* targets, int64_t N, int64_t V,
                                 float* dlogits, float* loss, float grad_scale);
@@ -708,6 +771,7 @@ int asca_model_decode_step_host(asca_ctx* ctx, asca_model* m, float* state, cons
     ASCA_REQUIRE(ctx, state && ids_h && ns > 0, "model_decode_step: bad arguments");
     const int64_t d = m->d, H = m->H, dh = d / H, E = m->E, F = m->F, V = m->vocab;
     for (int64_t i = 0; i < ns; ++i) ASCA_REQUIRE(ctx, ids_h[i] < (uint32_t)V, "model_decode_step: id out of range");
+    if (m->compute == ASCA_BF16) return decode_step_bf16(ctx, m, state, ids_h, ns, logits_h, next_h);
     float* P = m->params;
     Bufs bf(ctx);
     uint32_t* ids = (uint32_t*)bf.f(ns);

@@ -160,3 +160,31 @@ def test_grad_hook_covers_the_buffer_once_and_accumulation_scales(orc, gpu):
         a, b = ref.tensor(name, g), ref.tensor(name, g_ref)
         assert rel_err(a, b) < 2e-5, name
     dev.free()
+
+
+def test_bf16_compute_decode_within_tolerance(orc, gpu):
+    """bf16 decode step (tensor-core projections, grouped expert FFN; head dim 64 like the decode
+    configuration) against the f32 CPU oracle stepping the same tokens: logits and states within 2e-2."""
+    import asca_b200
+
+    cfg = (256, 128, 2, 2, 4, 256)
+    ref = orc.Model(*cfg)
+    ref.init_reference(orc.Rng(11))
+    dev = asca_b200.Model(gpu, *cfg)
+    dev.set_params(ref.params)
+    dev.set_compute(asca_b200.BF16)
+    n_streams, steps = 6, 40
+    prompts = orc.Rng(12).below(256, (n_streams, steps))
+    state = dev.new_decode_state(n_streams)
+    ref_states = [ref.new_decode_state() for _ in range(n_streams)]
+    worst = 0.0
+    for t in range(steps):
+        logits, nxt = dev.decode_step(state, prompts[:, t].copy())
+        for s in range(n_streams):
+            lr = ref.step(int(prompts[s, t]), ref_states[s])
+            worst = max(worst, rel_err(logits[s], lr[0]))
+    assert worst < 2e-2
+    st = state.cpu().numpy()
+    for s in range(n_streams):
+        assert rel_err(st[:, s], ref_states[s]) < 2e-2
+    dev.free()
