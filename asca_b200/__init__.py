@@ -344,6 +344,28 @@ class Model:
         self._hook = proto(lambda _user, off, cnt: fn(int(off), int(cnt)))   # kept alive with the model
         self.gpu._call("asca_model_set_grad_hook", self._h, self._hook, None)
 
+    def adam_counter(self, value=None) -> int:
+        """Read (and optionally set) AdamW's per-tensor step counter."""
+        got = C.c_uint32()
+        setp = C.byref(C.c_uint32(int(value))) if value is not None else None
+        self.gpu._call("asca_model_adam_counter", self._h, setp, C.byref(got))
+        return int(got.value)
+
+    def moments(self):
+        """Host copies of Adam's m and v."""
+        m, v = np.empty(self.n, np.float32), np.empty(self.n, np.float32)
+        b = self.buffers()
+        self.gpu._call("asca_memcpy_d2h", self.gpu._ctx, _p(m), C.c_void_p(b[2]), C.c_size_t(self.n * 4))
+        self.gpu._call("asca_memcpy_d2h", self.gpu._ctx, _p(v), C.c_void_p(b[3]), C.c_size_t(self.n * 4))
+        return m, v
+
+    def set_moments(self, m, v):
+        m, v = _as_f32(m), _as_f32(v)
+        assert m.size == self.n and v.size == self.n
+        b = self.buffers()
+        self.gpu._call("asca_memcpy_h2d", self.gpu._ctx, C.c_void_p(b[2]), _p(m), C.c_size_t(self.n * 4))
+        self.gpu._call("asca_memcpy_h2d", self.gpu._ctx, C.c_void_p(b[3]), _p(v), C.c_size_t(self.n * 4))
+
     def params_changed(self):
         """Tell the model that the flat parameter buffer was written through :meth:`buffers`."""
         self.gpu._call("asca_model_params_changed", self._h)

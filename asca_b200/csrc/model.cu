@@ -596,6 +596,13 @@ int asca_model_set_grad_hook(asca_model* m, asca_grad_ready_fn fn, void* user) {
     return ASCA_OK;
 }
 
+int asca_model_adam_counter(asca_model* m, const uint32_t* set, uint32_t* get) {
+    if (!m) return ASCA_ERR_ARG;
+    if (set) m->adam_counter = *set;
+    if (get) *get = m->adam_counter;
+    return ASCA_OK;
+}
+
 int asca_model_params_changed(asca_model* m) {
     if (!m) return ASCA_ERR_ARG;
     m->params16_stale = true;

@@ -332,6 +332,10 @@ int asca_model_set_grad_hook(asca_model* m, asca_grad_ready_fn fn, void* user);
 /* Call after writing the parameter buffer directly (asca_model_buffers): derived copies are rebuilt. */
 int asca_model_params_changed(asca_model* m);
 int asca_model_set_params_host(asca_ctx* ctx, asca_model* m, const float* params);
+/* AdamW's step counter (`AdamW::step`, rust/src/tensor.rs:393: it advances once per parameter tensor).
+ * set / get may be NULL. A resume checkpoint restores it with the training step number, as
+ * load_resume does (rust/src/train.rs:454-455). asca_model_set_params_host resets it to 0. */
+int asca_model_adam_counter(asca_model* m, const uint32_t* set, uint32_t* get);
 int asca_model_get_host(asca_ctx* ctx, asca_model* m, float* params, float* grads);
 int asca_model_zero_grads(asca_ctx* ctx, asca_model* m);
 /* Forward + backward over B sequences of T tokens (ids, targets: host uint32 arrays of B*T).
