@@ -691,18 +691,23 @@ __global__ void __launch_bounds__(CH_THREADS, 1) delta_fwd_tc_kernel(
 //   dq = gam X + G6.h0,  dk = G6.h1 + eg dW - beta gam Y  (X, Y = the two halves of G5),
 // followed by the L2-norm backward, the gate gradients and the [dq|dk|dv] concat as in the f32
 // kernel (delta_bwd.cu).
-constexpr int BW_THREADS = 256;
+constexpr int NCQ = 4;                   // column groups per row: warp w and w + 4 k share TMEM lane quarter (w & 3)
+constexpr int BW_THREADS = 128 * NCQ;
+constexpr int CW = DH / NCQ;             // columns of a row handled by one thread
+constexpr int NCI = CW / 32;             // 32-column TMEM loads per thread and product
+constexpr int DW = C / NCQ;              // columns of the 64 x 64 dL / dA products per thread
+constexpr int NWARPS = BW_THREADS / 32;
 constexpr int R_WH = 0, R_BK = 16384, R_QG = 32768, R_KW = 49152, R_K = 65536, R_Q = 81920, R_DO = 98304,
               R_A = 114688, R_TP = 122880, R_S0 = 131072, R_DS = 163840, R_DR = 196608, R_END = 212992;
 constexpr int R_U = R_WH, R_P = R_KW, R_DAG = R_A, R_M = R_TP, R_STG = R_S0;   // staging: S0 + dS regions (64 KiB)
-constexpr int BW_NVEC = 1664;
+constexpr int BW_NVEC = 128 + 6 * NCQ * 64 + BW_THREADS + 128 + 64 + (BW_THREADS / 64) * 64;
 constexpr size_t BW_SMEM = 1024 + R_END + BW_NVEC * 4 + 256;
 constexpr int BW_TX_A = 32768 + 16384 * 2;        // S0, W^, beta gam K
 constexpr int BW_TX_B = 16384 * 2 + 8192;         // Kw, dO, A
 constexpr int BW_TX_C = 16384 * 3 + 8192;         // Qg, K, Q, T'
 
-// 256 threads: warp w and warp w+4 share TMEM lane quarter (w & 3) and split every row's 128
-// columns in two (colhalf = w >> 2), so each thread handles 64 columns of one row.
+// 128 * NCQ threads: warps w, w + 4, ... share TMEM lane quarter (w & 3) and split every row's 128
+// columns in NCQ groups (colhalf = w >> 2), so each thread handles CW columns of one row.
 __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
     const __grid_constant__ CUtensorMap mapWQ, const __grid_constant__ CUtensorMap map64x128,  // BK tiles
     const __grid_constant__ CUtensorMap mapKW, const __grid_constant__ CUtensorMap mapKR,
@@ -716,16 +721,16 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
     float* vec = reinterpret_cast<float*>(sm + R_END);
     float* g_s = vec;              // cumulative log alpha
     float* be_s = vec + 64;        // beta
-    float* v_rowp = vec + 128;     // [2][64] row sums of P per column half
-    float* v_rqs = vec + 320;      // [2][64]
-    float* v_rkg = vec + 448;      // [2][64]
-    float* v_rkw = vec + 576;      // [2][64]
-    float* v_rdr = vec + 704;      // [2][64]
-    float* v_dls = vec + 832;      // [2][64]
-    float* v_red = vec + 960;      // [256] partials of <S0, dS>
-    float* v_nrm = vec + 1216;     // [128] |q| rows then |k| rows of the chunk
-    float* v_al = vec + 1344;      // [64] alpha
-    float* v_colp4 = vec + 1408;   // [4][64] partial column sums of P
+    float* v_rowp = vec + 128;                 // [NCQ][64] row sums of P per column group
+    float* v_rqs = v_rowp + NCQ * 64;          // [NCQ][64]
+    float* v_rkg = v_rqs + NCQ * 64;           // [NCQ][64]
+    float* v_rkw = v_rkg + NCQ * 64;           // [NCQ][64]
+    float* v_rdr = v_rkw + NCQ * 64;           // [NCQ][64]
+    float* v_dls = v_rdr + NCQ * 64;           // [NCQ][64]
+    float* v_red = v_dls + NCQ * 64;           // [BW_THREADS] partials of <S0, dS>
+    float* v_nrm = v_red + BW_THREADS;         // [128] |q| rows then |k| rows of the chunk
+    float* v_al = v_nrm + 128;                 // [64] alpha
+    float* v_colp4 = v_al + 64;                // [BW_THREADS / 64][64] partial column sums of P
     uint64_t* bars = reinterpret_cast<uint64_t*>(sm + R_END + BW_NVEC * 4);   // [0],[7],[8] TMA groups, [1..6] MMA groups
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -753,15 +758,15 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
     const uint32_t ACC_S = tm, ACC_A = tm + 128, ACC_B = tm + 256, ACC_C = tm + 384;
     const uint32_t H1 = 16u << 16;                         // lane offset of the second M=64 half
     const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
-    const int c0 = colhalf * 2;                            // first 32-column chunk of this thread
+    const int c0 = colhalf * NCI;                          // first 32-column chunk of this thread
 
     // dS = 0 (TMEM f32 and the bf16 operand copy)
     {
         uint32_t z[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) z[j] = 0u;
-        tc::tmem_st_32x32(ACC_S + lane_addr + c0 * 32, z);
-        tc::tmem_st_32x32(ACC_S + lane_addr + c0 * 32 + 32, z);
+#pragma unroll
+        for (int ci = 0; ci < NCI; ++ci) tc::tmem_st_32x32(ACC_S + lane_addr + (c0 + ci) * 32, z);
         tc::tmem_st_wait();
         for (int i = tid; i < 32768 / 16; i += BW_THREADS) *reinterpret_cast<uint4*>(sm + R_DS + i * 16) = make_uint4(0, 0, 0, 0);
     }
@@ -830,23 +835,23 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
 
     // Small per-chunk inputs are fetched one chunk ahead, before that chunk's TMA traffic is queued:
     // rows of Uv (half 0) / beta V (half 1), 64 columns each, and the per-token scalars.
-    uint4 pre[8];
+    uint4 pre[CW / 8];
     float nx0 = 0.0f, nx1 = 0.0f;
     auto fetch_small = [&](int c) {
         const int64_t tix = tile0 + c;
         const int t0 = c * C;
         const int n = T - t0 < C ? T - t0 : C;
         const int64_t grow = seq_row0 + t0;
-        const __nv_bfloat16* src = (half == 0 ? tl.UVT : tl.BV) + tix * (64 * DH) + lm_off128(row, colhalf * 8);
+        const __nv_bfloat16* src = (half == 0 ? tl.UVT : tl.BV) + tix * (64 * DH) + lm_off128(row, colhalf * (CW / 8));
 #pragma unroll
-        for (int j = 0; j < 8; ++j) pre[j] = *reinterpret_cast<const uint4*>(src + j * 128);
+        for (int j = 0; j < CW / 8; ++j) pre[j] = *reinterpret_cast<const uint4*>(src + j * 128);
         if (tid < 64) {
             nx0 = tl.GV[tix * 64 + tid];
             nx1 = tl.BE[tix * 64 + tid];
         } else if (tid < 128) {
             const int t = min(tid - 64, n - 1);          // unconditional loads: nothing waits on them here
             nx0 = alpha[(grow + t) * H + h];
-        } else {
+        } else if (tid < 256) {
             const int t = min(tid & 63, n - 1);
             nx0 = (tid < 192 ? qnorm : knorm)[(grow + t) * H + h];
         }
@@ -868,7 +873,7 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
             be_s[tid] = nx1;
         } else if (tid < 128) {
             v_al[tid - 64] = nx0;
-        } else {
+        } else if (tid < 256) {
             v_nrm[tid - 128] = nx0;
         }
         tc::fence_proxy_async_smem();   // the dS operand copy written at the end of the previous chunk
@@ -894,7 +899,7 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
         wait_bar(1, par);
         tc::tcgen05_fence_after();
 #pragma unroll
-        for (int ci = 0; ci < 2; ++ci) {
+        for (int ci = 0; ci < NCI; ++ci) {
             uint32_t r[32];
             tc::tmem_ld_32x32(ACC_A + lane_addr + (c0 + ci) * 32, r);
             tc::tmem_ld_wait();
@@ -912,7 +917,7 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
         wait_bar(2, par);
         tc::tcgen05_fence_after();
 #pragma unroll
-        for (int ci = 0; ci < 2; ++ci) {
+        for (int ci = 0; ci < NCI; ++ci) {
             uint32_t r[32];
             tc::tmem_ld_32x32(ACC_B + lane_addr + (c0 + ci) * 32, r);
             tc::tmem_ld_wait();
@@ -937,12 +942,12 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
             tc::umma_commit(&bars[3]);
         }
         // rows of K K^T and Q K^T (32 columns each) for the dL / dA phase, fetched ahead
-        uint4 pkk[4], pqk[4];
+        uint4 pkk[DW / 8], pqk[DW / 8];
         if (half == 0) {
-            const __nv_bfloat16* kk = tl.KKo + tix * 4096 + lm_off64(row, colhalf * 4);
-            const __nv_bfloat16* qk = tl.QKo + tix * 4096 + lm_off64(row, colhalf * 4);
+            const __nv_bfloat16* kk = tl.KKo + tix * 4096 + lm_off64(row, colhalf * (DW / 8));
+            const __nv_bfloat16* qk = tl.QKo + tix * 4096 + lm_off64(row, colhalf * (DW / 8));
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
+            for (int j = 0; j < DW / 8; ++j) {
                 pkk[j] = *reinterpret_cast<const uint4*>(kk + j * 128);
                 pqk[j] = *reinterpret_cast<const uint4*>(qk + j * 128);
             }
@@ -953,7 +958,7 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
         {
             float r_dr = 0.0f, r_kg = 0.0f;
 #pragma unroll
-            for (int ci = 0; ci < 2; ++ci) {
+            for (int ci = 0; ci < NCI; ++ci) {
                 uint32_t r[32], p2[32];
                 tc::tmem_ld_32x32(ACC_B + lane_addr + (c0 + ci) * 32, r);
                 tc::tmem_ld_32x32(ACC_A + lane_addr + (c0 + ci) * 32, p2);
@@ -998,8 +1003,8 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
         }
         // ---- D. while G4/G5 run: dV rows out (8 lanes per row, coalesced), scale dS by gam_C, <S0, dS>
 #pragma unroll
-        for (int itv = 0; itv < 2; ++itv) {
-            const int r_ = itv * 32 + (tid >> 3), l8 = tid & 7;
+        for (int itv = 0; itv < 64 / (BW_THREADS / 8); ++itv) {
+            const int r_ = itv * (BW_THREADS / 8) + (tid >> 3), l8 = tid & 7;
             if (r_ < n) {
                 float* dv = d_qkv + (grow + r_) * 3 * d + 2 * d + h * DH;
 #pragma unroll
@@ -1011,7 +1016,7 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
             const float gC = __expf(g_last);
             float part = 0.0f;
 #pragma unroll
-            for (int ci = 0; ci < 2; ++ci) {
+            for (int ci = 0; ci < NCI; ++ci) {
                 uint32_t r[32];
                 tc::tmem_ld_32x32(ACC_S + lane_addr + (c0 + ci) * 32, r);
                 tc::tmem_ld_wait();
@@ -1031,22 +1036,22 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
         }
         wait_bar(4, par);
         tc::tcgen05_fence_after();
-        // dL / dA rows (half 0; this thread's 32 columns): M tile, dA.Gam tile, P row, dbeta
+        // dL / dA rows (half 0; this thread's DW columns): M tile, dA.Gam tile, P row, dbeta
         {
             float rowp = 0.0f, dls = 0.0f;
-            uint32_t rl[32], ra[32];
-            tc::tmem_ld_32x32(ACC_C + lane_addr + colhalf * 32, rl);
-            tc::tmem_ld_32x32(ACC_C + lane_addr + 64 + colhalf * 32, ra);
+            uint32_t rl[DW], ra[DW];
+            tc::tmem_ld_cols<DW>(ACC_C + lane_addr + colhalf * DW, rl);
+            tc::tmem_ld_cols<DW>(ACC_C + lane_addr + 64 + colhalf * DW, ra);
             tc::tmem_ld_wait();
             if (half == 0) {
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
+                for (int j = 0; j < DW / 8; ++j) {
                     float kk8[8], qk8[8], m8[8], a8[8];
                     tc::unpack8_bf16(pkk[j], kk8);
                     tc::unpack8_bf16(pqk[j], qk8);
 #pragma unroll
                     for (int e = 0; e < 8; ++e) {
-                        const int i = colhalf * 32 + 8 * j + e;
+                        const int i = colhalf * DW + 8 * j + e;
                         const float gm = i <= row ? __expf(g_row - g_s[i]) : 0.0f;
                         const float dlg = i < row ? -__uint_as_float(rl[8 * j + e]) * gm : 0.0f;   // dL.Gam
                         const float dag = __uint_as_float(ra[8 * j + e]) * gm;                     // dA.Gam
@@ -1057,7 +1062,7 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
                         rowp += pv;
                         reinterpret_cast<float*>(sm + R_P)[row * 64 + ((i + row) & 63)] = pv;
                     }
-                    const int chunk16 = colhalf * 4 + j;
+                    const int chunk16 = colhalf * (DW / 8) + j;
                     *reinterpret_cast<uint4*>(sm + R_M + tc::sw128_off(row, chunk16)) = tc::pack8_bf16(m8);
                     *reinterpret_cast<uint4*>(sm + R_DAG + tc::sw128_off(row, chunk16)) = tc::pack8_bf16(a8);
                 }
@@ -1081,13 +1086,14 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
             _Pragma("unroll") for (int k16 = 0; k16 < 4; ++k16) tc::umma_bf16(ACC_S, mnmaj(R_BK, k16, 8192), mnmaj(R_DR, k16, 8192), I128_MM_NEG, 1u);
             tc::umma_commit(&bars[6]);
         }
-        // column sums of P while G6 runs: 4 threads per column, 16 rows each
+        // column sums of P while G6 runs: BW_THREADS / 64 threads per column
         {
+            constexpr int RPP = 64 / (BW_THREADS / 64);   // rows per partial sum
             const int col = tid & 63, part = tid >> 6;
             float cs = 0.0f;
             const float* P = reinterpret_cast<const float*>(sm + R_P);
 #pragma unroll
-            for (int t = part * 16; t < part * 16 + 16; ++t) cs += P[t * 64 + ((col + t) & 63)];
+            for (int t = part * RPP; t < part * RPP + RPP; ++t) cs += P[t * 64 + ((col + t) & 63)];
             v_colp4[part * 64 + col] = cs;
         }
         // ---- E. dq rows (half 0) and dk rows (half 1) into the f32 staging area (S0 + dS regions are free)
@@ -1099,15 +1105,16 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
             const int swz = (row + 16 * half) & 31;
             float rr = 0.0f;
 #pragma unroll
-            for (int ci = 0; ci < 2; ++ci) {
-                uint32_t xa[32], xb[32], xc[32];
-                tc::tmem_ld_32x32(ACC_A + lane_addr + (c0 + ci) * 32, xa);    // X (h0) | Y (h1)
-                tc::tmem_ld_32x32(ACC_B + lane_addr + (c0 + ci) * 32, xb);    // G6
-                tc::tmem_ld_32x32(ACC_C + lane_addr + (c0 + ci) * 32, xc);    // (h0: dL|dA) | dW (h1)
+            for (int pc = 0; pc < CW / 16; ++pc) {   // 16 columns at a time keeps the three accumulators in 48 registers
+                uint32_t xa[16], xb[16], xc[16];
+                const uint32_t col = (uint32_t)(colhalf * CW + pc * 16);
+                tc::tmem_ld_cols<16>(ACC_A + lane_addr + col, xa);    // X (h0) | Y (h1)
+                tc::tmem_ld_cols<16>(ACC_B + lane_addr + col, xb);    // G6
+                tc::tmem_ld_cols<16>(ACC_C + lane_addr + col, xc);    // (h0: dL|dA) | dW (h1)
                 tc::tmem_ld_wait();
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int chunk16 = (c0 + ci) * 4 + j;
+                for (int j = 0; j < 2; ++j) {
+                    const int chunk16 = colhalf * (CW / 8) + pc * 2 + j;
                     float z8[8], g8[8];
                     tc::unpack8_bf16(*tile64(half == 0 ? R_QG : R_K, row, chunk16), z8);   // Qg_t | k_t
 #pragma unroll
@@ -1132,11 +1139,12 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
         if (c > 0) fetch_small(c - 1);
         // L2-norm backward and store: 8 lanes per staged row (4 float4 each), 4 rows per warp at a time
         {
-            const int l8 = lane & 7, hh = warp >> 2;
+            constexpr int RPW = 128 / NWARPS;            // staged rows per warp (64 dq rows, then 64 dk rows)
+            const int l8 = lane & 7, hh = (warp * RPW) >> 6;
             const int ytile = hh == 0 ? R_Q : R_K;
 #pragma unroll
-            for (int itn = 0; itn < 4; ++itn) {
-                const int srow = warp * 16 + itn * 4 + (lane >> 3), r_ = srow & 63;
+            for (int itn = 0; itn < RPW / 4; ++itn) {
+                const int srow = warp * RPW + itn * 4 + (lane >> 3), r_ = srow & 63;
                 const int swz = (r_ + 16 * hh) & 31;
                 float4 g4[4];
                 float y[4][4];
@@ -1166,13 +1174,25 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
         // gates (warp 0): dg, reverse cumulative sum, sigmoid backward
         if (warp == 0) {
             float sds = 0.0f;
-            for (int i = lane; i < 256; i += 32) sds += v_red[i];
+            for (int i = lane; i < BW_THREADS; i += 32) sds += v_red[i];
             sds = warp_sum(sds);
+            auto sumq = [&](const float* v, int t) {   // the NCQ column-group partials of one token
+                float a = 0.0f;
+#pragma unroll
+                for (int qd = 0; qd < NCQ; ++qd) a += v[qd * 64 + t];
+                return a;
+            };
+            auto colp = [&](int t) {
+                float a = 0.0f;
+#pragma unroll
+                for (int qd = 0; qd < BW_THREADS / 64; ++qd) a += v_colp4[qd * 64 + t];
+                return a;
+            };
             const int tA = lane, tB = lane + 32;
-            const float kwA = v_rkw[tA] + v_rkw[64 + tA], kwB = v_rkw[tB] + v_rkw[64 + tB];
+            const float kwA = sumq(v_rkw, tA), kwB = sumq(v_rkw, tB);
             const float extra = __expf(g_last) * sds + warp_sum(kwA + kwB);
-            float dgA = v_rowp[tA] + v_rowp[64 + tA] - (v_colp4[tA] + v_colp4[64 + tA] + v_colp4[128 + tA] + v_colp4[192 + tA]) + v_rqs[tA] + v_rqs[64 + tA] + v_rkg[tA] + v_rkg[64 + tA] - kwA;
-            float dgB = v_rowp[tB] + v_rowp[64 + tB] - (v_colp4[tB] + v_colp4[64 + tB] + v_colp4[128 + tB] + v_colp4[192 + tB]) + v_rqs[tB] + v_rqs[64 + tB] + v_rkg[tB] + v_rkg[64 + tB] - kwB;
+            float dgA = sumq(v_rowp, tA) - colp(tA) + sumq(v_rqs, tA) + sumq(v_rkg, tA) - kwA;
+            float dgB = sumq(v_rowp, tB) - colp(tB) + sumq(v_rqs, tB) + sumq(v_rkg, tB) - kwB;
             if (lane == 31) dgB += extra;
             // suffix sums over t = 0..63 (A holds 0..31, B holds 32..63)
             float sB = dgB, sA = dgA;
@@ -1190,13 +1210,13 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
                 const int64_t r = grow + tA;
                 const float be = be_s[tA];
                 d_gate[r * 2 * H + h] = sA * (1.0f - v_al[tA]);
-                d_gate[r * 2 * H + H + h] = (v_rdr[tA] + v_rdr[64 + tA] + be * (v_dls[tA] + v_dls[64 + tA])) * (1.0f - be);
+                d_gate[r * 2 * H + H + h] = (sumq(v_rdr, tA) + be * sumq(v_dls, tA)) * (1.0f - be);
             }
             if (tB < n) {
                 const int64_t r = grow + tB;
                 const float be = be_s[tB];
                 d_gate[r * 2 * H + h] = sB * (1.0f - v_al[tB]);
-                d_gate[r * 2 * H + H + h] = (v_rdr[tB] + v_rdr[64 + tB] + be * (v_dls[tB] + v_dls[64 + tB])) * (1.0f - be);
+                d_gate[r * 2 * H + H + h] = (sumq(v_rdr, tB) + be * sumq(v_dls, tB)) * (1.0f - be);
             }
         }
         // ---- F. new dS -> bf16 operand copy for the next chunk; next chunk's tiles
@@ -1209,7 +1229,7 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
                 issue_tma(c - 1);
             }
 #pragma unroll
-            for (int ci = 0; ci < 2; ++ci) {
+            for (int ci = 0; ci < NCI; ++ci) {
                 uint32_t r[32];
                 tc::tmem_ld_32x32(ACC_S + lane_addr + (c0 + ci) * 32, r);
                 tc::tmem_ld_wait();
