@@ -11,6 +11,8 @@
 //     (stream, head) streams S through registers once (read + write = the HBM floor).
 #include "common.cuh"
 
+#include <cuda_bf16.h>
+
 bool asca_tc_enabled();  // gemm.cu
 namespace delta_tc {
 bool available();
@@ -309,6 +311,83 @@ __global__ void __launch_bounds__(StepCfg<DH>::THREADS) delta_step_kernel(
     }
 }
 
+// Decode step for head dim 64, one WARP per (stream, head): lane l owns value columns 2l and 2l+1 of the 64 x 64
+// state, all 64 rows (64 float2 loads issued back to back, 256 contiguous bytes per row across the warp). Every
+// per-column quantity (S^T k, u, the update, S^T q) is local to the lane, so the step needs no block barrier and
+// no cross-lane reduction except the two norms of the fused prologue; k and q are broadcast from the warp's slice
+// of shared memory. qkv / gate may be the two parts of one wider row (row pitches ld_qkv, ld_gate); o16, when
+// given, receives a bf16 copy of the output for a following tensor-core product.
+constexpr int SW_WARPS = 8;
+__global__ void __launch_bounds__(SW_WARPS * 32) delta_step_warp64_kernel(
+    const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, const float* __restrict__ alpha,
+    const float* __restrict__ beta, float* __restrict__ S, int64_t n_units, int H, int fused, int64_t ld_qkv,
+    int64_t ld_gate, float* __restrict__ o, __nv_bfloat16* __restrict__ o16) {
+    constexpr int DH = 64;
+    __shared__ __align__(16) float kq_s[SW_WARPS][2][DH];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int64_t unit = (int64_t)blockIdx.x * SW_WARPS + w;   // stream * H + h
+    if (unit >= n_units) return;
+    const int64_t s = unit / H;
+    const int h = (int)(unit % H);
+    const int d = H * DH;
+    float2* Sg = reinterpret_cast<float2*>(S + unit * DH * DH);
+    float2 st[DH];
+#pragma unroll
+    for (int a = 0; a < DH; ++a) st[a] = Sg[a * 32 + lane];   // in flight while the inputs are prepared
+    float2 q2, k2, v2;
+    float al, be;
+    if (fused) {
+        const float* row = q + s * ld_qkv + h * DH + 2 * lane;
+        q2 = *reinterpret_cast<const float2*>(row);
+        k2 = *reinterpret_cast<const float2*>(row + d);
+        v2 = *reinterpret_cast<const float2*>(row + 2 * d);
+        const float qq = warp_sum(q2.x * q2.x + q2.y * q2.y), kk = warp_sum(k2.x * k2.x + k2.y * k2.y);
+        const float qi = 1.0f / fmaxf(sqrtf(qq), 1e-8f), ki = 1.0f / fmaxf(sqrtf(kk), 1e-8f);
+        q2.x *= qi; q2.y *= qi; k2.x *= ki; k2.y *= ki;
+        al = 1.0f / (1.0f + expf(-alpha[s * ld_gate + h]));
+        be = 1.0f / (1.0f + expf(-alpha[s * ld_gate + H + h]));
+    } else {
+        const int64_t off = s * d + h * DH + 2 * lane;
+        q2 = *reinterpret_cast<const float2*>(q + off);
+        k2 = *reinterpret_cast<const float2*>(k + off);
+        v2 = *reinterpret_cast<const float2*>(v + off);
+        al = alpha[s * H + h];
+        be = beta[s * H + h];
+    }
+    *reinterpret_cast<float2*>(&kq_s[w][0][2 * lane]) = k2;
+    *reinterpret_cast<float2*>(&kq_s[w][1][2 * lane]) = q2;
+    __syncwarp();
+    const float* ks = kq_s[w][0];
+    const float* qs = kq_s[w][1];
+    float2 sk = make_float2(0.0f, 0.0f);
+#pragma unroll
+    for (int a4 = 0; a4 < DH; a4 += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(ks + a4);
+        sk.x = fmaf(st[a4].x, k4.x, sk.x);         sk.y = fmaf(st[a4].y, k4.x, sk.y);
+        sk.x = fmaf(st[a4 + 1].x, k4.y, sk.x);     sk.y = fmaf(st[a4 + 1].y, k4.y, sk.y);
+        sk.x = fmaf(st[a4 + 2].x, k4.z, sk.x);     sk.y = fmaf(st[a4 + 2].y, k4.z, sk.y);
+        sk.x = fmaf(st[a4 + 3].x, k4.w, sk.x);     sk.y = fmaf(st[a4 + 3].y, k4.w, sk.y);
+    }
+    const float2 u = make_float2(be * (v2.x - al * sk.x), be * (v2.y - al * sk.y));
+    float2 acc = make_float2(0.0f, 0.0f);
+#pragma unroll
+    for (int a4 = 0; a4 < DH; a4 += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(ks + a4), q4 = *reinterpret_cast<const float4*>(qs + a4);
+        const float kk[4] = {k4.x, k4.y, k4.z, k4.w}, qq[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            float2 t = st[a4 + e];
+            t.x = fmaf(kk[e], u.x, al * t.x);
+            t.y = fmaf(kk[e], u.y, al * t.y);
+            Sg[(a4 + e) * 32 + lane] = t;
+            acc.x = fmaf(t.x, qq[e], acc.x);
+            acc.y = fmaf(t.y, qq[e], acc.y);
+        }
+    }
+    *reinterpret_cast<float2*>(o + s * d + h * DH + 2 * lane) = acc;
+    if (o16) *reinterpret_cast<__nv_bfloat162*>(o16 + s * d + h * DH + 2 * lane) = __floats2bfloat162_rn(acc.x, acc.y);
+}
+
 template <int DH, typename T>
 cudaError_t launch_fwd(cudaStream_t st, const void* q, const void* k, const void* v, const float* alpha,
                        const float* beta, int B, int T_, int H, int chunk, void* o, const float* s_init,
@@ -373,6 +452,23 @@ int asca_delta_fwd(asca_ctx* ctx, const void* q, const void* k, const void* v, c
     return ASCA_OK;
 }
 
+// fused = 1 only: qkv rows of pitch ld_qkv, gate rows of pitch ld_gate (both may point into one wider buffer);
+// o16 (nullable) gets a bf16 copy of o. dh = 64.
+int asca_delta_step_strided(asca_ctx* ctx, const float* qkv, int64_t ld_qkv, const float* gate, int64_t ld_gate, float* S,
+                            int64_t n_streams, int64_t H, float* o, void* o16) {
+    if (!ctx) return ASCA_ERR_ARG;
+    ASCA_REQUIRE(ctx, qkv && gate && S && o && n_streams >= 0 && H > 0, "delta_step_strided: bad arguments");
+    ASCA_REQUIRE(ctx, ld_qkv >= 3 * H * 64 && ld_gate >= 2 * H && (ld_qkv & 1) == 0, "delta_step_strided: bad row pitch");
+    ASCA_REQUIRE(ctx, (((uintptr_t)S | (uintptr_t)o | (uintptr_t)qkv) & 7) == 0 && ((uintptr_t)o16 & 3) == 0,
+                 "delta_step_strided: misaligned pointer");
+    if (n_streams == 0) return ASCA_OK;
+    const int64_t units = n_streams * H;
+    delta_step_warp64_kernel<<<(unsigned)ceil_div64(units, SW_WARPS), SW_WARPS * 32, 0, ctx->stream>>>(
+        qkv, nullptr, nullptr, gate, nullptr, S, units, (int)H, 1, ld_qkv, ld_gate, o, (__nv_bfloat16*)o16);
+    ASCA_CHECK_LAUNCH(ctx);
+    return ASCA_OK;
+}
+
 int asca_delta_step(asca_ctx* ctx, const float* q, const float* k, const float* v, const float* alpha,
                     const float* beta, float* S, int64_t n_streams, int64_t H, int64_t dh, int fused, float* o) {
     if (!ctx) return ASCA_ERR_ARG;
@@ -383,6 +479,14 @@ int asca_delta_step(asca_ctx* ctx, const float* q, const float* k, const float* 
     ASCA_REQUIRE(ctx, (((uintptr_t)S | (uintptr_t)o) & 15) == 0, "delta_step: S and o must be 16-byte aligned");
     if (n_streams == 0) return ASCA_OK;
     const unsigned grid = (unsigned)(n_streams * H);
+    const bool in8 = fused ? ((uintptr_t)q & 7) == 0 : (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v) & 7) == 0;
+    if (dh == 64 && in8) {   // one warp per (stream, head), no block barrier
+        const int64_t units = n_streams * H;
+        delta_step_warp64_kernel<<<(unsigned)ceil_div64(units, SW_WARPS), SW_WARPS * 32, 0, ctx->stream>>>(
+            q, k, v, alpha, beta, S, units, (int)H, fused, 3 * H * dh, 2 * H, o, nullptr);
+        ASCA_CHECK_LAUNCH(ctx);
+        return ASCA_OK;
+    }
     switch (dh) {
         case 16: delta_step_kernel<16><<<grid, StepCfg<16>::THREADS, 0, ctx->stream>>>(q, k, v, alpha, beta, S, (int)H, fused, o); break;
         case 32: delta_step_kernel<32><<<grid, StepCfg<32>::THREADS, 0, ctx->stream>>>(q, k, v, alpha, beta, S, (int)H, fused, o); break;

@@ -143,6 +143,31 @@ __global__ void __launch_bounds__(256) add_kernel(const float* __restrict__ a, c
     const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
     if (i < n) out[i] = a[i] + 1.0f * b[i];
 }
+// out = a + b, with a bf16 copy (the next block's product reads the copy)
+__global__ void __launch_bounds__(256) add_cast_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                                                       float* __restrict__ out, __nv_bfloat16* __restrict__ out16, int64_t n) {
+    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (i < n) {
+        const float v = a[i] + b[i];
+        out[i] = v;
+        out16[i] = __float2bfloat16(v);
+    }
+}
+// dst (rows x ld, bf16) = [a (rows x ca) | b (rows x cb) | 0]; bias likewise (f32)
+__global__ void __launch_bounds__(256) concat_cols_kernel(const float* __restrict__ a, int ca, const float* __restrict__ b, int cb,
+                                                          int64_t rows, int ld, __nv_bfloat16* __restrict__ dst) {
+    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= rows * ld) return;
+    const int64_t r = i / ld;
+    const int c = (int)(i % ld);
+    const float v = c < ca ? a[r * ca + c] : (c < ca + cb ? b[r * cb + (c - ca)] : 0.0f);
+    dst[i] = __float2bfloat16(v);
+}
+__global__ void __launch_bounds__(256) concat_bias_kernel(const float* __restrict__ a, int ca, const float* __restrict__ b, int cb,
+                                                          int ld, float* __restrict__ dst) {
+    const int c = blockIdx.x * 256 + threadIdx.x;
+    if (c < ld) dst[c] = c < ca ? a[c] : (c < ca + cb ? b[c - ca] : 0.0f);
+}
 // greedy argmax per row, lowest index on ties
 __global__ void __launch_bounds__(256) argmax_kernel(const float* __restrict__ logits, int64_t N, int V,
                                                      uint32_t* __restrict__ out) {
@@ -205,6 +230,11 @@ struct asca_model {
     int compute = ASCA_F32;              // ASCA_BF16: tensor-core products on a bf16 copy of the weights
     __nv_bfloat16* params16 = nullptr;   // refreshed from the f32 master copy whenever that changed
     bool params16_stale = true;
+    // decode only: per block the qkv and gate projections side by side, [d x ldq] bf16 + bias [ldq] f32,
+    // so that one product feeds the state update
+    __nv_bfloat16* dec_w = nullptr;
+    float* dec_b = nullptr;
+    bool dec_stale = true;
     // asca_model_zero_grads only records the request: the next backward overwrites every gradient tensor instead
     // of adding to it (each tensor is written exactly once per backward), which saves the clearing pass and the
     // read half of the accumulation. Anything that exposes the buffer earlier clears it for real first.
@@ -230,6 +260,7 @@ static int decode_step_bf16(asca_ctx* ctx, asca_model* m, float* state, const ui
         if (cudaMalloc((void**)&m->params16, (size_t)m->n16 * 2) != cudaSuccess)
             return asca_fail(ctx, ASCA_ERR_OOM, "model: cannot allocate the bf16 weight copy");
         m->params16_stale = true;
+    m->dec_stale = true;
     }
     if (m->params16_stale) {
         if (m->n16 == m->n_params) {
@@ -256,18 +287,48 @@ static int decode_step_bf16(asca_ctx* ctx, asca_model* m, float* state, const ui
     ASCA_CUDA(ctx, cudaMemcpyAsync(ids, ids_h, (size_t)ns * 4, cudaMemcpyHostToDevice, ctx->stream));
     ASCA_TRY(asca_moe_dispatch(ctx, ids, ns, E, perm, offs, nullptr));
     ASCA_TRY(asca_embed_fwd(ctx, P + m->embed, ids, ns, d, x));
+    const bool fused64 = dh == 64;   // one projection for qkv + gate, the warp-per-head state update, casts folded in
+    const int64_t ldq = (3 * d + 2 * H + 7) & ~(int64_t)7;
+    if (fused64) {
+        if (!m->dec_w) {
+            if (cudaMalloc((void**)&m->dec_w, (size_t)m->L * d * ldq * 2) != cudaSuccess ||
+                cudaMalloc((void**)&m->dec_b, (size_t)m->L * ldq * 4) != cudaSuccess)
+                return asca_fail(ctx, ASCA_ERR_OOM, "model: cannot allocate the fused decode projection");
+            m->dec_stale = true;
+        }
+        if (m->dec_stale) {
+            for (int64_t li = 0; li < m->L; ++li) {
+                const Lyr& w = m->lay[li];
+                concat_cols_kernel<<<(unsigned)ceil_div64(d * ldq, 256), 256, 0, ctx->stream>>>(
+                    P + w.w_qkv, (int)(3 * d), P + w.w_gate, (int)(2 * H), d, (int)ldq, m->dec_w + li * d * ldq);
+                concat_bias_kernel<<<(unsigned)ceil_div64(ldq, 256), 256, 0, ctx->stream>>>(P + w.b_qkv, (int)(3 * d), P + w.b_gate,
+                                                                                         (int)(2 * H), (int)ldq, m->dec_b + li * ldq);
+                ctx->launches += 2;
+            }
+            ASCA_CUDA(ctx, cudaGetLastError());
+            m->dec_stale = false;
+        }
+    }
+    float* qg = fused64 ? bf.f(ns * ldq) : nullptr;
+    ASCA_REQUIRE(ctx, !fused64 || qg, "model_decode_step: out of memory");
+    ASCA_TRY(asca_cast_bf16(ctx, x, x16, ns * d));
     for (int64_t li = 0; li < m->L; ++li) {
         const Lyr& w = m->lay[li];
         const Lyr& w16 = m->lay16[li];
-        ASCA_TRY(asca_cast_bf16(ctx, x, x16, ns * d));
-        ASCA_TRY(asca_gemm(ctx, ASCA_NN, ns, 3 * d, d, x16, d, W + w16.w_qkv, 3 * d, qkv, 3 * d, P + w.b_qkv, 0, BF));
-        ASCA_TRY(asca_gemm(ctx, ASCA_NN, ns, 2 * H, d, x16, d, W + w16.w_gate, 2 * H, gate, 2 * H, P + w.b_gate, 0, BF));
-        ASCA_TRY(asca_delta_step(ctx, qkv, nullptr, nullptr, gate, nullptr, state + li * ns * H * dh * dh, ns, H, dh, 1, o));
-        ASCA_TRY(asca_cast_bf16(ctx, o, o16, ns * d));
+        if (fused64) {
+            ASCA_TRY(asca_gemm(ctx, ASCA_NN, ns, ldq, d, x16, d, m->dec_w + li * d * ldq, ldq, qg, ldq, m->dec_b + li * ldq, 0, BF));
+            ASCA_TRY(asca_delta_step_strided(ctx, qg, ldq, qg + 3 * d, ldq, state + li * ns * H * dh * dh, ns, H, o, o16));
+        } else {
+            ASCA_TRY(asca_gemm(ctx, ASCA_NN, ns, 3 * d, d, x16, d, W + w16.w_qkv, 3 * d, qkv, 3 * d, P + w.b_qkv, 0, BF));
+            ASCA_TRY(asca_gemm(ctx, ASCA_NN, ns, 2 * H, d, x16, d, W + w16.w_gate, 2 * H, gate, 2 * H, P + w.b_gate, 0, BF));
+            ASCA_TRY(asca_delta_step(ctx, qkv, nullptr, nullptr, gate, nullptr, state + li * ns * H * dh * dh, ns, H, dh, 1, o));
+            ASCA_TRY(asca_cast_bf16(ctx, o, o16, ns * d));
+        }
         ASCA_TRY(asca_gemm(ctx, ASCA_NN, ns, d, d, o16, d, W + w16.w_o, d, y, d, P + w.b_o, 0, BF));
         ASCA_TRY(asca_residual_rmsnorm_bf16(ctx, x, y, x_mid, xn16, ns, d, 1e-6f));
         ASCA_TRY(asca_moe_fwd(ctx, xn16, W + w16.w1, P + w.b1, W + w16.w2, P + w.b2, perm, offs, ns, d, F, E, BF, mo, pre_p, hid16));
-        ASCA_TRY(asca_residual_rmsnorm(ctx, x_mid, mo, x, nullptr, ns, d, 1e-6f));
+        add_cast_kernel<<<(unsigned)ceil_div64(ns * d, 256), 256, 0, ctx->stream>>>(x_mid, mo, x, x16, ns * d);   // x_out (+ bf16)
+        ASCA_CHECK_LAUNCH(ctx);
     }
     ASCA_TRY(asca_residual_rmsnorm_bf16(ctx, x, nullptr, nullptr, hf16, ns, d, 1e-6f));
     ASCA_TRY(asca_gemm(ctx, ASCA_NN, ns, V, d, hf16, d, W + m->head16, V, logits, V, nullptr, 0, BF));
@@ -311,6 +372,7 @@ static int forward_backward_bf16(asca_ctx* ctx, asca_model* m, const uint32_t* i
         if (cudaMalloc((void**)&m->params16, (size_t)m->n16 * 2) != cudaSuccess)
             return asca_fail(ctx, ASCA_ERR_OOM, "model: cannot allocate the bf16 weight copy");
         m->params16_stale = true;
+    m->dec_stale = true;
     }
     if (m->params16_stale) {
         if (m->n16 == m->n_params) {   // no padding anywhere: one pass over the flat buffer
@@ -558,6 +620,8 @@ int asca_model_destroy(asca_ctx* ctx, asca_model* m) {
     for (float* b : {m->params, m->grads, m->m, m->v})
         if (b) cudaFree(b);
     if (m->params16) cudaFree(m->params16);
+    if (m->dec_w) cudaFree(m->dec_w);
+    if (m->dec_b) cudaFree(m->dec_b);
     delete m;
     return ASCA_OK;
 }
@@ -606,6 +670,7 @@ int asca_model_adam_counter(asca_model* m, const uint32_t* set, uint32_t* get) {
 int asca_model_params_changed(asca_model* m) {
     if (!m) return ASCA_ERR_ARG;
     m->params16_stale = true;
+    m->dec_stale = true;
     return ASCA_OK;
 }
 
@@ -615,6 +680,7 @@ int asca_model_set_params_host(asca_ctx* ctx, asca_model* m, const float* params
     ASCA_CUDA(ctx, cudaMemsetAsync(m->m, 0, (size_t)m->n_params * 4, ctx->stream));
     ASCA_CUDA(ctx, cudaMemsetAsync(m->v, 0, (size_t)m->n_params * 4, ctx->stream));
     m->params16_stale = true;
+    m->dec_stale = true;
     return asca_memcpy_h2d(ctx, m->params, params, (size_t)m->n_params * 4);
 }
 
@@ -768,6 +834,7 @@ int asca_model_adamw_step(asca_ctx* ctx, asca_model* m, float lr, float beta1, f
     // bf16 mode with an unpadded copy: the update writes the bf16 weights itself
     const bool fuse = m->compute == ASCA_BF16 && m->params16 && m->n16 == m->n_params;
     m->params16_stale = !fuse;
+    m->dec_stale = true;
     return asca_adamw_segmented_cast(ctx, m->params, m->grads, m->m, m->v, m->seg_off.data(), lr_t.data(), eps_t.data(), n_seg,
                                      beta1, beta2, lr * wd, fuse ? (void*)m->params16 : nullptr);
 }

@@ -173,6 +173,11 @@ int asca_delta_bwd(asca_ctx* ctx, const void* q, const void* k, const void* v, c
 int asca_delta_step(asca_ctx* ctx, const float* q, const float* k, const float* v,
                     const float* alpha, const float* beta, float* S, int64_t n_streams, int64_t H,
                     int64_t dh, int fused, float* o);
+/* The fused form for head dim 64 with explicit row pitches: qkv rows (3*H*64 used) ld_qkv floats apart,
+ * gate-logit rows (2H used) ld_gate apart -- the two may be column ranges of one projection output.
+ * o16 (nullable): bf16 copy of o for a following tensor-core product. No counterpart in the reference. */
+int asca_delta_step_strided(asca_ctx* ctx, const float* qkv, int64_t ld_qkv, const float* gate,
+                            int64_t ld_gate, float* S, int64_t n_streams, int64_t H, float* o, void* o16);
 /* Fused prologue of DeltaBlock::forward (rust/src/delta.rs:134-179): split qkv (N, 3d) into
  * q,k,v (N, d), L2-normalise q,k per head keeping the norms, and alpha/beta = sigmoid of the
  * gate logits (N, 2H). */
