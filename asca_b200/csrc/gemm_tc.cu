@@ -453,8 +453,7 @@ int launch(asca_ctx* ctx, const Args& a) {
     else grid = (int64_t)a.n_groups * ((a.M + BM - 1) / BM) * tn;
     if (grid <= 0) return ASCA_OK;
     // persistent: two CTAs per SM walk the tiles round-robin (`grid` is an upper bound on the tile count)
-    int dev = 0, n_sm = 148;
-    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+    const int n_sm = ctx->sm_count > 0 ? ctx->sm_count : 148;
     if (grid > 2 * n_sm) grid = 2 * n_sm;
     const size_t smem = SMEM_FIXED + (size_t)((a.group_dim == GROUP_NONE ? 1 : a.n_groups) + 2) * 4;
     auto go = [&](auto kern) -> cudaError_t {
