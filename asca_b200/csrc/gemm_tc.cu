@@ -23,17 +23,29 @@
 // Every mbarrier wait is bounded; a wait that runs out raises an error word that the host reads
 // back as ASCA_ERR_DEVICE, and the CTA still frees its TMEM and exits.
 #include "gemm_tc.cuh"
+
+#include <algorithm>
 #include "tc_common.cuh"
 
 namespace gemm_tc {
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 64, STAGES = 3, THREADS = 192;
-constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int TMEM_COLS = 2 * BN;      // two accumulator buffers
+constexpr int BM = 128, BK = 64, THREADS = 192;
+constexpr int A_BYTES = BM * BK * 2;
+// Two tile shapes. 128 x 128: 3-stage ring, 256 TMEM columns, two CTAs per SM (two independent MMA streams keep the
+// tensor pipe fed). 128 x 256: one M128 N256 K16 instruction does twice the work of an N128 one for the same issue
+// latency, so a single stream per SM suffices: 4-stage ring of 48 KiB, all 512 TMEM columns, one CTA per SM. It is
+// used when the problem has at least two waves of such tiles.
+template <int BN> struct Shape {
+    static constexpr int STAGES = BN == 128 ? 3 : 4;
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int TMEM_COLS = 2 * BN;      // two accumulator buffers
+    static constexpr int CTAS_PER_SM = BN == 128 ? 2 : 1;
+    static constexpr size_t SMEM_FIXED = (size_t)STAGES * STAGE_BYTES + 4 * 2048 /*epilogue staging*/ + 1024 /*alignment slack*/ +
+                                         256 /*barriers*/;   // + (groups + 2) * 4 for the tile table
+};
 constexpr int MAX_GROUPS = 2048;
-constexpr size_t SMEM_FIXED = (size_t)STAGES * STAGE_BYTES + 4 * 2048 /*epilogue staging*/ + 1024 /*alignment slack*/ +
-                              256 /*barriers*/;   // + (groups + 2) * 4 for the tile table
 
 struct KP {
     float* C;
@@ -60,11 +72,12 @@ __device__ __forceinline__ float silu_grad_f(float p) {
     return sg * (1.0f + p * (1.0f - sg));
 }
 
-template <int MODE>
-__global__ void __launch_bounds__(THREADS, 2) gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA,
+template <int MODE, int BN>
+__global__ void __launch_bounds__(THREADS, Shape<BN>::CTAS_PER_SM) gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA,
                                                              const __grid_constant__ CUtensorMap mapB, const KP p) {
     constexpr bool A_MN = (MODE == ASCA_TN);   // A operand MN-major
     constexpr bool B_MN = (MODE != ASCA_NT);   // B operand MN-major
+    constexpr int STAGES = Shape<BN>::STAGES, STAGE_BYTES = Shape<BN>::STAGE_BYTES, TMEM_COLS = Shape<BN>::TMEM_COLS;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* staging = tiles + STAGES * STAGE_BYTES;                 // 4 epilogue warps x 2 KiB
@@ -178,8 +191,9 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_tc_kernel(const __grid_consta
                     }
                     if (B_MN) {   // memory (k rows x N)
                         const int kr = (MODE == ASCA_TN ? x.row_base_k : 0) + k0 + x.b_out;
-                        tc::tma_load_2d(b_s, &mapB, x.n0 + x.b_in, kr, &full[s]);
-                        tc::tma_load_2d(b_s + 8192, &mapB, x.n0 + 64 + x.b_in, kr, &full[s]);
+#pragma unroll
+                        for (int nb = 0; nb < BN / 64; ++nb)   // boxes of 64 columns
+                            tc::tma_load_2d(b_s + nb * 8192, &mapB, x.n0 + nb * 64 + x.b_in, kr, &full[s]);
                     } else {      // memory (N rows x K)
                         tc::tma_load_2d(b_s, &mapB, k0 + x.b_in, x.n0 + x.b_out, &full[s]);
                     }
@@ -430,12 +444,13 @@ bool supported(const Args& a) {
     return true;
 }
 
-int launch(asca_ctx* ctx, const Args& a) {
+template <int BN>
+static int launch_shape(asca_ctx* ctx, const Args& a, int64_t grid) {
     CUtensorMap mapA, mapB;
     bool ok;
     if (a.mode == ASCA_TN) ok = make_map(&mapA, a.A, a.a_rows, a.a_cols, a.lda, 64, 64);
     else ok = make_map(&mapA, a.A, a.a_rows, a.a_cols, a.lda, 64, 128);
-    if (a.mode == ASCA_NT) ok = ok && make_map(&mapB, a.B, a.b_rows, a.b_cols, a.ldb, 64, 128);
+    if (a.mode == ASCA_NT) ok = ok && make_map(&mapB, a.B, a.b_rows, a.b_cols, a.ldb, 64, BN);
     else ok = ok && make_map(&mapB, a.B, a.b_rows, a.b_cols, a.ldb, 64, 64);
     if (!ok) return asca_fail(ctx, ASCA_ERR_CUDA, "gemm_tc: cuTensorMapEncodeTiled failed");
     KP p{};
@@ -446,27 +461,40 @@ int launch(asca_ctx* ctx, const Args& a) {
     p.c_gstride = a.c_gstride; p.bias_gstride = a.bias_gstride;
     p.epi = a.epi; p.aux = a.aux; p.ldaux = a.ldaux; p.C2 = a.C2; p.ldc2 = a.ldc2;
     p.err_word = ctx->err_word;
-    const int64_t tn = (a.N + BN - 1) / BN;
-    int64_t grid;
-    if (a.group_dim == GROUP_NONE) grid = ((int64_t)(a.M + BM - 1) / BM) * tn;
-    else if (a.group_dim == GROUP_M) grid = (a.total_rows / BM + a.n_groups) * tn;
-    else grid = (int64_t)a.n_groups * ((a.M + BM - 1) / BM) * tn;
-    if (grid <= 0) return ASCA_OK;
-    // persistent: two CTAs per SM walk the tiles round-robin (`grid` is an upper bound on the tile count)
-    const int n_sm = ctx->sm_count > 0 ? ctx->sm_count : 148;
-    if (grid > 2 * n_sm) grid = 2 * n_sm;
-    const size_t smem = SMEM_FIXED + (size_t)((a.group_dim == GROUP_NONE ? 1 : a.n_groups) + 2) * 4;
+    const size_t smem = Shape<BN>::SMEM_FIXED + (size_t)((a.group_dim == GROUP_NONE ? 1 : a.n_groups) + 2) * 4;
     auto go = [&](auto kern) -> cudaError_t {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(SMEM_FIXED + (MAX_GROUPS + 2) * 4));
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)(Shape<BN>::SMEM_FIXED + (MAX_GROUPS + 2) * 4));
         if (e != cudaSuccess) return e;
         kern<<<(unsigned)grid, THREADS, smem, ctx->stream>>>(mapA, mapB, p);
         return cudaGetLastError();
     };
-    cudaError_t e = a.mode == ASCA_NN ? go(gemm_tc_kernel<ASCA_NN>)
-                    : a.mode == ASCA_TN ? go(gemm_tc_kernel<ASCA_TN>) : go(gemm_tc_kernel<ASCA_NT>);
+    cudaError_t e = a.mode == ASCA_NN ? go(gemm_tc_kernel<ASCA_NN, BN>)
+                    : a.mode == ASCA_TN ? go(gemm_tc_kernel<ASCA_TN, BN>) : go(gemm_tc_kernel<ASCA_NT, BN>);
     ASCA_CUDA(ctx, e);
     ctx->launches++;
     return ASCA_OK;
+}
+
+// upper bound on the number of 128 x bn tiles (exact unless rows are grouped by expert)
+static int64_t tile_bound(const Args& a, int bn) {
+    const int64_t tn = (a.N + bn - 1) / bn;
+    if (a.group_dim == GROUP_NONE) return ((int64_t)(a.M + BM - 1) / BM) * tn;
+    if (a.group_dim == GROUP_M) return (a.total_rows / BM + a.n_groups) * tn;
+    return (int64_t)a.n_groups * ((a.M + BM - 1) / BM) * tn;
+}
+
+int launch(asca_ctx* ctx, const Args& a) {
+    const int n_sm = ctx->sm_count > 0 ? ctx->sm_count : 148;
+    // persistent: the CTAs walk the tiles round-robin. Wide tiles for dense problems with a long k-loop and at least
+    // two waves of tiles (measured: +10-15 % there; with k <= 2048 or expert-grouped rows the 128 KiB epilogue per
+    // tile and the single stream per SM cost more than the wider instruction gains).
+    const int64_t wide = tile_bound(a, 256);
+    if (a.group_dim == GROUP_NONE && a.K >= 4096 && a.N >= 256 && wide >= 2 * n_sm)
+        return launch_shape<256>(ctx, a, std::min<int64_t>(wide, n_sm));
+    const int64_t grid = tile_bound(a, 128);
+    if (grid <= 0) return ASCA_OK;
+    return launch_shape<128>(ctx, a, std::min<int64_t>(grid, 2 * n_sm));
 }
 
 }  // namespace gemm_tc

@@ -67,6 +67,33 @@ def test_gemm_bias_accumulate_and_bf16(orc, gpu):
     assert rel_err(got_t.cpu().numpy(), ref16) < 1e-5 and rel_err(got_nt.cpu().numpy(), ref16) < 1e-5
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("mode", ["NN", "TN", "NT"])
+def test_gemm_bf16_large_shapes_take_the_wide_tile_path(gpu, mode):
+    """Dense bf16 products big enough for the 128 x 256 tiles (two waves, k >= 4096), with ragged M and N and
+    accumulation: sampled output rows against float64 products of the same rounded inputs."""
+    import torch
+    import asca_b200
+    from asca_b200 import ops
+
+    M, N, K = 4200, 5000 + 8, 4096 + 64
+    g = torch.Generator(device="cuda").manual_seed(17)
+    a = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    b = torch.randn(K, N, device="cuda", generator=g).bfloat16()
+    c0 = torch.randn(M, N, device="cuda", generator=g)
+    out = c0.clone()
+    if mode == "NN":
+        ops.gemm(gpu, a, b, asca_b200.NN, out=out, accumulate=True)
+    elif mode == "TN":
+        ops.gemm(gpu, a.t().contiguous(), b, asca_b200.TN, out=out, accumulate=True)
+    else:
+        ops.gemm(gpu, a, b.t().contiguous(), asca_b200.NT, out=out, accumulate=True)
+    gpu.sync()
+    rows = torch.tensor([0, 1, 127, 128, 2049, 4095, 4096, 4199], device="cuda")
+    ref = a[rows].double() @ b.double() + c0[rows].double()
+    assert rel_err(out[rows].cpu().numpy(), ref.cpu().numpy()) < 1e-5
+
+
 # ------------------------------------------------------------------ RMSNorm
 @pytest.mark.parametrize("rows,cols", [(1, 64), (257, 64), (100, 192), (33, 1024), (17, 2048), (5, 1000), (9, 7)])
 def test_rmsnorm_fwd_bwd(orc, gpu, rows, cols):
