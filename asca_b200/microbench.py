@@ -144,6 +144,14 @@ def main():
                 ms = timeit(lambda i: ops.gemm(gpu, a, b, asca_b200.NN, out=c), max(2, args.reps // 5), warmup=1)
                 report(f"gemm NN {m_}x{n_}x{k_} {str(dt).split('.')[-1]}", ms, flops=2 * m_ * n_ * k_)
                 del a, b, c
+        # the transposed forms at the training step's shapes (input gradient and weight gradient of the qkv projection)
+        for mode, name, (m_, n_, k_) in ((asca_b200.NT, "NT", (32768, 2048, 6144)), (asca_b200.TN, "TN", (2048, 6144, 32768))):
+            a = torch.randn((k_, m_) if mode == asca_b200.TN else (m_, k_), generator=g, **f32).bfloat16()
+            b = torch.randn((n_, k_) if mode == asca_b200.NT else (k_, n_), generator=g, **f32).bfloat16()
+            c = torch.empty(m_, n_, **f32)
+            ms = timeit(lambda i: ops.gemm(gpu, a, b, mode, out=c), max(2, args.reps // 5), warmup=1)
+            report(f"gemm {name} {m_}x{n_}x{k_} bfloat16", ms, flops=2 * m_ * n_ * k_)
+            del a, b, c
 
     if want("moe"):
         n, d, F, E = 65536, 1024, 4096, 64
