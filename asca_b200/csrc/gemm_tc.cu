@@ -202,7 +202,15 @@ __global__ void __launch_bounds__(THREADS, Shape<BN>::CTAS_PER_SM) gemm_tc_kerne
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
+        // One thread runs the loop (the rest of the warp joins only to zero a ragged k-tile): wait for the
+        // stage, four tcgen05.mma whose descriptors are the stage's base descriptor plus a constant, commit.
+        // The loop's own dependent instructions are what bounds a single MMA stream, so it is kept short.
         constexpr uint32_t IDESC = tc::idesc_bf16_f32(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+        constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);          // SBO 1024, version 1, 128-byte swizzle
+        constexpr uint32_t A_LBO = (A_MN ? 8192u : 16u) >> 4, B_LBO = (B_MN ? 8192u : 16u) >> 4;
+        constexpr uint32_t A_K16 = (A_MN ? 2048u : 32u) >> 4, B_K16 = (B_MN ? 2048u : 32u) >> 4;   // per k16 step, in 16-byte units
+        const uint32_t a_lo0 = ((tc::smem_u32(tiles) >> 4) & 0x3FFF) | (A_LBO << 16);
+        const uint32_t b_lo0 = (((tc::smem_u32(tiles) + A_BYTES) >> 4) & 0x3FFF) | (B_LBO << 16);
         bool ok = true;
         uint32_t it = 0;
         int tl = 0;   // tiles done by this CTA: accumulator buffer tl & 1
@@ -210,24 +218,40 @@ __global__ void __launch_bounds__(THREADS, Shape<BN>::CTAS_PER_SM) gemm_tc_kerne
             const Tile x = locate(t);
             const int buf = tl & 1;
             const uint32_t tmem_acc = tmem_base + buf * BN;
-            int got = 1;
-            if (tl >= 2 && lane == 0)   // the epilogue has read this buffer's previous tile out
-                got = tc::mbar_wait(&acc_empty[buf], ((tl >> 1) - 1) & 1, abort_flag, p.err_word, 104) ? 1 : 0;
-            ok = __shfl_sync(0xffffffffu, got, 0) != 0;
-            if (!ok) break;
-            tc::tcgen05_fence_after();
-            for (int kt = 0; kt < x.num_k && ok; ++kt, ++it) {
-                const int s = it % STAGES;
-                // lane 0 polls, the verdict is broadcast so the warp stays converged
-                got = 0;
-                if (lane == 0) got = tc::mbar_wait(&full[s], (it / STAGES) & 1, abort_flag, p.err_word, 102) ? 1 : 0;
-                ok = __shfl_sync(0xffffffffu, got, 0) != 0;
-                if (!ok) break;
+            const bool ragged = p.group_dim == GROUP_K && (x.K % BK) != 0;   // warp-uniform
+            const int n_plain = ragged ? x.num_k - 1 : x.num_k;
+            if (lane == 0) {
+                if (tl >= 2)   // the epilogue has read this buffer's previous tile out
+                    ok = tc::mbar_wait(&acc_empty[buf], ((tl >> 1) - 1) & 1, abort_flag, p.err_word, 104);
                 tc::tcgen05_fence_after();
-                uint8_t* a_s = tiles + s * STAGE_BYTES;
-                uint8_t* b_s = a_s + A_BYTES;
-                if (p.group_dim == GROUP_K && (kt + 1) * BK > x.K) {
-                    // ragged last k-tile of this expert: rows >= K - kt*BK belong to the next expert
+                for (int kt = 0; kt < n_plain && ok; ++kt, ++it) {
+                    const uint32_t s = it % STAGES;
+                    ok = tc::mbar_wait(&full[s], (it / STAGES) & 1, abort_flag, p.err_word, 102);
+                    if (!ok) break;
+                    tc::tcgen05_fence_after();
+                    const uint32_t a_lo = a_lo0 + s * (STAGE_BYTES >> 4), b_lo = b_lo0 + s * (STAGE_BYTES >> 4);
+#pragma unroll
+                    for (int k16 = 0; k16 < BK / 16; ++k16)
+                        tc::umma_bf16(tmem_acc, ((uint64_t)DESC_HI << 32) | (a_lo + k16 * A_K16),
+                                      ((uint64_t)DESC_HI << 32) | (b_lo + k16 * B_K16), IDESC, (kt > 0 || k16 > 0) ? 1u : 0u);
+                    tc::umma_commit(&empty[s]);                       // slot free once these MMAs retire
+                    if (kt == x.num_k - 1) tc::umma_commit(&acc_full[buf]);
+                }
+            }
+            if (ragged) {
+                // last k-tile of this expert: rows >= K - kt*BK belong to the next expert and are zeroed by the whole warp
+                const int kt = x.num_k - 1;
+                int got = 0;
+                if (lane == 0) {
+                    got = ok && tc::mbar_wait(&full[(it) % STAGES], ((it) / STAGES) & 1, abort_flag, p.err_word, 102) ? 1 : 0;
+                }
+                got = __shfl_sync(0xffffffffu, got, 0);
+                const uint32_t it_r = __shfl_sync(0xffffffffu, it, 0);
+                ok = got != 0;
+                if (ok) {
+                    tc::tcgen05_fence_after();
+                    const uint32_t s = it_r % STAGES;
+                    uint8_t* a_s = tiles + s * STAGE_BYTES;
                     const int valid = x.K - kt * BK;
                     const int lines = (BK - valid) * 2;  // 128-byte lines in the two A boxes
                     for (int i = lane; i < lines * 8; i += 32) {
@@ -237,23 +261,20 @@ __global__ void __launch_bounds__(THREADS, Shape<BN>::CTAS_PER_SM) gemm_tc_kerne
                     }
                     tc::fence_proxy_async_smem();
                     __syncwarp();
-                }
-                if (lane == 0) {
-                    const uint32_t a_addr = tc::smem_u32(a_s), b_addr = tc::smem_u32(b_s);
+                    if (lane == 0) {
+                        const uint32_t a_lo = a_lo0 + s * (STAGE_BYTES >> 4), b_lo = b_lo0 + s * (STAGE_BYTES >> 4);
 #pragma unroll
-                    for (int k16 = 0; k16 < BK / 16; ++k16) {
-                        const uint64_t ad = A_MN ? tc::smem_desc_sw128(a_addr + k16 * 2048, 8192, 1024)
-                                                 : tc::smem_desc_sw128(a_addr + k16 * 32, 16, 1024);
-                        const uint64_t bd = B_MN ? tc::smem_desc_sw128(b_addr + k16 * 2048, 8192, 1024)
-                                                 : tc::smem_desc_sw128(b_addr + k16 * 32, 16, 1024);
-                        tc::umma_bf16(tmem_acc, ad, bd, IDESC, (kt > 0 || k16 > 0) ? 1u : 0u);
+                        for (int k16 = 0; k16 < BK / 16; ++k16)
+                            tc::umma_bf16(tmem_acc, ((uint64_t)DESC_HI << 32) | (a_lo + k16 * A_K16),
+                                          ((uint64_t)DESC_HI << 32) | (b_lo + k16 * B_K16), IDESC, (kt > 0 || k16 > 0) ? 1u : 0u);
+                        tc::umma_commit(&empty[s]);
+                        tc::umma_commit(&acc_full[buf]);
+                        ++it;
                     }
-                    tc::umma_commit(&empty[s]);                       // slot free once these MMAs retire
-                    if (kt == x.num_k - 1) tc::umma_commit(&acc_full[buf]);
                 }
-                __syncwarp();
             }
-            if (ok && x.num_k == 0 && lane == 0) tc::mbar_arrive(&acc_full[buf]);   // empty expert: the epilogue stores zeros
+            if (lane == 0 && ok && x.num_k == 0) tc::mbar_arrive(&acc_full[buf]);   // empty expert: the epilogue stores zeros
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;   // lane 0's verdict; keeps the warp's tile loops in step
         }
     } else {
         // ------------------------------------------------------------ epilogue (warps 2..5)
@@ -280,6 +301,11 @@ __global__ void __launch_bounds__(THREADS, Shape<BN>::CTAS_PER_SM) gemm_tc_kerne
             tc::tcgen05_fence_after();
             float* cbase = p.C + (p.group_dim == GROUP_K ? (int64_t)x.g * p.c_gstride : 0);
             const int rows_here = x.M - (x.m0 + q * 32);   // live rows of this warp's quarter (may be <= 0 or > 32)
+            // the common case gets straight-line code: full tile, plain f32 output (bias and accumulate allowed)
+            const bool fast = c_vec && !p.c_idx && !p.C2 && p.epi == EPI_NONE && rows_here >= 32 && x.n0 + BN <= p.N &&
+                              (!p.bias || (((reinterpret_cast<uintptr_t>(p.bias) & 15) == 0) && (p.bias_gstride & 3) == 0));
+            float* frow = cbase + ((int64_t)x.row_base_m + x.m0 + q * 32 + rsub) * p.ldc + x.n0 + 4 * l4;   // row rsub, this lane's columns
+            const float* fbias = p.bias ? p.bias + (int64_t)x.g * p.bias_gstride + x.n0 + 4 * l4 : nullptr;
             // row bookkeeping of the 4 store iterations: row = 8 * i + rsub
             int64_t lrs[4], crs[4];
 #pragma unroll
@@ -311,6 +337,24 @@ __global__ void __launch_bounds__(THREADS, Shape<BN>::CTAS_PER_SM) gemm_tc_kerne
                             make_float4(__uint_as_float(r[16 * hlf + 4 * j]), __uint_as_float(r[16 * hlf + 4 * j + 1]),
                                         __uint_as_float(r[16 * hlf + 4 * j + 2]), __uint_as_float(r[16 * hlf + 4 * j + 3]));
                     __syncwarp();
+                    if (fast) {
+                        const int co = c * 32 + hlf * 16;
+                        float4 b4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f), acc4[4], old4[4];
+                        if (fbias) b4 = *reinterpret_cast<const float4*>(fbias + co);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            acc4[i] = stg[(8 * i + rsub) * 4 + (l4 ^ (((8 * i + rsub) >> 1) & 3))];
+                            old4[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                            if (p.accumulate) old4[i] = *reinterpret_cast<const float4*>(frow + (int64_t)(8 * i) * p.ldc + co);
+                        }
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            *reinterpret_cast<float4*>(frow + (int64_t)(8 * i) * p.ldc + co) =
+                                make_float4(acc4[i].x + b4.x + old4[i].x, acc4[i].y + b4.y + old4[i].y,
+                                            acc4[i].z + b4.z + old4[i].z, acc4[i].w + b4.w + old4[i].w);
+                        __syncwarp();
+                        continue;
+                    }
                     const int nb = x.n0 + c * 32 + hlf * 16 + 4 * l4;   // this lane's 4 columns in the store phase
                     if (nb < p.N) {
                         const bool full4 = nb + 4 <= p.N;
