@@ -36,12 +36,14 @@ constexpr int A_BYTES = BM * BK * 2;
 // tensor pipe fed). 128 x 256: one M128 N256 K16 instruction does twice the work of an N128 one for the same issue
 // latency, so a single stream per SM suffices: 4-stage ring of 48 KiB, all 512 TMEM columns, one CTA per SM. It is
 // used when the problem has at least two waves of such tiles.
-template <int BN> struct Shape {
-    static constexpr int STAGES = BN == 128 ? 3 : 4;
+// DEEP: a problem of at most one 128 x 128 tile per SM (a decode step's products) runs one CTA per SM with a
+// 6-stage ring: its k-loop streams weights that are cold in L2, and three stages do not cover the HBM latency.
+template <int BN, bool DEEP = false> struct Shape {
+    static constexpr int STAGES = BN == 128 ? (DEEP ? 6 : 3) : 4;
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int TMEM_COLS = 2 * BN;      // two accumulator buffers
-    static constexpr int CTAS_PER_SM = BN == 128 ? 2 : 1;
+    static constexpr int CTAS_PER_SM = (BN == 128 && !DEEP) ? 2 : 1;
     static constexpr size_t SMEM_FIXED = (size_t)STAGES * STAGE_BYTES + 4 * 2048 /*epilogue staging*/ + 1024 /*alignment slack*/ +
                                          256 /*barriers*/;   // + (groups + 2) * 4 for the tile table
 };
@@ -74,12 +76,12 @@ __device__ __forceinline__ float silu_grad_f(float p) {
     return sg * (1.0f + p * (1.0f - sg));
 }
 
-template <int MODE, int BN>
-__global__ void __launch_bounds__(THREADS, Shape<BN>::CTAS_PER_SM) gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA,
+template <int MODE, int BN, bool DEEP>
+__global__ void __launch_bounds__(THREADS, Shape<BN, DEEP>::CTAS_PER_SM) gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA,
                                                              const __grid_constant__ CUtensorMap mapB, const KP p) {
     constexpr bool A_MN = (MODE == ASCA_TN);   // A operand MN-major
     constexpr bool B_MN = (MODE != ASCA_NT);   // B operand MN-major
-    constexpr int STAGES = Shape<BN>::STAGES, STAGE_BYTES = Shape<BN>::STAGE_BYTES, TMEM_COLS = Shape<BN>::TMEM_COLS;
+    constexpr int STAGES = Shape<BN, DEEP>::STAGES, STAGE_BYTES = Shape<BN, DEEP>::STAGE_BYTES, TMEM_COLS = Shape<BN, DEEP>::TMEM_COLS;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* staging = tiles + STAGES * STAGE_BYTES;                 // 4 epilogue warps x 2 KiB
@@ -490,7 +492,7 @@ bool supported(const Args& a) {
     return true;
 }
 
-template <int BN>
+template <int BN, bool DEEP>
 static int launch_shape(asca_ctx* ctx, const Args& a, int64_t grid) {
     CUtensorMap mapA, mapB;
     bool ok;
@@ -507,16 +509,16 @@ static int launch_shape(asca_ctx* ctx, const Args& a, int64_t grid) {
     p.c_gstride = a.c_gstride; p.bias_gstride = a.bias_gstride;
     p.epi = a.epi; p.aux = a.aux; p.ldaux = a.ldaux; p.C2 = a.C2; p.ldc2 = a.ldc2;
     p.err_word = ctx->err_word;
-    const size_t smem = Shape<BN>::SMEM_FIXED + (size_t)((a.group_dim == GROUP_NONE ? 1 : a.n_groups) + 2) * 4;
+    const size_t smem = Shape<BN, DEEP>::SMEM_FIXED + (size_t)((a.group_dim == GROUP_NONE ? 1 : a.n_groups) + 2) * 4;
     auto go = [&](auto kern) -> cudaError_t {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)(Shape<BN>::SMEM_FIXED + (MAX_GROUPS + 2) * 4));
+                                             (int)(Shape<BN, DEEP>::SMEM_FIXED + (MAX_GROUPS + 2) * 4));
         if (e != cudaSuccess) return e;
         kern<<<(unsigned)grid, THREADS, smem, ctx->stream>>>(mapA, mapB, p);
         return cudaGetLastError();
     };
-    cudaError_t e = a.mode == ASCA_NN ? go(gemm_tc_kernel<ASCA_NN, BN>)
-                    : a.mode == ASCA_TN ? go(gemm_tc_kernel<ASCA_TN, BN>) : go(gemm_tc_kernel<ASCA_NT, BN>);
+    cudaError_t e = a.mode == ASCA_NN ? go(gemm_tc_kernel<ASCA_NN, BN, DEEP>)
+                    : a.mode == ASCA_TN ? go(gemm_tc_kernel<ASCA_TN, BN, DEEP>) : go(gemm_tc_kernel<ASCA_NT, BN, DEEP>);
     ASCA_CUDA(ctx, e);
     ctx->launches++;
     return ASCA_OK;
@@ -537,10 +539,11 @@ int launch(asca_ctx* ctx, const Args& a) {
     // tile and the single stream per SM cost more than the wider instruction gains).
     const int64_t wide = tile_bound(a, 256);
     if (a.group_dim == GROUP_NONE && a.K >= 4096 && a.N >= 256 && wide >= 2 * n_sm)
-        return launch_shape<256>(ctx, a, std::min<int64_t>(wide, n_sm));
+        return launch_shape<256, false>(ctx, a, std::min<int64_t>(wide, n_sm));
     const int64_t grid = tile_bound(a, 128);
     if (grid <= 0) return ASCA_OK;
-    return launch_shape<128>(ctx, a, std::min<int64_t>(grid, 2 * n_sm));
+    if (grid <= n_sm) return launch_shape<128, true>(ctx, a, grid);
+    return launch_shape<128, false>(ctx, a, std::min<int64_t>(grid, 2 * n_sm));
 }
 
 }  // namespace gemm_tc
