@@ -42,8 +42,6 @@ struct Tiles {            // intermediate buffers, one tile per (chain, chunk)
     __nv_bfloat16* BK;    // [tile][64][DH]  beta gam K
     __nv_bfloat16* BV;    // [tile] beta V, 64 x DH, lane-major (see lm_off128)
     __nv_bfloat16* UVT;   // [tile] Uv, 64 x DH, lane-major copy for the backward
-    __nv_bfloat16* KR;    // [tile][64][DH]  K (zero-padded copy)
-    __nv_bfloat16* QR;    // [tile][64][DH]  Q (zero-padded copy)
     __nv_bfloat16* TP;    // [tile][64][64]  T' = (I+L)^-1 - I, row-major
     __nv_bfloat16* KKo;   // [tile] K K^T, 64 x 64, lane-major (see lm_off64)
     __nv_bfloat16* QKo;   // [tile] Q K^T, 64 x 64, lane-major
@@ -195,8 +193,6 @@ __global__ void __launch_bounds__(PRE_THREADS, 3) delta_prep_tc_kernel(
             *reinterpret_cast<uint4*>(out.KW + o64) = tc::pack8_bf16(tmp);
             if (out.BK) {
                 *reinterpret_cast<uint4*>(out.BK + o64) = bk;
-                *reinterpret_cast<uint4*>(out.KR + o64) = k8[it];
-                *reinterpret_cast<uint4*>(out.QR + o64) = q8[it];
             }
         }
     }
@@ -428,7 +424,8 @@ constexpr size_t CH_SMEM = 1024 + 2 * STAGE_BYTES + NB * DH * 128 /*S bf16*/ + N
 template <typename TO>
 __global__ void __launch_bounds__(CH_THREADS, 1) delta_fwd_tc_kernel(
     const __grid_constant__ CUtensorMap mapWQ, const __grid_constant__ CUtensorMap mapUV,
-    const __grid_constant__ CUtensorMap mapKW, const __grid_constant__ CUtensorMap mapAA, const float* __restrict__ GC,
+    const __grid_constant__ CUtensorMap mapKW, const __grid_constant__ CUtensorMap mapAA,
+    const __grid_constant__ CUtensorMap mapS0, const float* __restrict__ GC,
     int T, int H, int n_chunks, TO* __restrict__ o, const float* __restrict__ s_init, float* __restrict__ s_final,
     float* __restrict__ ckpt, __nv_bfloat16* __restrict__ s0b, int* err_word) {
     extern __shared__ uint8_t smem_raw[];
@@ -507,6 +504,11 @@ __global__ void __launch_bounds__(CH_THREADS, 1) delta_fwd_tc_kernel(
                 if (!tc::mbar_wait(&full[s], (c >> 1) & 1, abort_flag, err_word, 211)) break;
                 if (!tc::mbar_wait(s_ready, c & 1, abort_flag, err_word, 212)) break;
                 tc::tcgen05_fence_after();
+                if (s0b) {   // the state at the start of chunk c, bf16, straight from the operand tile: two 128 x 64 boxes
+                    tc::tma_store_2d(&mapS0, S_s, 0, (int)(tile0 + c) * DH);
+                    tc::tma_store_2d(&mapS0, S_s + DH * 128, 64, (int)(tile0 + c) * DH);
+                    tc::bulk_commit_group();
+                }
                 // D1 = [W^ ; Qg] S0
 #pragma unroll
                 for (int k16 = 0; k16 < DH / 16; ++k16)
@@ -524,19 +526,19 @@ __global__ void __launch_bounds__(CH_THREADS, 1) delta_fwd_tc_kernel(
                 for (int k16 = 0; k16 < C / 16; ++k16)
                     tc::umma_bf16(tmem_S, tc::smem_desc_sw128(st + NB * 24576 + k16 * 2048, 8192, 1024),
                                   tc::smem_desc_sw128(u_addr + k16 * 2048, 8192, 1024), ID3, 1u);
+                if (s0b) tc::bulk_wait_read();   // the state store has read the operand tile: it may be rewritten after this commit
                 tc::umma_commit(mma2_done);
                 if (c + 2 < n_chunks) {
                     if (!tc::mbar_wait(mma2_done, c & 1, abort_flag, err_word, 214)) break;
                     load(c + 2, s);
                 }
             }
+            if (s0b) tc::bulk_wait_all();   // stores have landed before the CTA exits
         }
     } else {
         // ------------------------------------------------------------ compute threads: TMEM lane = tid
         const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
         float* ck = ckpt ? ckpt + tile0 * DH * DH : nullptr;
-        // bf16 copy of every chunk's starting state, row-major [DH][DH], for the backward's TMA loads
-        __nv_bfloat16* sb16 = s0b ? s0b + tile0 * DH * DH + (int64_t)tid * DH : nullptr;
         // initial state: checkpoint 0, bf16 operand copy, f32 state scaled by the first chunk's decay
         {
             const float g0 = GC[tile0];
@@ -558,7 +560,6 @@ __global__ void __launch_bounds__(CH_THREADS, 1) delta_fwd_tc_kernel(
                     const int chunk16 = cc * 4 + j;   // 16-byte chunk index along the row (8 bf16 each)
                     const uint4 pk = tc::pack8_bf16(f + 8 * j);
                     *reinterpret_cast<uint4*>(S_s + (chunk16 >> 3) * (DH * 128) + tc::sw128_off(tid, chunk16 & 7)) = pk;
-                    if (sb16) reinterpret_cast<uint4*>(sb16)[chunk16] = pk;
                 }
 #pragma unroll
                 for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(g0 * f[j]);
@@ -654,7 +655,6 @@ __global__ void __launch_bounds__(CH_THREADS, 1) delta_fwd_tc_kernel(
                         const int chunk16 = cc * 4 + j;
                         const uint4 pk = tc::pack8_bf16(f + 8 * j);
                         *reinterpret_cast<uint4*>(S_s + (chunk16 >> 3) * (DH * 128) + tc::sw128_off(tid, chunk16 & 7)) = pk;
-                        if (sb16) reinterpret_cast<uint4*>(sb16 + (int64_t)(c + 1) * DH * DH)[chunk16] = pk;
                     }
 #pragma unroll
                     for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(gnext * f[j]);
@@ -794,8 +794,11 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
 #pragma unroll
         for (int kb = 0; kb < 2; ++kb) {
             tc::tma_load_2d(sm + R_QG + kb * 8192, &mapWQ, kb * 64, t * 128 + 64, &bars[8]);
-            tc::tma_load_2d(sm + R_K + kb * 8192, &mapKR, kb * 64, t * 64, &bars[8]);
-            tc::tma_load_2d(sm + R_Q + kb * 8192, &mapQR, kb * 64, t * 64, &bars[8]);
+            // K and Q straight from the caller's tensors (like dO): rows past the sequence end hold the next
+            // sequence's tokens (or TMA's zero fill past the tensor); every product that reads them multiplies by an
+            // exact zero there (beta = 0, U rows = 0, and dA rows masked below)
+            tc::tma_load_2d(sm + R_K + kb * 8192, &mapKR, h * DH + kb * 64, grow, &bars[8]);
+            tc::tma_load_2d(sm + R_Q + kb * 8192, &mapQR, h * DH + kb * 64, grow, &bars[8]);
         }
     };
     auto wait_bar = [&](int i, uint32_t parity) {
@@ -1054,7 +1057,7 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
                         const int i = colhalf * DW + 8 * j + e;
                         const float gm = i <= row ? __expf(g_row - g_s[i]) : 0.0f;
                         const float dlg = i < row ? -__uint_as_float(rl[8 * j + e]) * gm : 0.0f;   // dL.Gam
-                        const float dag = __uint_as_float(ra[8 * j + e]) * gm;                     // dA.Gam
+                        const float dag = live ? __uint_as_float(ra[8 * j + e]) * gm : 0.0f;       // dA.Gam (dO rows past the end are not ours)
                         dls = fmaf(dlg, kk8[e], dls);
                         m8[e] = dlg * be_row;
                         a8[e] = dag;
@@ -1301,8 +1304,6 @@ static size_t carve_tiles(char* w, int64_t n_tiles, bool full, Tiles* t) {
         z.BK = (__nv_bfloat16*)take(b64);
         z.BV = (__nv_bfloat16*)take(b64);
         z.UVT = (__nv_bfloat16*)take(b64);
-        z.KR = (__nv_bfloat16*)take(b64);
-        z.QR = (__nv_bfloat16*)take(b64);
         z.TP = (__nv_bfloat16*)take(bcc);
         z.KKo = (__nv_bfloat16*)take(bcc);
         z.QKo = (__nv_bfloat16*)take(bcc);
@@ -1357,15 +1358,16 @@ int forward(asca_ctx* ctx, const void* q, const void* k, const void* v, const fl
     w = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(w) + 1023) & ~(uintptr_t)1023);
     carve_tiles(w, n_tiles, keep, &t);
     ASCA_TRY(run_prepass(ctx, q, k, v, alpha, beta, T, H, n_chunks, chains, t));
-    CUtensorMap mWQ, mUV, mKW, mAA;
+    CUtensorMap mWQ, mUV, mKW, mAA, mS0;
     if (!make_map(&mWQ, t.WQ, n_tiles * 128, DH, 64, 128) || !make_map(&mUV, t.UV, n_tiles * 64, DH, 64, 64) ||
-        !make_map(&mKW, t.KW, n_tiles * 64, DH, 64, 64) || !make_map(&mAA, t.AA, n_tiles * 64, 64, 64, 64))
+        !make_map(&mKW, t.KW, n_tiles * 64, DH, 64, 64) || !make_map(&mAA, t.AA, n_tiles * 64, 64, 64, 64) ||
+        !make_map(&mS0, keep ? (const void*)ckpt : (const void*)t.WQ, n_tiles * DH, DH, 64, 128))   // bf16 states in the checkpoint buffer
         return asca_fail(ctx, ASCA_ERR_CUDA, "delta_tc: cuTensorMapEncodeTiled failed");
     auto kern = delta_fwd_tc_kernel<__nv_bfloat16>;
     ASCA_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)CH_SMEM));
     {
         asca_span sp(ctx, "delta_fwd_tc_kernel");
-        kern<<<(unsigned)chains, CH_THREADS, CH_SMEM, ctx->stream>>>(mWQ, mUV, mKW, mAA, t.GC, (int)T, (int)H,
+        kern<<<(unsigned)chains, CH_THREADS, CH_SMEM, ctx->stream>>>(mWQ, mUV, mKW, mAA, mS0, t.GC, (int)T, (int)H,
                                                                     (int)n_chunks, (__nv_bfloat16*)o, s_init, s_final,
                                                                     nullptr, reinterpret_cast<__nv_bfloat16*>(ckpt), ctx->err_word);
     }
@@ -1400,8 +1402,8 @@ int backward(asca_ctx* ctx, const void* q, const void* k, const void* v, const f
     }
     CUtensorMap mWQ, mBK, mKW, mKR, mQR, mDO, mAA, mTP, mS0;
     bool ok = make_map(&mWQ, t.WQ, n_tiles * 128, DH, 64, 64) && make_map(&mBK, t.BK, n_tiles * 64, DH, 64, 64) &&
-              make_map(&mKW, t.KW, n_tiles * 64, DH, 64, 64) && make_map(&mKR, t.KR, n_tiles * 64, DH, 64, 64) &&
-              make_map(&mQR, t.QR, n_tiles * 64, DH, 64, 64) && make_map(&mDO, d_o, B * T, H * DH, 64, 64) &&
+              make_map(&mKW, t.KW, n_tiles * 64, DH, 64, 64) && make_map(&mKR, k, B * T, H * DH, 64, 64) &&
+              make_map(&mQR, q, B * T, H * DH, 64, 64) && make_map(&mDO, d_o, B * T, H * DH, 64, 64) &&
               make_map(&mAA, t.AA, n_tiles * 64, 64, 64, 64) && make_map(&mTP, t.TP, n_tiles * 64, 64, 64, 64) &&
               make_map(&mS0, ckpt, n_tiles * DH, DH, 64, 128);
     if (!ok) return asca_fail(ctx, ASCA_ERR_CUDA, "delta_tc: cuTensorMapEncodeTiled failed");
