@@ -29,11 +29,17 @@ struct asca_ctx {
     void* ws = nullptr;
     size_t ws_bytes = 0;
     int* err_word = nullptr;  // device int the kernels with bounded waits write to
-    // tiles of the last tensor-core delta forward that wrote checkpoints, kept for its backward
-    void* dcache = nullptr;
-    size_t dcache_bytes = 0;
-    const void* dcache_ckpt = nullptr;   // key: the checkpoint buffer the forward filled
-    int64_t dcache_B = 0, dcache_T = 0, dcache_H = 0;
+    // tiles of the tensor-core delta forwards that wrote checkpoints, kept for their backwards: one entry per
+    // checkpoint buffer (a model keeps one per block), least recently used evicted beyond 32 entries / 64 GiB
+    struct DeltaTiles {
+        const void* ckpt = nullptr;   // key: the checkpoint buffer the forward filled (null: contents invalid)
+        int64_t B = 0, T = 0, H = 0;
+        void* buf = nullptr;
+        size_t bytes = 0;
+        uint64_t stamp = 0;
+    };
+    std::vector<DeltaTiles> dtiles;
+    uint64_t dtiles_clock = 0;
     // optional per-kernel timing (asca_ctx_profile): CUDA events around selected launches
     bool profiling = false;
     struct Span {

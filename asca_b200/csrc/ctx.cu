@@ -70,7 +70,8 @@ int asca_ctx_destroy(asca_ctx* ctx) {
     for (auto& kv : ctx->pool) cudaFree(kv.second);
     for (auto& kv : ctx->live) cudaFree(kv.first);
     if (ctx->ws) cudaFree(ctx->ws);
-    if (ctx->dcache) cudaFree(ctx->dcache);
+    for (auto& e : ctx->dtiles)
+        if (e.buf) cudaFree(e.buf);
     if (ctx->err_word) cudaFree(ctx->err_word);
     cudaStreamDestroy(ctx->own_stream);
     delete ctx;

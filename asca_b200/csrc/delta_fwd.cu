@@ -430,7 +430,9 @@ int asca_delta_fwd(asca_ctx* ctx, const void* q, const void* k, const void* v, c
     // bf16 mode, dh = 128: chunk-parallel WY/UT form on the tensor cores (checkpoints every 64)
     if (dtype == ASCA_BF16 && dh == 128 && (!ckpt || chunk == 64) && asca_tc_enabled() && delta_tc::available())
         return delta_tc::forward(ctx, q, k, v, alpha, beta, B, T, H, o, s_init, s_final, ckpt);
-    if (ckpt && ctx->dcache_ckpt == (const void*)ckpt) ctx->dcache_ckpt = nullptr;  // tiles no longer match ckpt
+    if (ckpt)
+        for (auto& e : ctx->dtiles)
+            if (e.ckpt == (const void*)ckpt) e.ckpt = nullptr;   // kept tiles no longer match this buffer
     const int ch = ckpt ? (int)chunk : 1;
     cudaError_t e;
     asca_span sp(ctx, "delta_fwd_rec_kernel");

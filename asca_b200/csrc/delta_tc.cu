@@ -1339,17 +1339,37 @@ int forward(asca_ctx* ctx, const void* q, const void* k, const void* v, const fl
     const bool keep = ckpt != nullptr;
     const size_t need = carve_tiles(nullptr, n_tiles, keep, nullptr) + 1024;
     char* w;
+    int slot = -1;
     if (keep) {
-        ctx->dcache_ckpt = nullptr;
-        if (need > ctx->dcache_bytes) {
-            ASCA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-            if (ctx->dcache) cudaFree(ctx->dcache);
-            ctx->dcache = nullptr;
-            ctx->dcache_bytes = 0;
-            ASCA_CUDA(ctx, cudaMalloc(&ctx->dcache, need));
-            ctx->dcache_bytes = need;
+        auto& dt = ctx->dtiles;
+        for (size_t i = 0; i < dt.size(); ++i)
+            if (dt[i].buf && dt[i].ckpt == (const void*)ckpt) slot = (int)i;
+        if (slot < 0) {   // a free entry, a new one, or the least recently used one
+            for (size_t i = 0; i < dt.size() && slot < 0; ++i)
+                if (!dt[i].ckpt) slot = (int)i;
+            size_t total = 0;
+            for (auto& e : dt) total += e.bytes;
+            if (slot < 0 && dt.size() < 32 && total + need <= ((size_t)64 << 30)) {
+                dt.emplace_back();
+                slot = (int)dt.size() - 1;
+            }
+            if (slot < 0) {
+                slot = 0;
+                for (size_t i = 1; i < dt.size(); ++i)
+                    if (dt[i].stamp < dt[slot].stamp) slot = (int)i;
+            }
         }
-        w = (char*)ctx->dcache;
+        auto& e = dt[slot];
+        e.ckpt = nullptr;   // invalid until this forward has been queued
+        if (need > e.bytes) {
+            ASCA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+            if (e.buf) cudaFree(e.buf);
+            e.buf = nullptr;
+            e.bytes = 0;
+            ASCA_CUDA(ctx, cudaMalloc(&e.buf, need));
+            e.bytes = need;
+        }
+        w = (char*)e.buf;
     } else {
         void* ws;
         ASCA_TRY(asca_workspace(ctx, need, &ws));
@@ -1373,10 +1393,12 @@ int forward(asca_ctx* ctx, const void* q, const void* k, const void* v, const fl
     }
     ASCA_CHECK_LAUNCH(ctx);
     if (keep) {
-        ctx->dcache_ckpt = ckpt;
-        ctx->dcache_B = B;
-        ctx->dcache_T = T;
-        ctx->dcache_H = H;
+        auto& e = ctx->dtiles[slot];
+        e.ckpt = ckpt;
+        e.B = B;
+        e.T = T;
+        e.H = H;
+        e.stamp = ++ctx->dtiles_clock;
     }
     return ASCA_OK;
 }
@@ -1387,11 +1409,15 @@ int backward(asca_ctx* ctx, const void* q, const void* k, const void* v, const f
              float* d_qkv, float* d_gate) {
     const int64_t n_chunks = (T + C - 1) / C, chains = B * H, n_tiles = chains * n_chunks;
     Tiles t{};
-    const bool cached = ctx->dcache && ctx->dcache_ckpt == (const void*)ckpt && ctx->dcache_B == B && ctx->dcache_T == T &&
-                        ctx->dcache_H == H;
-    if (cached) {
+    int slot = -1;
+    for (size_t i = 0; i < ctx->dtiles.size(); ++i) {
+        const auto& e = ctx->dtiles[i];
+        if (e.buf && e.ckpt == (const void*)ckpt && e.B == B && e.T == T && e.H == H) slot = (int)i;
+    }
+    if (slot >= 0) {
         // the forward that wrote `ckpt` left its tiles (functions of the same q,k,v,alpha,beta) here
-        char* w = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(ctx->dcache) + 1023) & ~(uintptr_t)1023);
+        ctx->dtiles[slot].stamp = ++ctx->dtiles_clock;
+        char* w = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(ctx->dtiles[slot].buf) + 1023) & ~(uintptr_t)1023);
         carve_tiles(w, n_tiles, true, &t);
     } else {
         void* ws;

@@ -606,3 +606,27 @@ def test_delta_host_pipeline_matches_direct_calls(orc, gpu):
     assert torch.equal(o.cpu(), o_h)
     assert torch.equal(d_qkv.cpu(), dqkv_h)
     assert torch.equal(d_gate.cpu(), dgate_h)
+
+
+@pytest.mark.gpu
+def test_delta_tc_backward_without_kept_tiles_and_with_several_kept(orc, gpu):
+    """The tensor-core backward gives the same bits whether it finds the forward's tiles (several
+    forwards may be pending, one tile set per checkpoint buffer) or rebuilds them from q, k, v."""
+    import torch
+    from asca_b200 import ops
+
+    B, T, H, dh = 2, 200, 2, 128
+    sets = []
+    for seed in (31, 32, 33):
+        arrs = _delta_inputs(orc, seed, B, T, H, dh)
+        q, k, v, al, be, qn, kn, d_o = (torch.from_numpy(a).cuda() for a in arrs)
+        sets.append([q.bfloat16(), k.bfloat16(), v.bfloat16(), al, be, qn, kn, d_o.bfloat16()])
+    ckpts = []
+    for s in sets:      # three forwards first, as a model does for its blocks
+        _, _, ck = ops.delta_fwd(gpu, *s[:5], B, T, H, dh, chunk=64)
+        ckpts.append(ck)
+    for s, ck in zip(reversed(sets), reversed(ckpts)):
+        d1, g1 = ops.delta_bwd(gpu, *s[:5], s[5], s[6], s[7], ck, B, T, H, dh, chunk=64)        # kept tiles
+        d2, g2 = ops.delta_bwd(gpu, *s[:5], s[5], s[6], s[7], ck.clone(), B, T, H, dh, chunk=64)  # rebuilt
+        gpu.sync()
+        assert torch.equal(d1, d2) and torch.equal(g1, g2)
