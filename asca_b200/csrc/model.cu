@@ -239,13 +239,32 @@ struct asca_model {
     // of adding to it (each tensor is written exactly once per backward), which saves the clearing pass and the
     // read half of the accumulation. Anything that exposes the buffer earlier clears it for real first.
     bool grads_zero_pending = false;
+    float grad_scale = 1.0f;   // multiplies dLoss/dlogits: 1 / micro-batches when gradients are accumulated
     // called during the backward, on the host, each time a contiguous range of the gradient buffer has had all its
     // kernels enqueued (one block's tensors, last block first, then embedding + head): the data-parallel
     // exchange of that range can be queued behind them while the rest of the backward is still running
-    float grad_scale = 1.0f;   // multiplies dLoss/dlogits: 1 / micro-batches when gradients are accumulated
     asca_grad_ready_fn grad_hook = nullptr;
     void* grad_hook_user = nullptr;
 };
+
+// The bf16 copy of the weights that the tensor-core products read: allocated on first use, rebuilt whenever the
+// f32 master copy changed behind it (set_params, an AdamW step that did not write it itself, params_changed).
+static int refresh_params16(asca_ctx* ctx, asca_model* m) {
+    if (!m->params16) {
+        if (cudaMalloc((void**)&m->params16, (size_t)m->n16 * 2) != cudaSuccess)
+            return asca_fail(ctx, ASCA_ERR_OOM, "model: cannot allocate the bf16 weight copy");
+        m->params16_stale = true;
+    }
+    if (!m->params16_stale) return ASCA_OK;
+    if (m->n16 == m->n_params) {   // no padding anywhere: one pass over the flat buffer
+        ASCA_TRY(asca_cast_bf16(ctx, m->params, m->params16, m->n_params));
+    } else {
+        for (size_t i = 0; i + 1 < m->seg_off.size(); ++i)
+            ASCA_TRY(asca_cast_bf16(ctx, m->params + m->seg_off[i], m->params16 + m->seg16[i], m->seg_off[i + 1] - m->seg_off[i]));
+    }
+    m->params16_stale = false;
+    return ASCA_OK;
+}
 
 // Decode step in bf16 compute mode: same dataflow as Model::step (rust/src/model.rs:703-720) for ns streams at
 // once, products on the tensor cores from the bf16 weight copy, the expert FFN through the dispatch + grouped
@@ -256,21 +275,7 @@ static int decode_step_bf16(asca_ctx* ctx, asca_model* m, float* state, const ui
     typedef __nv_bfloat16 bf16;
     const int64_t d = m->d, H = m->H, dh = d / H, E = m->E, F = m->F, V = m->vocab;
     const int BF = ASCA_BF16;
-    if (!m->params16) {
-        if (cudaMalloc((void**)&m->params16, (size_t)m->n16 * 2) != cudaSuccess)
-            return asca_fail(ctx, ASCA_ERR_OOM, "model: cannot allocate the bf16 weight copy");
-        m->params16_stale = true;
-    m->dec_stale = true;
-    }
-    if (m->params16_stale) {
-        if (m->n16 == m->n_params) {
-            ASCA_TRY(asca_cast_bf16(ctx, m->params, m->params16, m->n_params));
-        } else {
-            for (size_t i = 0; i + 1 < m->seg_off.size(); ++i)
-                ASCA_TRY(asca_cast_bf16(ctx, m->params + m->seg_off[i], m->params16 + m->seg16[i], m->seg_off[i + 1] - m->seg_off[i]));
-        }
-        m->params16_stale = false;
-    }
+    ASCA_TRY(refresh_params16(ctx, m));
     const float* P = m->params;
     const bf16* W = m->params16;
     Bufs bf(ctx);
@@ -368,21 +373,7 @@ static int forward_backward_bf16(asca_ctx* ctx, asca_model* m, const uint32_t* i
     const int64_t N = B * T, d = m->d, H = m->H, dh = d / H, E = m->E, F = m->F, V = m->vocab, L = m->L;
     const int64_t CH = 64;
     const int BF = ASCA_BF16;
-    if (!m->params16) {
-        if (cudaMalloc((void**)&m->params16, (size_t)m->n16 * 2) != cudaSuccess)
-            return asca_fail(ctx, ASCA_ERR_OOM, "model: cannot allocate the bf16 weight copy");
-        m->params16_stale = true;
-    m->dec_stale = true;
-    }
-    if (m->params16_stale) {
-        if (m->n16 == m->n_params) {   // no padding anywhere: one pass over the flat buffer
-            ASCA_TRY(asca_cast_bf16(ctx, m->params, m->params16, m->n_params));
-        } else {
-            for (size_t i = 0; i + 1 < m->seg_off.size(); ++i)
-                ASCA_TRY(asca_cast_bf16(ctx, m->params + m->seg_off[i], m->params16 + m->seg16[i], m->seg_off[i + 1] - m->seg_off[i]));
-        }
-        m->params16_stale = false;
-    }
+    ASCA_TRY(refresh_params16(ctx, m));
     const float* P = m->params;
     const bf16* W = m->params16;
     float* G = m->grads;
