@@ -21,6 +21,9 @@ struct asca_ctx {
     std::string err;
     std::string desc;
     int64_t launches = 0;
+    // Programmatic dependent launch: while set, launches made through asca_launch may start their prologue before the
+    // previous kernel on the stream has finished (only kernels that execute pdl_wait() first are launched that way).
+    bool pdl = false;
     // size-class cache of freed blocks (the role of the reference's DevBuf pool,
     // rust/src/cuda/mod.rs:104-174): key = rounded size.
     std::multimap<size_t, void*> pool;
@@ -68,6 +71,32 @@ struct asca_span {
 };
 
 int asca_fail(asca_ctx* ctx, int code, const char* fmt, ...);
+
+#ifdef __CUDACC__
+// Programmatic dependent launch, device side. pdl_wait() returns once every kernel this launch depends on has
+// finished and its writes are visible (immediately when the launch was an ordinary one); nothing before it may
+// touch global memory that another kernel writes or reads. pdl_launch_dependents() lets the next kernel on the
+// stream be scheduled; it is called after pdl_wait(), so that at most one kernel is resident ahead of the running one.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Launches `kern` on the context's stream; with ctx->pdl set, as a programmatic dependent of the previous kernel.
+// Only for kernels whose every thread calls pdl_wait() before its first global memory access.
+template <typename... KArgs, typename... Args>
+inline cudaError_t asca_launch(asca_ctx* ctx, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = ctx->pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+#endif
 // Returns scratch of at least `bytes` (256-byte aligned); contents are undefined.
 int asca_workspace(asca_ctx* ctx, size_t bytes, void** out);
 

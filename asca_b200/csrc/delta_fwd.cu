@@ -326,6 +326,8 @@ __global__ void __launch_bounds__(SW_WARPS * 32) delta_step_warp64_kernel(
     __shared__ __align__(16) float kq_s[SW_WARPS][2][DH];
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
     const int64_t unit = (int64_t)blockIdx.x * SW_WARPS + w;   // stream * H + h
+    pdl_wait();
+    pdl_launch_dependents();
     if (unit >= n_units) return;
     const int64_t s = unit / H;
     const int h = (int)(unit % H);
@@ -465,9 +467,9 @@ int asca_delta_step_strided(asca_ctx* ctx, const float* qkv, int64_t ld_qkv, con
                  "delta_step_strided: misaligned pointer");
     if (n_streams == 0) return ASCA_OK;
     const int64_t units = n_streams * H;
-    delta_step_warp64_kernel<<<(unsigned)ceil_div64(units, SW_WARPS), SW_WARPS * 32, 0, ctx->stream>>>(
-        qkv, nullptr, nullptr, gate, nullptr, S, units, (int)H, 1, ld_qkv, ld_gate, o, (__nv_bfloat16*)o16);
-    ASCA_CHECK_LAUNCH(ctx);
+    ASCA_CUDA(ctx, asca_launch(ctx, delta_step_warp64_kernel, dim3((unsigned)ceil_div64(units, SW_WARPS)), dim3(SW_WARPS * 32), 0,
+                               qkv, nullptr, nullptr, gate, nullptr, S, units, (int)H, 1, ld_qkv, ld_gate, o, (__nv_bfloat16*)o16));
+    ctx->launches++;
     return ASCA_OK;
 }
 

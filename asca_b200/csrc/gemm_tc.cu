@@ -98,6 +98,8 @@ __global__ void __launch_bounds__(THREADS, Shape<BN, DEEP>::CTAS_PER_SM) gemm_tc
     const int n_groups = p.group_dim == GROUP_NONE ? 1 : p.n_groups;
 
     // ---- tile table: group g owns tiles [prefix[g], prefix[g+1]), tile = tile_m * tiles_n + tile_n within it
+    if (warp == 1) tc::tmem_alloc(tmem_slot, TMEM_COLS);
+    pdl_wait();   // the group offsets below may be the previous kernel's output
     if (warp == 0) {
         int base = 0;
         for (int g0 = 0; g0 < n_groups; g0 += 32) {
@@ -132,10 +134,10 @@ __global__ void __launch_bounds__(THREADS, Shape<BN, DEEP>::CTAS_PER_SM) gemm_tc
             tc::prefetch_tensormap(&mapB);
         }
     }
-    if (warp == 1) tc::tmem_alloc(tmem_slot, TMEM_COLS);
     tc::tcgen05_fence_before();
     __syncthreads();
     tc::tcgen05_fence_after();
+    pdl_launch_dependents();   // after this CTA holds its TMEM: a dependent that becomes resident early cannot take it
     const uint32_t tmem_base = *tmem_slot;
     const int total_tiles = prefix[n_groups];
 
@@ -489,6 +491,7 @@ bool supported(const Args& a) {
     if (a.group_dim != GROUP_NONE && a.n_groups > MAX_GROUPS) return false;
     if (a.group_dim == GROUP_K && a.mode != ASCA_TN) return false;
     if (a.group_dim == GROUP_M && a.mode == ASCA_TN) return false;
+    if (a.c2_mapped && !skinny_wanted(a)) return false;
     return true;
 }
 
@@ -514,8 +517,7 @@ static int launch_shape(asca_ctx* ctx, const Args& a, int64_t grid) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)(Shape<BN, DEEP>::SMEM_FIXED + (MAX_GROUPS + 2) * 4));
         if (e != cudaSuccess) return e;
-        kern<<<(unsigned)grid, THREADS, smem, ctx->stream>>>(mapA, mapB, p);
-        return cudaGetLastError();
+        return asca_launch(ctx, kern, dim3((unsigned)grid), dim3(THREADS), smem, mapA, mapB, p);
     };
     cudaError_t e = a.mode == ASCA_NN ? go(gemm_tc_kernel<ASCA_NN, BN, DEEP>)
                     : a.mode == ASCA_TN ? go(gemm_tc_kernel<ASCA_TN, BN, DEEP>) : go(gemm_tc_kernel<ASCA_NT, BN, DEEP>);
@@ -533,6 +535,7 @@ static int64_t tile_bound(const Args& a, int bn) {
 }
 
 int launch(asca_ctx* ctx, const Args& a) {
+    if (skinny_wanted(a)) return launch_skinny(ctx, a);
     const int n_sm = ctx->sm_count > 0 ? ctx->sm_count : 148;
     // persistent: the CTAs walk the tiles round-robin. Wide tiles for dense problems with a long k-loop and at least
     // two waves of tiles (measured: +10-15 % there; with k <= 2048 or expert-grouped rows the 128 KiB epilogue per

@@ -34,6 +34,7 @@ struct Args {
     int64_t ldaux;
     __nv_bfloat16* C2;        // EPI_SILU: silu(C); EPI_SILU_BWD: bf16 copy of C; nullable
     int64_t ldc2;
+    int c2_mapped;            // few-row kernel only: C2's rows go through c_idx like C's
 };
 
 // True when the tensor-core kernel can take this problem (alignment and divisibility rules of
@@ -41,5 +42,8 @@ struct Args {
 bool supported(const Args& a);
 // Enqueues the kernel on ctx->stream. Returns ASCA_OK or an error code.
 int launch(asca_ctx* ctx, const Args& a);
+// Few rows (per expert): the weight-streaming kernel of gemm_skinny.cu; launch() routes to it by itself.
+bool skinny_wanted(const Args& a);
+int launch_skinny(asca_ctx* ctx, const Args& a);
 
 }  // namespace gemm_tc

@@ -24,13 +24,16 @@ __global__ void __launch_bounds__(256) cast_bf16_kernel(const float* __restrict_
 }
 
 // Warp per row, the row held in registers (cols % 4 == 0, cols <= 128 * NV): x_mid = x (+ res), written
-// when xsum is given; xn = bf16(x_mid / sqrt(mean x_mid^2 + eps)).
+// when xsum is given (xsum may be x itself); xn = bf16(x_mid / sqrt(mean x_mid^2 + eps)), written to row y_row[r]
+// when a row map is given (the expert-order position of the row: the MoE gather folded into the norm).
 template <int NV>
-__global__ void __launch_bounds__(256) rmsnorm_bf16_warp_kernel(const float* __restrict__ x, const float* __restrict__ res,
-                                                                float* __restrict__ xsum, __nv_bfloat16* __restrict__ y,
-                                                                int64_t rows, int cols, float eps) {
+__global__ void __launch_bounds__(256) rmsnorm_bf16_warp_kernel(const float* x, const float* __restrict__ res,
+                                                                float* xsum, __nv_bfloat16* __restrict__ y,
+                                                                int64_t rows, int cols, float eps, const int32_t* __restrict__ y_row) {
     const int lane = threadIdx.x & 31;
     const int64_t r = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    pdl_wait();
+    pdl_launch_dependents();
     if (r >= rows) return;
     const float4* xr = reinterpret_cast<const float4*>(x + r * (int64_t)cols);
     const int n4 = cols >> 2;
@@ -64,12 +67,30 @@ __global__ void __launch_bounds__(256) rmsnorm_bf16_warp_kernel(const float* __r
     for (int i = 0; i < NV; ++i) acc += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
     acc = warp_sum(acc);
     const float inv = 1.0f / sqrtf(acc / (float)cols + eps);
-    uint2* yr = reinterpret_cast<uint2*>(y + r * (int64_t)cols);
+    uint2* yr = reinterpret_cast<uint2*>(y + (y_row ? (int64_t)y_row[r] : r) * (int64_t)cols);
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
         const int c = lane + 32 * i;
         if (c < n4) yr[c] = pack4_bf16(v[i].x * inv, v[i].y * inv, v[i].z * inv, v[i].w * inv);
     }
+}
+
+int residual_rmsnorm_bf16_impl(asca_ctx* ctx, const float* x, const float* yadd, float* x_mid, void* xn, int64_t rows, int64_t cols,
+                               float eps, const int32_t* y_row) {
+    ASCA_REQUIRE(ctx, x && xn && rows >= 0 && cols > 0, "residual_rmsnorm_bf16: bad arguments");
+    ASCA_REQUIRE(ctx, (cols & 3) == 0 && cols <= 2048, "residual_rmsnorm_bf16: cols must be a multiple of 4, at most 2048");
+    ASCA_REQUIRE(ctx, ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(yadd) | reinterpret_cast<uintptr_t>(x_mid)) & 15) == 0 &&
+                          (reinterpret_cast<uintptr_t>(xn) & 7) == 0, "residual_rmsnorm_bf16: misaligned pointer");
+    if (rows == 0) return ASCA_OK;
+    const unsigned grid = (unsigned)ceil_div64(rows, 8);
+    __nv_bfloat16* y = (__nv_bfloat16*)xn;
+    cudaError_t e;
+    if (cols <= 512) e = asca_launch(ctx, rmsnorm_bf16_warp_kernel<4>, dim3(grid), dim3(256), 0, x, yadd, x_mid, y, rows, (int)cols, eps, y_row);
+    else if (cols <= 1024) e = asca_launch(ctx, rmsnorm_bf16_warp_kernel<8>, dim3(grid), dim3(256), 0, x, yadd, x_mid, y, rows, (int)cols, eps, y_row);
+    else e = asca_launch(ctx, rmsnorm_bf16_warp_kernel<16>, dim3(grid), dim3(256), 0, x, yadd, x_mid, y, rows, (int)cols, eps, y_row);
+    ASCA_CUDA(ctx, e);
+    ctx->launches++;
+    return ASCA_OK;
 }
 
 // rust/src/delta.rs:134-179 with bf16 q, k, v outputs. One warp per (row, head); norms and gates f32.
@@ -126,6 +147,13 @@ __global__ void __launch_bounds__(256) delta_prep_bf16_kernel(const float* __res
 
 }  // namespace
 
+// residual + RMSNorm whose bf16 rows land in expert order: row r is written to row y_row[r] of xn
+int asca_residual_rmsnorm_bf16_rows(asca_ctx* ctx, const float* x, const float* yadd, float* x_mid, void* xn, int64_t rows,
+                                    int64_t cols, float eps, const int32_t* y_row) {
+    if (!ctx) return ASCA_ERR_ARG;
+    return residual_rmsnorm_bf16_impl(ctx, x, yadd, x_mid, xn, rows, cols, eps, y_row);
+}
+
 extern "C" {
 
 int asca_cast_bf16(asca_ctx* ctx, const float* src, void* dst, int64_t n) {
@@ -142,18 +170,7 @@ int asca_cast_bf16(asca_ctx* ctx, const float* src, void* dst, int64_t n) {
 int asca_residual_rmsnorm_bf16(asca_ctx* ctx, const float* x, const float* yadd, float* x_mid, void* xn, int64_t rows,
                                int64_t cols, float eps) {
     if (!ctx) return ASCA_ERR_ARG;
-    ASCA_REQUIRE(ctx, x && xn && rows >= 0 && cols > 0, "residual_rmsnorm_bf16: bad arguments");
-    ASCA_REQUIRE(ctx, (cols & 3) == 0 && cols <= 2048, "residual_rmsnorm_bf16: cols must be a multiple of 4, at most 2048");
-    ASCA_REQUIRE(ctx, ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(yadd) | reinterpret_cast<uintptr_t>(x_mid)) & 15) == 0 &&
-                          (reinterpret_cast<uintptr_t>(xn) & 7) == 0, "residual_rmsnorm_bf16: misaligned pointer");
-    if (rows == 0) return ASCA_OK;
-    const unsigned grid = (unsigned)ceil_div64(rows, 8);
-    __nv_bfloat16* y = (__nv_bfloat16*)xn;
-    if (cols <= 512) rmsnorm_bf16_warp_kernel<4><<<grid, 256, 0, ctx->stream>>>(x, yadd, x_mid, y, rows, (int)cols, eps);
-    else if (cols <= 1024) rmsnorm_bf16_warp_kernel<8><<<grid, 256, 0, ctx->stream>>>(x, yadd, x_mid, y, rows, (int)cols, eps);
-    else rmsnorm_bf16_warp_kernel<16><<<grid, 256, 0, ctx->stream>>>(x, yadd, x_mid, y, rows, (int)cols, eps);
-    ASCA_CHECK_LAUNCH(ctx);
-    return ASCA_OK;
+    return residual_rmsnorm_bf16_impl(ctx, x, yadd, x_mid, xn, rows, cols, eps, nullptr);
 }
 
 int asca_delta_prep_bf16(asca_ctx* ctx, const float* qkv, const float* gate, int64_t N, int64_t H, int64_t dh, void* q,

@@ -143,10 +143,17 @@ __global__ void __launch_bounds__(256) add_kernel(const float* __restrict__ a, c
     const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
     if (i < n) out[i] = a[i] + 1.0f * b[i];
 }
+// inv[perm[i]] = i
+__global__ void __launch_bounds__(256) invert_perm_kernel(const int32_t* __restrict__ perm, int32_t* __restrict__ inv, int64_t n) {
+    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (i < n) inv[perm[i]] = (int32_t)i;
+}
 // out = a + b, with a bf16 copy (the next block's product reads the copy)
 __global__ void __launch_bounds__(256) add_cast_kernel(const float* __restrict__ a, const float* __restrict__ b,
                                                        float* __restrict__ out, __nv_bfloat16* __restrict__ out16, int64_t n) {
     const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    pdl_wait();
+    pdl_launch_dependents();
     if (i < n) {
         const float v = a[i] + b[i];
         out[i] = v;
@@ -270,6 +277,13 @@ static int refresh_params16(asca_ctx* ctx, asca_model* m) {
 // once, products on the tensor cores from the bf16 weight copy, the expert FFN through the dispatch + grouped
 // GEMM path (every expert's weights are read once per step, not once per stream); state, residual stream and
 // logits stay f32.
+// moe.cu / mixed.cu: the decode-step forms on rows in expert order
+int asca_moe_fwd_sorted_residual(asca_ctx* ctx, const __nv_bfloat16* xp, const __nv_bfloat16* w1, const float* b1,
+                                 const __nv_bfloat16* w2, const float* b2, const int32_t* perm, const int32_t* offsets, int64_t N,
+                                 int64_t d, int64_t F, int64_t E, float* x, __nv_bfloat16* x16, __nv_bfloat16* hid_p, int check_only);
+int asca_residual_rmsnorm_bf16_rows(asca_ctx* ctx, const float* x, const float* yadd, float* x_mid, void* xn, int64_t rows,
+                                    int64_t cols, float eps, const int32_t* y_row);
+
 static int decode_step_bf16(asca_ctx* ctx, asca_model* m, float* state, const uint32_t* ids_h, int64_t ns, float* logits_h,
                             uint32_t* next_h) {
     typedef __nv_bfloat16 bf16;
@@ -316,7 +330,24 @@ static int decode_step_bf16(asca_ctx* ctx, asca_model* m, float* state, const ui
     }
     float* qg = fused64 ? bf.f(ns * ldq) : nullptr;
     ASCA_REQUIRE(ctx, !fused64 || qg, "model_decode_step: out of memory");
+    // With a handful of tokens per expert the MoE runs on rows in expert order end to end: the norm writes its bf16
+    // rows at their expert-order position (the gather), and the second expert product adds into the residual rows
+    // through the permutation and writes the next block's bf16 input (the combine, the residual add and the cast).
+    const bool sorted_moe = asca_moe_fwd_sorted_residual(ctx, xn16, W + m->lay16[0].w1, P + m->lay[0].b1, W + m->lay16[0].w2,
+                                                         P + m->lay[0].b2, perm, offs, ns, d, F, E, x, x16, hid16, 1) == ASCA_OK;
+    int32_t* inv_perm = sorted_moe ? (int32_t*)bf.f(ns) : nullptr;
+    if (sorted_moe) {
+        ASCA_REQUIRE(ctx, inv_perm, "model_decode_step: out of memory");
+        invert_perm_kernel<<<(unsigned)ceil_div64(ns, 256), 256, 0, ctx->stream>>>(perm, inv_perm, ns);
+        ASCA_CHECK_LAUNCH(ctx);
+    }
     ASCA_TRY(asca_cast_bf16(ctx, x, x16, ns * d));
+    // the block chain is short kernels back to back: each may become resident while its predecessor drains
+    struct PdlScope {
+        asca_ctx* c;
+        explicit PdlScope(asca_ctx* c_) : c(c_) { c->pdl = true; }
+        ~PdlScope() { c->pdl = false; }
+    } pdl_scope(ctx);
     for (int64_t li = 0; li < m->L; ++li) {
         const Lyr& w = m->lay[li];
         const Lyr& w16 = m->lay16[li];
@@ -330,10 +361,17 @@ static int decode_step_bf16(asca_ctx* ctx, asca_model* m, float* state, const ui
             ASCA_TRY(asca_cast_bf16(ctx, o, o16, ns * d));
         }
         ASCA_TRY(asca_gemm(ctx, ASCA_NN, ns, d, d, o16, d, W + w16.w_o, d, y, d, P + w.b_o, 0, BF));
+        if (sorted_moe) {
+            ASCA_TRY(asca_residual_rmsnorm_bf16_rows(ctx, x, y, x, xn16, ns, d, 1e-6f, inv_perm));   // x += y in place
+            ASCA_TRY(asca_moe_fwd_sorted_residual(ctx, xn16, W + w16.w1, P + w.b1, W + w16.w2, P + w.b2, perm, offs, ns, d, F, E, x,
+                                                  x16, hid16, 0));
+            continue;
+        }
         ASCA_TRY(asca_residual_rmsnorm_bf16(ctx, x, y, x_mid, xn16, ns, d, 1e-6f));
         ASCA_TRY(asca_moe_fwd(ctx, xn16, W + w16.w1, P + w.b1, W + w16.w2, P + w.b2, perm, offs, ns, d, F, E, BF, mo, pre_p, hid16));
-        add_cast_kernel<<<(unsigned)ceil_div64(ns * d, 256), 256, 0, ctx->stream>>>(x_mid, mo, x, x16, ns * d);   // x_out (+ bf16)
-        ASCA_CHECK_LAUNCH(ctx);
+        ASCA_CUDA(ctx, asca_launch(ctx, add_cast_kernel, dim3((unsigned)ceil_div64(ns * d, 256)), dim3(256), 0, x_mid, mo, x, x16,
+                                   ns * d));   // x_out (+ bf16)
+        ctx->launches++;
     }
     ASCA_TRY(asca_residual_rmsnorm_bf16(ctx, x, nullptr, nullptr, hf16, ns, d, 1e-6f));
     ASCA_TRY(asca_gemm(ctx, ASCA_NN, ns, V, d, hf16, d, W + m->head16, V, logits, V, nullptr, 0, BF));

@@ -88,6 +88,8 @@ __global__ void __launch_bounds__(256) gather_rows_bf16_kernel(const __nv_bfloat
                                                                int cols) {
     const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t r = (int64_t)blockIdx.x * 8 + w;
+    pdl_wait();
+    pdl_launch_dependents();
     if (r >= n_rows) return;
     const uint4* s = reinterpret_cast<const uint4*>(src + (int64_t)idx[r] * cols);
     uint4* d = reinterpret_cast<uint4*>(dst + r * cols);
@@ -138,8 +140,8 @@ int moe_fwd_tc(asca_ctx* ctx, const __nv_bfloat16* xn, const __nv_bfloat16* w1, 
     b.offsets = offsets; b.n_groups = (int)E; b.group_dim = gemm_tc::GROUP_M; b.total_rows = N;
     // nothing is launched unless every product can run here: the caller falls back as a whole
     if (!gemm_tc::supported(a) || !gemm_tc::supported(b)) return ASCA_ERR_UNSUPPORTED;
-    gather_rows_bf16_kernel<<<(unsigned)ceil_div64(N, 8), 256, 0, ctx->stream>>>(xn, perm, xp, N, (int)d);
-    ASCA_CHECK_LAUNCH(ctx);
+    ASCA_CUDA(ctx, asca_launch(ctx, gather_rows_bf16_kernel, dim3((unsigned)ceil_div64(N, 8)), dim3(256), 0, xn, perm, xp, N, (int)d));
+    ctx->launches++;
     ASCA_TRY(gemm_tc::launch(ctx, a));
     return gemm_tc::launch(ctx, b);
 }
@@ -202,6 +204,36 @@ int moe_bwd_tc(asca_ctx* ctx, const __nv_bfloat16* xn, const __nv_bfloat16* w1, 
 }
 
 }  // namespace
+
+// Decode-step form of the layer, on bf16 rows already in expert order: x[perm[r], :] += silu(xp[r] W1_e + b1_e) W2_e + b2
+// in place on the f32 residual rows, with a bf16 copy of the updated rows in x16. Two launches of the few-row
+// kernel; ASCA_ERR_UNSUPPORTED (nothing launched) when that kernel does not take the shapes. check_only: launch nothing.
+int asca_moe_fwd_sorted_residual(asca_ctx* ctx, const __nv_bfloat16* xp, const __nv_bfloat16* w1, const float* b1,
+                                 const __nv_bfloat16* w2, const float* b2, const int32_t* perm, const int32_t* offsets, int64_t N,
+                                 int64_t d, int64_t F, int64_t E, float* x, __nv_bfloat16* x16, __nv_bfloat16* hid_p, int check_only) {
+    if (!tc_shapes_ok(d, F) || N <= 0) return ASCA_ERR_UNSUPPORTED;
+    gemm_tc::Args a{};
+    a.mode = ASCA_NN;
+    a.A = xp; a.lda = d; a.a_rows = N; a.a_cols = d;
+    a.B = w1; a.ldb = E * F; a.b_rows = d; a.b_cols = E * F; a.b_goff_inner = (int)F;
+    a.C = nullptr; a.ldc = F; a.N = (int)F; a.K = (int)d;
+    a.bias = b1; a.bias_gstride = F;
+    a.offsets = offsets; a.n_groups = (int)E; a.group_dim = gemm_tc::GROUP_M; a.total_rows = N;
+    a.epi = gemm_tc::EPI_SILU; a.C2 = hid_p; a.ldc2 = F;
+    gemm_tc::Args b{};
+    b.mode = ASCA_NN;
+    b.A = hid_p; b.lda = F; b.a_rows = N; b.a_cols = F;
+    b.B = w2; b.ldb = d; b.b_rows = E * F; b.b_cols = d; b.b_goff_outer = (int)F;
+    b.C = x; b.ldc = d; b.N = (int)d; b.K = (int)F; b.c_idx = perm; b.accumulate = 1;
+    b.bias = b2; b.bias_gstride = 0;
+    b.offsets = offsets; b.n_groups = (int)E; b.group_dim = gemm_tc::GROUP_M; b.total_rows = N;
+    b.C2 = x16; b.ldc2 = d; b.c2_mapped = 1;
+    if (!gemm_tc::skinny_wanted(a) || !gemm_tc::skinny_wanted(b) || !gemm_tc::supported(a) || !gemm_tc::supported(b))
+        return ASCA_ERR_UNSUPPORTED;
+    if (check_only) return ASCA_OK;
+    ASCA_TRY(gemm_tc::launch_skinny(ctx, a));
+    return gemm_tc::launch_skinny(ctx, b);
+}
 
 extern "C" {
 

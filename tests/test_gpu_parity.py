@@ -565,6 +565,57 @@ def test_moe_bf16_tensor_core_ragged_experts(orc, gpu, n, d, F, E, vocab):
         assert rel_err(got.cpu().numpy(), want) < BF16_TOL, name
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("m,k,n", [(1, 64, 128), (17, 768, 2328), (32, 200, 136), (33, 72, 8), (64, 3072, 768), (200, 96, 264),
+                                   (256, 768, 768)])
+def test_bf16_few_row_gemm(orc, gpu, m, k, n):
+    """At most 256 rows: the weight-streaming kernel (output features on the instruction's 128 rows, tokens on its
+    N). Ragged rows, features and k; bias and accumulate."""
+    import torch
+    from asca_b200 import ops, NN
+
+    rng = orc.Rng(7 * m + k + n)
+    a, b = rng.normal((m, k)), rng.normal((k, n))
+    bias, c0 = rng.normal(n), rng.normal((m, n))
+    a16, b16 = torch.from_numpy(a).cuda().bfloat16(), torch.from_numpy(b).cuda().bfloat16()
+    ref = a16.float().cpu().numpy().astype(np.float64) @ b16.float().cpu().numpy().astype(np.float64)
+    got = ops.gemm(gpu, a16, b16, NN)
+    out = torch.from_numpy(c0.copy()).cuda()
+    ops.gemm(gpu, a16, b16, NN, bias=torch.from_numpy(bias).cuda(), out=out, accumulate=True)
+    gpu.sync()
+    assert rel_err(got.cpu().numpy(), ref) < 1e-5
+    assert rel_err(out.cpu().numpy(), ref + bias + c0) < 1e-5
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n,d,F,E,vocab", [(256, 128, 256, 16, 256), (100, 64, 128, 8, 5), (500, 192, 384, 8, 256), (1, 64, 128, 4, 256)])
+def test_moe_bf16_few_tokens_per_expert(orc, gpu, n, d, F, E, vocab):
+    """A decode step's load: a handful of tokens per expert, empty experts, one expert with several token tiles.
+    The forward goes through the weight-streaming grouped products and must equal the oracle on the rounded operands."""
+    import torch
+    from asca_b200 import ops
+
+    w1, b1, w2, b2 = _moe_params(orc, 21, d, F, E)
+    rng = orc.Rng(n + E)
+    ids = _zipf_ids(orc, n + 1, n) % vocab
+    xn = orc.rmsnorm(rng.normal((n, d)))[0]
+    c = lambda a: torch.from_numpy(a).cuda()
+    txn, tw1, tw2 = c(xn).bfloat16(), c(w1).bfloat16(), c(w2).bfloat16()
+    xr, w1r, w2r = (t.float().cpu().numpy() for t in (txn, tw1, tw2))
+    out_ref, pre_ref, hid_ref = orc.moe_ffn_forward(xr, w1r, b1, w2r, b2, ids, F, E, want_cache=True)
+    perm, offsets = ops.moe_dispatch(gpu, c(ids.view(np.int32)), E)
+    out, pre_p, hid_p = ops.moe_fwd(gpu, txn, tw1, c(b1), tw2, c(b2), perm, offsets, F, E)
+    gpu.sync()
+    pm = perm.cpu().numpy()
+    pre_tok = np.empty_like(pre_ref)
+    pre_tok[pm] = pre_p.cpu().numpy()
+    hid_tok = np.empty_like(hid_ref)
+    hid_tok[pm] = hid_p.float().cpu().numpy()
+    assert rel_err(pre_tok, pre_ref) < 1e-5
+    assert rel_err(hid_tok, hid_ref) < BF16_TOL
+    assert rel_err(out.cpu().numpy(), out_ref) < BF16_TOL
+
+
 # ------------------------------------------------------------------ argument errors (host side, before any launch)
 def test_bad_arguments_fail_before_launch(orc, gpu):
     import asca_b200
