@@ -35,6 +35,7 @@ struct Args {
     __nv_bfloat16* C2;        // EPI_SILU: silu(C); EPI_SILU_BWD: bf16 copy of C; nullable
     int64_t ldc2;
     int c2_mapped;            // few-row kernel only: C2's rows go through c_idx like C's
+    int b_packed;             // few-row kernel only: B is a buffer made by skinny_pack (b_rows = its rows of 64)
 };
 
 // True when the tensor-core kernel can take this problem (alignment and divisibility rules of
@@ -45,5 +46,11 @@ int launch(asca_ctx* ctx, const Args& a);
 // Few rows (per expert): the weight-streaming kernel of gemm_skinny.cu; launch() routes to it by itself.
 bool skinny_wanted(const Args& a);
 int launch_skinny(asca_ctx* ctx, const Args& a);
+// Weights in the order the few-row kernel streams them: for every (group, 128-feature tile, 64-row k-tile) the 16 KiB
+// of its shared-memory stage are contiguous (two halves of 64 k-rows x 64 features; zero beyond K and N), so a CTA
+// reads one sequential run of memory instead of 128-byte pieces a weight-matrix row apart.
+int64_t skinny_packed_rows(int64_t groups, int64_t K, int64_t N);   // rows of 64 bf16
+int skinny_pack(asca_ctx* ctx, const __nv_bfloat16* src, int64_t ld, int64_t groups, int64_t goff_inner, int64_t goff_outer,
+                int64_t K, int64_t N, __nv_bfloat16* dst);
 
 }  // namespace gemm_tc

@@ -3,6 +3,7 @@
 // rust/src/model.rs:631-802 and rust/src/delta.rs:121-207 / :615-674, composed from the
 // library's own entry points with every activation resident in HBM. f32 arithmetic.
 #include "common.cuh"
+#include "gemm_tc.cuh"
 
 namespace {
 
@@ -241,7 +242,8 @@ struct asca_model {
     // so that one product feeds the state update
     __nv_bfloat16* dec_w = nullptr;
     float* dec_b = nullptr;
-    bool dec_stale = true;
+    bool dec_stale = true, dec_pk_stale = true;
+    __nv_bfloat16* dec_pk = nullptr;   // decode: every product's weights in the few-row kernel's streaming order
     // asca_model_zero_grads only records the request: the next backward overwrites every gradient tensor instead
     // of adding to it (each tensor is written exactly once per backward), which saves the clearing pass and the
     // read half of the accumulation. Anything that exposes the buffer earlier clears it for real first.
@@ -280,7 +282,8 @@ static int refresh_params16(asca_ctx* ctx, asca_model* m) {
 // moe.cu / mixed.cu: the decode-step forms on rows in expert order
 int asca_moe_fwd_sorted_residual(asca_ctx* ctx, const __nv_bfloat16* xp, const __nv_bfloat16* w1, const float* b1,
                                  const __nv_bfloat16* w2, const float* b2, const int32_t* perm, const int32_t* offsets, int64_t N,
-                                 int64_t d, int64_t F, int64_t E, float* x, __nv_bfloat16* x16, __nv_bfloat16* hid_p, int check_only);
+                                 int64_t d, int64_t F, int64_t E, float* x, __nv_bfloat16* x16, __nv_bfloat16* hid_p, int check_only,
+                                 int packed);
 int asca_residual_rmsnorm_bf16_rows(asca_ctx* ctx, const float* x, const float* yadd, float* x_mid, void* xn, int64_t rows,
                                     int64_t cols, float eps, const int32_t* y_row);
 
@@ -314,6 +317,7 @@ static int decode_step_bf16(asca_ctx* ctx, asca_model* m, float* state, const ui
                 cudaMalloc((void**)&m->dec_b, (size_t)m->L * ldq * 4) != cudaSuccess)
                 return asca_fail(ctx, ASCA_ERR_OOM, "model: cannot allocate the fused decode projection");
             m->dec_stale = true;
+            m->dec_pk_stale = true;
         }
         if (m->dec_stale) {
             for (int64_t li = 0; li < m->L; ++li) {
@@ -334,7 +338,40 @@ static int decode_step_bf16(asca_ctx* ctx, asca_model* m, float* state, const ui
     // rows at their expert-order position (the gather), and the second expert product adds into the residual rows
     // through the permutation and writes the next block's bf16 input (the combine, the residual add and the cast).
     const bool sorted_moe = asca_moe_fwd_sorted_residual(ctx, xn16, W + m->lay16[0].w1, P + m->lay[0].b1, W + m->lay16[0].w2,
-                                                         P + m->lay[0].b2, perm, offs, ns, d, F, E, x, x16, hid16, 1) == ASCA_OK;
+                                                         P + m->lay[0].b2, perm, offs, ns, d, F, E, x, x16, hid16, 1, 0) == ASCA_OK;
+    // ... and then every product of the step is a few-row product whose weights are read once: they are kept a second
+    // time in the order that kernel streams them (per layer: qkv+gate, out, experts' W1, experts' W2; then the head)
+    const bool packed = fused64 && sorted_moe && ns <= 256;
+    const int64_t r_qg = gemm_tc::skinny_packed_rows(1, d, ldq), r_o = gemm_tc::skinny_packed_rows(1, d, d),
+                  r_w1 = gemm_tc::skinny_packed_rows(E, d, F), r_w2 = gemm_tc::skinny_packed_rows(E, F, d),
+                  r_layer = r_qg + r_o + r_w1 + r_w2, r_head = gemm_tc::skinny_packed_rows(1, d, V);
+    if (packed && !m->dec_pk) {
+        if (cudaMalloc((void**)&m->dec_pk, (size_t)(m->L * r_layer + r_head) * 128) != cudaSuccess)
+            return asca_fail(ctx, ASCA_ERR_OOM, "model: cannot allocate the decode weight copy");
+        m->dec_pk_stale = true;
+    }
+    if (packed && m->dec_pk_stale) {
+        for (int64_t li = 0; li < m->L; ++li) {
+            const Lyr& w16 = m->lay16[li];
+            bf16* pk = m->dec_pk + li * r_layer * 64;
+            ASCA_TRY(gemm_tc::skinny_pack(ctx, m->dec_w + li * d * ldq, ldq, 1, 0, 0, d, ldq, pk));
+            ASCA_TRY(gemm_tc::skinny_pack(ctx, W + w16.w_o, d, 1, 0, 0, d, d, pk + r_qg * 64));
+            ASCA_TRY(gemm_tc::skinny_pack(ctx, W + w16.w1, E * F, E, F, 0, d, F, pk + (r_qg + r_o) * 64));
+            ASCA_TRY(gemm_tc::skinny_pack(ctx, W + w16.w2, d, E, 0, F, F, d, pk + (r_qg + r_o + r_w1) * 64));
+        }
+        ASCA_TRY(gemm_tc::skinny_pack(ctx, W + m->head16, V, 1, 0, 0, d, V, m->dec_pk + m->L * r_layer * 64));
+        m->dec_pk_stale = false;
+    }
+    auto few_rows = [&](const bf16* X, int64_t K, const bf16* Wpk, int64_t N, float* C, int64_t ldc, const float* bias) -> int {
+        gemm_tc::Args t{};
+        t.mode = ASCA_NN;
+        t.A = X; t.lda = K; t.a_rows = ns; t.a_cols = K;
+        t.B = Wpk; t.ldb = 64; t.b_rows = gemm_tc::skinny_packed_rows(1, K, N); t.b_cols = 64; t.b_packed = 1;
+        t.C = C; t.ldc = ldc; t.M = (int)ns; t.N = (int)N; t.K = (int)K; t.bias = bias;
+        t.group_dim = gemm_tc::GROUP_NONE; t.epi = gemm_tc::EPI_NONE;
+        if (!gemm_tc::supported(t)) return asca_fail(ctx, ASCA_ERR_UNSUPPORTED, "model_decode_step: product not supported");
+        return gemm_tc::launch_skinny(ctx, t);
+    };
     int32_t* inv_perm = sorted_moe ? (int32_t*)bf.f(ns) : nullptr;
     if (sorted_moe) {
         ASCA_REQUIRE(ctx, inv_perm, "model_decode_step: out of memory");
@@ -352,7 +389,8 @@ static int decode_step_bf16(asca_ctx* ctx, asca_model* m, float* state, const ui
         const Lyr& w = m->lay[li];
         const Lyr& w16 = m->lay16[li];
         if (fused64) {
-            ASCA_TRY(asca_gemm(ctx, ASCA_NN, ns, ldq, d, x16, d, m->dec_w + li * d * ldq, ldq, qg, ldq, m->dec_b + li * ldq, 0, BF));
+            if (packed) ASCA_TRY(few_rows(x16, d, m->dec_pk + li * r_layer * 64, ldq, qg, ldq, m->dec_b + li * ldq));
+            else ASCA_TRY(asca_gemm(ctx, ASCA_NN, ns, ldq, d, x16, d, m->dec_w + li * d * ldq, ldq, qg, ldq, m->dec_b + li * ldq, 0, BF));
             ASCA_TRY(asca_delta_step_strided(ctx, qg, ldq, qg + 3 * d, ldq, state + li * ns * H * dh * dh, ns, H, o, o16));
         } else {
             ASCA_TRY(asca_gemm(ctx, ASCA_NN, ns, 3 * d, d, x16, d, W + w16.w_qkv, 3 * d, qkv, 3 * d, P + w.b_qkv, 0, BF));
@@ -360,11 +398,13 @@ static int decode_step_bf16(asca_ctx* ctx, asca_model* m, float* state, const ui
             ASCA_TRY(asca_delta_step(ctx, qkv, nullptr, nullptr, gate, nullptr, state + li * ns * H * dh * dh, ns, H, dh, 1, o));
             ASCA_TRY(asca_cast_bf16(ctx, o, o16, ns * d));
         }
-        ASCA_TRY(asca_gemm(ctx, ASCA_NN, ns, d, d, o16, d, W + w16.w_o, d, y, d, P + w.b_o, 0, BF));
+        if (packed) ASCA_TRY(few_rows(o16, d, m->dec_pk + (li * r_layer + r_qg) * 64, d, y, d, P + w.b_o));
+        else ASCA_TRY(asca_gemm(ctx, ASCA_NN, ns, d, d, o16, d, W + w16.w_o, d, y, d, P + w.b_o, 0, BF));
         if (sorted_moe) {
             ASCA_TRY(asca_residual_rmsnorm_bf16_rows(ctx, x, y, x, xn16, ns, d, 1e-6f, inv_perm));   // x += y in place
-            ASCA_TRY(asca_moe_fwd_sorted_residual(ctx, xn16, W + w16.w1, P + w.b1, W + w16.w2, P + w.b2, perm, offs, ns, d, F, E, x,
-                                                  x16, hid16, 0));
+            const bf16* pk = m->dec_pk + (li * r_layer + r_qg + r_o) * 64;
+            ASCA_TRY(asca_moe_fwd_sorted_residual(ctx, xn16, packed ? pk : W + w16.w1, P + w.b1, packed ? pk + r_w1 * 64 : W + w16.w2,
+                                                  P + w.b2, perm, offs, ns, d, F, E, x, x16, hid16, 0, packed ? 1 : 0));
             continue;
         }
         ASCA_TRY(asca_residual_rmsnorm_bf16(ctx, x, y, x_mid, xn16, ns, d, 1e-6f));
@@ -374,7 +414,8 @@ static int decode_step_bf16(asca_ctx* ctx, asca_model* m, float* state, const ui
         ctx->launches++;
     }
     ASCA_TRY(asca_residual_rmsnorm_bf16(ctx, x, nullptr, nullptr, hf16, ns, d, 1e-6f));
-    ASCA_TRY(asca_gemm(ctx, ASCA_NN, ns, V, d, hf16, d, W + m->head16, V, logits, V, nullptr, 0, BF));
+    if (packed) ASCA_TRY(few_rows(hf16, d, m->dec_pk + m->L * r_layer * 64, V, logits, V, nullptr));
+    else ASCA_TRY(asca_gemm(ctx, ASCA_NN, ns, V, d, hf16, d, W + m->head16, V, logits, V, nullptr, 0, BF));
     if (logits_h) ASCA_CUDA(ctx, cudaMemcpyAsync(logits_h, logits, (size_t)ns * V * 4, cudaMemcpyDeviceToHost, ctx->stream));
     if (next_h) {
         argmax_kernel<<<(unsigned)ceil_div64(ns, 8), 256, 0, ctx->stream>>>(logits, ns, (int)V, nxt);
@@ -651,6 +692,7 @@ int asca_model_destroy(asca_ctx* ctx, asca_model* m) {
     if (m->params16) cudaFree(m->params16);
     if (m->dec_w) cudaFree(m->dec_w);
     if (m->dec_b) cudaFree(m->dec_b);
+    if (m->dec_pk) cudaFree(m->dec_pk);
     delete m;
     return ASCA_OK;
 }
@@ -700,6 +742,7 @@ int asca_model_params_changed(asca_model* m) {
     if (!m) return ASCA_ERR_ARG;
     m->params16_stale = true;
     m->dec_stale = true;
+    m->dec_pk_stale = true;
     return ASCA_OK;
 }
 
@@ -710,6 +753,7 @@ int asca_model_set_params_host(asca_ctx* ctx, asca_model* m, const float* params
     ASCA_CUDA(ctx, cudaMemsetAsync(m->v, 0, (size_t)m->n_params * 4, ctx->stream));
     m->params16_stale = true;
     m->dec_stale = true;
+    m->dec_pk_stale = true;
     return asca_memcpy_h2d(ctx, m->params, params, (size_t)m->n_params * 4);
 }
 
@@ -864,6 +908,7 @@ int asca_model_adamw_step(asca_ctx* ctx, asca_model* m, float lr, float beta1, f
     const bool fuse = m->compute == ASCA_BF16 && m->params16 && m->n16 == m->n_params;
     m->params16_stale = !fuse;
     m->dec_stale = true;
+    m->dec_pk_stale = true;
     return asca_adamw_segmented_cast(ctx, m->params, m->grads, m->m, m->v, m->seg_off.data(), lr_t.data(), eps_t.data(), n_seg,
                                      beta1, beta2, lr * wd, fuse ? (void*)m->params16 : nullptr);
 }

@@ -208,9 +208,11 @@ int moe_bwd_tc(asca_ctx* ctx, const __nv_bfloat16* xn, const __nv_bfloat16* w1, 
 // Decode-step form of the layer, on bf16 rows already in expert order: x[perm[r], :] += silu(xp[r] W1_e + b1_e) W2_e + b2
 // in place on the f32 residual rows, with a bf16 copy of the updated rows in x16. Two launches of the few-row
 // kernel; ASCA_ERR_UNSUPPORTED (nothing launched) when that kernel does not take the shapes. check_only: launch nothing.
+// packed: w1 and w2 point to the experts' weights in the kernel's streaming order (gemm_tc::skinny_pack).
 int asca_moe_fwd_sorted_residual(asca_ctx* ctx, const __nv_bfloat16* xp, const __nv_bfloat16* w1, const float* b1,
                                  const __nv_bfloat16* w2, const float* b2, const int32_t* perm, const int32_t* offsets, int64_t N,
-                                 int64_t d, int64_t F, int64_t E, float* x, __nv_bfloat16* x16, __nv_bfloat16* hid_p, int check_only) {
+                                 int64_t d, int64_t F, int64_t E, float* x, __nv_bfloat16* x16, __nv_bfloat16* hid_p, int check_only,
+                                 int packed) {
     if (!tc_shapes_ok(d, F) || N <= 0) return ASCA_ERR_UNSUPPORTED;
     gemm_tc::Args a{};
     a.mode = ASCA_NN;
@@ -228,6 +230,10 @@ int asca_moe_fwd_sorted_residual(asca_ctx* ctx, const __nv_bfloat16* xp, const _
     b.bias = b2; b.bias_gstride = 0;
     b.offsets = offsets; b.n_groups = (int)E; b.group_dim = gemm_tc::GROUP_M; b.total_rows = N;
     b.C2 = x16; b.ldc2 = d; b.c2_mapped = 1;
+    if (packed) {   // w1 / w2 are skinny_pack buffers of the E expert matrices
+        a.b_packed = 1; a.ldb = 64; a.b_cols = 64; a.b_rows = gemm_tc::skinny_packed_rows(E, d, F); a.b_goff_inner = 0;
+        b.b_packed = 1; b.ldb = 64; b.b_cols = 64; b.b_rows = gemm_tc::skinny_packed_rows(E, F, d); b.b_goff_outer = 0;
+    }
     if (!gemm_tc::skinny_wanted(a) || !gemm_tc::skinny_wanted(b) || !gemm_tc::supported(a) || !gemm_tc::supported(b))
         return ASCA_ERR_UNSUPPORTED;
     if (check_only) return ASCA_OK;

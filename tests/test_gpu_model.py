@@ -190,6 +190,28 @@ def test_bf16_compute_decode_within_tolerance(orc, gpu):
     dev.free()
 
 
+def test_bf16_decode_sees_weight_updates_and_takes_more_than_256_streams(orc, gpu):
+    """The decode step keeps a second copy of the weights in streaming order: it must follow set_params, and the
+    step must give the same logits whether the streams go through that path (<= 256 streams) or not."""
+    import asca_b200
+
+    cfg = (256, 128, 2, 2, 8, 256)
+    ids = orc.Rng(5).below(256, 300)
+    dev = asca_b200.Model(gpu, *cfg)
+    dev.set_compute(asca_b200.BF16)
+    outs = []
+    for seed in (31, 32):
+        ref = orc.Model(*cfg)
+        ref.init_reference(orc.Rng(seed))
+        dev.set_params(ref.params)
+        lg_small, _ = dev.decode_step(dev.new_decode_state(200), ids[:200].copy())
+        lg_big, _ = dev.decode_step(dev.new_decode_state(300), ids.copy())
+        assert rel_err(lg_small, lg_big[:200]) < 1e-3, seed     # same bf16 operands, different kernels
+        outs.append(lg_small)
+    assert rel_err(outs[0], outs[1]) > 0.1                       # the second set of weights was used
+    dev.free()
+
+
 def test_trainer_loop_matches_oracle_loss_for_loss_and_resumes(orc, gpu, tmp_path):
     """Four steps of the reference's loop (lr schedule, data windows from the reference generator,
     forward + backward + AdamW) on the device against the same loop on the CPU oracle; then a resume
