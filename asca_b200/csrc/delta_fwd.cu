@@ -11,6 +11,8 @@
 //     (stream, head) streams S through registers once (read + write = the HBM floor).
 #include "common.cuh"
 
+#include <algorithm>
+
 #include <cuda_bf16.h>
 
 bool asca_tc_enabled();  // gemm.cu
@@ -325,10 +327,14 @@ __global__ void __launch_bounds__(SW_WARPS * 32) delta_step_warp64_kernel(
     constexpr int DH = 64;
     __shared__ __align__(16) float kq_s[SW_WARPS][2][DH];
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-    const int64_t unit = (int64_t)blockIdx.x * SW_WARPS + w;   // stream * H + h
     pdl_wait();
     pdl_launch_dependents();
-    if (unit >= n_units) return;
+    // The grid is at most one block per SM and block b owns the units [b n / G, (b + 1) n / G): every SM streams the same
+    // number of state bytes (within one unit), which is what it takes to reach the HBM rate -- an SM cannot pull more
+    // than its share, so a grid of fixed-size blocks that leaves some SMs a block short loses that share.
+    const int64_t lo = n_units * blockIdx.x / gridDim.x, hi = n_units * (blockIdx.x + 1) / gridDim.x;
+    for (int64_t unit = lo + w; unit < hi; unit += SW_WARPS) {   // unit = stream * H + h
+    __syncwarp();   // the previous unit's k and q have been read by every lane
     const int64_t s = unit / H;
     const int h = (int)(unit % H);
     const int d = H * DH;
@@ -388,6 +394,7 @@ __global__ void __launch_bounds__(SW_WARPS * 32) delta_step_warp64_kernel(
     }
     *reinterpret_cast<float2*>(o + s * d + h * DH + 2 * lane) = acc;
     if (o16) *reinterpret_cast<__nv_bfloat162*>(o16 + s * d + h * DH + 2 * lane) = __floats2bfloat162_rn(acc.x, acc.y);
+    }
 }
 
 template <int DH, typename T>
@@ -467,7 +474,8 @@ int asca_delta_step_strided(asca_ctx* ctx, const float* qkv, int64_t ld_qkv, con
                  "delta_step_strided: misaligned pointer");
     if (n_streams == 0) return ASCA_OK;
     const int64_t units = n_streams * H;
-    ASCA_CUDA(ctx, asca_launch(ctx, delta_step_warp64_kernel, dim3((unsigned)ceil_div64(units, SW_WARPS)), dim3(SW_WARPS * 32), 0,
+    const int64_t n_sm = ctx->sm_count > 0 ? ctx->sm_count : 148;
+    ASCA_CUDA(ctx, asca_launch(ctx, delta_step_warp64_kernel, dim3((unsigned)std::min(n_sm, ceil_div64(units, SW_WARPS))), dim3(SW_WARPS * 32), 0,
                                qkv, nullptr, nullptr, gate, nullptr, S, units, (int)H, 1, ld_qkv, ld_gate, o, (__nv_bfloat16*)o16));
     ctx->launches++;
     return ASCA_OK;
@@ -486,7 +494,8 @@ int asca_delta_step(asca_ctx* ctx, const float* q, const float* k, const float* 
     const bool in8 = fused ? ((uintptr_t)q & 7) == 0 : (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v) & 7) == 0;
     if (dh == 64 && in8) {   // one warp per (stream, head), no block barrier
         const int64_t units = n_streams * H;
-        delta_step_warp64_kernel<<<(unsigned)ceil_div64(units, SW_WARPS), SW_WARPS * 32, 0, ctx->stream>>>(
+        const int64_t n_sm = ctx->sm_count > 0 ? ctx->sm_count : 148;
+        delta_step_warp64_kernel<<<(unsigned)std::min(n_sm, ceil_div64(units, SW_WARPS)), SW_WARPS * 32, 0, ctx->stream>>>(
             q, k, v, alpha, beta, S, units, (int)H, fused, 3 * H * dh, 2 * H, o, nullptr);
         ASCA_CHECK_LAUNCH(ctx);
         return ASCA_OK;
