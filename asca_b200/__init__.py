@@ -423,6 +423,14 @@ class Model:
                        _p(nxt))
         return logits, nxt
 
+    def decode_greedy(self, state, ids, n_steps):
+        """n_steps greedy tokens per stream; the argmax feeds the next step on the device. Returns (n_steps, n_streams)."""
+        ids = np.ascontiguousarray(ids, dtype=np.uint32)
+        toks = np.empty((int(n_steps), ids.size), np.uint32)
+        self.gpu._call("asca_model_decode_greedy_host", self.gpu._ctx, self._h, _p(state), _p(ids), _i64(ids.size), _i64(n_steps),
+                       _p(toks))
+        return toks
+
     def free(self):
         if self._h is not None:
             self.gpu.lib.asca_model_destroy(self.gpu._ctx, self._h)

@@ -287,8 +287,10 @@ int asca_moe_fwd_sorted_residual(asca_ctx* ctx, const __nv_bfloat16* xp, const _
 int asca_residual_rmsnorm_bf16_rows(asca_ctx* ctx, const float* x, const float* yadd, float* x_mid, void* xn, int64_t rows,
                                     int64_t cols, float eps, const int32_t* y_row);
 
+// n_steps steps in bf16 mode. Step 0 consumes ids_h; a later step consumes the previous step's argmax, which never
+// leaves the device (tokens_h, n_steps x ns, receives all of them after the last step). One synchronisation at the end.
 static int decode_step_bf16(asca_ctx* ctx, asca_model* m, float* state, const uint32_t* ids_h, int64_t ns, float* logits_h,
-                            uint32_t* next_h) {
+                            uint32_t* next_h, int64_t n_steps = 1, uint32_t* tokens_h = nullptr) {
     typedef __nv_bfloat16 bf16;
     const int64_t d = m->d, H = m->H, dh = d / H, E = m->E, F = m->F, V = m->vocab;
     const int BF = ASCA_BF16;
@@ -298,17 +300,15 @@ static int decode_step_bf16(asca_ctx* ctx, asca_model* m, float* state, const ui
     Bufs bf(ctx);
     auto h16 = [&](int64_t n) { return (bf16*)bf.f((n + 1) / 2); };
     uint32_t* ids = (uint32_t*)bf.f(ns);
-    uint32_t* nxt = (uint32_t*)bf.f(ns);
+    uint32_t* toks = (uint32_t*)bf.f(ns * n_steps);   // every step's chosen ids
     int32_t* perm = (int32_t*)bf.f(ns);
     int32_t* offs = (int32_t*)bf.f(E + 1);
     float *x = bf.f(ns * d), *qkv = bf.f(ns * 3 * d), *gate = bf.f(ns * 2 * H), *o = bf.f(ns * d), *y = bf.f(ns * d),
           *x_mid = bf.f(ns * d), *mo = bf.f(ns * d), *logits = bf.f(ns * V), *pre_p = bf.f(ns * F);
     bf16 *x16 = h16(ns * d), *o16 = h16(ns * d), *xn16 = h16(ns * d), *hid16 = h16(ns * F), *hf16 = h16(ns * d);
-    ASCA_REQUIRE(ctx, ids && nxt && perm && offs && x && qkv && gate && o && y && x_mid && mo && logits && pre_p && x16 && o16 &&
+    ASCA_REQUIRE(ctx, ids && toks && perm && offs && x && qkv && gate && o && y && x_mid && mo && logits && pre_p && x16 && o16 &&
                           xn16 && hid16 && hf16, "model_decode_step: out of memory");
     ASCA_CUDA(ctx, cudaMemcpyAsync(ids, ids_h, (size_t)ns * 4, cudaMemcpyHostToDevice, ctx->stream));
-    ASCA_TRY(asca_moe_dispatch(ctx, ids, ns, E, perm, offs, nullptr));
-    ASCA_TRY(asca_embed_fwd(ctx, P + m->embed, ids, ns, d, x));
     const bool fused64 = dh == 64;   // one projection for qkv + gate, the warp-per-head state update, casts folded in
     const int64_t ldq = (3 * d + 2 * H + 7) & ~(int64_t)7;
     if (fused64) {
@@ -373,18 +373,25 @@ static int decode_step_bf16(asca_ctx* ctx, asca_model* m, float* state, const ui
         return gemm_tc::launch_skinny(ctx, t);
     };
     int32_t* inv_perm = sorted_moe ? (int32_t*)bf.f(ns) : nullptr;
+    ASCA_REQUIRE(ctx, !sorted_moe || inv_perm, "model_decode_step: out of memory");
+    struct PdlScope {
+        asca_ctx* c;
+        explicit PdlScope(asca_ctx* c_) : c(c_) {}
+        ~PdlScope() { c->pdl = false; }
+    } pdl_scope(ctx);
+    for (int64_t step = 0; step < n_steps; ++step) {
+    const uint32_t* cur = step == 0 ? ids : toks + (step - 1) * ns;
+    uint32_t* nxt = toks + step * ns;
+    ctx->pdl = false;
+    ASCA_TRY(asca_moe_dispatch(ctx, cur, ns, E, perm, offs, nullptr));
+    ASCA_TRY(asca_embed_fwd(ctx, P + m->embed, cur, ns, d, x));
     if (sorted_moe) {
-        ASCA_REQUIRE(ctx, inv_perm, "model_decode_step: out of memory");
         invert_perm_kernel<<<(unsigned)ceil_div64(ns, 256), 256, 0, ctx->stream>>>(perm, inv_perm, ns);
         ASCA_CHECK_LAUNCH(ctx);
     }
     ASCA_TRY(asca_cast_bf16(ctx, x, x16, ns * d));
     // the block chain is short kernels back to back: each may become resident while its predecessor drains
-    struct PdlScope {
-        asca_ctx* c;
-        explicit PdlScope(asca_ctx* c_) : c(c_) { c->pdl = true; }
-        ~PdlScope() { c->pdl = false; }
-    } pdl_scope(ctx);
+    ctx->pdl = true;
     for (int64_t li = 0; li < m->L; ++li) {
         const Lyr& w = m->lay[li];
         const Lyr& w16 = m->lay16[li];
@@ -416,12 +423,16 @@ static int decode_step_bf16(asca_ctx* ctx, asca_model* m, float* state, const ui
     ASCA_TRY(asca_residual_rmsnorm_bf16(ctx, x, nullptr, nullptr, hf16, ns, d, 1e-6f));
     if (packed) ASCA_TRY(few_rows(hf16, d, m->dec_pk + m->L * r_layer * 64, V, logits, V, nullptr));
     else ASCA_TRY(asca_gemm(ctx, ASCA_NN, ns, V, d, hf16, d, W + m->head16, V, logits, V, nullptr, 0, BF));
-    if (logits_h) ASCA_CUDA(ctx, cudaMemcpyAsync(logits_h, logits, (size_t)ns * V * 4, cudaMemcpyDeviceToHost, ctx->stream));
-    if (next_h) {
+    ctx->pdl = false;
+    if (logits_h && step == n_steps - 1)
+        ASCA_CUDA(ctx, cudaMemcpyAsync(logits_h, logits, (size_t)ns * V * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    if (next_h || tokens_h || step + 1 < n_steps) {
         argmax_kernel<<<(unsigned)ceil_div64(ns, 8), 256, 0, ctx->stream>>>(logits, ns, (int)V, nxt);
         ASCA_CHECK_LAUNCH(ctx);
-        ASCA_CUDA(ctx, cudaMemcpyAsync(next_h, nxt, (size_t)ns * 4, cudaMemcpyDeviceToHost, ctx->stream));
     }
+    }   // steps
+    if (next_h) ASCA_CUDA(ctx, cudaMemcpyAsync(next_h, toks + (n_steps - 1) * ns, (size_t)ns * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    if (tokens_h) ASCA_CUDA(ctx, cudaMemcpyAsync(tokens_h, toks, (size_t)ns * n_steps * 4, cudaMemcpyDeviceToHost, ctx->stream));
     return asca_ctx_sync(ctx);
 }
 
@@ -911,6 +922,20 @@ int asca_model_adamw_step(asca_ctx* ctx, asca_model* m, float lr, float beta1, f
     m->dec_pk_stale = true;
     return asca_adamw_segmented_cast(ctx, m->params, m->grads, m->m, m->v, m->seg_off.data(), lr_t.data(), eps_t.data(), n_seg,
                                      beta1, beta2, lr * wd, fuse ? (void*)m->params16 : nullptr);
+}
+
+int asca_model_decode_greedy_host(asca_ctx* ctx, asca_model* m, float* state, const uint32_t* ids_h, int64_t ns, int64_t n_steps,
+                                  uint32_t* tokens_h) {
+    if (!ctx || !m) return ASCA_ERR_ARG;
+    ASCA_REQUIRE(ctx, state && ids_h && tokens_h && ns > 0 && n_steps > 0, "model_decode_greedy: bad arguments");
+    for (int64_t i = 0; i < ns; ++i) ASCA_REQUIRE(ctx, ids_h[i] < (uint32_t)m->vocab, "model_decode_greedy: id out of range");
+    if (m->compute == ASCA_BF16) return decode_step_bf16(ctx, m, state, ids_h, ns, nullptr, nullptr, n_steps, tokens_h);
+    const uint32_t* cur = ids_h;   // f32 mode: the single-step path, token by token
+    for (int64_t t = 0; t < n_steps; ++t) {
+        ASCA_TRY(asca_model_decode_step_host(ctx, m, state, cur, ns, nullptr, tokens_h + t * ns));
+        cur = tokens_h + t * ns;
+    }
+    return ASCA_OK;
 }
 
 int asca_model_decode_step_host(asca_ctx* ctx, asca_model* m, float* state, const uint32_t* ids_h, int64_t ns,

@@ -360,6 +360,12 @@ int asca_model_adamw_step(asca_ctx* ctx, asca_model* m, float lr, float beta1, f
  * uint32 (n_streams), nullable -- the greedy argmax (lowest index on ties). */
 int asca_model_decode_step_host(asca_ctx* ctx, asca_model* m, float* state, const uint32_t* ids,
                                 int64_t n_streams, float* logits, uint32_t* next_ids);
+/* Greedy decode of n_steps tokens per stream (the loop of the reference's `asca gen` with argmax sampling,
+ * rust/src/main.rs: step, pick the largest logit, feed it back): step 0 consumes ids (host, n_streams), every later
+ * step the argmax of the step before, which stays on the device; tokens (host, n_steps x n_streams, one row per
+ * step) receives every chosen id after the last step. One synchronisation per call instead of one per token. */
+int asca_model_decode_greedy_host(asca_ctx* ctx, asca_model* m, float* state, const uint32_t* ids,
+                                  int64_t n_streams, int64_t n_steps, uint32_t* tokens);
 
 #ifdef __cplusplus
 }

@@ -212,6 +212,30 @@ def test_bf16_decode_sees_weight_updates_and_takes_more_than_256_streams(orc, gp
     dev.free()
 
 
+def test_greedy_decode_on_the_device_equals_step_by_step(orc, gpu):
+    """decode_greedy keeps the argmax on the device between steps; tokens and final states must equal feeding
+    decode_step's own argmax back from the host, in both compute modes."""
+    import asca_b200
+
+    cfg = (256, 128, 2, 2, 8, 256)
+    ref = orc.Model(*cfg)
+    ref.init_reference(orc.Rng(41))
+    first = orc.Rng(42).below(256, 24)
+    for mode in (asca_b200.BF16, asca_b200.F32):
+        dev = asca_b200.Model(gpu, *cfg)
+        dev.set_params(ref.params)
+        dev.set_compute(mode)
+        s1, s2 = dev.new_decode_state(24), dev.new_decode_state(24)
+        toks = dev.decode_greedy(s1, first.copy(), 12)
+        cur, want = first.copy(), []
+        for _ in range(12):
+            _, cur = dev.decode_step(s2, cur, want_logits=False)
+            want.append(cur.copy())
+        assert np.array_equal(toks, np.stack(want))
+        assert np.array_equal(s1.cpu().numpy(), s2.cpu().numpy())
+        dev.free()
+
+
 def test_trainer_loop_matches_oracle_loss_for_loss_and_resumes(orc, gpu, tmp_path):
     """Four steps of the reference's loop (lr schedule, data windows from the reference generator,
     forward + backward + AdamW) on the device against the same loop on the CPU oracle; then a resume
