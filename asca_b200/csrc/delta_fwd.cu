@@ -327,8 +327,8 @@ __global__ void __launch_bounds__(SW_WARPS * 32) delta_step_warp64_kernel(
     constexpr int DH = 64;
     __shared__ __align__(16) float kq_s[SW_WARPS][2][DH];
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-    pdl_wait();
-    pdl_launch_dependents();
+    bool waited = false;   // the state is this kernel's own (last written a step ago): the first unit's loads are issued
+                           // before the wait for the previous kernel, whose output is only q, k, v and the gates
     // The grid is at most one block per SM and block b owns the units [b n / G, (b + 1) n / G): every SM streams the same
     // number of state bytes (within one unit), which is what it takes to reach the HBM rate -- an SM cannot pull more
     // than its share, so a grid of fixed-size blocks that leaves some SMs a block short loses that share.
@@ -342,6 +342,11 @@ __global__ void __launch_bounds__(SW_WARPS * 32) delta_step_warp64_kernel(
     float2 st[DH];
 #pragma unroll
     for (int a = 0; a < DH; ++a) st[a] = Sg[a * 32 + lane];   // in flight while the inputs are prepared
+    if (!waited) {
+        pdl_wait();
+        pdl_launch_dependents();
+        waited = true;
+    }
     float2 q2, k2, v2;
     float al, be;
     if (fused) {
@@ -394,6 +399,10 @@ __global__ void __launch_bounds__(SW_WARPS * 32) delta_step_warp64_kernel(
     }
     *reinterpret_cast<float2*>(o + s * d + h * DH + 2 * lane) = acc;
     if (o16) *reinterpret_cast<__nv_bfloat162*>(o16 + s * d + h * DH + 2 * lane) = __floats2bfloat162_rn(acc.x, acc.y);
+    }
+    if (!waited) {   // a warp without a unit
+        pdl_wait();
+        pdl_launch_dependents();
     }
 }
 

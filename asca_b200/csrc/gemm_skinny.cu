@@ -53,6 +53,7 @@ struct SkP {
     int64_t ldc2;
     int c2_mapped;
     int w_packed;
+    int early;
     int* err_word;
 };
 
@@ -95,7 +96,7 @@ __global__ void __launch_bounds__(THREADS, SkShape<NT, ST>::CTAS_PER_SM) gemm_sk
         tc::prefetch_tensormap(&mapX);
     }
     if (warp == 1) tc::tmem_alloc(tmem_slot, TMEM_COLS);
-    pdl_wait();
+    if (!p.early) pdl_wait();
     // ---- tile table: group g owns tiles [prefix[g], prefix[g+1]); within it tile = token_tile * tiles_f + feature_tile
     if (warp == 0) {
         int base = 0;
@@ -155,26 +156,40 @@ __global__ void __launch_bounds__(THREADS, SkShape<NT, ST>::CTAS_PER_SM) gemm_sk
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer (one thread)
         if (lane == 0) {
+            const auto load_w = [&](const Tile& x, int kt, int s) {
+                uint8_t* w_s = tiles + s * STAGE_BYTES;
+                tc::mbar_expect_tx(&full[s], STAGE_BYTES);   // the stage's weights and tokens
+                if (p.w_packed) {   // the stage's 16 KiB are contiguous in memory: one box of 128 rows x 128 bytes
+                    tc::tma_load_2d(w_s, &mapW, 0, x.pk_row + kt * BF, &full[s]);
+                } else {
+                    tc::tma_load_2d(w_s, &mapW, x.f0 + x.w_in, kt * BK + x.w_out, &full[s]);          // 64 features x 64 k rows
+                    tc::tma_load_2d(w_s + 8192, &mapW, x.f0 + 64 + x.w_in, kt * BK + x.w_out, &full[s]);
+                }
+            };
+            // Weights that do not depend on the previous kernel: the ring is filled with them while that kernel is still
+            // running (this CTA is resident early under programmatic dependent launch); the tokens follow after the wait.
+            uint32_t n_pre = 0;
+            if (p.early) {
+                for (int t = blockIdx.x; t < total_tiles && n_pre < STAGES; t += gridDim.x) {
+                    const Tile x = locate(t);
+                    for (int kt = 0; kt < num_k && n_pre < STAGES; ++kt, ++n_pre) load_w(x, kt, n_pre);
+                }
+                pdl_wait();
+            }
             uint32_t it = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                 const Tile x = locate(t);
                 for (int kt = 0; kt < num_k; ++kt, ++it) {
                     const int s = it % STAGES;
-                    if (it >= STAGES && !tc::mbar_wait(&empty[s], ((it / STAGES) - 1) & 1, abort_flag, p.err_word, 111)) {
-                        ok = false;
-                        break;
+                    if (it >= n_pre) {
+                        if (it >= STAGES && !tc::mbar_wait(&empty[s], ((it / STAGES) - 1) & 1, abort_flag, p.err_word, 111)) {
+                            ok = false;
+                            break;
+                        }
+                        load_w(x, kt, s);
                     }
-                    uint8_t* w_s = tiles + s * STAGE_BYTES;
-                    tc::mbar_expect_tx(&full[s], STAGE_BYTES);
-                    const int k0 = kt * BK;
-                    if (p.w_packed) {   // the stage's 16 KiB are contiguous in memory: one box of 128 rows x 128 bytes
-                        tc::tma_load_2d(w_s, &mapW, 0, x.pk_row + kt * BF, &full[s]);
-                    } else {
-                        tc::tma_load_2d(w_s, &mapW, x.f0 + x.w_in, k0 + x.w_out, &full[s]);          // 64 features x 64 k rows
-                        tc::tma_load_2d(w_s + 8192, &mapW, x.f0 + 64 + x.w_in, k0 + x.w_out, &full[s]);
-                    }
-                    tc::tma_load_2d(w_s + W_BYTES, &mapX, k0, x.row0, &full[s]);                     // 64 k x NT token rows
+                    tc::tma_load_2d(tiles + s * STAGE_BYTES + W_BYTES, &mapX, kt * BK, x.row0, &full[s]);   // 64 k x NT token rows
                 }
             }
         }
@@ -216,6 +231,7 @@ __global__ void __launch_bounds__(THREADS, SkShape<NT, ST>::CTAS_PER_SM) gemm_sk
         // the warp's 2 KiB of shared memory as [token][feature] -> global memory with 8 lanes on each token's 128 bytes
         // (16-byte accesses), where bias, activation, accumulation and the row map are applied.
         const int q = warp & 3;
+        if (p.early) pdl_wait();   // the output rows may be the previous kernel's (accumulate) or its inputs'
         float* stg = reinterpret_cast<float*>(staging + q * 2048);
         const int col4 = lane & 7, rsub = lane >> 3;   // store phase: features 4 col4 .. + 3 of token row 4 i + rsub
         const bool vec_c = p.C && (p.ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0;
@@ -387,6 +403,7 @@ int sk_launch_shape(asca_ctx* ctx, const Args& a, int64_t tiles) {
     p.w_goff_inner = a.b_goff_inner; p.w_goff_outer = a.b_goff_outer;
     p.bias_gstride = a.bias_gstride; p.epi = a.epi; p.C2 = a.C2; p.ldc2 = a.ldc2; p.c2_mapped = a.c2_mapped;
     p.w_packed = a.b_packed;
+    p.early = a.b_early;
     p.err_word = ctx->err_word;
     const int n_sm = ctx->sm_count > 0 ? ctx->sm_count : 148;
     const int64_t grid = std::min<int64_t>(tiles, (int64_t)n_sm * SkShape<NT, ST>::CTAS_PER_SM);

@@ -36,6 +36,8 @@ struct Args {
     int64_t ldc2;
     int c2_mapped;            // few-row kernel only: C2's rows go through c_idx like C's
     int b_packed;             // few-row kernel only: B is a buffer made by skinny_pack (b_rows = its rows of 64)
+    int b_early;              // few-row kernel only: B and the group offsets were written before the PREVIOUS kernel on
+                              // the stream started, so under programmatic dependent launch they may be read while it runs
 };
 
 // True when the tensor-core kernel can take this problem (alignment and divisibility rules of

@@ -369,6 +369,7 @@ static int decode_step_bf16(asca_ctx* ctx, asca_model* m, float* state, const ui
         t.B = Wpk; t.ldb = 64; t.b_rows = gemm_tc::skinny_packed_rows(1, K, N); t.b_cols = 64; t.b_packed = 1;
         t.C = C; t.ldc = ldc; t.M = (int)ns; t.N = (int)N; t.K = (int)K; t.bias = bias;
         t.group_dim = gemm_tc::GROUP_NONE; t.epi = gemm_tc::EPI_NONE;
+        t.b_early = 1;   // weights: written long before the previous kernel
         if (!gemm_tc::supported(t)) return asca_fail(ctx, ASCA_ERR_UNSUPPORTED, "model_decode_step: product not supported");
         return gemm_tc::launch_skinny(ctx, t);
     };

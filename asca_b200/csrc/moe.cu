@@ -230,6 +230,7 @@ int asca_moe_fwd_sorted_residual(asca_ctx* ctx, const __nv_bfloat16* xp, const _
     b.bias = b2; b.bias_gstride = 0;
     b.offsets = offsets; b.n_groups = (int)E; b.group_dim = gemm_tc::GROUP_M; b.total_rows = N;
     b.C2 = x16; b.ldc2 = d; b.c2_mapped = 1;
+    a.b_early = b.b_early = 1;   // weights and the dispatch tables predate the kernel before each product
     if (packed) {   // w1 / w2 are skinny_pack buffers of the E expert matrices
         a.b_packed = 1; a.ldb = 64; a.b_cols = 64; a.b_rows = gemm_tc::skinny_packed_rows(E, d, F); a.b_goff_inner = 0;
         b.b_packed = 1; b.ldb = 64; b.b_cols = 64; b.b_rows = gemm_tc::skinny_packed_rows(E, F, d); b.b_goff_outer = 0;
