@@ -3,6 +3,8 @@
 // rust/src/model.rs:631-802 and rust/src/delta.rs:121-207 / :615-674, composed from the
 // library's own entry points with every activation resident in HBM. f32 arithmetic.
 #include "common.cuh"
+
+#include <algorithm>
 #include "gemm_tc.cuh"
 
 namespace {
@@ -143,6 +145,18 @@ __global__ void __launch_bounds__(256) add_kernel(const float* __restrict__ a, c
                                                   float* __restrict__ out, int64_t n) {
     const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
     if (i < n) out[i] = a[i] + 1.0f * b[i];
+}
+// out = a + b with a bf16 copy, four elements per thread (n % 4 == 0, 16-byte aligned; out may be a)
+__global__ void __launch_bounds__(256) add_cast4_kernel(const float* a, const float* __restrict__ b, float* out,
+                                                        __nv_bfloat16* __restrict__ out16, int64_t n4) {
+    const int64_t stride = (int64_t)gridDim.x * 256;
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n4; i += stride) {
+        const float4 x = reinterpret_cast<const float4*>(a)[i], y = reinterpret_cast<const float4*>(b)[i];
+        const float4 v = make_float4(x.x + y.x, x.y + y.y, x.z + y.z, x.w + y.w);
+        reinterpret_cast<float4*>(out)[i] = v;
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+        reinterpret_cast<uint2*>(out16)[i] = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+    }
 }
 // inv[perm[i]] = i
 __global__ void __launch_bounds__(256) invert_perm_kernel(const int32_t* __restrict__ perm, int32_t* __restrict__ inv, int64_t n) {
@@ -494,17 +508,20 @@ static int forward_backward_bf16(asca_ctx* ctx, asca_model* m, const uint32_t* i
     float* mo = bf.f(N * d);
     ASCA_REQUIRE(ctx, x && qkv && gate && y && mo, "model_forward_backward: out of memory");
     ASCA_TRY(asca_embed_fwd(ctx, P + m->embed, ids, N, d, x));
+    const bool vec4 = (d & 3) == 0;
+    const unsigned add_grid = (unsigned)std::min<int64_t>(ceil_div64(N * d / 4, 256), 148 * 16);
+    bf16* next_x_in = nullptr;
     for (int64_t li = 0; li < L; ++li) {
         const Lyr& w = m->lay[li];
         const Lyr& w16 = m->lay16[li];
         Act& a = acts[li];
-        a.x_in = h16(N * d); a.q = h16(N * d); a.k = h16(N * d); a.v = h16(N * d); a.o = h16(N * d); a.xn = h16(N * d);
+        a.x_in = li == 0 ? h16(N * d) : next_x_in; a.q = h16(N * d); a.k = h16(N * d); a.v = h16(N * d); a.o = h16(N * d); a.xn = h16(N * d);
         a.hid_p = h16(N * F);
         a.qn = bf.f(N * H); a.kn = bf.f(N * H); a.al = bf.f(N * H); a.be = bf.f(N * H);
         a.ckpt = bf.f(nck); a.x_mid = bf.f(N * d); a.pre_p = bf.f(N * F);
         ASCA_REQUIRE(ctx, a.x_in && a.q && a.k && a.v && a.o && a.xn && a.hid_p && a.qn && a.kn && a.al && a.be && a.ckpt &&
                               a.x_mid && a.pre_p, "model_forward_backward: out of memory");
-        ASCA_TRY(asca_cast_bf16(ctx, x, a.x_in, N * d));
+        if (li == 0) ASCA_TRY(asca_cast_bf16(ctx, x, a.x_in, N * d));   // later blocks: written with the residual add below
         ASCA_TRY(asca_gemm(ctx, ASCA_NN, N, 3 * d, d, a.x_in, d, W + w16.w_qkv, 3 * d, qkv, 3 * d, P + w.b_qkv, 0, BF));
         ASCA_TRY(asca_gemm(ctx, ASCA_NN, N, 2 * H, d, a.x_in, d, W + w16.w_gate, 2 * H, gate, 2 * H, P + w.b_gate, 0, BF));
         ASCA_TRY(asca_delta_prep_bf16(ctx, qkv, gate, N, H, dh, a.q, a.k, a.v, a.qn, a.kn, a.al, a.be));
@@ -513,7 +530,19 @@ static int forward_backward_bf16(asca_ctx* ctx, asca_model* m, const uint32_t* i
         ASCA_TRY(asca_residual_rmsnorm_bf16(ctx, x, y, a.x_mid, a.xn, N, d, 1e-6f));
         ASCA_TRY(asca_moe_fwd(ctx, a.xn, W + w16.w1, P + w.b1, W + w16.w2, P + w.b2, perm, offs, N, d, F, E, BF, mo, a.pre_p,
                               a.hid_p));
-        ASCA_TRY(asca_residual_rmsnorm(ctx, a.x_mid, mo, x, nullptr, N, d, 1e-6f));
+        if (li + 1 < L && vec4) {   // x_out = x_mid + moe, with the bf16 copy the next block's products read
+            next_x_in = h16(N * d);
+            ASCA_REQUIRE(ctx, next_x_in, "model_forward_backward: out of memory");
+            add_cast4_kernel<<<add_grid, 256, 0, ctx->stream>>>(a.x_mid, mo, x, next_x_in, N * d / 4);
+            ASCA_CHECK_LAUNCH(ctx);
+        } else {
+            ASCA_TRY(asca_residual_rmsnorm(ctx, a.x_mid, mo, x, nullptr, N, d, 1e-6f));
+            if (li + 1 < L) {
+                next_x_in = h16(N * d);
+                ASCA_REQUIRE(ctx, next_x_in, "model_forward_backward: out of memory");
+                ASCA_TRY(asca_cast_bf16(ctx, x, next_x_in, N * d));
+            }
+        }
     }
     bf16* h_final = h16(N * d);
     float* logits = bf.f(N * V);
@@ -551,9 +580,14 @@ static int forward_backward_bf16(asca_ctx* ctx, asca_model* m, const uint32_t* i
         ASCA_TRY((acc ? asca_moe_bwd_acc : asca_moe_bwd)(ctx, a.xn, W + w16.w1, W + w16.w2, a.pre_p, a.hid_p, dx, perm, offs, N, d, F, E, BF, G + w.w1,
                                   G + w.b1, G + w.w2, G + w.b2, dxn));
         ASCA_TRY(asca_rmsnorm_bwd(ctx, a.x_mid, dxn, d_moe, N, d, 1e-6f));
-        add_kernel<<<(unsigned)blocks_nd, 256, 0, ctx->stream>>>(dx, d_moe, dx, N * d);   // d_mid
-        ctx->launches++;
-        ASCA_TRY(asca_cast_bf16(ctx, dx, dx16, N * d));
+        if (vec4) {   // d_mid = dx + d_moe, with its bf16 copy
+            add_cast4_kernel<<<add_grid, 256, 0, ctx->stream>>>(dx, d_moe, dx, dx16, N * d / 4);
+            ASCA_CHECK_LAUNCH(ctx);
+        } else {
+            add_kernel<<<(unsigned)blocks_nd, 256, 0, ctx->stream>>>(dx, d_moe, dx, N * d);
+            ctx->launches++;
+            ASCA_TRY(asca_cast_bf16(ctx, dx, dx16, N * d));
+        }
         ASCA_TRY(asca_gemm(ctx, ASCA_NT, N, d, d, dx16, d, W + w16.w_o, d, d_o, d, nullptr, 0, BF));
         ASCA_TRY(asca_cast_bf16(ctx, d_o, do16, N * d));
         ASCA_TRY(asca_gemm(ctx, ASCA_TN, d, d, N, a.o, d, dx16, d, G + w.w_o, d, nullptr, acc, BF));
