@@ -437,7 +437,9 @@ int launch_skinny(asca_ctx* ctx, const Args& a) {
     // One CTA per SM with the whole shared memory as its ring: a CTA's k-loop is one latency-bound stream, and what
     // keeps HBM busy is the bytes in flight per SM (10 stages of 20 KiB, or 8 of 24 KiB).
     if (a.group_dim == GROUP_NONE) {
-        if (a.M <= 32) return sk_launch_shape<32, 10>(ctx, a, tiles_f);
+        const int n_sm = ctx->sm_count > 0 ? ctx->sm_count : 148;
+        // token tiles of 32 while they still fit one wave: more CTAs streaming, and 10 of a tile's k-tiles in its ring
+        if (a.M <= 32 || ((a.M + 31) / 32) * tiles_f <= n_sm) return sk_launch_shape<32, 10>(ctx, a, ((a.M + 31) / 32) * tiles_f);
         return sk_launch_shape<64, 8>(ctx, a, ((a.M + 63) / 64) * tiles_f);
     }
     return sk_launch_shape<32, 10>(ctx, a, (a.total_rows / 32 + a.n_groups) * tiles_f);
