@@ -158,6 +158,55 @@ __global__ void __launch_bounds__(256) add_cast4_kernel(const float* a, const fl
         reinterpret_cast<uint2*>(out16)[i] = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
     }
 }
+// A decode step's token prologue in one launch (at most 1024 streams and 1024 experts, d % 4 == 0): every block
+// embeds 8 rows (f32 + bf16 copy); block 0 also builds the dispatch tables -- expert = hash(id) % E
+// (rust/src/model.rs:69-77), stable counting sort by expert: perm (tokens grouped by expert, ascending inside an
+// expert), offsets, and the inverse permutation. Integer work, the same permutation as asca_moe_dispatch.
+__global__ void __launch_bounds__(256) decode_prologue_kernel(const float* __restrict__ table, const uint32_t* __restrict__ ids, int ns,
+                                                              int d, int E, float* __restrict__ x, __nv_bfloat16* __restrict__ x16,
+                                                              int32_t* __restrict__ perm, int32_t* __restrict__ offs,
+                                                              int32_t* __restrict__ inv_perm) {
+    __shared__ int32_t cnt[1024 + 1];
+    __shared__ uint16_t ex[1024];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int t = blockIdx.x * 8 + w;
+    if (t < ns) {
+        const float4* src = reinterpret_cast<const float4*>(table + (int64_t)ids[t] * d);
+        float4* dst = reinterpret_cast<float4*>(x + (int64_t)t * d);
+        uint2* dst16 = reinterpret_cast<uint2*>(x16 + (int64_t)t * d);
+        for (int c = lane; c < d / 4; c += 32) {
+            const float4 v = src[c];
+            dst[c] = v;
+            const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+            dst16[c] = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+        }
+    }
+    if (blockIdx.x != 0) return;
+    for (int e = threadIdx.x; e <= E; e += 256) cnt[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < ns; i += 256) {
+        uint32_t h = ids[i] * 0x9E3779B1u;
+        h ^= h >> 15;
+        h *= 0x85EBCA6Bu;
+        h ^= h >> 13;
+        const uint32_t e = h % (uint32_t)E;
+        ex[i] = (uint16_t)e;
+        atomicAdd(&cnt[e + 1], 1);   // integer counts: the order of the additions does not matter
+    }
+    __syncthreads();
+    if (threadIdx.x == 0)
+        for (int e = 0; e < E; ++e) cnt[e + 1] += cnt[e];   // cnt[e] = first position of expert e
+    __syncthreads();
+    for (int e = threadIdx.x; e <= E; e += 256) offs[e] = cnt[e];
+    for (int i = threadIdx.x; i < ns; i += 256) {
+        const uint16_t e = ex[i];
+        int rank = 0;
+        for (int j = 0; j < i; ++j) rank += ex[j] == e;   // tokens of the same expert before this one
+        const int pos = cnt[e] + rank;
+        perm[pos] = i;
+        inv_perm[i] = pos;
+    }
+}
 // inv[perm[i]] = i
 __global__ void __launch_bounds__(256) invert_perm_kernel(const int32_t* __restrict__ perm, int32_t* __restrict__ inv, int64_t n) {
     const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
@@ -398,13 +447,19 @@ static int decode_step_bf16(asca_ctx* ctx, asca_model* m, float* state, const ui
     const uint32_t* cur = step == 0 ? ids : toks + (step - 1) * ns;
     uint32_t* nxt = toks + step * ns;
     ctx->pdl = false;
-    ASCA_TRY(asca_moe_dispatch(ctx, cur, ns, E, perm, offs, nullptr));
-    ASCA_TRY(asca_embed_fwd(ctx, P + m->embed, cur, ns, d, x));
-    if (sorted_moe) {
-        invert_perm_kernel<<<(unsigned)ceil_div64(ns, 256), 256, 0, ctx->stream>>>(perm, inv_perm, ns);
+    if (sorted_moe && ns <= 1024 && E <= 1024 && (d & 3) == 0) {   // dispatch, embedding and its bf16 copy: one launch
+        decode_prologue_kernel<<<(unsigned)ceil_div64(ns, 8), 256, 0, ctx->stream>>>(P + m->embed, cur, (int)ns, (int)d, (int)E, x, x16,
+                                                                                     perm, offs, inv_perm);
         ASCA_CHECK_LAUNCH(ctx);
+    } else {
+        ASCA_TRY(asca_moe_dispatch(ctx, cur, ns, E, perm, offs, nullptr));
+        ASCA_TRY(asca_embed_fwd(ctx, P + m->embed, cur, ns, d, x));
+        if (sorted_moe) {
+            invert_perm_kernel<<<(unsigned)ceil_div64(ns, 256), 256, 0, ctx->stream>>>(perm, inv_perm, ns);
+            ASCA_CHECK_LAUNCH(ctx);
+        }
+        ASCA_TRY(asca_cast_bf16(ctx, x, x16, ns * d));
     }
-    ASCA_TRY(asca_cast_bf16(ctx, x, x16, ns * d));
     // the block chain is short kernels back to back: each may become resident while its predecessor drains
     ctx->pdl = true;
     for (int64_t li = 0; li < m->L; ++li) {
