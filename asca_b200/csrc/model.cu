@@ -170,6 +170,8 @@ __global__ void __launch_bounds__(256) decode_prologue_kernel(const float* __res
     __shared__ uint16_t ex[1024];
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
     const int t = blockIdx.x * 8 + w;
+    pdl_wait();   // the ids may be the previous kernel's argmax
+    pdl_launch_dependents();
     if (t < ns) {
         const float4* src = reinterpret_cast<const float4*>(table + (int64_t)ids[t] * d);
         float4* dst = reinterpret_cast<float4*>(x + (int64_t)t * d);
@@ -244,6 +246,8 @@ __global__ void __launch_bounds__(256) argmax_kernel(const float* __restrict__ l
                                                      uint32_t* __restrict__ out) {
     const int lane = threadIdx.x & 31;
     const int64_t t = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    pdl_wait();
+    pdl_launch_dependents();
     if (t >= N) return;
     float best = -INFINITY;
     int bi = 0x7fffffff;
@@ -448,9 +452,10 @@ static int decode_step_bf16(asca_ctx* ctx, asca_model* m, float* state, const ui
     uint32_t* nxt = toks + step * ns;
     ctx->pdl = false;
     if (sorted_moe && ns <= 1024 && E <= 1024 && (d & 3) == 0) {   // dispatch, embedding and its bf16 copy: one launch
-        decode_prologue_kernel<<<(unsigned)ceil_div64(ns, 8), 256, 0, ctx->stream>>>(P + m->embed, cur, (int)ns, (int)d, (int)E, x, x16,
-                                                                                     perm, offs, inv_perm);
-        ASCA_CHECK_LAUNCH(ctx);
+        ctx->pdl = step > 0;   // after the previous step's argmax
+        ASCA_CUDA(ctx, asca_launch(ctx, decode_prologue_kernel, dim3((unsigned)ceil_div64(ns, 8)), dim3(256), 0, P + m->embed, cur, (int)ns,
+                                   (int)d, (int)E, x, x16, perm, offs, inv_perm));
+        ctx->launches++;
     } else {
         ASCA_TRY(asca_moe_dispatch(ctx, cur, ns, E, perm, offs, nullptr));
         ASCA_TRY(asca_embed_fwd(ctx, P + m->embed, cur, ns, d, x));
@@ -493,13 +498,15 @@ static int decode_step_bf16(asca_ctx* ctx, asca_model* m, float* state, const ui
     ASCA_TRY(asca_residual_rmsnorm_bf16(ctx, x, nullptr, nullptr, hf16, ns, d, 1e-6f));
     if (packed) ASCA_TRY(few_rows(hf16, d, m->dec_pk + m->L * r_layer * 64, V, logits, V, nullptr));
     else ASCA_TRY(asca_gemm(ctx, ASCA_NN, ns, V, d, hf16, d, W + m->head16, V, logits, V, nullptr, 0, BF));
-    ctx->pdl = false;
-    if (logits_h && step == n_steps - 1)
+    if (logits_h && step == n_steps - 1) {
+        ctx->pdl = false;   // a copy sits between the head product and the argmax
         ASCA_CUDA(ctx, cudaMemcpyAsync(logits_h, logits, (size_t)ns * V * 4, cudaMemcpyDeviceToHost, ctx->stream));
-    if (next_h || tokens_h || step + 1 < n_steps) {
-        argmax_kernel<<<(unsigned)ceil_div64(ns, 8), 256, 0, ctx->stream>>>(logits, ns, (int)V, nxt);
-        ASCA_CHECK_LAUNCH(ctx);
     }
+    if (next_h || tokens_h || step + 1 < n_steps) {
+        ASCA_CUDA(ctx, asca_launch(ctx, argmax_kernel, dim3((unsigned)ceil_div64(ns, 8)), dim3(256), 0, (const float*)logits, ns, (int)V, nxt));
+        ctx->launches++;
+    }
+    ctx->pdl = false;
     }   // steps
     if (next_h) ASCA_CUDA(ctx, cudaMemcpyAsync(next_h, toks + (n_steps - 1) * ns, (size_t)ns * 4, cudaMemcpyDeviceToHost, ctx->stream));
     if (tokens_h) ASCA_CUDA(ctx, cudaMemcpyAsync(tokens_h, toks, (size_t)ns * n_steps * 4, cudaMemcpyDeviceToHost, ctx->stream));
