@@ -145,10 +145,12 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_warp_kernel(const float* __re
     }
 }
 
+// add (nullable, may be dx): a row added to the result -- the other branch of a residual; dx16 (nullable): bf16 copy
 template <int NV>
 __global__ void __launch_bounds__(256) rmsnorm_bwd_warp_kernel(const float* __restrict__ x,
-                                                               const float* __restrict__ dy, float* __restrict__ dx,
-                                                               int64_t rows, int cols, float eps) {
+                                                               const float* __restrict__ dy, float* dx,
+                                                               int64_t rows, int cols, float eps, const float* add = nullptr,
+                                                               __nv_bfloat16* __restrict__ dx16 = nullptr) {
     const int lane = threadIdx.x & 31;
     const int64_t r = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
     if (r >= rows) return;
@@ -173,12 +175,24 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_warp_kernel(const float* __re
     const float inv = 1.0f / sqrtf(s2 / (float)cols + eps);
     const float im = inv * ((sd * inv) / (float)cols);
     float4* o = reinterpret_cast<float4*>(dx + r * (int64_t)cols);
+    const float4* ad = add ? reinterpret_cast<const float4*>(add + r * (int64_t)cols) : nullptr;
+    uint2* o16 = dx16 ? reinterpret_cast<uint2*>(dx16 + r * (int64_t)cols) : nullptr;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
         const int c = lane + 32 * i;
-        if (c < n4)
-            o[c] = make_float4(inv * (g[i].x - a[i].x * im), inv * (g[i].y - a[i].y * im), inv * (g[i].z - a[i].z * im),
-                               inv * (g[i].w - a[i].w * im));
+        if (c < n4) {
+            float4 v = make_float4(inv * (g[i].x - a[i].x * im), inv * (g[i].y - a[i].y * im), inv * (g[i].z - a[i].z * im),
+                                   inv * (g[i].w - a[i].w * im));
+            if (ad) {
+                const float4 e = ad[c];
+                v.x += e.x; v.y += e.y; v.z += e.z; v.w += e.w;
+            }
+            o[c] = v;
+            if (o16) {
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+                o16[c] = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+            }
+        }
     }
 }
 
@@ -378,6 +392,26 @@ int asca_moe_combine(asca_ctx* ctx, const float* x_mid, const float* moe_out, fl
                      int64_t rows, int64_t cols, float eps) {
     return asca_residual_rmsnorm(ctx, x_mid, moe_out, x_out, xn_next, rows, cols, eps);
 }
+
+}  // extern "C"
+
+// dx = add + rmsnorm_bwd(x, dy) with a bf16 copy, one pass (the residual join of the backward: the gradient through the
+// norm meets the gradient of the skip branch). ASCA_ERR_UNSUPPORTED, nothing launched, when the rows do not fit the
+// warp-per-row kernel; add may be dx.
+int asca_rmsnorm_bwd_add_cast(asca_ctx* ctx, const float* x, const float* dy, const float* add, float* dx, void* dx16, int64_t rows,
+                              int64_t cols, float eps) {
+    if (!ctx) return ASCA_ERR_ARG;
+    if (!(warp_rows_ok(cols, x, dy) && warp_rows_ok(cols, dx, add)) || (reinterpret_cast<uintptr_t>(dx16) & 7)) return ASCA_ERR_UNSUPPORTED;
+    if (rows == 0) return ASCA_OK;
+    const unsigned grid = (unsigned)ceil_div64(rows, 8);
+#define ASCA_RN(NV_) rmsnorm_bwd_warp_kernel<NV_><<<grid, 256, 0, ctx->stream>>>(x, dy, dx, rows, (int)cols, eps, add, (__nv_bfloat16*)dx16)
+    if (cols <= 512) ASCA_RN(4); else if (cols <= 1024) ASCA_RN(8); else ASCA_RN(16);
+#undef ASCA_RN
+    ASCA_CHECK_LAUNCH(ctx);
+    return ASCA_OK;
+}
+
+extern "C" {
 
 int asca_rmsnorm_bwd(asca_ctx* ctx, const float* x, const float* dy, float* dx, int64_t rows, int64_t cols, float eps) {
     if (!ctx) return ASCA_ERR_ARG;

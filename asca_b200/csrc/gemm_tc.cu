@@ -65,6 +65,7 @@ struct KP {
     int64_t ldaux;
     __nv_bfloat16* C2;
     int64_t ldc2;
+    int c2_only;
     int* err_word;
 };
 
@@ -308,7 +309,7 @@ __global__ void __launch_bounds__(THREADS, Shape<BN, DEEP>::CTAS_PER_SM) gemm_tc
             float* cbase = p.C + (p.group_dim == GROUP_K ? (int64_t)x.g * p.c_gstride : 0);
             const int rows_here = x.M - (x.m0 + q * 32);   // live rows of this warp's quarter (may be <= 0 or > 32)
             // the common case gets straight-line code: full tile, plain f32 output (bias and accumulate allowed)
-            const bool fast = c_vec && !p.c_idx && !p.C2 && p.epi == EPI_NONE && rows_here >= 32 && x.n0 + BN <= p.N &&
+            const bool fast = c_vec && !p.c_idx && (!p.C2 || (p.c2_only && c2_vec)) && p.epi == EPI_NONE && rows_here >= 32 && x.n0 + BN <= p.N &&
                               (!p.bias || (((reinterpret_cast<uintptr_t>(p.bias) & 15) == 0) && (p.bias_gstride & 3) == 0));
             float* frow = cbase + ((int64_t)x.row_base_m + x.m0 + q * 32 + rsub) * p.ldc + x.n0 + 4 * l4;   // row rsub, this lane's columns
             const float* fbias = p.bias ? p.bias + (int64_t)x.g * p.bias_gstride + x.n0 + 4 * l4 : nullptr;
@@ -352,6 +353,18 @@ __global__ void __launch_bounds__(THREADS, Shape<BN, DEEP>::CTAS_PER_SM) gemm_tc
                             acc4[i] = stg[(8 * i + rsub) * 4 + (l4 ^ (((8 * i + rsub) >> 1) & 3))];
                             old4[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
                             if (p.accumulate) old4[i] = *reinterpret_cast<const float4*>(frow + (int64_t)(8 * i) * p.ldc + co);
+                        }
+                        if (p.c2_only) {   // bf16 is all the consumer reads
+                            __nv_bfloat16* hrow = p.C2 + ((int64_t)x.row_base_m + x.m0 + q * 32 + rsub) * p.ldc2 + x.n0 + 4 * l4 + co;
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const __nv_bfloat162 lo2 = __floats2bfloat162_rn(acc4[i].x + b4.x, acc4[i].y + b4.y),
+                                                     hi2 = __floats2bfloat162_rn(acc4[i].z + b4.z, acc4[i].w + b4.w);
+                                *reinterpret_cast<uint2*>(hrow + (int64_t)(8 * i) * p.ldc2) =
+                                    make_uint2(*reinterpret_cast<const uint32_t*>(&lo2), *reinterpret_cast<const uint32_t*>(&hi2));
+                            }
+                            __syncwarp();
+                            continue;
                         }
 #pragma unroll
                         for (int i = 0; i < 4; ++i)
@@ -410,7 +423,9 @@ __global__ void __launch_bounds__(THREADS, Shape<BN, DEEP>::CTAS_PER_SM) gemm_tc
                             }
                             v[0] += old4[i].x; v[1] += old4[i].y; v[2] += old4[i].z; v[3] += old4[i].w;
                             float* crow = cbase + crs[i] * p.ldc + nb;
-                            if (full4 && c_vec) {
+                            if (p.c2_only) {
+                                // bf16 output only
+                            } else if (full4 && c_vec) {
                                 *reinterpret_cast<float4*>(crow) = make_float4(v[0], v[1], v[2], v[3]);
                             } else {
 #pragma unroll
@@ -491,6 +506,7 @@ bool supported(const Args& a) {
     if (a.group_dim != GROUP_NONE && a.n_groups > MAX_GROUPS) return false;
     if (a.group_dim == GROUP_K && a.mode != ASCA_TN) return false;
     if (a.group_dim == GROUP_M && a.mode == ASCA_TN) return false;
+    if (a.c2_only && (!a.C2 || a.accumulate || a.epi != EPI_NONE || a.c_idx || skinny_wanted(a))) return false;
     if ((a.c2_mapped || a.b_packed) && !skinny_wanted(a)) return false;
     return true;
 }
@@ -510,7 +526,7 @@ static int launch_shape(asca_ctx* ctx, const Args& a, int64_t grid) {
     p.offsets = a.offsets; p.n_groups = a.n_groups; p.group_dim = a.group_dim;
     p.b_goff_inner = a.b_goff_inner; p.b_goff_outer = a.b_goff_outer;
     p.c_gstride = a.c_gstride; p.bias_gstride = a.bias_gstride;
-    p.epi = a.epi; p.aux = a.aux; p.ldaux = a.ldaux; p.C2 = a.C2; p.ldc2 = a.ldc2;
+    p.epi = a.epi; p.aux = a.aux; p.ldaux = a.ldaux; p.C2 = a.C2; p.ldc2 = a.ldc2; p.c2_only = a.c2_only;
     p.err_word = ctx->err_word;
     const size_t smem = Shape<BN, DEEP>::SMEM_FIXED + (size_t)((a.group_dim == GROUP_NONE ? 1 : a.n_groups) + 2) * 4;
     auto go = [&](auto kern) -> cudaError_t {

@@ -34,6 +34,7 @@ struct Args {
     int64_t ldaux;
     __nv_bfloat16* C2;        // EPI_SILU: silu(C); EPI_SILU_BWD: bf16 copy of C; nullable
     int64_t ldc2;
+    int c2_only;              // row-tiled kernel, EPI_NONE, no accumulate: the result is wanted as bf16 only (C is not written)
     int c2_mapped;            // few-row kernel only: C2's rows go through c_idx like C's
     int b_packed;             // few-row kernel only: B is a buffer made by skinny_pack (b_rows = its rows of 64)
     int b_early;              // few-row kernel only: B and the group offsets were written before the PREVIOUS kernel on

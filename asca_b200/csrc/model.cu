@@ -346,6 +346,10 @@ static int refresh_params16(asca_ctx* ctx, asca_model* m) {
 // once, products on the tensor cores from the bf16 weight copy, the expert FFN through the dispatch + grouped
 // GEMM path (every expert's weights are read once per step, not once per stream); state, residual stream and
 // logits stay f32.
+bool asca_tc_enabled();  // gemm.cu
+// elementwise.cu
+int asca_rmsnorm_bwd_add_cast(asca_ctx* ctx, const float* x, const float* dy, const float* add, float* dx, void* dx16, int64_t rows,
+                              int64_t cols, float eps);
 // moe.cu / mixed.cu: the decode-step forms on rows in expert order
 int asca_moe_fwd_sorted_residual(asca_ctx* ctx, const __nv_bfloat16* xp, const __nv_bfloat16* w1, const float* b1,
                                  const __nv_bfloat16* w2, const float* b2, const int32_t* perm, const int32_t* offsets, int64_t N,
@@ -641,17 +645,34 @@ static int forward_backward_bf16(asca_ctx* ctx, asca_model* m, const uint32_t* i
         Act& a = acts[li];
         ASCA_TRY((acc ? asca_moe_bwd_acc : asca_moe_bwd)(ctx, a.xn, W + w16.w1, W + w16.w2, a.pre_p, a.hid_p, dx, perm, offs, N, d, F, E, BF, G + w.w1,
                                   G + w.b1, G + w.w2, G + w.b2, dxn));
-        ASCA_TRY(asca_rmsnorm_bwd(ctx, a.x_mid, dxn, d_moe, N, d, 1e-6f));
-        if (vec4) {   // d_mid = dx + d_moe, with its bf16 copy
+        // d_mid = dx + rmsnorm_bwd(x_mid, dxn), with its bf16 copy: one pass where the rows fit the warp kernel
+        const int rc_join = asca_rmsnorm_bwd_add_cast(ctx, a.x_mid, dxn, dx, dx, dx16, N, d, 1e-6f);
+        if (rc_join != ASCA_ERR_UNSUPPORTED) {
+            ASCA_TRY(rc_join);
+        } else if (vec4) {
+            ASCA_TRY(asca_rmsnorm_bwd(ctx, a.x_mid, dxn, d_moe, N, d, 1e-6f));
             add_cast4_kernel<<<add_grid, 256, 0, ctx->stream>>>(dx, d_moe, dx, dx16, N * d / 4);
             ASCA_CHECK_LAUNCH(ctx);
         } else {
+            ASCA_TRY(asca_rmsnorm_bwd(ctx, a.x_mid, dxn, d_moe, N, d, 1e-6f));
             add_kernel<<<(unsigned)blocks_nd, 256, 0, ctx->stream>>>(dx, d_moe, dx, N * d);
             ctx->launches++;
             ASCA_TRY(asca_cast_bf16(ctx, dx, dx16, N * d));
         }
-        ASCA_TRY(asca_gemm(ctx, ASCA_NT, N, d, d, dx16, d, W + w16.w_o, d, d_o, d, nullptr, 0, BF));
-        ASCA_TRY(asca_cast_bf16(ctx, d_o, do16, N * d));
+        {   // d_o = d_mid Wo^T, wanted as bf16 only (the delta backward's input)
+            gemm_tc::Args t{};
+            t.mode = ASCA_NT; t.A = dx16; t.lda = d; t.a_rows = N; t.a_cols = d;
+            t.B = W + w16.w_o; t.ldb = d; t.b_rows = d; t.b_cols = d;
+            t.C = d_o; t.ldc = d; t.M = (int)N; t.N = (int)d; t.K = (int)d;
+            t.group_dim = gemm_tc::GROUP_NONE; t.epi = gemm_tc::EPI_NONE;
+            t.C2 = do16; t.ldc2 = d; t.c2_only = 1;
+            if (asca_tc_enabled() && gemm_tc::supported(t)) {
+                ASCA_TRY(gemm_tc::launch(ctx, t));
+            } else {
+                ASCA_TRY(asca_gemm(ctx, ASCA_NT, N, d, d, dx16, d, W + w16.w_o, d, d_o, d, nullptr, 0, BF));
+                ASCA_TRY(asca_cast_bf16(ctx, d_o, do16, N * d));
+            }
+        }
         ASCA_TRY(asca_gemm(ctx, ASCA_TN, d, d, N, a.o, d, dx16, d, G + w.w_o, d, nullptr, acc, BF));
         ASCA_TRY(asca_colsum(ctx, dx, d, N, d, G + w.b_o, acc));
         ASCA_TRY(asca_delta_bwd(ctx, a.q, a.k, a.v, a.al, a.be, a.qn, a.kn, do16, a.ckpt, B, T, H, dh, CH, BF, d_qkv, d_gate));
