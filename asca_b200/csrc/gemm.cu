@@ -3,6 +3,8 @@
 #include "gemm_simt.cuh"
 #include "gemm_tc.cuh"
 
+#include <algorithm>
+
 #include <cstdlib>
 
 // ASCA_B200_NO_TC=1 keeps bf16 problems on the SIMT kernel (A/B comparisons).
@@ -14,6 +16,70 @@ bool asca_tc_enabled() {
     }
     return v == 1;
 }
+
+namespace {
+
+__global__ void splitk_offsets_kernel(int32_t* offs, int n_split, int chunk, int K) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i <= n_split) offs[i] = min(i * chunk, K);
+}
+// C = (accumulate ? C : 0) + bias + sum over the k-slices' partial products, slices added in order
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ part, int n_split, int64_t mn, int N, float* __restrict__ C,
+                                                            int64_t ldc, const float* __restrict__ bias, int accumulate) {
+    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= mn) return;
+    const int64_t r = i / N;
+    const int c = (int)(i % N);
+    float acc = 0.0f;
+    for (int s = 0; s < n_split; ++s) acc += part[(int64_t)s * mn + i];
+    if (bias) acc += bias[c];
+    float* dst = C + r * ldc + c;
+    *dst = accumulate ? *dst + acc : acc;
+}
+
+// A^T B with few output tiles and a very long k (a weight gradient over all tokens of a micro-batch for a narrow
+// layer: the gates, the head): the k range is cut into slices that run as the groups of the kernel's grouped-k
+// form into a scratch buffer, and a second pass adds the slices in order. Returns ASCA_ERR_UNSUPPORTED when the
+// shape does not call for it.
+int gemm_tn_split_k(asca_ctx* ctx, gemm_tc::Args t) {
+    const int n_sm = ctx->sm_count > 0 ? ctx->sm_count : 148;
+    const int64_t tiles = ((int64_t)(t.M + 127) / 128) * ((t.N + 127) / 128);
+    if (t.mode != ASCA_TN || tiles * 4 > n_sm || t.K < 16384) return ASCA_ERR_UNSUPPORTED;
+    int n_split = (int)std::min<int64_t>(2 * n_sm / tiles, t.K / 4096);
+    if (n_split < 2) return ASCA_ERR_UNSUPPORTED;
+    const int chunk = (int)(((t.K + n_split - 1) / n_split + 63) / 64 * 64);
+    n_split = (t.K + chunk - 1) / chunk;
+    const int64_t mn = (int64_t)t.M * t.N;
+    void *part = nullptr, *offs = nullptr;
+    ASCA_TRY(asca_malloc(ctx, (size_t)n_split * mn * 4, &part));
+    if (asca_malloc(ctx, (size_t)(n_split + 1) * 4, &offs) != ASCA_OK) {
+        asca_free(ctx, part);
+        return ASCA_ERR_OOM;
+    }
+    float* C = t.C;
+    const int64_t ldc = t.ldc;
+    const float* bias = t.bias;
+    const int accumulate = t.accumulate;
+    t.C = (float*)part; t.ldc = t.N; t.bias = nullptr; t.accumulate = 0;
+    t.group_dim = gemm_tc::GROUP_K; t.offsets = (const int32_t*)offs; t.n_groups = n_split; t.total_rows = t.K;
+    t.c_gstride = mn;
+    int rc = gemm_tc::supported(t) ? ASCA_OK : ASCA_ERR_UNSUPPORTED;
+    if (rc == ASCA_OK) {
+        splitk_offsets_kernel<<<1, 256, 0, ctx->stream>>>((int32_t*)offs, n_split, chunk, t.K);
+        ctx->launches++;
+        rc = gemm_tc::launch(ctx, t);
+    }
+    if (rc == ASCA_OK) {
+        splitk_reduce_kernel<<<(unsigned)((mn + 255) / 256), 256, 0, ctx->stream>>>((const float*)part, n_split, mn, t.N, C, ldc, bias, accumulate);
+        ctx->launches++;
+        if (cudaGetLastError() != cudaSuccess) rc = ASCA_ERR_CUDA;
+    }
+    asca_free(ctx, offs);
+    asca_free(ctx, part);
+    return rc;
+}
+
+}  // namespace
 
 extern "C" {
 
@@ -36,7 +102,11 @@ int asca_gemm(asca_ctx* ctx, int mode, int64_t M, int64_t N, int64_t K, const vo
         t.C = (float*)C; t.ldc = ldc; t.M = (int)M; t.N = (int)N; t.K = (int)K;
         t.bias = bias; t.accumulate = accumulate;
         t.group_dim = gemm_tc::GROUP_NONE; t.epi = gemm_tc::EPI_NONE;
-        if (gemm_tc::supported(t)) return gemm_tc::launch(ctx, t);
+        if (gemm_tc::supported(t)) {
+            const int rc = gemm_tn_split_k(ctx, t);
+            if (rc != ASCA_ERR_UNSUPPORTED) return rc;
+            return gemm_tc::launch(ctx, t);
+        }
     }
     gemm::Params p{};
     p.A = A; p.B = B; p.C = (float*)C;

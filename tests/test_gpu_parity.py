@@ -566,6 +566,28 @@ def test_moe_bf16_tensor_core_ragged_experts(orc, gpu, n, d, F, E, vocab):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("m,k,n", [(256, 20000, 32), (128, 16384, 264), (72, 40008, 8)])
+def test_bf16_weight_gradient_with_few_tiles_and_long_k(orc, gpu, m, k, n):
+    """A^T B over tens of thousands of rows into a narrow output (the gate and head weight gradients): the k range
+    is cut into slices and the slices are added in order; plain, and accumulating onto an existing C."""
+    import torch
+    from asca_b200 import ops, TN
+
+    rng = orc.Rng(m + k + n)
+    a, b, c0 = rng.normal((k, m)), rng.normal((k, n)), rng.normal((m, n))
+    a16, b16 = torch.from_numpy(a).cuda().bfloat16(), torch.from_numpy(b).cuda().bfloat16()
+    ref = a16.float().cpu().numpy().astype(np.float64).T @ b16.float().cpu().numpy().astype(np.float64)
+    got = ops.gemm(gpu, a16, b16, TN)
+    out = torch.from_numpy(c0.copy()).cuda()
+    ops.gemm(gpu, a16, b16, TN, out=out, accumulate=True)
+    again = ops.gemm(gpu, a16, b16, TN)
+    gpu.sync()
+    assert rel_err(got.cpu().numpy(), ref) < 1e-5
+    assert rel_err(out.cpu().numpy(), ref + c0) < 1e-5
+    assert torch.equal(got, again)      # fixed order of the slices: run-to-run identical
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("m,k,n", [(1, 64, 128), (17, 768, 2328), (32, 200, 136), (33, 72, 8), (64, 3072, 768), (200, 96, 264),
                                    (256, 768, 768)])
 def test_bf16_few_row_gemm(orc, gpu, m, k, n):
