@@ -209,6 +209,18 @@ __global__ void __launch_bounds__(256) decode_prologue_kernel(const float* __res
         inv_perm[i] = pos;
     }
 }
+// dst[r, 0:cols] (bf16, row pitch ld_dst) = src[r, 0:cols] (f32, contiguous rows); cols % 4 == 0
+__global__ void __launch_bounds__(256) cast_cols_kernel(const float* __restrict__ src, int cols4, int64_t n4, __nv_bfloat16* __restrict__ dst,
+                                                        int64_t ld_dst) {
+    const int64_t stride = (int64_t)gridDim.x * 256;
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n4; i += stride) {
+        const int64_t r = i / cols4;
+        const int c = (int)(i % cols4);
+        const float4 v = reinterpret_cast<const float4*>(src)[i];
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+        *reinterpret_cast<uint2*>(dst + r * ld_dst + 4 * c) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+    }
+}
 // inv[perm[i]] = i
 __global__ void __launch_bounds__(256) invert_perm_kernel(const int32_t* __restrict__ perm, int32_t* __restrict__ inv, int64_t n) {
     const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
@@ -358,6 +370,33 @@ int asca_moe_fwd_sorted_residual(asca_ctx* ctx, const __nv_bfloat16* xp, const _
 int asca_residual_rmsnorm_bf16_rows(asca_ctx* ctx, const float* x, const float* yadd, float* x_mid, void* xn, int64_t rows,
                                     int64_t cols, float eps, const int32_t* y_row);
 
+// The qkv and gate projections of every block as one (d, 3d + 2H rounded up to 8) bf16 matrix, and their biases:
+// one product instead of two wherever both read the same rows (the decode step; the input gradient of the block).
+static int refresh_dec_w(asca_ctx* ctx, asca_model* m) {
+    const int64_t d = m->d, H = m->H, ldq = (3 * d + 2 * H + 7) & ~(int64_t)7;
+    const float* P = m->params;
+    if (!m->dec_w) {
+        if (cudaMalloc((void**)&m->dec_w, (size_t)m->L * d * ldq * 2) != cudaSuccess ||
+            cudaMalloc((void**)&m->dec_b, (size_t)m->L * ldq * 4) != cudaSuccess)
+            return asca_fail(ctx, ASCA_ERR_OOM, "model: cannot allocate the fused qkv + gate projection");
+        m->dec_stale = true;
+        m->dec_pk_stale = true;
+    }
+    if (m->dec_stale) {
+        for (int64_t li = 0; li < m->L; ++li) {
+            const Lyr& w = m->lay[li];
+            concat_cols_kernel<<<(unsigned)ceil_div64(d * ldq, 256), 256, 0, ctx->stream>>>(
+                P + w.w_qkv, (int)(3 * d), P + w.w_gate, (int)(2 * H), d, (int)ldq, m->dec_w + li * d * ldq);
+            concat_bias_kernel<<<(unsigned)ceil_div64(ldq, 256), 256, 0, ctx->stream>>>(P + w.b_qkv, (int)(3 * d), P + w.b_gate,
+                                                                                     (int)(2 * H), (int)ldq, m->dec_b + li * ldq);
+            ctx->launches += 2;
+        }
+        ASCA_CUDA(ctx, cudaGetLastError());
+        m->dec_stale = false;
+    }
+    return ASCA_OK;
+}
+
 // n_steps steps in bf16 mode. Step 0 consumes ids_h; a later step consumes the previous step's argmax, which never
 // leaves the device (tokens_h, n_steps x ns, receives all of them after the last step). One synchronisation at the end.
 static int decode_step_bf16(asca_ctx* ctx, asca_model* m, float* state, const uint32_t* ids_h, int64_t ns, float* logits_h,
@@ -382,27 +421,7 @@ static int decode_step_bf16(asca_ctx* ctx, asca_model* m, float* state, const ui
     ASCA_CUDA(ctx, cudaMemcpyAsync(ids, ids_h, (size_t)ns * 4, cudaMemcpyHostToDevice, ctx->stream));
     const bool fused64 = dh == 64;   // one projection for qkv + gate, the warp-per-head state update, casts folded in
     const int64_t ldq = (3 * d + 2 * H + 7) & ~(int64_t)7;
-    if (fused64) {
-        if (!m->dec_w) {
-            if (cudaMalloc((void**)&m->dec_w, (size_t)m->L * d * ldq * 2) != cudaSuccess ||
-                cudaMalloc((void**)&m->dec_b, (size_t)m->L * ldq * 4) != cudaSuccess)
-                return asca_fail(ctx, ASCA_ERR_OOM, "model: cannot allocate the fused decode projection");
-            m->dec_stale = true;
-            m->dec_pk_stale = true;
-        }
-        if (m->dec_stale) {
-            for (int64_t li = 0; li < m->L; ++li) {
-                const Lyr& w = m->lay[li];
-                concat_cols_kernel<<<(unsigned)ceil_div64(d * ldq, 256), 256, 0, ctx->stream>>>(
-                    P + w.w_qkv, (int)(3 * d), P + w.w_gate, (int)(2 * H), d, (int)ldq, m->dec_w + li * d * ldq);
-                concat_bias_kernel<<<(unsigned)ceil_div64(ldq, 256), 256, 0, ctx->stream>>>(P + w.b_qkv, (int)(3 * d), P + w.b_gate,
-                                                                                         (int)(2 * H), (int)ldq, m->dec_b + li * ldq);
-                ctx->launches += 2;
-            }
-            ASCA_CUDA(ctx, cudaGetLastError());
-            m->dec_stale = false;
-        }
-    }
+    if (fused64) ASCA_TRY(refresh_dec_w(ctx, m));
     float* qg = fused64 ? bf.f(ns * ldq) : nullptr;
     ASCA_REQUIRE(ctx, !fused64 || qg, "model_decode_step: out of memory");
     // With a handful of tokens per expert the MoE runs on rows in expert order end to end: the norm writes its bf16
@@ -632,8 +651,14 @@ static int forward_backward_bf16(asca_ctx* ctx, asca_model* m, const uint32_t* i
     float* d_gate = bf.f(N * 2 * H);
     bf16* dx16 = h16(N * d);
     bf16* do16 = h16(N * d);
-    bf16* dqkv16 = h16(N * 3 * d);
-    bf16* dg16 = h16(N * 2 * H);
+    // d_qkv and d_gate side by side as bf16 (row pitch ldq) when that needs no padding: their input gradient is then one
+    // product with the concatenated projection instead of two passes over dx
+    const int64_t ldq = 3 * d + 2 * H;
+    const bool cat = (ldq & 7) == 0 && (d & 3) == 0 && ((2 * H) & 3) == 0;
+    if (cat) ASCA_TRY(refresh_dec_w(ctx, m));
+    bf16* dqkv16 = cat ? h16(N * ldq) : h16(N * 3 * d);
+    bf16* dg16 = cat ? dqkv16 + 3 * d : h16(N * 2 * H);
+    const int64_t ld_dq = cat ? ldq : 3 * d, ld_dg = cat ? ldq : 2 * H;
     ASCA_REQUIRE(ctx, dh_ && dx && dxn && d_moe && d_o && d_qkv && d_gate && dx16 && do16 && dqkv16 && dg16,
                  "model_forward_backward: out of memory");
     ASCA_TRY(asca_gemm(ctx, ASCA_NT, N, d, V, dl16, V, W + m->head16, V, dh_, d, nullptr, 0, BF));
@@ -676,14 +701,26 @@ static int forward_backward_bf16(asca_ctx* ctx, asca_model* m, const uint32_t* i
         ASCA_TRY(asca_gemm(ctx, ASCA_TN, d, d, N, a.o, d, dx16, d, G + w.w_o, d, nullptr, acc, BF));
         ASCA_TRY(asca_colsum(ctx, dx, d, N, d, G + w.b_o, acc));
         ASCA_TRY(asca_delta_bwd(ctx, a.q, a.k, a.v, a.al, a.be, a.qn, a.kn, do16, a.ckpt, B, T, H, dh, CH, BF, d_qkv, d_gate));
-        ASCA_TRY(asca_cast_bf16(ctx, d_qkv, dqkv16, N * 3 * d));
-        ASCA_TRY(asca_cast_bf16(ctx, d_gate, dg16, N * 2 * H));
-        ASCA_TRY(asca_gemm(ctx, ASCA_TN, d, 3 * d, N, a.x_in, d, dqkv16, 3 * d, G + w.w_qkv, 3 * d, nullptr, acc, BF));
+        if (cat) {
+            cast_cols_kernel<<<add_grid, 256, 0, ctx->stream>>>(d_qkv, (int)(3 * d / 4), N * 3 * d / 4, dqkv16, ldq);
+            cast_cols_kernel<<<(unsigned)std::min<int64_t>(ceil_div64(N * 2 * H / 4, 256), 148 * 16), 256, 0, ctx->stream>>>(
+                d_gate, (int)(2 * H / 4), N * 2 * H / 4, dg16, ldq);
+            ctx->launches += 2;
+            ASCA_CUDA(ctx, cudaGetLastError());
+        } else {
+            ASCA_TRY(asca_cast_bf16(ctx, d_qkv, dqkv16, N * 3 * d));
+            ASCA_TRY(asca_cast_bf16(ctx, d_gate, dg16, N * 2 * H));
+        }
+        ASCA_TRY(asca_gemm(ctx, ASCA_TN, d, 3 * d, N, a.x_in, d, dqkv16, ld_dq, G + w.w_qkv, 3 * d, nullptr, acc, BF));
         ASCA_TRY(asca_colsum(ctx, d_qkv, 3 * d, N, 3 * d, G + w.b_qkv, acc));
-        ASCA_TRY(asca_gemm(ctx, ASCA_TN, d, 2 * H, N, a.x_in, d, dg16, 2 * H, G + w.w_gate, 2 * H, nullptr, acc, BF));
+        ASCA_TRY(asca_gemm(ctx, ASCA_TN, d, 2 * H, N, a.x_in, d, dg16, ld_dg, G + w.w_gate, 2 * H, nullptr, acc, BF));
         ASCA_TRY(asca_colsum(ctx, d_gate, 2 * H, N, 2 * H, G + w.b_gate, acc));
-        ASCA_TRY(asca_gemm(ctx, ASCA_NT, N, d, 3 * d, dqkv16, 3 * d, W + w16.w_qkv, 3 * d, dx, d, nullptr, 1, BF));
-        ASCA_TRY(asca_gemm(ctx, ASCA_NT, N, d, 2 * H, dg16, 2 * H, W + w16.w_gate, 2 * H, dx, d, nullptr, 1, BF));
+        if (cat) {   // dx += [d_qkv | d_gate] [W_qkv | W_gate]^T
+            ASCA_TRY(asca_gemm(ctx, ASCA_NT, N, d, ldq, dqkv16, ldq, m->dec_w + li * d * ldq, ldq, dx, d, nullptr, 1, BF));
+        } else {
+            ASCA_TRY(asca_gemm(ctx, ASCA_NT, N, d, 3 * d, dqkv16, 3 * d, W + w16.w_qkv, 3 * d, dx, d, nullptr, 1, BF));
+            ASCA_TRY(asca_gemm(ctx, ASCA_NT, N, d, 2 * H, dg16, 2 * H, W + w16.w_gate, 2 * H, dx, d, nullptr, 1, BF));
+        }
         if (m->grad_hook) m->grad_hook(m->grad_hook_user, w.w_qkv, (li + 1 < L ? m->lay[li + 1].w_qkv : m->n_params) - w.w_qkv);
     }
     if (!acc) ASCA_CUDA(ctx, cudaMemsetAsync(G + m->embed, 0, (size_t)V * d * 4, ctx->stream));

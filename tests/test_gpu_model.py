@@ -90,12 +90,13 @@ def test_config1_greedy_decode_matches_oracle(orc, gpu):
     dev.free()
 
 
-def test_bf16_compute_train_step_within_tolerance(orc, gpu):
+@pytest.mark.parametrize("cfg", [(256, 256, 2, 2, 4, 256), (256, 512, 4, 1, 4, 256)])
+def test_bf16_compute_train_step_within_tolerance(orc, gpu, cfg):
     """bf16 compute mode (tensor-core GEMMs, delta kernels and expert FFN; head dim 128) against the
-    f32 CPU oracle on the same weights and tokens: loss, logits and every gradient within 2e-2."""
+    f32 CPU oracle on the same weights and tokens: loss, logits and every gradient within 2e-2. The second
+    configuration has 3 d + 2 H a multiple of 8: d_qkv and d_gate share one bf16 buffer and one input-gradient product."""
     import asca_b200
 
-    cfg = (256, 256, 2, 2, 4, 256)
     ref = orc.Model(*cfg)
     ref.init_reference(orc.Rng(3))
     dev = asca_b200.Model(gpu, *cfg)
