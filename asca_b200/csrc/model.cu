@@ -1079,6 +1079,62 @@ int asca_model_adamw_step(asca_ctx* ctx, asca_model* m, float lr, float beta1, f
                                      beta1, beta2, lr * wd, fuse ? (void*)m->params16 : nullptr);
 }
 
+// One optimizer step restricted to n sorted, disjoint slices [lo[i], hi[i]) of the flat buffer (a rank's share under a
+// sharded optimizer: its parts of the large tensors, and whatever small tensors every rank updates). Every tensor gets
+// the step number asca_model_adamw_step would give it; the counter advances as for a full step. bf16 mode with an
+// unpadded bf16 copy only (the update writes that copy for the slices; the caller exchanges the rest).
+int asca_model_adamw_slices(asca_ctx* ctx, asca_model* m, float lr, float beta1, float beta2, float eps, float wd, const int64_t* lo,
+                            const int64_t* hi, int n) {
+    if (!ctx || !m) return ASCA_ERR_ARG;
+    ASCA_REQUIRE(ctx, lo && hi && n > 0, "model_adamw_slices: bad arguments");
+    ASCA_REQUIRE(ctx, m->compute == ASCA_BF16 && m->params16 && m->n16 == m->n_params,
+                 "model_adamw_slices: needs bf16 compute mode with an unpadded bf16 weight copy");
+    ASCA_TRY(materialize_zero_grads(ctx, m));
+    ASCA_TRY(refresh_params16(ctx, m));
+    const int n_seg = (int)m->seg_off.size() - 1;
+    auto powi = [](float b, int e) {
+        float r = 1.0f, x = b;
+        while (e > 0) {
+            if (e & 1) r *= x;
+            x *= x;
+            e >>= 1;
+        }
+        return r;
+    };
+    int64_t prev = 0;
+    for (int s = 0; s < n; ++s) {
+        ASCA_REQUIRE(ctx, lo[s] >= prev && hi[s] > lo[s] && hi[s] <= m->n_params && (lo[s] & 3) == 0,
+                     "model_adamw_slices: slices must be sorted, disjoint, inside the buffer and start at multiples of 4");
+        prev = hi[s];
+        std::vector<int64_t> off{0};
+        std::vector<float> lr_t, eps_t;
+        for (int i = 0; i < n_seg; ++i) {
+            const int64_t a = std::max(lo[s], m->seg_off[i]), b = std::min(hi[s], m->seg_off[i + 1]);
+            if (a >= b) continue;
+            const int t = (int)(m->adam_counter + (uint32_t)i + 1u);
+            const float bc1 = 1.0f - powi(beta1, t), bc2 = 1.0f - powi(beta2, t);
+            off.push_back(b - lo[s]);
+            lr_t.push_back(lr * sqrtf(bc1 / bc2));
+            eps_t.push_back(eps * sqrtf(bc2));
+        }
+        ASCA_TRY(asca_adamw_segmented_cast(ctx, m->params + lo[s], m->grads + lo[s], m->m + lo[s], m->v + lo[s], off.data(), lr_t.data(),
+                                           eps_t.data(), (int)lr_t.size(), beta1, beta2, lr * wd, m->params16 + lo[s]));
+    }
+    m->adam_counter += (uint32_t)n_seg;
+    m->dec_stale = true;
+    m->dec_pk_stale = true;
+    return ASCA_OK;
+}
+
+// Device address of the bf16 weight copy (bf16 compute mode; same element offsets as the f32 buffer when unpadded).
+int asca_model_params16(asca_ctx* ctx, asca_model* m, void** out, int64_t* n16) {
+    if (!ctx || !m || !out) return ASCA_ERR_ARG;
+    ASCA_TRY(refresh_params16(ctx, m));
+    *out = m->params16;
+    if (n16) *n16 = m->n16;
+    return ASCA_OK;
+}
+
 int asca_model_decode_greedy_host(asca_ctx* ctx, asca_model* m, float* state, const uint32_t* ids_h, int64_t ns, int64_t n_steps,
                                   uint32_t* tokens_h) {
     if (!ctx || !m) return ASCA_ERR_ARG;

@@ -13,7 +13,10 @@ sequence over the ranks; each rank runs its share as micro-batches of at most --
 gradient accumulation (the larger the micro-batch, the fewer passes over the 4.4 GB of expert weight
 gradients per block: 8 -> 32 sequences is worth 13 % of the step), the flat gradient buffer is averaged over ranks by NCCL all-reduce queued
 block by block from inside the last backward (asca_b200.dp.GradOverlap), then every rank applies the
-same AdamW update. One JSON line from rank 0.
+same AdamW update (--optimizer replicated). Default at N > 1 (--optimizer sharded, dp.ShardedOverlap): the
+experts' W1 / W2 gradients are reduce-scattered instead, each rank updates its 1/N chunk of them (and all
+small tensors), and the updated bf16 chunks are all-gathered; --verify runs two steps both ways and checks
+that the weights are identical. One JSON line from rank 0.
 """
 from __future__ import annotations
 
@@ -36,6 +39,9 @@ def main():
     ap.add_argument("--global-batch", type=int, default=64)
     ap.add_argument("--micro", type=int, default=32, help="sequences per micro-batch (at most the rank's share)")
     ap.add_argument("--seq", type=int, default=4096)
+    ap.add_argument("--optimizer", default="sharded", choices=["sharded", "replicated"],
+                    help="sharded: expert weights reduce-scattered, updated 1/N per rank, bf16 all-gathered (N > 1)")
+    ap.add_argument("--verify", action="store_true", help="N > 1: run two steps with both optimizers and compare the weights")
     ap.add_argument("--steps", type=int, default=3)
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -66,7 +72,8 @@ def main():
     tg = ids.copy()
     tg[:, :-1] = ids[:, 1:]
     model.set_grad_scale(1.0 / n_micro)
-    overlap = dp.GradOverlap(model)
+    sharded = args.optimizer == "sharded" and world > 1
+    overlap = dp.ShardedOverlap(model) if sharded else dp.GradOverlap(model)
 
     def step():
         model.zero_grads()
@@ -81,8 +88,12 @@ def main():
                 loss += model.forward_backward(ids[rows].reshape(-1), tg[rows].reshape(-1), mb)
         torch.cuda.synchronize()
         t1 = time.perf_counter()
-        model.adamw_step(3e-4)
+        if sharded:
+            overlap.step(3e-4)       # sliced AdamW + all-gather of the bf16 expert chunks
+        else:
+            model.adamw_step(3e-4)
         gpu.sync()
+        torch.cuda.synchronize()
         t2 = time.perf_counter()
         return loss / n_micro, t1 - t0, t2 - t1
 
@@ -91,6 +102,41 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    if args.verify and world > 1:
+        # the same two steps with the replicated optimizer on a second model: the bf16 weights every rank computes
+        # with must be identical, and so must this rank's slices of the f32 master weights
+        other = asca_b200.Model(gpu, V, d, H, L, E, F)
+        other.set_compute(asca_b200.BF16)
+        po = dp.device_tensor(other.buffers()[0], other.n, local)
+        po.copy_(params)
+        other.params_changed()
+        other.set_grad_scale(1.0 / n_micro)
+        ov_s, ov_r = dp.ShardedOverlap(model), dp.GradOverlap(other)
+        for _ in range(2):
+            for mdl, ov in ((model, ov_s), (other, ov_r)):
+                mdl.zero_grads()
+                for i in range(n_micro):
+                    rows = slice(i * mb, (i + 1) * mb)
+                    if i == n_micro - 1:
+                        with ov:
+                            mdl.forward_backward(ids[rows].reshape(-1), tg[rows].reshape(-1), mb)
+                    else:
+                        mdl.forward_backward(ids[rows].reshape(-1), tg[rows].reshape(-1), mb)
+            ov_s.step(3e-4)
+            other.adamw_step(3e-4)
+        torch.cuda.synchronize()
+        a16 = dp.device_tensor_bf16(*model.params16(), local)
+        b16 = dp.device_tensor_bf16(*other.params16(), local)
+        same16 = bool(torch.equal(a16, b16))
+        same32 = all(bool(torch.equal(params[lo:hi], po[lo:hi])) for lo, hi in ov_s.slices)
+        ov_s.gather_master()
+        same_all = bool(torch.equal(params, po))
+        print(json.dumps({"verify": "sharded vs replicated optimizer, 2 steps", "rank": rank, "bf16_weights_equal": same16,
+                          "own_master_slices_equal": same32, "master_equal_after_gather": same_all}), flush=True)
+        other.free()
+        model.free()
+        dist.destroy_process_group()
+        return
     step()          # warms the pools and NCCL up
     barrier()
     t_fb = t_opt = 0.0
@@ -118,7 +164,7 @@ def main():
             "tok_s": round(n_tok / wall, 1), "algorithmic_flop_per_token": flop_tok,
             "TFLOP/s_per_gpu": round(n_tok * flop_tok / wall / 1e12 / world, 1),
             "frac_of_bf16_peak_per_gpu": round(n_tok * flop_tok / wall / 1e12 / world / tf, 4), "peak": src,
-            "scaling": "strong (global batch fixed)"}), flush=True)
+            "optimizer": "sharded" if sharded else "replicated", "scaling": "strong (global batch fixed)"}), flush=True)
     model.free()
     if world > 1:
         dist.destroy_process_group()
