@@ -116,3 +116,26 @@ def test_data_windows_use_the_reference_offsets(orc):
     assert np.array_equal(ids, data.tokens[start:start + 64])
     with pytest.raises(ValueError):
         train.Data.from_bytes(b"short")
+
+
+def test_shard_plan_partitions_the_expert_weights_and_keeps_the_rest_everywhere():
+    """dp.shard_plan: over all ranks the chunks of every sharded tensor tile it exactly once, every other element is in
+    every rank's slices, slices are sorted, disjoint and start at multiples of 4."""
+    from asca_b200.dp import shard_plan
+    from asca_b200.train import tensor_sizes
+
+    cfg = (256, 64, 4, 2, 4, 256)
+    n = sum(tensor_sizes(cfg))
+    for world in (1, 2, 4, 8):
+        cover = np.zeros(n, np.int32)
+        for rank in range(world):
+            big, slices = shard_plan(cfg, rank, world)
+            assert all(lo % 4 == 0 and hi > lo for lo, hi in slices)
+            assert all(a[1] < b[0] for a, b in zip(slices, slices[1:]))          # sorted, disjoint, merged
+            for lo, hi in slices:
+                cover[lo:hi] += 1
+        sharded = np.zeros(n, bool)
+        for lo, size in big:
+            sharded[lo:lo + size] = True
+        assert (cover[sharded] == 1).all() and (cover[~sharded] == world).all()
+        assert len(big) == (0 if world == 1 else 2 * cfg[3])                        # W1 and W2 of every block
