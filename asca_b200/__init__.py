@@ -407,12 +407,12 @@ class Model:
     def adamw_step(self, lr, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.01):
         self.gpu._call("asca_model_adamw_step", self.gpu._ctx, self._h, _f(lr), _f(beta1), _f(beta2), _f(eps), _f(wd))
 
-    def adamw_slices(self, lr, slices, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.01):
+    def adamw_slices(self, lr, slices, advance=True, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.01):
         """One optimizer step restricted to the sorted, disjoint (lo, hi) slices of the flat buffer (bf16 mode)."""
         lo = np.ascontiguousarray([s[0] for s in slices], dtype=np.int64)
         hi = np.ascontiguousarray([s[1] for s in slices], dtype=np.int64)
         self.gpu._call("asca_model_adamw_slices", self.gpu._ctx, self._h, _f(lr), _f(beta1), _f(beta2), _f(eps), _f(wd), _p(lo), _p(hi),
-                       C.c_int(len(slices)))
+                       C.c_int(len(slices)), C.c_int(1 if advance else 0))
 
     def params16(self):
         """(device address, element count) of the bf16 weight copy."""

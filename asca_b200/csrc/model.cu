@@ -1081,10 +1081,11 @@ int asca_model_adamw_step(asca_ctx* ctx, asca_model* m, float lr, float beta1, f
 
 // One optimizer step restricted to n sorted, disjoint slices [lo[i], hi[i]) of the flat buffer (a rank's share under a
 // sharded optimizer: its parts of the large tensors, and whatever small tensors every rank updates). Every tensor gets
-// the step number asca_model_adamw_step would give it; the counter advances as for a full step. bf16 mode with an
+// the step number asca_model_adamw_step would give it; the counter advances as for a full step when `advance` is set
+// (a step may be issued as several calls, the last one advancing). bf16 mode with an
 // unpadded bf16 copy only (the update writes that copy for the slices; the caller exchanges the rest).
 int asca_model_adamw_slices(asca_ctx* ctx, asca_model* m, float lr, float beta1, float beta2, float eps, float wd, const int64_t* lo,
-                            const int64_t* hi, int n) {
+                            const int64_t* hi, int n, int advance) {
     if (!ctx || !m) return ASCA_ERR_ARG;
     ASCA_REQUIRE(ctx, lo && hi && n > 0, "model_adamw_slices: bad arguments");
     ASCA_REQUIRE(ctx, m->compute == ASCA_BF16 && m->params16 && m->n16 == m->n_params,
@@ -1120,7 +1121,7 @@ int asca_model_adamw_slices(asca_ctx* ctx, asca_model* m, float lr, float beta1,
         ASCA_TRY(asca_adamw_segmented_cast(ctx, m->params + lo[s], m->grads + lo[s], m->m + lo[s], m->v + lo[s], off.data(), lr_t.data(),
                                            eps_t.data(), (int)lr_t.size(), beta1, beta2, lr * wd, m->params16 + lo[s]));
     }
-    m->adam_counter += (uint32_t)n_seg;
+    if (advance) m->adam_counter += (uint32_t)n_seg;   // the last call of an optimizer step
     m->dec_stale = true;
     m->dec_pk_stale = true;
     return ASCA_OK;

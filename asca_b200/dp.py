@@ -153,6 +153,24 @@ class ShardedOverlap(GradOverlap):
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.big, self.slices = shard_plan(model.cfg, self.rank, self.world)
+        # the update is issued tensor group by tensor group, so that the all-gather of a sharded tensor's bf16 chunks
+        # runs on the side stream while the next group is being updated: cut the slices at the sharded tensors' ends
+        cuts = [lo + n for lo, n in self.big]
+        pieces = []
+        for a, b in self.slices:
+            for c in cuts:
+                if a < c < b:
+                    pieces.append((a, c))
+                    a = c
+            pieces.append((a, b))
+        self.groups, k = [], 0
+        for (lo, n), c in zip(self.big, cuts):
+            grp = []
+            while k < len(pieces) and pieces[k][1] <= c:
+                grp.append(pieces[k])
+                k += 1
+            self.groups.append((grp, (lo, n)))
+        self.groups.append((pieces[k:], None))
 
     def _ready(self, off, cnt):
         self.ranges.append((off, cnt))
@@ -185,15 +203,19 @@ class ShardedOverlap(GradOverlap):
         if self.world == 1:
             self.model.adamw_step(lr)
             return
-        self.model.adamw_slices(lr, self.slices)
         ptr, n16 = self.model.params16()
         p16 = device_tensor_bf16(ptr, n16, self.model.gpu.device)
-        ev = torch.cuda.current_stream().record_event()
-        self.side.wait_event(ev)
-        with torch.cuda.stream(self.side):
-            for lo, n in self.big:
+        last = max(i for i, g in enumerate(self.groups) if g[0])
+        for i, (grp, big) in enumerate(self.groups):
+            if grp:
+                self.model.adamw_slices(lr, grp, advance=(i == last))
+            if big is not None:
+                lo, n = big
                 c = n // self.world
-                dist.all_gather_into_tensor(p16[lo:lo + n], p16[lo + self.rank * c:lo + (self.rank + 1) * c], group=self.group)
+                ev = torch.cuda.current_stream().record_event()
+                self.side.wait_event(ev)
+                with torch.cuda.stream(self.side):
+                    dist.all_gather_into_tensor(p16[lo:lo + n], p16[lo + self.rank * c:lo + (self.rank + 1) * c], group=self.group)
         torch.cuda.current_stream().wait_stream(self.side)
 
     def gather_master(self):

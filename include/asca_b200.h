@@ -357,12 +357,14 @@ int asca_model_adamw_step(asca_ctx* ctx, asca_model* m, float lr, float beta1, f
 /* Sharded optimizer support (bf16 compute mode, unpadded bf16 copy). asca_model_adamw_slices is one optimizer step
  * restricted to n sorted, disjoint slices [lo[i], hi[i]) of the flat buffer -- a rank's parts of the large tensors
  * plus the small tensors every rank updates; every tensor gets the step number asca_model_adamw_step would give
- * it and the counter advances as for a full step; the bf16 copy is written for the slices only.
+ * it; the counter advances as for a full step when `advance` is non-zero (an optimizer step may be issued as several
+ * calls so that the exchange of finished tensors can start, the last call advancing); the bf16 copy is written for
+ * the slices only.
  * asca_model_params16 returns the device address of the bf16 copy so that the caller can all-gather the other
  * ranks' slices into it. The f32 master weights and moments outside a rank's slices are then stale on that rank
  * by design. No reference counterpart (the reference's trainer is single-process). */
 int asca_model_adamw_slices(asca_ctx* ctx, asca_model* m, float lr, float beta1, float beta2, float eps,
-                            float wd, const int64_t* lo, const int64_t* hi, int n);
+                            float wd, const int64_t* lo, const int64_t* hi, int n, int advance);
 int asca_model_params16(asca_ctx* ctx, asca_model* m, void** out, int64_t* n16);
 /* Decode: n_streams independent streams advance one token each (Model::step,
  * rust/src/model.rs:631-649). state: device f32 (L, n_streams, H, dh, dh), updated in place;
