@@ -181,12 +181,17 @@ class Gpu:
         """Switch per-kernel CUDA-event timing of the delta-rule kernels on or off (clears the record)."""
         self._call("asca_ctx_profile", self._ctx, C.c_int(1 if on else 0))
 
-    def profile_read(self):
-        """[(kernel name, milliseconds)] recorded since profile(True)."""
+    def profile_read(self, with_work=False):
+        """[(kernel name, milliseconds)] recorded since profile(True); with_work adds the launch's stated
+        algorithmic FLOPs or bytes (0 where the launcher states none)."""
         out, i = [], 0
-        name, ms = C.c_char_p(), C.c_float()
+        name, ms, work = C.c_char_p(), C.c_float(), C.c_double()
         while self.lib.asca_ctx_profile_read(self._ctx, C.c_int(i), C.byref(name), C.byref(ms)) == 0:
-            out.append((name.value.decode(), float(ms.value)))
+            if with_work:
+                self.lib.asca_ctx_profile_work(self._ctx, C.c_int(i), C.byref(work))
+                out.append((name.value.decode(), float(ms.value), float(work.value)))
+            else:
+                out.append((name.value.decode(), float(ms.value)))
             i += 1
         return out
 

@@ -48,6 +48,7 @@ struct asca_ctx {
     struct Span {
         const char* name;
         cudaEvent_t e0, e1;
+        double work;   // algorithmic FLOPs (products) or bytes of the launch; 0 = not stated
     };
     std::vector<Span> spans;
 };
@@ -57,7 +58,8 @@ struct asca_span {
     asca_ctx* ctx;
     cudaEvent_t e0 = nullptr, e1 = nullptr;
     const char* name;
-    asca_span(asca_ctx* c, const char* n) : ctx(c), name(n) {
+    double work;
+    asca_span(asca_ctx* c, const char* n, double w = 0.0) : ctx(c), name(n), work(w) {
         if (!ctx->profiling) return;
         cudaEventCreate(&e0);
         cudaEventCreate(&e1);
@@ -66,7 +68,7 @@ struct asca_span {
     ~asca_span() {
         if (!e0) return;
         cudaEventRecord(e1, ctx->stream);
-        ctx->spans.push_back({name, e0, e1});
+        ctx->spans.push_back({name, e0, e1, work});
     }
 };
 

@@ -117,6 +117,13 @@ int asca_ctx_profile_read(asca_ctx* ctx, int index, const char** name, float* ms
     return ASCA_OK;
 }
 
+int asca_ctx_profile_work(asca_ctx* ctx, int index, double* work) {
+    if (!ctx || !work) return ASCA_ERR_ARG;
+    if (index < 0 || index >= (int)ctx->spans.size()) return 1;
+    *work = ctx->spans[index].work;
+    return ASCA_OK;
+}
+
 const char* asca_last_error(const asca_ctx* ctx) { return ctx ? ctx->err.c_str() : "null context"; }
 const char* asca_describe(asca_ctx* ctx) { return ctx ? ctx->desc.c_str() : "null context"; }
 int64_t asca_launch_count(const asca_ctx* ctx) { return ctx ? ctx->launches : 0; }

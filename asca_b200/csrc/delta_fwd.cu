@@ -484,6 +484,7 @@ int asca_delta_step_strided(asca_ctx* ctx, const float* qkv, int64_t ld_qkv, con
     if (n_streams == 0) return ASCA_OK;
     const int64_t units = n_streams * H;
     const int64_t n_sm = ctx->sm_count > 0 ? ctx->sm_count : 148;
+    asca_span sp(ctx, "delta_step_warp64_kernel", (double)units * 2.0 * 64 * 64 * 4);   // state bytes read + written
     ASCA_CUDA(ctx, asca_launch(ctx, delta_step_warp64_kernel, dim3((unsigned)std::min(n_sm, ceil_div64(units, SW_WARPS))), dim3(SW_WARPS * 32), 0,
                                qkv, nullptr, nullptr, gate, nullptr, S, units, (int)H, 1, ld_qkv, ld_gate, o, (__nv_bfloat16*)o16));
     ctx->launches++;

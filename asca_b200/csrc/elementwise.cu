@@ -495,6 +495,7 @@ int asca_adamw_segmented_cast(asca_ctx* ctx, float* p, const float* g, float* m,
     int64_t blocks = ceil_div64(n, 1024);
     int64_t cap = (int64_t)ctx->sm_count * 16;
     if (blocks > cap) blocks = cap;
+    asca_span sp(ctx, "adamw_seg_kernel", (double)n * (p_bf16 ? 30.0 : 28.0));   // bytes read + written
     adamw_seg_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(p, g, m, v, (const int64_t*)w, (const float*)(w + off_b),
                                                                  (const float*)(w + off_b + f_b), n_seg, beta1, beta2,
                                                                  wd_eff, (__nv_bfloat16*)p_bf16);

@@ -434,6 +434,9 @@ bool skinny_wanted(const Args& a) {
 
 int launch_skinny(asca_ctx* ctx, const Args& a) {
     const int64_t tiles_f = (a.N + BF - 1) / BF;
+    // measurement harnesses: the weight bytes the product must stream go with the timed span
+    asca_span sp(ctx, a.group_dim == GROUP_NONE ? "gemm_skinny_kernel (dense)" : "gemm_skinny_kernel (expert-grouped)",
+                 2.0 * (double)a.K * (double)a.N * (a.group_dim == GROUP_NONE ? 1.0 : (double)a.n_groups));
     // One CTA per SM with the whole shared memory as its ring: a CTA's k-loop is one latency-bound stream, and what
     // keeps HBM busy is the bytes in flight per SM (10 stages of 20 KiB, or 8 of 24 KiB).
     if (a.group_dim == GROUP_NONE) {

@@ -552,6 +552,13 @@ static int64_t tile_bound(const Args& a, int bn) {
 
 int launch(asca_ctx* ctx, const Args& a) {
     if (skinny_wanted(a)) return launch_skinny(ctx, a);
+    // measurement harnesses: the product's algorithmic FLOPs go with the timed span
+    const double rows_m = a.group_dim == GROUP_M ? (double)a.total_rows : (double)a.M;
+    const double rows_k = a.group_dim == GROUP_K ? (double)a.total_rows : (double)a.K;
+    asca_span sp(ctx, a.group_dim == GROUP_NONE ? "gemm_tc_kernel (dense)"
+                      : a.group_dim == GROUP_M  ? "gemm_tc_kernel (expert-grouped rows)"
+                                                : "gemm_tc_kernel (expert-grouped k)",
+                 2.0 * rows_m * (double)a.N * rows_k);
     const int n_sm = ctx->sm_count > 0 ? ctx->sm_count : 148;
     // persistent: the CTAs walk the tiles round-robin. Wide tiles for dense problems with a long k-loop and at least
     // two waves of tiles (measured: +10-15 % there; with k <= 2048 or expert-grouped rows the 128 KiB epilogue per

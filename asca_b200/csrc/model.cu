@@ -6,6 +6,7 @@
 
 #include <algorithm>
 #include "gemm_tc.cuh"
+#include "model.cuh"
 
 namespace {
 
@@ -282,10 +283,6 @@ __global__ void __launch_bounds__(256) argmax_kernel(const float* __restrict__ l
     if (lane == 0) out[t] = (uint32_t)bi;
 }
 
-struct Lyr {
-    int64_t w_qkv, b_qkv, w_gate, b_gate, w_o, b_o, w1, b1, w2, b2;
-};
-
 struct Bufs {   // device buffers from the context cache, released together
     asca_ctx* ctx;
     std::vector<void*> p;
@@ -303,37 +300,14 @@ struct Bufs {   // device buffers from the context cache, released together
 
 }  // namespace
 
-struct asca_model {
-    int64_t vocab, d, H, L, E, F, n_params;
-    int64_t embed, head;
-    std::vector<Lyr> lay;
-    // offsets of the same tensors in the bf16 copy, each rounded up to 8 elements (16 bytes: TMA base alignment)
-    std::vector<Lyr> lay16;
-    int64_t embed16 = 0, head16 = 0, n16 = 0;
-    std::vector<int64_t> seg16;
-    std::vector<int64_t> seg_off;   // tensor offsets in parameter order, + total
-    float *params = nullptr, *grads = nullptr, *m = nullptr, *v = nullptr;
-    uint32_t adam_counter = 0;
-    int compute = ASCA_F32;              // ASCA_BF16: tensor-core products on a bf16 copy of the weights
-    __nv_bfloat16* params16 = nullptr;   // refreshed from the f32 master copy whenever that changed
-    bool params16_stale = true;
-    // decode only: per block the qkv and gate projections side by side, [d x ldq] bf16 + bias [ldq] f32,
-    // so that one product feeds the state update
-    __nv_bfloat16* dec_w = nullptr;
-    float* dec_b = nullptr;
-    bool dec_stale = true, dec_pk_stale = true;
-    __nv_bfloat16* dec_pk = nullptr;   // decode: every product's weights in the few-row kernel's streaming order
-    // asca_model_zero_grads only records the request: the next backward overwrites every gradient tensor instead
-    // of adding to it (each tensor is written exactly once per backward), which saves the clearing pass and the
-    // read half of the accumulation. Anything that exposes the buffer earlier clears it for real first.
-    bool grads_zero_pending = false;
-    float grad_scale = 1.0f;   // multiplies dLoss/dlogits: 1 / micro-batches when gradients are accumulated
-    // called during the backward, on the host, each time a contiguous range of the gradient buffer has had all its
-    // kernels enqueued (one block's tensors, last block first, then embedding + head): the data-parallel
-    // exchange of that range can be queued behind them while the rest of the backward is still running
-    asca_grad_ready_fn grad_hook = nullptr;
-    void* grad_hook_user = nullptr;
-};
+
+// A contiguous range of the gradient buffer has had all its kernels enqueued: tell the caller's hook and the
+// data-parallel exchange. Per block, in backward order: the expert tensors (w1, b1, w2, b2 -- final right after the
+// expert backward, the first thing a block's backward does), then the block's projections; last embedding + head.
+static int grad_ready(asca_ctx* ctx, asca_model* m, int64_t off, int64_t cnt) {
+    if (m->grad_hook) m->grad_hook(m->grad_hook_user, off, cnt);
+    return m->dp ? asca_dp_grad_ready(ctx, m, off, cnt) : ASCA_OK;
+}
 
 // The bf16 copy of the weights that the tensor-core products read: allocated on first use, rebuilt whenever the
 // f32 master copy changed behind it (set_params, an AdamW step that did not write it itself, params_changed).
@@ -344,6 +318,9 @@ static int refresh_params16(asca_ctx* ctx, asca_model* m) {
         m->params16_stale = true;
     }
     if (!m->params16_stale) return ASCA_OK;
+    ASCA_REQUIRE(ctx, !m->master_stale,
+                 "model: the bf16 weight copy would be rebuilt from master weights that are stale on this rank (sharded "
+                 "optimizer); call asca_model_dp_gather_master first");
     if (m->n16 == m->n_params) {   // no padding anywhere: one pass over the flat buffer
         ASCA_TRY(asca_cast_bf16(ctx, m->params, m->params16, m->n_params));
     } else {
@@ -405,6 +382,7 @@ static int decode_step_bf16(asca_ctx* ctx, asca_model* m, float* state, const ui
     const int64_t d = m->d, H = m->H, dh = d / H, E = m->E, F = m->F, V = m->vocab;
     const int BF = ASCA_BF16;
     ASCA_TRY(refresh_params16(ctx, m));
+    ASCA_TRY(asca_dp_wait_all(ctx, m));
     const float* P = m->params;
     const bf16* W = m->params16;
     Bufs bf(ctx);
@@ -613,6 +591,7 @@ static int forward_backward_bf16(asca_ctx* ctx, asca_model* m, const uint32_t* i
         ASCA_TRY(asca_delta_fwd(ctx, a.q, a.k, a.v, a.al, a.be, B, T, H, dh, CH, BF, a.o, nullptr, nullptr, a.ckpt));
         ASCA_TRY(asca_gemm(ctx, ASCA_NN, N, d, d, a.o, d, W + w16.w_o, d, y, d, P + w.b_o, 0, BF));
         ASCA_TRY(asca_residual_rmsnorm_bf16(ctx, x, y, a.x_mid, a.xn, N, d, 1e-6f));
+        ASCA_TRY(asca_dp_before_expert_weights(ctx, m, li));
         ASCA_TRY(asca_moe_fwd(ctx, a.xn, W + w16.w1, P + w.b1, W + w16.w2, P + w.b2, perm, offs, N, d, F, E, BF, mo, a.pre_p,
                               a.hid_p));
         if (li + 1 < L && vec4) {   // x_out = x_mid + moe, with the bf16 copy the next block's products read
@@ -670,6 +649,7 @@ static int forward_backward_bf16(asca_ctx* ctx, asca_model* m, const uint32_t* i
         Act& a = acts[li];
         ASCA_TRY((acc ? asca_moe_bwd_acc : asca_moe_bwd)(ctx, a.xn, W + w16.w1, W + w16.w2, a.pre_p, a.hid_p, dx, perm, offs, N, d, F, E, BF, G + w.w1,
                                   G + w.b1, G + w.w2, G + w.b2, dxn));
+        ASCA_TRY(grad_ready(ctx, m, w.w1, (li + 1 < L ? m->lay[li + 1].w_qkv : m->n_params) - w.w1));   // the block's experts
         // d_mid = dx + rmsnorm_bwd(x_mid, dxn), with its bf16 copy: one pass where the rows fit the warp kernel
         const int rc_join = asca_rmsnorm_bwd_add_cast(ctx, a.x_mid, dxn, dx, dx, dx16, N, d, 1e-6f);
         if (rc_join != ASCA_ERR_UNSUPPORTED) {
@@ -721,11 +701,11 @@ static int forward_backward_bf16(asca_ctx* ctx, asca_model* m, const uint32_t* i
             ASCA_TRY(asca_gemm(ctx, ASCA_NT, N, d, 3 * d, dqkv16, 3 * d, W + w16.w_qkv, 3 * d, dx, d, nullptr, 1, BF));
             ASCA_TRY(asca_gemm(ctx, ASCA_NT, N, d, 2 * H, dg16, 2 * H, W + w16.w_gate, 2 * H, dx, d, nullptr, 1, BF));
         }
-        if (m->grad_hook) m->grad_hook(m->grad_hook_user, w.w_qkv, (li + 1 < L ? m->lay[li + 1].w_qkv : m->n_params) - w.w_qkv);
+        ASCA_TRY(grad_ready(ctx, m, w.w_qkv, w.w1 - w.w_qkv));   // the block's projections
     }
     if (!acc) ASCA_CUDA(ctx, cudaMemsetAsync(G + m->embed, 0, (size_t)V * d * 4, ctx->stream));
     ASCA_TRY(asca_embed_bwd(ctx, dx, ids, N, d, V, G + m->embed));
-    if (m->grad_hook) m->grad_hook(m->grad_hook_user, 0, m->lay[0].w_qkv);   // embedding + head
+    ASCA_TRY(grad_ready(ctx, m, 0, m->lay[0].w_qkv));   // embedding + head
     ASCA_CUDA(ctx, cudaGetLastError());
     return asca_ctx_sync(ctx);
 }
@@ -859,6 +839,10 @@ int asca_model_destroy(asca_ctx* ctx, asca_model* m) {
     if (m->dec_w) cudaFree(m->dec_w);
     if (m->dec_b) cudaFree(m->dec_b);
     if (m->dec_pk) cudaFree(m->dec_pk);
+    if (m->dp) {
+        cudaStreamSynchronize(ctx ? ctx->stream : nullptr);
+        asca_dp_free(m);
+    }
     delete m;
     return ASCA_OK;
 }
@@ -915,6 +899,8 @@ int asca_model_params_changed(asca_model* m) {
 int asca_model_set_params_host(asca_ctx* ctx, asca_model* m, const float* params) {
     if (!ctx || !m || !params) return ASCA_ERR_ARG;
     m->adam_counter = 0;
+    m->master_stale = false;
+    ASCA_TRY(asca_dp_wait_all(ctx, m));
     ASCA_CUDA(ctx, cudaMemsetAsync(m->m, 0, (size_t)m->n_params * 4, ctx->stream));
     ASCA_CUDA(ctx, cudaMemsetAsync(m->v, 0, (size_t)m->n_params * 4, ctx->stream));
     m->params16_stale = true;
@@ -925,6 +911,9 @@ int asca_model_set_params_host(asca_ctx* ctx, asca_model* m, const float* params
 
 int asca_model_get_host(asca_ctx* ctx, asca_model* m, float* params, float* grads) {
     if (!ctx || !m) return ASCA_ERR_ARG;
+    ASCA_REQUIRE(ctx, !(params && m->master_stale),
+                 "model_get: after a sharded optimizer step the master weights of other ranks' chunks are stale on this "
+                 "rank; call asca_model_dp_gather_master first");
     if (params) ASCA_TRY(asca_memcpy_d2h(ctx, params, m->params, (size_t)m->n_params * 4));
     if (grads) {
         ASCA_TRY(materialize_zero_grads(ctx, m));
@@ -1025,6 +1014,7 @@ int asca_model_forward_backward_host(asca_ctx* ctx, asca_model* m, const uint32_
         // HashMoe::backward: gradients accumulate into the flat buffer
         ASCA_TRY((acc ? asca_moe_bwd_acc : asca_moe_bwd)(ctx, a.xn, P + w.w1, P + w.w2, a.pre_p, a.hid_p, dx, perm, offs, N, d, F, E, ASCA_F32,
                                   G + w.w1, G + w.b1, G + w.w2, G + w.b2, dxn));
+        ASCA_TRY(grad_ready(ctx, m, w.w1, (li + 1 < L ? m->lay[li + 1].w_qkv : m->n_params) - w.w1));   // the block's experts
         ASCA_TRY(asca_rmsnorm_bwd(ctx, a.x_mid, dxn, d_moe, N, d, 1e-6f));
         add_kernel<<<(unsigned)blocks_nd, 256, 0, ctx->stream>>>(dx, d_moe, dx, N * d);   // d_mid
         ctx->launches++;
@@ -1041,11 +1031,11 @@ int asca_model_forward_backward_host(asca_ctx* ctx, asca_model* m, const uint32_
         // dx = d_mid + d_qkv Wqkv^T + d_gate Wg^T   (accumulate onto d_mid in place)
         ASCA_TRY(asca_gemm(ctx, ASCA_NT, N, d, 3 * d, d_qkv, 3 * d, P + w.w_qkv, 3 * d, dx, d, nullptr, 1, ASCA_F32));
         ASCA_TRY(asca_gemm(ctx, ASCA_NT, N, d, 2 * H, d_gate, 2 * H, P + w.w_gate, 2 * H, dx, d, nullptr, 1, ASCA_F32));
-        if (m->grad_hook) m->grad_hook(m->grad_hook_user, w.w_qkv, (li + 1 < L ? m->lay[li + 1].w_qkv : m->n_params) - w.w_qkv);
+        ASCA_TRY(grad_ready(ctx, m, w.w_qkv, w.w1 - w.w_qkv));   // the block's projections
     }
     if (!acc) ASCA_CUDA(ctx, cudaMemsetAsync(G + m->embed, 0, (size_t)V * d * 4, ctx->stream));
     ASCA_TRY(asca_embed_bwd(ctx, dx, ids, N, d, V, G + m->embed));
-    if (m->grad_hook) m->grad_hook(m->grad_hook_user, 0, m->lay[0].w_qkv);   // embedding + head
+    ASCA_TRY(grad_ready(ctx, m, 0, m->lay[0].w_qkv));   // embedding + head
     ASCA_CUDA(ctx, cudaGetLastError());
     return asca_ctx_sync(ctx);
 }
@@ -1131,6 +1121,7 @@ int asca_model_adamw_slices(asca_ctx* ctx, asca_model* m, float lr, float beta1,
 int asca_model_params16(asca_ctx* ctx, asca_model* m, void** out, int64_t* n16) {
     if (!ctx || !m || !out) return ASCA_ERR_ARG;
     ASCA_TRY(refresh_params16(ctx, m));
+    ASCA_TRY(asca_dp_wait_all(ctx, m));
     *out = m->params16;
     if (n16) *n16 = m->n16;
     return ASCA_OK;

@@ -1,17 +1,25 @@
-"""Data parallelism by sequence (one process per GPU).
+"""Data parallelism by sequence (one process per GPU): bindings of the library's exchange.
 
 The hot path shards without any data-path collective: a (sequence, head) chain, a MoE token row
 and a decode stream never read another rank's data, and every rank holds the full weights
-(heads and experts stay local). Training needs exactly one exchange per step: the sum of the
-flat gradient buffer over ranks, scaled by 1/world so that equal per-rank token counts
-reproduce the single-process token mean (the property rust/tests/batch_parity.rs pins).
-torch.distributed is the plumbing (NCCL over NVLink on GPUs, gloo in CPU tests).
+(heads and experts stay local). Training needs exactly one exchange per step: the mean of the
+flat gradient buffer over ranks, which with equal per-rank token counts reproduces the
+single-process token mean (the property rust/tests/batch_parity.rs pins).
+
+The exchange itself lives in the library (csrc/dp.cu, behind ``asca_comm_*`` /
+``asca_allreduce_grads`` / ``asca_model_dp_*`` of include/asca_b200.h): NCCL collectives on a side
+stream owned by the communicator, queued from inside the backward as gradient ranges become final,
+ordered against the CONTEXT's stream -- whichever stream that is. This module only binds it.
+``torch.distributed`` is used for nothing but handing the 128-byte NCCL id to the other ranks (and,
+in CPU tests on gloo, for the host-side helpers at the top).
 """
 from __future__ import annotations
 
+import ctypes as C
+
 import numpy as np
-import torch
-import torch.distributed as dist
+
+from . import AscaError, _f, _i64, _p, load
 
 
 def shard_sequences(n_sequences: int, rank: int, world: int) -> range:
@@ -28,9 +36,11 @@ def shard_tokens(ids: np.ndarray, batch: int, rank: int, world: int):
     return ids.reshape(batch, seq)[own.start:own.stop].reshape(-1).copy(), len(own)
 
 
-def allreduce_mean_(flat: torch.Tensor, weight: float = 1.0, group=None) -> torch.Tensor:
-    """In-place sum over ranks of weight * flat. With weight = local_tokens / global_tokens this is
-    the global token mean of per-rank means."""
+def allreduce_mean_(flat, weight: float = 1.0, group=None):
+    """Host-side statement of the exchange on a torch tensor (used by the gloo tests): in-place sum over
+    ranks of weight * flat. With weight = local_tokens / global_tokens this is the global token mean."""
+    import torch.distributed as dist
+
     if weight != 1.0:
         flat.mul_(weight)
     if dist.is_initialized() and dist.get_world_size(group) > 1:
@@ -45,187 +55,160 @@ class _DevView:
         self.__cuda_array_interface__ = {"shape": (n,), "typestr": "<f4", "data": (ptr, False), "version": 2}
 
 
-def device_tensor(ptr: int, n: int, device: int) -> torch.Tensor:
+def device_tensor(ptr: int, n: int, device: int):
+    import torch
+
     return torch.as_tensor(_DevView(ptr, n), device=f"cuda:{device}")
 
 
-def device_tensor_bf16(ptr: int, n: int, device: int) -> torch.Tensor:
+def device_tensor_bf16(ptr: int, n: int, device: int):
     """bf16 view of a device buffer of n 2-byte elements."""
+    import torch
+
     v = _DevView(ptr, n)
     v.__cuda_array_interface__["typestr"] = "<i2"
     return torch.as_tensor(v, device=f"cuda:{device}").view(torch.bfloat16)
 
 
-def allreduce_model_grads(model, local_tokens: int, global_tokens: int, group=None) -> None:
-    """Average the device-resident flat gradient buffer of an asca_b200.Model over all ranks."""
-    grads = device_tensor(model.buffers()[1], model.n, model.gpu.device)
-    model.gpu.sync()
-    allreduce_mean_(grads, local_tokens / global_tokens, group)
+def shard_plan(cfg, rank: int, world: int):
+    """Which parts of the flat parameter buffer `rank` updates under the sharded optimizer
+    (``asca_dp_shard_plan``; host arithmetic only, no GPU needed).
+
+    The experts' W1 and W2 of every block (98 % of the parameters at the training configuration) are cut into
+    `world` equal contiguous chunks, one per rank; every other tensor is updated by every rank. Returns
+    (big, slices): big = [(offset, size)] of the sharded tensors in buffer order, slices = the sorted, disjoint
+    (lo, hi) ranges this rank updates, adjacent ranges merged. Sizes that 4 x `world` does not divide are not sharded.
+    """
+    lib = load()
+    vocab, d, H, L, E, F = (int(x) for x in cfg)
+    cap = 12 * L + 8
+    lo, hi = (C.c_int64 * cap)(), (C.c_int64 * cap)()
+    boff, blen = (C.c_int64 * (2 * L))(), (C.c_int64 * (2 * L))()
+    ns, nb = C.c_int(), C.c_int()
+    rc = lib.asca_dp_shard_plan(_i64(vocab), _i64(d), _i64(H), _i64(L), _i64(E), _i64(F), C.c_int(world), C.c_int(rank),
+                                lo, hi, C.c_int(cap), C.byref(ns), boff, blen, C.c_int(2 * L), C.byref(nb))
+    if rc != 0:
+        raise AscaError(rc, "asca_dp_shard_plan: bad arguments")
+    big = [(int(boff[i]), int(blen[i])) for i in range(nb.value)]
+    slices = [(int(lo[i]), int(hi[i])) for i in range(ns.value)]
+    return big, slices
+
+
+class Comm:
+    """One rank's end of an NCCL communicator owned by the library (``asca_comm_*``)."""
+
+    def __init__(self, gpu, nranks: int, rank: int, unique_id: bytes | None):
+        self.gpu, self.nranks, self.rank = gpu, nranks, rank
+        h = C.c_void_p()
+        buf = C.create_string_buffer(unique_id, 128) if unique_id is not None else None
+        gpu._call("asca_comm_init", gpu._ctx, C.c_int(nranks), C.c_int(rank), buf, C.byref(h))
+        self._h = h
+
+    @staticmethod
+    def unique_id(gpu) -> bytes:
+        buf = C.create_string_buffer(128)
+        gpu._call("asca_comm_unique_id", gpu._ctx, buf)
+        return buf.raw
+
+    @classmethod
+    def from_torch(cls, gpu, group=None):
+        """Rank 0 of an initialised torch.distributed group draws the id; the group carries it to the others."""
+        import torch.distributed as dist
+
+        if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+            return cls(gpu, 1, 0, None)
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        box = [cls.unique_id(gpu) if rank == 0 else None]
+        dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+        return cls(gpu, world, rank, box[0])
+
+    def allreduce_grads(self, ptr: int, n: int, bucket_off=None):
+        """Mean over ranks of the n floats at device address `ptr`, in stream order with the context's stream."""
+        if bucket_off is None:
+            self.gpu._call("asca_allreduce_grads", self.gpu._ctx, self._h, C.c_void_p(ptr), _i64(n), None, C.c_int(0))
+        else:
+            off = np.ascontiguousarray(bucket_off, dtype=np.int64)
+            self.gpu._call("asca_allreduce_grads", self.gpu._ctx, self._h, C.c_void_p(ptr), _i64(n), _p(off), C.c_int(off.size - 1))
+
+    def close(self):
+        if self._h is not None:
+            self.gpu.lib.asca_comm_destroy(self.gpu._ctx, self._h)
+            self._h = None
+
+
+def allreduce_model_grads(model, comm: Comm) -> None:
+    """Blocking form: average the device-resident flat gradient buffer of an asca_b200.Model over all ranks."""
+    comm.allreduce_grads(model.buffers()[1], model.n)
 
 
 class GradOverlap:
-    """All-reduce (average) of an asca_b200.Model's flat gradient buffer, overlapped with its backward.
+    """The gradient exchange of an asca_b200.Model overlapped with its backward, replicated optimizer.
 
-    The model reports each finished gradient range from inside ``forward_backward`` (one block at a
-    time, last block first). For every range this records an event on the compute stream, makes a
-    side stream wait for it and queues ``all_reduce(AVG)`` of that slice there, so the exchange of
-    block i runs under the backward of blocks i-1 .. 0. ``finish()`` makes the compute stream wait
-    for the exchanges; AdamW queued after it sees the averaged gradients.
-
-    With gradient accumulation, arm it only around the last micro-batch (``with overlap:``).
+    ``with overlap:`` arms the model for the backward(s) inside the block (with gradient accumulation, wrap the
+    last micro-batch only); the library queues the all-reduce (mean) of every finished gradient range on the
+    communicator's side stream from inside ``forward_backward``. ``step(lr)`` waits for the exchanges and applies
+    AdamW (use it instead of ``model.adamw_step``). ``ranges`` lists the (offset, count) ranges the last armed
+    backward reported, in order. Without a communicator (``comm=None`` and no initialised process group) the
+    exchange is a no-op and ``step`` is the plain optimizer step.
     """
 
-    def __init__(self, model, group=None):
-        self.model, self.group = model, group
-        dev = model.gpu.device
-        self.grads = device_tensor(model.buffers()[1], model.n, dev)
-        self.side = torch.cuda.Stream(device=dev)
-        self.works = []
-        self.ranges = []
+    sharded = False
 
-    def _ready(self, off, cnt):
+    def __init__(self, model, comm: Comm | None = None, group=None):
+        self.model = model
+        self.comm = comm if comm is not None else Comm.from_torch(model.gpu, group)
+        self.world, self.rank = self.comm.nranks, self.comm.rank
+        self.ranges = []
+        model.gpu._call("asca_model_dp_attach", model.gpu._ctx, model._h, self.comm._h, C.c_int(1 if self.sharded else 0))
+
+    def _seen(self, off, cnt):
         self.ranges.append((off, cnt))
-        if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(self.group) == 1:
-            return
-        ev = torch.cuda.current_stream().record_event()
-        self.side.wait_event(ev)
-        with torch.cuda.stream(self.side):
-            self.works.append(dist.all_reduce(self.grads[off:off + cnt], op=dist.ReduceOp.AVG, group=self.group, async_op=True))
 
     def __enter__(self):
         self.ranges = []
-        self.model.set_grad_hook(self._ready)
+        self.model.set_grad_hook(self._seen)
+        self.model.gpu._call("asca_model_dp_arm", self.model._h, C.c_int(1))
         return self
 
     def __exit__(self, *exc):
         self.model.set_grad_hook(None)
-        self.finish()
         return False
 
-    def finish(self):
-        for w in self.works:
-            w.wait()          # stream-level wait on the side stream
-        self.works = []
-        torch.cuda.current_stream().wait_stream(self.side)
+    def step(self, lr, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.01):
+        """After the backward: wait for the exchanges, then the optimizer step (this rank's share when sharded)."""
+        g = self.model.gpu
+        g._call("asca_model_dp_step", g._ctx, self.model._h, _f(lr), _f(beta1), _f(beta2), _f(eps), _f(wd))
 
+    def timeline(self):
+        """Milliseconds of the last step: exposed gradient exchange, optimizer update, weight all-gather running
+        past the update, and the wait of that step's forward for gathered weights."""
+        out = (C.c_float * 4)()
+        g = self.model.gpu
+        g._call("asca_model_dp_timeline", g._ctx, self.model._h, out)
+        return {"exposed_grad_exchange_ms": out[0], "optimizer_ms": out[1], "allgather_past_update_ms": out[2],
+                "forward_waited_for_weights_ms": out[3]}
 
-def shard_plan(cfg, rank: int, world: int):
-    """Which parts of the flat parameter buffer `rank` updates under the sharded optimizer.
+    def gather_master(self):
+        """Collect the f32 master weights and moments of the other ranks' chunks (before reading parameters out)."""
+        g = self.model.gpu
+        g._call("asca_model_dp_gather_master", g._ctx, self.model._h)
 
-    The experts' W1 and W2 of every block (98 % of the parameters at the training configuration) are cut into `world`
-    equal contiguous chunks, one per rank; every other tensor is updated by every rank. Returns (big, slices):
-    big = [(offset, size)] of the sharded tensors in buffer order, slices = the sorted, disjoint (lo, hi) ranges this
-    rank updates, adjacent ranges merged. Sizes that `world` x 4 does not divide are not sharded.
-    """
-    from asca_b200.train import tensor_sizes
-
-    sizes = tensor_sizes(cfg)
-    offs = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)
-    big, slices = [], []
-    for i, n in enumerate(sizes):
-        lo = int(offs[i])
-        is_expert = i >= 2 and (i - 2) % 10 in (6, 8)      # w1, w2 in the per-block order of tensor_sizes
-        if is_expert and world > 1 and n % (4 * world) == 0:
-            big.append((lo, int(n)))
-            c = n // world
-            piece = (lo + rank * c, lo + (rank + 1) * c)
-        else:
-            piece = (lo, lo + int(n))
-        if slices and slices[-1][1] == piece[0]:
-            slices[-1] = (slices[-1][0], piece[1])
-        else:
-            slices.append(piece)
-    return big, slices
+    def detach(self):
+        g = self.model.gpu
+        g._call("asca_model_dp_attach", g._ctx, self.model._h, None, C.c_int(0))
 
 
 class ShardedOverlap(GradOverlap):
     """GradOverlap with the optimizer sharded over the ranks for the expert weights (bf16 compute mode).
 
-    For W1 / W2 of every block the gradient exchange is a reduce-scatter (each rank receives the mean of its chunk
-    only: half the bytes of an all-reduce), the rank updates its chunk (``finish(lr)`` runs one sliced AdamW over the
-    chunks and all small tensors), and the updated bf16 chunks are all-gathered into every rank's bf16 weight copy
-    (2 bytes per parameter). The f32 master weights and moments of the other ranks' chunks are never exchanged and
-    are stale on this rank: ``gather_master()`` collects them before the parameters are read out.
+    W1 / W2 of every block are reduce-scattered instead of all-reduced (half the bytes), ``step(lr)`` updates this
+    rank's 1/N chunk of them and all small tensors, and the updated bf16 chunks are all-gathered into every rank's
+    bf16 weight copy block by block under the next forward. The f32 master weights and moments of the other ranks'
+    chunks are then stale on this rank; the library refuses to read them out until ``gather_master()`` has run.
     """
 
-    def __init__(self, model, group=None):
-        super().__init__(model, group)
-        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
-        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
-        self.big, self.slices = shard_plan(model.cfg, self.rank, self.world)
-        # the update is issued tensor group by tensor group, so that the all-gather of a sharded tensor's bf16 chunks
-        # runs on the side stream while the next group is being updated: cut the slices at the sharded tensors' ends
-        cuts = [lo + n for lo, n in self.big]
-        pieces = []
-        for a, b in self.slices:
-            for c in cuts:
-                if a < c < b:
-                    pieces.append((a, c))
-                    a = c
-            pieces.append((a, b))
-        self.groups, k = [], 0
-        for (lo, n), c in zip(self.big, cuts):
-            grp = []
-            while k < len(pieces) and pieces[k][1] <= c:
-                grp.append(pieces[k])
-                k += 1
-            self.groups.append((grp, (lo, n)))
-        self.groups.append((pieces[k:], None))
+    sharded = True
 
-    def _ready(self, off, cnt):
-        self.ranges.append((off, cnt))
-        if self.world == 1:
-            return
-        ev = torch.cuda.current_stream().record_event()
-        self.side.wait_event(ev)
-        pieces, pos = [], off
-        for lo, n in self.big:                      # cut the range at the sharded tensors inside it
-            if lo >= off and lo + n <= off + cnt:
-                if lo > pos:
-                    pieces.append((pos, lo - pos, False))
-                pieces.append((lo, n, True))
-                pos = lo + n
-        if pos < off + cnt:
-            pieces.append((pos, off + cnt - pos, False))
-        with torch.cuda.stream(self.side):
-            for lo, n, sharded in pieces:
-                g = self.grads[lo:lo + n]
-                if sharded:
-                    c = n // self.world
-                    self.works.append(dist.reduce_scatter_tensor(g[self.rank * c:(self.rank + 1) * c], g, op=dist.ReduceOp.AVG,
-                                                                 group=self.group, async_op=True))
-                else:
-                    self.works.append(dist.all_reduce(g, op=dist.ReduceOp.AVG, group=self.group, async_op=True))
-
-    def step(self, lr):
-        """After the backward: wait for the exchanges, update this rank's slices, all-gather the bf16 chunks."""
-        self.finish()
-        if self.world == 1:
-            self.model.adamw_step(lr)
-            return
-        ptr, n16 = self.model.params16()
-        p16 = device_tensor_bf16(ptr, n16, self.model.gpu.device)
-        last = max(i for i, g in enumerate(self.groups) if g[0])
-        for i, (grp, big) in enumerate(self.groups):
-            if grp:
-                self.model.adamw_slices(lr, grp, advance=(i == last))
-            if big is not None:
-                lo, n = big
-                c = n // self.world
-                ev = torch.cuda.current_stream().record_event()
-                self.side.wait_event(ev)
-                with torch.cuda.stream(self.side):
-                    dist.all_gather_into_tensor(p16[lo:lo + n], p16[lo + self.rank * c:lo + (self.rank + 1) * c], group=self.group)
-        torch.cuda.current_stream().wait_stream(self.side)
-
-    def gather_master(self):
-        """All-gather the f32 master weights and Adam moments of the sharded tensors (before a checkpoint)."""
-        if self.world == 1:
-            return
-        b = self.model.buffers()
-        for ptr in (b[0], b[2], b[3]):
-            t = device_tensor(ptr, self.model.n, self.model.gpu.device)
-            for lo, n in self.big:
-                c = n // self.world
-                dist.all_gather_into_tensor(t[lo:lo + n], t[lo + self.rank * c:lo + (self.rank + 1) * c], group=self.group)
-        torch.cuda.synchronize()
+    def __init__(self, model, comm: Comm | None = None, group=None):
+        super().__init__(model, comm, group)
+        self.big, self.slices = shard_plan(model.cfg, self.rank, self.world) if self.world > 1 else ([], [(0, model.n)])

@@ -58,11 +58,13 @@ const char* asca_describe(asca_ctx* ctx);
 /* Kernel launches issued through this context since creation (rust/src/cuda/mod.rs:25-33). */
 int64_t asca_launch_count(const asca_ctx* ctx);
 /* Per-kernel timing for measurement harnesses (the role of the reference's ASCA_PROF scopes,
- * rust/src/prof.rs): while on, the delta-rule kernels are bracketed by CUDA events on the
+ * rust/src/prof.rs): while on, the delta-rule kernels and the tensor-core products are bracketed by CUDA events on the
  * context's stream. asca_ctx_profile(ctx, on) clears the record and switches it;
  * asca_ctx_profile_read returns entry `index` (kernel name, milliseconds), or 1 past the end. */
 int asca_ctx_profile(asca_ctx* ctx, int on);
 int asca_ctx_profile_read(asca_ctx* ctx, int index, const char** name, float* ms);
+/* Algorithmic work of entry `index` where the launcher states it (FLOPs of a tensor-core product), else 0. */
+int asca_ctx_profile_work(asca_ctx* ctx, int index, double* work);
 /* Library version string and the arch it was compiled for ("sm_100a"). */
 const char* asca_version(void);
 
@@ -323,12 +325,13 @@ int64_t asca_model_num_params(const asca_model* m);
 /* Device pointers of the flat buffers (params, grads, Adam m, Adam v), each num_params floats. */
 int asca_model_buffers(asca_model* m, float** params, float** grads, float** adam_m, float** adam_v);
 int asca_model_set_compute(asca_ctx* ctx, asca_model* m, int dtype);
-/* Data-parallel overlap (the NCCL gradient all-reduce of the flat buffer, overlapped with the backward):
- * `fn(user, offset, count)` is called on the host, from inside asca_model_forward_backward_host, each
- * time every kernel that writes grads[offset, offset+count) has been enqueued on the context's stream --
- * one call per block, last block first, then one for embedding + head; together they cover the buffer
- * exactly once. The callee typically records an event on that stream and queues the exchange of the
- * range on another stream. NULL removes the hook. */
+/* Gradient-ready hook: `fn(user, offset, count)` is called on the host, from inside
+ * asca_model_forward_backward_host, each time every kernel that writes grads[offset, offset+count) has been
+ * enqueued on the context's stream. Per block, last block first, there are two calls: the block's expert tensors
+ * (w1, b1, w2, b2 -- final as soon as the expert backward is queued, before the rest of the block's backward), then
+ * the block's projections; a last call covers embedding + head. Together they cover the buffer exactly once.
+ * The library's own exchange (asca_model_dp_attach below) is driven from the same points; the hook is for callers
+ * that bring their own collective. NULL removes the hook. */
 /* Gradient accumulation over k micro-batches: with scale = 1/k every backward adds its share of the
  * mean over all k micro-batches (the loss returned stays the mean over the micro-batch's own tokens). */
 int asca_model_set_grad_scale(asca_model* m, float scale);
@@ -366,6 +369,53 @@ int asca_model_adamw_step(asca_ctx* ctx, asca_model* m, float lr, float beta1, f
 int asca_model_adamw_slices(asca_ctx* ctx, asca_model* m, float lr, float beta1, float beta2, float eps,
                             float wd, const int64_t* lo, const int64_t* hi, int n, int advance);
 int asca_model_params16(asca_ctx* ctx, asca_model* m, void** out, int64_t* n16);
+/* ------------------------------------------------------------------ data-parallel training (the gradient exchange)
+ * The path shards by sequence with heads and experts local, so the only exchange is the mean of the flat
+ * gradient buffer over the ranks, once per step (one process per GPU; the property rust/tests/batch_parity.rs
+ * pins: batch = B equals the mean of B x batch = 1). The reference's trainer is single-process
+ * (rust/src/train.rs:201-288) and has no counterpart; these entry points keep its FFI as thin as
+ * rust/src/cuda/sys.rs:33-65: the Rust side binds five functions and never sees NCCL. NCCL is loaded with dlopen
+ * on the first call (ASCA_NCCL_LIB overrides the path); a single-GPU user needs none.
+ *
+ * asca_comm_unique_id fills 128 bytes on one rank; the caller hands them to every rank (a file, a socket, an
+ * environment variable) and all ranks call asca_comm_init together. A communicator owns a side stream on which
+ * all its collectives run; it is tied to the context's device. */
+typedef struct asca_comm asca_comm;
+int asca_comm_unique_id(asca_ctx* ctx, void* id128);
+int asca_comm_init(asca_ctx* ctx, int nranks, int rank, const void* id128, asca_comm** out);
+int asca_comm_destroy(asca_ctx* ctx, asca_comm* comm);
+int asca_comm_info(const asca_comm* comm, int* nranks, int* rank);
+/* flat_grad[0, n) <- mean over ranks, in stream order with the context's stream (work queued before the call is
+ * waited for; work queued after the call sees the result). bucket_off[n_buckets + 1] cuts the buffer into
+ * buckets exchanged last bucket first (the backward finishes the end of the buffer first); NULL = one bucket. */
+int asca_allreduce_grads(asca_ctx* ctx, asca_comm* comm, float* flat_grad, int64_t n, const int64_t* bucket_off,
+                         int n_buckets);
+/* The exchange overlapped with the backward. After asca_model_dp_attach, a backward that runs while the model is
+ * armed (asca_model_dp_arm(m, 1); with gradient accumulation arm the last micro-batch only) queues the exchange of
+ * every finished gradient range on the communicator's side stream from inside asca_model_forward_backward_host.
+ * asca_model_dp_step then waits for the exchanges and applies the optimizer step (it replaces
+ * asca_model_adamw_step and disarms the model):
+ *   sharded = 0  every range is all-reduced; every rank applies the same full update.
+ *   sharded = 1  (bf16 compute mode) W1 / W2 of every block are reduce-scattered instead, this rank updates its
+ *                1/nranks chunk of them and all small tensors, and the updated bf16 chunks are all-gathered into
+ *                the bf16 weight copy block by block; the next forward waits for a block's gathered weights only when
+ *                it reaches that block's expert products. The f32 master weights and moments of other ranks' chunks
+ *                are then stale on this rank: asca_model_get_host refuses to read them until
+ *                asca_model_dp_gather_master has collected them (do that before writing a checkpoint).
+ * comm = NULL detaches. asca_model_dp_timeline reads, for the last step, in milliseconds: [0] how long the end of
+ * the backward waited for the gradient exchange, [1] the optimizer update, [2] how long the weight all-gather ran
+ * past the update, [3] how long the forward of that step waited for gathered weights of the step before.
+ * asca_dp_shard_plan is the host-side arithmetic alone (no GPU needed): the sorted, disjoint [lo, hi) ranges of
+ * the flat buffer that `rank` updates under the sharded optimizer, and the sharded tensors (offset, length). */
+int asca_model_dp_attach(asca_ctx* ctx, asca_model* m, asca_comm* comm, int sharded);
+int asca_model_dp_arm(asca_model* m, int on);
+int asca_model_dp_step(asca_ctx* ctx, asca_model* m, float lr, float beta1, float beta2, float eps, float wd);
+int asca_model_dp_gather_master(asca_ctx* ctx, asca_model* m);
+int asca_model_dp_timeline(asca_ctx* ctx, asca_model* m, float* ms4);
+int asca_dp_shard_plan(int64_t vocab, int64_t d, int64_t H, int64_t L, int64_t E, int64_t F, int nranks, int rank,
+                       int64_t* lo, int64_t* hi, int capacity, int* n_slices, int64_t* big_off, int64_t* big_len,
+                       int big_capacity, int* n_big);
+
 /* Decode: n_streams independent streams advance one token each (Model::step,
  * rust/src/model.rs:631-649). state: device f32 (L, n_streams, H, dh, dh), updated in place;
  * ids: host uint32 (n_streams); logits: host (n_streams x vocab), nullable; next_ids: host

@@ -81,3 +81,45 @@ def test_two_ranks_reproduce_the_single_process_step(tmp_path):
         assert np.max(np.abs(a - b)) / max(np.max(np.abs(b)), 1e-9) <= 2e-4, name
     l0 = float(np.load(tmp_path / "l0.npy")[0])
     assert abs(l0 - loss) / abs(loss) <= 1e-5
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_shard_plan_of_the_library_tiles_the_buffer(world):
+    """The sharded optimizer's plan (asca_dp_shard_plan, host arithmetic inside the library; no GPU, no NCCL, no
+    process group): over all ranks the expert tensors are covered exactly once, in equal 16-byte-aligned chunks;
+    every other tensor is covered by every rank; a rank's ranges are sorted and disjoint. Checked against an
+    independent statement built from the tensor sizes."""
+    from asca_b200 import dp
+    from asca_b200.train import tensor_sizes
+
+    cfg = (256, 2048, 16, 2, 64, 4096)      # two blocks of the 1.3B-class training configuration
+    sizes = tensor_sizes(cfg)
+    offs = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)
+    total = int(offs[-1])
+    expert = [i for i in range(len(sizes)) if i >= 2 and (i - 2) % 10 in (6, 8)]
+    plans = [dp.shard_plan(cfg, r, world) for r in range(world)]
+    want_big = [(int(offs[i]), int(sizes[i])) for i in expert]
+    for big, slices in plans:
+        assert big == want_big
+        assert all(lo < hi for lo, hi in slices)
+        assert all(a[1] < b[0] for a, b in zip(slices, slices[1:]))       # sorted, disjoint, merged
+        assert slices[0][0] == 0 and slices[-1][1] == total
+    # coverage counts at the tensor boundaries and chunk boundaries
+    edges = sorted({0, total} | {e for _, sl in plans for s in sl for e in s})
+    for a, b in zip(edges, edges[1:]):
+        owners = [r for r, (_, sl) in enumerate(plans) if any(lo <= a and b <= hi for lo, hi in sl)]
+        in_big = next(((o, n) for o, n in want_big if o <= a and b <= o + n), None)
+        if in_big is None:
+            assert owners == list(range(world)), (a, b)
+        else:
+            o, n = in_big
+            c = n // world
+            assert owners == [(a - o) // c], (a, b)
+            assert (a - o) % c == 0 and c % 4 == 0
+    # one rank: nothing is sharded
+    big1, sl1 = dp.shard_plan(cfg, 0, 1)
+    assert big1 == [] and sl1 == [(0, total)]
+    # a size that 4 x world does not divide stays whole
+    odd = (256, 64, 4, 1, 3, 10)           # 64 * 3 * 10 = 1920 numbers per expert tensor
+    big_o, sl_o = dp.shard_plan(odd, 0, 7)
+    assert big_o == [] and sl_o == [(0, sum(tensor_sizes(odd)))]
