@@ -317,6 +317,103 @@ class Gpu:
         return r
 
 
+    def moe_forward_dev_buckets(self, xn, w1, b1, w2, b2, buckets, d_ff, keep=True):
+        """Gpu::moe_forward_dev with the reference's own argument list (rust/src/cuda/mod.rs:523-532): `buckets` is
+        the host-built list of per-expert token-index lists; nothing is sorted on the device."""
+        xn, w1, b1, w2, b2 = map(_as_f32, (xn, w1, b1, w2, b2))
+        n, d = xn.shape
+        e = len(buckets)
+        idx = np.ascontiguousarray(np.concatenate([np.asarray(b, np.int32) for b in buckets]), dtype=np.int32)
+        off = np.concatenate([[0], np.cumsum([len(b) for b in buckets])]).astype(np.int32)
+        out = np.empty((n, d), np.float32)
+        h = C.c_void_p()
+        self._call("asca_moe_forward_dev_buckets_host", self._ctx, _p(xn), _p(w1), _p(b1), _p(w2), _p(b2), _p(idx), _p(off),
+                   _i64(n), _i64(d), _i64(d_ff), _i64(e), _p(out), C.byref(h) if keep else None)
+        return out, (MoeDev(self, h, n, d, d_ff, e) if keep else None)
+
+    # ---- head / loss / resident AdamW (rust/src/cuda/mod.rs:828-1055, :1224-1250)
+    def head_forward_dev(self, h_final, head):
+        h_final, head = _as_f32(h_final), _as_f32(head)
+        assert h_final.shape[1] == head.shape[0], "head_forward_dev: head dimension does not match"
+        h = C.c_void_p()
+        self._call("asca_head_forward_dev_host", self._ctx, _p(h_final), _p(head), _i64(h_final.shape[0]), _i64(h_final.shape[1]),
+                   _i64(head.shape[1]), C.byref(h))
+        return LogitsDev(self, h, h_final.shape[0], head.shape[1])
+
+    def head_bwd_dev(self, dev, targets, head_t):
+        """(loss, d_head (d, V), dh (T, d)); head_t is the head transposed, (V, d), as the reference passes it."""
+        head_t = _as_f32(head_t)
+        targets = np.ascontiguousarray(targets, dtype=np.uint32)
+        assert targets.size == dev.t_len and head_t.shape[0] == dev.vocab
+        d = head_t.shape[1]
+        loss = C.c_float()
+        d_head, dh = np.empty((d, dev.vocab), np.float32), np.empty((dev.t_len, d), np.float32)
+        self._call("asca_head_bwd_dev_host", self._ctx, dev._h, _p(targets), _p(head_t), C.byref(loss), _p(d_head), _p(dh))
+        return float(loss.value), d_head, dh
+
+    def cross_entropy_bwd(self, logits, targets):
+        logits = _as_f32(logits)
+        targets = np.ascontiguousarray(targets, dtype=np.uint32)
+        assert logits.shape[0] == targets.size
+        loss, dl = C.c_float(), np.empty_like(logits)
+        self._call("asca_cross_entropy_bwd_host", self._ctx, _p(logits), _p(targets), _i64(logits.shape[0]), _i64(logits.shape[1]),
+                   C.byref(loss), _p(dl))
+        return float(loss.value), dl
+
+    def adamw_resident(self, key, val, grad, m0, v0, lr, beta1, beta2, eps_t, wd):
+        """`key` = (host address of the caller's m buffer, length), as param_key builds it."""
+        for a in (val, grad, m0, v0):
+            assert a.dtype == np.float32 and a.flags.c_contiguous
+        assert key[1] == val.size
+        self._call("asca_adamw_resident_host", self._ctx, C.c_void_p(key[0]), _p(val), _p(grad), _p(m0), _p(v0), _i64(val.size),
+                   _f(lr), _f(beta1), _f(beta2), _f(eps_t), _f(wd))
+
+    def param_moments(self, key):
+        m, v = np.empty(key[1], np.float32), np.empty(key[1], np.float32)
+        rc = self.lib.asca_param_moments_host(self._ctx, C.c_void_p(key[0]), _i64(key[1]), _p(m), _p(v))
+        if rc == 1:
+            return None
+        if rc != 0:
+            raise AscaError(rc, self.lib.asca_last_error(self._ctx).decode())
+        return m, v
+
+    def reset_param_cache(self):
+        self._call("asca_reset_param_cache", self._ctx)
+
+    def silu_inplace(self, x):
+        assert x.dtype == np.float32 and x.flags.c_contiguous
+        self._call("asca_silu_inplace_host", self._ctx, _p(x), _i64(x.size))
+
+
+def param_key(m: np.ndarray):
+    """Cache key of one parameter's moments (rust/src/cuda/mod.rs:57-59): host address and length of its m buffer."""
+    return (m.ctypes.data, m.size)
+
+
+class LogitsDev:
+    """Logits and h_final resident on the device between head_forward_dev and head_bwd_dev
+    (the reference's LogitsDev, rust/src/cuda/mod.rs:1400-1413)."""
+
+    def __init__(self, gpu, handle, t_len, vocab):
+        self._gpu, self._h, self.t_len, self.vocab = gpu, handle, t_len, vocab
+
+    def download(self):
+        out = np.empty((self.t_len, self.vocab), np.float32)
+        self._gpu._call("asca_logits_dev_download", self._gpu._ctx, self._h, _p(out))
+        return out
+
+    def free(self):
+        if self._h is not None:
+            self._gpu._call("asca_logits_dev_free", self._gpu._ctx, self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
 class Model:
     """Device-resident ASCA model on one flat f32 parameter buffer (reference parameter order,
     rust/src/model.rs:593-609): forward + backward + AdamW and the per-token decode step."""
@@ -441,6 +538,16 @@ class Model:
                        _p(nxt))
         return logits, nxt
 
+    def prefill(self, state, ids, want_logits=True):
+        """Chunked prefill of ids (n_streams, T): the recurrent state after the last token lands in `state` (whose
+        incoming contents are the initial state); returns (logits of each stream's last token or None, their argmax)."""
+        ids = np.ascontiguousarray(ids, dtype=np.uint32)
+        ns, t = ids.shape
+        logits = np.empty((ns, self.cfg[0]), np.float32) if want_logits else None
+        nxt = np.empty(ns, np.uint32)
+        self.gpu._call("asca_model_prefill_host", self.gpu._ctx, self._h, _p(state), _p(ids), _i64(ns), _i64(t), _p(logits), _p(nxt))
+        return logits, nxt
+
     def decode_greedy(self, state, ids, n_steps):
         """n_steps greedy tokens per stream; the argmax feeds the next step on the device. Returns (n_steps, n_streams)."""
         ids = np.ascontiguousarray(ids, dtype=np.uint32)
@@ -455,4 +562,4 @@ class Model:
             self._h = None
 
 
-__all__ = ["Gpu", "Model", "DeltaDev", "MoeDev", "MoeBwd", "AscaError", "load", "LIB_PATH", "F32", "BF16", "NN", "TN", "NT"]
+__all__ = ["Gpu", "Model", "DeltaDev", "MoeDev", "MoeBwd", "LogitsDev", "param_key", "AscaError", "load", "LIB_PATH", "F32", "BF16", "NN", "TN", "NT"]

@@ -33,9 +33,10 @@ struct asca_ctx {
     size_t ws_bytes = 0;
     int* err_word = nullptr;  // device int the kernels with bounded waits write to
     // tiles of the tensor-core delta forwards that wrote checkpoints, kept for their backwards: one entry per
-    // checkpoint buffer (a model keeps one per block), least recently used evicted beyond 32 entries / 64 GiB
+    // checkpoint buffer (a model keeps one per block), least recently used evicted beyond 32 entries / dtiles_cap bytes
     struct DeltaTiles {
         const void* ckpt = nullptr;   // key: the checkpoint buffer the forward filled (null: contents invalid)
+        const void *q = nullptr, *k = nullptr, *v = nullptr, *alpha = nullptr, *beta = nullptr;   // and its inputs
         int64_t B = 0, T = 0, H = 0;
         void* buf = nullptr;
         size_t bytes = 0;
@@ -43,6 +44,10 @@ struct asca_ctx {
     };
     std::vector<DeltaTiles> dtiles;
     uint64_t dtiles_clock = 0;
+    size_t dtiles_cap = (size_t)32 << 30;   // bytes of kept tiles beyond which the least recently used set is reused
+    // Adam moments kept on the device between optimizer calls of the host-pointer API, keyed by the caller's
+    // (host address of m, length) as the reference keys them (rust/src/cuda/mod.rs:36-73)
+    std::map<std::pair<uintptr_t, size_t>, std::pair<float*, float*>> resident;
     // optional per-kernel timing (asca_ctx_profile): CUDA events around selected launches
     bool profiling = false;
     struct Span {

@@ -72,6 +72,10 @@ int asca_ctx_destroy(asca_ctx* ctx) {
     if (ctx->ws) cudaFree(ctx->ws);
     for (auto& e : ctx->dtiles)
         if (e.buf) cudaFree(e.buf);
+    for (auto& kv : ctx->resident) {
+        cudaFree(kv.second.first);
+        cudaFree(kv.second.second);
+    }
     if (ctx->err_word) cudaFree(ctx->err_word);
     cudaStreamDestroy(ctx->own_stream);
     delete ctx;
@@ -94,6 +98,27 @@ int asca_ctx_sync(asca_ctx* ctx) {
         cudaMemset(ctx->err_word, 0, sizeof(int));
         return asca_fail(ctx, ASCA_ERR_DEVICE, "a kernel gave up on a bounded wait (code %d)", word);
     }
+    return ASCA_OK;
+}
+
+int asca_ctx_trim(asca_ctx* ctx) {
+    if (!ctx) return ASCA_ERR_ARG;
+    cudaSetDevice(ctx->device);
+    ASCA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    for (auto& e : ctx->dtiles)
+        if (e.buf) cudaFree(e.buf);
+    ctx->dtiles.clear();
+    for (auto& kv : ctx->pool) cudaFree(kv.second);
+    ctx->pool.clear();
+    if (ctx->ws) cudaFree(ctx->ws);
+    ctx->ws = nullptr;
+    ctx->ws_bytes = 0;
+    return ASCA_OK;
+}
+
+int asca_ctx_set_tile_cache_bytes(asca_ctx* ctx, size_t bytes) {
+    if (!ctx) return ASCA_ERR_ARG;
+    ctx->dtiles_cap = bytes;
     return ASCA_OK;
 }
 
@@ -165,6 +190,9 @@ int asca_free(asca_ctx* ctx, void* dptr) {
     if (it == ctx->live.end()) return asca_fail(ctx, ASCA_ERR_ARG, "asca_free: pointer not from asca_malloc");
     ctx->pool.insert({it->second, dptr});
     ctx->live.erase(it);
+    // tiles kept for a backward of this checkpoint buffer can no longer be claimed: their storage becomes reusable
+    for (auto& e : ctx->dtiles)
+        if (e.ckpt == dptr) e.ckpt = nullptr;
     return ASCA_OK;
 }
 

@@ -1349,7 +1349,7 @@ int forward(asca_ctx* ctx, const void* q, const void* k, const void* v, const fl
                 if (!dt[i].ckpt) slot = (int)i;
             size_t total = 0;
             for (auto& e : dt) total += e.bytes;
-            if (slot < 0 && dt.size() < 32 && total + need <= ((size_t)64 << 30)) {
+            if (slot < 0 && dt.size() < 32 && total + need <= ctx->dtiles_cap) {
                 dt.emplace_back();
                 slot = (int)dt.size() - 1;
             }
@@ -1395,6 +1395,7 @@ int forward(asca_ctx* ctx, const void* q, const void* k, const void* v, const fl
     if (keep) {
         auto& e = ctx->dtiles[slot];
         e.ckpt = ckpt;
+        e.q = q; e.k = k; e.v = v; e.alpha = alpha; e.beta = beta;
         e.B = B;
         e.T = T;
         e.H = H;
@@ -1412,7 +1413,11 @@ int backward(asca_ctx* ctx, const void* q, const void* k, const void* v, const f
     int slot = -1;
     for (size_t i = 0; i < ctx->dtiles.size(); ++i) {
         const auto& e = ctx->dtiles[i];
-        if (e.buf && e.ckpt == (const void*)ckpt && e.B == B && e.T == T && e.H == H) slot = (int)i;
+        // the tiles are functions of q, k, v, alpha, beta: the same buffers must come back (their contents are the
+        // caller's contract, see the header); anything else rebuilds the tiles
+        if (e.buf && e.ckpt == (const void*)ckpt && e.q == q && e.k == k && e.v == v && e.alpha == (const void*)alpha &&
+            e.beta == (const void*)beta && e.B == B && e.T == T && e.H == H)
+            slot = (int)i;
     }
     if (slot >= 0) {
         // the forward that wrote `ckpt` left its tiles (functions of the same q,k,v,alpha,beta) here

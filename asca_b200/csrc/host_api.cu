@@ -53,6 +53,20 @@ struct asca_moe_dev {
     int32_t *perm, *offsets;
     int64_t N, d, F, E;
 };
+struct asca_logits_dev {   // LogitsDev, rust/src/cuda/mod.rs:1400-1413: logits and h_final stay on the device
+    float *logits, *h_final;
+    int64_t T, d, V;
+};
+
+namespace {
+__global__ void silu_inplace_kernel(float* __restrict__ x, int64_t n) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) {
+        const float v = x[i];
+        x[i] = v / (1.0f + expf(-v));   // rust/src/model.rs:79-85
+    }
+}
+}  // namespace
 
 extern "C" {
 
@@ -338,6 +352,191 @@ int asca_moe_dev_free(asca_ctx* ctx, asca_moe_dev* dev) {
         asca_free(ctx, p);
     delete dev;
     return ASCA_OK;
+}
+
+// The reference's own call shape for the expert FFN: the caller has already built `buckets` on the host
+// (rust/src/model.rs:190-193) and passes them (Gpu::moe_forward_dev, rust/src/cuda/mod.rs:523-532). Flattened for
+// the C ABI: bucket_idx holds the buckets back to back (N token indices), bucket_off[E + 1] their bounds. They ARE the
+// dispatch permutation and its offsets, so nothing is sorted on the device.
+int asca_moe_forward_dev_buckets_host(asca_ctx* ctx, const float* xn, const float* w1, const float* b1, const float* w2,
+                                      const float* b2, const int32_t* bucket_idx, const int32_t* bucket_off, int64_t N,
+                                      int64_t d, int64_t F, int64_t E, float* out, asca_moe_dev** dev) {
+    if (!ctx) return ASCA_ERR_ARG;
+    ASCA_REQUIRE(ctx, xn && w1 && b1 && w2 && b2 && bucket_idx && bucket_off && out && N > 0 && d > 0 && F > 0 && E > 0,
+                 "moe_forward_dev_buckets_host: bad arguments");
+    ASCA_REQUIRE(ctx, bucket_off[0] == 0 && bucket_off[E] == N, "moe_forward_dev_buckets_host: the buckets must hold every token once");
+    for (int64_t e = 0; e < E; ++e)
+        ASCA_REQUIRE(ctx, bucket_off[e + 1] >= bucket_off[e], "moe_forward_dev_buckets_host: bucket bounds must ascend");
+    for (int64_t i = 0; i < N; ++i)
+        ASCA_REQUIRE(ctx, bucket_idx[i] >= 0 && bucket_idx[i] < N, "moe_forward_dev_buckets_host: token index out of range");
+    if (dev) *dev = nullptr;
+    Scope s(ctx);
+    void *dxn, *dw1, *db1, *dw2, *db2, *dperm, *doff, *dout, *dpre, *dhid;
+    ASCA_TRY(s.upload(xn, (size_t)(N * d) * 4, &dxn));
+    ASCA_TRY(s.upload(w1, (size_t)(d * E * F) * 4, &dw1));
+    ASCA_TRY(s.upload(b1, (size_t)(E * F) * 4, &db1));
+    ASCA_TRY(s.upload(w2, (size_t)(E * F * d) * 4, &dw2));
+    ASCA_TRY(s.upload(b2, (size_t)d * 4, &db2));
+    ASCA_TRY(s.upload(bucket_idx, (size_t)N * 4, &dperm));
+    ASCA_TRY(s.upload(bucket_off, (size_t)(E + 1) * 4, &doff));
+    ASCA_TRY(s.alloc((size_t)(N * d) * 4, &dout));
+    ASCA_TRY(s.alloc((size_t)(N * F) * 4, &dpre));
+    ASCA_TRY(s.alloc((size_t)(N * F) * 4, &dhid));
+    ASCA_TRY(asca_moe_fwd(ctx, dxn, dw1, (float*)db1, dw2, (float*)db2, (int32_t*)dperm, (int32_t*)doff, N, d, F, E,
+                          ASCA_F32, (float*)dout, (float*)dpre, dhid));
+    ASCA_TRY(download(ctx, out, dout, (size_t)(N * d) * 4));
+    ASCA_TRY(asca_ctx_sync(ctx));
+    if (dev) {
+        *dev = new asca_moe_dev{(float*)dxn, (float*)dw1, (float*)dw2, (float*)dpre, (float*)dhid,
+                                (int32_t*)dperm, (int32_t*)doff, N, d, F, E};
+        for (void* p : {dxn, dw1, dw2, dpre, dhid, dperm, doff}) s.keep(p);
+    }
+    return ASCA_OK;
+}
+
+// ------------------------------------------------------------------ head, cross-entropy, resident AdamW, SiLU
+// Gpu::head_forward_dev (rust/src/cuda/mod.rs:828-846): logits = h_final head, kept on the device with h_final.
+int asca_head_forward_dev_host(asca_ctx* ctx, const float* h_final, const float* head, int64_t T, int64_t d, int64_t V,
+                               asca_logits_dev** dev) {
+    if (!ctx) return ASCA_ERR_ARG;
+    ASCA_REQUIRE(ctx, h_final && head && dev && T > 0 && d > 0 && V > 0, "head_forward_dev_host: bad arguments");
+    *dev = nullptr;
+    Scope s(ctx);
+    void *dh, *dw, *dl;
+    ASCA_TRY(s.upload(h_final, (size_t)(T * d) * 4, &dh));
+    ASCA_TRY(s.upload(head, (size_t)(d * V) * 4, &dw));
+    ASCA_TRY(s.alloc((size_t)(T * V) * 4, &dl));
+    ASCA_TRY(asca_matmul(ctx, dh, dw, dl, T, d, V, ASCA_NN, ASCA_F32));
+    ASCA_TRY(asca_ctx_sync(ctx));
+    *dev = new asca_logits_dev{(float*)dl, (float*)dh, T, d, V};
+    s.keep(dl);
+    s.keep(dh);
+    return ASCA_OK;
+}
+
+// LogitsDev::download (rust/src/cuda/mod.rs:1400-1413)
+int asca_logits_dev_download(asca_ctx* ctx, const asca_logits_dev* dev, float* logits) {
+    if (!ctx) return ASCA_ERR_ARG;
+    ASCA_REQUIRE(ctx, dev && logits, "logits_dev_download: null pointer");
+    ASCA_TRY(download(ctx, logits, dev->logits, (size_t)(dev->T * dev->V) * 4));
+    return asca_ctx_sync(ctx);
+}
+
+// Gpu::head_bwd_dev (rust/src/cuda/mod.rs:851-908): cross-entropy backward on the resident logits, then
+// d_head = h_final^T dlogits (d x V) and dh = dlogits head_t (T x d), head_t being the head transposed (V x d).
+int asca_head_bwd_dev_host(asca_ctx* ctx, const asca_logits_dev* dev, const uint32_t* targets, const float* head_t, float* loss,
+                           float* d_head, float* dh) {
+    if (!ctx) return ASCA_ERR_ARG;
+    ASCA_REQUIRE(ctx, dev && targets && head_t && loss && d_head && dh, "head_bwd_dev_host: null pointer");
+    const int64_t T = dev->T, d = dev->d, V = dev->V;
+    for (int64_t i = 0; i < T; ++i) ASCA_REQUIRE(ctx, targets[i] < (uint32_t)V, "head_bwd_dev_host: target out of range");
+    Scope s(ctx);
+    void *dt, *dht, *ddl, *dloss, *ddh, *ddx;
+    ASCA_TRY(s.upload(targets, (size_t)T * 4, &dt));
+    ASCA_TRY(s.upload(head_t, (size_t)(V * d) * 4, &dht));
+    ASCA_TRY(s.alloc((size_t)(T * V) * 4, &ddl));
+    ASCA_TRY(s.alloc(256, &dloss));
+    ASCA_TRY(s.alloc((size_t)(d * V) * 4, &ddh));
+    ASCA_TRY(s.alloc((size_t)(T * d) * 4, &ddx));
+    ASCA_TRY(asca_cross_entropy(ctx, dev->logits, (const uint32_t*)dt, T, V, (float*)ddl, (float*)dloss));
+    ASCA_TRY(asca_matmul(ctx, dev->h_final, ddl, ddh, d, T, V, ASCA_TN, ASCA_F32));
+    ASCA_TRY(asca_matmul(ctx, ddl, dht, ddx, T, V, d, ASCA_NN, ASCA_F32));
+    ASCA_TRY(download(ctx, loss, dloss, 4));
+    ASCA_TRY(download(ctx, d_head, ddh, (size_t)(d * V) * 4));
+    ASCA_TRY(download(ctx, dh, ddx, (size_t)(T * d) * 4));
+    return asca_ctx_sync(ctx);
+}
+
+int asca_logits_dev_free(asca_ctx* ctx, asca_logits_dev* dev) {
+    if (!ctx) return ASCA_ERR_ARG;
+    if (!dev) return ASCA_OK;
+    cudaStreamSynchronize(ctx->stream);
+    asca_free(ctx, dev->logits);
+    asca_free(ctx, dev->h_final);
+    delete dev;
+    return ASCA_OK;
+}
+
+// Gpu::cross_entropy_bwd (rust/src/cuda/mod.rs:945-1000): mean loss and dlogits = (softmax - onehot) / T.
+int asca_cross_entropy_bwd_host(asca_ctx* ctx, const float* logits, const uint32_t* targets, int64_t T, int64_t V, float* loss,
+                                float* dlogits) {
+    if (!ctx) return ASCA_ERR_ARG;
+    ASCA_REQUIRE(ctx, logits && targets && loss && dlogits && T > 0 && V > 0, "cross_entropy_bwd_host: bad arguments");
+    for (int64_t i = 0; i < T; ++i) ASCA_REQUIRE(ctx, targets[i] < (uint32_t)V, "cross_entropy_bwd_host: target out of range");
+    Scope s(ctx);
+    void *dl, *dt, *ddl, *dloss;
+    ASCA_TRY(s.upload(logits, (size_t)(T * V) * 4, &dl));
+    ASCA_TRY(s.upload(targets, (size_t)T * 4, &dt));
+    ASCA_TRY(s.alloc((size_t)(T * V) * 4, &ddl));
+    ASCA_TRY(s.alloc(256, &dloss));
+    ASCA_TRY(asca_cross_entropy(ctx, (const float*)dl, (const uint32_t*)dt, T, V, (float*)ddl, (float*)dloss));
+    ASCA_TRY(download(ctx, loss, dloss, 4));
+    ASCA_TRY(download(ctx, dlogits, ddl, (size_t)(T * V) * 4));
+    return asca_ctx_sync(ctx);
+}
+
+// Gpu::adamw_resident (rust/src/cuda/mod.rs:1003-1055): the moments live on the device between calls, keyed by the
+// caller's (host address of its m buffer, length); the first call for a key uploads m0 / v0. val and grad cross per
+// call. CPU-path decay, as asca_adamw. asca_param_moments_host = param_moments (:57-73); asca_reset_param_cache =
+// reset_param_cache (:50-54), to be called whenever a new model is created.
+int asca_adamw_resident_host(asca_ctx* ctx, const void* key_addr, float* val, const float* grad, const float* m0,
+                             const float* v0, int64_t n, float lr_t, float beta1, float beta2, float eps_t, float wd_eff) {
+    if (!ctx) return ASCA_ERR_ARG;
+    ASCA_REQUIRE(ctx, key_addr && val && grad && m0 && v0 && n > 0, "adamw_resident_host: bad arguments");
+    const auto key = std::make_pair((uintptr_t)key_addr, (size_t)n);
+    auto it = ctx->resident.find(key);
+    if (it == ctx->resident.end()) {
+        float *dm = nullptr, *dv = nullptr;
+        if (cudaMalloc((void**)&dm, (size_t)n * 4) != cudaSuccess || cudaMalloc((void**)&dv, (size_t)n * 4) != cudaSuccess) {
+            if (dm) cudaFree(dm);
+            return asca_fail(ctx, ASCA_ERR_OOM, "adamw_resident_host: cannot allocate the moments");
+        }
+        ASCA_CUDA(ctx, cudaMemcpyAsync(dm, m0, (size_t)n * 4, cudaMemcpyHostToDevice, ctx->stream));
+        ASCA_CUDA(ctx, cudaMemcpyAsync(dv, v0, (size_t)n * 4, cudaMemcpyHostToDevice, ctx->stream));
+        it = ctx->resident.emplace(key, std::make_pair(dm, dv)).first;
+    }
+    Scope s(ctx);
+    void *dp, *dg;
+    ASCA_TRY(s.upload(val, (size_t)n * 4, &dp));
+    ASCA_TRY(s.upload(grad, (size_t)n * 4, &dg));
+    ASCA_TRY(asca_adamw(ctx, (float*)dp, (const float*)dg, it->second.first, it->second.second, n, lr_t, beta1, beta2, eps_t, wd_eff));
+    ASCA_TRY(download(ctx, val, dp, (size_t)n * 4));
+    return asca_ctx_sync(ctx);
+}
+
+int asca_param_moments_host(asca_ctx* ctx, const void* key_addr, int64_t n, float* m, float* v) {
+    if (!ctx) return ASCA_ERR_ARG;
+    ASCA_REQUIRE(ctx, key_addr && m && v && n > 0, "param_moments_host: bad arguments");
+    auto it = ctx->resident.find(std::make_pair((uintptr_t)key_addr, (size_t)n));
+    if (it == ctx->resident.end()) return 1;   // this parameter has no state on the device
+    ASCA_TRY(download(ctx, m, it->second.first, (size_t)n * 4));
+    ASCA_TRY(download(ctx, v, it->second.second, (size_t)n * 4));
+    return asca_ctx_sync(ctx);
+}
+
+int asca_reset_param_cache(asca_ctx* ctx) {
+    if (!ctx) return ASCA_ERR_ARG;
+    ASCA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    for (auto& kv : ctx->resident) {
+        cudaFree(kv.second.first);
+        cudaFree(kv.second.second);
+    }
+    ctx->resident.clear();
+    return ASCA_OK;
+}
+
+// Gpu::silu_inplace (rust/src/cuda/mod.rs:1224-1250)
+int asca_silu_inplace_host(asca_ctx* ctx, float* x, int64_t n) {
+    if (!ctx) return ASCA_ERR_ARG;
+    ASCA_REQUIRE(ctx, x && n >= 0, "silu_inplace_host: bad arguments");
+    if (n == 0) return ASCA_OK;
+    Scope s(ctx);
+    void* dx;
+    ASCA_TRY(s.upload(x, (size_t)n * 4, &dx));
+    silu_inplace_kernel<<<(unsigned)ceil_div64(n, 256), 256, 0, ctx->stream>>>((float*)dx, n);
+    ASCA_CHECK_LAUNCH(ctx);
+    ASCA_TRY(download(ctx, x, dx, (size_t)n * 4));
+    return asca_ctx_sync(ctx);
 }
 
 }  // extern "C"

@@ -1127,6 +1127,98 @@ int asca_model_params16(asca_ctx* ctx, asca_model* m, void** out, int64_t* n16) 
     return ASCA_OK;
 }
 
+// Chunked prefill: the forward of Model::forward (rust/src/model.rs:651-690) over n_streams prompts of T tokens at
+// once, keeping only what a decoder needs -- the recurrent state after the last token, per block, head and stream,
+// written into the decode state -- and the logits of each stream's last token. The reference prefills by stepping the
+// decoder token by token (rust/src/main.rs:367-371); the result is the same state (stepping equals the full forward,
+// rust/tests/decode_parity.rs), reached with T-token products and the chunked scan instead of T decode steps.
+// The incoming `state` is the initial state (zeros for a fresh stream), so a prompt may be fed in several calls.
+int asca_model_prefill_host(asca_ctx* ctx, asca_model* m, float* state, const uint32_t* ids_h, int64_t ns, int64_t T,
+                            float* logits_h, uint32_t* next_h) {
+    typedef __nv_bfloat16 bf16;
+    if (!ctx || !m) return ASCA_ERR_ARG;
+    ASCA_REQUIRE(ctx, state && ids_h && ns > 0 && T > 0, "model_prefill: bad arguments");
+    const int64_t N = ns * T, d = m->d, H = m->H, dh = d / H, E = m->E, F = m->F, V = m->vocab, L = m->L;
+    ASCA_REQUIRE(ctx, N < (1ll << 31), "model_prefill: too many tokens in one call");
+    for (int64_t i = 0; i < N; ++i) ASCA_REQUIRE(ctx, ids_h[i] < (uint32_t)V, "model_prefill: id out of range");
+    const bool bfm = m->compute == ASCA_BF16;
+    const int DT = bfm ? ASCA_BF16 : ASCA_F32;
+    if (bfm) {
+        ASCA_TRY(refresh_params16(ctx, m));
+        ASCA_TRY(asca_dp_wait_all(ctx, m));
+    }
+    const float* P = m->params;
+    const bf16* W = m->params16;
+    Bufs bf(ctx);
+    auto h16 = [&](int64_t n) { return (bf16*)bf.f((n + 1) / 2); };
+    uint32_t* ids = (uint32_t*)bf.f(N);
+    int32_t* perm = (int32_t*)bf.f(N);
+    int32_t* offs = (int32_t*)bf.f(E + 1);
+    int32_t* last = (int32_t*)bf.f(ns);
+    uint32_t* nxt = (uint32_t*)bf.f(ns);
+    float *x = bf.f(N * d), *qkv = bf.f(N * 3 * d), *gate = bf.f(N * 2 * H), *y = bf.f(N * d), *x_mid = bf.f(N * d), *mo = bf.f(N * d);
+    float *qn = bf.f(N * H), *kn = bf.f(N * H), *al = bf.f(N * H), *be = bf.f(N * H), *pre_p = bf.f(N * F);
+    float* s_fin = bf.f(ns * H * dh * dh);
+    float *xl = bf.f(ns * d), *hf = bf.f(ns * d), *logits = bf.f(ns * V);
+    // activations a product reads: bf16 in bf16 mode, f32 otherwise (same element counts)
+    auto act = [&](int64_t n) { return bfm ? (void*)h16(n) : (void*)bf.f(n); };
+    void *x_in = bfm ? act(N * d) : nullptr, *q = act(N * d), *k = act(N * d), *v = act(N * d), *o = act(N * d), *xn = act(N * d),
+         *hid_p = act(N * F), *hf_in = bfm ? act(ns * d) : nullptr;
+    ASCA_REQUIRE(ctx, ids && perm && offs && last && nxt && x && qkv && gate && y && x_mid && mo && qn && kn && al && be && pre_p &&
+                          s_fin && xl && hf && logits && q && k && v && o && xn && hid_p && (!bfm || (x_in && hf_in)),
+                 "model_prefill: out of memory");
+    ASCA_CUDA(ctx, cudaMemcpyAsync(ids, ids_h, (size_t)N * 4, cudaMemcpyHostToDevice, ctx->stream));
+    {
+        std::vector<int32_t> lh(ns);
+        for (int64_t s_ = 0; s_ < ns; ++s_) lh[s_] = (int32_t)(s_ * T + T - 1);
+        ASCA_CUDA(ctx, cudaMemcpyAsync(last, lh.data(), (size_t)ns * 4, cudaMemcpyHostToDevice, ctx->stream));
+        ASCA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));   // lh leaves scope
+    }
+    ASCA_TRY(asca_moe_dispatch(ctx, ids, N, E, perm, offs, nullptr));
+    ASCA_TRY(asca_embed_fwd(ctx, P + m->embed, ids, N, d, x));
+    const size_t st_layer = (size_t)ns * H * dh * dh;
+    for (int64_t li = 0; li < L; ++li) {
+        const Lyr& w = m->lay[li];
+        const Lyr& w16 = m->lay16[li];
+        const void* xi = x;
+        if (bfm) {
+            ASCA_TRY(asca_cast_bf16(ctx, x, x_in, N * d));
+            xi = x_in;
+        }
+        const void *Wqkv = bfm ? (const void*)(W + w16.w_qkv) : (const void*)(P + w.w_qkv), *Wg = bfm ? (const void*)(W + w16.w_gate) : (const void*)(P + w.w_gate),
+                   *Wo = bfm ? (const void*)(W + w16.w_o) : (const void*)(P + w.w_o), *W1 = bfm ? (const void*)(W + w16.w1) : (const void*)(P + w.w1),
+                   *W2 = bfm ? (const void*)(W + w16.w2) : (const void*)(P + w.w2);
+        ASCA_TRY(asca_gemm(ctx, ASCA_NN, N, 3 * d, d, xi, d, Wqkv, 3 * d, qkv, 3 * d, P + w.b_qkv, 0, DT));
+        ASCA_TRY(asca_gemm(ctx, ASCA_NN, N, 2 * H, d, xi, d, Wg, 2 * H, gate, 2 * H, P + w.b_gate, 0, DT));
+        if (bfm) ASCA_TRY(asca_delta_prep_bf16(ctx, qkv, gate, N, H, dh, q, k, v, qn, kn, al, be));
+        else ASCA_TRY(asca_delta_prep(ctx, qkv, gate, N, H, dh, (float*)q, (float*)k, (float*)v, qn, kn, al, be));
+        float* st = state + (size_t)li * st_layer;
+        ASCA_TRY(asca_delta_fwd(ctx, q, k, v, al, be, ns, T, H, dh, 64, DT, o, st, s_fin, nullptr));
+        ASCA_CUDA(ctx, cudaMemcpyAsync(st, s_fin, st_layer * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+        ASCA_TRY(asca_gemm(ctx, ASCA_NN, N, d, d, o, d, Wo, d, y, d, P + w.b_o, 0, DT));
+        if (bfm) ASCA_TRY(asca_residual_rmsnorm_bf16(ctx, x, y, x_mid, xn, N, d, 1e-6f));
+        else ASCA_TRY(asca_residual_rmsnorm(ctx, x, y, x_mid, (float*)xn, N, d, 1e-6f));
+        ASCA_TRY(asca_moe_fwd(ctx, xn, W1, P + w.b1, W2, P + w.b2, perm, offs, N, d, F, E, DT, mo, pre_p, hid_p));
+        ASCA_TRY(asca_residual_rmsnorm(ctx, x_mid, mo, x, nullptr, N, d, 1e-6f));
+    }
+    // the head on each stream's last token only
+    ASCA_TRY(asca_gather_rows(ctx, x, last, ns, d, xl));
+    if (bfm) {
+        ASCA_TRY(asca_residual_rmsnorm_bf16(ctx, xl, nullptr, nullptr, hf_in, ns, d, 1e-6f));
+        ASCA_TRY(asca_gemm(ctx, ASCA_NN, ns, V, d, hf_in, d, W + m->head16, V, logits, V, nullptr, 0, DT));
+    } else {
+        ASCA_TRY(asca_rmsnorm_fwd(ctx, xl, hf, nullptr, ns, d, 1e-6f));
+        ASCA_TRY(asca_gemm(ctx, ASCA_NN, ns, V, d, hf, d, P + m->head, V, logits, V, nullptr, 0, DT));
+    }
+    if (logits_h) ASCA_CUDA(ctx, cudaMemcpyAsync(logits_h, logits, (size_t)ns * V * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    if (next_h) {
+        argmax_kernel<<<(unsigned)ceil_div64(ns, 8), 256, 0, ctx->stream>>>(logits, ns, (int)V, nxt);
+        ASCA_CHECK_LAUNCH(ctx);
+        ASCA_CUDA(ctx, cudaMemcpyAsync(next_h, nxt, (size_t)ns * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    }
+    return asca_ctx_sync(ctx);
+}
+
 int asca_model_decode_greedy_host(asca_ctx* ctx, asca_model* m, float* state, const uint32_t* ids_h, int64_t ns, int64_t n_steps,
                                   uint32_t* tokens_h) {
     if (!ctx || !m) return ASCA_ERR_ARG;

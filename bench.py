@@ -1,29 +1,42 @@
 #!/usr/bin/env python
-"""Benchmark of the Delta Memory hot path: one step = the gated delta-rule forward (chunk
-checkpoints every 64 tokens) plus the BPTT backward over one batch of synthetic input.
+"""Benchmark of the Delta Memory + hash-MoE hot path on B200: the training step, batched decode, and the two
+isolated ops, each with its roofline, beside the reference's CPU path timed on the host cores of the same box.
 
-Workload (the isolated delta op of the baseline configuration list): B=8 sequences, H=16
-heads, T=4096 tokens, dh=128, q/k L2-normalised N(0,1), v ~ N(0,1), alpha = sigmoid(N(2,.5)),
-beta = sigmoid(N(0,1)), dO ~ N(0,1); seeded synthetic data.
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--only train,decode,moe,delta]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \\
+        bench.py --gpus N --steps K --warmup W
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--dtype bf16|f32] [--impl ours|reference]
+Headline (the JSON line's top level): **train tok/s** of the 1.3B-class architecture (d 2048, 16 heads of 128, 64
+hash experts of 2048 -> 4096 -> 2048, byte vocabulary; bf16 compute, f32 recurrent state, f32 master weights and
+AdamW) cut to --layers blocks (24 blocks are 26 B parameters x 18 bytes and fit no GPU; every block costs the same,
+so `extrapolated_24_blocks_tok_s` = value x layers / 24). One step = forward + BPTT + optimizer over a FIXED global
+batch of 64 sequences x 4096 random bytes ("scaling": "strong"), split by sequence over the ranks, micro-batches of at
+most 32 sequences; at N > 1 the gradient exchange (NCCL, inside the library) is queued from inside the backward and the
+optimizer is sharded over the ranks. `value` is timed with CUDA events on the launching stream; `e2e` is the same K
+steps by the wall clock through the host-pointer entry point (`asca_model_forward_backward_host`: token ids and
+targets are host arrays copied in every micro-batch, the loss is copied out) plus the optimizer step.
 
-Default mode: bf16 activations (tcgen05 tensor cores, f32 accumulation, f32 recurrent state and
-gates; parity tolerance 2e-2). --dtype f32 runs the f32-exact FFMA kernels (tolerance 1e-5).
+Sub-records under "records", each with its own roofline / cpu_baseline / e2e / clocks:
+  decode      ~125M decode configuration: 256 streams (sharded over ranks), 512-token prefill, 2048 greedy tokens
+  moe         isolated hash-MoE layer, 65,536 Zipf tokens, d 1024, 64 experts of 1024 -> 4096 -> 1024, fwd + bwd   (N = 1)
+  delta_bf16  isolated gated delta-rule op, B8 H16 T4096 dh128 chunk 64, fwd + BPTT, tensor-core kernels          (N = 1)
+  delta_f32   the same op on the f32-exact kernels                                                                (N = 1)
 
-Under torchrun every rank owns its own batch of B sequences (weak scaling, no collective on the
-data path: chains are independent per (sequence, head)). Timing: CUDA events on the launching
-stream, barrier + synchronize on both sides, max over ranks. The inputs (4 x 268 MB in f32)
-are larger than the 126 MB L2, so no flush is needed between iterations.
+Inputs are synthetic and seeded: token ids come from the reference's xorshift128+ generator
+(rust/src/tensor.rs:306-337); weights and float activations are drawn on the device with torch's seeded generator
+(the reference's scalar Box-Muller would need minutes for 1e9 numbers). They stand in for the TinyStories bytes the
+reference trains on. Timing: >= 3 warm-up steps, CUDA events on the launching stream, barrier + synchronize on both
+sides, max over ranks; every workload is far larger than the 126 MB L2, so nothing is flushed between iterations.
 
-`--impl reference` times the reference's own CPU algorithm for the same path (its Rust crate
-cannot be built here, so this is the C++ restatement under oracle/) on the host cores, on a
-bounded sample of the same workload.
+`--impl reference` times the reference's own CPU algorithm for the train step (its Rust crate cannot be built here:
+the C++ restatement under oracle/) on all host cores, on a bounded slice (one block, one sequence of 512 tokens),
+scaled linearly in tokens x blocks to the headline configuration and labelled as that.
 """
 from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import sys
 import threading
@@ -35,21 +48,25 @@ import numpy as np
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-B, H, T, DH, CHUNK = 8, 16, 4096, 128, 64
-METRIC = "delta fwd+bwd tok/s"
-WORKLOAD = f"isolated gated delta-rule op fwd+BPTT: B{B} H{H} T{T} dh{DH} chunk{CHUNK} per GPU"
+METRIC = "train tok/s (delta+hashMoE)"
+TRAIN = dict(V=256, d=2048, H=16, E=64, F=4096, T=4096, global_batch=64, micro=32)
+DECODE = dict(V=256, d=768, H=12, L=12, E=16, F=3072, streams=256, prefill=512, tokens=2048)
+MOE = dict(n=65536, d=1024, F=4096, E=64)
+DELTA = dict(B=8, H=16, T=4096, dh=128, chunk=64)
+LR = 3e-4
 
 
-def measured_peaks():
+def peaks():
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
         d = json.loads(p.read_text())
-        return float(d["hbm_gbs"]), "measured"
-    return 6650.0, "fallback"
+        return {"hbm": float(d["hbm_gbs"]), "burst": float(d["bf16_tflops"]), "sustained": float(d["bf16_tflops_sustained"]),
+                "source": "measured"}
+    return {"hbm": 6650.0, "burst": 1590.0, "sustained": 1400.0, "source": "fallback"}
 
 
 class ClockSampler:
-    """SM clock and throttle reasons sampled every 2 ms (NVML, read-only) while the timed region runs."""
+    """SM clock and throttle reasons sampled every 2 ms (NVML, read-only) while a timed region runs."""
 
     REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
@@ -62,12 +79,10 @@ class ClockSampler:
     def start(self):
         try:
             import pynvml
-
-            pynvml.nvmlInit()
-            # CUDA_VISIBLE_DEVICES may renumber devices: match by the UUID torch reports
             import torch
 
-            uuid = str(torch.cuda.get_device_properties(self.index).uuid)
+            pynvml.nvmlInit()
+            uuid = str(torch.cuda.get_device_properties(self.index).uuid)   # CUDA_VISIBLE_DEVICES may renumber devices
             self.h = None
             for i in range(pynvml.nvmlDeviceGetCount()):
                 h = pynvml.nvmlDeviceGetHandleByIndex(i)
@@ -82,9 +97,10 @@ class ClockSampler:
         except Exception as e:  # noqa: BLE001
             self.err = repr(e)
             self.nv = None
-            return
+            return self
         self._th = threading.Thread(target=self._run, daemon=True)
         self._th.start()
+        return self
 
     def _run(self):
         nv = self.nv
@@ -106,46 +122,137 @@ class ClockSampler:
                 "samples": len(self.sm)}
 
 
-def make_inputs(seed: int, b: int, t: int, h: int, dh: int):
-    """Seeded synthetic inputs with the workload's distributions (numpy, host)."""
-    rs = np.random.RandomState(seed)
-    n, d = b * t, h * dh
-    q = rs.standard_normal((n, h, dh)).astype(np.float32)
-    k = rs.standard_normal((n, h, dh)).astype(np.float32)
-    qn = np.linalg.norm(q, axis=-1).astype(np.float32)
-    kn = np.linalg.norm(k, axis=-1).astype(np.float32)
-    q = (q / qn[..., None]).reshape(n, d)
-    k = (k / kn[..., None]).reshape(n, d)
-    v = rs.standard_normal((n, d)).astype(np.float32)
-    d_o = rs.standard_normal((n, d)).astype(np.float32)
-    alpha = (1 / (1 + np.exp(-(2 + 0.5 * rs.standard_normal((n, h)))))).astype(np.float32)
-    beta = (1 / (1 + np.exp(-rs.standard_normal((n, h))))).astype(np.float32)
-    return q, k, v, alpha, beta, qn, kn, d_o
+def reference_ids(seed: int, n: int, below: int = 256) -> np.ndarray:
+    """n token ids from the reference's generator (`rng.below`, rust/src/tensor.rs:322-324)."""
+    from asca_b200.train import Rng
+
+    r = Rng(seed)
+    return np.fromiter((r.below(below) for _ in range(n)), dtype=np.uint32, count=n)
 
 
-# ------------------------------------------------------------------ reference arm (CPU)
-def cpu_sample(threads: int):
-    """Bounded sample of the same workload: T tokens of dh=128 chains, one chain per host thread
-    (the reference's BPTT partitioning, rust/src/delta.rs:461-475), full sequence length cut to
-    keep the run at 10-30 s. Threads are capped at 64: every running chain holds its own
-    (T+1)*dh*dh state history (268 MB at T=4096)."""
+def zipf_ids(seed: int, n: int, s: float = 1.1) -> np.ndarray:
+    """Byte ids with Zipf(s) popularity over ranks 1..256 (id = rank - 1), inverse CDF of the reference's `rng.uniform()`."""
+    from asca_b200.train import Rng
+
+    w = 1.0 / np.arange(1, 257) ** s
+    cdf = np.cumsum(w) / w.sum()
+    r = Rng(seed)
+    u = np.fromiter((r.uniform() for _ in range(n)), dtype=np.float64, count=n)
+    return np.minimum(np.searchsorted(cdf, u), 255).astype(np.uint32)
+
+
+class Harness:
+    """Process-wide plumbing: ranks, the library context, torch.distributed for barriers and max-over-ranks."""
+
+    def __init__(self):
+        import torch
+        import torch.distributed as dist
+
+        import asca_b200
+
+        self.torch, self.dist = torch, dist
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local = int(os.environ.get("LOCAL_RANK", "0"))
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py: no CUDA device; the hot path has no CPU fallback")
+        torch.cuda.set_device(self.local)
+        self.dev = torch.device("cuda", self.local)
+        if self.world > 1:
+            dist.init_process_group("nccl", device_id=self.dev)
+        self.gpu = asca_b200.Gpu(self.local)
+        self.gpu.use_torch_stream()
+        self.peaks = peaks()
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def max_over_ranks(self, x: float) -> float:
+        if self.world == 1:
+            return float(x)
+        t = self.torch.tensor([x], device=self.dev, dtype=self.torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def timed(self, fn, steps, warmup, sample_clocks=True):
+        """W untimed calls, then K calls between CUDA events on the launching stream and by the wall clock, barrier +
+        synchronize on both sides, max over ranks. Returns (device ms per call, wall ms per call, clocks, launches)."""
+        torch = self.torch
+        for _ in range(warmup):
+            fn()
+        self.barrier()
+        sampler = ClockSampler(self.local).start() if (sample_clocks and self.rank == 0) else None
+        l0 = self.gpu.launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        self.barrier()
+        t0 = time.perf_counter()
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        self.barrier()
+        wall = (time.perf_counter() - t0) * 1e3 / steps
+        dev_ms = e0.elapsed_time(e1) / steps
+        clocks = sampler.stop() if sampler else None
+        return self.max_over_ranks(dev_ms), self.max_over_ranks(wall), clocks, self.gpu.launch_count() - l0
+
+    def kernel_table(self, fn):
+        """One extra call with the library's per-launch CUDA events on: {kernel: (launches, total ms, total work)}."""
+        self.gpu.profile(True)
+        fn()
+        self.torch.cuda.synchronize()
+        tab = {}
+        for name, ms, work in self.gpu.profile_read(with_work=True):
+            n, t, w = tab.get(name, (0, 0.0, 0.0))
+            tab[name] = (n + 1, t + ms, w + work)
+        self.gpu.profile(False)
+        return tab
+
+    def fill_normal(self, ptr, n, seed, scale=0.02):
+        """n f32 numbers N(0, scale) written at device address ptr (seeded, identical on every rank)."""
+        from asca_b200 import dp
+
+        torch = self.torch
+        g = torch.Generator(device=self.dev).manual_seed(seed)
+        t = dp.device_tensor(ptr, n, self.local)
+        for lo in range(0, n, 1 << 28):
+            hi = min(n, lo + (1 << 28))
+            t[lo:hi] = torch.randn(hi - lo, generator=g, dtype=torch.float32, device=self.dev) * scale
+
+
+# ------------------------------------------------------------------ CPU arm (the oracle as the timed baseline)
+def cpu_threads():
+    return min(os.cpu_count() or 1, 64)
+
+
+def cpu_train_slice(steps=1, warmup=0, layers=1, tokens=512):
+    """The restated CPU train step (forward + BPTT + AdamW) on one block, one sequence of `tokens` bytes, at the
+    training configuration's widths, all host cores. Returns (seconds per step, sample description)."""
     import oracle
 
     oracle.build()
-    t_s = T
-    h_s = max(threads, 1)
-    arrs = make_inputs(1, 2, t_s, h_s, DH)
-    return oracle, arrs, (2, t_s, h_s, DH)
-
-
-def time_cpu(steps: int, warmup: int):
-    threads = min(os.cpu_count() or 1, 64)
-    oracle, arrs, (b, t, h, dh) = cpu_sample(threads)
-    q, k, v, alpha, beta, qn, kn, d_o = arrs
+    oracle.set_threads(0)
+    c = TRAIN
+    m = oracle.Model(c["V"], c["d"], c["H"], layers, c["E"], c["F"])
+    # uniform with the N(0, 0.02) standard deviation: the arithmetic does not depend on the values, and a billion
+    # normals would take longer to draw than the step takes
+    g = np.random.default_rng(0)
+    for lo in range(0, m.n, 1 << 27):
+        hi = min(m.n, lo + (1 << 27))
+        m.params[lo:hi] = (g.random(hi - lo, dtype=np.float32) - 0.5) * np.float32(0.02 * math.sqrt(12.0))
+    ids = reference_ids(1, tokens)
+    tg = np.roll(ids, -1).astype(np.uint32)
+    grads = np.zeros(m.n, np.float32)
+    mo, vo = np.zeros(m.n, np.float32), np.zeros(m.n, np.float32)
+    cnt = 0
 
     def step():
-        oracle.delta_scan(q, k, v, alpha, beta, b, t, h, dh)
-        oracle.delta_bptt(q, k, v, alpha, beta, qn, kn, d_o, b, t, h, dh, max_workers=threads)
+        nonlocal cnt
+        grads[:] = 0
+        m.forward_backward(ids, tg, 1, grads=grads)
+        cnt = m.adamw_step(grads, mo, vo, cnt, LR)
 
     for _ in range(warmup):
         step()
@@ -153,134 +260,425 @@ def time_cpu(steps: int, warmup: int):
     for _ in range(steps):
         step()
     dt = (time.perf_counter() - t0) / steps
-    chain_steps = b * t * h
-    tok_s = chain_steps / H / dt  # a workload token carries H=16 heads
-    sample = (f"{b * h} chains x {t} tokens, dh={dh}, scan + BPTT with per-chain state history, one chain per thread; "
-              f"tok/s = chain-steps/s / {H} heads")
-    return tok_s, dt * 1e3, threads, sample
+    return dt, (f"{layers} block, 1 sequence x {tokens} tokens of the training configuration's widths, f32, forward + BPTT + "
+                f"AdamW; scaled linearly in tokens x blocks to the benchmark's step")
+
+
+def cpu_baseline_train(layers, steps=1, warmup=0):
+    dt, sample = cpu_train_slice(steps, warmup, 1, 512)
+    tok_s = 512.0 / (dt * layers)          # tokens/s of the `layers`-block model
+    return {"value": tok_s, "unit": "tok/s", "cores": cpu_threads(), "kind": "port", "sample": sample,
+            "slice_seconds_per_step": dt, "extrapolated": True}
 
 
 def run_reference(args):
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+    if int(os.environ.get("RANK", "0")) != 0:
         return
-    steps, warmup = max(args.steps, 1), max(args.warmup, 0)
-    steps = min(steps, 5)
-    tok_s, ms, threads, sample = time_cpu(steps, min(warmup, 1))
+    steps, warmup = max(1, min(args.steps, 2)), min(max(args.warmup, 0), 1)
+    base = cpu_baseline_train(args.layers, steps, warmup)
+    c = TRAIN
+    n_tok = c["global_batch"] * c["T"]
     line = {
-        "impl": "reference", "metric": METRIC, "value": tok_s, "unit": "tok/s", "n_gpus": args.gpus, "steps": steps,
-        "warmup": min(warmup, 1), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "l2": "n/a (CPU)"},
-        "cpu_baseline": {"value": tok_s, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample},
-        "e2e": {"value": tok_s, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "impl": "reference", "metric": METRIC, "value": base["value"], "unit": "tok/s", "n_gpus": args.gpus, "steps": steps,
+        "warmup": warmup, "ms_per_step": n_tok / base["value"] * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": train_config(args.layers, 1, "n/a (CPU)"),
+        "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
+        "note": "the reference's CPU algorithm (C++ restatement) on a bounded slice, scaled to the configuration; "
+                "steps and warm-up are capped so that the run ends within minutes",
     }
     print(json.dumps(line))
 
 
+# ------------------------------------------------------------------ train step (headline)
+def train_config(layers, world, l2):
+    c = TRAIN
+    return {"workload": (f"ASCA 1.3B-class data-parallel training step, {layers} of 24 blocks: d {c['d']}, {c['H']} heads of "
+                         f"{c['d'] // c['H']}, {c['E']} hash experts of {c['d']}->{c['F']}->{c['d']}, byte vocabulary; global batch "
+                         f"{c['global_batch']} x {c['T']} random bytes; forward + BPTT + AdamW"),
+            "layers": layers, "global_batch": c["global_batch"], "seq_len": c["T"],
+            "parallelism": f"dp{world} by sequence; heads and experts local; NCCL gradient exchange overlapped with the backward"
+                           + ("; optimizer sharded over the ranks" if world > 1 else ""),
+            "l2": l2}
+
+
+def train_flop_per_token(layers):
+    c = TRAIN
+    d, H, F, V = c["d"], c["H"], c["F"], c["V"]
+    per_layer = d * 3 * d + d * 2 * H + d * d + 2 * d * F          # GEMM parameters a token touches per block
+    return 6 * (layers * per_layer + d * V) + 22 * (d // H) ** 2 * H * layers
+
+
+def run_train(hs: Harness, args):
+    import asca_b200
+    from asca_b200 import dp
+
+    torch = hs.torch
+    c = TRAIN
+    L = args.layers
+    own = dp.shard_sequences(c["global_batch"], hs.rank, hs.world)
+    n_micro = max(1, -(-len(own) // c["micro"]))
+    mb = len(own) // n_micro
+    assert mb * n_micro == len(own), "the rank's share must be a whole number of micro-batches"
+    model = asca_b200.Model(hs.gpu, c["V"], c["d"], c["H"], L, c["E"], c["F"])
+    model.set_compute(asca_b200.BF16)
+    hs.fill_normal(model.buffers()[0], model.n, seed=0)
+    model.params_changed()
+    ids_all = reference_ids(1, c["global_batch"] * c["T"]).reshape(c["global_batch"], c["T"])
+    ids = torch.from_numpy(ids_all[own.start:own.stop].astype(np.int32)).pin_memory()
+    tg = torch.roll(ids, -1, dims=1).contiguous().pin_memory()
+    ids_np, tg_np = ids.numpy().view(np.uint32), tg.numpy().view(np.uint32)
+    model.set_grad_scale(1.0 / n_micro)
+    comm = dp.Comm.from_torch(hs.gpu)
+    ov = dp.ShardedOverlap(model, comm) if hs.world > 1 else dp.GradOverlap(model, comm)
+    last = {"loss": float("nan")}
+
+    def step():
+        model.zero_grads()
+        loss = 0.0
+        for i in range(n_micro):
+            rows = slice(i * mb, (i + 1) * mb)
+            if i == n_micro - 1:
+                with ov:
+                    loss += model.forward_backward(ids_np[rows].reshape(-1), tg_np[rows].reshape(-1), mb)
+            else:
+                loss += model.forward_backward(ids_np[rows].reshape(-1), tg_np[rows].reshape(-1), mb)
+        ov.step(LR)
+        last["loss"] = loss / n_micro
+
+    first_loss = None
+    step()
+    torch.cuda.synchronize()
+    first_loss = last["loss"]
+    dev_ms, wall_ms, clocks, launches = hs.timed(step, args.steps, max(args.warmup - 1, 2))
+    # exposed collectives, per step, max over ranks (two more steps; reading the events synchronises)
+    tl = {}
+    for _ in range(2):
+        step()
+        t = ov.timeline()
+        for k, v in t.items():
+            tl[k] = max(tl.get(k, 0.0), hs.max_over_ranks(v))
+    free_b, total_b = torch.cuda.mem_get_info()
+    table = hs.kernel_table(step) if hs.rank == 0 else None
+    n_tok = c["global_batch"] * c["T"]
+    flop_tok = train_flop_per_token(L)
+    tf_per_gpu = n_tok * flop_tok / (dev_ms * 1e-3) / 1e12 / hs.world
+    rec = None
+    if hs.rank == 0:
+        pk = hs.peaks
+        total_k = sum(t for _, t, _ in table.values()) or 1.0
+        kernels = {k: {"launches": n, "ms": round(t, 3), "share_of_profiled": round(t / total_k, 4),
+                       **({"TFLOP/s": round(w / (t * 1e-3) / 1e12, 1)} if "gemm_tc" in k and t > 0 else {}),
+                       **({"GB/s": round(w / (t * 1e-3) / 1e9, 1)} if "adamw" in k and t > 0 else {})}
+                   for k, (n, t, w) in sorted(table.items(), key=lambda kv: -kv[1][1])}
+        top = max(table, key=lambda k: table[k][1])
+        n_top, t_top, w_top = table[top]
+        top_tf = w_top / (t_top * 1e-3) / 1e12 if "gemm_tc" in top else None
+        h2d = 2 * len(own) * c["T"] * 4
+        rec = {
+            "metric": METRIC, "value": n_tok / (dev_ms * 1e-3), "unit": "tok/s", "n_gpus": hs.world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": dev_ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": train_config(L, hs.world, "activations and weights of a step (tens of GB) far exceed L2; no flush"),
+            "extrapolated_24_blocks_tok_s": n_tok / (dev_ms * 1e-3) * L / 24,
+            "micro_batches_per_rank": n_micro, "sequences_per_micro_batch": mb, "params": model.n,
+            "loss_first_step": first_loss, "loss_last_step": last["loss"],
+            "roofline": {"bound": "tensor", "achieved": tf_per_gpu, "peak": pk["sustained"], "unit": "TFLOP/s",
+                         "frac": tf_per_gpu / pk["sustained"], "frac_of_burst": tf_per_gpu / pk["burst"], "peak_source": pk["source"],
+                         "algorithmic_flop_per_token": flop_tok, "traffic": None,
+                         "note": "whole step per GPU: 6 x GEMM parameters a token touches + 22 dh^2 H per block for the recurrence, "
+                                 "/ CUDA-event step time / the sustained cuBLAS bf16 figure (a kernel timed inside a long step); "
+                                 "dominant kernel below against the burst figure (timed alone by its own events)",
+                         "dominant_kernel": {"kernel": top, "launches_per_step": n_top, "ms_per_step": t_top,
+                                             "achieved": top_tf, "unit": "TFLOP/s", "peak": pk["burst"],
+                                             "frac": (top_tf / pk["burst"]) if top_tf else None}},
+            "timeline_ms": {**{k: round(v, 3) for k, v in tl.items()},
+                            "note": "per step, max over ranks: how long the end of the backward waited for the gradient exchange, the "
+                                    "optimizer update, how long the bf16 weight all-gather ran past the update, and how long the next "
+                                    "forward waited for gathered weights; the rest of the step is compute"},
+            "kernels_profiled_step": kernels,
+            "e2e": {"value": n_tok / (wall_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": h2d * hs.world,
+                    "d2h_bytes_per_step": 4 * n_micro * hs.world, "ms_per_step": wall_ms,
+                    "api": "asca_model_forward_backward_host (host token ids and targets in, loss out, every micro-batch) + "
+                           "asca_model_dp_step; wall clock over the same K steps"},
+            "gpu_launches": launches, "clocks": clocks,
+            "device_memory_gb": {"used": round((total_b - free_b) / 1e9, 1), "total": round(total_b / 1e9, 1)},
+        }
+    ov.detach()
+    comm.close()
+    model.free()
+    hs.gpu.lib.asca_ctx_trim(hs.gpu._ctx)
+    torch.cuda.empty_cache()
+    return rec
+
+
+# ------------------------------------------------------------------ decode
+def cpu_baseline_decode():
+    """The restated CPU decode (Model::step per stream, f32) on min(cores, 16) streams x 6 tokens, one thread per stream."""
+    import oracle
+
+    oracle.build()
+    c = DECODE
+    m = oracle.Model(c["V"], c["d"], c["H"], c["L"], c["E"], c["F"])
+    g = np.random.default_rng(0)
+    for lo in range(0, m.n, 1 << 27):
+        hi = min(m.n, lo + (1 << 27))
+        m.params[lo:hi] = (g.random(hi - lo, dtype=np.float32) - 0.5) * np.float32(0.02 * math.sqrt(12.0))
+    n_streams, n_tok = min(cpu_threads(), 16), 6
+    oracle.set_threads(1)
+    states = [m.new_decode_state() for _ in range(n_streams)]
+    toks = reference_ids(3, n_streams * n_tok).reshape(n_streams, n_tok)
+
+    def run(s):
+        for t in range(n_tok):
+            m.step(int(toks[s, t]), states[s])
+
+    run(0)
+    t0 = time.perf_counter()
+    ths = [threading.Thread(target=run, args=(s,)) for s in range(n_streams)]
+    for th in ths:
+        th.start()
+    for th in ths:
+        th.join()
+    dt = time.perf_counter() - t0
+    oracle.set_threads(0)
+    return {"value": n_streams * n_tok / dt, "unit": "tok/s", "cores": n_streams, "kind": "port",
+            "sample": f"{n_streams} streams x {n_tok} tokens, one stream per thread, f32 Model::step of the decode configuration"}
+
+
+def run_decode(hs: Harness, args):
+    import asca_b200
+    from asca_b200 import dp
+
+    torch = hs.torch
+    c = DECODE
+    V, d, H, L, E, F = c["V"], c["d"], c["H"], c["L"], c["E"], c["F"]
+    dh = d // H
+    own = dp.shard_sequences(c["streams"], hs.rank, hs.world)
+    ns = len(own)
+    model = asca_b200.Model(hs.gpu, V, d, H, L, E, F)
+    model.set_compute(asca_b200.BF16)
+    hs.fill_normal(model.buffers()[0], model.n, seed=0)
+    model.params_changed()
+    prompts = reference_ids(2, c["streams"] * c["prefill"]).reshape(c["streams"], c["prefill"])[own.start:own.stop]
+    state = model.new_decode_state(ns)
+    nxt = None
+    for t in range(c["prefill"]):      # the reference's decoder prefills by stepping (rust/src/main.rs:367-371); untimed
+        _, nxt = model.decode_step(state, prompts[:, t].copy(), want_logits=False)
+    cur = {"ids": nxt}
+    chunk = 64
+
+    def greedy_chunk():
+        cur["ids"] = model.decode_greedy(state, cur["ids"], chunk)[-1]
+
+    n_chunks = c["tokens"] // chunk
+    dev_ms, wall_ms, clocks, launches = hs.timed(greedy_chunk, n_chunks, 3)
+    ms_step, wall_step = dev_ms / chunk, wall_ms / chunk
+    table = hs.kernel_table(lambda: model.decode_greedy(state, cur["ids"], 4)) if hs.rank == 0 else None
+    rec = None
+    if hs.rank == 0:
+        pk = hs.peaks
+        state_bytes = 2 * L * H * dh * dh * 4 * ns
+        weight_bytes = (L * (d * 3 * d + d * 2 * H + d * d + 2 * E * d * F) + d * V) * 2
+        step_bytes = state_bytes + weight_bytes
+        gbs = step_bytes / (ms_step * 1e-3) / 1e9
+        total_k = sum(t for _, t, _ in table.values()) or 1.0
+        top = max(table, key=lambda k: table[k][1])
+        n_top, t_top, w_top = table[top]
+        kernels = {k: {"launches": n // 4, "ms_per_step": round(t / 4, 4), "share_of_profiled": round(t / total_k, 4),
+                       "GB/s": round(w / (t * 1e-3) / 1e9, 1) if w else None}
+                   for k, (n, t, w) in sorted(table.items(), key=lambda kv: -kv[1][1])}
+        rec = {
+            "metric": "decode tok/s", "value": c["streams"] * 1e3 / ms_step, "unit": "tok/s", "n_gpus": hs.world,
+            "steps": c["tokens"], "ms_per_step": ms_step, "scaling": "strong", "dtype": "bf16",
+            "config": {"workload": (f"ASCA ~125M greedy decode: {L} blocks, d {d}, {H} heads of {dh}, {E} hash experts of {d}->{F}->{d}, bf16 "
+                                    f"weights; {c['streams']} streams sharded over {hs.world} GPU(s), {c['prefill']}-token prefill (stepped, "
+                                    f"untimed), {c['tokens']} greedy tokens timed"),
+                       "streams_per_gpu": ns, "steps_per_call": chunk,
+                       "l2": "a step reads 1.9 GB of weights and 1.2 GB of state: far larger than L2, no flush"},
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm"], "unit": "GB/s", "frac": gbs / pk["hbm"],
+                         "peak_source": pk["source"], "algorithmic_bytes": step_bytes, "state_bytes": state_bytes,
+                         "weight_bytes": weight_bytes, "traffic": None,
+                         "note": "per GPU and step: recurrent state read + written once (2 L H dh^2 4 B per stream) + every bf16 weight "
+                                 "byte once (with 256 streams over 16 experts every expert is hit) / CUDA-event time of a step",
+                         "dominant_kernel": {"kernel": top, "ms_per_step": t_top / 4,
+                                             "achieved": (w_top / (t_top * 1e-3) / 1e9) if w_top else None, "unit": "GB/s",
+                                             "note": "from a separate pass with per-launch events, which serialises the chain"}},
+            "kernels_profiled_step": kernels,
+            "e2e": {"value": c["streams"] * 1e3 / wall_step, "unit": "tok/s", "h2d_bytes_per_step": 4 * ns * hs.world / chunk,
+                    "d2h_bytes_per_step": 4 * ns * hs.world, "ms_per_step": wall_step,
+                    "api": "asca_model_decode_greedy_host: ids in from the host, the chosen tokens of every step back to the host, "
+                           f"one call per {chunk} steps; wall clock"},
+            "gpu_launches": launches, "clocks": clocks,
+            "cpu_baseline": cpu_baseline_decode() if (hs.world == 1 and not args.no_cpu) else None,
+        }
+    model.free()
+    torch.cuda.empty_cache()
+    return rec
+
+
+# ------------------------------------------------------------------ isolated hash-MoE layer
+def run_moe(hs: Harness, args):
+    from asca_b200 import ops
+
+    torch = hs.torch
+    c = MOE
+    n, d, F, E = c["n"], c["d"], c["F"], c["E"]
+    dev = hs.dev
+    f32 = dict(dtype=torch.float32, device=dev)
+    g = torch.Generator(device=dev).manual_seed(0)
+    ids_h = zipf_ids(4, n)
+    ids = torch.from_numpy(ids_h.view(np.int32)).to(dev)
+    xn = torch.randn(n, d, generator=g, **f32).bfloat16()
+    w1 = (torch.randn(d, E * F, generator=g, **f32) * 0.02).bfloat16()
+    w2 = (torch.randn(E * F, d, generator=g, **f32) * 0.02).bfloat16()
+    b1, b2 = torch.zeros(E * F, **f32), torch.zeros(d, **f32)
+    dout = torch.randn(n, d, generator=g, **f32)
+    perm, off = ops.moe_dispatch(hs.gpu, ids, E)
+    out, pre_p, hid_p = ops.moe_fwd(hs.gpu, xn, w1, b1, w2, b2, perm, off, F, E)
+    grads = ops.moe_bwd(hs.gpu, xn, w1, w2, pre_p, hid_p, dout, perm, off, F, E)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    acc = {"fwd": 0.0, "bwd": 0.0, "n": 0}
+
+    def step():
+        ev[0].record()
+        ops.moe_dispatch(hs.gpu, ids, E)
+        ops.moe_fwd(hs.gpu, xn, w1, b1, w2, b2, perm, off, F, E, out=out, pre_p=pre_p, hid_p=hid_p)
+        ev[1].record()
+        ops.moe_bwd(hs.gpu, xn, w1, w2, pre_p, hid_p, dout, perm, off, F, E, grads=grads)
+        ev[2].record()
+
+    dev_ms, _, clocks, launches = hs.timed(step, 150, 3)
+    for _ in range(5):
+        step()
+        torch.cuda.synchronize()
+        acc["fwd"] += ev[0].elapsed_time(ev[1])
+        acc["bwd"] += ev[1].elapsed_time(ev[2])
+        acc["n"] += 1
+    table = hs.kernel_table(step)
+    # end to end: host ids, activations and upstream gradient in; outputs and input gradient out (weights stay resident)
+    ids_p = torch.from_numpy(ids_h.view(np.int32)).pin_memory()
+    xn_p, dout_p = xn.cpu().pin_memory(), dout.cpu().pin_memory()
+    out_p, dxn_p = torch.empty((n, d)).pin_memory(), torch.empty((n, d)).pin_memory()
+
+    def e2e_step():
+        ids.copy_(ids_p, non_blocking=True)
+        xn.copy_(xn_p, non_blocking=True)
+        dout.copy_(dout_p, non_blocking=True)
+        step()
+        out_p.copy_(out, non_blocking=True)
+        dxn_p.copy_(grads[4], non_blocking=True)
+        torch.cuda.synchronize()
+
+    _, e2e_ms, _, _ = hs.timed(e2e_step, 10, 2, sample_clocks=False)
+    pk = hs.peaks
+    flop = 12.0 * n * d * F
+    tf = flop / (dev_ms * 1e-3) / 1e12
+    total_k = sum(t for _, t, _ in table.values()) or 1.0
+    top = max(table, key=lambda k: table[k][1])
+    n_top, t_top, w_top = table[top]
+    cpu = None
+    if not args.no_cpu:
+        import oracle
+
+        oracle.build()
+        oracle.set_threads(0)
+        ns = 2048
+        sel = np.arange(0, n, n // ns)[:ns]
+        t0 = time.perf_counter()
+        oracle.moe_forward_backward(xn[sel].float().cpu().numpy(), w1.float().cpu().numpy(), b1.cpu().numpy(), w2.float().cpu().numpy(),
+                                    b2.cpu().numpy(), ids_h[sel].copy(), dout[sel].cpu().numpy(), F, E)
+        dt = time.perf_counter() - t0
+        cpu = {"value": ns / dt, "unit": "tok/s", "cores": cpu_threads(), "kind": "port",
+               "sample": f"{ns} of the 65,536 tokens (every 32nd) through the restated f32 HashMoe forward + backward with the full weights"}
+    return {
+        "metric": "hash-MoE layer fwd+bwd tok/s", "value": n * 1e3 / dev_ms, "unit": "tok/s", "n_gpus": 1, "steps": 150, "ms_per_step": dev_ms,
+        "ops_ms": {"dispatch+fwd": acc["fwd"] / acc["n"], "bwd": acc["bwd"] / acc["n"]}, "dtype": "bf16",
+        "config": {"workload": f"isolated hash-MoE layer: {n} tokens, byte ids Zipf(1.1), d {d}, {E} experts of {d}->{F}->{d}, bf16 weights "
+                               "N(0,0.02), activations N(0,1); dispatch + grouped expert FFN + combine, forward + backward",
+                   "l2": "weights 1.07 GB, activations 0.8 GB per pass: larger than L2, no flush"},
+        "roofline": {"bound": "tensor", "achieved": tf, "peak": pk["sustained"], "unit": "TFLOP/s", "frac": tf / pk["sustained"],
+                     "frac_of_burst": tf / pk["burst"], "peak_source": pk["source"], "algorithmic_flop": flop, "traffic": None,
+                     "note": "4 N d F forward + 8 N d F backward / CUDA-event time of a pass",
+                     "dominant_kernel": {"kernel": top, "launches_per_step": n_top, "ms_per_step": t_top,
+                                         "achieved": w_top / (t_top * 1e-3) / 1e12 if w_top else None, "unit": "TFLOP/s",
+                                         "peak": pk["burst"], "frac": (w_top / (t_top * 1e-3) / 1e12 / pk["burst"]) if w_top else None}},
+        "kernels_profiled_step": {k: {"launches": a, "ms": round(t, 3), "share_of_profiled": round(t / total_k, 4),
+                                      "TFLOP/s": round(w / (t * 1e-3) / 1e12, 1) if w else None}
+                                  for k, (a, t, w) in sorted(table.items(), key=lambda kv: -kv[1][1])},
+        "e2e": {"value": n * 1e3 / e2e_ms, "unit": "tok/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": ids_p.numel() * 4 + xn_p.numel() * 2 + dout_p.numel() * 4,
+                "d2h_bytes_per_step": out_p.numel() * 4 + dxn_p.numel() * 4,
+                "api": "asca_moe_dispatch + asca_moe_fwd + asca_moe_bwd on device buffers, pinned-host copies of ids, activations, "
+                       "upstream gradient in and outputs, input gradient out inside the timed region; weights resident"},
+        "gpu_launches": launches, "clocks": clocks, "cpu_baseline": cpu,
+    }
+
+
+# ------------------------------------------------------------------ isolated delta op
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch at B=2, H=16, T=4096, dh=128 (32 chains), divided by 32:
 # traffic is proportional to the number of chains (profiles/delta_tc_bf16_cfg2.md).
 NCU_TRAFFIC_PER_CHAIN = {
-    ("bf16", "delta_bwd_tc_kernel"): (438.934784e6 + 179.197440e6) / 32,
-    ("bf16", "delta_fwd_tc_kernel"): (151.054336e6 + 63.292160e6) / 32,
-    ("bf16", "delta_prep_tc_kernel"): (102.092288e6 + 310.865920e6) / 32,
+    "delta_bwd_tc_kernel": (438.934784e6 + 179.197440e6) / 32,
+    "delta_fwd_tc_kernel": (151.054336e6 + 63.292160e6) / 32,
+    "delta_prep_tc_kernel": (102.092288e6 + 310.865920e6) / 32,
 }
 
 
-# ------------------------------------------------------------------ our arm (GPU)
-def run_ours(args):
-    import torch
-    import torch.distributed as dist
-
-    import asca_b200
+def run_delta(hs: Harness, args, bf16: bool):
     from asca_b200 import ops
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py: no CUDA device; the hot path has no CPU fallback")
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    gpu = asca_b200.Gpu(local)
-    gpu.use_torch_stream()
-    dev = torch.device("cuda", local)
-    bf16 = args.dtype == "bf16"
-    b, t, h, dh = args.batch, args.seq, H, DH
-
-    host = make_inputs(1234 + rank, b, t, h, dh)
-    pin = [torch.from_numpy(a).pin_memory() for a in host]
-    q, k, v, alpha, beta, qn, kn, d_o = (x.to(dev) for x in pin)
+    torch = hs.torch
+    c = DELTA
+    b, h, t, dh, chunk = c["B"], c["H"], c["T"], c["dh"], c["chunk"]
+    n, d = b * t, h * dh
+    dev = hs.dev
+    f32 = dict(dtype=torch.float32, device=dev)
+    g = torch.Generator(device=dev).manual_seed(1234)
+    q = torch.randn(n, h, dh, generator=g, **f32)
+    k = torch.randn(n, h, dh, generator=g, **f32)
+    qn, kn = q.norm(dim=-1).contiguous(), k.norm(dim=-1).contiguous()
+    q = (q / qn[..., None]).reshape(n, d).contiguous()
+    k = (k / kn[..., None]).reshape(n, d).contiguous()
+    v = torch.randn(n, d, generator=g, **f32)
+    d_o = torch.randn(n, d, generator=g, **f32)
+    alpha = torch.sigmoid(2 + 0.5 * torch.randn(n, h, generator=g, **f32))
+    beta = torch.sigmoid(torch.randn(n, h, generator=g, **f32))
+    host32 = [x.cpu() for x in (q, k, v, alpha, beta, qn, kn, d_o)]
     if bf16:
         q, k, v, d_o = (x.bfloat16() for x in (q, k, v, d_o))
-    n, d = b * t, h * dh
-    f32 = dict(dtype=torch.float32, device=dev)
     o = torch.empty_like(q)
-    ckpt = torch.empty(ops.delta_ckpt_floats(gpu, b, t, h, dh, CHUNK), **f32)
+    ckpt = torch.empty(ops.delta_ckpt_floats(hs.gpu, b, t, h, dh, chunk), **f32)
     d_qkv = torch.empty((n, 3 * d), **f32)
     d_gate = torch.empty((n, 2 * h), **f32)
 
-    def step(ev=None):
-        if ev:
-            ev[0].record()
-        ops.delta_fwd(gpu, q, k, v, alpha, beta, b, t, h, dh, chunk=CHUNK, out=o, ckpt=ckpt)
-        if ev:
-            ev[1].record()
-        ops.delta_bwd(gpu, q, k, v, alpha, beta, qn, kn, d_o, ckpt, b, t, h, dh, chunk=CHUNK, d_qkv=d_qkv,
-                      d_gate=d_gate)
-        if ev:
-            ev[2].record()
+    def step():
+        ops.delta_fwd(hs.gpu, q, k, v, alpha, beta, b, t, h, dh, chunk=chunk, out=o, ckpt=ckpt)
+        ops.delta_bwd(hs.gpu, q, k, v, alpha, beta, qn, kn, d_o, ckpt, b, t, h, dh, chunk=chunk, d_qkv=d_qkv, d_gate=d_gate)
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for _ in range(args.warmup):
-        step()
-    barrier()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    launches0 = gpu.launch_count()
-    gpu.profile(True)   # CUDA events around every delta kernel launch, on the launching stream
-    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for i in range(args.steps):
-        step(evs[i])
-    e1.record()
-    barrier()
-    ms_total = e0.elapsed_time(e1)
-    launches = gpu.launch_count() - launches0
-    clocks = sampler.stop() if rank == 0 else None
-    per_kernel = {}
-    for name, ms in gpu.profile_read():
-        per_kernel.setdefault(name, []).append(ms)
-    gpu.profile(False)
-    fwd_ms = float(np.mean([e[0].elapsed_time(e[1]) for e in evs]))
-    bwd_ms = float(np.mean([e[1].elapsed_time(e[2]) for e in evs]))
-    if world > 1:
-        tt = torch.tensor([ms_total], device=dev)
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        ms_total = float(tt.item())
-    ms_step = ms_total / args.steps
-    tok_s = world * b * t / (ms_step * 1e-3)
-
-    # ---- end to end: pinned host buffers in, host results out, every copy inside the timed region
-    e2e_steps = max(1, min(args.steps, 3))
+    steps = 600 if bf16 else 50
+    dev_ms, _, clocks, launches = hs.timed(step, steps, 3)
+    table = hs.kernel_table(lambda: [step() for _ in range(5)])
     s_io = 2 if bf16 else 4
+    # SURVEY-style algorithmic bytes: q,k,v,o (+ gates) forward; q,k,v,dO in and dq,dk,dv out in the activation dtype
+    # (+ gates and their gradients) backward
+    fwd_bytes = 4 * n * d * s_io + 2 * n * h * 4
+    bwd_bytes = 7 * n * d * s_io + 6 * n * h * 4
+    top = max(table, key=lambda kk: table[kk][1])
+    n_top, t_top, _ = table[top]
+    top_ms = t_top / n_top
+    top_bytes = bwd_bytes if "bwd" in top else fwd_bytes
+    pk = hs.peaks
+    achieved = top_bytes / (top_ms * 1e-3) / 1e9
+    # end to end from pinned host buffers
     if bf16:
-        # bf16 mode: the caller holds bf16 activations; device-pointer API + explicit pinned copies
-        hp = [x.bfloat16().pin_memory() if i in (0, 1, 2, 7) else x for i, x in enumerate(pin)]
+        hp = [x.bfloat16().pin_memory() if i in (0, 1, 2, 7) else x.pin_memory() for i, x in enumerate(host32)]
         o_h = torch.empty((n, d), dtype=torch.bfloat16).pin_memory()
         dqkv_h = torch.empty((n, 3 * d), dtype=torch.float32).pin_memory()
         dgate_h = torch.empty((n, 2 * h), dtype=torch.float32).pin_memory()
-
-        pipe = ops.DeltaHostPipeline(gpu, t, h, dh, chunk=CHUNK, dtype=torch.bfloat16)
+        pipe = ops.DeltaHostPipeline(hs.gpu, t, h, dh, chunk=chunk, dtype=torch.bfloat16)
 
         def e2e_step():
             pipe.run(hp[0], hp[1], hp[2], hp[3], hp[4], hp[5], hp[6], hp[7], o_h, dqkv_h, dgate_h, b)
@@ -289,87 +687,128 @@ def run_ours(args):
         d2h = sum(x.numel() * x.element_size() for x in (o_h, dqkv_h, dgate_h))
         api = "asca_b200.ops.DeltaHostPipeline (device-pointer C ABI; per-sequence copy/compute/copy pipeline from pinned host memory)"
     else:
-        # f32 mode: the host-pointer API with the reference's call shape (Gpu.delta_scan + Gpu.delta_bwd_dev)
-        hq, hk, hv, ha, hb, hqn, hkn, hdo = (x.numpy() for x in pin)
+        hq, hk, hv, ha, hb, hqn, hkn, hdo = (x.pin_memory().numpy() for x in host32)
         o_h = torch.empty((n, d), dtype=torch.float32).pin_memory().numpy()
         dqkv_h = torch.empty((n, 3 * d), dtype=torch.float32).pin_memory().numpy()
         dgate_h = torch.empty((n, 2 * h), dtype=torch.float32).pin_memory().numpy()
-        del q, k, v, d_o, o, ckpt, d_qkv, d_gate
-        torch.cuda.empty_cache()
 
         def e2e_step():
-            _, dd = gpu.delta_scan(hq, hk, hv, ha, hb, b, t, h, dh, out=o_h)
-            gpu.delta_bwd_dev(dd, hdo, hqn, hkn, out=(dqkv_h, dgate_h))
+            _, dd = hs.gpu.delta_scan(hq, hk, hv, ha, hb, b, t, h, dh, out=o_h)
+            hs.gpu.delta_bwd_dev(dd, hdo, hqn, hkn, out=(dqkv_h, dgate_h))
             dd.free()
 
         h2d = sum(a.nbytes for a in (hq, hk, hv, ha, hb, hdo, hqn, hkn))
         d2h = o_h.nbytes + dqkv_h.nbytes + dgate_h.nbytes
-        api = "asca_b200.Gpu.delta_scan + delta_bwd_dev (host-pointer C ABI)"
-    e2e_step()
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        e2e_step()
-    barrier()
-    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
-    if world > 1:
-        tt = torch.tensor([e2e_ms], device=dev)
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        e2e_ms = float(tt.item())
+        api = "asca_delta_scan_host + asca_delta_bwd_dev_host (host-pointer C ABI, the reference's call shape)"
+    _, e2e_ms, _, _ = hs.timed(e2e_step, 20 if bf16 else 5, 2, sample_clocks=False)
+    # CPU leg: the oracle times a bounded sample of the same chains AND checks one chain of what was just timed
+    cpu, parity = None, None
+    if not args.no_cpu:
+        import oracle
 
-    if rank == 0:
-        peak, which = measured_peaks()
-        # algorithmic bytes of the two ops (q,k,v,o / q,k,v,dO,dq,dk,dv + gates), s_io bytes per activation
-        bwd_bytes = 4 * n * d * s_io + 3 * n * d * 4 + 6 * n * h * 4
-        fwd_bytes = 4 * n * d * s_io + 2 * n * h * 4
-        kern_ms = {name: float(np.mean(v)) for name, v in per_kernel.items()}
-        kern_n = {name: len(v) for name, v in per_kernel.items()}
-        total_k = sum(float(np.sum(v)) for v in per_kernel.values()) or 1.0
-        share = {name: float(np.sum(v)) / total_k for name, v in per_kernel.items()}
-        top = max(share, key=share.get)
-        # the dominant kernel: the backward chain kernel moves the whole backward's algorithmic bytes
-        top_bytes = bwd_bytes if "bwd" in top else fwd_bytes
-        achieved = top_bytes / (kern_ms[top] * 1e-3) / 1e9
-        cpu_tok, cpu_ms, cores, sample = time_cpu(1, 1) if world == 1 and not args.no_cpu else (None, None, 0, "skipped")
-        line = {
-            "metric": METRIC, "value": tok_s, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16" if bf16 else "f32", "data": "synthetic",
-            "config": {"workload": WORKLOAD if (b, t) == (B, T) else f"delta fwd+BPTT B{b} H{h} T{t} dh{dh} chunk{CHUNK}",
-                       "mode": ("bf16 activations on tcgen05 tensor cores, f32 accumulate, f32 state and gates"
-                                if bf16 else "f32 activations and arithmetic (FFMA)"),
-                       "l2": "inputs larger than L2 (no flush)", "parallelism": f"dp{world} by sequence, no collective"},
-            "ops_ms": {"delta_fwd": fwd_ms, "delta_bwd": bwd_ms},
-            "kernels_ms": kern_ms, "kernel_launches_per_step": {k_: v_ / args.steps for k_, v_ in kern_n.items()},
-            "kernel_share": share,
-            "roofline": {"kernel": top, "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "peak_source": which,
-                         "traffic": NCU_TRAFFIC_PER_CHAIN.get((args.dtype, top), 0) * b * h * t / 4096 or None,
-                         "algorithmic_bytes": top_bytes,
-                         "note": "algorithmic bytes of the op the kernel belongs to / that kernel's mean CUDA-event time; "
-                                 "traffic = dram bytes read + written per launch, from one ncu capture at B=2 scaled by the "
-                                 "number of (sequence, head) chains (profiles/)"},
-            "cpu_baseline": {"value": cpu_tok, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
-            "e2e": {"value": world * b * t / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "api": api},
-            "gpu_launches": launches,
-            "clocks": clocks,
-        }
+        oracle.build()
+        oracle.set_threads(0)
+        threads = cpu_threads()
+        hh = min(h, max(1, threads // 2))
+        sl = [x.numpy().reshape(b, t, -1)[:2] for x in host32]
+
+        def heads(a, width):
+            return np.ascontiguousarray(a[:, :, : hh * width]).reshape(2 * t, hh * width)
+
+        cq, ck_, cv, cdo = (heads(sl[i], dh) for i in (0, 1, 2, 7))
+        ca, cb, cqn, ckn = (heads(sl[i], 1) for i in (3, 4, 5, 6))
+        t0 = time.perf_counter()
+        o_ref, _ = oracle.delta_scan(cq, ck_, cv, ca, cb, 2, t, hh, dh)
+        dqkv_ref, dgate_ref = oracle.delta_bptt(cq, ck_, cv, ca, cb, cqn, ckn, cdo, 2, t, hh, dh, max_workers=threads)
+        dt = time.perf_counter() - t0
+        cpu = {"value": 2 * t * hh / h / dt, "unit": "tok/s", "cores": threads, "kind": "port",
+               "sample": f"{2 * hh} of the {b * h} chains x {t} tokens (2 sequences x {hh} heads), scan + BPTT with per-chain state "
+                         f"history, one chain per thread; tok/s = chain-steps/s / {h} heads"}
+        # parity of what was just timed: sequence 0, head 0, against the CPU path on the same (unrounded) inputs
+        tol = 2e-2 if bf16 else 1e-5
+        got_o = o[:t, :dh].float().cpu().numpy()
+        got_q = d_qkv[:t].cpu().numpy()
+        ref_q = dqkv_ref[:t]
+
+        def rel(a, r):
+            return float(np.abs(a.astype(np.float64) - r).max() / max(float(np.abs(r).max()), 1e-9))
+
+        errs = {"o": rel(got_o, o_ref[:t, :dh]), "dq": rel(got_q[:, :dh], ref_q[:, :dh]),
+                "dk": rel(got_q[:, d:d + dh], ref_q[:, hh * dh:hh * dh + dh]),
+                "dv": rel(got_q[:, 2 * d:2 * d + dh], ref_q[:, 2 * hh * dh:2 * hh * dh + dh]),
+                "d_alpha": rel(d_gate[:t, 0].cpu().numpy(), dgate_ref[:t, 0]),
+                "d_beta": rel(d_gate[:t, h].cpu().numpy(), dgate_ref[:t, hh])}
+        parity = {"chain": "sequence 0, head 0 of the timed batch", "tolerance": tol, "rel_err": errs, "ok": all(e < tol for e in errs.values())}
+        assert parity["ok"], f"bench: the timed delta op disagrees with the CPU path: {errs}"
+    total_k = sum(tt for _, tt, _ in table.values()) or 1.0
+    traffic = NCU_TRAFFIC_PER_CHAIN.get(top) if bf16 else None
+    return {
+        "metric": "delta fwd+bwd tok/s", "value": b * t * 1e3 / dev_ms, "unit": "tok/s", "n_gpus": 1, "steps": steps, "ms_per_step": dev_ms,
+        "dtype": "bf16" if bf16 else "f32",
+        "config": {"workload": f"isolated gated delta-rule op fwd+BPTT: B{b} H{h} T{t} dh{dh} chunk{chunk}",
+                   "mode": ("bf16 activations on tcgen05 tensor cores, f32 accumulate, f32 state and gates" if bf16
+                            else "f32 activations and arithmetic (FFMA)"),
+                   "l2": "inputs (4 x 134 MB in bf16) larger than L2, no flush"},
+        "kernels_ms": {kk: tt / nn for kk, (nn, tt, _) in table.items()},
+        "kernel_share": {kk: tt / total_k for kk, (_, tt, _) in table.items()},
+        "roofline": {"kernel": top, "bound": "hbm", "achieved": achieved, "peak": pk["hbm"], "unit": "GB/s", "frac": achieved / pk["hbm"],
+                     "peak_source": pk["source"], "algorithmic_bytes": top_bytes,
+                     "traffic": traffic * b * h if traffic else None,
+                     "whole_step": {"algorithmic_bytes": fwd_bytes + bwd_bytes,
+                                    "achieved": (fwd_bytes + bwd_bytes) / (dev_ms * 1e-3) / 1e9,
+                                    "frac": (fwd_bytes + bwd_bytes) / (dev_ms * 1e-3) / 1e9 / pk["hbm"]},
+                     "note": "algorithmic bytes of the op the dominant kernel belongs to (q,k,v,o + gates forward; q,k,v,dO in and "
+                             "dq,dk,dv out in the activation dtype + gates backward) / that kernel's mean CUDA-event time; traffic = dram "
+                             "bytes of one ncu capture at B=2 scaled by the number of chains"},
+        "e2e": {"value": b * t * 1e3 / e2e_ms, "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
+                "api": api},
+        "gpu_launches": launches, "clocks": clocks, "cpu_baseline": cpu, "parity_of_timed_batch": parity,
+    }
+
+
+# ------------------------------------------------------------------ driver
+def run_ours(args):
+    hs = Harness()
+    only = set(filter(None, args.only.split(","))) or {"train", "decode", "moe", "delta"}
+    line = run_train(hs, args) if "train" in only else None
+    records = {}
+    if "decode" in only:
+        records["decode"] = run_decode(hs, args)
+    if hs.world == 1:        # the isolated ops are per-GPU workloads: measured once, at N = 1
+        if "moe" in only:
+            records["moe"] = run_moe(hs, args)
+        if "delta" in only:
+            records["delta_bf16"] = run_delta(hs, args, True)
+            hs.gpu.lib.asca_ctx_trim(hs.gpu._ctx)
+            hs.torch.cuda.empty_cache()
+            records["delta_f32"] = run_delta(hs, args, False)
+    if hs.rank == 0:
+        if line is None:      # a partial run (--only without train): the first record stands in as the line
+            key = next(iter(records))
+            line = dict(records.pop(key))
+            line.setdefault("warmup", args.warmup)
+            line.setdefault("higher_is_better", True)
+            line.setdefault("vs_baseline", None)
+            line.setdefault("data", "synthetic")
+        elif hs.world == 1 and not args.no_cpu:
+            line["cpu_baseline"] = cpu_baseline_train(args.layers)
+        else:
+            line["cpu_baseline"] = {"value": None, "unit": "tok/s", "cores": 0, "kind": "port", "sample": "skipped (rank 0 at N = 1 only)"}
+        line["records"] = records
         print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
+    if hs.world > 1:
+        hs.dist.destroy_process_group()
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--dtype", default="bf16", choices=["f32", "bf16"])
-    ap.add_argument("--batch", type=int, default=B)
-    ap.add_argument("--seq", type=int, default=T)
-    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--layers", type=int, default=4, help="blocks of the 24-block training stack to run (the largest that fits one GPU)")
+    ap.add_argument("--only", default="", help="comma-separated subset of train,decode,moe,delta")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline legs")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -68,6 +68,13 @@ int asca_ctx_profile_work(asca_ctx* ctx, int index, double* work);
 /* Library version string and the arch it was compiled for ("sm_100a"). */
 const char* asca_version(void);
 
+/* Memory the context holds beyond what the caller sees: freed asca_malloc blocks (cached per size class),
+ * the grow-only scratch of the kernels, and the tiles the tensor-core delta forward keeps for its backward
+ * (at most `bytes` of them, default 32 GiB, least recently used set reused beyond that).
+ * asca_ctx_trim synchronises the stream and gives all three back to the driver. */
+int asca_ctx_trim(asca_ctx* ctx);
+int asca_ctx_set_tile_cache_bytes(asca_ctx* ctx, size_t bytes);
+
 /* Device memory for callers that have no allocator of their own (the reference's DevBuf,
  * rust/src/cuda/mod.rs:104-174). Freed blocks are cached per size class. */
 int asca_malloc(asca_ctx* ctx, size_t bytes, void** dptr);
@@ -151,6 +158,13 @@ int asca_adamw_host(asca_ctx* ctx, float* p, const float* g, float* m, float* v,
  *             With dtype ASCA_BF16, dh = 128 and chunk = 64 (the tensor-core kernels) the same
  *             states are stored rounded to bf16, same layout, in the first half of the buffer;
  *             either way the buffer is meant to be handed back to asca_delta_bwd unchanged.
+ *             Contract of the tensor-core mode: that forward also keeps, inside the context, tiles it derived
+ *             from q, k, v, alpha, beta, filed under the addresses of ckpt and of those five inputs. A backward
+ *             that presents the same six addresses (and B, T, H) reuses the tiles instead of rebuilding them, so
+ *             between the two calls the CONTENTS of q, k, v, alpha, beta and ckpt must not change (a caller that
+ *             offloads and restores them may restore them anywhere but into the same addresses with other
+ *             contents). Any other address combination rebuilds the tiles from the arguments. The kept tiles
+ *             count against asca_ctx_set_tile_cache_bytes and are released by asca_ctx_trim.
  *   s_init  : nullable, (B, H, dh, dh) f32 initial state (continuing a prefix); NULL = 0. */
 int64_t asca_delta_ckpt_floats(int64_t B, int64_t T, int64_t H, int64_t dh, int64_t chunk);
 int asca_delta_fwd(asca_ctx* ctx, const void* q, const void* k, const void* v, const float* alpha,
@@ -281,6 +295,14 @@ int asca_moe_forward_dev_host(asca_ctx* ctx, const float* xn, const float* w1, c
                               int64_t d, int64_t F, int64_t E, float* out, asca_moe_dev** dev);
 int asca_moe_bwd_dev_host(asca_ctx* ctx, const asca_moe_dev* dev, const float* dout, float* d_w1,
                           float* d_b1, float* d_w2, float* d_b2, float* dxn);
+/* Gpu::moe_forward_dev with its own argument list (rust/src/cuda/mod.rs:523-532): the caller passes the
+ * host-built `buckets` (rust/src/model.rs:190-193), flattened -- bucket_idx holds the buckets back to back (N token
+ * indices), bucket_off[E + 1] their bounds. They are used as the dispatch permutation as they are; no sort runs on
+ * the device, and `Model::forward` needs no edit. The handle is consumed by asca_moe_bwd_dev_host. */
+int asca_moe_forward_dev_buckets_host(asca_ctx* ctx, const float* xn, const float* w1, const float* b1,
+                                      const float* w2, const float* b2, const int32_t* bucket_idx,
+                                      const int32_t* bucket_off, int64_t N, int64_t d, int64_t F, int64_t E,
+                                      float* out, asca_moe_dev** dev);
 /* MoeDev::download_pre_hidden (rust/src/cuda/mod.rs:1445-1470): pre and hidden as (N,F) in
  * token order. */
 int asca_moe_dev_download_pre_hidden(asca_ctx* ctx, const asca_moe_dev* dev, float* pre,
@@ -307,6 +329,36 @@ int asca_embed_fwd(asca_ctx* ctx, const float* table, const uint32_t* ids, int64
                    float* x);
 int asca_embed_bwd(asca_ctx* ctx, const float* dx, const uint32_t* ids, int64_t N, int64_t d,
                    int64_t vocab, float* d_table);
+
+/* Host forms of the head / loss / optimizer methods of `impl Gpu`:
+ *   asca_head_forward_dev_host   Gpu::head_forward_dev (rust/src/cuda/mod.rs:828-846): logits = h_final (T,d) x head
+ *                                (d,V), kept on the device with h_final behind a LogitsDev handle (:1400-1413)
+ *   asca_logits_dev_download     LogitsDev::download
+ *   asca_head_bwd_dev_host       Gpu::head_bwd_dev (:851-908): *loss = mean token loss, d_head (d,V) = h_final^T dlogits,
+ *                                dh (T,d) = dlogits x head_t, head_t (V,d) the transposed head the caller passes
+ *   asca_cross_entropy_bwd_host  Gpu::cross_entropy_bwd (:945-1000): *loss and dlogits = (softmax - onehot) / T
+ *   asca_adamw_resident_host     Gpu::adamw_resident (:1003-1055): Adam moments stay on the device between calls,
+ *                                keyed by (key_addr = host address of the caller's m buffer, n); the first call for a
+ *                                key uploads m0 / v0; val is updated in place. CPU-path decay, scalars as asca_adamw.
+ *   asca_param_moments_host      param_moments (:57-73): the device-resident moments of a key; returns 1 if the key
+ *                                has none
+ *   asca_reset_param_cache       reset_param_cache (:50-54): drop every resident moment (call when a new model is built)
+ *   asca_silu_inplace_host       Gpu::silu_inplace (:1224-1250) */
+typedef struct asca_logits_dev asca_logits_dev;
+int asca_head_forward_dev_host(asca_ctx* ctx, const float* h_final, const float* head, int64_t T, int64_t d,
+                               int64_t V, asca_logits_dev** dev);
+int asca_logits_dev_download(asca_ctx* ctx, const asca_logits_dev* dev, float* logits);
+int asca_head_bwd_dev_host(asca_ctx* ctx, const asca_logits_dev* dev, const uint32_t* targets,
+                           const float* head_t, float* loss, float* d_head, float* dh);
+int asca_logits_dev_free(asca_ctx* ctx, asca_logits_dev* dev);
+int asca_cross_entropy_bwd_host(asca_ctx* ctx, const float* logits, const uint32_t* targets, int64_t T, int64_t V,
+                                float* loss, float* dlogits);
+int asca_adamw_resident_host(asca_ctx* ctx, const void* key_addr, float* val, const float* grad, const float* m0,
+                             const float* v0, int64_t n, float lr_t, float beta1, float beta2, float eps_t,
+                             float wd_eff);
+int asca_param_moments_host(asca_ctx* ctx, const void* key_addr, int64_t n, float* m, float* v);
+int asca_reset_param_cache(asca_ctx* ctx);
+int asca_silu_inplace_host(asca_ctx* ctx, float* x, int64_t n);
 
 /* ------------------------------------------------------------------ model glue (X1)
  * Model::forward / backward / step and the AdamW loop (rust/src/model.rs:631-802) on one flat
@@ -422,6 +474,15 @@ int asca_dp_shard_plan(int64_t vocab, int64_t d, int64_t H, int64_t L, int64_t E
  * uint32 (n_streams), nullable -- the greedy argmax (lowest index on ties). */
 int asca_model_decode_step_host(asca_ctx* ctx, asca_model* m, float* state, const uint32_t* ids,
                                 int64_t n_streams, float* logits, uint32_t* next_ids);
+/* Chunked prefill (no counterpart in the reference, whose decoder prefills by stepping, rust/src/main.rs:367-371):
+ * the forward of Model::forward (rust/src/model.rs:651-690) over n_streams prompts of T tokens each (ids: host
+ * uint32, n_streams x T, one prompt per row), keeping the recurrent state after the last token of every block, head
+ * and stream in `state` (same layout as the decode step; its incoming contents are the initial state, zeros for a
+ * fresh stream, so a prompt may be fed in several calls) and returning the logits of each stream's LAST token
+ * (host, n_streams x vocab, nullable) and their argmax (next_ids, nullable). Stepping the same tokens through
+ * asca_model_decode_step_host gives the same state and logits (the property rust/tests/decode_parity.rs pins). */
+int asca_model_prefill_host(asca_ctx* ctx, asca_model* m, float* state, const uint32_t* ids, int64_t n_streams,
+                            int64_t T, float* logits, uint32_t* next_ids);
 /* Greedy decode of n_steps tokens per stream (the loop of the reference's `asca gen` with argmax sampling,
  * rust/src/main.rs: step, pick the largest logit, feed it back): step 0 consumes ids (host, n_streams), every later
  * step the argmax of the step before, which stays on the device; tokens (host, n_steps x n_streams, one row per

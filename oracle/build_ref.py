@@ -4,7 +4,10 @@ oracle/_ref/libasca_ref.so. TEST INFRASTRUCTURE: it lets GPU tests pin the CPU o
 outputs of the reference's own code. Runs only where the reference tree is present; the built
 library travels with the repository snapshot to the GPU machine.
 
-    python oracle/build_ref.py [path-to-reference-root]
+    python oracle/build_ref.py <path-to-reference-root>
+
+The reference root comes from the argument or from the environment variable ASCA_REFERENCE_ROOT; without either
+nothing is built and an already built library is used as it is.
 """
 from __future__ import annotations
 
@@ -19,9 +22,9 @@ OUT = DIR / "_ref" / "libasca_ref.so"
 
 
 def build(reference_root: str | None = None, force: bool = False) -> Path | None:
-    root = Path(reference_root or os.environ.get("ASCA_REFERENCE_ROOT", "/root/reference"))
-    src = root / "rust" / "kernels" / "asca.cu"
-    if not src.exists():
+    where = reference_root or os.environ.get("ASCA_REFERENCE_ROOT")
+    src = Path(where) / "rust" / "kernels" / "asca.cu" if where else None
+    if src is None or not src.exists():
         return OUT if OUT.exists() else None
     wrap = DIR / "ref_kernels.cu"
     if not force and OUT.exists() and OUT.stat().st_mtime >= max(src.stat().st_mtime, wrap.stat().st_mtime):

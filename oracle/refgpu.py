@@ -93,3 +93,43 @@ def cross_entropy(logits, targets):
     _ok(lib().ref_cross_entropy(_f(logits), tg.ctypes.data_as(C.POINTER(C.c_uint32)), _f(dl), _f(ls), t, v),
         "cross_entropy_bwd_f32")
     return ls, dl
+
+
+def _i(a):
+    assert a.dtype == np.int32 and a.flags.c_contiguous
+    return a.ctypes.data_as(C.POINTER(C.c_int32))
+
+
+def moe_forward_backward(xn, w1, b1, w2, b2, buckets, dout, F):
+    """The reference's moe_forward_dev + moe_bwd_dev launch sequence on host-built buckets (a list of index arrays,
+    one per expert). Returns out, pre, hid (token order), d_w1, d_b1, d_w2, d_b2, dxn."""
+    t, d = xn.shape
+    e = len(buckets)
+    idx = np.ascontiguousarray(np.concatenate([np.asarray(b, np.int32) for b in buckets]) if t else np.zeros(0, np.int32))
+    off = np.concatenate([[0], np.cumsum([len(b) for b in buckets])]).astype(np.int32)
+    out, dxn = np.empty((t, d), np.float32), np.empty((t, d), np.float32)
+    pre, hid = np.empty((t, F), np.float32), np.empty((t, F), np.float32)
+    d_w1, d_w2 = np.empty_like(w1), np.empty_like(w2)
+    d_b1, d_b2 = np.empty(e * F, np.float32), np.empty(d, np.float32)
+    _ok(lib().ref_moe_fwd_bwd(_f(xn), _f(w1), _f(b1), _f(w2), _f(b2), _i(idx), _i(off), _f(dout), t, d, F, e, _f(out), _f(pre),
+                              _f(hid), _f(d_w1), _f(d_b1), _f(d_w2), _f(d_b2), _f(dxn)), "moe forward + backward sequence")
+    return out, pre, hid, d_w1, d_b1, d_w2, d_b2, dxn
+
+
+def gather_rows(src, idx):
+    idx = np.ascontiguousarray(idx, np.int32)
+    dst = np.empty((idx.size, src.shape[1]), np.float32)
+    _ok(lib().ref_gather_rows(_f(src), src.shape[0], _i(idx), idx.size, src.shape[1], _f(dst)), "gather_rows_f32")
+    return dst
+
+
+def scatter_rows(src, idx, dst):
+    idx = np.ascontiguousarray(idx, np.int32)
+    _ok(lib().ref_scatter_rows(_f(src), _i(idx), idx.size, src.shape[1], _f(dst), dst.shape[0]), "scatter_rows_f32")
+    return dst
+
+
+def adamw(val, grad, m, v, lr_t, beta1, beta2, eps_t, wd):
+    """In place on val, m, v (copies of the caller's arrays are the caller's business)."""
+    _ok(lib().ref_adamw(_f(val), _f(grad), _f(m), _f(v), val.size, C.c_float(lr_t), C.c_float(beta1), C.c_float(beta2),
+                        C.c_float(eps_t), C.c_float(wd)), "adamw_f32")

@@ -12,6 +12,16 @@ pytestmark = pytest.mark.gpu
 CFG1 = (256, 64, 4, 2, 4, 256)
 
 
+def _bf16_grad_tol(ref_tensor):
+    """2e-2, the bf16-mode contract, for every gradient tensor -- except that the gate biases of the TOY shapes in
+    this file get 2.5e-2. Each of their 2H numbers is a cancelling sum of d_gate over all tokens; at a few hundred
+    tokens the bf16 rounding of q, k, v alone moves such a sum by 1.5-2.4e-2 of the largest entry (measured: 2.06e-2
+    and 2.37e-2 on two of these shapes), so 2e-2 cannot be promised there. It is a stated miss of the contract at toy
+    sizes; at the training configuration's widths the same tensors are held to 2e-2 (9.0e-3 measured,
+    tests/test_gpu_baseline_sizes.py)."""
+    return 2e-2 if ref_tensor.size >= 64 else 2.5e-2
+
+
 def _setup(orc, gpu, init):
     import asca_b200
 
@@ -44,7 +54,7 @@ def test_config1_train_step_matches_oracle(orc, gpu, init):
         if np.abs(b).max() == 0:
             assert np.abs(a).max() == 0, name
         else:
-            assert rel_err(a, b) < 2e-5, name
+            assert rel_err(a, b) < 1e-5, name
     # AdamW: the counter advances once per tensor; two steps to exercise t > P. Adam's m/sqrt(v) is
     # ill-conditioned where |g| ~ eps, so the optimizer is compared on IDENTICAL gradients.
     dev.set_grads(g_ref)
@@ -119,9 +129,7 @@ def test_bf16_compute_train_step_within_tolerance(orc, gpu, cfg):
         if np.abs(b).max() == 0:
             assert np.abs(a).max() == 0, name
         else:
-            # a handful of numbers that are each a cancelling sum over all tokens (the gate biases)
-            # carry the bf16 noise of the whole batch: twice the tolerance for tensors under 64 entries
-            assert rel_err(a, b) < (2e-2 if b.size >= 64 else 4e-2), name
+            assert rel_err(a, b) < _bf16_grad_tol(b), name
     # a second step after AdamW refreshes the bf16 weight copy
     dev.adamw_step(3e-3)
     m_ref, v_ref = np.zeros(ref.n, np.float32), np.zeros(ref.n, np.float32)
@@ -159,7 +167,7 @@ def test_grad_hook_covers_the_buffer_once_and_accumulation_scales(orc, gpu):
     _, g = dev.get()
     for name in ref.names:
         a, b = ref.tensor(name, g), ref.tensor(name, g_ref)
-        assert rel_err(a, b) < 2e-5, name
+        assert rel_err(a, b) < 1e-5, name
     dev.free()
 
 
@@ -277,8 +285,8 @@ def test_trainer_loop_matches_oracle_loss_for_loss_and_resumes(orc, gpu, tmp_pat
 
 def test_bf16_compute_train_step_head_dim_64(orc, gpu):
     """bf16 compute mode with head dim 64 (the decode configuration's head size): the delta op runs on the
-    bf16-storage FFMA kernels instead of the tensor-core ones; loss and gradients stay within 2e-2 (4e-2 for the
-    few-entry gate tensors) of the f32 oracle."""
+    bf16-storage FFMA kernels instead of the tensor-core ones; loss and gradients stay within 2e-2 of the f32
+    oracle (the gate biases of these toy shapes: see _bf16_grad_tol)."""
     import asca_b200
 
     cfg = (256, 128, 2, 2, 4, 256)
@@ -301,5 +309,51 @@ def test_bf16_compute_train_step_head_dim_64(orc, gpu):
         if np.abs(b).max() == 0:
             assert np.abs(a).max() == 0, name
         else:
-            assert rel_err(a, b) < (2e-2 if b.size >= 64 else 4e-2), name
+            assert rel_err(a, b) < _bf16_grad_tol(b), name
+    dev.free()
+
+
+@pytest.mark.parametrize("cfg,mode,tol", [((256, 64, 4, 2, 4, 256), "f32", 1e-5), ((256, 128, 2, 2, 4, 256), "f32", 1e-5),
+                                          ((256, 128, 2, 2, 4, 256), "bf16", 2e-2), ((256, 256, 2, 2, 4, 256), "bf16", 2e-2)])
+def test_chunked_prefill_equals_stepping(orc, gpu, cfg, mode, tol):
+    """asca_model_prefill_host (T-token products + the chunked scan) leaves the decoder in the state that stepping the
+    same prompt token by token does -- against the oracle's Model::step, and against the library's own decode step;
+    a prompt fed in two calls continues from the state of the first; the decode that follows agrees too."""
+    import asca_b200
+
+    ref = orc.Model(*cfg)
+    ref.init_reference(orc.Rng(41))
+    dev = asca_b200.Model(gpu, *cfg)
+    dev.set_params(ref.params)
+    if mode == "bf16":
+        dev.set_compute(asca_b200.BF16)
+    ns, T = 3, 150                      # ragged against the 64-token chunks
+    prompts = orc.Rng(42).below(256, (ns, T))
+    ref_states = [ref.new_decode_state() for _ in range(ns)]
+    ref_last = np.empty((ns, 256), np.float32)
+    for s in range(ns):
+        for t in range(T):
+            ref_last[s] = ref.step(int(prompts[s, t]), ref_states[s])[0]
+    state = dev.new_decode_state(ns)
+    logits, nxt = dev.prefill(state, prompts)
+    st = state.cpu().numpy()
+    assert rel_err(logits, ref_last) < tol
+    for s in range(ns):
+        assert rel_err(st[:, s], ref_states[s]) < tol
+    # the library's own stepping
+    state2 = dev.new_decode_state(ns)
+    for t in range(T):
+        lg2, nx2 = dev.decode_step(state2, prompts[:, t].copy())
+    assert rel_err(logits, lg2) < (1e-4 if mode == "f32" else tol)
+    # in two calls
+    state3 = dev.new_decode_state(ns)
+    dev.prefill(state3, prompts[:, :70].copy(), want_logits=False)
+    lg3, _ = dev.prefill(state3, prompts[:, 70:].copy())
+    assert rel_err(state3.cpu().numpy(), st) < (1e-5 if mode == "f32" else tol)
+    assert rel_err(lg3, logits) < (1e-4 if mode == "f32" else tol)
+    # and one decode step after the prefill
+    tok = orc.Rng(43).below(256, ns)
+    lg4, _ = dev.decode_step(state, tok.copy())
+    for s in range(ns):
+        assert rel_err(lg4[s], ref.step(int(tok[s]), ref_states[s])[0]) < tol
     dev.free()

@@ -703,3 +703,112 @@ def test_delta_tc_backward_without_kept_tiles_and_with_several_kept(orc, gpu):
         d2, g2 = ops.delta_bwd(gpu, *s[:5], s[5], s[6], s[7], ck.clone(), B, T, H, dh, chunk=64)  # rebuilt
         gpu.sync()
         assert torch.equal(d1, d2) and torch.equal(g1, g2)
+
+
+@pytest.mark.gpu
+def test_delta_tc_kept_tiles_are_filed_under_the_inputs_too(orc, gpu):
+    """A backward that presents the forward's checkpoint buffer but other q/k/v buffers must not pick up the
+    forward's tiles: it rebuilds them from what it was given. Trimming the context drops every kept tile."""
+    import ctypes
+
+    import torch
+    from asca_b200 import ops
+
+    B, T, H, dh = 1, 192, 2, 128
+    a1 = [torch.from_numpy(a).cuda() for a in _delta_inputs(orc, 41, B, T, H, dh)]
+    a2 = [torch.from_numpy(a).cuda() for a in _delta_inputs(orc, 42, B, T, H, dh)]
+    s1 = [a1[0].bfloat16(), a1[1].bfloat16(), a1[2].bfloat16(), a1[3], a1[4], a1[5], a1[6], a1[7].bfloat16()]
+    s2 = [a2[0].bfloat16(), a2[1].bfloat16(), a2[2].bfloat16(), a2[3], a2[4], a2[5], a2[6], a2[7].bfloat16()]
+    _, _, ck1 = ops.delta_fwd(gpu, *s1[:5], B, T, H, dh, chunk=64)
+    want, want_g = ops.delta_bwd(gpu, *s1[:5], s1[5], s1[6], s1[7], ck1, B, T, H, dh, chunk=64)
+    # the second problem's forward writes its checkpoints into a fresh buffer; copy them over ck1 and present ck1 with
+    # the second problem's inputs: same checkpoint address as the kept tiles, different inputs
+    _, _, ck2 = ops.delta_fwd(gpu, *s2[:5], B, T, H, dh, chunk=64)
+    ref2, ref2_g = ops.delta_bwd(gpu, *s2[:5], s2[5], s2[6], s2[7], ck2, B, T, H, dh, chunk=64)
+    _, _, ck1 = ops.delta_fwd(gpu, *s1[:5], B, T, H, dh, chunk=64, ckpt=ck1)
+    ck1.copy_(ck2)
+    got2, got2_g = ops.delta_bwd(gpu, *s2[:5], s2[5], s2[6], s2[7], ck1, B, T, H, dh, chunk=64)
+    gpu.sync()
+    assert torch.equal(got2, ref2) and torch.equal(got2_g, ref2_g)
+    assert not torch.equal(got2, want)
+    gpu._call("asca_ctx_trim", gpu._ctx)
+    gpu._call("asca_ctx_set_tile_cache_bytes", gpu._ctx, ctypes.c_size_t(1 << 30))
+    _, _, ck3 = ops.delta_fwd(gpu, *s1[:5], B, T, H, dh, chunk=64)
+    again, again_g = ops.delta_bwd(gpu, *s1[:5], s1[5], s1[6], s1[7], ck3, B, T, H, dh, chunk=64)
+    gpu.sync()
+    assert torch.equal(again, want) and torch.equal(again_g, want_g)
+    gpu._call("asca_ctx_set_tile_cache_bytes", gpu._ctx, ctypes.c_size_t(32 << 30))
+
+
+# ------------------------------------------------------------------ the remaining `impl Gpu` call shapes
+@pytest.mark.gpu
+def test_moe_forward_dev_with_host_built_buckets(orc, gpu):
+    """Gpu::moe_forward_dev as the reference calls it (rust/src/model.rs:159-172): the caller's buckets go in, and the
+    result equals the ids form (device dispatch) bit for bit, forward and backward."""
+    n, d, F, E = 700, 64, 128, 8
+    w1, b1, w2, b2 = _moe_params(orc, 9, d, F, E)
+    rng = orc.Rng(10)
+    xn = orc.rmsnorm(rng.normal((n, d)))[0]
+    ids = rng.below(256, n)
+    dout = rng.normal((n, d))
+    buckets = [[] for _ in range(E)]
+    for t, i in enumerate(ids):
+        buckets[orc.hash_route(int(i), E)].append(t)
+    out_b, dev_b = gpu.moe_forward_dev_buckets(xn, w1, b1, w2, b2, buckets, F)
+    out_i, dev_i = gpu.moe_forward_dev(xn, w1, b1, w2, b2, ids, F)
+    assert np.array_equal(out_b, out_i)
+    assert rel_err(out_b, orc.moe_ffn_forward(xn, w1, b1, w2, b2, ids, F, E)) < F32_TOL
+    rb, ri = gpu.moe_bwd_dev(dev_b, dout), gpu.moe_bwd_dev(dev_i, dout)
+    for name in ("d_w1", "d_b1", "d_w2", "d_b2", "dxn"):
+        assert np.array_equal(getattr(rb, name), getattr(ri, name)), name
+    dev_b.free()
+    dev_i.free()
+    with pytest.raises(Exception):
+        gpu.moe_forward_dev_buckets(xn, w1, b1, w2, b2, [b[:-1] for b in buckets], F)    # a token is missing
+
+
+@pytest.mark.gpu
+def test_head_cross_entropy_and_resident_adamw_host_forms(orc, gpu):
+    import asca_b200
+
+    rng = orc.Rng(12)
+    T, d, V = 300, 96, 256
+    h_final, head = rng.normal((T, d)), rng.normal((d, V), 0.1)
+    targets = rng.below(V, T)
+    ldev = gpu.head_forward_dev(h_final, head)
+    logits = ldev.download()
+    assert rel_err(logits, orc.matmul(h_final, head)) < F32_TOL
+    loss, d_head, dh = gpu.head_bwd_dev(ldev, targets, np.ascontiguousarray(head.T))
+    lg = logits.astype(np.float64)
+    lse = np.log(np.exp(lg - lg.max(1, keepdims=True)).sum(1)) + lg.max(1)
+    loss_ref = float((lse - lg[np.arange(T), targets]).mean())
+    dl_ref = np.exp(lg - lse[:, None]) / T
+    dl_ref[np.arange(T), targets] -= 1.0 / T
+    assert abs(loss - loss_ref) / loss_ref < F32_TOL
+    assert rel_err(d_head, h_final.astype(np.float64).T @ dl_ref) < F32_TOL
+    assert rel_err(dh, dl_ref @ head.astype(np.float64).T) < F32_TOL
+    loss2, dl = gpu.cross_entropy_bwd(logits, targets)
+    assert abs(loss2 - loss_ref) / loss_ref < F32_TOL and rel_err(dl, dl_ref) < F32_TOL
+    ldev.free()
+    # resident AdamW: the moments stay on the device, keyed by the caller's m buffer
+    n = 5000
+    p_ref, g1, g2 = rng.normal(n, 0.1), rng.normal(n, 0.01), rng.normal(n, 0.01)
+    m_host, v_host = np.zeros(n, np.float32), np.zeros(n, np.float32)     # the caller's (stale) host moments
+    key = asca_b200.param_key(m_host)
+    gpu.reset_param_cache()
+    assert gpu.param_moments(key) is None
+    p_dev = p_ref.copy()
+    mo, vo = np.zeros(n, np.float32), np.zeros(n, np.float32)
+    for t, g in ((1, g1), (2, g2)):
+        lr_t, eps_t, wd_eff = orc.adamw_scalars(3e-3, 0.9, 0.95, 1e-8, 0.01, t)
+        gpu.adamw_resident(key, p_dev, g, m_host, v_host, lr_t, 0.9, 0.95, eps_t, wd_eff)
+        orc.adamw_apply(p_ref, g, mo, vo, lr_t, 0.9, 0.95, eps_t, wd_eff)
+    assert rel_err(p_dev, p_ref) < F32_TOL
+    m_dev, v_dev = gpu.param_moments(key)
+    assert rel_err(m_dev, mo) < F32_TOL and rel_err(v_dev, vo) < F32_TOL and not m_host.any()
+    gpu.reset_param_cache()
+    assert gpu.param_moments(key) is None
+    x = rng.normal(1000, 2.0)
+    want = x.astype(np.float64) / (1 + np.exp(-x.astype(np.float64)))
+    gpu.silu_inplace(x)
+    assert rel_err(x, want) < F32_TOL

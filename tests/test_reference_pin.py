@@ -104,3 +104,64 @@ def test_silu_and_cross_entropy_kernels_pin_oracle(orc, ref):
     p_soft = np.exp(logits.astype(np.float64) - lse[:, None]) / t
     p_soft[np.arange(t), targets] -= 1.0 / t
     assert rel_err(dl, p_soft) < PIN_TOL
+
+
+@pytest.mark.parametrize("T,d,F,E,vocab", [(1024, 192, 384, 8, 4096), (300, 64, 256, 4, 256)])
+def test_moe_layer_sequence_pins_oracle(orc, ref, gpu, T, d, F, E, vocab):
+    """The oracle's HashMoe forward + backward against the reference's own per-expert launch sequence of its own
+    kernels (gather, matmul_ld, add_bias, silu_out, matmul_ld, add_bias, scatter; then gather, matmul_ta_ld, colsum,
+    matmul_tb, silu_bwd, colsum, gather, matmul_ta_ld, matmul_tb, scatter -- rust/src/cuda/mod.rs:575-584, :768-804),
+    at the shape `asca gpu` uses for the MoE (T 1024, d 192, d_ff 384, 8 experts, rust/src/main.rs:991-1051), on
+    host-built buckets as the reference passes them. The library is compared with the same outputs directly."""
+    rng = orc.Rng(T + d)
+    w1 = rng.normal((d, E * F), float(np.sqrt(1.0 / d)))
+    w2 = rng.normal((E * F, d), float(np.sqrt(1.0 / F)))
+    b1, b2 = rng.normal(E * F, 0.1), rng.normal(d, 0.1)
+    xn = orc.rmsnorm(rng.normal((T, d), 0.5))[0]
+    ids = rng.below(vocab, T)
+    dout = rng.normal((T, d))
+    # buckets as HashMoe::forward builds them (rust/src/model.rs:190-193)
+    buckets = [[] for _ in range(E)]
+    for t, i in enumerate(ids):
+        buckets[orc.hash_route(int(i), E)].append(t)
+    out_r, pre_r, hid_r, dw1_r, db1_r, dw2_r, db2_r, dxn_r = ref.moe_forward_backward(xn, w1, b1, w2, b2, buckets, dout, F)
+    out, pre, hid = orc.moe_ffn_forward(xn, w1, b1, w2, b2, ids, F, E, want_cache=True)
+    g = orc.moe_ffn_backward(xn, w1, w2, pre, hid, ids, dout, F, E)
+    assert rel_err(out, out_r) < PIN_TOL and rel_err(pre, pre_r) < PIN_TOL and rel_err(hid, hid_r) < PIN_TOL
+    for name, got, want in zip(("d_w1", "d_b1", "d_w2", "d_b2", "dxn"), g, (dw1_r, db1_r, dw2_r, db2_r, dxn_r)):
+        assert rel_err(got, want) < PIN_TOL, name
+    og, dev = gpu.moe_forward_dev(xn, w1, b1, w2, b2, ids, F)
+    r = gpu.moe_bwd_dev(dev, dout)
+    assert rel_err(og, out_r) < PIN_TOL
+    for name, got, want in zip(("d_w1", "d_b1", "d_w2", "d_b2", "dxn"), (r.d_w1, r.d_b1, r.d_w2, r.d_b2, r.dxn),
+                               (dw1_r, db1_r, dw2_r, db2_r, dxn_r)):
+        assert rel_err(got, want) < PIN_TOL, name
+    dev.free()
+
+
+def test_gather_scatter_and_adamw_kernels_pin_oracle(orc, ref, gpu):
+    rng = orc.Rng(17)
+    src = rng.normal((500, 96))
+    idx = rng.below(500, 200).astype(np.int32)
+    assert np.array_equal(ref.gather_rows(src, idx), src[idx])
+    assert np.array_equal(gpu.gather_rows(src, idx), src[idx])
+    perm = np.argsort(rng.uniform(300)).astype(np.int32)
+    rows = rng.normal((300, 96))
+    want = ref.scatter_rows(rows, perm, np.zeros((300, 96), np.float32))
+    got = np.zeros((300, 96), np.float32)
+    gpu.scatter_rows(rows, perm, got)
+    assert np.array_equal(got, want)
+    # AdamW with no decay, where the reference kernel and the CPU path state the same update
+    # (rust/kernels/asca.cu:551-572 against rust/src/tensor.rs:444-453), two steps so that the moments matter
+    n = 10007
+    p0, g1, g2 = rng.normal(n, 0.1), rng.normal(n, 0.01), rng.normal(n, 0.01)
+    pr, mr, vr = p0.copy(), np.zeros(n, np.float32), np.zeros(n, np.float32)
+    po, mo, vo = p0.copy(), np.zeros(n, np.float32), np.zeros(n, np.float32)
+    pg, mg, vg = p0.copy(), np.zeros(n, np.float32), np.zeros(n, np.float32)
+    for t, g in ((1, g1), (2, g2)):
+        lr_t, eps_t, _ = orc.adamw_scalars(3e-3, 0.9, 0.95, 1e-8, 0.0, t)
+        ref.adamw(pr, g, mr, vr, lr_t, 0.9, 0.95, eps_t, 0.0)
+        orc.adamw_apply(po, g, mo, vo, lr_t, 0.9, 0.95, eps_t, 0.0)
+        gpu.adamw_update(pg, g, mg, vg, lr_t, 0.9, 0.95, eps_t, 0.0)
+    for a, b in ((po, pr), (mo, mr), (vo, vr), (pg, pr), (mg, mr), (vg, vr)):
+        assert rel_err(a, b) < PIN_TOL
