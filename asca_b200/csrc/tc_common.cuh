@@ -56,20 +56,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait: returns false (after raising *abort_flag and the global error word) when the
-// phase does not complete within WAIT_LIMIT_CYCLES or when another role has already aborted.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* err_word,
-                                          int code) {
+// phase does not complete within `limit` cycles or when another role has already aborted.
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* err_word,
+                                                int code, long long limit) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
-        if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+        if (clock64() - t0 > limit) {
             *abort_flag = 1;
             if (err_word) atomicExch(err_word, code);
             return false;
         }
     }
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* err_word,
+                                          int code) {
+    return mbar_wait_limit(bar, parity, abort_flag, err_word, code, WAIT_LIMIT_CYCLES);
 }
 
 // ---------------------------------------------------------------- TMA (plain tile loads only)

@@ -3,6 +3,7 @@
 isolated ops, each with its roofline, beside the reference's CPU path timed on the host cores of the same box.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--only train,decode,moe,delta]
+    python bench.py --case gemm_dense|gemm_dense_nt|gemm_dense_tn|moe_fwd|moe_bwd|delta_bf16|delta_f32|decode   (profiler captures)
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \\
         bench.py --gpus N --steps K --warmup W
 
@@ -361,7 +362,7 @@ def run_train(hs: Harness, args):
         for k, v in t.items():
             tl[k] = max(tl.get(k, 0.0), hs.max_over_ranks(v))
     free_b, total_b = torch.cuda.mem_get_info()
-    table = hs.kernel_table(step) if hs.rank == 0 else None
+    table = hs.kernel_table(step)      # every rank: the step holds collectives
     n_tok = c["global_batch"] * c["T"]
     flop_tok = train_flop_per_token(L)
     tf_per_gpu = n_tok * flop_tok / (dev_ms * 1e-3) / 1e12 / hs.world
@@ -766,9 +767,107 @@ def run_delta(hs: Harness, args, bf16: bool):
     }
 
 
+# ------------------------------------------------------------------ single-kernel cases (for profiler captures)
+def run_case(hs: Harness, args):
+    """One small case of one kernel family, a few launches, a few GB on the device at most: what a profiler capture
+    should run (`ncu -k regex:... -c 3 python bench.py --case NAME`). Prints one JSON line with the CUDA-event time."""
+    import asca_b200
+    from asca_b200 import ops
+
+    torch = hs.torch
+    dev = hs.dev
+    f32 = dict(dtype=torch.float32, device=dev)
+    g = torch.Generator(device=dev).manual_seed(0)
+    name = args.case
+    reps = 3
+    if name.startswith("gemm_dense"):
+        # the qkv projection of the training configuration at 8 sequences: 32768 x 6144 x 2048 (forward, input gradient,
+        # weight gradient forms)
+        mode = {"gemm_dense": asca_b200.NN, "gemm_dense_nt": asca_b200.NT, "gemm_dense_tn": asca_b200.TN}[name]
+        m_, n_, k_ = {asca_b200.NN: (32768, 6144, 2048), asca_b200.NT: (32768, 2048, 6144), asca_b200.TN: (2048, 6144, 32768)}[mode]
+        a = torch.randn((k_, m_) if mode == asca_b200.TN else (m_, k_), generator=g, **f32).bfloat16()
+        b = torch.randn((n_, k_) if mode == asca_b200.NT else (k_, n_), generator=g, **f32).bfloat16()
+        c = torch.empty(m_, n_, **f32)
+        fn = lambda: ops.gemm(hs.gpu, a, b, mode, out=c)  # noqa: E731
+        work, unit = 2.0 * m_ * n_ * k_, "TFLOP/s"
+    elif name in ("moe_fwd", "moe_bwd"):
+        # the expert FFN of the training configuration on one micro-batch of 2 sequences (8192 uniform random bytes)
+        n, d, F, E = 8192, 2048, 4096, 64
+        ids = torch.from_numpy(reference_ids(5, n).view(np.int32)).to(dev)
+        xn = torch.randn(n, d, generator=g, **f32).bfloat16()
+        w1 = (torch.randn(d, E * F, generator=g, **f32) * 0.02).bfloat16()
+        w2 = (torch.randn(E * F, d, generator=g, **f32) * 0.02).bfloat16()
+        b1, b2 = torch.zeros(E * F, **f32), torch.zeros(d, **f32)
+        dout = torch.randn(n, d, generator=g, **f32)
+        perm, off = ops.moe_dispatch(hs.gpu, ids, E)
+        out, pre_p, hid_p = ops.moe_fwd(hs.gpu, xn, w1, b1, w2, b2, perm, off, F, E)
+        if name == "moe_fwd":
+            fn = lambda: ops.moe_fwd(hs.gpu, xn, w1, b1, w2, b2, perm, off, F, E, out=out, pre_p=pre_p, hid_p=hid_p)  # noqa: E731
+            work = 4.0 * n * d * F
+        else:
+            grads = ops.moe_bwd(hs.gpu, xn, w1, w2, pre_p, hid_p, dout, perm, off, F, E)
+            fn = lambda: ops.moe_bwd(hs.gpu, xn, w1, w2, pre_p, hid_p, dout, perm, off, F, E, grads=grads)  # noqa: E731
+            work = 8.0 * n * d * F
+        unit = "TFLOP/s"
+    elif name in ("delta_bf16", "delta_f32"):
+        # the isolated delta op at B = 2 (32 chains x 4096 tokens): traffic scales with the number of chains
+        b, h, t, dh = 2, 16, 4096, 128
+        n, d = b * t, h * dh
+        q = torch.nn.functional.normalize(torch.randn(n, h, dh, generator=g, **f32), dim=-1).reshape(n, d).contiguous()
+        k = torch.nn.functional.normalize(torch.randn(n, h, dh, generator=g, **f32), dim=-1).reshape(n, d).contiguous()
+        v, d_o = torch.randn(n, d, generator=g, **f32), torch.randn(n, d, generator=g, **f32)
+        alpha = torch.sigmoid(2 + 0.5 * torch.randn(n, h, generator=g, **f32))
+        beta = torch.sigmoid(torch.randn(n, h, generator=g, **f32))
+        qn, kn = torch.ones(n, h, **f32), torch.ones(n, h, **f32)
+        if name == "delta_bf16":
+            q, k, v, d_o = (x.bfloat16() for x in (q, k, v, d_o))
+        o = torch.empty_like(q)
+        ckpt = torch.empty(ops.delta_ckpt_floats(hs.gpu, b, t, h, dh, 64), **f32)
+        d_qkv, d_gate = torch.empty((n, 3 * d), **f32), torch.empty((n, 2 * h), **f32)
+
+        def fn():
+            ops.delta_fwd(hs.gpu, q, k, v, alpha, beta, b, t, h, dh, chunk=64, out=o, ckpt=ckpt)
+            ops.delta_bwd(hs.gpu, q, k, v, alpha, beta, qn, kn, d_o, ckpt, b, t, h, dh, chunk=64, d_qkv=d_qkv, d_gate=d_gate)
+
+        s_io = 2 if name == "delta_bf16" else 4
+        work, unit = 11.0 * n * d * s_io + 8.0 * n * h * 4, "GB/s"
+    elif name == "decode":
+        # a few greedy steps of the decode configuration (256 streams)
+        c = DECODE
+        model = asca_b200.Model(hs.gpu, c["V"], c["d"], c["H"], c["L"], c["E"], c["F"])
+        model.set_compute(asca_b200.BF16)
+        hs.fill_normal(model.buffers()[0], model.n, seed=0)
+        model.params_changed()
+        state = model.new_decode_state(c["streams"])
+        ids0 = reference_ids(2, c["streams"])
+        model.decode_greedy(state, ids0, 2)
+        fn = lambda: model.decode_greedy(state, ids0, 2)  # noqa: E731
+        dh = c["d"] // c["H"]
+        work = 2.0 * (2 * c["L"] * c["H"] * dh * dh * 4 * c["streams"]
+                      + (c["L"] * (c["d"] * 3 * c["d"] + c["d"] * 2 * c["H"] + c["d"] * c["d"] + 2 * c["E"] * c["d"] * c["F"]) + c["d"] * c["V"]) * 2)
+        unit = "GB/s"
+        reps = 2
+    else:
+        raise SystemExit(f"bench.py: unknown --case {name}")
+    fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    print(json.dumps({"case": name, "ms": ms, "achieved": work / (ms * 1e-3) / (1e12 if unit == "TFLOP/s" else 1e9), "unit": unit,
+                      "launches": hs.gpu.launch_count()}))
+
+
 # ------------------------------------------------------------------ driver
 def run_ours(args):
     hs = Harness()
+    if args.case:
+        run_case(hs, args)
+        return
     only = set(filter(None, args.only.split(","))) or {"train", "decode", "moe", "delta"}
     line = run_train(hs, args) if "train" in only else None
     records = {}
@@ -809,6 +908,8 @@ def main():
     ap.add_argument("--layers", type=int, default=4, help="blocks of the 24-block training stack to run (the largest that fits one GPU)")
     ap.add_argument("--only", default="", help="comma-separated subset of train,decode,moe,delta")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline legs")
+    ap.add_argument("--case", default="", help="run one small single-kernel case instead (for profiler captures): gemm_dense, "
+                                               "gemm_dense_nt, gemm_dense_tn, moe_fwd, moe_bwd, delta_bf16, delta_f32, decode")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

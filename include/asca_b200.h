@@ -65,6 +65,12 @@ int asca_ctx_profile(asca_ctx* ctx, int on);
 int asca_ctx_profile_read(asca_ctx* ctx, int index, const char** name, float* ms);
 /* Algorithmic work of entry `index` where the launcher states it (FLOPs of a tensor-core product), else 0. */
 int asca_ctx_profile_work(asca_ctx* ctx, int index, double* work);
+/* Self-test of the kernels' give-up path: launches one CTA that holds TMEM and waits, with the same bounded wait
+ * the tensor-core kernels use but a limit of `limit_cycles` (at most 1e8), on an mbarrier nothing will complete. The
+ * wait runs out, the kernel raises the context's error word, frees its TMEM and returns; the call reports
+ * ASCA_ERR_DEVICE (the expected answer), *gave_up = 1 and *abort_seen = 1, and the context stays usable. Nothing
+ * hangs and nothing faults: this is how the error path is tested. */
+int asca_selftest_wait_timeout(asca_ctx* ctx, int64_t limit_cycles, int* gave_up, int* abort_seen);
 /* Library version string and the arch it was compiled for ("sm_100a"). */
 const char* asca_version(void);
 

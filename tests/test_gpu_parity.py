@@ -812,3 +812,28 @@ def test_head_cross_entropy_and_resident_adamw_host_forms(orc, gpu):
     want = x.astype(np.float64) / (1 + np.exp(-x.astype(np.float64)))
     gpu.silu_inplace(x)
     assert rel_err(x, want) < F32_TOL
+
+
+@pytest.mark.gpu
+def test_a_bounded_wait_that_runs_out_reports_and_leaves_the_context_usable(orc, gpu):
+    """The give-up path of the tensor-core kernels (a wait limit passed from the host as 20,000 cycles, on an mbarrier
+    nothing arms): the kernel returns by itself, the call answers ASCA_ERR_DEVICE, the TMEM it held is free again (a
+    tensor-core product right after allocates all of it) and the next calls work."""
+    import ctypes
+
+    import asca_b200
+    import torch
+    from asca_b200 import NN, ops
+
+    gave_up, seen = ctypes.c_int(), ctypes.c_int()
+    rc = gpu.lib.asca_selftest_wait_timeout(gpu._ctx, ctypes.c_int64(20000), ctypes.byref(gave_up), ctypes.byref(seen))
+    assert rc == -5 and gave_up.value == 1 and seen.value == 1
+    assert b"bounded wait" in gpu.lib.asca_last_error(gpu._ctx)
+    gpu.sync()                                                   # the error word was cleared: no stale error
+    rng = orc.Rng(1)
+    a, b = rng.normal((512, 4096)), rng.normal((4096, 512), 0.1)
+    got = ops.gemm(gpu, torch.from_numpy(a).cuda().bfloat16(), torch.from_numpy(b).cuda().bfloat16(), NN)   # 512 TMEM columns
+    gpu.sync()
+    assert rel_err(got.cpu().numpy(), orc.matmul(a, b)) < BF16_TOL
+    with pytest.raises(asca_b200.AscaError):
+        gpu._call("asca_selftest_wait_timeout", gpu._ctx, ctypes.c_int64(10 ** 10), None, None)   # limit out of range
