@@ -25,6 +25,7 @@
 #include "gemm_tc.cuh"
 
 #include <algorithm>
+#include <cstdlib>
 #include "tc_common.cuh"
 
 namespace gemm_tc {
@@ -38,9 +39,13 @@ constexpr int A_BYTES = BM * BK * 2;
 // used when the problem has at least two waves of such tiles.
 // DEEP: a problem of at most one 128 x 128 tile per SM (a decode step's products) runs one CTA per SM with a
 // 6-stage ring: its k-loop streams weights that are cold in L2, and three stages do not cover the HBM latency.
-template <int BN, bool DEEP = false> struct Shape {
-    static constexpr int STAGES = BN == 128 ? (DEEP ? 6 : 3) : 4;
-    static constexpr int B_BYTES = BN * BK * 2;
+// PAIR: a cluster of two CTAs computes 256 x 256 tiles with cta_group::2 instructions (M = 256, N = 256). Each CTA
+// loads its own 128 rows of A and its own 128 of the tile's 256 B columns (32 KiB per k-tile for 4.2 MFLOP on this SM
+// against 48 KiB for the 128 x 256 tile and 32 KiB per 2.1 MFLOP for the 128 x 128 one): shared-memory traffic per
+// FLOP, which is what bounds the single-CTA shapes, halves. 6-stage ring, all 512 TMEM columns, one CTA per SM.
+template <int BN, bool DEEP = false, bool PAIR = false> struct Shape {
+    static constexpr int STAGES = PAIR ? 6 : BN == 128 ? (DEEP ? 6 : 3) : 4;
+    static constexpr int B_BYTES = (PAIR ? BN / 2 : BN) * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int TMEM_COLS = 2 * BN;      // two accumulator buffers
     static constexpr int CTAS_PER_SM = (BN == 128 && !DEEP) ? 2 : 1;
@@ -77,12 +82,17 @@ __device__ __forceinline__ float silu_grad_f(float p) {
     return sg * (1.0f + p * (1.0f - sg));
 }
 
-template <int MODE, int BN, bool DEEP>
-__global__ void __launch_bounds__(THREADS, Shape<BN, DEEP>::CTAS_PER_SM) gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA,
+template <int MODE, int BN, bool DEEP, bool PAIR>
+__global__ void __launch_bounds__(THREADS, Shape<BN, DEEP, PAIR>::CTAS_PER_SM) gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA,
                                                              const __grid_constant__ CUtensorMap mapB, const KP p) {
     constexpr bool A_MN = (MODE == ASCA_TN);   // A operand MN-major
     constexpr bool B_MN = (MODE != ASCA_NT);   // B operand MN-major
-    constexpr int STAGES = Shape<BN, DEEP>::STAGES, STAGE_BYTES = Shape<BN, DEEP>::STAGE_BYTES, TMEM_COLS = Shape<BN, DEEP>::TMEM_COLS;
+    using SH = Shape<BN, DEEP, PAIR>;
+    constexpr int STAGES = SH::STAGES, STAGE_BYTES = SH::STAGE_BYTES, TMEM_COLS = SH::TMEM_COLS;
+    constexpr int TM = PAIR ? 2 * BM : BM;       // rows of an output tile (both CTAs of a pair)
+    constexpr int BNL = PAIR ? BN / 2 : BN;      // B columns this CTA loads per tile
+    const int rank = PAIR ? (int)tc::cluster_ctarank() : 0;   // 0 = the CTA that issues the pair's instructions
+    const int n_walkers = PAIR ? (int)gridDim.x / 2 : (int)gridDim.x, walker = PAIR ? (int)blockIdx.x / 2 : (int)blockIdx.x;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* staging = tiles + STAGES * STAGE_BYTES;                 // 4 epilogue warps x 2 KiB
@@ -90,7 +100,8 @@ __global__ void __launch_bounds__(THREADS, Shape<BN, DEEP>::CTAS_PER_SM) gemm_tc
     uint64_t* empty = full + STAGES;
     uint64_t* acc_full = empty + STAGES;     // [2] accumulator buffer written (MMA -> epilogue)
     uint64_t* acc_empty = acc_full + 2;      // [2] accumulator buffer read out (epilogue -> MMA)
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    uint64_t* peer_full = acc_empty + 2;     // [STAGES] PAIR, even CTA: the odd CTA's stage has landed
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(peer_full + STAGES);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     int* prefix = const_cast<int*>(abort_flag) + 1;                  // [n_groups + 1] first tile of every group
 
@@ -99,7 +110,10 @@ __global__ void __launch_bounds__(THREADS, Shape<BN, DEEP>::CTAS_PER_SM) gemm_tc
     const int n_groups = p.group_dim == GROUP_NONE ? 1 : p.n_groups;
 
     // ---- tile table: group g owns tiles [prefix[g], prefix[g+1]), tile = tile_m * tiles_n + tile_n within it
-    if (warp == 1) tc::tmem_alloc(tmem_slot, TMEM_COLS);
+    if (warp == 1) {
+        if (PAIR) tc::tmem_alloc_pair(tmem_slot, TMEM_COLS);
+        else tc::tmem_alloc(tmem_slot, TMEM_COLS);
+    }
     pdl_wait();   // the group offsets below may be the previous kernel's output
     if (warp == 0) {
         int base = 0;
@@ -107,8 +121,8 @@ __global__ void __launch_bounds__(THREADS, Shape<BN, DEEP>::CTAS_PER_SM) gemm_tc
             const int g = g0 + lane;
             int cnt = 0;
             if (g < n_groups) {
-                if (p.group_dim == GROUP_M) cnt = ((p.offsets[g + 1] - p.offsets[g] + BM - 1) / BM) * tiles_n;
-                else cnt = ((p.M + BM - 1) / BM) * tiles_n;
+                if (p.group_dim == GROUP_M) cnt = ((p.offsets[g + 1] - p.offsets[g] + TM - 1) / TM) * tiles_n;
+                else cnt = ((p.M + TM - 1) / TM) * tiles_n;
             }
             int inc = cnt;
 #pragma unroll
@@ -125,10 +139,11 @@ __global__ void __launch_bounds__(THREADS, Shape<BN, DEEP>::CTAS_PER_SM) gemm_tc
             for (int s = 0; s < STAGES; ++s) {
                 tc::mbar_init(&full[s], 1);
                 tc::mbar_init(&empty[s], 1);
+                tc::mbar_init(&peer_full[s], 1);
             }
             for (int b = 0; b < 2; ++b) {
                 tc::mbar_init(&acc_full[b], 1);
-                tc::mbar_init(&acc_empty[b], 4);
+                tc::mbar_init(&acc_empty[b], PAIR ? 8 : 4);   // epilogue warps of both CTAs
             }
             tc::mbar_fence_init();
             tc::prefetch_tensormap(&mapA);
@@ -137,6 +152,7 @@ __global__ void __launch_bounds__(THREADS, Shape<BN, DEEP>::CTAS_PER_SM) gemm_tc
     }
     tc::tcgen05_fence_before();
     __syncthreads();
+    if (PAIR) tc::cluster_sync_all();   // the peer's barriers exist before anything is signalled across
     tc::tcgen05_fence_after();
     pdl_launch_dependents();   // after this CTA holds its TMEM: a dependent that becomes resident early cannot take it
     const uint32_t tmem_base = *tmem_slot;
@@ -155,7 +171,7 @@ __global__ void __launch_bounds__(THREADS, Shape<BN, DEEP>::CTAS_PER_SM) gemm_tc
         Tile x;
         x.g = lo;
         const int in = t - prefix[lo];
-        x.m0 = (in / tiles_n) * BM;
+        x.m0 = (in / tiles_n) * TM + rank * BM;   // this CTA's 128 rows of the tile
         x.n0 = (in % tiles_n) * BN;
         int seg_lo = 0;
         x.M = p.M;
@@ -178,8 +194,9 @@ __global__ void __launch_bounds__(THREADS, Shape<BN, DEEP>::CTAS_PER_SM) gemm_tc
         if (lane == 0) {
             uint32_t it = 0;   // k-tiles issued so far, across tiles: ring slot it % STAGES
             bool ok = true;
-            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+            for (int t = walker; t < total_tiles && ok; t += n_walkers) {
                 const Tile x = locate(t);
+                const int nl0 = x.n0 + rank * BNL;   // first B column this CTA loads
                 for (int kt = 0; kt < x.num_k; ++kt, ++it) {
                     const int s = it % STAGES;
                     if (it >= STAGES && !tc::mbar_wait(&empty[s], ((it / STAGES) - 1) & 1, abort_flag, p.err_word, 101)) {
@@ -199,10 +216,10 @@ __global__ void __launch_bounds__(THREADS, Shape<BN, DEEP>::CTAS_PER_SM) gemm_tc
                     if (B_MN) {   // memory (k rows x N)
                         const int kr = (MODE == ASCA_TN ? x.row_base_k : 0) + k0 + x.b_out;
 #pragma unroll
-                        for (int nb = 0; nb < BN / 64; ++nb)   // boxes of 64 columns
-                            tc::tma_load_2d(b_s + nb * 8192, &mapB, x.n0 + nb * 64 + x.b_in, kr, &full[s]);
+                        for (int nb = 0; nb < BNL / 64; ++nb)   // boxes of 64 columns
+                            tc::tma_load_2d(b_s + nb * 8192, &mapB, nl0 + nb * 64 + x.b_in, kr, &full[s]);
                     } else {      // memory (N rows x K)
-                        tc::tma_load_2d(b_s, &mapB, k0 + x.b_in, x.n0 + x.b_out, &full[s]);
+                        tc::tma_load_2d(b_s, &mapB, k0 + x.b_in, nl0 + x.b_out, &full[s]);
                     }
                 }
             }
@@ -212,7 +229,7 @@ __global__ void __launch_bounds__(THREADS, Shape<BN, DEEP>::CTAS_PER_SM) gemm_tc
         // One thread runs the loop (the rest of the warp joins only to zero a ragged k-tile): wait for the
         // stage, four tcgen05.mma whose descriptors are the stage's base descriptor plus a constant, commit.
         // The loop's own dependent instructions are what bounds a single MMA stream, so it is kept short.
-        constexpr uint32_t IDESC = tc::idesc_bf16_f32(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+        constexpr uint32_t IDESC = tc::idesc_bf16_f32(TM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
         constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);          // SBO 1024, version 1, 128-byte swizzle
         constexpr uint32_t A_LBO = (A_MN ? 8192u : 16u) >> 4, B_LBO = (B_MN ? 8192u : 16u) >> 4;
         constexpr uint32_t A_K16 = (A_MN ? 2048u : 32u) >> 4, B_K16 = (B_MN ? 2048u : 32u) >> 4;   // per k16 step, in 16-byte units
@@ -221,28 +238,47 @@ __global__ void __launch_bounds__(THREADS, Shape<BN, DEEP>::CTAS_PER_SM) gemm_tc
         bool ok = true;
         uint32_t it = 0;
         int tl = 0;   // tiles done by this CTA: accumulator buffer tl & 1
-        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tl) {
+        for (int t = walker; t < total_tiles && ok; t += n_walkers, ++tl) {
             const Tile x = locate(t);
             const int buf = tl & 1;
             const uint32_t tmem_acc = tmem_base + buf * BN;
             const bool ragged = p.group_dim == GROUP_K && (x.K % BK) != 0;   // warp-uniform
             const int n_plain = ragged ? x.num_k - 1 : x.num_k;
-            if (lane == 0) {
-                if (tl >= 2)   // the epilogue has read this buffer's previous tile out
-                    ok = tc::mbar_wait(&acc_empty[buf], ((tl >> 1) - 1) & 1, abort_flag, p.err_word, 104);
+            if (PAIR && rank == 1) {
+                // the odd CTA issues nothing: it tells the even CTA when each of its stages has landed
+                if (lane == 0) {
+                    for (int kt = 0; kt < n_plain && ok; ++kt, ++it) {
+                        const uint32_t s = it % STAGES;
+                        ok = tc::mbar_wait(&full[s], (it / STAGES) & 1, abort_flag, p.err_word, 105);
+                        if (ok) tc::mbar_arrive_cluster(tc::mapa_u32(tc::smem_u32(&peer_full[s]), 0));
+                    }
+                }
+            } else if (lane == 0) {
+                if (tl >= 2) {   // the epilogue (of both CTAs) has read this buffer's previous tile out
+                    ok = PAIR ? tc::mbar_wait_cluster(&acc_empty[buf], ((tl >> 1) - 1) & 1, abort_flag, p.err_word, 104)
+                              : tc::mbar_wait(&acc_empty[buf], ((tl >> 1) - 1) & 1, abort_flag, p.err_word, 104);
+                }
                 tc::tcgen05_fence_after();
                 for (int kt = 0; kt < n_plain && ok; ++kt, ++it) {
                     const uint32_t s = it % STAGES;
                     ok = tc::mbar_wait(&full[s], (it / STAGES) & 1, abort_flag, p.err_word, 102);
+                    if (ok && PAIR) ok = tc::mbar_wait_cluster(&peer_full[s], (it / STAGES) & 1, abort_flag, p.err_word, 106);
                     if (!ok) break;
                     tc::tcgen05_fence_after();
                     const uint32_t a_lo = a_lo0 + s * (STAGE_BYTES >> 4), b_lo = b_lo0 + s * (STAGE_BYTES >> 4);
 #pragma unroll
-                    for (int k16 = 0; k16 < BK / 16; ++k16)
-                        tc::umma_bf16(tmem_acc, ((uint64_t)DESC_HI << 32) | (a_lo + k16 * A_K16),
-                                      ((uint64_t)DESC_HI << 32) | (b_lo + k16 * B_K16), IDESC, (kt > 0 || k16 > 0) ? 1u : 0u);
-                    tc::umma_commit(&empty[s]);                       // slot free once these MMAs retire
-                    if (kt == x.num_k - 1) tc::umma_commit(&acc_full[buf]);
+                    for (int k16 = 0; k16 < BK / 16; ++k16) {
+                        const uint64_t da = ((uint64_t)DESC_HI << 32) | (a_lo + k16 * A_K16), db = ((uint64_t)DESC_HI << 32) | (b_lo + k16 * B_K16);
+                        if (PAIR) tc::umma_bf16_pair(tmem_acc, da, db, IDESC, (kt > 0 || k16 > 0) ? 1u : 0u);
+                        else tc::umma_bf16(tmem_acc, da, db, IDESC, (kt > 0 || k16 > 0) ? 1u : 0u);
+                    }
+                    if (PAIR) {
+                        tc::umma_commit_pair(&empty[s]);              // the slot is free in both CTAs once these MMAs retire
+                        if (kt == x.num_k - 1) tc::umma_commit_pair(&acc_full[buf]);
+                    } else {
+                        tc::umma_commit(&empty[s]);                   // slot free once these MMAs retire
+                        if (kt == x.num_k - 1) tc::umma_commit(&acc_full[buf]);
+                    }
                 }
             }
             if (ragged) {
@@ -251,6 +287,8 @@ __global__ void __launch_bounds__(THREADS, Shape<BN, DEEP>::CTAS_PER_SM) gemm_tc
                 int got = 0;
                 if (lane == 0) {
                     got = ok && tc::mbar_wait(&full[(it) % STAGES], ((it) / STAGES) & 1, abort_flag, p.err_word, 102) ? 1 : 0;
+                    if (got && PAIR && rank == 0)   // the odd CTA zeroes its own tile before it reports the stage
+                        got = tc::mbar_wait_cluster(&peer_full[(it) % STAGES], ((it) / STAGES) & 1, abort_flag, p.err_word, 106) ? 1 : 0;
                 }
                 got = __shfl_sync(0xffffffffu, got, 0);
                 const uint32_t it_r = __shfl_sync(0xffffffffu, it, 0);
@@ -269,18 +307,32 @@ __global__ void __launch_bounds__(THREADS, Shape<BN, DEEP>::CTAS_PER_SM) gemm_tc
                     tc::fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0) {
-                        const uint32_t a_lo = a_lo0 + s * (STAGE_BYTES >> 4), b_lo = b_lo0 + s * (STAGE_BYTES >> 4);
+                        if (PAIR && rank == 1) {
+                            tc::mbar_arrive_cluster(tc::mapa_u32(tc::smem_u32(&peer_full[s]), 0));
+                        } else {
+                            const uint32_t a_lo = a_lo0 + s * (STAGE_BYTES >> 4), b_lo = b_lo0 + s * (STAGE_BYTES >> 4);
 #pragma unroll
-                        for (int k16 = 0; k16 < BK / 16; ++k16)
-                            tc::umma_bf16(tmem_acc, ((uint64_t)DESC_HI << 32) | (a_lo + k16 * A_K16),
-                                          ((uint64_t)DESC_HI << 32) | (b_lo + k16 * B_K16), IDESC, (kt > 0 || k16 > 0) ? 1u : 0u);
-                        tc::umma_commit(&empty[s]);
-                        tc::umma_commit(&acc_full[buf]);
+                            for (int k16 = 0; k16 < BK / 16; ++k16) {
+                                const uint64_t da = ((uint64_t)DESC_HI << 32) | (a_lo + k16 * A_K16), db = ((uint64_t)DESC_HI << 32) | (b_lo + k16 * B_K16);
+                                if (PAIR) tc::umma_bf16_pair(tmem_acc, da, db, IDESC, (kt > 0 || k16 > 0) ? 1u : 0u);
+                                else tc::umma_bf16(tmem_acc, da, db, IDESC, (kt > 0 || k16 > 0) ? 1u : 0u);
+                            }
+                            if (PAIR) {
+                                tc::umma_commit_pair(&empty[s]);
+                                tc::umma_commit_pair(&acc_full[buf]);
+                            } else {
+                                tc::umma_commit(&empty[s]);
+                                tc::umma_commit(&acc_full[buf]);
+                            }
+                        }
                         ++it;
                     }
                 }
             }
-            if (lane == 0 && ok && x.num_k == 0) tc::mbar_arrive(&acc_full[buf]);   // empty expert: the epilogue stores zeros
+            if (lane == 0 && ok && x.num_k == 0 && rank == 0) {   // empty expert: the epilogue stores zeros
+                tc::mbar_arrive(&acc_full[buf]);
+                if (PAIR) tc::mbar_arrive_cluster(tc::mapa_u32(tc::smem_u32(&acc_full[buf]), 1));
+            }
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;   // lane 0's verdict; keeps the warp's tile loops in step
         }
     } else {
@@ -297,12 +349,14 @@ __global__ void __launch_bounds__(THREADS, Shape<BN, DEEP>::CTAS_PER_SM) gemm_tc
         const int l4 = lane & 3, rsub = lane >> 2;   // store phase: 4 lanes per row (64 bytes), 8 rows per instruction
         bool ok = true;
         int tl = 0;
-        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tl) {
+        for (int t = walker; t < total_tiles && ok; t += n_walkers, ++tl) {
             const Tile x = locate(t);
             const int buf = tl & 1;
             const uint32_t tmem_acc = tmem_base + buf * BN;
             int got = 0;
-            if (lane == 0) got = tc::mbar_wait(&acc_full[buf], (tl >> 1) & 1, abort_flag, p.err_word, 103) ? 1 : 0;
+            if (lane == 0)
+                got = (PAIR ? tc::mbar_wait_cluster(&acc_full[buf], (tl >> 1) & 1, abort_flag, p.err_word, 103)
+                            : tc::mbar_wait(&acc_full[buf], (tl >> 1) & 1, abort_flag, p.err_word, 103)) ? 1 : 0;
             ok = __shfl_sync(0xffffffffu, got, 0) != 0;  // uniform: tcgen05.ld below is warp-aligned
             if (!ok) break;
             tc::tcgen05_fence_after();
@@ -334,7 +388,10 @@ __global__ void __launch_bounds__(THREADS, Shape<BN, DEEP>::CTAS_PER_SM) gemm_tc
                 if (c == BN / 32 - 1) {   // this warp's quarter of the buffer is free for the tile after next
                     tc::tcgen05_fence_before();
                     __syncwarp();
-                    if (lane == 0) tc::mbar_arrive(&acc_empty[buf]);
+                    if (lane == 0) {
+                        if (PAIR) tc::mbar_arrive_cluster(tc::mapa_u32(tc::smem_u32(&acc_empty[buf]), 0));   // counted by the even CTA
+                        else tc::mbar_arrive(&acc_empty[buf]);
+                    }
                 }
 #pragma unroll
                 for (int hlf = 0; hlf < 2; ++hlf) {
@@ -459,8 +516,12 @@ __global__ void __launch_bounds__(THREADS, Shape<BN, DEEP>::CTAS_PER_SM) gemm_tc
     // ---- teardown: everyone meets, then the allocating warp frees TMEM
     tc::tcgen05_fence_before();
     __syncthreads();
+    if (PAIR) tc::cluster_sync_all();     // neither CTA leaves (or frees TMEM) while its peer may still signal it
     if (*abort_flag) __nanosleep(20000);  // let copies already in flight land before the CTA exits
-    if (warp == 1) tc::tmem_dealloc(tmem_base, TMEM_COLS);
+    if (warp == 1) {
+        if (PAIR) tc::tmem_dealloc_pair(tmem_base, TMEM_COLS);
+        else tc::tmem_dealloc(tmem_base, TMEM_COLS);
+    }
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -511,13 +572,13 @@ bool supported(const Args& a) {
     return true;
 }
 
-template <int BN, bool DEEP>
+template <int BN, bool DEEP, bool PAIR = false>
 static int launch_shape(asca_ctx* ctx, const Args& a, int64_t grid) {
     CUtensorMap mapA, mapB;
     bool ok;
     if (a.mode == ASCA_TN) ok = make_map(&mapA, a.A, a.a_rows, a.a_cols, a.lda, 64, 64);
     else ok = make_map(&mapA, a.A, a.a_rows, a.a_cols, a.lda, 64, 128);
-    if (a.mode == ASCA_NT) ok = ok && make_map(&mapB, a.B, a.b_rows, a.b_cols, a.ldb, 64, BN);
+    if (a.mode == ASCA_NT) ok = ok && make_map(&mapB, a.B, a.b_rows, a.b_cols, a.ldb, 64, PAIR ? BN / 2 : BN);
     else ok = ok && make_map(&mapB, a.B, a.b_rows, a.b_cols, a.ldb, 64, 64);
     if (!ok) return asca_fail(ctx, ASCA_ERR_CUDA, "gemm_tc: cuTensorMapEncodeTiled failed");
     KP p{};
@@ -528,26 +589,51 @@ static int launch_shape(asca_ctx* ctx, const Args& a, int64_t grid) {
     p.c_gstride = a.c_gstride; p.bias_gstride = a.bias_gstride;
     p.epi = a.epi; p.aux = a.aux; p.ldaux = a.ldaux; p.C2 = a.C2; p.ldc2 = a.ldc2; p.c2_only = a.c2_only;
     p.err_word = ctx->err_word;
-    const size_t smem = Shape<BN, DEEP>::SMEM_FIXED + (size_t)((a.group_dim == GROUP_NONE ? 1 : a.n_groups) + 2) * 4;
+    using SH = Shape<BN, DEEP, PAIR>;
+    const size_t smem = SH::SMEM_FIXED + (size_t)((a.group_dim == GROUP_NONE ? 1 : a.n_groups) + 2) * 4;
     auto go = [&](auto kern) -> cudaError_t {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)(Shape<BN, DEEP>::SMEM_FIXED + (MAX_GROUPS + 2) * 4));
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(SH::SMEM_FIXED + (MAX_GROUPS + 2) * 4));
         if (e != cudaSuccess) return e;
-        return asca_launch(ctx, kern, dim3((unsigned)grid), dim3(THREADS), smem, mapA, mapB, p);
+        if (!PAIR) return asca_launch(ctx, kern, dim3((unsigned)grid), dim3(THREADS), smem, mapA, mapB, p);
+        // pairs of CTAs: a cluster of two per walker (grid = 2 x walkers)
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)grid);
+        cfg.blockDim = dim3(THREADS);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = ctx->stream;
+        cudaLaunchAttribute at[2];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = 2;
+        at[0].val.clusterDim.y = 1;
+        at[0].val.clusterDim.z = 1;
+        at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = at;
+        cfg.numAttrs = ctx->pdl ? 2 : 1;
+        return cudaLaunchKernelEx(&cfg, kern, mapA, mapB, p);
     };
-    cudaError_t e = a.mode == ASCA_NN ? go(gemm_tc_kernel<ASCA_NN, BN, DEEP>)
-                    : a.mode == ASCA_TN ? go(gemm_tc_kernel<ASCA_TN, BN, DEEP>) : go(gemm_tc_kernel<ASCA_NT, BN, DEEP>);
+    cudaError_t e = a.mode == ASCA_NN ? go(gemm_tc_kernel<ASCA_NN, BN, DEEP, PAIR>)
+                    : a.mode == ASCA_TN ? go(gemm_tc_kernel<ASCA_TN, BN, DEEP, PAIR>) : go(gemm_tc_kernel<ASCA_NT, BN, DEEP, PAIR>);
     ASCA_CUDA(ctx, e);
     ctx->launches++;
     return ASCA_OK;
 }
 
-// upper bound on the number of 128 x bn tiles (exact unless rows are grouped by expert)
-static int64_t tile_bound(const Args& a, int bn) {
+// upper bound on the number of bm x bn tiles (exact unless rows are grouped by expert)
+static int64_t tile_bound(const Args& a, int bn, int bm = BM) {
     const int64_t tn = (a.N + bn - 1) / bn;
-    if (a.group_dim == GROUP_NONE) return ((int64_t)(a.M + BM - 1) / BM) * tn;
-    if (a.group_dim == GROUP_M) return (a.total_rows / BM + a.n_groups) * tn;
-    return (int64_t)a.n_groups * ((a.M + BM - 1) / BM) * tn;
+    if (a.group_dim == GROUP_NONE) return ((int64_t)(a.M + bm - 1) / bm) * tn;
+    if (a.group_dim == GROUP_M) return (a.total_rows / bm + a.n_groups) * tn;
+    return (int64_t)a.n_groups * ((a.M + bm - 1) / bm) * tn;
+}
+
+// ASCA_GEMM_PAIR=0 switches the CTA-pair shape off (A/B measurements); read once.
+static bool pair_enabled() {
+    static const bool on = [] {
+        const char* e = getenv("ASCA_GEMM_PAIR");
+        return !(e && e[0] == '0');
+    }();
+    return on;
 }
 
 int launch(asca_ctx* ctx, const Args& a) {
@@ -563,6 +649,12 @@ int launch(asca_ctx* ctx, const Args& a) {
     // persistent: the CTAs walk the tiles round-robin. Wide tiles for dense problems with a long k-loop and at least
     // two waves of tiles (measured: +10-15 % there; with k <= 2048 or expert-grouped rows the 128 KiB epilogue per
     // tile and the single stream per SM cost more than the wider instruction gains).
+    // CTA pairs on 256 x 256 tiles: dense and expert-grouped products with at least one tile per pair of SMs
+    const int64_t pairs = tile_bound(a, 256, 256);
+    const bool pair_shape = a.group_dim == GROUP_M ? a.total_rows >= 512 * (int64_t)a.n_groups   // ragged 256-row tiles cost <= 1/4
+                                                   : a.M >= 256;
+    if (pair_enabled() && pair_shape && a.N >= 256 && pairs >= n_sm / 2)
+        return launch_shape<256, false, true>(ctx, a, 2 * std::min<int64_t>(pairs, n_sm / 2));
     const int64_t wide = tile_bound(a, 256);
     if (a.group_dim == GROUP_NONE && a.K >= 4096 && a.N >= 256 && wide >= 2 * n_sm)
         return launch_shape<256, false>(ctx, a, std::min<int64_t>(wide, n_sm));

@@ -35,4 +35,7 @@ def gpu():
     """The library's context on cuda:0. Fails loudly when the CUDA library is absent."""
     import asca_b200
 
-    return asca_b200.Gpu(0)
+    g = asca_b200.Gpu(0)
+    # the tests mix torch kernels (casts, transposes, clones) with the library's: one stream, so that they are ordered
+    g.use_torch_stream()
+    return g

@@ -536,9 +536,11 @@ def test_bf16_tensor_core_gemm_all_modes(orc, gpu, m, k, n):
     assert rel_err(out.cpu().numpy(), ref + bias + c0) < 1e-5
 
 
-@pytest.mark.parametrize("n,d,F,E,vocab", [(4096, 256, 512, 16, 256), (700, 64, 128, 64, 30), (9000, 128, 192, 8, 256)])
+@pytest.mark.parametrize("n,d,F,E,vocab", [(4096, 256, 512, 16, 256), (700, 64, 128, 64, 30), (9000, 128, 192, 8, 256),
+                                           (12288, 512, 1024, 16, 256)])
 def test_moe_bf16_tensor_core_ragged_experts(orc, gpu, n, d, F, E, vocab):
-    """Grouped tcgen05 products: skewed loads, experts with fewer than 64 rows and empty experts."""
+    """Grouped tcgen05 products: skewed loads, experts with fewer than 64 rows and empty experts; the last case is
+    large enough for the 256-row tiles of CTA pairs in all six grouped products (ragged 256-row tiles, ragged k)."""
     import torch
     from asca_b200 import ops
 
@@ -837,3 +839,37 @@ def test_a_bounded_wait_that_runs_out_reports_and_leaves_the_context_usable(orc,
     assert rel_err(got.cpu().numpy(), orc.matmul(a, b)) < BF16_TOL
     with pytest.raises(asca_b200.AscaError):
         gpu._call("asca_selftest_wait_timeout", gpu._ctx, ctypes.c_int64(10 ** 10), None, None)   # limit out of range
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("m,k,n", [(2304, 520, 2560), (2400, 2048, 2504), (4096, 64, 1288), (2560, 4104, 2304)])
+def test_bf16_gemm_cta_pair_tiles(gpu, m, k, n):
+    """Dense products large enough for the 256 x 256 tiles of CTA pairs (cta_group::2): all three operand forms,
+    ragged edges in M, N and K, bias and accumulate, against an f64 product of the same bf16 operands."""
+    import torch
+    from asca_b200 import ops, NN, TN, NT
+
+    g = torch.Generator(device="cuda").manual_seed(m + k + n)
+    a = torch.randn(m, k, generator=g, device="cuda").bfloat16()
+    b = (torch.randn(k, n, generator=g, device="cuda") * 0.1).bfloat16()
+    bias = torch.randn(n, generator=g, device="cuda")
+    c0 = torch.randn(m, n, generator=g, device="cuda")
+    ref = a.double() @ b.double()
+    scale = float(ref.abs().max())
+
+    def err(x, r):
+        return float((x.double() - r).abs().max()) / scale
+
+    got = ops.gemm(gpu, a, b, NN)
+    got_nt = ops.gemm(gpu, a, b.t().contiguous(), NT)
+    got_tn = ops.gemm(gpu, a.t().contiguous(), b, TN) if m % 8 == 0 else None
+    out = c0.clone()
+    ops.gemm(gpu, a, b, NN, bias=bias, out=out, accumulate=True)
+    again = ops.gemm(gpu, a, b, NN)
+    gpu.sync()
+    assert err(got, ref) < 1e-5
+    assert err(got_nt, ref) < 1e-5
+    if got_tn is not None:
+        assert err(got_tn, ref) < 1e-5
+    assert err(out, ref + bias.double() + c0.double()) < 1e-5
+    assert torch.equal(got, again)
