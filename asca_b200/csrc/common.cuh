@@ -83,7 +83,10 @@ int asca_fail(asca_ctx* ctx, int code, const char* fmt, ...);
 // Programmatic dependent launch, device side. pdl_wait() returns once every kernel this launch depends on has
 // finished and its writes are visible (immediately when the launch was an ordinary one); nothing before it may
 // touch global memory that another kernel writes or reads. pdl_launch_dependents() lets the next kernel on the
-// stream be scheduled; it is called after pdl_wait(), so that at most one kernel is resident ahead of the running one.
+// stream be scheduled. Most kernels call it after pdl_wait(), so that at most one kernel is resident ahead of the running
+// one; the few-row product triggers BEFORE its wait when its caller sets b_early (gemm_tc.cuh), so several of a decode
+// step's products can be resident behind one running kernel, each having read only weights, dispatch offsets and state
+// that were final before the nearest preceding kernel that waits before it triggers.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

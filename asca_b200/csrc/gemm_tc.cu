@@ -31,7 +31,7 @@
 namespace gemm_tc {
 namespace {
 
-constexpr int BM = 128, BK = 64, THREADS = 192;
+constexpr int BM = 128, BK = 64;
 constexpr int A_BYTES = BM * BK * 2;
 // Two tile shapes. 128 x 128: 3-stage ring, 256 TMEM columns, two CTAs per SM (two independent MMA streams keep the
 // tensor pipe fed). 128 x 256: one M128 N256 K16 instruction does twice the work of an N128 one for the same issue
@@ -49,7 +49,11 @@ template <int BN, bool DEEP = false, bool PAIR = false> struct Shape {
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int TMEM_COLS = 2 * BN;      // two accumulator buffers
     static constexpr int CTAS_PER_SM = (BN == 128 && !DEEP) ? 2 : 1;
-    static constexpr size_t SMEM_FIXED = (size_t)STAGES * STAGE_BYTES + 4 * 2048 /*epilogue staging*/ + 1024 /*alignment slack*/ +
+    // epilogue warps: one per TMEM lane quarter; the pair shape has one CTA per SM and 256 columns per row to move, so
+    // two warps share each quarter and split the columns
+    static constexpr int EPI_WARPS = PAIR ? 8 : 4;
+    static constexpr int THREADS = 64 + 32 * EPI_WARPS;
+    static constexpr size_t SMEM_FIXED = (size_t)STAGES * STAGE_BYTES + EPI_WARPS * 2048 /*epilogue staging*/ + 1024 /*alignment slack*/ +
                                          256 /*barriers*/;   // + (groups + 2) * 4 for the tile table
 };
 constexpr int MAX_GROUPS = 2048;
@@ -71,6 +75,9 @@ struct KP {
     __nv_bfloat16* C2;
     int64_t ldc2;
     int c2_only;
+    __nv_bfloat16 *qkv_q, *qkv_k, *qkv_v;
+    float *qkv_qn, *qkv_kn;
+    int qkv_d;
     int* err_word;
 };
 
@@ -83,7 +90,7 @@ __device__ __forceinline__ float silu_grad_f(float p) {
 }
 
 template <int MODE, int BN, bool DEEP, bool PAIR>
-__global__ void __launch_bounds__(THREADS, Shape<BN, DEEP, PAIR>::CTAS_PER_SM) gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA,
+__global__ void __launch_bounds__(Shape<BN, DEEP, PAIR>::THREADS, Shape<BN, DEEP, PAIR>::CTAS_PER_SM) gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA,
                                                              const __grid_constant__ CUtensorMap mapB, const KP p) {
     constexpr bool A_MN = (MODE == ASCA_TN);   // A operand MN-major
     constexpr bool B_MN = (MODE != ASCA_NT);   // B operand MN-major
@@ -96,7 +103,7 @@ __global__ void __launch_bounds__(THREADS, Shape<BN, DEEP, PAIR>::CTAS_PER_SM) g
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* staging = tiles + STAGES * STAGE_BYTES;                 // 4 epilogue warps x 2 KiB
-    uint64_t* full = reinterpret_cast<uint64_t*>(staging + 4 * 2048);
+    uint64_t* full = reinterpret_cast<uint64_t*>(staging + SH::EPI_WARPS * 2048);
     uint64_t* empty = full + STAGES;
     uint64_t* acc_full = empty + STAGES;     // [2] accumulator buffer written (MMA -> epilogue)
     uint64_t* acc_empty = acc_full + 2;      // [2] accumulator buffer read out (epilogue -> MMA)
@@ -143,7 +150,7 @@ __global__ void __launch_bounds__(THREADS, Shape<BN, DEEP, PAIR>::CTAS_PER_SM) g
             }
             for (int b = 0; b < 2; ++b) {
                 tc::mbar_init(&acc_full[b], 1);
-                tc::mbar_init(&acc_empty[b], PAIR ? 8 : 4);   // epilogue warps of both CTAs
+                tc::mbar_init(&acc_empty[b], PAIR ? 2 * SH::EPI_WARPS : SH::EPI_WARPS);   // epilogue warps (of both CTAs)
             }
             tc::mbar_fence_init();
             tc::prefetch_tensormap(&mapA);
@@ -342,7 +349,10 @@ __global__ void __launch_bounds__(THREADS, Shape<BN, DEEP, PAIR>::CTAS_PER_SM) g
         // memory with 4 lanes on each row's 64 bytes, where bias, activation and accumulation are applied. The TMEM buffer is
         // released after the last tcgen05.ld; the next tile's main loop runs meanwhile in the other buffer.
         const int q = warp & 3;                 // TMEM lane quarter this warp may read
-        float4* stg = reinterpret_cast<float4*>(staging + q * 2048);   // [32 rows][4 float4], index XOR ((row >> 1) & 3)
+        const int ew = warp - 2;                // epilogue warp index; warps ew and ew + 4 share lane quarter q
+        constexpr int C_PER_WARP = (BN / 32) / (SH::EPI_WARPS / 4);   // 32-column passes of a row per warp
+        const int c_lo = (ew >> 2) * C_PER_WARP;
+        float4* stg = reinterpret_cast<float4*>(staging + ew * 2048);   // [32 rows][4 float4], index XOR ((row >> 1) & 3)
         const bool c_vec = ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) && ((p.c_gstride & 3) == 0);
         const bool c2_vec = p.C2 && ((p.ldc2 & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.C2) & 7) == 0);
         const bool aux_vec = p.aux && ((p.ldaux & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.aux) & 15) == 0);
@@ -363,10 +373,42 @@ __global__ void __launch_bounds__(THREADS, Shape<BN, DEEP, PAIR>::CTAS_PER_SM) g
             float* cbase = p.C + (p.group_dim == GROUP_K ? (int64_t)x.g * p.c_gstride : 0);
             const int rows_here = x.M - (x.m0 + q * 32);   // live rows of this warp's quarter (may be <= 0 or > 32)
             // the common case gets straight-line code: full tile, plain f32 output (bias and accumulate allowed)
-            const bool fast = c_vec && !p.c_idx && (!p.C2 || (p.c2_only && c2_vec)) && p.epi == EPI_NONE && rows_here >= 32 && x.n0 + BN <= p.N &&
-                              (!p.bias || (((reinterpret_cast<uintptr_t>(p.bias) & 15) == 0) && (p.bias_gstride & 3) == 0));
+            // fused qkv epilogue (pair shape, whole tiles: the launcher checks): this warp's 128 columns are one head of q, k or v
+            const bool qkv = PAIR && p.epi == EPI_QKV;
+            float qkv_scale = 1.0f;                 // 1 / max(|z|, 1e-8) of this lane's row (q, k), 1 for v
+            __nv_bfloat16* c2p = p.C2;
+            int64_t ldc2 = p.ldc2;
+            if (qkv) {
+                const int hc0 = x.n0 + c_lo * 32;   // first column of the head
+                const int sec = hc0 / p.qkv_d;      // 0 q, 1 k, 2 v
+                c2p = (sec == 0 ? p.qkv_q : sec == 1 ? p.qkv_k : p.qkv_v) - sec * p.qkv_d;   // column = global column - sec d
+                ldc2 = p.qkv_d;
+                if (sec < 2) {
+                    float ss = 0.0f;
+#pragma unroll 1
+                    for (int c = c_lo; c < c_lo + C_PER_WARP; ++c) {
+                        uint32_t r[32];
+                        tc::tmem_ld_32x32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
+                        tc::tmem_ld_wait();
+                        const float4* bb = reinterpret_cast<const float4*>(p.bias + x.n0 + c * 32);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const float4 b4 = bb[j];
+                            const float v0 = __uint_as_float(r[4 * j]) + b4.x, v1 = __uint_as_float(r[4 * j + 1]) + b4.y,
+                                        v2 = __uint_as_float(r[4 * j + 2]) + b4.z, v3 = __uint_as_float(r[4 * j + 3]) + b4.w;
+                            ss += (v0 * v0 + v1 * v1) + (v2 * v2 + v3 * v3);
+                        }
+                    }
+                    const float nrm = fmaxf(sqrtf(ss), 1e-8f);
+                    qkv_scale = 1.0f / nrm;
+                    const int heads = p.qkv_d / 128, head = (hc0 - sec * p.qkv_d) / 128;
+                    (sec == 0 ? p.qkv_qn : p.qkv_kn)[((int64_t)x.m0 + q * 32 + lane) * heads + head] = nrm;
+                }
+            }
+            const bool fast = qkv || (c_vec && !p.c_idx && (!p.C2 || (p.c2_only && c2_vec)) && p.epi == EPI_NONE && rows_here >= 32 && x.n0 + BN <= p.N &&
+                              (!p.bias || (((reinterpret_cast<uintptr_t>(p.bias) & 15) == 0) && (p.bias_gstride & 3) == 0)));
             float* frow = cbase + ((int64_t)x.row_base_m + x.m0 + q * 32 + rsub) * p.ldc + x.n0 + 4 * l4;   // row rsub, this lane's columns
-            const float* fbias = p.bias ? p.bias + (int64_t)x.g * p.bias_gstride + x.n0 + 4 * l4 : nullptr;
+            const float* fbias = (p.bias && !qkv) ? p.bias + (int64_t)x.g * p.bias_gstride + x.n0 + 4 * l4 : nullptr;
             // row bookkeeping of the 4 store iterations: row = 8 * i + rsub
             int64_t lrs[4], crs[4];
 #pragma unroll
@@ -376,7 +418,7 @@ __global__ void __launch_bounds__(THREADS, Shape<BN, DEEP, PAIR>::CTAS_PER_SM) g
                 crs[i] = p.c_idx && rr < rows_here ? (int64_t)p.c_idx[lrs[i]] : lrs[i];
             }
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
+            for (int c = c_lo; c < c_lo + C_PER_WARP; ++c) {
                 uint32_t r[32];
                 if (x.num_k > 0) {
                     tc::tmem_ld_32x32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
@@ -385,7 +427,18 @@ __global__ void __launch_bounds__(THREADS, Shape<BN, DEEP, PAIR>::CTAS_PER_SM) g
 #pragma unroll
                     for (int j = 0; j < 32; ++j) r[j] = 0u;
                 }
-                if (c == BN / 32 - 1) {   // this warp's quarter of the buffer is free for the tile after next
+                if (qkv) {   // bias, then the row's scale, on the f32 accumulators (lane = row)
+                    const float4* bb = reinterpret_cast<const float4*>(p.bias + x.n0 + c * 32);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float4 b4 = bb[j];
+                        r[4 * j] = __float_as_uint((__uint_as_float(r[4 * j]) + b4.x) * qkv_scale);
+                        r[4 * j + 1] = __float_as_uint((__uint_as_float(r[4 * j + 1]) + b4.y) * qkv_scale);
+                        r[4 * j + 2] = __float_as_uint((__uint_as_float(r[4 * j + 2]) + b4.z) * qkv_scale);
+                        r[4 * j + 3] = __float_as_uint((__uint_as_float(r[4 * j + 3]) + b4.w) * qkv_scale);
+                    }
+                }
+                if (c == c_lo + C_PER_WARP - 1) {   // this warp's share of the buffer is free for the tile after next
                     tc::tcgen05_fence_before();
                     __syncwarp();
                     if (lane == 0) {
@@ -411,13 +464,13 @@ __global__ void __launch_bounds__(THREADS, Shape<BN, DEEP, PAIR>::CTAS_PER_SM) g
                             old4[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
                             if (p.accumulate) old4[i] = *reinterpret_cast<const float4*>(frow + (int64_t)(8 * i) * p.ldc + co);
                         }
-                        if (p.c2_only) {   // bf16 is all the consumer reads
-                            __nv_bfloat16* hrow = p.C2 + ((int64_t)x.row_base_m + x.m0 + q * 32 + rsub) * p.ldc2 + x.n0 + 4 * l4 + co;
+                        if (p.c2_only || qkv) {   // bf16 is all the consumer reads
+                            __nv_bfloat16* hrow = c2p + ((int64_t)x.row_base_m + x.m0 + q * 32 + rsub) * ldc2 + x.n0 + 4 * l4 + co;
 #pragma unroll
                             for (int i = 0; i < 4; ++i) {
                                 const __nv_bfloat162 lo2 = __floats2bfloat162_rn(acc4[i].x + b4.x, acc4[i].y + b4.y),
                                                      hi2 = __floats2bfloat162_rn(acc4[i].z + b4.z, acc4[i].w + b4.w);
-                                *reinterpret_cast<uint2*>(hrow + (int64_t)(8 * i) * p.ldc2) =
+                                *reinterpret_cast<uint2*>(hrow + (int64_t)(8 * i) * ldc2) =
                                     make_uint2(*reinterpret_cast<const uint32_t*>(&lo2), *reinterpret_cast<const uint32_t*>(&hi2));
                             }
                             __syncwarp();
@@ -588,17 +641,18 @@ static int launch_shape(asca_ctx* ctx, const Args& a, int64_t grid) {
     p.b_goff_inner = a.b_goff_inner; p.b_goff_outer = a.b_goff_outer;
     p.c_gstride = a.c_gstride; p.bias_gstride = a.bias_gstride;
     p.epi = a.epi; p.aux = a.aux; p.ldaux = a.ldaux; p.C2 = a.C2; p.ldc2 = a.ldc2; p.c2_only = a.c2_only;
+    p.qkv_q = a.qkv_q; p.qkv_k = a.qkv_k; p.qkv_v = a.qkv_v; p.qkv_qn = a.qkv_qn; p.qkv_kn = a.qkv_kn; p.qkv_d = a.qkv_d;
     p.err_word = ctx->err_word;
     using SH = Shape<BN, DEEP, PAIR>;
     const size_t smem = SH::SMEM_FIXED + (size_t)((a.group_dim == GROUP_NONE ? 1 : a.n_groups) + 2) * 4;
     auto go = [&](auto kern) -> cudaError_t {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(SH::SMEM_FIXED + (MAX_GROUPS + 2) * 4));
         if (e != cudaSuccess) return e;
-        if (!PAIR) return asca_launch(ctx, kern, dim3((unsigned)grid), dim3(THREADS), smem, mapA, mapB, p);
+        if (!PAIR) return asca_launch(ctx, kern, dim3((unsigned)grid), dim3(SH::THREADS), smem, mapA, mapB, p);
         // pairs of CTAs: a cluster of two per walker (grid = 2 x walkers)
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3((unsigned)grid);
-        cfg.blockDim = dim3(THREADS);
+        cfg.blockDim = dim3(SH::THREADS);
         cfg.dynamicSmemBytes = smem;
         cfg.stream = ctx->stream;
         cudaLaunchAttribute at[2];
@@ -636,7 +690,17 @@ static bool pair_enabled() {
     return on;
 }
 
+static bool pair_wanted(asca_ctx* ctx, const Args& a);
+
+bool qkv_fusable(asca_ctx* ctx, const Args& a) {
+    return supported(a) && !skinny_wanted(a) && a.group_dim == GROUP_NONE && a.mode == ASCA_NN && pair_wanted(ctx, a) && a.qkv_d > 0 &&
+           a.qkv_d % 256 == 0 && a.N == 3 * a.qkv_d && a.M % 256 == 0 && a.bias && (reinterpret_cast<uintptr_t>(a.bias) & 15) == 0 &&
+           a.qkv_q && a.qkv_k && a.qkv_v && a.qkv_qn && a.qkv_kn && !a.accumulate && !a.c_idx &&
+           ((reinterpret_cast<uintptr_t>(a.qkv_q) | reinterpret_cast<uintptr_t>(a.qkv_k) | reinterpret_cast<uintptr_t>(a.qkv_v)) & 7) == 0;
+}
+
 int launch(asca_ctx* ctx, const Args& a) {
+    if (a.epi == EPI_QKV && !qkv_fusable(ctx, a)) return asca_fail(ctx, ASCA_ERR_UNSUPPORTED, "gemm_tc: this product cannot take the fused qkv epilogue");
     if (skinny_wanted(a)) return launch_skinny(ctx, a);
     // measurement harnesses: the product's algorithmic FLOPs go with the timed span
     const double rows_m = a.group_dim == GROUP_M ? (double)a.total_rows : (double)a.M;
@@ -651,10 +715,9 @@ int launch(asca_ctx* ctx, const Args& a) {
     // tile and the single stream per SM cost more than the wider instruction gains).
     // CTA pairs on 256 x 256 tiles: dense and expert-grouped products with at least one tile per pair of SMs
     const int64_t pairs = tile_bound(a, 256, 256);
-    const bool pair_shape = a.group_dim == GROUP_M ? a.total_rows >= 512 * (int64_t)a.n_groups   // ragged 256-row tiles cost <= 1/4
-                                                   : a.M >= 256;
-    if (pair_enabled() && pair_shape && a.N >= 256 && pairs >= n_sm / 2)
-        return launch_shape<256, false, true>(ctx, a, 2 * std::min<int64_t>(pairs, n_sm / 2));
+    // (row-grouped products are left on 128-row tiles unless ASCA_GEMM_PAIR=2: measured slower on pairs, 603 against 801
+    // TFLOP/s inside the training step -- ragged 256-row tiles and an epilogue with activation and two outputs)
+    if (pair_wanted(ctx, a)) return launch_shape<256, false, true>(ctx, a, 2 * std::min<int64_t>(pairs, n_sm / 2));
     const int64_t wide = tile_bound(a, 256);
     if (a.group_dim == GROUP_NONE && a.K >= 4096 && a.N >= 256 && wide >= 2 * n_sm)
         return launch_shape<256, false>(ctx, a, std::min<int64_t>(wide, n_sm));
@@ -662,6 +725,14 @@ int launch(asca_ctx* ctx, const Args& a) {
     if (grid <= 0) return ASCA_OK;
     if (grid <= n_sm) return launch_shape<128, true>(ctx, a, grid);
     return launch_shape<128, false>(ctx, a, std::min<int64_t>(grid, 2 * n_sm));
+}
+
+static bool pair_wanted(asca_ctx* ctx, const Args& a) {
+    const int n_sm = ctx->sm_count > 0 ? ctx->sm_count : 148;
+    const int64_t pairs = tile_bound(a, 256, 256);
+    static const bool pair_rows = [] { const char* e = getenv("ASCA_GEMM_PAIR"); return e && e[0] == '2'; }();
+    const bool pair_shape = a.group_dim == GROUP_M ? (pair_rows && a.total_rows >= 512 * (int64_t)a.n_groups) : a.M >= 256;
+    return pair_enabled() && pair_shape && a.N >= 256 && pairs >= n_sm / 2;
 }
 
 }  // namespace gemm_tc

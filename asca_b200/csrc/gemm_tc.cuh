@@ -5,7 +5,10 @@
 
 namespace gemm_tc {
 
-enum { EPI_NONE = 0, EPI_SILU = 1, EPI_SILU_BWD = 2 };
+// EPI_QKV: the product is the qkv projection of a Delta block (N = 3 d, head dim 128): instead of C, the epilogue writes
+// q and k L2-normalised per head (z / max(|z|, 1e-8), rust/src/delta.rs:146-165) and v, all as bf16 (rows x d each), and
+// the norms of q and k (rows x H, f32). Bias is added first. CTA-pair shape only; see qkv_fusable().
+enum { EPI_NONE = 0, EPI_SILU = 1, EPI_SILU_BWD = 2, EPI_QKV = 3 };
 enum { GROUP_NONE = 0, GROUP_M = 1, GROUP_K = 2 };
 
 struct Args {
@@ -37,8 +40,14 @@ struct Args {
     int c2_only;              // row-tiled kernel, EPI_NONE, no accumulate: the result is wanted as bf16 only (C is not written)
     int c2_mapped;            // few-row kernel only: C2's rows go through c_idx like C's
     int b_packed;             // few-row kernel only: B is a buffer made by skinny_pack (b_rows = its rows of 64)
+    __nv_bfloat16 *qkv_q, *qkv_k, *qkv_v;   // EPI_QKV outputs (rows x qkv_d, bf16)
+    float *qkv_qn, *qkv_kn;                 // EPI_QKV: norms (rows x qkv_d / 128)
+    int qkv_d;
     int b_early;              // few-row kernel only: B and the group offsets were written before the PREVIOUS kernel on
-                              // the stream started, so under programmatic dependent launch they may be read while it runs
+                              // the stream started, so under programmatic dependent launch they may be read while it runs.
+                              // Rule for every call site that sets it: whatever the kernel reads before its wait (B, the
+                              // offsets) must have been written before the nearest preceding kernel on the stream that
+                              // waits before it triggers its dependents -- never by the kernel directly ahead.
 };
 
 // True when the tensor-core kernel can take this problem (alignment and divisibility rules of
@@ -46,6 +55,9 @@ struct Args {
 bool supported(const Args& a);
 // Enqueues the kernel on ctx->stream. Returns ASCA_OK or an error code.
 int launch(asca_ctx* ctx, const Args& a);
+// True when launch() would run this dense product on CTA pairs AND its shape suits the fused qkv epilogue (EPI_QKV):
+// whole 256-row tiles, N = 3 d with d a multiple of 256, bias present and 16-byte aligned.
+bool qkv_fusable(asca_ctx* ctx, const Args& a);
 // Few rows (per expert): the weight-streaming kernel of gemm_skinny.cu; launch() routes to it by itself.
 bool skinny_wanted(const Args& a);
 int launch_skinny(asca_ctx* ctx, const Args& a);

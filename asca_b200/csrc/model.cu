@@ -283,6 +283,17 @@ __global__ void __launch_bounds__(256) argmax_kernel(const float* __restrict__ l
     if (lane == 0) out[t] = (uint32_t)bi;
 }
 
+// alpha, beta = sigmoid of the gate logits (rust/src/delta.rs:167-179): logits (N, 2H), one thread per (row, head).
+__global__ void __launch_bounds__(256) gate_sigmoid_kernel(const float* __restrict__ gate, int64_t units, int H,
+                                                           float* __restrict__ alpha, float* __restrict__ beta) {
+    for (int64_t u = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; u < units; u += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = u / H;
+        const int h = (int)(u % H);
+        alpha[u] = 1.0f / (1.0f + expf(-gate[r * 2 * H + h]));
+        beta[u] = 1.0f / (1.0f + expf(-gate[r * 2 * H + H + h]));
+    }
+}
+
 struct Bufs {   // device buffers from the context cache, released together
     asca_ctx* ctx;
     std::vector<void*> p;
@@ -585,9 +596,23 @@ static int forward_backward_bf16(asca_ctx* ctx, asca_model* m, const uint32_t* i
         ASCA_REQUIRE(ctx, a.x_in && a.q && a.k && a.v && a.o && a.xn && a.hid_p && a.qn && a.kn && a.al && a.be && a.ckpt &&
                               a.x_mid && a.pre_p, "model_forward_backward: out of memory");
         if (li == 0) ASCA_TRY(asca_cast_bf16(ctx, x, a.x_in, N * d));   // later blocks: written with the residual add below
-        ASCA_TRY(asca_gemm(ctx, ASCA_NN, N, 3 * d, d, a.x_in, d, W + w16.w_qkv, 3 * d, qkv, 3 * d, P + w.b_qkv, 0, BF));
+        // qkv projection: where the CTA-pair product can take it, its epilogue adds the bias, L2-normalises q and k per
+        // head and writes q, k, v as bf16 with the norms (the f32 qkv matrix and the prologue pass over it disappear)
+        gemm_tc::Args tq{};
+        tq.mode = ASCA_NN; tq.A = a.x_in; tq.lda = d; tq.a_rows = N; tq.a_cols = d;
+        tq.B = W + w16.w_qkv; tq.ldb = 3 * d; tq.b_rows = d; tq.b_cols = 3 * d;
+        tq.C = qkv; tq.ldc = 3 * d; tq.M = (int)N; tq.N = (int)(3 * d); tq.K = (int)d;
+        tq.bias = P + w.b_qkv; tq.group_dim = gemm_tc::GROUP_NONE; tq.epi = gemm_tc::EPI_QKV;
+        tq.qkv_q = a.q; tq.qkv_k = a.k; tq.qkv_v = a.v; tq.qkv_qn = a.qn; tq.qkv_kn = a.kn; tq.qkv_d = (int)d;
         ASCA_TRY(asca_gemm(ctx, ASCA_NN, N, 2 * H, d, a.x_in, d, W + w16.w_gate, 2 * H, gate, 2 * H, P + w.b_gate, 0, BF));
-        ASCA_TRY(asca_delta_prep_bf16(ctx, qkv, gate, N, H, dh, a.q, a.k, a.v, a.qn, a.kn, a.al, a.be));
+        if (dh == 128 && asca_tc_enabled() && gemm_tc::qkv_fusable(ctx, tq)) {
+            ASCA_TRY(gemm_tc::launch(ctx, tq));
+            gate_sigmoid_kernel<<<(unsigned)std::min<int64_t>(ceil_div64(N * H, 256), 148 * 8), 256, 0, ctx->stream>>>(gate, N * H, (int)H, a.al, a.be);
+            ASCA_CHECK_LAUNCH(ctx);
+        } else {
+            ASCA_TRY(asca_gemm(ctx, ASCA_NN, N, 3 * d, d, a.x_in, d, W + w16.w_qkv, 3 * d, qkv, 3 * d, P + w.b_qkv, 0, BF));
+            ASCA_TRY(asca_delta_prep_bf16(ctx, qkv, gate, N, H, dh, a.q, a.k, a.v, a.qn, a.kn, a.al, a.be));
+        }
         ASCA_TRY(asca_delta_fwd(ctx, a.q, a.k, a.v, a.al, a.be, B, T, H, dh, CH, BF, a.o, nullptr, nullptr, a.ckpt));
         ASCA_TRY(asca_gemm(ctx, ASCA_NN, N, d, d, a.o, d, W + w16.w_o, d, y, d, P + w.b_o, 0, BF));
         ASCA_TRY(asca_residual_rmsnorm_bf16(ctx, x, y, a.x_mid, a.xn, N, d, 1e-6f));

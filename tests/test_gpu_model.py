@@ -357,3 +357,33 @@ def test_chunked_prefill_equals_stepping(orc, gpu, cfg, mode, tol):
     for s in range(ns):
         assert rel_err(lg4[s], ref.step(int(tok[s]), ref_states[s])[0]) < tol
     dev.free()
+
+
+def test_bf16_train_step_with_the_fused_qkv_epilogue(orc, gpu):
+    """8192 tokens at d 256 / head dim 128: large enough for the CTA-pair products, so the qkv projection's epilogue
+    normalises q and k and writes q, k, v as bf16 itself (no f32 qkv matrix, no prologue pass). Loss, logits and every
+    gradient against the f32 oracle on the same weights and tokens."""
+    import asca_b200
+
+    cfg = (256, 256, 2, 1, 4, 256)
+    ref = orc.Model(*cfg)
+    ref.init_reference(orc.Rng(51))
+    dev = asca_b200.Model(gpu, *cfg)
+    dev.set_params(ref.params)
+    dev.set_compute(asca_b200.BF16)
+    B, T = 2, 4096
+    ids = np.random.default_rng(52).integers(0, 256, B * T, dtype=np.uint32)
+    tg = np.roll(ids, -1).astype(np.uint32)
+    loss_ref, g_ref, logits_ref = ref.forward_backward(ids, tg, B, want_logits=True)
+    dev.zero_grads()
+    loss, logits = dev.forward_backward(ids, tg, B, want_logits=True)
+    _, g = dev.get()
+    dev.free()
+    assert abs(loss - loss_ref) / abs(loss_ref) < 2e-2
+    assert rel_err(logits, logits_ref) < 2e-2
+    for name in ref.names:
+        a, b = ref.tensor(name, g), ref.tensor(name, g_ref)
+        if np.abs(b).max() == 0:
+            assert np.abs(a).max() == 0, name
+        else:
+            assert rel_err(a, b) < _bf16_grad_tol(b), name

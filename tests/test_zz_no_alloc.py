@@ -30,7 +30,7 @@ def _dispatch(gpu, fn, ids, e):
     return perm[:n].cpu().numpy(), off.cpu().numpy(), route[:n].cpu().numpy()
 
 
-def test_noalloc_dispatch_matches_allocating_entry_point_twice_in_a_row(gpu):
+def test_noalloc_dispatch_matches_allocating_entry_point_twice_in_a_row(gpu, orc):
     rs = np.random.RandomState(123)
     # two different problems back to back; the second is smaller, so stale entries of the first
     # stay in the shared scratch beyond what the second call uses
@@ -41,6 +41,8 @@ def test_noalloc_dispatch_matches_allocating_entry_point_twice_in_a_row(gpu):
         for a, b in zip(got, want):
             assert np.array_equal(a, b)
         assert sorted(got[0].tolist()) == list(range(n))  # a permutation of all tokens
+        for a, b in zip(got, orc.moe_dispatch(ids, e)):   # and the CPU oracle's buckets, directly
+            assert np.array_equal(a, b)
 
 
 def test_noalloc_dispatch_rejects_sizes_beyond_its_fixed_scratch(gpu):
