@@ -43,15 +43,17 @@ constexpr int A_BYTES = BM * BK * 2;
 // loads its own 128 rows of A and its own 128 of the tile's 256 B columns (32 KiB per k-tile for 4.2 MFLOP on this SM
 // against 48 KiB for the 128 x 256 tile and 32 KiB per 2.1 MFLOP for the 128 x 128 one): shared-memory traffic per
 // FLOP, which is what bounds the single-CTA shapes, halves. 6-stage ring, all 512 TMEM columns, one CTA per SM.
-template <int BN, bool DEEP = false, bool PAIR = false> struct Shape {
+template <int BN, bool DEEP = false, bool PAIR = false, bool EW8 = false> struct Shape {
     static constexpr int STAGES = PAIR ? 6 : BN == 128 ? (DEEP ? 6 : 3) : 4;
     static constexpr int B_BYTES = (PAIR ? BN / 2 : BN) * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int TMEM_COLS = 2 * BN;      // two accumulator buffers
     static constexpr int CTAS_PER_SM = (BN == 128 && !DEEP) ? 2 : 1;
-    // epilogue warps: one per TMEM lane quarter; the pair shape has one CTA per SM and 256 columns per row to move, so
-    // two warps share each quarter and split the columns
-    static constexpr int EPI_WARPS = PAIR ? 8 : 4;
+    // epilogue warps: one per TMEM lane quarter. EW8 (pair shape): two warps share each quarter and split the 256 columns
+    // -- for the row-grouped expert products, whose epilogues (activation, two outputs, row scatter) would otherwise
+    // outlast the main loop (837 against 603 TFLOP/s inside the training step), and for the fused qkv epilogue (a warp's
+    // 128 columns are one head). Plain dense and k-grouped products are faster with four (1181 / 878 against 1056 / 781).
+    static constexpr int EPI_WARPS = (PAIR && EW8) ? 8 : 4;
     static constexpr int THREADS = 64 + 32 * EPI_WARPS;
     static constexpr size_t SMEM_FIXED = (size_t)STAGES * STAGE_BYTES + EPI_WARPS * 2048 /*epilogue staging*/ + 1024 /*alignment slack*/ +
                                          256 /*barriers*/;   // + (groups + 2) * 4 for the tile table
@@ -89,12 +91,12 @@ __device__ __forceinline__ float silu_grad_f(float p) {
     return sg * (1.0f + p * (1.0f - sg));
 }
 
-template <int MODE, int BN, bool DEEP, bool PAIR>
-__global__ void __launch_bounds__(Shape<BN, DEEP, PAIR>::THREADS, Shape<BN, DEEP, PAIR>::CTAS_PER_SM) gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA,
+template <int MODE, int BN, bool DEEP, bool PAIR, bool EW8>
+__global__ void __launch_bounds__(Shape<BN, DEEP, PAIR, EW8>::THREADS, Shape<BN, DEEP, PAIR, EW8>::CTAS_PER_SM) gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA,
                                                              const __grid_constant__ CUtensorMap mapB, const KP p) {
     constexpr bool A_MN = (MODE == ASCA_TN);   // A operand MN-major
     constexpr bool B_MN = (MODE != ASCA_NT);   // B operand MN-major
-    using SH = Shape<BN, DEEP, PAIR>;
+    using SH = Shape<BN, DEEP, PAIR, EW8>;
     constexpr int STAGES = SH::STAGES, STAGE_BYTES = SH::STAGE_BYTES, TMEM_COLS = SH::TMEM_COLS;
     constexpr int TM = PAIR ? 2 * BM : BM;       // rows of an output tile (both CTAs of a pair)
     constexpr int BNL = PAIR ? BN / 2 : BN;      // B columns this CTA loads per tile
@@ -374,7 +376,7 @@ __global__ void __launch_bounds__(Shape<BN, DEEP, PAIR>::THREADS, Shape<BN, DEEP
             const int rows_here = x.M - (x.m0 + q * 32);   // live rows of this warp's quarter (may be <= 0 or > 32)
             // the common case gets straight-line code: full tile, plain f32 output (bias and accumulate allowed)
             // fused qkv epilogue (pair shape, whole tiles: the launcher checks): this warp's 128 columns are one head of q, k or v
-            const bool qkv = PAIR && p.epi == EPI_QKV;
+            const bool qkv = PAIR && EW8 && p.epi == EPI_QKV;
             float qkv_scale = 1.0f;                 // 1 / max(|z|, 1e-8) of this lane's row (q, k), 1 for v
             __nv_bfloat16* c2p = p.C2;
             int64_t ldc2 = p.ldc2;
@@ -625,7 +627,7 @@ bool supported(const Args& a) {
     return true;
 }
 
-template <int BN, bool DEEP, bool PAIR = false>
+template <int BN, bool DEEP, bool PAIR = false, bool EW8 = false>
 static int launch_shape(asca_ctx* ctx, const Args& a, int64_t grid) {
     CUtensorMap mapA, mapB;
     bool ok;
@@ -643,7 +645,7 @@ static int launch_shape(asca_ctx* ctx, const Args& a, int64_t grid) {
     p.epi = a.epi; p.aux = a.aux; p.ldaux = a.ldaux; p.C2 = a.C2; p.ldc2 = a.ldc2; p.c2_only = a.c2_only;
     p.qkv_q = a.qkv_q; p.qkv_k = a.qkv_k; p.qkv_v = a.qkv_v; p.qkv_qn = a.qkv_qn; p.qkv_kn = a.qkv_kn; p.qkv_d = a.qkv_d;
     p.err_word = ctx->err_word;
-    using SH = Shape<BN, DEEP, PAIR>;
+    using SH = Shape<BN, DEEP, PAIR, EW8>;
     const size_t smem = SH::SMEM_FIXED + (size_t)((a.group_dim == GROUP_NONE ? 1 : a.n_groups) + 2) * 4;
     auto go = [&](auto kern) -> cudaError_t {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(SH::SMEM_FIXED + (MAX_GROUPS + 2) * 4));
@@ -666,8 +668,8 @@ static int launch_shape(asca_ctx* ctx, const Args& a, int64_t grid) {
         cfg.numAttrs = ctx->pdl ? 2 : 1;
         return cudaLaunchKernelEx(&cfg, kern, mapA, mapB, p);
     };
-    cudaError_t e = a.mode == ASCA_NN ? go(gemm_tc_kernel<ASCA_NN, BN, DEEP, PAIR>)
-                    : a.mode == ASCA_TN ? go(gemm_tc_kernel<ASCA_TN, BN, DEEP, PAIR>) : go(gemm_tc_kernel<ASCA_NT, BN, DEEP, PAIR>);
+    cudaError_t e = a.mode == ASCA_NN ? go(gemm_tc_kernel<ASCA_NN, BN, DEEP, PAIR, EW8>)
+                    : a.mode == ASCA_TN ? go(gemm_tc_kernel<ASCA_TN, BN, DEEP, PAIR, EW8>) : go(gemm_tc_kernel<ASCA_NT, BN, DEEP, PAIR, EW8>);
     ASCA_CUDA(ctx, e);
     ctx->launches++;
     return ASCA_OK;
@@ -715,11 +717,16 @@ int launch(asca_ctx* ctx, const Args& a) {
     // tile and the single stream per SM cost more than the wider instruction gains).
     // CTA pairs on 256 x 256 tiles: dense and expert-grouped products with at least one tile per pair of SMs
     const int64_t pairs = tile_bound(a, 256, 256);
-    // (row-grouped products are left on 128-row tiles unless ASCA_GEMM_PAIR=2: measured slower on pairs, 603 against 801
-    // TFLOP/s inside the training step -- ragged 256-row tiles and an epilogue with activation and two outputs)
-    if (pair_wanted(ctx, a)) return launch_shape<256, false, true>(ctx, a, 2 * std::min<int64_t>(pairs, n_sm / 2));
     const int64_t wide = tile_bound(a, 256);
-    if (a.group_dim == GROUP_NONE && a.K >= 4096 && a.N >= 256 && wide >= 2 * n_sm)
+    const bool wide_ok = a.group_dim == GROUP_NONE && a.K >= 4096 && a.N >= 256 && wide >= 2 * n_sm;
+    // measured at 32768 x 2048 x 6144: A B^T with a long k runs 1389 TFLOP/s on 128 x 256 single-CTA tiles against 1320 on
+    // pairs (both operands K-major: the widest TMA boxes); every other dense form is faster on pairs
+    if (pair_wanted(ctx, a) && !(wide_ok && a.mode == ASCA_NT && a.epi != EPI_QKV)) {
+        const int64_t g2 = 2 * std::min<int64_t>(pairs, n_sm / 2);
+        if (a.group_dim == GROUP_M || a.epi == EPI_QKV) return launch_shape<256, false, true, true>(ctx, a, g2);
+        return launch_shape<256, false, true, false>(ctx, a, g2);
+    }
+    if (wide_ok)
         return launch_shape<256, false>(ctx, a, std::min<int64_t>(wide, n_sm));
     const int64_t grid = tile_bound(a, 128);
     if (grid <= 0) return ASCA_OK;
@@ -730,7 +737,7 @@ int launch(asca_ctx* ctx, const Args& a) {
 static bool pair_wanted(asca_ctx* ctx, const Args& a) {
     const int n_sm = ctx->sm_count > 0 ? ctx->sm_count : 148;
     const int64_t pairs = tile_bound(a, 256, 256);
-    static const bool pair_rows = [] { const char* e = getenv("ASCA_GEMM_PAIR"); return e && e[0] == '2'; }();
+    static const bool pair_rows = [] { const char* e = getenv("ASCA_GEMM_PAIR"); return !(e && e[0] == '1'); }();
     const bool pair_shape = a.group_dim == GROUP_M ? (pair_rows && a.total_rows >= 512 * (int64_t)a.n_groups) : a.M >= 256;
     return pair_enabled() && pair_shape && a.N >= 256 && pairs >= n_sm / 2;
 }

@@ -605,7 +605,7 @@ static int forward_backward_bf16(asca_ctx* ctx, asca_model* m, const uint32_t* i
         tq.bias = P + w.b_qkv; tq.group_dim = gemm_tc::GROUP_NONE; tq.epi = gemm_tc::EPI_QKV;
         tq.qkv_q = a.q; tq.qkv_k = a.k; tq.qkv_v = a.v; tq.qkv_qn = a.qn; tq.qkv_kn = a.kn; tq.qkv_d = (int)d;
         ASCA_TRY(asca_gemm(ctx, ASCA_NN, N, 2 * H, d, a.x_in, d, W + w16.w_gate, 2 * H, gate, 2 * H, P + w.b_gate, 0, BF));
-        if (dh == 128 && asca_tc_enabled() && gemm_tc::qkv_fusable(ctx, tq)) {
+        if (m->fused_qkv && dh == 128 && asca_tc_enabled() && gemm_tc::qkv_fusable(ctx, tq)) {
             ASCA_TRY(gemm_tc::launch(ctx, tq));
             gate_sigmoid_kernel<<<(unsigned)std::min<int64_t>(ceil_div64(N * H, 256), 148 * 8), 256, 0, ctx->stream>>>(gate, N * H, (int)H, a.al, a.be);
             ASCA_CHECK_LAUNCH(ctx);
@@ -890,6 +890,12 @@ int asca_model_set_compute(asca_ctx* ctx, asca_model* m, int dtype) {
     if (!ctx || !m) return ASCA_ERR_ARG;
     ASCA_REQUIRE(ctx, dtype == ASCA_F32 || dtype == ASCA_BF16, "model_set_compute: unknown dtype %d", dtype);
     m->compute = dtype;
+    return ASCA_OK;
+}
+
+int asca_model_set_fused_qkv(asca_model* m, int on) {
+    if (!m) return ASCA_ERR_ARG;
+    m->fused_qkv = on != 0;
     return ASCA_OK;
 }
 

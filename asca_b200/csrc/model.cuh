@@ -42,6 +42,9 @@ struct asca_model {
     // exchange of that range can be queued behind them while the rest of the backward is still running
     asca_grad_ready_fn grad_hook = nullptr;
     void* grad_hook_user = nullptr;
+    // bf16 mode: let the qkv projection's epilogue normalise q, k and write q, k, v as bf16 where the product runs on
+    // CTA pairs (asca_model_set_fused_qkv)
+    bool fused_qkv = true;
     // data parallelism (dp.cu): the communicator attached to this model and what is in flight on its side stream
     asca_dp* dp = nullptr;
     // set by a sharded optimizer step: the f32 master weights and moments of the other ranks' chunks are not

@@ -390,6 +390,12 @@ int asca_model_set_compute(asca_ctx* ctx, asca_model* m, int dtype);
  * the block's projections; a last call covers embedding + head. Together they cover the buffer exactly once.
  * The library's own exchange (asca_model_dp_attach below) is driven from the same points; the hook is for callers
  * that bring their own collective. NULL removes the hook. */
+/* bf16 compute mode, head dim 128: with on != 0 (the default) the qkv projection's own epilogue adds the bias, L2-normalises q and k
+ * per head and writes q, k, v as bf16 (with the norms) wherever that product runs on CTA pairs (whole 256-row tiles,
+ * d a multiple of 256); the f32 qkv matrix and the separate prologue pass then do not exist. Same results to bf16
+ * rounding (the scale is a multiply by 1/norm where the prologue divides). Elsewhere, and with on = 0, the product
+ * writes f32 qkv and asca_delta_prep_bf16 follows. No counterpart in the reference. */
+int asca_model_set_fused_qkv(asca_model* m, int on);
 /* Gradient accumulation over k micro-batches: with scale = 1/k every backward adds its share of the
  * mean over all k micro-batches (the loss returned stays the mean over the micro-batch's own tokens). */
 int asca_model_set_grad_scale(asca_model* m, float scale);
