@@ -477,8 +477,12 @@ def run_decode(hs: Harness, args):
     cur = {"ids": nxt}
     chunk = 64
 
+    fed = []      # the ids every timed step consumed (its expert routing decides which weights the step must read)
+
     def greedy_chunk():
-        cur["ids"] = model.decode_greedy(state, cur["ids"], chunk)[-1]
+        toks = model.decode_greedy(state, cur["ids"], chunk)
+        fed.append(np.concatenate([cur["ids"][None, :], toks[:-1]], axis=0))
+        cur["ids"] = toks[-1]
 
     n_chunks = c["tokens"] // chunk
     dev_ms, wall_ms, clocks, launches = hs.timed(greedy_chunk, n_chunks, 3)
@@ -488,7 +492,16 @@ def run_decode(hs: Harness, args):
     if hs.rank == 0:
         pk = hs.peaks
         state_bytes = 2 * L * H * dh * dh * 4 * ns
-        weight_bytes = (L * (d * 3 * d + d * 2 * H + d * d + 2 * E * d * F) + d * V) * 2
+        # weights a step must read: the dense ones, and W1 / W2 of the experts its tokens route to
+        # (hash_route, rust/src/model.rs:69-77) -- counted from the ids the timed steps actually consumed
+        ids_fed = np.concatenate(fed[-n_chunks:], axis=0).astype(np.uint64)
+        hsh = (ids_fed * 0x9E3779B1) & 0xFFFFFFFF
+        hsh ^= hsh >> 15
+        hsh = (hsh * 0x85EBCA6B) & 0xFFFFFFFF
+        hsh ^= hsh >> 13
+        experts_hit = float(np.mean([np.unique(r).size for r in (hsh % E)]))
+        weight_bytes_all = (L * (d * 3 * d + d * 2 * H + d * d + 2 * E * d * F) + d * V) * 2
+        weight_bytes = int((L * (d * 3 * d + d * 2 * H + d * d + 2 * experts_hit * d * F) + d * V) * 2)
         step_bytes = state_bytes + weight_bytes
         gbs = step_bytes / (ms_step * 1e-3) / 1e9
         total_k = sum(t for _, t, _ in table.values()) or 1.0
@@ -508,9 +521,11 @@ def run_decode(hs: Harness, args):
                        "l2": "a step reads 1.9 GB of weights and 1.2 GB of state: far larger than L2, no flush"},
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm"], "unit": "GB/s", "frac": gbs / pk["hbm"],
                          "peak_source": pk["source"], "algorithmic_bytes": step_bytes, "state_bytes": state_bytes,
-                         "weight_bytes": weight_bytes, "traffic": None,
+                         "weight_bytes": weight_bytes, "experts_hit_per_step": experts_hit, "weight_bytes_if_all_experts_hit": weight_bytes_all,
+                         "frac_if_all_experts_hit": (state_bytes + weight_bytes_all) / (ms_step * 1e-3) / 1e9 / pk["hbm"], "traffic": None,
                          "note": "per GPU and step: recurrent state read + written once (2 L H dh^2 4 B per stream) + every bf16 weight "
-                                 "byte once (with 256 streams over 16 experts every expert is hit) / CUDA-event time of a step",
+                                 "byte the step needs once (dense weights + W1, W2 of the experts the step's tokens route to, counted from "
+                                 "the ids the timed steps consumed) / CUDA-event time of a step",
                          "dominant_kernel": {"kernel": top, "ms_per_step": t_top / 4,
                                              "achieved": (w_top / (t_top * 1e-3) / 1e9) if w_top else None, "unit": "GB/s",
                                              "note": "from a separate pass with per-launch events, which serialises the chain"}},
