@@ -430,6 +430,10 @@ class Model:
         """F32 (default) or BF16: tensor-core products on a bf16 copy of the weights, f32 everything else."""
         self.gpu._call("asca_model_set_compute", self.gpu._ctx, self._h, C.c_int(dtype))
 
+    def set_fused_head(self, on: bool):
+        """bf16 mode, vocabulary 256: cross-entropy taken in the head product's epilogue where it can be."""
+        self.gpu._call("asca_model_set_fused_head", self._h, C.c_int(1 if on else 0))
+
     def set_fused_qkv(self, on: bool):
         """bf16 mode: q/k normalisation and the bf16 q, k, v written by the qkv product's epilogue where it can."""
         self.gpu._call("asca_model_set_fused_qkv", self._h, C.c_int(1 if on else 0))

@@ -80,6 +80,9 @@ struct KP {
     __nv_bfloat16 *qkv_q, *qkv_k, *qkv_v;
     float *qkv_qn, *qkv_kn;
     int qkv_d;
+    const uint32_t* ce_targets;
+    float* ce_loss;
+    float ce_scale;
     int* err_word;
 };
 
@@ -407,7 +410,37 @@ __global__ void __launch_bounds__(Shape<BN, DEEP, PAIR, EW8>::THREADS, Shape<BN,
                     (sec == 0 ? p.qkv_qn : p.qkv_kn)[((int64_t)x.m0 + q * 32 + lane) * heads + head] = nrm;
                 }
             }
-            const bool fast = qkv || (c_vec && !p.c_idx && (!p.C2 || (p.c2_only && c2_vec)) && p.epi == EPI_NONE && rows_here >= 32 && x.n0 + BN <= p.N &&
+            // fused cross-entropy (pair shape, four epilogue warps: a warp's lanes hold whole rows of 256 logits)
+            const bool ce = PAIR && !EW8 && p.epi == EPI_CE;
+            float ce_max = 0.0f, ce_inv = 0.0f;
+            int ce_t = 0;
+            if (ce) {
+                const int64_t row = (int64_t)x.m0 + q * 32 + lane;
+                ce_t = (int)p.ce_targets[row];
+                float mx = -INFINITY, sum = 0.0f, zt = 0.0f;
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {   // online max / sum of exponentials over the row
+                    uint32_t r[32];
+                    tc::tmem_ld_32x32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
+                    tc::tmem_ld_wait();
+                    float cm = mx;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const float z = __uint_as_float(r[j]);
+                        cm = fmaxf(cm, z);
+                        if (c * 32 + j == ce_t) zt = z;
+                    }
+                    float part = 0.0f;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) part += expf(__uint_as_float(r[j]) - cm);
+                    sum = sum * expf(mx - cm) + part;
+                    mx = cm;
+                }
+                p.ce_loss[row] = (mx + logf(sum)) - zt;
+                ce_max = mx;
+                ce_inv = 1.0f / sum;
+            }
+            const bool fast = qkv || ce || (c_vec && !p.c_idx && (!p.C2 || (p.c2_only && c2_vec)) && p.epi == EPI_NONE && rows_here >= 32 && x.n0 + BN <= p.N &&
                               (!p.bias || (((reinterpret_cast<uintptr_t>(p.bias) & 15) == 0) && (p.bias_gstride & 3) == 0)));
             float* frow = cbase + ((int64_t)x.row_base_m + x.m0 + q * 32 + rsub) * p.ldc + x.n0 + 4 * l4;   // row rsub, this lane's columns
             const float* fbias = (p.bias && !qkv) ? p.bias + (int64_t)x.g * p.bias_gstride + x.n0 + 4 * l4 : nullptr;
@@ -428,6 +461,14 @@ __global__ void __launch_bounds__(Shape<BN, DEEP, PAIR, EW8>::THREADS, Shape<BN,
                 } else {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) r[j] = 0u;
+                }
+                if (ce) {    // dlogits = (softmax - onehot) * scale
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        float pr = expf(__uint_as_float(r[j]) - ce_max) * ce_inv;
+                        if (c * 32 + j == ce_t) pr -= 1.0f;
+                        r[j] = __float_as_uint(pr * p.ce_scale);
+                    }
                 }
                 if (qkv) {   // bias, then the row's scale, on the f32 accumulators (lane = row)
                     const float4* bb = reinterpret_cast<const float4*>(p.bias + x.n0 + c * 32);
@@ -466,7 +507,7 @@ __global__ void __launch_bounds__(Shape<BN, DEEP, PAIR, EW8>::THREADS, Shape<BN,
                             old4[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
                             if (p.accumulate) old4[i] = *reinterpret_cast<const float4*>(frow + (int64_t)(8 * i) * p.ldc + co);
                         }
-                        if (p.c2_only || qkv) {   // bf16 is all the consumer reads
+                        if (p.c2_only || qkv || ce) {   // bf16 is all the consumer reads
                             __nv_bfloat16* hrow = c2p + ((int64_t)x.row_base_m + x.m0 + q * 32 + rsub) * ldc2 + x.n0 + 4 * l4 + co;
 #pragma unroll
                             for (int i = 0; i < 4; ++i) {
@@ -643,6 +684,7 @@ static int launch_shape(asca_ctx* ctx, const Args& a, int64_t grid) {
     p.b_goff_inner = a.b_goff_inner; p.b_goff_outer = a.b_goff_outer;
     p.c_gstride = a.c_gstride; p.bias_gstride = a.bias_gstride;
     p.epi = a.epi; p.aux = a.aux; p.ldaux = a.ldaux; p.C2 = a.C2; p.ldc2 = a.ldc2; p.c2_only = a.c2_only;
+    p.ce_targets = a.ce_targets; p.ce_loss = a.ce_loss; p.ce_scale = a.ce_scale;
     p.qkv_q = a.qkv_q; p.qkv_k = a.qkv_k; p.qkv_v = a.qkv_v; p.qkv_qn = a.qkv_qn; p.qkv_kn = a.qkv_kn; p.qkv_d = a.qkv_d;
     p.err_word = ctx->err_word;
     using SH = Shape<BN, DEEP, PAIR, EW8>;
@@ -701,7 +743,14 @@ bool qkv_fusable(asca_ctx* ctx, const Args& a) {
            ((reinterpret_cast<uintptr_t>(a.qkv_q) | reinterpret_cast<uintptr_t>(a.qkv_k) | reinterpret_cast<uintptr_t>(a.qkv_v)) & 7) == 0;
 }
 
+bool ce_fusable(asca_ctx* ctx, const Args& a) {
+    return supported(a) && !skinny_wanted(a) && a.group_dim == GROUP_NONE && a.mode == ASCA_NN && pair_wanted(ctx, a) && a.N == 256 &&
+           a.M % 256 == 0 && !a.bias && !a.accumulate && !a.c_idx && a.C2 && a.ldc2 == 256 && (reinterpret_cast<uintptr_t>(a.C2) & 7) == 0 &&
+           a.ce_targets && a.ce_loss;
+}
+
 int launch(asca_ctx* ctx, const Args& a) {
+    if (a.epi == EPI_CE && !ce_fusable(ctx, a)) return asca_fail(ctx, ASCA_ERR_UNSUPPORTED, "gemm_tc: this product cannot take the fused cross-entropy epilogue");
     if (a.epi == EPI_QKV && !qkv_fusable(ctx, a)) return asca_fail(ctx, ASCA_ERR_UNSUPPORTED, "gemm_tc: this product cannot take the fused qkv epilogue");
     if (skinny_wanted(a)) return launch_skinny(ctx, a);
     // measurement harnesses: the product's algorithmic FLOPs go with the timed span

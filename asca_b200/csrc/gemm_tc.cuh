@@ -8,7 +8,11 @@ namespace gemm_tc {
 // EPI_QKV: the product is the qkv projection of a Delta block (N = 3 d, head dim 128): instead of C, the epilogue writes
 // q and k L2-normalised per head (z / max(|z|, 1e-8), rust/src/delta.rs:146-165) and v, all as bf16 (rows x d each), and
 // the norms of q and k (rows x H, f32). Bias is added first. CTA-pair shape only; see qkv_fusable().
-enum { EPI_NONE = 0, EPI_SILU = 1, EPI_SILU_BWD = 2, EPI_QKV = 3 };
+// EPI_CE: the product is the output head (N = 256 = the byte vocabulary, one tile wide): the epilogue holds a row's 256
+// logits in TMEM, so it takes the softmax cross-entropy there (cpu_cross_entropy, rust/src/model.rs:821-837): per-row loss
+// log-sum-exp - z[target] to ce_loss (f32, one per row) and dlogits = (softmax - onehot) * ce_scale as bf16 to C2; the
+// logits never reach HBM. CTA-pair shape only; see ce_fusable().
+enum { EPI_NONE = 0, EPI_SILU = 1, EPI_SILU_BWD = 2, EPI_QKV = 3, EPI_CE = 4 };
 enum { GROUP_NONE = 0, GROUP_M = 1, GROUP_K = 2 };
 
 struct Args {
@@ -43,6 +47,9 @@ struct Args {
     __nv_bfloat16 *qkv_q, *qkv_k, *qkv_v;   // EPI_QKV outputs (rows x qkv_d, bf16)
     float *qkv_qn, *qkv_kn;                 // EPI_QKV: norms (rows x qkv_d / 128)
     int qkv_d;
+    const uint32_t* ce_targets;             // EPI_CE: target id per row
+    float* ce_loss;                         // EPI_CE: per-row loss
+    float ce_scale;                         // EPI_CE: multiplies (softmax - onehot): grad scale / rows
     int b_early;              // few-row kernel only: B and the group offsets were written before the PREVIOUS kernel on
                               // the stream started, so under programmatic dependent launch they may be read while it runs.
                               // Rule for every call site that sets it: whatever the kernel reads before its wait (B, the
@@ -58,6 +65,8 @@ int launch(asca_ctx* ctx, const Args& a);
 // True when launch() would run this dense product on CTA pairs AND its shape suits the fused qkv epilogue (EPI_QKV):
 // whole 256-row tiles, N = 3 d with d a multiple of 256, bias present and 16-byte aligned.
 bool qkv_fusable(asca_ctx* ctx, const Args& a);
+// Likewise for the fused cross-entropy epilogue (EPI_CE): N = 256, whole 256-row tiles, no bias, bf16 dlogits in C2.
+bool ce_fusable(asca_ctx* ctx, const Args& a);
 // Few rows (per expert): the weight-streaming kernel of gemm_skinny.cu; launch() routes to it by itself.
 bool skinny_wanted(const Args& a);
 int launch_skinny(asca_ctx* ctx, const Args& a);

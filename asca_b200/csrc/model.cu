@@ -640,11 +640,26 @@ static int forward_backward_bf16(asca_ctx* ctx, asca_model* m, const uint32_t* i
     float* loss_d = bf.f(1);
     ASCA_REQUIRE(ctx, h_final && logits && dlogits && dl16 && loss_d, "model_forward_backward: out of memory");
     ASCA_TRY(asca_residual_rmsnorm_bf16(ctx, x, nullptr, nullptr, h_final, N, d, 1e-6f));
-    ASCA_TRY(asca_gemm(ctx, ASCA_NN, N, V, d, h_final, d, W + m->head16, V, logits, V, nullptr, 0, BF));
-    if (logits_h) ASCA_CUDA(ctx, cudaMemcpyAsync(logits_h, logits, (size_t)N * V * 4, cudaMemcpyDeviceToHost, ctx->stream));
-    ASCA_TRY(cross_entropy_scaled(ctx, logits, tg, N, V, dlogits, loss_d, m->grad_scale));
-    ASCA_CUDA(ctx, cudaMemcpyAsync(loss_h, loss_d, 4, cudaMemcpyDeviceToHost, ctx->stream));
-    ASCA_TRY(asca_cast_bf16(ctx, dlogits, dl16, N * V));
+    // head + cross-entropy: fused into the head product's epilogue where it can be (the logits then never reach HBM)
+    gemm_tc::Args th{};
+    th.mode = ASCA_NN; th.A = h_final; th.lda = d; th.a_rows = N; th.a_cols = d;
+    th.B = W + m->head16; th.ldb = V; th.b_rows = d; th.b_cols = V;
+    th.C = logits; th.ldc = V; th.M = (int)N; th.N = (int)V; th.K = (int)d;
+    th.group_dim = gemm_tc::GROUP_NONE; th.epi = gemm_tc::EPI_CE;
+    th.C2 = dl16; th.ldc2 = V; th.ce_targets = tg; th.ce_loss = dlogits /* N floats of it hold the per-row losses */;
+    th.ce_scale = m->grad_scale / (float)N;
+    if (m->fused_head && !logits_h && asca_tc_enabled() && gemm_tc::ce_fusable(ctx, th)) {
+        ASCA_TRY(gemm_tc::launch(ctx, th));
+        mean_kernel<<<1, 1024, 0, ctx->stream>>>(dlogits, N, 1.0f / (float)N, loss_d);
+        ASCA_CHECK_LAUNCH(ctx);
+        ASCA_CUDA(ctx, cudaMemcpyAsync(loss_h, loss_d, 4, cudaMemcpyDeviceToHost, ctx->stream));
+    } else {
+        ASCA_TRY(asca_gemm(ctx, ASCA_NN, N, V, d, h_final, d, W + m->head16, V, logits, V, nullptr, 0, BF));
+        if (logits_h) ASCA_CUDA(ctx, cudaMemcpyAsync(logits_h, logits, (size_t)N * V * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        ASCA_TRY(cross_entropy_scaled(ctx, logits, tg, N, V, dlogits, loss_d, m->grad_scale));
+        ASCA_CUDA(ctx, cudaMemcpyAsync(loss_h, loss_d, 4, cudaMemcpyDeviceToHost, ctx->stream));
+        ASCA_TRY(asca_cast_bf16(ctx, dlogits, dl16, N * V));
+    }
     ASCA_TRY(asca_gemm(ctx, ASCA_TN, d, V, N, h_final, d, dl16, V, G + m->head, V, nullptr, acc, BF));
     float* dh_ = bf.f(N * d);
     float* dx = bf.f(N * d);
@@ -890,6 +905,12 @@ int asca_model_set_compute(asca_ctx* ctx, asca_model* m, int dtype) {
     if (!ctx || !m) return ASCA_ERR_ARG;
     ASCA_REQUIRE(ctx, dtype == ASCA_F32 || dtype == ASCA_BF16, "model_set_compute: unknown dtype %d", dtype);
     m->compute = dtype;
+    return ASCA_OK;
+}
+
+int asca_model_set_fused_head(asca_model* m, int on) {
+    if (!m) return ASCA_ERR_ARG;
+    m->fused_head = on != 0;
     return ASCA_OK;
 }
 

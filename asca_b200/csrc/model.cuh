@@ -45,6 +45,9 @@ struct asca_model {
     // bf16 mode: let the qkv projection's epilogue normalise q, k and write q, k, v as bf16 where the product runs on
     // CTA pairs (asca_model_set_fused_qkv)
     bool fused_qkv = true;
+    // bf16 mode, vocabulary 256: let the head product's epilogue take the cross-entropy (loss and bf16 dlogits) where
+    // it runs on CTA pairs and the caller does not ask for the logits (asca_model_set_fused_head)
+    bool fused_head = true;
     // data parallelism (dp.cu): the communicator attached to this model and what is in flight on its side stream
     asca_dp* dp = nullptr;
     // set by a sharded optimizer step: the f32 master weights and moments of the other ranks' chunks are not

@@ -396,6 +396,13 @@ int asca_model_set_compute(asca_ctx* ctx, asca_model* m, int dtype);
  * rounding (the scale is a multiply by 1/norm where the prologue divides). Elsewhere, and with on = 0, the product
  * writes f32 qkv and asca_delta_prep_bf16 follows. No counterpart in the reference. */
 int asca_model_set_fused_qkv(asca_model* m, int on);
+/* bf16 compute mode, vocabulary 256: with on != 0 (the default) the output head's product takes the cross-entropy in its own
+ * epilogue wherever it runs on CTA pairs and the caller asks for no logits: a CTA holds each of its rows' 256 logits in
+ * TMEM, so the per-row loss and dlogits = (softmax - onehot) / N (bf16, what the two head gradients read) are produced
+ * there and the (N x 256) logits and f32 dlogits never reach HBM -- the fusion of final norm's successor steps
+ * Model::forward + cpu_cross_entropy (rust/src/model.rs:680-690, :821-837). Elsewhere the product writes the logits and
+ * asca_cross_entropy's kernel follows. */
+int asca_model_set_fused_head(asca_model* m, int on);
 /* Gradient accumulation over k micro-batches: with scale = 1/k every backward adds its share of the
  * mean over all k micro-batches (the loss returned stays the mean over the micro-batch's own tokens). */
 int asca_model_set_grad_scale(asca_model* m, float scale);

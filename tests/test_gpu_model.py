@@ -397,3 +397,35 @@ def test_bf16_train_step_with_the_fused_qkv_epilogue(orc, gpu):
             assert np.abs(a).max() == 0, name
         else:
             assert rel_err(a, b) < _bf16_grad_tol(b), name
+
+
+def test_bf16_train_step_with_the_fused_head_cross_entropy(orc, gpu):
+    """32768 tokens: enough 256-row tiles for the head product to run on CTA pairs, where its epilogue takes the
+    cross-entropy (loss and bf16 dlogits) itself. Against the separate kernels on the same model (same loss to f32
+    rounding, gradients to bf16 rounding of dlogits), and loss + head / embedding gradients against the f32 oracle."""
+    import asca_b200
+
+    cfg = (256, 256, 2, 1, 4, 256)
+    ref = orc.Model(*cfg)
+    ref.init_reference(orc.Rng(61))
+    dev = asca_b200.Model(gpu, *cfg)
+    dev.set_params(ref.params)
+    dev.set_compute(asca_b200.BF16)
+    B, T = 8, 4096
+    ids = np.random.default_rng(62).integers(0, 256, B * T, dtype=np.uint32)
+    tg = np.roll(ids, -1).astype(np.uint32)
+    dev.set_fused_head(False)
+    dev.zero_grads()
+    loss_plain = dev.forward_backward(ids, tg, B)
+    _, g_plain = dev.get()
+    dev.set_fused_head(True)
+    dev.zero_grads()
+    loss = dev.forward_backward(ids, tg, B)
+    _, g = dev.get()
+    dev.free()
+    assert abs(loss - loss_plain) / abs(loss_plain) < 1e-5
+    assert rel_err(g, g_plain) < 1e-2 and not np.array_equal(g, g_plain)
+    loss_ref, g_ref = ref.forward_backward(ids, tg, B)
+    assert abs(loss - loss_ref) / abs(loss_ref) < 2e-2
+    for name in ("head", "embed", "l0.w_o", "l0.w2"):
+        assert rel_err(ref.tensor(name, g), ref.tensor(name, g_ref)) < 2e-2, name
