@@ -222,6 +222,35 @@ __global__ void __launch_bounds__(256) cast_cols_kernel(const float* __restrict_
         *reinterpret_cast<uint2*>(dst + r * ld_dst + 4 * c) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
     }
 }
+// The same cast with the column sums of src taken in the same pass (a bias gradient): CTA (x, y) owns 128 columns (a
+// lane 4 consecutive ones) of row slab y, its 8 warps stride the slab's rows, fixed-order tree -> part[y][c]; the slabs
+// are added in order by colsum_finish_kernel. cols % 4 == 0.
+__global__ void __launch_bounds__(256) cast_colsum_kernel(const float* __restrict__ src, int cols, int64_t rows, int64_t rows_per_slab,
+                                                          __nv_bfloat16* __restrict__ dst, int64_t ld_dst, float* __restrict__ part) {
+    __shared__ float4 red[8][32];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int c = (blockIdx.x * 32 + lane) * 4;
+    const int64_t lo = blockIdx.y * rows_per_slab, hi = lo + rows_per_slab < rows ? lo + rows_per_slab : rows;
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (c < cols) {
+        for (int64_t r = lo + w; r < hi; r += 8) {
+            const float4 v = *reinterpret_cast<const float4*>(src + r * cols + c);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            const __nv_bfloat162 l2 = __floats2bfloat162_rn(v.x, v.y), h2 = __floats2bfloat162_rn(v.z, v.w);
+            *reinterpret_cast<uint2*>(dst + r * ld_dst + c) = make_uint2(*reinterpret_cast<const uint32_t*>(&l2), *reinterpret_cast<const uint32_t*>(&h2));
+        }
+    }
+    red[w][lane] = acc;
+    __syncthreads();
+    if (w == 0 && c < cols) {
+        float4 t = red[0][lane];
+#pragma unroll
+        for (int i = 1; i < 8; ++i) {
+            t.x += red[i][lane].x; t.y += red[i][lane].y; t.z += red[i][lane].z; t.w += red[i][lane].w;
+        }
+        *reinterpret_cast<float4*>(part + (int64_t)blockIdx.y * cols + c) = t;
+    }
+}
 // inv[perm[i]] = i
 __global__ void __launch_bounds__(256) invert_perm_kernel(const int32_t* __restrict__ perm, int32_t* __restrict__ inv, int64_t n) {
     const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
@@ -721,18 +750,35 @@ static int forward_backward_bf16(asca_ctx* ctx, asca_model* m, const uint32_t* i
         ASCA_TRY(asca_gemm(ctx, ASCA_TN, d, d, N, a.o, d, dx16, d, G + w.w_o, d, nullptr, acc, BF));
         ASCA_TRY(asca_colsum(ctx, dx, d, N, d, G + w.b_o, acc));
         ASCA_TRY(asca_delta_bwd(ctx, a.q, a.k, a.v, a.al, a.be, a.qn, a.kn, do16, a.ckpt, B, T, H, dh, CH, BF, d_qkv, d_gate));
+        bool bqkv_done = false;   // the d_qkv bias gradient was taken in the cast pass
         if (cat) {
-            cast_cols_kernel<<<add_grid, 256, 0, ctx->stream>>>(d_qkv, (int)(3 * d / 4), N * 3 * d / 4, dqkv16, ldq);
+            {   // bf16 copy of d_qkv and its column sums (the b_qkv gradient) in one pass over the 3 d wide f32 matrix
+                const int64_t cols = 3 * d, col_blocks = ceil_div64(cols, 128);
+                int64_t n_slabs = std::max<int64_t>(1, std::min<int64_t>(ceil_div64(148 * 8, col_blocks), ceil_div64(N, 256)));
+                const int64_t rps = ceil_div64(N, n_slabs);
+                n_slabs = ceil_div64(N, rps);
+                void* part;
+                ASCA_TRY(asca_malloc(ctx, (size_t)n_slabs * cols * 4 + 256, &part));
+                cast_colsum_kernel<<<dim3((unsigned)col_blocks, (unsigned)n_slabs), 256, 0, ctx->stream>>>(d_qkv, (int)cols, N, rps, dqkv16, ldq,
+                                                                                                         (float*)part);
+                colsum_finish_kernel<<<(unsigned)ceil_div64(cols, 256), 256, 0, ctx->stream>>>((const float*)part, (int)n_slabs, (int)cols,
+                                                                                              G + w.b_qkv, acc);
+                const cudaError_t le = cudaGetLastError();
+                asca_free(ctx, part);
+                ASCA_CUDA(ctx, le);
+                ctx->launches += 2;
+                bqkv_done = true;
+            }
             cast_cols_kernel<<<(unsigned)std::min<int64_t>(ceil_div64(N * 2 * H / 4, 256), 148 * 16), 256, 0, ctx->stream>>>(
                 d_gate, (int)(2 * H / 4), N * 2 * H / 4, dg16, ldq);
-            ctx->launches += 2;
+            ctx->launches += 1;
             ASCA_CUDA(ctx, cudaGetLastError());
         } else {
             ASCA_TRY(asca_cast_bf16(ctx, d_qkv, dqkv16, N * 3 * d));
             ASCA_TRY(asca_cast_bf16(ctx, d_gate, dg16, N * 2 * H));
         }
         ASCA_TRY(asca_gemm(ctx, ASCA_TN, d, 3 * d, N, a.x_in, d, dqkv16, ld_dq, G + w.w_qkv, 3 * d, nullptr, acc, BF));
-        ASCA_TRY(asca_colsum(ctx, d_qkv, 3 * d, N, 3 * d, G + w.b_qkv, acc));
+        if (!bqkv_done) ASCA_TRY(asca_colsum(ctx, d_qkv, 3 * d, N, 3 * d, G + w.b_qkv, acc));
         ASCA_TRY(asca_gemm(ctx, ASCA_TN, d, 2 * H, N, a.x_in, d, dg16, ld_dg, G + w.w_gate, 2 * H, nullptr, acc, BF));
         ASCA_TRY(asca_colsum(ctx, d_gate, 2 * H, N, 2 * H, G + w.b_gate, acc));
         if (cat) {   // dx += [d_qkv | d_gate] [W_qkv | W_gate]^T

@@ -388,7 +388,11 @@ def run_train(hs: Harness, args):
             "loss_first_step": first_loss, "loss_last_step": last["loss"],
             "roofline": {"bound": "tensor", "achieved": tf_per_gpu, "peak": pk["sustained"], "unit": "TFLOP/s",
                          "frac": tf_per_gpu / pk["sustained"], "frac_of_burst": tf_per_gpu / pk["burst"], "peak_source": pk["source"],
-                         "algorithmic_flop_per_token": flop_tok, "traffic": None,
+                         "algorithmic_flop_per_token": flop_tok,
+                         # dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel at the captured case
+                         # (bench.py --case gemm_dense: 32768 x 6144 x 2048, CTA pairs; profiles/): 224 + 765 MB per launch
+                         # against 964 MB algorithmic (A and B once as bf16, C once as f32)
+                         "traffic": 989.0e6, "traffic_algorithmic_bytes": 964.7e6, "traffic_case": "bench.py --case gemm_dense",
                          "note": "whole step per GPU: 6 x GEMM parameters a token touches + 22 dh^2 H per block for the recurrence, "
                                  "/ CUDA-event step time / the sustained cuBLAS bf16 figure (a kernel timed inside a long step); "
                                  "dominant kernel below against the burst figure (timed alone by its own events)",
