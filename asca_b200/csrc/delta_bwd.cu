@@ -97,12 +97,13 @@ __device__ __forceinline__ void cta_gemm(const float* __restrict__ A, int lda, c
                 acc[i][3] = fmaf(av, b.w, acc[i][3]);
             }
         }
-    } else {  // L_MK x L_NK: both contiguous along k
+    } else {  // L_MK x L_NK: both contiguous along k; this thread's columns are tn + THR_N * j, so that the lanes of a
+              // quarter warp read 8 consecutive rows of B (row stride = 4 banks: all 32 banks, no conflict)
 #pragma unroll 2
         for (int k = 0; k < K; k += 4) {
             float4 b[TN];
 #pragma unroll
-            for (int j = 0; j < TN; ++j) b[j] = *reinterpret_cast<const float4*>(B + (n0 + j) * ldb + k);
+            for (int j = 0; j < TN; ++j) b[j] = *reinterpret_cast<const float4*>(B + (tn + THR_N * j) * ldb + k);
 #pragma unroll
             for (int i = 0; i < TM; ++i) {
                 const float4 a = *reinterpret_cast<const float4*>(A + (tm + THR_M * i) * lda + k);
@@ -119,7 +120,7 @@ __device__ __forceinline__ void cta_gemm(const float* __restrict__ A, int lda, c
 #pragma unroll
     for (int i = 0; i < TM; ++i)
 #pragma unroll
-        for (int j = 0; j < TN; ++j) epi(tm + THR_M * i, n0 + j, acc[i][j]);
+        for (int j = 0; j < TN; ++j) epi(tm + THR_M * i, (ALAY == L_MK && BLAY == L_NK) ? tn + THR_N * j : n0 + j, acc[i][j]);
 }
 
 template <typename T>
