@@ -54,6 +54,7 @@ __device__ __forceinline__ void cta_gemm(const float* __restrict__ A, int lda, c
     constexpr int THR_M_MAX = BT / THR_N > 0 ? BT / THR_N : 1;
     constexpr int THR_M = THR_M_MAX < M ? THR_M_MAX : M;
     constexpr int TM = M / THR_M;
+    constexpr bool KM_VEC = ALAY == L_KM && BLAY == L_KN && TM % 4 == 0 && THR_N % 32 == 0;
     static_assert(N % TN == 0 && THR_N <= BT && M % THR_M == 0, "tile shape");
     const int tid = threadIdx.x;
     if (tid >= THR_N * THR_M) return;
@@ -85,16 +86,35 @@ __device__ __forceinline__ void cta_gemm(const float* __restrict__ A, int lda, c
             }
         }
     } else if (ALAY == L_KM && BLAY == L_KN) {
-#pragma unroll 4
-        for (int k = 0; k < K; ++k) {
-            const float4 b = *reinterpret_cast<const float4*>(B + k * ldb + n0);
+        if (KM_VEC) {   // rows tm * TM + i: the lanes of a warp share tm, so A arrives as broadcast float4 loads
+#pragma unroll 2
+            for (int k = 0; k < K; ++k) {
+                const float4 b = *reinterpret_cast<const float4*>(B + k * ldb + n0);
 #pragma unroll
-            for (int i = 0; i < TM; ++i) {
-                const float av = A[k * lda + tm + THR_M * i];
-                acc[i][0] = fmaf(av, b.x, acc[i][0]);
-                acc[i][1] = fmaf(av, b.y, acc[i][1]);
-                acc[i][2] = fmaf(av, b.z, acc[i][2]);
-                acc[i][3] = fmaf(av, b.w, acc[i][3]);
+                for (int i4 = 0; i4 < TM / 4; ++i4) {
+                    const float4 a4 = *reinterpret_cast<const float4*>(A + k * lda + tm * TM + 4 * i4);
+                    const float av[4] = {a4.x, a4.y, a4.z, a4.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        acc[4 * i4 + e][0] = fmaf(av[e], b.x, acc[4 * i4 + e][0]);
+                        acc[4 * i4 + e][1] = fmaf(av[e], b.y, acc[4 * i4 + e][1]);
+                        acc[4 * i4 + e][2] = fmaf(av[e], b.z, acc[4 * i4 + e][2]);
+                        acc[4 * i4 + e][3] = fmaf(av[e], b.w, acc[4 * i4 + e][3]);
+                    }
+                }
+            }
+        } else {
+#pragma unroll 4
+            for (int k = 0; k < K; ++k) {
+                const float4 b = *reinterpret_cast<const float4*>(B + k * ldb + n0);
+#pragma unroll
+                for (int i = 0; i < TM; ++i) {
+                    const float av = A[k * lda + tm + THR_M * i];
+                    acc[i][0] = fmaf(av, b.x, acc[i][0]);
+                    acc[i][1] = fmaf(av, b.y, acc[i][1]);
+                    acc[i][2] = fmaf(av, b.z, acc[i][2]);
+                    acc[i][3] = fmaf(av, b.w, acc[i][3]);
+                }
             }
         }
     } else {  // L_MK x L_NK: both contiguous along k; this thread's columns are tn + THR_N * j, so that the lanes of a
@@ -120,7 +140,8 @@ __device__ __forceinline__ void cta_gemm(const float* __restrict__ A, int lda, c
 #pragma unroll
     for (int i = 0; i < TM; ++i)
 #pragma unroll
-        for (int j = 0; j < TN; ++j) epi(tm + THR_M * i, (ALAY == L_MK && BLAY == L_NK) ? tn + THR_N * j : n0 + j, acc[i][j]);
+        for (int j = 0; j < TN; ++j)
+            epi(KM_VEC ? tm * TM + i : tm + THR_M * i, (ALAY == L_MK && BLAY == L_NK) ? tn + THR_N * j : n0 + j, acc[i][j]);
 }
 
 template <typename T>
@@ -168,6 +189,7 @@ __global__ void __launch_bounds__(BT, 1) delta_bwd_kernel(
     int chunk, float* __restrict__ d_qkv, float* __restrict__ d_gate) {
     using SM = BwdSmem<DH, C>;
     constexpr int LDK = SM::LDK, LDV = SM::LDV, LDC = SM::LDC;
+    static_assert(C <= 32, "the gate scans run in one warp");
     extern __shared__ __align__(16) float smem[];
     float* Ks = smem;
     float* Qs = Ks + C * LDK;
@@ -240,12 +262,14 @@ __global__ void __launch_bounds__(BT, 1) delta_bwd_kernel(
             g_s[tid] = logf(a);
         }
         __syncthreads();
-        if (tid == 0) {
-            float run = 0.0f;
-            for (int t = 0; t < C; ++t) {
-                run += g_s[t];
-                g_s[t] = run;
+        if (warp == 0) {   // inclusive scan of the C (<= 32) log alphas, left to right
+            float gx = lane < C ? g_s[lane] : 0.0f;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const float y = __shfl_up_sync(0xffffffffu, gx, o);
+                if (lane >= o) gx += y;
             }
+            if (lane < C) g_s[lane] = gx;
         }
         __syncthreads();
         if (tid < C) {
@@ -485,15 +509,17 @@ __global__ void __launch_bounds__(BT, 1) delta_bwd_kernel(
             }
             const float sds = block_sum(part, red);  // contains __syncthreads
             // gates: dg_last += sum_t r_kw[t] + gam_last <S0,dS>; reverse cumsum; sigmoid backward
-            if (tid == 0) {
-                float extra = gam_s[C - 1] * sds;
-                for (int t = 0; t < C; ++t) extra += r_kw[t];
-                dg_s[C - 1] += extra;
-                float run = 0.0f;
-                for (int t = C - 1; t >= 0; --t) {
-                    run += dg_s[t];
-                    dg_s[t] = run;  // dlogalpha_t
+            if (warp == 0) {
+                float kw = lane < C ? r_kw[lane] : 0.0f;
+                kw = warp_sum(kw);
+                float gx = lane < C ? dg_s[lane] : 0.0f;
+                if (lane == C - 1) gx += gam_s[C - 1] * sds + kw;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {   // suffix sums: dlogalpha_t = sum_{j >= t} dg_j
+                    const float y = __shfl_down_sync(0xffffffffu, gx, o);
+                    if (lane + o < 32) gx += y;
                 }
+                if (lane < C) dg_s[lane] = gx;
             }
             __syncthreads();
             if (tid < n) {

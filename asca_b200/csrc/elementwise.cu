@@ -157,12 +157,18 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_warp_kernel(const float* __re
     const float4* xr = reinterpret_cast<const float4*>(x + r * (int64_t)cols);
     const float4* dr = reinterpret_cast<const float4*>(dy + r * (int64_t)cols);
     const int n4 = cols >> 2;
-    float4 a[NV], g[NV];
+    const float4* ad = add ? reinterpret_cast<const float4*>(add + r * (int64_t)cols) : nullptr;
+    float4 a[NV], g[NV], e[NV];   // every load of the row is issued before the reductions wait on any
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
         const int c = lane + 32 * i;
         a[i] = c < n4 ? xr[c] : make_float4(0, 0, 0, 0);
         g[i] = c < n4 ? dr[c] : make_float4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = lane + 32 * i;
+        e[i] = ad && c < n4 ? ad[c] : make_float4(0, 0, 0, 0);
     }
     float s2 = 0.0f, sd = 0.0f;
 #pragma unroll
@@ -175,7 +181,6 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_warp_kernel(const float* __re
     const float inv = 1.0f / sqrtf(s2 / (float)cols + eps);
     const float im = inv * ((sd * inv) / (float)cols);
     float4* o = reinterpret_cast<float4*>(dx + r * (int64_t)cols);
-    const float4* ad = add ? reinterpret_cast<const float4*>(add + r * (int64_t)cols) : nullptr;
     uint2* o16 = dx16 ? reinterpret_cast<uint2*>(dx16 + r * (int64_t)cols) : nullptr;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
@@ -183,10 +188,7 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_warp_kernel(const float* __re
         if (c < n4) {
             float4 v = make_float4(inv * (g[i].x - a[i].x * im), inv * (g[i].y - a[i].y * im), inv * (g[i].z - a[i].z * im),
                                    inv * (g[i].w - a[i].w * im));
-            if (ad) {
-                const float4 e = ad[c];
-                v.x += e.x; v.y += e.y; v.z += e.z; v.w += e.w;
-            }
+            v.x += e[i].x; v.y += e[i].y; v.z += e[i].z; v.w += e[i].w;
             o[c] = v;
             if (o16) {
                 const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);

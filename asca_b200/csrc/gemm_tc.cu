@@ -663,7 +663,7 @@ bool supported(const Args& a) {
     if (a.group_dim != GROUP_NONE && a.n_groups > MAX_GROUPS) return false;
     if (a.group_dim == GROUP_K && a.mode != ASCA_TN) return false;
     if (a.group_dim == GROUP_M && a.mode == ASCA_TN) return false;
-    if (a.c2_only && (!a.C2 || a.accumulate || a.epi != EPI_NONE || a.c_idx || skinny_wanted(a))) return false;
+    if (a.c2_only && (!a.C2 || a.accumulate || (a.epi != EPI_NONE && a.epi != EPI_SILU_BWD) || a.c_idx || skinny_wanted(a))) return false;
     if ((a.c2_mapped || a.b_packed) && !skinny_wanted(a)) return false;
     return true;
 }

@@ -41,7 +41,8 @@ struct Args {
     int64_t ldaux;
     __nv_bfloat16* C2;        // EPI_SILU: silu(C); EPI_SILU_BWD: bf16 copy of C; nullable
     int64_t ldc2;
-    int c2_only;              // row-tiled kernel, EPI_NONE, no accumulate: the result is wanted as bf16 only (C is not written)
+    int c2_only;              // row-tiled kernel, EPI_NONE or EPI_SILU_BWD, no accumulate: the result is wanted as bf16 only (C is
+                              // not written and may be null)
     int c2_mapped;            // few-row kernel only: C2's rows go through c_idx like C's
     int b_packed;             // few-row kernel only: B is a buffer made by skinny_pack (b_rows = its rows of 64)
     __nv_bfloat16 *qkv_q, *qkv_k, *qkv_v;   // EPI_QKV outputs (rows x qkv_d, bf16)

@@ -222,34 +222,30 @@ __global__ void __launch_bounds__(256) cast_cols_kernel(const float* __restrict_
         *reinterpret_cast<uint2*>(dst + r * ld_dst + 4 * c) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
     }
 }
-// The same cast with the column sums of src taken in the same pass (a bias gradient): CTA (x, y) owns 128 columns (a
-// lane 4 consecutive ones) of row slab y, its 8 warps stride the slab's rows, fixed-order tree -> part[y][c]; the slabs
-// are added in order by colsum_finish_kernel. cols % 4 == 0.
+// The same cast with the column sums of src taken in the same pass (a bias gradient): CTA (x, y) owns 1024 columns (a
+// thread 4 consecutive ones: every row is read in runs of 4 KiB) of row slab y; a thread adds its slab's rows in order
+// -> part[y][c], and the slabs are added in order by colsum_finish_kernel. cols % 4 == 0.
 __global__ void __launch_bounds__(256) cast_colsum_kernel(const float* __restrict__ src, int cols, int64_t rows, int64_t rows_per_slab,
                                                           __nv_bfloat16* __restrict__ dst, int64_t ld_dst, float* __restrict__ part) {
-    __shared__ float4 red[8][32];
-    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-    const int c = (blockIdx.x * 32 + lane) * 4;
+    const int c = (blockIdx.x * 256 + threadIdx.x) * 4;
+    if (c >= cols) return;
     const int64_t lo = blockIdx.y * rows_per_slab, hi = lo + rows_per_slab < rows ? lo + rows_per_slab : rows;
     float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    if (c < cols) {
-        for (int64_t r = lo + w; r < hi; r += 8) {
-            const float4 v = *reinterpret_cast<const float4*>(src + r * cols + c);
-            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-            const __nv_bfloat162 l2 = __floats2bfloat162_rn(v.x, v.y), h2 = __floats2bfloat162_rn(v.z, v.w);
-            *reinterpret_cast<uint2*>(dst + r * ld_dst + c) = make_uint2(*reinterpret_cast<const uint32_t*>(&l2), *reinterpret_cast<const uint32_t*>(&h2));
-        }
-    }
-    red[w][lane] = acc;
-    __syncthreads();
-    if (w == 0 && c < cols) {
-        float4 t = red[0][lane];
+    const auto put = [&](int64_t r, const float4& v) {
+        const __nv_bfloat162 l2 = __floats2bfloat162_rn(v.x, v.y), h2 = __floats2bfloat162_rn(v.z, v.w);
+        *reinterpret_cast<uint2*>(dst + r * ld_dst + c) = make_uint2(*reinterpret_cast<const uint32_t*>(&l2), *reinterpret_cast<const uint32_t*>(&h2));
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    };
+    int64_t r = lo;
+    for (; r + 4 <= hi; r += 4) {   // four rows in flight per thread
+        float4 v[4];
 #pragma unroll
-        for (int i = 1; i < 8; ++i) {
-            t.x += red[i][lane].x; t.y += red[i][lane].y; t.z += red[i][lane].z; t.w += red[i][lane].w;
-        }
-        *reinterpret_cast<float4*>(part + (int64_t)blockIdx.y * cols + c) = t;
+        for (int i = 0; i < 4; ++i) v[i] = *reinterpret_cast<const float4*>(src + (r + i) * cols + c);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) put(r + i, v[i]);
     }
+    for (; r < hi; ++r) put(r, *reinterpret_cast<const float4*>(src + r * cols + c));
+    *reinterpret_cast<float4*>(part + (int64_t)blockIdx.y * cols + c) = acc;
 }
 // inv[perm[i]] = i
 __global__ void __launch_bounds__(256) invert_perm_kernel(const int32_t* __restrict__ perm, int32_t* __restrict__ inv, int64_t n) {
@@ -753,8 +749,8 @@ static int forward_backward_bf16(asca_ctx* ctx, asca_model* m, const uint32_t* i
         bool bqkv_done = false;   // the d_qkv bias gradient was taken in the cast pass
         if (cat) {
             {   // bf16 copy of d_qkv and its column sums (the b_qkv gradient) in one pass over the 3 d wide f32 matrix
-                const int64_t cols = 3 * d, col_blocks = ceil_div64(cols, 128);
-                int64_t n_slabs = std::max<int64_t>(1, std::min<int64_t>(ceil_div64(148 * 8, col_blocks), ceil_div64(N, 256)));
+                const int64_t cols = 3 * d, col_blocks = ceil_div64(cols, 1024);
+                int64_t n_slabs = std::max<int64_t>(1, std::min<int64_t>(ceil_div64(148 * 8, col_blocks), ceil_div64(N, 64)));
                 const int64_t rps = ceil_div64(N, n_slabs);
                 n_slabs = ceil_div64(N, rps);
                 void* part;

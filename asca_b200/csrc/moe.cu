@@ -41,6 +41,48 @@ __global__ void __launch_bounds__(256) colsum_kernel(const float* __restrict__ s
     }
 }
 
+// The same sums for a bf16 matrix grouped by expert segment: each CTA owns 64 columns (a lane two) of one segment.
+__global__ void __launch_bounds__(256) colsum_bf16_seg_kernel(const __nv_bfloat16* __restrict__ src, int64_t ld,
+                                                              const int32_t* __restrict__ offsets, int cols,
+                                                              float* __restrict__ out, int64_t out_gstride, int accumulate) {
+    __shared__ float2 part[8][32];
+    const int g = blockIdx.y, lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int64_t lo = offsets[g], hi = offsets[g + 1];
+    const int c = blockIdx.x * 64 + 2 * lane;
+    float2 acc = make_float2(0.0f, 0.0f);
+    if (c < cols) {
+        int64_t r = lo + w;
+        for (; r + 24 < hi; r += 32) {   // four rows in flight per thread
+            __nv_bfloat162 v[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) v[i] = *reinterpret_cast<const __nv_bfloat162*>(src + (r + 8 * i) * ld + c);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                acc.x += __low2float(v[i]);
+                acc.y += __high2float(v[i]);
+            }
+        }
+        for (; r < hi; r += 8) {
+            const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(src + r * ld + c);
+            acc.x += __low2float(v);
+            acc.y += __high2float(v);
+        }
+    }
+    part[w][lane] = acc;
+    __syncthreads();
+    if (w == 0 && c < cols) {
+        float2 t = make_float2(0.0f, 0.0f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            t.x += part[i][lane].x;
+            t.y += part[i][lane].y;
+        }
+        float* o = out + (int64_t)g * out_gstride + c;
+        o[0] = accumulate ? o[0] + t.x : t.x;
+        if (c + 1 < cols) o[1] = accumulate ? o[1] + t.y : t.y;
+    }
+}
+
 // Decode step: one CTA per token. rmsnorm -> pre = b1[e] + xn W1[:, e] -> silu -> out = b2 + h W2[e].
 template <typename T>
 __global__ void __launch_bounds__(256) moe_step_kernel(const float* __restrict__ x, const uint32_t* __restrict__ ids,
@@ -152,14 +194,13 @@ int moe_bwd_tc(asca_ctx* ctx, const __nv_bfloat16* xn, const __nv_bfloat16* w1, 
                const int32_t* offsets, int64_t N, int64_t d, int64_t F, int64_t E, float* d_w1, float* d_b1,
                float* d_w2, float* d_b2, float* dxn, int acc) {
     cudaStream_t s = ctx->stream;
-    const size_t b_xp = align256((size_t)N * d * 2), b_dp = align256((size_t)N * F * 4), b_dp16 = align256((size_t)N * F * 2);
+    const size_t b_xp = align256((size_t)N * d * 2), b_dp16 = align256((size_t)N * F * 2);
     void* ws;
-    ASCA_TRY(asca_workspace(ctx, 2 * b_xp + b_dp + b_dp16 + 256, &ws));
+    ASCA_TRY(asca_workspace(ctx, 2 * b_xp + b_dp16 + 256, &ws));
     char* w = (char*)ws;
     __nv_bfloat16* xp = (__nv_bfloat16*)w;
     __nv_bfloat16* dout_p = (__nv_bfloat16*)(w + b_xp);
-    float* dpre_p = (float*)(w + 2 * b_xp);
-    __nv_bfloat16* dpre16 = (__nv_bfloat16*)(w + 2 * b_xp + b_dp);
+    __nv_bfloat16* dpre16 = (__nv_bfloat16*)(w + 2 * b_xp);
     gemm_tc::Args g1{}, g2{}, g3{}, g4{};
     // d_w2[eF+j, c] = sum_r hid_p[r,j] dout_p[r,c]
     g1.mode = ASCA_TN;
@@ -167,11 +208,12 @@ int moe_bwd_tc(asca_ctx* ctx, const __nv_bfloat16* xn, const __nv_bfloat16* w1, 
     g1.B = dout_p; g1.ldb = d; g1.b_rows = N; g1.b_cols = d;
     g1.C = d_w2; g1.ldc = d; g1.c_gstride = F * d; g1.M = (int)F; g1.N = (int)d; g1.accumulate = acc;
     g1.offsets = offsets; g1.n_groups = (int)E; g1.group_dim = gemm_tc::GROUP_K; g1.total_rows = N;
-    // dpre_p[r,j] = (sum_c dout_p[r,c] W2[eF+j,c]) * silu'(pre_p[r,j]), plus a bf16 copy
+    // dpre16[r,j] = (sum_c dout_p[r,c] W2[eF+j,c]) * silu'(pre_p[r,j]), written as bf16 only: the weight-gradient product
+    // below reads bf16, and the bias gradient sums the same rounded values
     g2.mode = ASCA_NT;
     g2.A = dout_p; g2.lda = d; g2.a_rows = N; g2.a_cols = d;
     g2.B = w2; g2.ldb = d; g2.b_rows = E * F; g2.b_cols = d; g2.b_goff_outer = (int)F;
-    g2.C = dpre_p; g2.ldc = F; g2.N = (int)F; g2.K = (int)d;
+    g2.C = nullptr; g2.ldc = F; g2.N = (int)F; g2.K = (int)d; g2.c2_only = 1;
     g2.offsets = offsets; g2.n_groups = (int)E; g2.group_dim = gemm_tc::GROUP_M; g2.total_rows = N;
     g2.epi = gemm_tc::EPI_SILU_BWD; g2.aux = pre_p; g2.ldaux = F; g2.C2 = dpre16; g2.ldc2 = F;
     // d_w1[c, eF+j] = sum_r xp[r,c] dpre16[r,j]
@@ -197,7 +239,7 @@ int moe_bwd_tc(asca_ctx* ctx, const __nv_bfloat16* xn, const __nv_bfloat16* w1, 
     ASCA_TRY(asca_colsum(ctx, dout, d, N, d, d_b2, acc));   // row-sliced, deterministic
     ASCA_TRY(gemm_tc::launch(ctx, g1));
     ASCA_TRY(gemm_tc::launch(ctx, g2));
-    colsum_kernel<<<dim3((unsigned)ceil_div64(F, 32), (unsigned)E), 256, 0, s>>>(dpre_p, F, nullptr, offsets, N, (int)F, d_b1, F, acc);
+    colsum_bf16_seg_kernel<<<dim3((unsigned)ceil_div64(F, 64), (unsigned)E), 256, 0, s>>>(dpre16, F, offsets, (int)F, d_b1, F, acc);
     ASCA_CHECK_LAUNCH(ctx);
     ASCA_TRY(gemm_tc::launch(ctx, g3));
     return gemm_tc::launch(ctx, g4);
