@@ -33,7 +33,7 @@ namespace delta_tc {
 bool available();
 int backward(asca_ctx* ctx, const void* q, const void* k, const void* v, const float* alpha, const float* beta,
              const float* qnorm, const float* knorm, const void* d_o, const float* ckpt, int64_t B, int64_t T, int64_t H,
-             float* d_qkv, float* d_gate);
+             int64_t dh, float* d_qkv, float* d_gate);
 }  // namespace delta_tc
 
 namespace {
@@ -591,8 +591,8 @@ extern "C" int asca_delta_bwd(asca_ctx* ctx, const void* q, const void* k, const
     ASCA_REQUIRE(ctx, (al & 15) == 0, "delta_bwd: q, k, v, d_o, ckpt must be 16-byte aligned");
     if (B == 0 || T == 0) return ASCA_OK;
     // bf16 mode, dh = 128, checkpoints every 64 tokens: reverse chunked scan on the tensor cores
-    if (dtype == ASCA_BF16 && dh == 128 && chunk == 64 && asca_tc_enabled() && delta_tc::available())
-        return delta_tc::backward(ctx, q, k, v, alpha, beta, qnorm, knorm, d_o, ckpt, B, T, H, d_qkv, d_gate);
+    if (dtype == ASCA_BF16 && (dh == 128 || dh == 64) && chunk == 64 && asca_tc_enabled() && delta_tc::available())
+        return delta_tc::backward(ctx, q, k, v, alpha, beta, qnorm, knorm, d_o, ckpt, B, T, H, dh, d_qkv, d_gate);
 #define ASCA_BWD(DH_, C_)                                                                                             \
     return dtype == ASCA_BF16                                                                                         \
                ? launch_bwd<DH_, C_, __nv_bfloat16>(ctx, q, k, v, alpha, beta, qnorm, knorm, d_o, ckpt, (int)B, (int)T, \

@@ -19,7 +19,7 @@ bool asca_tc_enabled();  // gemm.cu
 namespace delta_tc {
 bool available();
 int forward(asca_ctx* ctx, const void* q, const void* k, const void* v, const float* alpha, const float* beta,
-            int64_t B, int64_t T, int64_t H, void* o, const float* s_init, float* s_final, float* ckpt);
+            int64_t B, int64_t T, int64_t H, int64_t dh, void* o, const float* s_init, float* s_final, float* ckpt);
 }  // namespace delta_tc
 
 namespace {
@@ -445,9 +445,9 @@ int asca_delta_fwd(asca_ctx* ctx, const void* q, const void* k, const void* v, c
         }
         return ASCA_OK;
     }
-    // bf16 mode, dh = 128: chunk-parallel WY/UT form on the tensor cores (checkpoints every 64)
-    if (dtype == ASCA_BF16 && dh == 128 && (!ckpt || chunk == 64) && asca_tc_enabled() && delta_tc::available())
-        return delta_tc::forward(ctx, q, k, v, alpha, beta, B, T, H, o, s_init, s_final, ckpt);
+    // bf16 mode, dh = 128 (or 64, zero-padded inside): chunk-parallel WY/UT form on the tensor cores (checkpoints every 64)
+    if (dtype == ASCA_BF16 && (dh == 128 || dh == 64) && (!ckpt || chunk == 64) && asca_tc_enabled() && delta_tc::available())
+        return delta_tc::forward(ctx, q, k, v, alpha, beta, B, T, H, dh, o, s_init, s_final, ckpt);
     if (ckpt)
         for (auto& e : ctx->dtiles)
             if (e.ckpt == (const void*)ckpt) e.ckpt = nullptr;   // kept tiles no longer match this buffer

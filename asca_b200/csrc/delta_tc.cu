@@ -23,6 +23,12 @@
 //
 // Every mbarrier wait is bounded (tc::mbar_wait): a wait that runs out sets the context's error
 // word, and the CTA still frees its TMEM and exits.
+//
+// Head dim 64 runs on the same kernels with every head zero-padded to 128 (`dhi` = the head dim in the caller's
+// tensors): the pre-pass reads 64 columns and fills the other 64 of its operand tiles with zeros, the chain kernels'
+// tiles, TMEM state and products keep the 128 shapes (the padded rows and columns of S, dS and of every product are
+// exact zeros), and only the accesses to the caller's tensors (q, k, v, o, dO, d_qkv, initial / final state, and the
+// chunk-start states kept for the backward: the live 64 x 64 block as bf16) use the 64-wide layout.
 #include "common.cuh"
 #include "tc_common.cuh"
 
@@ -89,7 +95,7 @@ __device__ __forceinline__ void strip16(const float* __restrict__ lrow, const fl
 
 __global__ void __launch_bounds__(PRE_THREADS, 3) delta_prep_tc_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
-    const float* __restrict__ alpha, const float* __restrict__ beta, int T, int H, int n_chunks, Tiles out,
+    const float* __restrict__ alpha, const float* __restrict__ beta, int T, int H, int dhi, int n_chunks, Tiles out,
     int* err_word) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -111,7 +117,7 @@ __global__ void __launch_bounds__(PRE_THREADS, 3) delta_prep_tc_kernel(
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int chunk = blockIdx.x, chain = blockIdx.y;
     const int b = chain / H, h = chain % H;
-    const int d = H * DH;
+    const int d = H * dhi;
     const int t0 = chunk * C;
     const int n = T - t0 < C ? T - t0 : C;
     const int64_t row0 = (int64_t)b * T + t0;
@@ -124,8 +130,8 @@ __global__ void __launch_bounds__(PRE_THREADS, 3) delta_prep_tc_kernel(
     for (int it = 0; it < 8; ++it) {
         const int t = (tid >> 4) + it * 8;
         k8[it] = q8[it] = v8[it] = make_uint4(0, 0, 0, 0);
-        if (t < n) {
-            const int64_t off = (row0 + t) * d + h * DH + sj * 8;
+        if (t < n && sj * 8 < dhi) {
+            const int64_t off = (row0 + t) * d + h * dhi + sj * 8;
             k8[it] = *reinterpret_cast<const uint4*>(k + off);
             q8[it] = *reinterpret_cast<const uint4*>(q + off);
             v8[it] = *reinterpret_cast<const uint4*>(v + off);
@@ -426,7 +432,7 @@ __global__ void __launch_bounds__(CH_THREADS, 1) delta_fwd_tc_kernel(
     const __grid_constant__ CUtensorMap mapWQ, const __grid_constant__ CUtensorMap mapUV,
     const __grid_constant__ CUtensorMap mapKW, const __grid_constant__ CUtensorMap mapAA,
     const __grid_constant__ CUtensorMap mapS0, const float* __restrict__ GC,
-    int T, int H, int n_chunks, TO* __restrict__ o, const float* __restrict__ s_init, float* __restrict__ s_final,
+    int T, int H, int dhi, int n_chunks, TO* __restrict__ o, const float* __restrict__ s_init, float* __restrict__ s_final,
     float* __restrict__ ckpt, __nv_bfloat16* __restrict__ s0b, int* err_word) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -445,7 +451,7 @@ __global__ void __launch_bounds__(CH_THREADS, 1) delta_fwd_tc_kernel(
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int chain = blockIdx.x;
     const int b = chain / H, h = chain % H;
-    const int d = H * DH;
+    const int d = H * dhi;
     const int64_t row0 = (int64_t)b * T;
     const int64_t tile0 = (int64_t)chain * n_chunks;
 
@@ -505,8 +511,9 @@ __global__ void __launch_bounds__(CH_THREADS, 1) delta_fwd_tc_kernel(
                 if (!tc::mbar_wait(s_ready, c & 1, abort_flag, err_word, 212)) break;
                 tc::tcgen05_fence_after();
                 if (s0b) {   // the state at the start of chunk c, bf16, straight from the operand tile: two 128 x 64 boxes
-                    tc::tma_store_2d(&mapS0, S_s, 0, (int)(tile0 + c) * DH);
-                    tc::tma_store_2d(&mapS0, S_s + DH * 128, 64, (int)(tile0 + c) * DH);
+                             // (head dim 64: the live 64 x 64 block, the first 8 KiB of the first box)
+                    tc::tma_store_2d(&mapS0, S_s, 0, (int)(tile0 + c) * dhi);
+                    if (dhi == DH) tc::tma_store_2d(&mapS0, S_s + DH * 128, 64, (int)(tile0 + c) * DH);
                     tc::bulk_commit_group();
                 }
                 // D1 = [W^ ; Qg] S0
@@ -542,13 +549,13 @@ __global__ void __launch_bounds__(CH_THREADS, 1) delta_fwd_tc_kernel(
         // initial state: checkpoint 0, bf16 operand copy, f32 state scaled by the first chunk's decay
         {
             const float g0 = GC[tile0];
-            const float* si = s_init ? s_init + (int64_t)chain * DH * DH + (int64_t)tid * DH : nullptr;
+            const float* si = s_init && tid < dhi ? s_init + (int64_t)chain * dhi * dhi + (int64_t)tid * dhi : nullptr;
 #pragma unroll 1
             for (int cc = 0; cc < DH / 32; ++cc) {
                 uint32_t r[32];
                 float f[32];
 #pragma unroll
-                for (int j = 0; j < 32; ++j) f[j] = si ? si[cc * 32 + j] : 0.0f;
+                for (int j = 0; j < 32; ++j) f[j] = si && cc * 32 < dhi ? si[cc * 32 + j] : 0.0f;
                 if (ck) {
 #pragma unroll
                     for (int j = 0; j < 8; ++j)
@@ -605,13 +612,13 @@ __global__ void __launch_bounds__(CH_THREADS, 1) delta_fwd_tc_kernel(
                 // O rows (TMEM lanes 64-127 of D1)
                 const int t = tid - 64;
                 const bool live = c * C + t < T;
-                TO* orow = o + (row0 + c * C + (live ? t : 0)) * d + h * DH;
+                TO* orow = o + (row0 + c * C + (live ? t : 0)) * d + h * dhi;
 #pragma unroll 1
                 for (int cc = 0; cc < DH / 32; ++cc) {
                     uint32_t r[32];
                     tc::tmem_ld_32x32(tmem_D + lane_addr + cc * 32, r);
                     tc::tmem_ld_wait();
-                    if (live) {
+                    if (live && cc * 32 < dhi) {
                         if (sizeof(TO) == 2) {
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {
@@ -633,8 +640,8 @@ __global__ void __launch_bounds__(CH_THREADS, 1) delta_fwd_tc_kernel(
             // new state: checkpoint / final state (f32), bf16 operand copy, pre-scale for the next chunk
             const bool last = c + 1 == n_chunks;
             const float gnext = last ? 1.0f : GC[tile0 + c + 1];
-            float* dst = last ? (s_final ? s_final + (int64_t)chain * DH * DH : nullptr)
-                              : (ck ? ck + (int64_t)(c + 1) * DH * DH : nullptr);
+            float* dst = last ? (s_final ? s_final + (int64_t)chain * dhi * dhi : nullptr)
+                              : (ck ? ck + (int64_t)(c + 1) * DH * DH : nullptr);   // (f32 checkpoints: head dim 128 only)
 #pragma unroll 1
             for (int cc = 0; cc < DH / 32; ++cc) {
                 uint32_t r[32];
@@ -643,10 +650,10 @@ __global__ void __launch_bounds__(CH_THREADS, 1) delta_fwd_tc_kernel(
                 float f[32];
 #pragma unroll
                 for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(r[j]);
-                if (dst) {
+                if (dst && tid < dhi && cc * 32 < dhi) {
 #pragma unroll
                     for (int j = 0; j < 8; ++j)
-                        reinterpret_cast<float4*>(dst + (int64_t)tid * DH + cc * 32)[j] =
+                        reinterpret_cast<float4*>(dst + (int64_t)tid * dhi + cc * 32)[j] =
                             make_float4(f[4 * j], f[4 * j + 1], f[4 * j + 2], f[4 * j + 3]);
                 }
                 if (!last) {
@@ -714,8 +721,8 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
     const __grid_constant__ CUtensorMap mapQR, const __grid_constant__ CUtensorMap mapDO,
     const __grid_constant__ CUtensorMap mapAA, const __grid_constant__ CUtensorMap mapTP,
     const __grid_constant__ CUtensorMap mapS0, Tiles tl,
-    const float* __restrict__ alpha, const float* __restrict__ qnorm, const float* __restrict__ knorm, int T, int H, int n_chunks, float* __restrict__ d_qkv,
-    float* __restrict__ d_gate, int* err_word) {
+    const float* __restrict__ alpha, const float* __restrict__ qnorm, const float* __restrict__ knorm, int T, int H, int dhi, int n_chunks,
+    float* __restrict__ d_qkv, float* __restrict__ d_gate, int* err_word) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     float* vec = reinterpret_cast<float*>(sm + R_END);
@@ -741,7 +748,7 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
     const int arow = 32 * wq + lane;                                 // M=128 accumulator (dS) mapping
     const int chain = blockIdx.x;
     const int b = chain / H, h = chain % H;
-    const int d = H * DH;
+    const int d = H * dhi;
     const int64_t seq_row0 = (int64_t)b * T;
     const int64_t tile0 = (int64_t)chain * n_chunks;
 
@@ -770,15 +777,24 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
         tc::tmem_st_wait();
         for (int i = tid; i < 32768 / 16; i += BW_THREADS) *reinterpret_cast<uint4*>(sm + R_DS + i * 16) = make_uint4(0, 0, 0, 0);
     }
+    // Head dim 64: a chunk-start state arrives as its live 64 x 64 block (rows 0-63 of the first column box); the rest of
+    // the S0 operand must read as zeros. The region doubles as staging, so it is cleared again after every chunk.
+    auto clear_s0_pad = [&] {
+        for (int i = tid; i < (32768 - 8192) / 16; i += BW_THREADS) *reinterpret_cast<uint4*>(sm + R_S0 + 8192 + i * 16) = make_uint4(0, 0, 0, 0);
+    };
+    if (dhi != DH) clear_s0_pad();
 
     // Three groups in the order the chunk needs them: [0] S0, W^, beta gam K; [7] Kw, dO, A; [8] the rest.
     auto issue_tma = [&](int c) {
         const int t = (int)(tile0 + c);
         const int grow = (int)(seq_row0 + (int64_t)c * C);
-        tc::mbar_expect_tx(&bars[0], BW_TX_A);
+        tc::mbar_expect_tx(&bars[0], dhi == DH ? BW_TX_A : BW_TX_A - 32768 + 8192);
+        // caller's tensors, head dim 64: the second column box starts past the last column and arrives as TMA's zero fill
+        const int xc[2] = {h * dhi, dhi == DH ? h * DH + 64 : H * dhi};
 #pragma unroll
         for (int kb = 0; kb < 2; ++kb) {
-            tc::tma_load_2d(sm + R_S0 + kb * 16384, &mapS0, kb * 64, t * 128, &bars[0]);
+            if (dhi == DH) tc::tma_load_2d(sm + R_S0 + kb * 16384, &mapS0, kb * 64, t * 128, &bars[0]);
+            else if (kb == 0) tc::tma_load_2d(sm + R_S0, &mapS0, 0, t * 64, &bars[0]);
             tc::tma_load_2d(sm + R_WH + kb * 8192, &mapWQ, kb * 64, t * 128, &bars[0]);
             tc::tma_load_2d(sm + R_BK + kb * 8192, &map64x128, kb * 64, t * 64, &bars[0]);
         }
@@ -786,7 +802,7 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
         tc::tma_load_2d(sm + R_A, &mapAA, 0, t * 64, &bars[7]);
 #pragma unroll
         for (int kb = 0; kb < 2; ++kb) {
-            tc::tma_load_2d(sm + R_DO + kb * 8192, &mapDO, h * DH + kb * 64, grow, &bars[7]);
+            tc::tma_load_2d(sm + R_DO + kb * 8192, &mapDO, xc[kb], grow, &bars[7]);
             tc::tma_load_2d(sm + R_KW + kb * 8192, &mapKW, kb * 64, t * 64, &bars[7]);
         }
         tc::mbar_expect_tx(&bars[8], BW_TX_C);
@@ -797,8 +813,8 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
             // K and Q straight from the caller's tensors (like dO): rows past the sequence end hold the next
             // sequence's tokens (or TMA's zero fill past the tensor); every product that reads them multiplies by an
             // exact zero there (beta = 0, U rows = 0, and dA rows masked below)
-            tc::tma_load_2d(sm + R_K + kb * 8192, &mapKR, h * DH + kb * 64, grow, &bars[8]);
-            tc::tma_load_2d(sm + R_Q + kb * 8192, &mapQR, h * DH + kb * 64, grow, &bars[8]);
+            tc::tma_load_2d(sm + R_K + kb * 8192, &mapKR, xc[kb], grow, &bars[8]);
+            tc::tma_load_2d(sm + R_Q + kb * 8192, &mapQR, xc[kb], grow, &bars[8]);
         }
     };
     auto wait_bar = [&](int i, uint32_t parity) {
@@ -1009,10 +1025,11 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
         for (int itv = 0; itv < 64 / (BW_THREADS / 8); ++itv) {
             const int r_ = itv * (BW_THREADS / 8) + (tid >> 3), l8 = tid & 7;
             if (r_ < n) {
-                float* dv = d_qkv + (grow + r_) * 3 * d + 2 * d + h * DH;
+                float* dv = d_qkv + (grow + r_) * 3 * d + 2 * d + h * dhi;
 #pragma unroll
                 for (int i = 0; i < 4; ++i)
-                    reinterpret_cast<float4*>(dv)[l8 + 8 * i] = reinterpret_cast<const float4*>(sm + R_DS)[r_ * 32 + ((l8 + 8 * i) ^ (r_ & 31))];
+                    if ((l8 + 8 * i) * 4 < dhi)
+                        reinterpret_cast<float4*>(dv)[l8 + 8 * i] = reinterpret_cast<const float4*>(sm + R_DS)[r_ * 32 + ((l8 + 8 * i) ^ (r_ & 31))];
             }
         }
         {
@@ -1166,10 +1183,11 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
                 dot += __shfl_xor_sync(0xffffffffu, dot, 4);
                 if (r_ < n) {
                     const float inv = 1.0f / v_nrm[srow];
-                    float* dst = d_qkv + (grow + r_) * 3 * d + (hh == 0 ? 0 : d) + h * DH;
+                    float* dst = d_qkv + (grow + r_) * 3 * d + (hh == 0 ? 0 : d) + h * dhi;
 #pragma unroll
                     for (int i = 0; i < 4; ++i)
-                        reinterpret_cast<float4*>(dst)[l8 + 8 * i] = make_float4((g4[i].x - y[i][0] * dot) * inv, (g4[i].y - y[i][1] * dot) * inv,
+                        if ((l8 + 8 * i) * 4 < dhi)
+                            reinterpret_cast<float4*>(dst)[l8 + 8 * i] = make_float4((g4[i].x - y[i][0] * dot) * inv, (g4[i].y - y[i][1] * dot) * inv,
                                                                                   (g4[i].z - y[i][2] * dot) * inv, (g4[i].w - y[i][3] * dot) * inv);
                 }
             }
@@ -1227,6 +1245,7 @@ __global__ void __launch_bounds__(BW_THREADS, 1) delta_bwd_tc_kernel(
         tc::tcgen05_fence_after();
         __syncthreads();   // staging reads are finished before the dS region is rewritten
         if (c > 0) {
+            if (dhi != DH) clear_s0_pad();
             if (tid == 0) {
                 tc::fence_proxy_async_smem();
                 issue_tma(c - 1);
@@ -1315,25 +1334,25 @@ static size_t carve_tiles(char* w, int64_t n_tiles, bool full, Tiles* t) {
 }
 
 static int run_prepass(asca_ctx* ctx, const void* q, const void* k, const void* v, const float* alpha,
-                       const float* beta, int64_t T, int64_t H, int64_t n_chunks, int64_t chains, const Tiles& t) {
+                       const float* beta, int64_t T, int64_t H, int64_t dh, int64_t n_chunks, int64_t chains, const Tiles& t) {
     ASCA_CUDA(ctx, cudaFuncSetAttribute(delta_prep_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PRE_SMEM));
     {
         asca_span sp(ctx, "delta_prep_tc_kernel");
         delta_prep_tc_kernel<<<dim3((unsigned)n_chunks, (unsigned)chains), PRE_THREADS, PRE_SMEM, ctx->stream>>>(
-            (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, alpha, beta, (int)T, (int)H,
+            (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, alpha, beta, (int)T, (int)H, (int)dh,
             (int)n_chunks, t, ctx->err_word);
     }
     ASCA_CHECK_LAUNCH(ctx);
     return ASCA_OK;
 }
 
-// Forward for bf16 q,k,v (dh = 128). o is bf16. When checkpoints are requested (a backward will
-// follow) the pre-pass also writes the backward-only tiles into a context-owned buffer keyed by
+// Forward for bf16 q,k,v (dh = 128, or 64 zero-padded to 128 inside). o is bf16. When checkpoints are requested (a
+// backward will follow) the pre-pass also writes the backward-only tiles into a context-owned buffer keyed by
 // the checkpoint pointer, so that the backward does not repeat the pre-pass. In this mode the
-// checkpoint buffer holds the chunk-start states rounded to bf16, (B, H, n_chunks, DH, DH) row-major
+// checkpoint buffer holds the chunk-start states rounded to bf16, (B, H, n_chunks, dh, dh) row-major
 // in its first half: the backward loads them by TMA as tensor-core operands.
 int forward(asca_ctx* ctx, const void* q, const void* k, const void* v, const float* alpha, const float* beta,
-            int64_t B, int64_t T, int64_t H, void* o, const float* s_init, float* s_final, float* ckpt) {
+            int64_t B, int64_t T, int64_t H, int64_t dh, void* o, const float* s_init, float* s_final, float* ckpt) {
     const int64_t n_chunks = (T + C - 1) / C, chains = B * H, n_tiles = chains * n_chunks;
     Tiles t{};
     const bool keep = ckpt != nullptr;
@@ -1377,17 +1396,18 @@ int forward(asca_ctx* ctx, const void* q, const void* k, const void* v, const fl
     }
     w = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(w) + 1023) & ~(uintptr_t)1023);
     carve_tiles(w, n_tiles, keep, &t);
-    ASCA_TRY(run_prepass(ctx, q, k, v, alpha, beta, T, H, n_chunks, chains, t));
+    ASCA_TRY(run_prepass(ctx, q, k, v, alpha, beta, T, H, dh, n_chunks, chains, t));
     CUtensorMap mWQ, mUV, mKW, mAA, mS0;
     if (!make_map(&mWQ, t.WQ, n_tiles * 128, DH, 64, 128) || !make_map(&mUV, t.UV, n_tiles * 64, DH, 64, 64) ||
         !make_map(&mKW, t.KW, n_tiles * 64, DH, 64, 64) || !make_map(&mAA, t.AA, n_tiles * 64, 64, 64, 64) ||
-        !make_map(&mS0, keep ? (const void*)ckpt : (const void*)t.WQ, n_tiles * DH, DH, 64, 128))   // bf16 states in the checkpoint buffer
+        !(keep ? make_map(&mS0, ckpt, n_tiles * dh, dh, 64, (int)dh)   // bf16 states in the checkpoint buffer
+               : make_map(&mS0, t.WQ, n_tiles * DH, DH, 64, 128)))    // (unused)
         return asca_fail(ctx, ASCA_ERR_CUDA, "delta_tc: cuTensorMapEncodeTiled failed");
     auto kern = delta_fwd_tc_kernel<__nv_bfloat16>;
     ASCA_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)CH_SMEM));
     {
         asca_span sp(ctx, "delta_fwd_tc_kernel");
-        kern<<<(unsigned)chains, CH_THREADS, CH_SMEM, ctx->stream>>>(mWQ, mUV, mKW, mAA, mS0, t.GC, (int)T, (int)H,
+        kern<<<(unsigned)chains, CH_THREADS, CH_SMEM, ctx->stream>>>(mWQ, mUV, mKW, mAA, mS0, t.GC, (int)T, (int)H, (int)dh,
                                                                     (int)n_chunks, (__nv_bfloat16*)o, s_init, s_final,
                                                                     nullptr, reinterpret_cast<__nv_bfloat16*>(ckpt), ctx->err_word);
     }
@@ -1398,16 +1418,16 @@ int forward(asca_ctx* ctx, const void* q, const void* k, const void* v, const fl
         e.q = q; e.k = k; e.v = v; e.alpha = alpha; e.beta = beta;
         e.B = B;
         e.T = T;
-        e.H = H;
+        e.H = H * 1024 + dh;   // heads and head dim in one key field
         e.stamp = ++ctx->dtiles_clock;
     }
     return ASCA_OK;
 }
 
-// Backward for bf16 q,k,v,d_o (dh = 128, checkpoints every 64 tokens from the forward).
+// Backward for bf16 q,k,v,d_o (dh = 128 or 64, checkpoints every 64 tokens from the forward).
 int backward(asca_ctx* ctx, const void* q, const void* k, const void* v, const float* alpha, const float* beta,
              const float* qnorm, const float* knorm, const void* d_o, const float* ckpt, int64_t B, int64_t T, int64_t H,
-             float* d_qkv, float* d_gate) {
+             int64_t dh, float* d_qkv, float* d_gate) {
     const int64_t n_chunks = (T + C - 1) / C, chains = B * H, n_tiles = chains * n_chunks;
     Tiles t{};
     int slot = -1;
@@ -1416,7 +1436,7 @@ int backward(asca_ctx* ctx, const void* q, const void* k, const void* v, const f
         // the tiles are functions of q, k, v, alpha, beta: the same buffers must come back (their contents are the
         // caller's contract, see the header); anything else rebuilds the tiles
         if (e.buf && e.ckpt == (const void*)ckpt && e.q == q && e.k == k && e.v == v && e.alpha == (const void*)alpha &&
-            e.beta == (const void*)beta && e.B == B && e.T == T && e.H == H)
+            e.beta == (const void*)beta && e.B == B && e.T == T && e.H == H * 1024 + dh)
             slot = (int)i;
     }
     if (slot >= 0) {
@@ -1429,20 +1449,20 @@ int backward(asca_ctx* ctx, const void* q, const void* k, const void* v, const f
         ASCA_TRY(asca_workspace(ctx, carve_tiles(nullptr, n_tiles, true, nullptr) + 1024, &ws));
         char* w = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(ws) + 1023) & ~(uintptr_t)1023);
         carve_tiles(w, n_tiles, true, &t);
-        ASCA_TRY(run_prepass(ctx, q, k, v, alpha, beta, T, H, n_chunks, chains, t));
+        ASCA_TRY(run_prepass(ctx, q, k, v, alpha, beta, T, H, dh, n_chunks, chains, t));
     }
     CUtensorMap mWQ, mBK, mKW, mKR, mQR, mDO, mAA, mTP, mS0;
     bool ok = make_map(&mWQ, t.WQ, n_tiles * 128, DH, 64, 64) && make_map(&mBK, t.BK, n_tiles * 64, DH, 64, 64) &&
-              make_map(&mKW, t.KW, n_tiles * 64, DH, 64, 64) && make_map(&mKR, k, B * T, H * DH, 64, 64) &&
-              make_map(&mQR, q, B * T, H * DH, 64, 64) && make_map(&mDO, d_o, B * T, H * DH, 64, 64) &&
+              make_map(&mKW, t.KW, n_tiles * 64, DH, 64, 64) && make_map(&mKR, k, B * T, H * dh, 64, 64) &&
+              make_map(&mQR, q, B * T, H * dh, 64, 64) && make_map(&mDO, d_o, B * T, H * dh, 64, 64) &&
               make_map(&mAA, t.AA, n_tiles * 64, 64, 64, 64) && make_map(&mTP, t.TP, n_tiles * 64, 64, 64, 64) &&
-              make_map(&mS0, ckpt, n_tiles * DH, DH, 64, 128);
+              make_map(&mS0, ckpt, n_tiles * dh, dh, 64, (int)dh);
     if (!ok) return asca_fail(ctx, ASCA_ERR_CUDA, "delta_tc: cuTensorMapEncodeTiled failed");
     ASCA_CUDA(ctx, cudaFuncSetAttribute(delta_bwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)BW_SMEM));
     {
         asca_span sp(ctx, "delta_bwd_tc_kernel");
         delta_bwd_tc_kernel<<<(unsigned)chains, BW_THREADS, BW_SMEM, ctx->stream>>>(
-            mWQ, mBK, mKW, mKR, mQR, mDO, mAA, mTP, mS0, t, alpha, qnorm, knorm, (int)T, (int)H, (int)n_chunks, d_qkv,
+            mWQ, mBK, mKW, mKR, mQR, mDO, mAA, mTP, mS0, t, alpha, qnorm, knorm, (int)T, (int)H, (int)dh, (int)n_chunks, d_qkv,
             d_gate, ctx->err_word);
     }
     ASCA_CHECK_LAUNCH(ctx);

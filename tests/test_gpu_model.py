@@ -285,8 +285,8 @@ def test_trainer_loop_matches_oracle_loss_for_loss_and_resumes(orc, gpu, tmp_pat
 
 def test_bf16_compute_train_step_head_dim_64(orc, gpu):
     """bf16 compute mode with head dim 64 (the decode configuration's head size): the delta op runs on the
-    bf16-storage FFMA kernels instead of the tensor-core ones; loss and gradients stay within 2e-2 of the f32
-    oracle (the gate biases of these toy shapes: see _bf16_grad_tol)."""
+    tensor-core kernels with every head zero-padded to 128; loss and gradients stay within 2e-2 of the f32
+    oracle (the gate biases of these toy shapes: see _bf16_grad_tol). 1024 tokens, four chunks per chain."""
     import asca_b200
 
     cfg = (256, 128, 2, 2, 4, 256)
@@ -296,12 +296,16 @@ def test_bf16_compute_train_step_head_dim_64(orc, gpu):
     dev.set_params(ref.params)
     dev.set_compute(asca_b200.BF16)
     rng = orc.Rng(14)
-    B, T = 2, 96
+    B, T = 4, 256
     ids = rng.below(256, B * T)
     tg = np.concatenate([ids.reshape(B, T)[:, 1:], rng.below(256, (B, 1))], axis=1).reshape(-1).astype(np.uint32)
     loss_ref, g_ref = ref.forward_backward(ids, tg, B)
     dev.zero_grads()
+    gpu.profile(True)
     loss = dev.forward_backward(ids, tg, B)
+    names = {n for n, _ in gpu.profile_read()}
+    gpu.profile(False)
+    assert {"delta_prep_tc_kernel", "delta_fwd_tc_kernel", "delta_bwd_tc_kernel"} <= names, names
     _, g = dev.get()
     assert abs(loss - loss_ref) / abs(loss_ref) < 2e-2
     for name in ref.names:

@@ -288,15 +288,15 @@ def test_delta_bf16_mode(orc, gpu):
     assert rel_err(d_gate.cpu().numpy(), dgate_ref) < BF16_TOL
 
 
+@pytest.mark.parametrize("dh", [128, 64])
 @pytest.mark.parametrize("B,T,H", [(1, 64, 1), (2, 128, 2), (2, 200, 3), (1, 1000, 2), (3, 37, 1)])
-def test_delta_bf16_tensor_core_forward(orc, gpu, B, T, H):
-    """bf16 inputs at dh = 128 take the chunked WY/UT tcgen05 forward: outputs, final state and every
-    chunk checkpoint against the f32 recurrence on the same (bf16-rounded) inputs; ragged last chunk;
-    continuation from an initial state."""
+def test_delta_bf16_tensor_core_forward(orc, gpu, B, T, H, dh):
+    """bf16 inputs at dh = 128 (and dh = 64, zero-padded to 128 inside the kernels) take the chunked WY/UT tcgen05
+    forward: outputs, final state and every chunk checkpoint against the f32 recurrence on the same (bf16-rounded)
+    inputs; ragged last chunk; continuation from an initial state."""
     import torch
     from asca_b200 import ops
 
-    dh = 128
     arrs = _delta_inputs(orc, 300 + T, B, T, H, dh)
     q, k, v, alpha, beta = (torch.from_numpy(a).cuda() for a in arrs[:5])
     q16, k16, v16 = q.bfloat16(), k.bfloat16(), v.bfloat16()
@@ -329,23 +329,28 @@ def test_delta_bf16_tensor_core_forward(orc, gpu, B, T, H):
         assert rel_err(s2.cpu().numpy(), sfin_ref) < BF16_TOL
 
 
+@pytest.mark.parametrize("dh", [128, 64])
 @pytest.mark.parametrize("B,T,H", [(1, 64, 1), (2, 128, 2), (2, 200, 3), (1, 700, 2), (3, 37, 1)])
-def test_delta_bf16_tensor_core_backward(orc, gpu, B, T, H):
-    """bf16 inputs at dh = 128, chunk 64: the reverse chunked scan on tcgen05 against the f32 BPTT of
-    the oracle on the same (bf16-rounded) inputs; every output block checked separately."""
+def test_delta_bf16_tensor_core_backward(orc, gpu, B, T, H, dh):
+    """bf16 inputs at dh = 128 or 64, chunk 64: the reverse chunked scan on tcgen05 against the f32 BPTT of
+    the oracle on the same (bf16-rounded) inputs; every output block checked separately; the launch list must
+    name the tensor-core kernels."""
     import torch
     from asca_b200 import ops
 
-    dh = 128
     d = H * dh
     arrs = _delta_inputs(orc, 500 + T, B, T, H, dh)
     q, k, v, alpha, beta, qn, kn, d_o = (torch.from_numpy(a).cuda() for a in arrs)
     q16, k16, v16, do16 = (x.bfloat16() for x in (q, k, v, d_o))
     qr, kr, vr, dor = (x.float().cpu().numpy() for x in (q16, k16, v16, do16))
     dqkv_ref, dgate_ref = orc.delta_bptt(qr, kr, vr, arrs[3], arrs[4], arrs[5], arrs[6], dor, B, T, H, dh)
+    gpu.profile(True)
     o, _, ckpt = ops.delta_fwd(gpu, q16, k16, v16, alpha, beta, B, T, H, dh, chunk=64)
     d_qkv, d_gate = ops.delta_bwd(gpu, q16, k16, v16, alpha, beta, qn, kn, do16, ckpt, B, T, H, dh, chunk=64)
     gpu.sync()
+    names = {n for n, _ in gpu.profile_read()}
+    gpu.profile(False)
+    assert {"delta_prep_tc_kernel", "delta_fwd_tc_kernel", "delta_bwd_tc_kernel"} <= names, names
     got, gg = d_qkv.cpu().numpy(), d_gate.cpu().numpy()
     assert rel_err(got[:, 2 * d:], dqkv_ref[:, 2 * d:]) < BF16_TOL, "dv"
     assert rel_err(got[:, :d], dqkv_ref[:, :d]) < BF16_TOL, "dq"
