@@ -66,8 +66,9 @@ __device__ __forceinline__ void cta_gemm(const float* __restrict__ A, int lda, c
     for (int i = 0; i < TM; ++i)
 #pragma unroll
         for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;
+    constexpr int UNR = TM <= 2 ? 4 : 2;   // small register tiles: more k-steps of loads in flight per warp
     if (ALAY == L_MK && BLAY == L_KN) {
-#pragma unroll 2
+#pragma unroll UNR
         for (int k = 0; k < K; k += 4) {
             float4 a[TM];
 #pragma unroll
@@ -119,7 +120,7 @@ __device__ __forceinline__ void cta_gemm(const float* __restrict__ A, int lda, c
         }
     } else {  // L_MK x L_NK: both contiguous along k; this thread's columns are tn + THR_N * j, so that the lanes of a
               // quarter warp read 8 consecutive rows of B (row stride = 4 banks: all 32 banks, no conflict)
-#pragma unroll 2
+#pragma unroll UNR
         for (int k = 0; k < K; k += 4) {
             float4 b[TN];
 #pragma unroll
@@ -356,6 +357,20 @@ __global__ void __launch_bounds__(BT, 1) delta_bwd_kernel(
             }
         }
 
+        // the interval processed next (the one before this): its k, v rows and its checkpoint are requested into L2 now,
+        // so that its phase F does not start on DRAM latency (q and dO of an interval are re-read shortly after phase F)
+        if (ck > 0) {
+            const int p_lo = (ck - 1) * chunk;
+            constexpr int LPR = DH * (int)sizeof(T) / 128 > 0 ? DH * (int)sizeof(T) / 128 : 1;   // 128-byte lines per row
+            for (int idx = tid; idx < chunk * LPR * 2; idx += BT) {
+                const int which = idx / (chunk * LPR), rem = idx % (chunk * LPR);
+                const T* base = which == 0 ? k : v;
+                const char* ptr = reinterpret_cast<const char*>(base + (row0 + p_lo + rem / LPR) * d + h * DH) + (rem % LPR) * 128;
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(ptr));
+            }
+            const char* st = reinterpret_cast<const char*>(ckpt + ((int64_t)chain * n_ck + ck - 1) * DH * DH);
+            for (int idx = tid; idx < DH * DH * 4 / 128; idx += BT) asm volatile("prefetch.global.L2 [%0];" ::"l"(st + idx * 128));
+        }
         // ---- phase B: sub-chunks in reverse
         for (int j = nsub - 1; j >= 0; --j) {
             const int t0 = t_lo + j * C;
