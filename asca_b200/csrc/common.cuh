@@ -32,6 +32,10 @@ struct asca_ctx {
     void* ws = nullptr;
     size_t ws_bytes = 0;
     int* err_word = nullptr;  // device int the kernels with bounded waits write to
+    // Dynamic tile claims of the persistent tensor-core products (gemm_tc.cu; ASCA_GEMM_DYNAMIC=0 turns them off).
+    // dyn_buf: two counters + the walkers' claim rings.
+    void* dyn_buf = nullptr;
+    uint32_t dyn_seq = 0;
     // tiles of the tensor-core delta forwards that wrote checkpoints, kept for their backwards: one entry per
     // checkpoint buffer (a model keeps one per block), least recently used evicted beyond 32 entries / dtiles_cap bytes
     struct DeltaTiles {

@@ -77,6 +77,7 @@ int asca_ctx_destroy(asca_ctx* ctx) {
         cudaFree(kv.second.second);
     }
     if (ctx->err_word) cudaFree(ctx->err_word);
+    if (ctx->dyn_buf) cudaFree(ctx->dyn_buf);
     cudaStreamDestroy(ctx->own_stream);
     delete ctx;
     return ASCA_OK;

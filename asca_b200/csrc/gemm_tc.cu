@@ -83,8 +83,19 @@ struct KP {
     const uint32_t* ce_targets;
     float* ce_loss;
     float ce_scale;
+    // Dynamic tile claims (null: every walker takes tiles walker, walker + n_walkers, ...). With them a walker -- a CTA,
+    // or a CTA pair -- takes the next unclaimed tile whenever it starts one, so CTAs that find their SM occupied by
+    // another stream's kernels (a collective running beside the step) simply claim fewer tiles instead of holding the
+    // launch up with a fixed share. The producer thread of the walker's first CTA claims (atomicAdd) and publishes the
+    // claim in a small ring in global memory, tagged with launch and claim number; every other role of the walker, and
+    // the pair's second CTA, read it from there.
+    int* dyn_ctr;                      // this launch's counter (zero at launch)
+    int* dyn_reset;                    // the next launch's counter, zeroed by this launch
+    unsigned long long* dyn_ring;      // [walkers][DYN_Q] (tag << 32 | tile)
+    uint32_t dyn_seq;                  // launch number
     int* err_word;
 };
+constexpr int DYN_Q = 16;              // claims a walker's producer can be ahead of its slowest role, with room to spare
 
 // bf16 mode only (2e-2 tolerance; the results are rounded to bf16 or multiply bf16 products): fast exp and divide.
 // A 128 x 128 tile applies these 16 k times, which with the accurate forms costs more than the tile's main loop.
@@ -201,12 +212,47 @@ __global__ void __launch_bounds__(Shape<BN, DEEP, PAIR, EW8>::THREADS, Shape<BN,
         return x;
     };
 
+    // The i-th tile of this walker (-1: none left). claim_tile is for the walker's claiming thread only.
+    const bool dyn = p.dyn_ctr != nullptr;
+    unsigned long long* dyn_slot0 = dyn ? p.dyn_ring + (size_t)walker * DYN_Q : nullptr;
+    auto dyn_tag = [&](int i) { return p.dyn_seq * 4096u + (uint32_t)(i & 4095); };
+    auto claim_tile = [&](int i) -> int {
+        int t = atomicAdd(p.dyn_ctr, 1);
+        if (t >= total_tiles) t = -1;
+        const unsigned long long v = ((unsigned long long)dyn_tag(i) << 32) | (uint32_t)t;
+        asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(dyn_slot0 + (i % DYN_Q)), "l"(v) : "memory");
+        return t;
+    };
+    auto read_tile = [&](int i) -> int {   // one thread polls; bounded like every other wait of the kernel
+        if (!dyn) {
+            const int t = walker + i * n_walkers;
+            return t < total_tiles ? t : -1;
+        }
+        const unsigned long long* e = dyn_slot0 + (i % DYN_Q);
+        const uint32_t want = dyn_tag(i);
+        const long long t0 = clock64();
+        while (true) {
+            unsigned long long v;
+            asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(e) : "memory");
+            if ((uint32_t)(v >> 32) == want) return (int)(uint32_t)v;
+            if (*abort_flag) return -1;
+            if (clock64() - t0 > tc::WAIT_LIMIT_CYCLES) {
+                *abort_flag = 1;
+                if (p.err_word) atomicExch(p.err_word, 107);
+                return -1;
+            }
+        }
+    };
+    if (dyn && blockIdx.x == 0 && threadIdx.x == 0) *p.dyn_reset = 0;   // the launch after this one starts from zero
+
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer (one thread)
         if (lane == 0) {
             uint32_t it = 0;   // k-tiles issued so far, across tiles: ring slot it % STAGES
             bool ok = true;
-            for (int t = walker; t < total_tiles && ok; t += n_walkers) {
+            for (int ti = 0; ok; ++ti) {
+                const int t = dyn && rank == 0 ? claim_tile(ti) : read_tile(ti);
+                if (t < 0) break;
                 const Tile x = locate(t);
                 const int nl0 = x.n0 + rank * BNL;   // first B column this CTA loads
                 for (int kt = 0; kt < x.num_k; ++kt, ++it) {
@@ -234,6 +280,10 @@ __global__ void __launch_bounds__(Shape<BN, DEEP, PAIR, EW8>::THREADS, Shape<BN,
                         tc::tma_load_2d(b_s, &mapB, k0 + x.b_in, nl0 + x.b_out, &full[s]);
                     }
                 }
+                if (!ok && dyn && rank == 0) {   // gave up: the walker's other roles must not wait for more claims
+                    const unsigned long long v = ((unsigned long long)dyn_tag(ti + 1) << 32) | 0xFFFFFFFFu;
+                    asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(dyn_slot0 + ((ti + 1) % DYN_Q)), "l"(v) : "memory");
+                }
             }
         }
     } else if (warp == 1) {
@@ -250,7 +300,10 @@ __global__ void __launch_bounds__(Shape<BN, DEEP, PAIR, EW8>::THREADS, Shape<BN,
         bool ok = true;
         uint32_t it = 0;
         int tl = 0;   // tiles done by this CTA: accumulator buffer tl & 1
-        for (int t = walker; t < total_tiles && ok; t += n_walkers, ++tl) {
+        for (;; ++tl) {
+            int t = lane == 0 && ok ? read_tile(tl) : -1;
+            t = __shfl_sync(0xffffffffu, t, 0);
+            if (t < 0) break;
             const Tile x = locate(t);
             const int buf = tl & 1;
             const uint32_t tmem_acc = tmem_base + buf * BN;
@@ -364,7 +417,10 @@ __global__ void __launch_bounds__(Shape<BN, DEEP, PAIR, EW8>::THREADS, Shape<BN,
         const int l4 = lane & 3, rsub = lane >> 2;   // store phase: 4 lanes per row (64 bytes), 8 rows per instruction
         bool ok = true;
         int tl = 0;
-        for (int t = walker; t < total_tiles && ok; t += n_walkers, ++tl) {
+        for (;; ++tl) {
+            int t = lane == 0 && ok ? read_tile(tl) : -1;
+            t = __shfl_sync(0xffffffffu, t, 0);
+            if (t < 0) break;
             const Tile x = locate(t);
             const int buf = tl & 1;
             const uint32_t tmem_acc = tmem_base + buf * BN;
@@ -687,6 +743,26 @@ static int launch_shape(asca_ctx* ctx, const Args& a, int64_t grid) {
     p.ce_targets = a.ce_targets; p.ce_loss = a.ce_loss; p.ce_scale = a.ce_scale;
     p.qkv_q = a.qkv_q; p.qkv_k = a.qkv_k; p.qkv_v = a.qkv_v; p.qkv_qn = a.qkv_qn; p.qkv_kn = a.qkv_kn; p.qkv_d = a.qkv_d;
     p.err_word = ctx->err_word;
+    {   // dynamic tile claims: not under programmatic dependent launch (the counter hand-over relies on stream order)
+        static const int dyn_env = [] { const char* e = getenv("ASCA_GEMM_DYNAMIC"); return e ? atoi(e) : 1; }();
+        const bool want = dyn_env != 0;   // on unless ASCA_GEMM_DYNAMIC=0
+        if (want && !ctx->pdl) {
+            constexpr size_t RING_OFF = 256, BYTES = RING_OFF + 1024 * DYN_Q * 8;   // up to 1024 walkers
+            if (!ctx->dyn_buf) {
+                if (cudaMalloc(&ctx->dyn_buf, BYTES) != cudaSuccess) return asca_fail(ctx, ASCA_ERR_OOM, "gemm_tc: cannot allocate the tile-claim buffer");
+                ASCA_CUDA(ctx, cudaMemsetAsync(ctx->dyn_buf, 0, BYTES, ctx->stream));
+                ctx->dyn_seq = 0;
+            }
+            if (grid <= 1024) {
+                const uint32_t seq = ++ctx->dyn_seq;
+                int* ctrs = static_cast<int*>(ctx->dyn_buf);
+                p.dyn_ctr = ctrs + (seq & 1) * 32;          // the two counters sit in different 128-byte lines
+                p.dyn_reset = ctrs + ((seq + 1) & 1) * 32;
+                p.dyn_ring = reinterpret_cast<unsigned long long*>(static_cast<char*>(ctx->dyn_buf) + RING_OFF);
+                p.dyn_seq = seq;
+            }
+        }
+    }
     using SH = Shape<BN, DEEP, PAIR, EW8>;
     const size_t smem = SH::SMEM_FIXED + (size_t)((a.group_dim == GROUP_NONE ? 1 : a.n_groups) + 2) * 4;
     auto go = [&](auto kern) -> cudaError_t {

@@ -3,7 +3,7 @@
 isolated ops, each with its roofline, beside the reference's CPU path timed on the host cores of the same box.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--only train,decode,moe,delta]
-    python bench.py --case gemm_dense|gemm_dense_nt|gemm_dense_tn|moe_fwd|moe_bwd|delta_bf16|delta_f32|decode   (profiler captures)
+    python bench.py --case gemm_dense|gemm_dense_nt|gemm_dense_tn|moe_fwd|moe_bwd|delta_bf16|delta_bf16_dh64|delta_f32|decode   (profiler captures)
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \\
         bench.py --gpus N --steps K --warmup W
 
@@ -838,9 +838,10 @@ def run_case(hs: Harness, args):
             fn = lambda: ops.moe_bwd(hs.gpu, xn, w1, w2, pre_p, hid_p, dout, perm, off, F, E, grads=grads)  # noqa: E731
             work = 8.0 * n * d * F
         unit = "TFLOP/s"
-    elif name in ("delta_bf16", "delta_f32"):
-        # the isolated delta op at B = 2 (32 chains x 4096 tokens): traffic scales with the number of chains
-        b, h, t, dh = 2, 16, 4096, 128
+    elif name in ("delta_bf16", "delta_f32", "delta_bf16_dh64"):
+        # the isolated delta op at B = 2 (32 chains x 4096 tokens): traffic scales with the number of chains;
+        # delta_bf16_dh64: heads of 64 (the decode configuration's head size) at the same width, B = 8 (256 chains)
+        b, h, t, dh = (8, 32, 4096, 64) if name == "delta_bf16_dh64" else (2, 16, 4096, 128)
         n, d = b * t, h * dh
         q = torch.nn.functional.normalize(torch.randn(n, h, dh, generator=g, **f32), dim=-1).reshape(n, d).contiguous()
         k = torch.nn.functional.normalize(torch.randn(n, h, dh, generator=g, **f32), dim=-1).reshape(n, d).contiguous()
@@ -848,7 +849,7 @@ def run_case(hs: Harness, args):
         alpha = torch.sigmoid(2 + 0.5 * torch.randn(n, h, generator=g, **f32))
         beta = torch.sigmoid(torch.randn(n, h, generator=g, **f32))
         qn, kn = torch.ones(n, h, **f32), torch.ones(n, h, **f32)
-        if name == "delta_bf16":
+        if name != "delta_f32":
             q, k, v, d_o = (x.bfloat16() for x in (q, k, v, d_o))
         o = torch.empty_like(q)
         ckpt = torch.empty(ops.delta_ckpt_floats(hs.gpu, b, t, h, dh, 64), **f32)
@@ -858,7 +859,7 @@ def run_case(hs: Harness, args):
             ops.delta_fwd(hs.gpu, q, k, v, alpha, beta, b, t, h, dh, chunk=64, out=o, ckpt=ckpt)
             ops.delta_bwd(hs.gpu, q, k, v, alpha, beta, qn, kn, d_o, ckpt, b, t, h, dh, chunk=64, d_qkv=d_qkv, d_gate=d_gate)
 
-        s_io = 2 if name == "delta_bf16" else 4
+        s_io = 4 if name == "delta_f32" else 2
         work, unit = 11.0 * n * d * s_io + 8.0 * n * h * 4, "GB/s"
     elif name == "decode":
         # a few greedy steps of the decode configuration (256 streams)
@@ -991,7 +992,8 @@ def main():
     ap.add_argument("--only", default="", help="comma-separated subset of train,decode,moe,delta")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline legs")
     ap.add_argument("--case", default="", help="run one small single-kernel case instead (for profiler captures): gemm_dense, "
-                                               "gemm_dense_nt, gemm_dense_tn, moe_fwd, moe_bwd, delta_bf16, delta_f32, decode")
+                                               "gemm_dense_nt, gemm_dense_tn, moe_fwd, moe_bwd, delta_bf16, delta_bf16_dh64, delta_f32, decode, rmsnorm, rmsnorm_bwd, "
+                                               "residual_rmsnorm, adamw, gather, dispatch, delta_step")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

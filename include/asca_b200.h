@@ -161,7 +161,8 @@ int asca_adamw_host(asca_ctx* ctx, float* p, const float* g, float* m, float* v,
  *             boundary, layout (B, H, ceil(T/chunk), dh, dh); entry c is S before token
  *             c*chunk. This replaces the reference's per-step state history
  *             ((T+1)*dh*dh per chain) and is what asca_delta_bwd recomputes from.
- *             With dtype ASCA_BF16, dh = 128 and chunk = 64 (the tensor-core kernels) the same
+ *             With dtype ASCA_BF16, dh = 128 or 64 and chunk = 64 (the tensor-core kernels; heads of 64 are
+ *             zero-padded to 128 inside them) the same
  *             states are stored rounded to bf16, same layout, in the first half of the buffer;
  *             either way the buffer is meant to be handed back to asca_delta_bwd unchanged.
  *             Contract of the tensor-core mode: that forward also keeps, inside the context, tiles it derived
