@@ -93,6 +93,7 @@ struct KP {
     int* dyn_reset;                    // the next launch's counter, zeroed by this launch
     unsigned long long* dyn_ring;      // [walkers][DYN_Q] (tag << 32 | tile)
     uint32_t dyn_seq;                  // launch number
+    int dyn_batch;                     // consecutive tiles per claim (short tiles: one claim's latency per several tiles)
     int* err_word;
 };
 constexpr int DYN_Q = 16;              // claims a walker's producer can be ahead of its slowest role, with room to spare
@@ -156,6 +157,8 @@ __global__ void __launch_bounds__(Shape<BN, DEEP, PAIR, EW8>::THREADS, Shape<BN,
             if (g < n_groups) prefix[g] = base + inc - cnt;
             base += __shfl_sync(0xffffffffu, inc, 31);
         }
+        if (p.group_dim != GROUP_NONE)   // the group offsets once more in shared memory: locate() runs per tile and role
+            for (int g = lane; g <= n_groups; g += 32) prefix[n_groups + 1 + g] = p.offsets[g];
         if (lane == 0) {
             prefix[n_groups] = base;
             *abort_flag = 0;
@@ -200,8 +203,8 @@ __global__ void __launch_bounds__(Shape<BN, DEEP, PAIR, EW8>::THREADS, Shape<BN,
         x.M = p.M;
         x.K = p.K;
         if (p.group_dim != GROUP_NONE) {
-            seg_lo = p.offsets[lo];
-            const int n_g = p.offsets[lo + 1] - seg_lo;
+            seg_lo = prefix[n_groups + 1 + lo];
+            const int n_g = prefix[n_groups + 2 + lo] - seg_lo;
             if (p.group_dim == GROUP_M) x.M = n_g; else x.K = n_g;
         }
         x.num_k = (x.K + BK - 1) / BK;
@@ -216,12 +219,11 @@ __global__ void __launch_bounds__(Shape<BN, DEEP, PAIR, EW8>::THREADS, Shape<BN,
     const bool dyn = p.dyn_ctr != nullptr;
     unsigned long long* dyn_slot0 = dyn ? p.dyn_ring + (size_t)walker * DYN_Q : nullptr;
     auto dyn_tag = [&](int i) { return p.dyn_seq * 4096u + (uint32_t)(i & 4095); };
-    auto claim_tile = [&](int i) -> int {
-        int t = atomicAdd(p.dyn_ctr, 1);
+    const int batch = dyn ? p.dyn_batch : 1;
+    auto publish_claim = [&](int i, int t) {   // claim i = tiles [t, t + batch) (-1: none left)
         if (t >= total_tiles) t = -1;
         const unsigned long long v = ((unsigned long long)dyn_tag(i) << 32) | (uint32_t)t;
         asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(dyn_slot0 + (i % DYN_Q)), "l"(v) : "memory");
-        return t;
     };
     auto read_tile = [&](int i) -> int {   // one thread polls; bounded like every other wait of the kernel
         if (!dyn) {
@@ -250,9 +252,20 @@ __global__ void __launch_bounds__(Shape<BN, DEEP, PAIR, EW8>::THREADS, Shape<BN,
         if (lane == 0) {
             uint32_t it = 0;   // k-tiles issued so far, across tiles: ring slot it % STAGES
             bool ok = true;
-            for (int ti = 0; ok; ++ti) {
-                const int t = dyn && rank == 0 ? claim_tile(ti) : read_tile(ti);
-                if (t < 0) break;
+            // The claiming thread asks for claim ci + 1 before it loads claim ci's tiles and publishes it after them: the
+            // atomic's round trip hides behind the loads, and no other role needs the next claim before this one is used up.
+            const bool claimer = dyn && rank == 0;
+            int cur = 0;
+            if (claimer) {
+                cur = atomicAdd(p.dyn_ctr, batch);
+                publish_claim(0, cur);
+            }
+            for (int ci = 0; ok; ++ci) {
+                const int t0 = claimer ? (cur < total_tiles ? cur : -1) : read_tile(ci);
+                if (t0 < 0) break;
+                int nxt = 0;
+                if (claimer) nxt = atomicAdd(p.dyn_ctr, batch);
+              for (int t = t0; t < t0 + batch && t < total_tiles && ok; ++t) {
                 const Tile x = locate(t);
                 const int nl0 = x.n0 + rank * BNL;   // first B column this CTA loads
                 for (int kt = 0; kt < x.num_k; ++kt, ++it) {
@@ -280,9 +293,10 @@ __global__ void __launch_bounds__(Shape<BN, DEEP, PAIR, EW8>::THREADS, Shape<BN,
                         tc::tma_load_2d(b_s, &mapB, k0 + x.b_in, nl0 + x.b_out, &full[s]);
                     }
                 }
-                if (!ok && dyn && rank == 0) {   // gave up: the walker's other roles must not wait for more claims
-                    const unsigned long long v = ((unsigned long long)dyn_tag(ti + 1) << 32) | 0xFFFFFFFFu;
-                    asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(dyn_slot0 + ((ti + 1) % DYN_Q)), "l"(v) : "memory");
+              }
+                if (claimer) {   // (after a wait that gave up: "none left", so that the walker's other roles stop too)
+                    cur = ok ? nxt : total_tiles;
+                    publish_claim(ci + 1, cur);
                 }
             }
         }
@@ -300,10 +314,11 @@ __global__ void __launch_bounds__(Shape<BN, DEEP, PAIR, EW8>::THREADS, Shape<BN,
         bool ok = true;
         uint32_t it = 0;
         int tl = 0;   // tiles done by this CTA: accumulator buffer tl & 1
-        for (;; ++tl) {
-            int t = lane == 0 && ok ? read_tile(tl) : -1;
-            t = __shfl_sync(0xffffffffu, t, 0);
-            if (t < 0) break;
+        for (int ci = 0;; ++ci) {
+            int t0 = lane == 0 && ok ? read_tile(ci) : -1;
+            t0 = __shfl_sync(0xffffffffu, t0, 0);
+            if (t0 < 0) break;
+          for (int t = t0; t < t0 + batch && t < total_tiles && ok; ++t, ++tl) {
             const Tile x = locate(t);
             const int buf = tl & 1;
             const uint32_t tmem_acc = tmem_base + buf * BN;
@@ -399,6 +414,7 @@ __global__ void __launch_bounds__(Shape<BN, DEEP, PAIR, EW8>::THREADS, Shape<BN,
                 if (PAIR) tc::mbar_arrive_cluster(tc::mapa_u32(tc::smem_u32(&acc_full[buf]), 1));
             }
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;   // lane 0's verdict; keeps the warp's tile loops in step
+          }
         }
     } else {
         // ------------------------------------------------------------ epilogue (warps 2..5)
@@ -417,10 +433,11 @@ __global__ void __launch_bounds__(Shape<BN, DEEP, PAIR, EW8>::THREADS, Shape<BN,
         const int l4 = lane & 3, rsub = lane >> 2;   // store phase: 4 lanes per row (64 bytes), 8 rows per instruction
         bool ok = true;
         int tl = 0;
-        for (;; ++tl) {
-            int t = lane == 0 && ok ? read_tile(tl) : -1;
-            t = __shfl_sync(0xffffffffu, t, 0);
-            if (t < 0) break;
+        for (int ci = 0; ok; ++ci) {
+            int t0 = lane == 0 ? read_tile(ci) : -1;
+            t0 = __shfl_sync(0xffffffffu, t0, 0);
+            if (t0 < 0) break;
+          for (int t = t0; t < t0 + batch && t < total_tiles; ++t, ++tl) {
             const Tile x = locate(t);
             const int buf = tl & 1;
             const uint32_t tmem_acc = tmem_base + buf * BN;
@@ -663,6 +680,7 @@ __global__ void __launch_bounds__(Shape<BN, DEEP, PAIR, EW8>::THREADS, Shape<BN,
                     __syncwarp();   // every lane is done with the staging rows before the next pass overwrites them
                 }
             }
+          }
         }
     }
     // ---- teardown: everyone meets, then the allocating warp frees TMEM
@@ -725,7 +743,7 @@ bool supported(const Args& a) {
 }
 
 template <int BN, bool DEEP, bool PAIR = false, bool EW8 = false>
-static int launch_shape(asca_ctx* ctx, const Args& a, int64_t grid) {
+static int launch_shape(asca_ctx* ctx, const Args& a, int64_t grid, int64_t tiles_est) {
     CUtensorMap mapA, mapB;
     bool ok;
     if (a.mode == ASCA_TN) ok = make_map(&mapA, a.A, a.a_rows, a.a_cols, a.lda, 64, 64);
@@ -760,13 +778,18 @@ static int launch_shape(asca_ctx* ctx, const Args& a, int64_t grid) {
                 p.dyn_reset = ctrs + ((seq + 1) & 1) * 32;
                 p.dyn_ring = reinterpret_cast<unsigned long long*>(static_cast<char*>(ctx->dyn_buf) + RING_OFF);
                 p.dyn_seq = seq;
+                // One tile per claim. Several consecutive tiles per claim were measured (8 where a walker has > 128 tiles):
+                // the train step went from 335.9 to 355.4 ms -- neighbouring walkers no longer work on neighbouring tiles
+                // at the same time, which is what lets them share operand tiles in L2.
+                (void)tiles_est;
+                p.dyn_batch = 1;
             }
         }
     }
     using SH = Shape<BN, DEEP, PAIR, EW8>;
-    const size_t smem = SH::SMEM_FIXED + (size_t)((a.group_dim == GROUP_NONE ? 1 : a.n_groups) + 2) * 4;
+    const size_t smem = SH::SMEM_FIXED + (size_t)(2 * (a.group_dim == GROUP_NONE ? 1 : a.n_groups) + 4) * 4;   // tile table + group offsets
     auto go = [&](auto kern) -> cudaError_t {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(SH::SMEM_FIXED + (MAX_GROUPS + 2) * 4));
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(SH::SMEM_FIXED + (2 * MAX_GROUPS + 4) * 4));
         if (e != cudaSuccess) return e;
         if (!PAIR) return asca_launch(ctx, kern, dim3((unsigned)grid), dim3(SH::THREADS), smem, mapA, mapB, p);
         // pairs of CTAs: a cluster of two per walker (grid = 2 x walkers)
@@ -848,15 +871,15 @@ int launch(asca_ctx* ctx, const Args& a) {
     // pairs (both operands K-major: the widest TMA boxes); every other dense form is faster on pairs
     if (pair_wanted(ctx, a) && !(wide_ok && a.mode == ASCA_NT && a.epi != EPI_QKV)) {
         const int64_t g2 = 2 * std::min<int64_t>(pairs, n_sm / 2);
-        if (a.group_dim == GROUP_M || a.epi == EPI_QKV) return launch_shape<256, false, true, true>(ctx, a, g2);
-        return launch_shape<256, false, true, false>(ctx, a, g2);
+        if (a.group_dim == GROUP_M || a.epi == EPI_QKV) return launch_shape<256, false, true, true>(ctx, a, g2, pairs);
+        return launch_shape<256, false, true, false>(ctx, a, g2, pairs);
     }
     if (wide_ok)
-        return launch_shape<256, false>(ctx, a, std::min<int64_t>(wide, n_sm));
+        return launch_shape<256, false>(ctx, a, std::min<int64_t>(wide, n_sm), wide);
     const int64_t grid = tile_bound(a, 128);
     if (grid <= 0) return ASCA_OK;
-    if (grid <= n_sm) return launch_shape<128, true>(ctx, a, grid);
-    return launch_shape<128, false>(ctx, a, std::min<int64_t>(grid, 2 * n_sm));
+    if (grid <= n_sm) return launch_shape<128, true>(ctx, a, grid, grid);
+    return launch_shape<128, false>(ctx, a, std::min<int64_t>(grid, 2 * n_sm), grid);
 }
 
 static bool pair_wanted(asca_ctx* ctx, const Args& a) {
