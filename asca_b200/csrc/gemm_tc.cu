@@ -96,6 +96,11 @@ struct KP {
     int dyn_batch;                     // consecutive tiles per claim (short tiles: one claim's latency per several tiles)
     int* err_word;
 };
+// 32-column accumulator loads issued per wait in the epilogue. 4 (128 registers) was measured on the four-warp shapes:
+// no gain (expert weight-gradient products at 512 rows per expert 1.09 against 1.05 ms, train step 335.6 against 334.4 ms).
+#ifndef ASCA_EPI_LG
+#define ASCA_EPI_LG 1
+#endif
 constexpr int DYN_Q = 16;              // claims a walker's producer can be ahead of its slowest role, with room to spare
 
 // bf16 mode only (2e-2 tolerance; the results are rounded to bf16 or multiply bf16 products): fast exp and divide.
@@ -525,16 +530,36 @@ __global__ void __launch_bounds__(Shape<BN, DEEP, PAIR, EW8>::THREADS, Shape<BN,
                 lrs[i] = (int64_t)x.row_base_m + x.m0 + (rr < rows_here ? q * 32 + rr : 0);
                 crs[i] = p.c_idx && rr < rows_here ? (int64_t)p.c_idx[lrs[i]] : lrs[i];
             }
+            // LG 32-column loads are issued together and waited for once: a tcgen05.ld queues behind the MMAs the issuer
+            // has in flight for the next tile, and one wait per load pays that queue once per 32 columns.
+            constexpr int LG = (SH::CTAS_PER_SM == 2 || EW8) ? 1 : ASCA_EPI_LG;   // (two CTAs per SM, or 320 threads: no room for 128 more registers)
+            static_assert(C_PER_WARP % LG == 0, "epilogue load groups");
 #pragma unroll 1
-            for (int c = c_lo; c < c_lo + C_PER_WARP; ++c) {
-                uint32_t r[32];
+            for (int cg = c_lo; cg < c_lo + C_PER_WARP; cg += LG) {
+                uint32_t rr[LG][32];
                 if (x.num_k > 0) {
-                    tc::tmem_ld_32x32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
+#pragma unroll
+                    for (int g = 0; g < LG; ++g)
+                        tc::tmem_ld_32x32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)((cg + g) * 32), rr[g]);
                     tc::tmem_ld_wait();
                 } else {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) r[j] = 0u;
+                    for (int g = 0; g < LG; ++g)
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) rr[g][j] = 0u;
                 }
+                if (cg + LG == c_lo + C_PER_WARP) {   // this warp's share of the buffer is free for the tile after next
+                    tc::tcgen05_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (PAIR) tc::mbar_arrive_cluster(tc::mapa_u32(tc::smem_u32(&acc_empty[buf]), 0));   // counted by the even CTA
+                        else tc::mbar_arrive(&acc_empty[buf]);
+                    }
+                }
+#pragma unroll
+              for (int g = 0; g < LG; ++g) {
+                const int c = cg + g;
+                uint32_t(&r)[32] = rr[g];
                 if (ce) {    // dlogits = (softmax - onehot) * scale
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
@@ -552,14 +577,6 @@ __global__ void __launch_bounds__(Shape<BN, DEEP, PAIR, EW8>::THREADS, Shape<BN,
                         r[4 * j + 1] = __float_as_uint((__uint_as_float(r[4 * j + 1]) + b4.y) * qkv_scale);
                         r[4 * j + 2] = __float_as_uint((__uint_as_float(r[4 * j + 2]) + b4.z) * qkv_scale);
                         r[4 * j + 3] = __float_as_uint((__uint_as_float(r[4 * j + 3]) + b4.w) * qkv_scale);
-                    }
-                }
-                if (c == c_lo + C_PER_WARP - 1) {   // this warp's share of the buffer is free for the tile after next
-                    tc::tcgen05_fence_before();
-                    __syncwarp();
-                    if (lane == 0) {
-                        if (PAIR) tc::mbar_arrive_cluster(tc::mapa_u32(tc::smem_u32(&acc_empty[buf]), 0));   // counted by the even CTA
-                        else tc::mbar_arrive(&acc_empty[buf]);
                     }
                 }
 #pragma unroll
@@ -679,6 +696,7 @@ __global__ void __launch_bounds__(Shape<BN, DEEP, PAIR, EW8>::THREADS, Shape<BN,
                     }
                     __syncwarp();   // every lane is done with the staging rows before the next pass overwrites them
                 }
+              }
             }
           }
         }

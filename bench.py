@@ -819,9 +819,10 @@ def run_case(hs: Harness, args):
         c = torch.empty(m_, n_, **f32)
         fn = lambda: ops.gemm(hs.gpu, a, b, mode, out=c)  # noqa: E731
         work, unit = 2.0 * m_ * n_ * k_, "TFLOP/s"
-    elif name in ("moe_fwd", "moe_bwd"):
-        # the expert FFN of the training configuration on one micro-batch of 2 sequences (8192 uniform random bytes)
-        n, d, F, E = 8192, 2048, 4096, 64
+    elif name in ("moe_fwd", "moe_bwd", "moe_bwd_8seq"):
+        # the expert FFN of the training configuration on one micro-batch of 2 sequences (8192 uniform random bytes);
+        # moe_bwd_8seq: 8 sequences, a rank's micro-batch in an 8-GPU run (512 rows per expert)
+        n, d, F, E = 32768 if name == "moe_bwd_8seq" else 8192, 2048, 4096, 64
         ids = torch.from_numpy(reference_ids(5, n).view(np.int32)).to(dev)
         xn = torch.randn(n, d, generator=g, **f32).bfloat16()
         w1 = (torch.randn(d, E * F, generator=g, **f32) * 0.02).bfloat16()
@@ -992,7 +993,7 @@ def main():
     ap.add_argument("--only", default="", help="comma-separated subset of train,decode,moe,delta")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline legs")
     ap.add_argument("--case", default="", help="run one small single-kernel case instead (for profiler captures): gemm_dense, "
-                                               "gemm_dense_nt, gemm_dense_tn, moe_fwd, moe_bwd, delta_bf16, delta_bf16_dh64, delta_f32, decode, rmsnorm, rmsnorm_bwd, "
+                                               "gemm_dense_nt, gemm_dense_tn, moe_fwd, moe_bwd, moe_bwd_8seq, delta_bf16, delta_bf16_dh64, delta_f32, decode, rmsnorm, rmsnorm_bwd, "
                                                "residual_rmsnorm, adamw, gather, dispatch, delta_step")
     args = ap.parse_args()
     if args.impl == "reference":
