@@ -130,9 +130,67 @@ struct asca_dp {
     cudaEvent_t t_bwd_end = nullptr, t_comm_end = nullptr, t_adam_start = nullptr, t_adam_end = nullptr, t_ag_end = nullptr;
     bool have_step = false;
     float last_exposed_gather_ms = 0.0f;
+    // Copy-engine transport for the sharded tensors (asca_model_dp_peer_export / _open): the peers' staging, flag and bf16
+    // weight buffers mapped through CUDA IPC. A gradient chunk travels as one cudaMemcpyAsync per peer into that peer's
+    // staging slot for this rank, followed by a flag (the step number) written into the peer's flag array; the owner of
+    // the chunk waits for the flags of all peers (a bounded poll) and sums the slots in rank order. Updated bf16 chunks
+    // travel the same way straight into the peers' weight copies. No SM is held while bytes move.
+    bool ce = false;
+    bool ce_gather = false;                  // the bf16 all-gather on the copy engines too (ASCA_DP_CE_GATHER=1); default: NCCL
+    float* stage = nullptr;                  // [(nranks - 1) sources][stage_per_src] incoming gradient chunks
+    int* flags = nullptr;                    // [2 kinds][big tensors][nranks]: last step whose chunk from that rank has landed
+    std::vector<float*> peer_stage;
+    std::vector<int*> peer_flags;
+    std::vector<__nv_bfloat16*> peer_p16;
+    std::vector<int64_t> stage_off;          // offset (floats) of big tensor i inside one source's staging area
+    int64_t stage_per_src = 0;
+    static constexpr int N_PUSH = 8;         // copies in flight at once (a single copy does not fill the NVLink ports)
+    cudaStream_t push[N_PUSH] = {};
+    cudaEvent_t push_ev[N_PUSH] = {}, piece_ev[N_PUSH] = {};
+    bool push_open = false;                  // copies queued that the next writer of their sources has not yet waited for
+    int step_no = 0;
 };
 
 namespace {
+
+// ---- copy-engine transport: the three small kernels
+// Peer store of a landed-chunk flag; runs on the stream that carried the chunk, after it.
+__global__ void ce_flag_kernel(int* flag, int step) {
+    __threadfence_system();
+    *reinterpret_cast<volatile int*>(flag) = step;
+    __threadfence_system();
+}
+// Waits until every peer's flag for tensor `t` has reached `step` (lane = rank). Bounded: gives up after `limit` cycles and
+// raises the error word; the kernels behind it then run on whatever has landed and the host sees ASCA_ERR_DEVICE.
+__global__ void ce_wait_kernel(const int* flags, int nranks, int self, int step, long long limit, int* err_word) {
+    const int r = threadIdx.x;
+    if (r >= nranks || r == self) return;
+    const volatile int* f = flags + r;
+    const long long t0 = clock64();
+    while (*f < step) {
+        if (clock64() - t0 > limit) {
+            atomicExch(err_word, 401);
+            break;
+        }
+        __nanosleep(500);
+    }
+    __threadfence_system();
+}
+// own[i] = (sum over ranks, in rank order, of that rank's chunk) * scale; the peers' chunks sit in the staging slots.
+__global__ void __launch_bounds__(256) ce_reduce_kernel(float* __restrict__ own, const float* __restrict__ stage, int64_t stage_per_src,
+                                                        int64_t n4, int nranks, int self, float scale) {
+    const int64_t stride = (int64_t)gridDim.x * 256;
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n4; i += stride) {
+        float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (int r = 0; r < nranks; ++r) {
+            const float4 v = r == self ? reinterpret_cast<const float4*>(own)[i]
+                                       : reinterpret_cast<const float4*>(stage + (int64_t)(r < self ? r : r - 1) * stage_per_src)[i];
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        reinterpret_cast<float4*>(own)[i] = make_float4(acc.x * scale, acc.y * scale, acc.z * scale, acc.w * scale);
+    }
+}
+constexpr long long CE_WAIT_CYCLES = 40000000000ll;   // about 20 s: ranks may be seconds apart in their first step
 
 int side_after_compute(asca_ctx* ctx, asca_comm* c) {
     ASCA_CUDA(ctx, cudaEventRecord(c->ev, ctx->stream));
@@ -142,6 +200,64 @@ int side_after_compute(asca_ctx* ctx, asca_comm* c) {
 int compute_after_side(asca_ctx* ctx, asca_comm* c) {
     ASCA_CUDA(ctx, cudaEventRecord(c->ev, c->side));
     ASCA_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, c->ev, 0));
+    return ASCA_OK;
+}
+
+// The push streams start after whatever the context's stream has queued so far.
+int push_after_compute(asca_ctx* ctx, asca_dp* dp) {
+    ASCA_CUDA(ctx, cudaEventRecord(dp->comm->ev, ctx->stream));
+    for (int i = 0; i < asca_dp::N_PUSH; ++i) ASCA_CUDA(ctx, cudaStreamWaitEvent(dp->push[i], dp->comm->ev, 0));
+    return ASCA_OK;
+}
+// The context's stream waits for every copy the push streams hold (before the copies' sources are written again).
+int compute_after_push(asca_ctx* ctx, asca_dp* dp) {
+    if (!dp->push_open) return ASCA_OK;
+    for (int i = 0; i < asca_dp::N_PUSH; ++i) {
+        ASCA_CUDA(ctx, cudaEventRecord(dp->push_ev[i], dp->push[i]));
+        ASCA_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, dp->push_ev[i], 0));
+    }
+    dp->push_open = false;
+    return ASCA_OK;
+}
+// This rank's chunk-for-p of sharded tensor `bi` to every peer p (kind 0: f32 gradient chunk p into p's staging slot for
+// this rank; kind 1: this rank's updated bf16 chunk into p's weight copy), each followed by the landed-chunk flag.
+int ce_push(asca_ctx* ctx, asca_model* m, asca_dp* dp, int bi, int kind) {
+    const asca_dp::Big& b = dp->big[bi];
+    const int N = dp->comm->nranks, me = dp->comm->rank;
+    const int64_t chunk = b.n / N;
+    const int step = dp->step_no + 1;
+    // a peer's chunk goes as `pieces` copies on different streams, so that about N_PUSH copies are in flight whatever N is
+    const int pieces = std::max(1, asca_dp::N_PUSH / (N - 1));
+    const size_t esz = kind == 0 ? 4 : 2;
+    for (int k = 1; k < N; ++k) {
+        const int p = (me + k) % N;
+        char* dst = kind == 0 ? reinterpret_cast<char*>(dp->peer_stage[p] + (int64_t)(me < p ? me : me - 1) * dp->stage_per_src + dp->stage_off[bi])
+                              : reinterpret_cast<char*>(dp->peer_p16[p] + b.off + me * chunk);
+        const char* src = kind == 0 ? reinterpret_cast<const char*>(m->grads + b.off + p * chunk)
+                                    : reinterpret_cast<const char*>(m->params16 + b.off + me * chunk);
+        const size_t bytes = (size_t)chunk * esz, piece = ((bytes / pieces) + 255) & ~(size_t)255;
+        const int s0 = ((k - 1) * pieces) % asca_dp::N_PUSH;
+        for (int j = 0; j < pieces; ++j) {
+            const size_t lo = (size_t)j * piece, n = lo < bytes ? std::min(piece, bytes - lo) : 0;
+            const int sj = (s0 + j) % asca_dp::N_PUSH;
+            if (n) ASCA_CUDA(ctx, cudaMemcpyAsync(dst + lo, src + lo, n, cudaMemcpyDefault, dp->push[sj]));
+            if (j > 0) {   // the flag's stream learns of the other pieces
+                ASCA_CUDA(ctx, cudaEventRecord(dp->piece_ev[sj], dp->push[sj]));
+                ASCA_CUDA(ctx, cudaStreamWaitEvent(dp->push[s0], dp->piece_ev[sj], 0));
+            }
+        }
+        ce_flag_kernel<<<1, 1, 0, dp->push[s0]>>>(dp->peer_flags[p] + ((size_t)kind * dp->big.size() + bi) * N + me, step);
+        ASCA_CUDA(ctx, cudaGetLastError());
+    }
+    dp->push_open = true;
+    return ASCA_OK;
+}
+// On the side stream: wait for every peer's chunk of tensor `bi` (kind as above).
+int ce_wait(asca_ctx* ctx, asca_dp* dp, int bi, int kind) {
+    const int N = dp->comm->nranks;
+    ce_wait_kernel<<<1, 32 * ((N + 31) / 32), 0, dp->comm->side>>>(dp->flags + ((size_t)kind * dp->big.size() + bi) * N, N, dp->comm->rank,
+                                                                   dp->step_no + 1, CE_WAIT_CYCLES, ctx->err_word);
+    ASCA_CUDA(ctx, cudaGetLastError());
     return ASCA_OK;
 }
 
@@ -375,6 +491,86 @@ int asca_model_dp_attach(asca_ctx* ctx, asca_model* m, asca_comm* comm, int shar
     return ASCA_OK;
 }
 
+int asca_model_dp_peer_export(asca_ctx* ctx, asca_model* m, void* blob256) {
+    if (!ctx || !m || !blob256) return ASCA_ERR_ARG;
+    ASCA_REQUIRE(ctx, m->dp && m->dp->sharded && m->dp->comm->nranks > 1 && !m->dp->big.empty(),
+                 "model_dp_peer_export: needs the sharded optimizer on more than one rank");
+    asca_dp* dp = m->dp;
+    const int N = dp->comm->nranks;
+    cudaSetDevice(ctx->device);
+    if (!dp->stage) {
+        dp->stage_off.clear();
+        dp->stage_per_src = 0;
+        for (const asca_dp::Big& b : dp->big) {
+            dp->stage_off.push_back(dp->stage_per_src);
+            dp->stage_per_src += b.n / N;
+        }
+        const size_t n_flags = 2 * dp->big.size() * (size_t)N;
+        if (cudaMalloc((void**)&dp->stage, (size_t)(N - 1) * dp->stage_per_src * 4) != cudaSuccess ||
+            cudaMalloc((void**)&dp->flags, n_flags * 4) != cudaSuccess)
+            return asca_fail(ctx, ASCA_ERR_OOM, "model_dp_peer_export: cannot allocate the staging area (%.1f GB)",
+                             (double)(N - 1) * dp->stage_per_src * 4 / 1e9);
+        ASCA_CUDA(ctx, cudaMemset(dp->flags, 0, n_flags * 4));
+    }
+    {
+        void* p16 = nullptr;   // the bf16 copy must exist before its handle does
+        ASCA_TRY(asca_model_params16(ctx, m, &p16, nullptr));
+    }
+    char* out = static_cast<char*>(blob256);
+    memset(out, 0, 256);
+    cudaIpcMemHandle_t h;
+    ASCA_CUDA(ctx, cudaIpcGetMemHandle(&h, dp->stage));
+    memcpy(out, &h, sizeof h);
+    ASCA_CUDA(ctx, cudaIpcGetMemHandle(&h, dp->flags));
+    memcpy(out + 64, &h, sizeof h);
+    ASCA_CUDA(ctx, cudaIpcGetMemHandle(&h, m->params16));
+    memcpy(out + 128, &h, sizeof h);
+    const int64_t sps = dp->stage_per_src;
+    memcpy(out + 192, &sps, 8);
+    return ASCA_OK;
+}
+
+int asca_model_dp_peer_open(asca_ctx* ctx, asca_model* m, const void* blobs, int nranks) {
+    if (!ctx || !m || !blobs) return ASCA_ERR_ARG;
+    ASCA_REQUIRE(ctx, m->dp && m->dp->stage && nranks == m->dp->comm->nranks, "model_dp_peer_open: export first, and pass one blob per rank");
+    asca_dp* dp = m->dp;
+    const int N = nranks, me = dp->comm->rank;
+    cudaSetDevice(ctx->device);
+    dp->peer_stage.assign(N, nullptr);
+    dp->peer_flags.assign(N, nullptr);
+    dp->peer_p16.assign(N, nullptr);
+    const char* in = static_cast<const char*>(blobs);
+    for (int p = 0; p < N; ++p) {
+        if (p == me) continue;
+        const char* b = in + (size_t)p * 256;
+        int64_t sps = 0;
+        memcpy(&sps, b + 192, 8);
+        ASCA_REQUIRE(ctx, sps == dp->stage_per_src, "model_dp_peer_open: rank %d was built for another model or world size", p);
+        cudaIpcMemHandle_t h;
+        void* ptr = nullptr;
+        memcpy(&h, b, sizeof h);
+        ASCA_CUDA(ctx, cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess));
+        dp->peer_stage[p] = static_cast<float*>(ptr);
+        memcpy(&h, b + 64, sizeof h);
+        ASCA_CUDA(ctx, cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess));
+        dp->peer_flags[p] = static_cast<int*>(ptr);
+        memcpy(&h, b + 128, sizeof h);
+        ASCA_CUDA(ctx, cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess));
+        dp->peer_p16[p] = static_cast<__nv_bfloat16*>(ptr);
+    }
+    for (int i = 0; i < asca_dp::N_PUSH; ++i) {
+        ASCA_CUDA(ctx, cudaStreamCreateWithFlags(&dp->push[i], cudaStreamNonBlocking));
+        ASCA_CUDA(ctx, cudaEventCreateWithFlags(&dp->push_ev[i], cudaEventDisableTiming));
+        ASCA_CUDA(ctx, cudaEventCreateWithFlags(&dp->piece_ev[i], cudaEventDisableTiming));
+    }
+    dp->ce = true;
+    {
+        const char* e = getenv("ASCA_DP_CE_GATHER");
+        dp->ce_gather = e && e[0] == '1';
+    }
+    return ASCA_OK;
+}
+
 int asca_model_dp_arm(asca_model* m, int on) {
     if (!m || !m->dp) return ASCA_ERR_ARG;
     m->dp->armed = on != 0;
@@ -387,6 +583,7 @@ int asca_model_dp_step(asca_ctx* ctx, asca_model* m, float lr, float beta1, floa
     asca_dp* dp = m->dp;
     asca_comm* c = dp->comm;
     ASCA_TRY(asca_dp_wait_all(ctx, m));   // a gather of the previous step nobody waited for
+    if (dp->ce) ASCA_TRY(compute_after_push(ctx, dp));   // this rank's chunks have left: the update may rewrite their sources
     // wait for the exchanges queued by the backward
     ASCA_CUDA(ctx, cudaEventRecord(dp->t_bwd_end, ctx->stream));
     ASCA_CUDA(ctx, cudaEventRecord(dp->t_comm_end, c->side));
@@ -421,10 +618,18 @@ int asca_model_dp_step(asca_ctx* ctx, asca_model* m, float lr, float beta1, floa
         if (g.big >= 0) {
             const asca_dp::Big& b = dp->big[g.big];
             const int64_t chunk = b.n / c->nranks;
-            ASCA_TRY(side_after_compute(ctx, c));
-            ASCA_NCCL(ctx, nc->AllGather(m->params16 + b.off + c->rank * chunk, m->params16 + b.off, (size_t)chunk, NCCL_BFLOAT16,
-                                         c->comm, c->side));
             const bool last_of_layer = (size_t)g.big + 1 == dp->big.size() || dp->big[g.big + 1].layer != b.layer;
+            if (dp->ce && dp->ce_gather) {
+                ASCA_TRY(push_after_compute(ctx, dp));
+                ASCA_TRY(ce_push(ctx, m, dp, g.big, 1));
+                if (last_of_layer)   // the block's chunks of every peer have landed in this rank's copy
+                    for (int bj = 0; bj <= g.big; ++bj)
+                        if (dp->big[bj].layer == b.layer) ASCA_TRY(ce_wait(ctx, dp, bj, 1));
+            } else {
+                ASCA_TRY(side_after_compute(ctx, c));
+                ASCA_NCCL(ctx, nc->AllGather(m->params16 + b.off + c->rank * chunk, m->params16 + b.off, (size_t)chunk, NCCL_BFLOAT16,
+                                             c->comm, c->side));
+            }
             if (last_of_layer) {
                 ASCA_CUDA(ctx, cudaEventRecord(dp->ag_done[b.layer], c->side));
                 dp->ag_pending[b.layer] = 1;
@@ -435,6 +640,7 @@ int asca_model_dp_step(asca_ctx* ctx, asca_model* m, float lr, float beta1, floa
     ASCA_CUDA(ctx, cudaEventRecord(dp->t_ag_end, c->side));
     m->master_stale = true;
     dp->have_step = true;
+    ++dp->step_no;
     return ASCA_OK;
 }
 
@@ -493,6 +699,26 @@ int asca_dp_grad_ready(asca_ctx* ctx, asca_model* m, int64_t off, int64_t cnt) {
     Nccl* nc = nccl();
     ASCA_TRY(side_after_compute(ctx, c));
     float* g = m->grads;
+    if (dp->ce) {   // the sharded tensors inside the range travel on the copy engines
+        bool any = false;
+        for (size_t bi = 0; bi < dp->big.size(); ++bi) {
+            const asca_dp::Big& b = dp->big[bi];
+            if (b.off < off || b.off + b.n > off + cnt) continue;
+            if (!any) ASCA_TRY(push_after_compute(ctx, dp));
+            any = true;
+            ASCA_TRY(ce_push(ctx, m, dp, (int)bi, 0));
+        }
+        for (size_t bi = 0; bi < dp->big.size(); ++bi) {
+            const asca_dp::Big& b = dp->big[bi];
+            if (b.off < off || b.off + b.n > off + cnt) continue;
+            const int64_t chunk = b.n / c->nranks;
+            ASCA_TRY(ce_wait(ctx, dp, (int)bi, 0));
+            ce_reduce_kernel<<<(unsigned)std::min<int64_t>((chunk / 4 + 255) / 256, 148 * 8), 256, 0, c->side>>>(
+                g + b.off + c->rank * chunk, dp->stage + dp->stage_off[bi], dp->stage_per_src, chunk / 4, c->nranks, c->rank,
+                1.0f / (float)c->nranks);
+            ASCA_CUDA(ctx, cudaGetLastError());
+        }
+    }
     ASCA_NCCL(ctx, nc->GroupStart());
     int64_t pos = off;
     const int64_t end = off + cnt;
@@ -500,7 +726,8 @@ int asca_dp_grad_ready(asca_ctx* ctx, asca_model* m, int64_t off, int64_t cnt) {
         if (b.off < off || b.off + b.n > end) continue;
         if (b.off > pos) ASCA_NCCL(ctx, nc->AllReduce(g + pos, g + pos, (size_t)(b.off - pos), NCCL_FLOAT32, NCCL_AVG, c->comm, c->side));
         const int64_t chunk = b.n / c->nranks;
-        ASCA_NCCL(ctx, nc->ReduceScatter(g + b.off, g + b.off + c->rank * chunk, (size_t)chunk, NCCL_FLOAT32, NCCL_AVG, c->comm, c->side));
+        if (!dp->ce)
+            ASCA_NCCL(ctx, nc->ReduceScatter(g + b.off, g + b.off + c->rank * chunk, (size_t)chunk, NCCL_FLOAT32, NCCL_AVG, c->comm, c->side));
         pos = b.off + b.n;
     }
     if (pos < end) ASCA_NCCL(ctx, nc->AllReduce(g + pos, g + pos, (size_t)(end - pos), NCCL_FLOAT32, NCCL_AVG, c->comm, c->side));
@@ -511,6 +738,7 @@ int asca_dp_grad_ready(asca_ctx* ctx, asca_model* m, int64_t off, int64_t cnt) {
 
 int asca_dp_before_expert_weights(asca_ctx* ctx, asca_model* m, int64_t layer) {
     asca_dp* dp = m->dp;
+    if (dp && dp->ce) ASCA_TRY(compute_after_push(ctx, dp));   // before this step's backward rewrites the gradient buffer
     if (!dp || dp->ag_pending.empty() || !dp->ag_pending[layer]) return ASCA_OK;
     ASCA_CUDA(ctx, cudaEventRecord(dp->fwd_reach[layer], ctx->stream));
     ASCA_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, dp->ag_done[layer], 0));
@@ -534,11 +762,27 @@ int asca_dp_wait_all(asca_ctx* ctx, asca_model* m) {
 void asca_dp_free(asca_model* m) {
     asca_dp* dp = m->dp;
     if (!dp) return;
+    // Everything this rank queued has run: in particular its polls for the peers' chunks, so no peer copy into this
+    // rank's buffers is still on its way when they are freed below (a peer frees only after the same waits on its side).
+    if (dp->comm && dp->comm->side) cudaStreamSynchronize(dp->comm->side);
     for (cudaEvent_t e : dp->ag_done) cudaEventDestroy(e);
     for (cudaEvent_t e : dp->ag_waited) cudaEventDestroy(e);
     for (cudaEvent_t e : dp->fwd_reach) cudaEventDestroy(e);
     for (cudaEvent_t e : {dp->t_bwd_end, dp->t_comm_end, dp->t_adam_start, dp->t_adam_end, dp->t_ag_end})
         if (e) cudaEventDestroy(e);
+    for (int i = 0; i < asca_dp::N_PUSH; ++i) {
+        if (dp->push[i]) {
+            cudaStreamSynchronize(dp->push[i]);
+            cudaStreamDestroy(dp->push[i]);
+        }
+        if (dp->push_ev[i]) cudaEventDestroy(dp->push_ev[i]);
+        if (dp->piece_ev[i]) cudaEventDestroy(dp->piece_ev[i]);
+    }
+    for (float* p : dp->peer_stage) if (p) cudaIpcCloseMemHandle(p);
+    for (int* p : dp->peer_flags) if (p) cudaIpcCloseMemHandle(p);
+    for (__nv_bfloat16* p : dp->peer_p16) if (p) cudaIpcCloseMemHandle(p);
+    if (dp->stage) cudaFree(dp->stage);
+    if (dp->flags) cudaFree(dp->flags);
     delete dp;
     m->dp = nullptr;
 }

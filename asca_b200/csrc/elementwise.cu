@@ -253,12 +253,12 @@ __global__ void __launch_bounds__(256) adamw_kernel(float* __restrict__ p, const
 
 // One launch over a flat buffer of n_seg tensors with per-tensor lr_t / eps_t
 // (the counter advances per tensor, rust/src/tensor.rs:393).
-__global__ void __launch_bounds__(256) adamw_seg_kernel(float* __restrict__ p, const float* __restrict__ g,
-                                                        float* __restrict__ m, float* __restrict__ v,
-                                                        const int64_t* __restrict__ seg_off,
-                                                        const float* __restrict__ lr_t,
-                                                        const float* __restrict__ eps_t, int n_seg, float b1,
-                                                        float b2, float wd, __nv_bfloat16* __restrict__ p16) {
+__device__ __forceinline__ void adamw_seg_body(float* __restrict__ p, const float* __restrict__ g,
+                                               float* __restrict__ m, float* __restrict__ v,
+                                               const int64_t* __restrict__ seg_off,
+                                               const float* __restrict__ lr_t,
+                                               const float* __restrict__ eps_t, int n_seg, float b1,
+                                               float b2, float wd, __nv_bfloat16* __restrict__ p16) {
     const int64_t n = seg_off[n_seg];
     const int64_t stride = (int64_t)gridDim.x * blockDim.x * 4;
     const bool vec_ok = ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(m) |
@@ -300,6 +300,26 @@ __global__ void __launch_bounds__(256) adamw_seg_kernel(float* __restrict__ p, c
             if (p16) p16[j] = __float2bfloat16(p[j]);
         }
     }
+}
+__global__ void __launch_bounds__(256) adamw_seg_kernel(float* __restrict__ p, const float* __restrict__ g,
+                                                        float* __restrict__ m, float* __restrict__ v,
+                                                        const int64_t* __restrict__ seg_off,
+                                                        const float* __restrict__ lr_t,
+                                                        const float* __restrict__ eps_t, int n_seg, float b1,
+                                                        float b2, float wd, __nv_bfloat16* __restrict__ p16) {
+    adamw_seg_body(p, g, m, v, seg_off, lr_t, eps_t, n_seg, b1, b2, wd, p16);
+}
+// The same with the segment table passed by value (up to 32 tensors): no host-to-device copy in front of the launch. A
+// copy would queue on a copy engine, behind whatever long peer-to-peer transfers the data-parallel exchange has in flight.
+struct AdamSegTab {
+    int64_t off[33];
+    float lr[32], eps[32];
+};
+__global__ void __launch_bounds__(256) adamw_seg_tab_kernel(float* __restrict__ p, const float* __restrict__ g,
+                                                            float* __restrict__ m, float* __restrict__ v,
+                                                            const __grid_constant__ AdamSegTab tab, int n_seg, float b1,
+                                                            float b2, float wd, __nv_bfloat16* __restrict__ p16) {
+    adamw_seg_body(p, g, m, v, tab.off, tab.lr, tab.eps, n_seg, b1, b2, wd, p16);
 }
 
 // ------------------------------------------------------------------ delta prologue
@@ -485,6 +505,18 @@ int asca_adamw_segmented_cast(asca_ctx* ctx, float* p, const float* g, float* m,
         ASCA_REQUIRE(ctx, seg_off[i] <= seg_off[i + 1], "adamw_segmented: offsets must be non-decreasing");
     const int64_t n = seg_off[n_seg];
     if (n == 0) return ASCA_OK;
+    int64_t blocks = ceil_div64(n, 1024);
+    const int64_t cap = (int64_t)ctx->sm_count * 16;
+    if (blocks > cap) blocks = cap;
+    if (n_seg <= 32) {   // the table travels with the launch
+        AdamSegTab tab{};
+        for (int i = 0; i <= n_seg; ++i) tab.off[i] = seg_off[i];
+        for (int i = 0; i < n_seg; ++i) tab.lr[i] = lr_t[i], tab.eps[i] = eps_t[i];
+        asca_span sp(ctx, "adamw_seg_kernel", (double)n * (p_bf16 ? 30.0 : 28.0));   // bytes read + written
+        adamw_seg_tab_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(p, g, m, v, tab, n_seg, beta1, beta2, wd_eff, (__nv_bfloat16*)p_bf16);
+        ASCA_CHECK_LAUNCH(ctx);
+        return ASCA_OK;
+    }
     // table -> device scratch: [seg_off (n_seg+1) i64][lr_t n_seg f32][eps_t n_seg f32]
     size_t off_b = (size_t)(n_seg + 1) * 8, f_b = (size_t)n_seg * 4;
     void* ws;
@@ -494,9 +526,6 @@ int asca_adamw_segmented_cast(asca_ctx* ctx, float* p, const float* g, float* m,
     ASCA_CUDA(ctx, cudaMemcpyAsync(w + off_b, lr_t, f_b, cudaMemcpyHostToDevice, ctx->stream));
     ASCA_CUDA(ctx, cudaMemcpyAsync(w + off_b + f_b, eps_t, f_b, cudaMemcpyHostToDevice, ctx->stream));
     // pageable host arrays: the copies above have been staged by the time they return
-    int64_t blocks = ceil_div64(n, 1024);
-    int64_t cap = (int64_t)ctx->sm_count * 16;
-    if (blocks > cap) blocks = cap;
     asca_span sp(ctx, "adamw_seg_kernel", (double)n * (p_bf16 ? 30.0 : 28.0));   // bytes read + written
     adamw_seg_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(p, g, m, v, (const int64_t*)w, (const float*)(w + off_b),
                                                                  (const float*)(w + off_b + f_b), n_seg, beta1, beta2,

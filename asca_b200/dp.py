@@ -209,6 +209,25 @@ class ShardedOverlap(GradOverlap):
 
     sharded = True
 
-    def __init__(self, model, comm: Comm | None = None, group=None):
+    def __init__(self, model, comm: Comm | None = None, group=None, transport: str = "nccl", exchange=None):
+        """transport "ce": the sharded tensors travel on the copy engines through peer memory mapped with CUDA IPC
+        (``asca_model_dp_peer_export`` / ``_open``) instead of NCCL kernels. `exchange` carries one rank's 256-byte
+        blob to all ranks and returns the list in rank order; by default the initialised torch.distributed group does."""
         super().__init__(model, comm, group)
         self.big, self.slices = shard_plan(model.cfg, self.rank, self.world) if self.world > 1 else ([], [(0, model.n)])
+        self.transport = "nccl"
+        if transport == "ce" and self.world > 1 and self.big:
+            g = model.gpu
+            blob = C.create_string_buffer(256)
+            g._call("asca_model_dp_peer_export", g._ctx, model._h, blob)
+            if exchange is None:
+                import torch.distributed as dist
+
+                def exchange(b):
+                    out = [None] * self.world
+                    dist.all_gather_object(out, b, group=group)
+                    return out
+            blobs = exchange(blob.raw)
+            assert len(blobs) == self.world and all(len(b) == 256 for b in blobs)
+            g._call("asca_model_dp_peer_open", g._ctx, model._h, C.create_string_buffer(b"".join(blobs), 256 * self.world), C.c_int(self.world))
+            self.transport = "ce"

@@ -333,7 +333,7 @@ def run_train(hs: Harness, args):
     ids_np, tg_np = ids.numpy().view(np.uint32), tg.numpy().view(np.uint32)
     model.set_grad_scale(1.0 / n_micro)
     comm = dp.Comm.from_torch(hs.gpu)
-    ov = dp.ShardedOverlap(model, comm) if hs.world > 1 else dp.GradOverlap(model, comm)
+    ov = dp.ShardedOverlap(model, comm, transport=args.transport) if hs.world > 1 else dp.GradOverlap(model, comm)
     last = {"loss": float("nan")}
 
     def step():
@@ -990,6 +990,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=4, help="blocks of the 24-block training stack to run (the largest that fits one GPU)")
+    ap.add_argument("--transport", default="nccl", choices=["nccl", "ce"],
+                    help="N > 1: how the sharded expert tensors travel (NCCL kernels, or copy engines through peer memory)")
     ap.add_argument("--only", default="", help="comma-separated subset of train,decode,moe,delta")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline legs")
     ap.add_argument("--case", default="", help="run one small single-kernel case instead (for profiler captures): gemm_dense, "

@@ -487,6 +487,18 @@ int asca_model_dp_timeline(asca_ctx* ctx, asca_model* m, float* ms4);
 int asca_dp_shard_plan(int64_t vocab, int64_t d, int64_t H, int64_t L, int64_t E, int64_t F, int nranks, int rank,
                        int64_t* lo, int64_t* hi, int capacity, int* n_slices, int64_t* big_off, int64_t* big_len,
                        int big_capacity, int* n_big);
+/* Copy-engine transport for the sharded tensors (ranks of one node, one process per GPU; no counterpart in the
+ * reference). After asca_model_dp_attach(..., sharded = 1) every rank calls asca_model_dp_peer_export, which allocates
+ * a staging area for incoming gradient chunks ((nranks - 1) / nranks of the sharded tensors' bytes) and fills 256 bytes
+ * (CUDA IPC handles of the staging area, a flag array and the bf16 weight copy); the caller carries the ranks' blobs to
+ * every rank (rank order) and each calls asca_model_dp_peer_open. From then on a sharded tensor's gradient chunks move
+ * as one cudaMemcpyAsync per peer into that peer's staging slot, each followed by a step-numbered flag in the peer's
+ * flag array; the chunk's owner polls the flags of all peers (bounded: about 20 s, then ASCA_ERR_DEVICE) and sums the
+ * slots in rank order. The updated bf16 chunks go straight into the peers' weight copies the same way. No SM is held
+ * while bytes move (NCCL's collectives keep 24 - 32 CTAs resident); the small tensors stay on NCCL. The mean then differs
+ * from NCCL's in summation order only. Every rank must keep stepping in lock-step and detach together. */
+int asca_model_dp_peer_export(asca_ctx* ctx, asca_model* m, void* blob256);
+int asca_model_dp_peer_open(asca_ctx* ctx, asca_model* m, const void* blobs, int nranks);
 
 /* Decode: n_streams independent streams advance one token each (Model::step,
  * rust/src/model.rs:631-649). state: device f32 (L, n_streams, H, dh, dh), updated in place;

@@ -133,14 +133,29 @@ def _rank_main(rank, world, tmp):
     my_ids, lb = dp.shard_tokens(ids, B, rank, world)
     my_tg, _ = dp.shard_tokens(tg, B, rank, world)
     models = {}
-    for name in ("sharded", "replicated", "blocking"):
+    for name in ("sharded", "replicated", "blocking", "ce"):
         m = asca_b200.Model(gpu, *CFG)
         m.set_params(ref.params)
         m.set_compute(asca_b200.BF16)
         models[name] = m
     ov_s = dp.ShardedOverlap(models["sharded"], comm)
     ov_r = dp.GradOverlap(models["replicated"], comm)
-    out = {"rank": rank}
+
+    def exchange(blob):   # the 256-byte peer blobs travel through files, like the NCCL id
+        (Path(tmp) / f"ce_blob{rank}.tmp").write_bytes(blob)
+        os.replace(Path(tmp) / f"ce_blob{rank}.tmp", Path(tmp) / f"ce_blob{rank}")
+        blobs = []
+        for r in range(world):
+            f = Path(tmp) / f"ce_blob{r}"
+            for _ in range(600):
+                if f.exists():
+                    break
+                time.sleep(0.05)
+            blobs.append(f.read_bytes())
+        return blobs
+
+    ov_c = dp.ShardedOverlap(models["ce"], comm, transport="ce", exchange=exchange)
+    out = {"rank": rank, "ce_transport": ov_c.transport}
     for step in range(3):
         for name, m in models.items():
             m.zero_grads()
@@ -149,6 +164,9 @@ def _rank_main(rank, world, tmp):
                     m.forward_backward(my_ids, my_tg, lb)
             elif name == "replicated":
                 with ov_r:
+                    m.forward_backward(my_ids, my_tg, lb)
+            elif name == "ce":
+                with ov_c:
                     m.forward_backward(my_ids, my_tg, lb)
             else:
                 m.forward_backward(my_ids, my_tg, lb)
@@ -164,10 +182,13 @@ def _rank_main(rank, world, tmp):
             np.save(Path(tmp) / f"grads{rank}.npy", g_b.cpu().numpy())
         ov_s.step(3e-3)
         ov_r.step(3e-3)
+        ov_c.step(3e-3)
         models["blocking"].adamw_step(3e-3)
     w16 = {k: dp.device_tensor_bf16(*m.params16(), rank).view(torch.int16) for k, m in models.items()}
     out["bf16_weights_sharded_equal_replicated"] = bool(torch.equal(w16["sharded"], w16["replicated"]))
     out["bf16_weights_replicated_equal_blocking"] = bool(torch.equal(w16["replicated"], w16["blocking"]))
+    # copy-engine transport: at two ranks the sum of two numbers has one order, so it equals the NCCL path bit for bit
+    out["bf16_weights_ce_equal_sharded"] = bool(torch.equal(w16["ce"], w16["sharded"]))
     try:
         models["sharded"].get()
         out["stale_master_refused"] = False
@@ -204,6 +225,7 @@ def test_two_ranks_overlapped_exchange_and_sharded_optimizer(orc, tmp_path):
         assert o["reduce_scattered_own_slices_equal"], o
         assert o["bf16_weights_sharded_equal_replicated"], o
         assert o["bf16_weights_replicated_equal_blocking"], o
+        assert o["ce_transport"] == "ce" and o["bf16_weights_ce_equal_sharded"], o
         assert o["stale_master_refused"], o
         assert o["master_equal_after_gather"], o
     g0, g1 = np.load(tmp_path / "grads0.npy"), np.load(tmp_path / "grads1.npy")
