@@ -692,7 +692,7 @@ def run_delta(hs: Harness, args, bf16: bool):
     dev_ms, _, clocks, launches = hs.timed(step, steps, 3)
     table = hs.kernel_table(lambda: [step() for _ in range(5)])
     s_io = 2 if bf16 else 4
-    # SURVEY-style algorithmic bytes: q,k,v,o (+ gates) forward; q,k,v,dO in and dq,dk,dv out in the activation dtype
+    # algorithmic bytes: q,k,v,o (+ gates) forward; q,k,v,dO in and dq,dk,dv out in the activation dtype
     # (+ gates and their gradients) backward
     fwd_bytes = 4 * n * d * s_io + 2 * n * h * 4
     bwd_bytes = 7 * n * d * s_io + 6 * n * h * 4
