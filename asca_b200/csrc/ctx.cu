@@ -85,7 +85,20 @@ int asca_ctx_destroy(asca_ctx* ctx) {
 
 int asca_ctx_set_stream(asca_ctx* ctx, void* s) {
     if (!ctx) return ASCA_ERR_ARG;
-    ctx->stream = s ? (cudaStream_t)s : ctx->own_stream;
+    cudaStream_t next = s ? (cudaStream_t)s : ctx->own_stream;
+    if (next != ctx->stream && ctx->stream) {
+        // the context's scratch, caches and tile-claim counters are handed from launch to launch in stream order: what
+        // the old stream still holds runs before anything the new one gets
+        cudaSetDevice(ctx->device);
+        cudaEvent_t e;
+        if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) == cudaSuccess) {
+            // (an old stream its owner has destroyed meanwhile has nothing left to wait for)
+            if (cudaEventRecord(e, ctx->stream) == cudaSuccess) cudaStreamWaitEvent(next, e, 0);
+            cudaEventDestroy(e);
+        }
+        cudaGetLastError();
+    }
+    ctx->stream = next;
     return ASCA_OK;
 }
 

@@ -49,7 +49,8 @@ int asca_ctx_create(int device, asca_ctx** out);
 int asca_ctx_destroy(asca_ctx* ctx);
 /* Use an existing cudaStream_t (e.g. the caller framework's current stream); NULL = the
  * context's own non-blocking stream. To run on CUDA's legacy default stream pass its explicit
- * handle cudaStreamLegacy ((cudaStream_t)0x1), not 0. */
+ * handle cudaStreamLegacy ((cudaStream_t)0x1), not 0. The new stream is made to wait for what the
+ * old one still holds (the context's scratch and counters pass from launch to launch in stream order). */
 int asca_ctx_set_stream(asca_ctx* ctx, void* cuda_stream);
 int asca_ctx_sync(asca_ctx* ctx);
 const char* asca_last_error(const asca_ctx* ctx);
