@@ -915,16 +915,13 @@ int asca_model_create(asca_ctx* ctx, int64_t vocab, int64_t d, int64_t H, int64_
 int asca_model_destroy(asca_ctx* ctx, asca_model* m) {
     if (!m) return ASCA_OK;
     if (ctx) cudaStreamSynchronize(ctx->stream);
+    if (m->dp) asca_dp_free(m);   // before the buffers its copies and collectives touch
     for (float* b : {m->params, m->grads, m->m, m->v})
         if (b) cudaFree(b);
     if (m->params16) cudaFree(m->params16);
     if (m->dec_w) cudaFree(m->dec_w);
     if (m->dec_b) cudaFree(m->dec_b);
     if (m->dec_pk) cudaFree(m->dec_pk);
-    if (m->dp) {
-        cudaStreamSynchronize(ctx ? ctx->stream : nullptr);
-        asca_dp_free(m);
-    }
     delete m;
     return ASCA_OK;
 }
