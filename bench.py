@@ -3,7 +3,9 @@
 isolated ops, each with its roofline, beside the reference's CPU path timed on the host cores of the same box.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--only train,decode,moe,delta]
-    python bench.py --case gemm_dense|gemm_dense_nt|gemm_dense_tn|moe_fwd|moe_bwd|delta_bf16|delta_bf16_dh64|delta_f32|decode   (profiler captures)
+                    [--transport nccl|ce]   (N > 1: the sharded expert tensors on NCCL kernels, the default, or on the copy engines)
+    python bench.py --case gemm_dense|gemm_dense_nt|gemm_dense_tn|moe_fwd|moe_bwd|moe_bwd_8seq|delta_bf16|delta_bf16_dh64|delta_f32|decode|...
+                                                                                             (one kernel family, for profiler captures)
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \\
         bench.py --gpus N --steps K --warmup W
 
