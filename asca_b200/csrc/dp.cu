@@ -14,7 +14,9 @@
 //               reaches that block's expert products, so the gather runs under the forward.
 // NCCL is loaded at run time (dlopen) on the first asca_comm_* call: a single-GPU user of the library needs no NCCL
 // at all, and a process that already holds a copy (a framework's) shares it. No peer-memory loads and no multicast
-// loads of our own; NCCL moves the bytes.
+// loads of our own; NCCL moves the bytes -- or, as an option for the sharded tensors, the copy engines do
+// (asca_model_dp_peer_export / _open: peer buffers mapped through CUDA IPC, one cudaMemcpyAsync and one flag store per
+// chunk and peer, a bounded poll and a rank-ordered sum on the receiving side; see struct asca_dp).
 #include "model.cuh"
 
 #include <dlfcn.h>

@@ -1,6 +1,7 @@
 // bf16 GEMM on the 5th-generation tensor cores (tcgen05) for sm_100a.
 //
-// Persistent: two CTAs per SM walk the 128 x 128 f32 output tiles round-robin. Warp roles (192 threads):
+// Persistent: two CTAs per SM work through the 128 x 128 f32 output tiles, each claiming the next unclaimed tile when it
+// starts one (KP::dyn_ctr below; a fixed walk t, t + grid, ... with ASCA_GEMM_DYNAMIC=0). Warp roles (192 threads):
 //   warp 0      TMA producer: one thread streams 128x64 A and 64x128 B bf16 tiles (128-byte
 //               swizzle, plain non-multicast cp.async.bulk.tensor) through a 3-stage ring of
 //               mbarriers, running ahead across tile boundaries;
@@ -878,7 +879,7 @@ int launch(asca_ctx* ctx, const Args& a) {
                                                 : "gemm_tc_kernel (expert-grouped k)",
                  2.0 * rows_m * (double)a.N * rows_k);
     const int n_sm = ctx->sm_count > 0 ? ctx->sm_count : 148;
-    // persistent: the CTAs walk the tiles round-robin. Wide tiles for dense problems with a long k-loop and at least
+    // persistent: the CTAs claim tile after tile. Wide tiles for dense problems with a long k-loop and at least
     // two waves of tiles (measured: +10-15 % there; with k <= 2048 or expert-grouped rows the 128 KiB epilogue per
     // tile and the single stream per SM cost more than the wider instruction gains).
     // CTA pairs on 256 x 256 tiles: dense and expert-grouped products with at least one tile per pair of SMs
